@@ -1,0 +1,173 @@
+"""ctypes access to the reference's own CPU functions (oracle/_ref/libnnabla_ref.so).
+
+TEST INFRASTRUCTURE ONLY. The library is the reference's C++ runtime and
+hot-path functions compiled from the reference checkout by oracle/Makefile
+(target `ref`); this module calls them through the C ABI in
+oracle/ref_shim/ref_capi.cpp. It is used to pin the C restatement in
+oracle/, to generate tests/golden/ fixtures and as bench.py's timed CPU
+baseline. The product package never imports it.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_ref", "libnnabla_ref.so")
+
+
+class _Tensor(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("ndim", ctypes.c_int32),
+                ("shape", ctypes.c_int64 * 8)]
+
+
+_lib = None
+
+
+def available():
+    return os.path.exists(LIB_PATH)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.nbref_last_error.restype = ctypes.c_char_p
+        _lib.nbref_forward.restype = ctypes.c_int
+    return _lib
+
+
+def forward(op, scalars, ivecs, inputs, n_out=1, repeat=1):
+    """Run reference function `op` on the "cpu:float" context.
+
+    scalars: constructor scalars in order; ivecs: constructor vector<int>
+    arguments in order; inputs: list of float32 arrays (None entries are
+    dropped, mirroring optional trailing inputs such as bias).
+    Returns (outputs, inputs_after, forward_seconds). inputs_after holds the
+    input buffers after the call because several functions write them.
+    """
+    L = lib()
+    ins = [np.ascontiguousarray(a, dtype=np.float32).copy() for a in inputs if a is not None]
+    s = (ctypes.c_double * max(1, len(scalars)))(*[float(v) for v in scalars])
+    flat = [int(v) for vec in ivecs for v in vec]
+    iv = (ctypes.c_int32 * max(1, len(flat)))(*flat)
+    ivl = (ctypes.c_int32 * max(1, len(ivecs)))(*[len(v) for v in ivecs])
+    tin = (_Tensor * len(ins))()
+    for t, a in zip(tin, ins):
+        t.data = a.ctypes.data
+        t.ndim = a.ndim
+        for d, n in enumerate(a.shape):
+            t.shape[d] = n
+    tout = (_Tensor * n_out)()
+    secs = ctypes.c_double(0.0)
+
+    def call(mode):
+        rc = L.nbref_forward(op.encode(), s, len(scalars), iv, ivl, len(ivecs),
+                             tin, len(ins), tout, n_out, mode, repeat,
+                             ctypes.byref(secs))
+        if rc != 0:
+            raise RuntimeError(L.nbref_last_error().decode())
+
+    call(0)
+    outs = []
+    for t in tout:
+        shape = tuple(t.shape[d] for d in range(t.ndim))
+        a = np.empty(shape, dtype=np.float32)
+        t.data = a.ctypes.data
+        outs.append(a)
+    call(1)
+    return outs, ins, secs.value
+
+
+# Convenience wrappers named after the reference functions -------------------
+
+def fixed_point_quantize(x, sign=True, n=8, delta=2.0 ** -4, ste_fine_grained=True, repeat=1, timed=False):
+    o, _, t = forward("FixedPointQuantize", [sign, n, delta, ste_fine_grained], [], [x], repeat=repeat)
+    return (o[0], t) if timed else o[0]
+
+
+def pow2_quantize(x, sign=True, with_zero=True, n=8, m=1, ste_fine_grained=True, repeat=1, timed=False):
+    o, _, t = forward("Pow2Quantize", [sign, with_zero, n, m, ste_fine_grained], [], [x], repeat=repeat)
+    return (o[0], t) if timed else o[0]
+
+
+def min_max_quantize(x, qr_min, qr_max, ql_min, ql_max, decay=0.999, x_min_max=False, ema=False,
+                     ste_fine_grained=True, eps=0.01, repeat=1, timed=False):
+    """Returns (y, qr_min_after, qr_max_after[, seconds])."""
+    o, i, t = forward("MinMaxQuantize", [decay, x_min_max, ema, ste_fine_grained, eps], [],
+                      [x, qr_min, qr_max, ql_min, ql_max], repeat=repeat)
+    r = (o[0], i[1], i[2])
+    return r + (t,) if timed else r
+
+
+def sign(x, alpha=1.0):
+    return forward("Sign", [alpha], [], [x])[0][0]
+
+
+def binary_weight_affine(x, w, b=None, base_axis=1, quantize_zero_to=1.0, repeat=1, timed=False):
+    """Returns (y, wb, alpha[, seconds])."""
+    wb = np.zeros_like(w, dtype=np.float32)
+    alpha = np.zeros(int(np.prod(w.shape[1:])), dtype=np.float32)
+    o, i, t = forward("BinaryWeightAffine", [base_axis, quantize_zero_to], [], [x, w, wb, alpha, b], repeat=repeat)
+    r = (o[0], i[2], i[3])
+    return r + (t,) if timed else r
+
+
+def binary_connect_affine(x, w, b=None, base_axis=1, quantize_zero_to=1.0):
+    wb = np.zeros_like(w, dtype=np.float32)
+    o, i, _ = forward("BinaryConnectAffine", [base_axis, quantize_zero_to], [], [x, w, wb, b])
+    return o[0], i[2]
+
+
+def binary_weight_convolution(x, w, b=None, base_axis=1, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1,
+                              quantize_zero_to=1.0, repeat=1, timed=False):
+    wb = np.zeros_like(w, dtype=np.float32)
+    alpha = np.zeros(w.shape[0], dtype=np.float32)
+    o, i, t = forward("BinaryWeightConvolution", [base_axis, group, quantize_zero_to], [pad, stride, dilation],
+                      [x, w, wb, alpha, b], repeat=repeat)
+    r = (o[0], i[2], i[3])
+    return r + (t,) if timed else r
+
+
+def binary_connect_convolution(x, w, b=None, base_axis=1, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1,
+                               quantize_zero_to=1.0):
+    wb = np.zeros_like(w, dtype=np.float32)
+    o, i, _ = forward("BinaryConnectConvolution", [base_axis, group, quantize_zero_to], [pad, stride, dilation],
+                      [x, w, wb, b])
+    return o[0], i[2]
+
+
+def affine(x, w, b=None, base_axis=1, repeat=1, timed=False):
+    o, _, t = forward("Affine", [base_axis], [], [x, w, b], repeat=repeat)
+    return (o[0], t) if timed else o[0]
+
+
+def convolution(x, w, b=None, base_axis=1, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1, repeat=1, timed=False):
+    o, _, t = forward("Convolution", [base_axis, group, False], [pad, stride, dilation], [x, w, b], repeat=repeat)
+    return (o[0], t) if timed else o[0]
+
+
+def batch_normalization(x, beta, gamma, mean, var, axes=(1,), decay_rate=0.9, eps=1e-5, batch_stat=False):
+    o, _, _ = forward("BatchNormalization", [decay_rate, eps, batch_stat, False, False], [axes],
+                      [x, beta, gamma, mean, var])
+    return o[0]
+
+
+def relu(x):
+    return forward("ReLU", [False], [], [x])[0][0]
+
+
+def add2(a, b):
+    return forward("Add2", [False], [], [a, b])[0][0]
+
+
+def max_pooling(x, kernel, stride, ignore_border=True, pad=(0, 0)):
+    return forward("MaxPooling", [ignore_border, False], [kernel, stride, pad], [x])[0][0]
+
+
+def average_pooling(x, kernel, stride, ignore_border=True, pad=(0, 0), including_pad=True):
+    return forward("AveragePooling", [ignore_border, False, including_pad], [kernel, stride, pad], [x])[0][0]
+
+
+def global_average_pooling(x):
+    return forward("GlobalAveragePooling", [], [], [x])[0][0]
