@@ -1,0 +1,251 @@
+"""NumPy-level access to the CPU restatement in oracle/oracle_*.c.
+
+TEST INFRASTRUCTURE ONLY: the checker that the CUDA path is compared with.
+Only tests/, the smoke check and the benchmark's CPU-baseline leg import this
+module; the product package never does.
+
+Parity status: pinned against the reference's own compiled CPU functions
+(oracle/ref.py) and the fixtures in tests/golden/ — see the header of
+oracle_quant.c; the fp32 summation order of the contractions is unpinned
+(Eigen is not available), see oracle_contract.c.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liboracle.so")
+_lib = None
+
+_f32p = ctypes.POINTER(ctypes.c_float)
+_i64p = ctypes.POINTER(ctypes.c_int64)
+
+
+def build(force=False):
+    """Compile liboracle.so with the flags of oracle/Makefile (target `oracle`)."""
+    srcs = sorted(os.path.join(_HERE, f) for f in os.listdir(_HERE) if f.startswith("oracle_") and f.endswith(".c"))
+    if not force and os.path.exists(LIB_PATH) and all(
+            os.path.getmtime(LIB_PATH) >= os.path.getmtime(s) for s in srcs):
+        return LIB_PATH
+    subprocess.check_call(["gcc", "-O2", "-fPIC", "-shared", "-fno-fast-math", "-ffp-contract=off",
+                           "-o", LIB_PATH] + srcs + ["-lm"])
+    return LIB_PATH
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.oracle_min_max_quantize.restype = ctypes.c_int
+        _lib.oracle_convolution.restype = ctypes.c_int
+        _lib.oracle_pow2_thresholds.restype = ctypes.c_int
+        _lib.oracle_pool_out.restype = ctypes.c_int
+    return _lib
+
+
+def _f(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a):
+    return a.ctypes.data_as(_f32p) if a is not None else None
+
+
+def _shape(s):
+    return (ctypes.c_int64 * max(1, len(s)))(*[int(v) for v in s])
+
+
+def fixed_point_quantize(x, sign=True, n=8, delta=2.0 ** -4):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().oracle_fixed_point_quantize(_p(x), _p(y), ctypes.c_int64(x.size), int(sign), int(n),
+                                      ctypes.c_float(delta))
+    return y
+
+
+def pow2_quantize(x, sign=True, with_zero=True, n=8, m=1):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().oracle_pow2_quantize(_p(x), _p(y), ctypes.c_int64(x.size), int(sign), int(with_zero), int(n), int(m))
+    return y
+
+
+def pow2_constants(sign, with_zero, n, m):
+    a, b, c = ctypes.c_float(), ctypes.c_float(), ctypes.c_float()
+    lib().oracle_pow2_constants(int(sign), int(with_zero), int(n), int(m), ctypes.byref(a), ctypes.byref(b),
+                                ctypes.byref(c))
+    return a.value, b.value, c.value
+
+
+def pow2_thresholds():
+    """(table[254] of uint32 mantissa cuts for e = -126..127, n_non_monotone)."""
+    t = np.zeros(254, dtype=np.uint32)
+    bad = lib().oracle_pow2_thresholds(t.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32)))
+    return t, bad
+
+
+def min_max_quantize(x, qr_min, qr_max, ql_min, ql_max, decay=0.999, x_min_max=False, ema=False, eps=0.01):
+    """Returns (y, qr_min_after, qr_max_after, scale)."""
+    x = _f(x)
+    qr_min, qr_max = _f(qr_min).copy(), _f(qr_max).copy()
+    ql_min, ql_max = _f(ql_min), _f(ql_max)
+    qshape = qr_min.shape
+    if len(qshape) != x.ndim:
+        raise ValueError("q tensors must have the same ndim as x")
+    y = np.empty_like(x)
+    scale = np.empty_like(qr_min)
+    rc = lib().oracle_min_max_quantize(_p(x), _shape(x.shape), x.ndim, _p(qr_min), _p(qr_max), _p(ql_min),
+                                       _p(ql_max), _shape(qshape), ctypes.c_float(decay), int(x_min_max),
+                                       int(ema), ctypes.c_float(eps), _p(y), _p(scale))
+    if rc != 0:
+        raise ValueError("oracle_min_max_quantize: bad shapes")
+    return y, qr_min, qr_max, scale
+
+
+def sign(x, alpha=1.0):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().oracle_sign(_p(x), _p(y), ctypes.c_int64(x.size), ctypes.c_float(alpha))
+    return y
+
+
+def binarize_columns(w2d, quantize_zero_to=1.0):
+    """BinaryWeightAffine weight step: (wb, alpha[cols], scaled)."""
+    w = _f(w2d)
+    r, c = w.shape
+    wb, sc, al = np.empty_like(w), np.empty_like(w), np.empty(c, np.float32)
+    lib().oracle_binarize_columns(_p(w), ctypes.c_int64(r), ctypes.c_int64(c), ctypes.c_float(quantize_zero_to),
+                                  _p(wb), _p(al), _p(sc))
+    return wb, al, sc
+
+
+def binarize_rows(w2d, quantize_zero_to=1.0):
+    """BinaryWeightConvolution weight step: (wb, alpha[rows], scaled)."""
+    w = _f(w2d)
+    r, c = w.shape
+    wb, sc, al = np.empty_like(w), np.empty_like(w), np.empty(r, np.float32)
+    lib().oracle_binarize_rows(_p(w), ctypes.c_int64(r), ctypes.c_int64(c), ctypes.c_float(quantize_zero_to),
+                               _p(wb), _p(al), _p(sc))
+    return wb, al, sc
+
+
+def affine(x, w, b=None, base_axis=1, f64=False):
+    x, w = _f(x), _f(w)
+    M = int(np.prod(x.shape[:base_axis]))
+    K = x.size // M
+    N = w.size // w.shape[0]
+    if w.shape[0] != K:
+        raise ValueError("affine: size of input and weights mismatch")
+    b = _f(b).reshape(-1) if b is not None else None
+    out_shape = x.shape[:base_axis] + w.shape[1:]
+    if f64:
+        y = np.empty((M, N), np.float64)
+        lib().oracle_affine_f64(_p(x), _p(w), _p(b), ctypes.c_int64(M), ctypes.c_int64(K), ctypes.c_int64(N),
+                                y.ctypes.data_as(ctypes.POINTER(ctypes.c_double)))
+    else:
+        y = np.empty((M, N), np.float32)
+        lib().oracle_affine(_p(x), _p(w), _p(b), ctypes.c_int64(M), ctypes.c_int64(K), ctypes.c_int64(N), _p(y))
+    return y.reshape(out_shape)
+
+
+def conv_out_shape(xshape, wshape, pad, stride, dilation):
+    N, C, H, W = xshape
+    Ko, _, kh, kw = wshape
+    Ho = (H + 2 * pad[0] - (dilation[0] * (kh - 1) + 1)) // stride[0] + 1
+    Wo = (W + 2 * pad[1] - (dilation[1] * (kw - 1) + 1)) // stride[1] + 1
+    return (N, Ko, Ho, Wo)
+
+
+def convolution(x, w, b=None, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1, f64=False):
+    x, w = _f(x), _f(w)
+    N, C, H, W = x.shape
+    Ko, Cg, kh, kw = w.shape
+    oshape = conv_out_shape(x.shape, w.shape, pad, stride, dilation)
+    b = _f(b) if b is not None else None
+    y = np.empty(oshape, np.float64 if f64 else np.float32)
+    rc = lib().oracle_convolution(
+        _p(x), _p(w), _p(b), N, C, H, W, Ko, kh, kw, pad[0], pad[1], stride[0], stride[1], dilation[0],
+        dilation[1], group, None if f64 else _p(y), int(f64),
+        y.ctypes.data_as(ctypes.POINTER(ctypes.c_double)) if f64 else None)
+    if rc != 0:
+        raise ValueError("oracle_convolution: invalid configuration")
+    return y
+
+
+def binary_weight_affine(x, w, b=None, base_axis=1, quantize_zero_to=1.0):
+    """Returns (y, wb, alpha) like binary_weight_affine.cpp:75-122."""
+    w = _f(w)
+    w2 = w.reshape(w.shape[0], -1)
+    wb, al, sc = binarize_columns(w2, quantize_zero_to)
+    y = affine(x, sc.reshape(w.shape), b, base_axis)
+    return y, wb.reshape(w.shape), al
+
+
+def binary_connect_affine(x, w, b=None, base_axis=1, quantize_zero_to=1.0):
+    w = _f(w)
+    wb = sign(w, quantize_zero_to)
+    return affine(x, wb, b, base_axis), wb
+
+
+def binary_weight_convolution(x, w, b=None, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1,
+                              quantize_zero_to=1.0):
+    w = _f(w)
+    wb, al, sc = binarize_rows(w.reshape(w.shape[0], -1), quantize_zero_to)
+    y = convolution(x, sc.reshape(w.shape), b, pad, stride, dilation, group)
+    return y, wb.reshape(w.shape), al
+
+
+def binary_connect_convolution(x, w, b=None, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1,
+                               quantize_zero_to=1.0):
+    w = _f(w)
+    wb = sign(w, quantize_zero_to)
+    return convolution(x, wb, b, pad, stride, dilation, group), wb
+
+
+def batch_norm_inference(x, beta, gamma, mean, var, eps=1e-5):
+    x = _f(x)
+    N, C = x.shape[:2]
+    S = x.size // (N * C)
+    y = np.empty_like(x)
+    lib().oracle_batch_norm_inference(_p(x), _p(_f(beta).reshape(-1)), _p(_f(gamma).reshape(-1)),
+                                      _p(_f(mean).reshape(-1)), _p(_f(var).reshape(-1)), ctypes.c_int64(N),
+                                      ctypes.c_int64(C), ctypes.c_int64(S), ctypes.c_float(eps), _p(y))
+    return y
+
+
+def relu(x):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().oracle_relu(_p(x), _p(y), ctypes.c_int64(x.size))
+    return y
+
+
+def add2(a, b):
+    a, b = _f(a), _f(b)
+    y = np.empty_like(a)
+    lib().oracle_add2(_p(a), _p(b), _p(y), ctypes.c_int64(a.size))
+    return y
+
+
+def max_pooling(x, kernel, stride, ignore_border=True, pad=(0, 0)):
+    x = _f(x)
+    H, W = x.shape[-2:]
+    maps = x.size // (H * W)
+    Ho = lib().oracle_pool_out(H, kernel[0], stride[0], pad[0], int(ignore_border))
+    Wo = lib().oracle_pool_out(W, kernel[1], stride[1], pad[1], int(ignore_border))
+    y = np.empty(x.shape[:-2] + (Ho, Wo), np.float32)
+    lib().oracle_max_pooling(_p(x), ctypes.c_int64(maps), H, W, kernel[0], kernel[1], stride[0], stride[1], pad[0],
+                             pad[1], int(ignore_border), _p(y))
+    return y
+
+
+def global_average_pooling(x):
+    x = _f(x)
+    N, C = x.shape[:2]
+    S = x.size // (N * C)
+    y = np.empty((N, C, 1, 1), np.float32)
+    lib().oracle_global_average_pooling(_p(x), ctypes.c_int64(N * C), ctypes.c_int64(S), _p(y))
+    return y

@@ -1,0 +1,76 @@
+"""The C restatement against the committed golden vectors (produced by the
+reference's own CPU functions). Runs without the reference checkout."""
+import numpy as np
+import pytest
+
+import cases
+from golden_util import bits, golden, sha
+from oracle import oracle
+
+
+@pytest.mark.parametrize("i", range(len(cases.FXP_GRID)))
+def test_fxp(i):
+    g = golden()
+    sign, n, delta = g[f"fxp{i}/args"]
+    got = oracle.fixed_point_quantize(g[f"fxp{i}/x"], bool(sign), int(n), float(delta))
+    assert np.array_equal(bits(got), bits(g[f"fxp{i}/out"]))
+
+
+@pytest.mark.parametrize("i", range(len(cases.POW2_GRID) + 1))
+def test_pow2(i):
+    g = golden()
+    sign, wz, n, m = g[f"pow2_{i}/args"]
+    got = oracle.pow2_quantize(g["pow2/x"], bool(sign), bool(wz), int(n), int(m))
+    assert np.array_equal(bits(got), bits(g[f"pow2_{i}/out"]))
+
+
+@pytest.mark.parametrize("i", range(len(cases.MINMAX_GRID)))
+def test_minmax(i):
+    g = golden()
+    decay, xmm, ema, eps = g[f"minmax{i}/args"]
+    x, qmin, qmax, lmin, lmax = cases.minmax_inputs(tuple(g[f"minmax{i}/xshape"]), tuple(g[f"minmax{i}/qshape"]))
+    y, amin, amax, _ = oracle.min_max_quantize(x, qmin, qmax, lmin, lmax, float(decay), bool(xmm), bool(ema), float(eps))
+    assert np.array_equal(sha(y), g[f"minmax{i}/out_sha"])
+    assert np.array_equal(bits(amin), bits(g[f"minmax{i}/out_qr_min"]))
+    assert np.array_equal(bits(amax), bits(g[f"minmax{i}/out_qr_max"]))
+
+
+@pytest.mark.parametrize("i", range(len(cases.AFFINE_CASES)))
+@pytest.mark.parametrize("qzt", cases.QZT)
+def test_binary_affine(i, qzt):
+    g = golden()
+    xs, ws, ba = cases.AFFINE_CASES[i]
+    x, w, b = cases.affine_inputs(xs, ws, with_zeros=True)
+    y, wb, al = oracle.binary_weight_affine(x, w, b, ba, qzt)
+    k = f"bwa{i}_{int(qzt)}"
+    assert np.array_equal(bits(wb), bits(g[k + "/out_wb"]))
+    np.testing.assert_allclose(al, g[k + "/out_alpha"], rtol=1e-6)
+    assert cases.rel_rms(y, g[k + "/out_y"]) < 1e-6
+    y, wb = oracle.binary_connect_affine(x, w, b, ba, qzt)
+    k = f"bca{i}_{int(qzt)}"
+    assert np.array_equal(bits(wb), bits(g[k + "/out_wb"]))
+    assert cases.rel_rms(y, g[k + "/out_y"]) < 1e-6
+
+
+@pytest.mark.parametrize("i", range(len(cases.CONV_CASES)))
+def test_binary_convolution(i):
+    g = golden()
+    xs, ws, pad, stride, dil, grp = cases.CONV_CASES[i]
+    x, w, b = cases.conv_inputs(xs, ws, with_zeros=True)
+    y, wb, al = oracle.binary_weight_convolution(x, w, b, pad, stride, dil, grp, 1.0)
+    assert np.array_equal(bits(wb), bits(g[f"bwc{i}/out_wb"]))
+    np.testing.assert_allclose(al, g[f"bwc{i}/out_alpha"], rtol=1e-6)
+    assert cases.rel_rms(y, g[f"bwc{i}/out_y"]) < 1e-6
+    y, wb = oracle.binary_connect_convolution(x, w, b, pad, stride, dil, grp, 1.0)
+    assert np.array_equal(bits(wb), bits(g[f"bcc{i}/out_wb"]))
+    assert cases.rel_rms(y, g[f"bcc{i}/out_y"]) < 1e-6
+
+
+def test_baseline_config_digests():
+    g = golden()
+    rng = np.random.RandomState(0)
+    x = rng.uniform(-4, 4, 1 << 20).astype(np.float32)
+    one = lambda v: np.array([v], np.float32)
+    assert np.array_equal(sha(oracle.fixed_point_quantize(x, True, 8, 2.0 ** -4)), g["cfg2_fxp/sha"])
+    assert np.array_equal(sha(oracle.pow2_quantize(x, True, True, 8, 1)), g["cfg2_pow2/sha"])
+    assert np.array_equal(sha(oracle.min_max_quantize(x, one(-4), one(4), one(0), one(255))[0]), g["cfg2_minmax/sha"])
