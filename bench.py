@@ -1,0 +1,313 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Headline workload (BASELINE.json configs[1], the configuration the quantizer
+GB/s metric is quoted on): one step = FixedPointQuantize(sign, n=8, delta=2^-4),
+Pow2Quantize(sign, with_zero, n=8, m=1) and MinMaxQuantize(ql 0..255, given
+per-tensor range -4..4) each applied to an fp32 tensor of 2^30 elements
+~U(-4,4). Algorithmic traffic is 8 bytes per element per quantizer.
+
+Prints ONE JSON line (rank 0). With N > 1 (torchrun) every rank processes its
+own tensor: the path shards by elements with no collective (weak scaling).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BYTES_PER_ELEM = 8  # 4 read + 4 written, per quantizer
+QUANTIZERS = ("fixed_point_quantize", "pow2_quantize", "min_max_quantize")
+CPU_SAMPLE_LOG2 = 24
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--size-log2", type=int, default=30)
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_functions():
+    """(kind, {name: callable(x)->seconds}) — the reference's own compiled CPU
+    functions when oracle/_ref is present, else the C restatement."""
+    from oracle import ref
+    if ref.available():
+        one = lambda v: np.array([v], np.float32)
+        return "reference", {
+            "fixed_point_quantize": lambda x: ref.fixed_point_quantize(x, True, 8, 2.0 ** -4, timed=True)[1],
+            "pow2_quantize": lambda x: ref.pow2_quantize(x, True, True, 8, 1, timed=True)[1],
+            "min_max_quantize": lambda x: ref.min_max_quantize(x, one(-4), one(4), one(0), one(255), timed=True)[3],
+        }
+    from oracle import oracle
+
+    def timed(fn):
+        def run(x):
+            t0 = time.perf_counter()
+            fn(x)
+            return time.perf_counter() - t0
+        return run
+    return "port", {
+        "fixed_point_quantize": timed(lambda x: oracle.fixed_point_quantize(x, True, 8, 2.0 ** -4)),
+        "pow2_quantize": timed(lambda x: oracle.pow2_quantize(x, True, True, 8, 1)),
+        "min_max_quantize": timed(lambda x: oracle.min_max_quantize(x, [-4], [4], [0], [255])),
+    }
+
+
+def cpu_step(fns, slices):
+    """One bounded CPU step: every quantizer over every slice, one host thread
+    per slice (the reference functions are single-threaded; independent
+    function instances may run on separate threads). Returns wall seconds."""
+    def work(x):
+        for name in QUANTIZERS:
+            fns[name](x)
+    t0 = time.perf_counter()
+    ths = [threading.Thread(target=work, args=(s,)) for s in slices]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    return time.perf_counter() - t0
+
+
+def cpu_inputs(threads):
+    rng = np.random.RandomState(0)
+    n = 1 << CPU_SAMPLE_LOG2
+    x = rng.uniform(-4, 4, n).astype(np.float32)
+    per = n // threads
+    return [x[i * per:(i + 1) * per] for i in range(threads)], per * threads
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    kind, fns = cpu_functions()
+    threads = os.cpu_count() or 1
+    slices, n = cpu_inputs(threads)
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_step(fns, slices)
+    times = [cpu_step(fns, slices) for _ in range(args.steps)]
+    total = sum(times)
+    value = len(QUANTIZERS) * BYTES_PER_ELEM * n * args.steps / total / 1e9
+    sample = "each step: 3 quantizers over 2^%d elements split over %d host threads" % (CPU_SAMPLE_LOG2, threads)
+    line = {
+        "impl": "reference", "metric": "quantizer_GBps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: FixedPoint+Pow2+MinMax quantize, fp32 U(-4,4); CPU arm on a bounded "
+                               "sample of 2^%d elements per step" % CPU_SAMPLE_LOG2},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- GPU arm
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while
+    the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in out.splitlines():
+            p = [s.strip() for s in ln.split(",")]
+            if len(p) < 6:
+                continue
+            try:
+                sm.append(float(p[0]))
+                mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f), "measured"
+    except OSError:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def run_b200_arm(args):
+    import torch
+    import torch.distributed as dist
+    from nnabla_b200 import _capi as C
+    from nnabla_b200 import functions as F
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    C.call("nb200_check_device")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    n = 1 << args.size_log2
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    x = torch.rand(n, device="cuda", generator=gen) * 8 - 4
+    y = torch.empty_like(x)
+    one = lambda v: torch.tensor([v], device="cuda", dtype=torch.float32)
+    qr_min, qr_max, ql_min, ql_max = one(-4.0), one(4.0), one(0.0), one(255.0)
+
+    def step(events=None):
+        if events:
+            events[0].record()
+        F.fixed_point_quantize(x, True, 8, 2.0 ** -4, outputs=[y])
+        if events:
+            events[1].record()
+        F.pow2_quantize(x, True, True, 8, 1, outputs=[y])
+        if events:
+            events[2].record()
+        F.min_max_quantize(x, qr_min, qr_max, ql_min, ql_max, outputs=[y])
+        if events:
+            events[3].record()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for s in range(args.steps):
+        step(ev[s])
+    t_end.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    elapsed_ms = t_start.elapsed_time(t_end)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    per_kernel_ms = [statistics.mean(ev[s][k].elapsed_time(ev[s][k + 1]) for s in range(args.steps))
+                     for k in range(3)]
+
+    # ---- end to end through the host-buffer entry points -------------------
+    e2e = None
+    try:
+        hx = torch.empty(n, dtype=torch.float32, pin_memory=True)
+        hy = torch.empty(n, dtype=torch.float32, pin_memory=True)
+        hx.copy_(x)
+        hq = np.array([-4.0, 4.0, 0.0, 255.0], np.float32)
+
+        def e2e_step():
+            C.call("nb200_fixed_point_quantize_f32_host", C.ptr(hx), C.ptr(hy), C.size_t(n), 1, 8,
+                   C.c_float(2.0 ** -4))
+            C.call("nb200_pow2_quantize_f32_host", C.ptr(hx), C.ptr(hy), C.size_t(n), 1, 1, 8, 1)
+            C.call("nb200_min_max_quantize_f32_host", C.ptr(hx), C.size_t(n), C.ptr(hq[0:]), C.ptr(hq[1:]),
+                   C.ptr(hq[2:]), C.ptr(hq[3:]), C.c_float(0.01), C.ptr(hy))
+
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        e2e = {"value": world * 3 * BYTES_PER_ELEM * n * args.e2e_steps / e2e_s / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": 3 * 4 * n, "d2h_bytes_per_step": 3 * 4 * n, "steps": args.e2e_steps,
+               "api": "nb200_*_quantize_f32_host (pinned host buffers)"}
+        del hx, hy
+    except RuntimeError as exc:  # pinned allocation failure: report, do not fake
+        e2e = {"value": None, "unit": "GB/s", "error": str(exc)[:200]}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    value = world * 3 * BYTES_PER_ELEM * n * args.steps / (elapsed_ms / 1e3) / 1e9
+    k_dom = int(np.argmax(per_kernel_ms))
+    achieved = BYTES_PER_ELEM * n / (per_kernel_ms[k_dom] / 1e3) / 1e9
+    roofline = {"bound": "hbm", "kernel": QUANTIZERS[k_dom], "achieved": achieved, "peak": peaks["hbm_gbs"],
+                "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                "per_kernel_GBps": {QUANTIZERS[k]: BYTES_PER_ELEM * n / (per_kernel_ms[k] / 1e3) / 1e9
+                                    for k in range(3)}}
+    cpu_baseline = None
+    if not args.no_cpu_baseline:
+        kind, fns = cpu_functions()
+        slices, ncpu = cpu_inputs(1)
+        secs = {name: fns[name](slices[0]) for name in QUANTIZERS}
+        cpu_baseline = {"value": 3 * BYTES_PER_ELEM * ncpu / sum(secs.values()) / 1e9, "unit": "GB/s", "cores": 1,
+                        "kind": kind, "sample": "3 quantizers over 2^%d elements, 1 thread" % CPU_SAMPLE_LOG2,
+                        "per_function_GBps": {k: BYTES_PER_ELEM * ncpu / v / 1e9 for k, v in secs.items()}}
+    line = {
+        "metric": "quantizer_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: FixedPointQuantize(sign,n=8,delta=2^-4) + Pow2Quantize(sign,with_zero,"
+                               "n=8,m=1) + MinMaxQuantize(0..255, range -4..4) on fp32 U(-4,4), 2^%d elements per GPU"
+                               % args.size_log2,
+                   "elements_per_gpu": n, "l2": "inputs (4 GiB) larger than L2; no flush needed"},
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": 4 * args.steps,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_b200_arm(args)
+
+
+if __name__ == "__main__":
+    main()

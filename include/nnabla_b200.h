@@ -1,0 +1,127 @@
+/* nnabla_b200 — C ABI of the B200 (sm_100a) implementation of nnabla's
+ * quantized-layer forward path.
+ *
+ * nnabla has no C plugin ABI: a backend plugs in by registering C++ Function
+ * classes (include/nbla/function_registry.hpp:165-197) whose forward_impl is
+ * called by Function::forward (src/nbla/function.cpp:107-123). Each entry point
+ * below is the body of one such forward_impl with plain pointers and sizes, so
+ * that the nnabla extension classes (ext/ in this repository), the Python
+ * mirror (nnabla_b200/functions.py) and any other host can bind it without
+ * sharing C++ types. The comment on each entry names the reference code it
+ * replaces.
+ *
+ * Conventions
+ *  - Every function returns 0 on success; otherwise a non-zero NB200_E* code,
+ *    and nb200_last_error() returns a message for the calling thread. This is
+ *    the C form of the reference's NBLA_CHECK / NBLA_ERROR exceptions
+ *    (include/nbla/exception.hpp:42-82).
+ *  - Unless the name ends in _host, data pointers are DEVICE pointers on the
+ *    current CUDA device, fp32, densely packed, row-major. `stream` is a
+ *    cudaStream_t passed as void* (NULL = the legacy default stream). Calls are
+ *    asynchronous with respect to the host unless stated otherwise.
+ *  - _host variants take HOST pointers (pinned memory from nb200_malloc_host
+ *    runs fastest; pageable memory works), copy in, compute and copy out in
+ *    overlapped chunks, and return after the result is in the host buffer.
+ *  - Sizes are element counts (size_t / int64_t), never bytes, unless named
+ *    `bytes`.
+ */
+#ifndef NNABLA_B200_H_
+#define NNABLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NB200_OK 0
+#define NB200_EVALUE 1   /* bad argument (reference: error_code::value) */
+#define NB200_ECUDA 2    /* CUDA runtime/driver failure (error_code::target_specific) */
+#define NB200_EMEMORY 3  /* allocation failure (error_code::memory) */
+#define NB200_ENOTIMPL 4 /* configuration not supported (error_code::not_implemented) */
+#define NB200_EDEVICE 5  /* a bounded device-side wait gave up; the context stays usable */
+
+/* ---- runtime: what nnabla's backend layer needs from a device ------------- */
+
+/* Message of the last failure on this thread ("" if none). */
+const char *nb200_last_error(void);
+/* ABI version of this library (bumped on incompatible changes). */
+int nb200_abi_version(void);
+/* Replaces Cpu::get_device_count-style queries of an extension
+ * (python/src/nnabla_ext/cpu/__init__.py:17-45): number of CUDA devices. */
+int nb200_device_count(int *count);
+int nb200_set_device(int device);
+int nb200_get_device(int *device);
+/* Fails with NB200_ENOTIMPL unless the current device is compute capability
+ * 10.x: the kernels are built for sm_100a only and there is no fallback. */
+int nb200_check_device(void);
+/* Memory::alloc_impl / ~Memory of a device Memory class
+ * (include/nbla/memory/memory.hpp:285-312; CPU counterpart
+ * src/nbla/memory/cpu_memory.cpp:31-80). */
+int nb200_malloc(void **dev_ptr, size_t bytes);
+int nb200_free(void *dev_ptr);
+/* Pinned host memory for the _host entry points and for synchronizers. */
+int nb200_malloc_host(void **host_ptr, size_t bytes);
+int nb200_free_host(void *host_ptr);
+/* ArraySynchronizer bodies (include/nbla/array_registry.hpp:136-137): raw
+ * copies between a host array and a device array, asynchronous on `stream`. */
+int nb200_memcpy_h2d(void *dev_dst, const void *host_src, size_t bytes, void *stream);
+int nb200_memcpy_d2h(void *host_dst, const void *dev_src, size_t bytes, void *stream);
+int nb200_memcpy_d2d(void *dev_dst, const void *dev_src, size_t bytes, void *stream);
+/* Array::zero / Array::fill (include/nbla/array.hpp:128-140) for fp32 arrays. */
+int nb200_fill_f32(float *dev_ptr, size_t n, float value, void *stream);
+int nb200_stream_create(void **stream);
+int nb200_stream_destroy(void *stream);
+/* BackendBase::device_synchronize (include/nbla/backend_base.hpp:32-91). */
+int nb200_stream_synchronize(void *stream);
+int nb200_device_synchronize(void);
+
+/* ---- elementwise quantizers ------------------------------------------------ */
+
+/* FixedPointQuantize<float>::forward_impl
+ * (src/nbla/function/generic/fixed_point_quantize.cpp:45-66; limits :37-39).
+ * y[i] = max if x>max; min if x<min; else sgn(x)*float(int(|x|/delta + 0.5))*delta,
+ * bit-identical to the reference for every non-NaN input. Requires n > 0,
+ * delta > 0 and n - sign > 0 (the reference's setup checks). x == y allowed. */
+int nb200_fixed_point_quantize_f32(const float *x, float *y, size_t size, int sign, int n, float delta,
+                                   void *stream);
+/* Same, and additionally writes the integer code k (y = k*delta, |k| <= 127)
+ * as int8 to `codes` (size elements): the operand format of the int8
+ * tensor-core contraction. Requires n - sign <= 7. */
+int nb200_fixed_point_quantize_f32_codes(const float *x, float *y, int8_t *codes, size_t size, int sign, int n,
+                                         float delta, void *stream);
+int nb200_fixed_point_quantize_f32_host(const float *x, float *y, size_t size, int sign, int n, float delta);
+
+/* Pow2Quantize<float>::forward_impl
+ * (src/nbla/function/generic/pow2_quantize.cpp:47-82; constants :35-39).
+ * The reference evaluates powf(2, roundf(log2f(|x|))) with the host libm; this
+ * library derives, once per process and with the host libm, the mantissa cut
+ * per exponent at which that expression steps, and the kernel snaps with
+ * integer compares against that table — bit-identical for every non-NaN
+ * input, denormals included. */
+int nb200_pow2_quantize_f32(const float *x, float *y, size_t size, int sign, int with_zero, int n, int m,
+                            void *stream);
+int nb200_pow2_quantize_f32_host(const float *x, float *y, size_t size, int sign, int with_zero, int n, int m);
+
+/* MinMaxQuantize<float>::forward_impl
+ * (src/nbla/function/generic/min_max_quantize.cpp:129-223, nudge_range
+ * :352-361, nudge_qr_min_max :362-390). x has shape x_shape[0..ndim); qr_min,
+ * qr_max, ql_min, ql_max share q_shape[0..ndim) whose extents are 1 or equal
+ * to x's. Like the reference, the call UPDATES qr_min and qr_max in place
+ * (min/max of x or their moving average when x_min_max, then the eps nudge of
+ * qr_max). `scale` (q-sized, may be NULL) receives the scale the reference
+ * keeps for backward. Every fp32 operation rounds separately (no FMA), so y,
+ * qr_min and qr_max are bit-identical to the reference for non-NaN input. */
+int nb200_min_max_quantize_f32(const float *x, const int64_t *x_shape, int ndim, float *qr_min, float *qr_max,
+                               const float *ql_min, const float *ql_max, const int64_t *q_shape, float decay,
+                               int x_min_max, int ema, float eps, float *y, float *scale, void *stream);
+/* Host variant for per-tensor ranges with x_min_max == 0 (q tensors of one
+ * element each, host pointers; qr_max is updated by the eps nudge). */
+int nb200_min_max_quantize_f32_host(const float *x, size_t size, float *qr_min, float *qr_max, const float *ql_min,
+                                    const float *ql_max, float eps, float *y);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNABLA_B200_H_ */

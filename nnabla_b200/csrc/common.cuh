@@ -1,0 +1,55 @@
+// Shared host/device helpers of the nnabla_b200 library (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "nnabla_b200.h"
+
+namespace nb200 {
+
+// Records a message for nb200_last_error() on this thread and returns `code`.
+int fail(int code, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+void clear_error();
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+#define NB_CUDA(expr)                                                                              \
+  do {                                                                                             \
+    cudaError_t nb_e_ = (expr);                                                                    \
+    if (nb_e_ != cudaSuccess)                                                                      \
+      return ::nb200::fail(NB200_ECUDA, "%s: %s (%s:%d)", #expr, cudaGetErrorString(nb_e_),        \
+                           __FILE__, __LINE__);                                                    \
+  } while (0)
+
+#define NB_CHECK(cond, code, ...)                                                                  \
+  do {                                                                                             \
+    if (!(cond))                                                                                   \
+      return ::nb200::fail(code, __VA_ARGS__);                                                     \
+  } while (0)
+
+#define NB_TRY(expr)                                                                               \
+  do {                                                                                             \
+    int nb_rc_ = (expr);                                                                           \
+    if (nb_rc_ != NB200_OK)                                                                        \
+      return nb_rc_;                                                                               \
+  } while (0)
+
+// Launch-error check that does not synchronise.
+#define NB_LAUNCH_CHECK() NB_CUDA(cudaGetLastError())
+
+// Streaming (evict-first) 128-bit global accesses for data touched once.
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
+
+// Host-buffer pipeline shared by the _host entry points: copies `n` floats
+// from hx to the device in chunks, runs `launch(dx, dy, count, offset, stream)`
+// on each chunk and copies the result to hy, overlapping the three stages
+// across chunks. Returns after hy is complete.
+typedef int (*chunk_fn)(const float *dx, float *dy, size_t count, size_t offset, cudaStream_t st, void *user);
+int host_pipeline(const float *hx, float *hy, size_t n, chunk_fn fn, void *user);
+
+} // namespace nb200
