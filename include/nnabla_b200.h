@@ -121,6 +121,50 @@ int nb200_min_max_quantize_f32(const float *x, const int64_t *x_shape, int ndim,
 int nb200_min_max_quantize_f32_host(const float *x, size_t size, float *qr_min, float *qr_max, const float *ql_min,
                                     const float *ql_max, float eps, float *y);
 
+/* ---- binary-weight and fixed-point affine layers ----------------------------- */
+
+/* Device-side waits in the contraction kernels are time-bounded. A wait that
+ * gives up stores a non-zero code in a per-device status word and the kernel
+ * returns (its output is then incomplete). This call synchronises `stream`,
+ * returns the word in *code (0 = no wait ever gave up) and clears it. */
+int nb200_take_device_status(int *code, void *stream);
+
+/* BinaryWeightAffine<float>::forward_impl
+ * (src/nbla/function/generic/binary_weight_affine.cpp:74-122).
+ * x [rows, w_row], w [w_row, w_col] (the reference's 2-D view of N-D weights,
+ * :57-59), bias [w_col] or NULL. WRITES wb = sign(w; quantize_zero_to)
+ * [w_row, w_col] and alpha[c] = (sum_r |w[r,c]|) * float(1/w_row) [w_col],
+ * like the reference writes inputs[2] and inputs[3]; y [rows, w_col] =
+ * (x . wb) * alpha + bias. x is split into three bf16 pieces whose products
+ * with the +-1 weights are exact; accumulation is fp32 in tensor memory. */
+int nb200_binary_weight_affine_f32(const float *x, const float *w, float *wb, float *alpha, const float *bias,
+                                   float *y, int64_t rows, int64_t w_row, int64_t w_col, float quantize_zero_to,
+                                   void *stream);
+/* BinaryConnectAffine<float>::forward_impl
+ * (src/nbla/function/generic/binary_connect_affine.cpp:59-71): as above
+ * without alpha. */
+int nb200_binary_connect_affine_f32(const float *x, const float *w, float *wb, const float *bias, float *y,
+                                    int64_t rows, int64_t w_row, int64_t w_col, float quantize_zero_to,
+                                    void *stream);
+/* Affine<float>::forward_impl (src/nbla/function/generic/affine.cpp:80-96)
+ * for operands that are outputs of FixedPointQuantize with at most 8 bits:
+ * xq [rows, w_row] holds multiples of delta_x, wq [w_row, w_col] multiples of
+ * delta_w (|code| <= 127). The product runs on the int8 tensor-core path with
+ * int32 accumulation; y = float(acc) * (delta_x * delta_w) + bias, which
+ * equals the reference's fp32 result whenever that is itself exact. */
+int nb200_affine_fxp8_f32(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias, float *y,
+                          int64_t rows, int64_t w_row, int64_t w_col, void *stream);
+/* Same contraction from the int8 codes that
+ * nb200_fixed_point_quantize_f32_codes wrote (x_codes [rows, w_row],
+ * w_codes [w_row, w_col]). */
+int nb200_affine_codes_i8_f32(const int8_t *x_codes, const int8_t *w_codes, float delta_x, float delta_w,
+                              const float *bias, float *y, int64_t rows, int64_t w_row, int64_t w_col, void *stream);
+/* Affine<float>::forward_impl (affine.cpp:80-96) for arbitrary fp32 operands:
+ * both are split into bf16 pieces and the six leading piece products are
+ * accumulated in fp32 (error of the order of fp32 rounding). */
+int nb200_affine_f32(const float *x, const float *w, const float *bias, float *y, int64_t rows, int64_t w_row,
+                     int64_t w_col, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,316 @@
+// Host side of the tcgen05 contractions: tensor-map encoding, kernel
+// selection, and the C-ABI entry points for the affine layers.
+#include <cstring>
+#include <mutex>
+
+#include "gemm.cuh"
+#include "prepare.cuh"
+
+namespace nb200 {
+
+// ---- driver entry point for tensor-map encoding (no link against libcuda) --
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int get_encode_fn(EncodeTiledFn *out) {
+  static std::mutex m;
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(m);
+  if (fn == nullptr) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    NB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    NB_CHECK(q == cudaDriverEntryPointSuccess && p != nullptr, NB200_ECUDA,
+             "cuTensorMapEncodeTiled is not available from this driver");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  *out = fn;
+  return NB200_OK;
+}
+
+// dtype_code: 0 = bf16, 1 = uint8/int8 bytes
+int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, const uint64_t *dims,
+                 const uint64_t *strides_bytes, const uint32_t *box, const uint32_t *elem_strides) {
+  EncodeTiledFn fn;
+  NB_TRY(get_encode_fn(&fn));
+  NB_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, NB200_EVALUE, "tensor-map base must be 16-byte aligned");
+  for (int i = 0; i < rank - 1; ++i)
+    NB_CHECK(strides_bytes[i] % 16 == 0, NB200_EVALUE, "tensor-map stride %d (%llu bytes) is not a multiple of 16", i,
+             (unsigned long long)strides_bytes[i]);
+  cuuint64_t d[5], s[5];
+  cuuint32_t b[5], e[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    e[i] = elem_strides ? elem_strides[i] : 1;
+    if (i < rank - 1)
+      s[i] = strides_bytes[i];
+  }
+  const CUresult r = fn(map, dtype_code == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                        (cuuint32_t)rank, const_cast<void *>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  NB_CHECK(r == CUDA_SUCCESS, NB200_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return NB200_OK;
+}
+
+int make_operand_map(CUtensorMap *map, const void *base, bool int8, int64_t k_extent, int64_t pitch_elems,
+                     int64_t rows, int planes, int box_rows) {
+  const uint64_t es = int8 ? 1 : 2;
+  const uint64_t dims[3] = {(uint64_t)k_extent, (uint64_t)rows, (uint64_t)planes};
+  const uint64_t strides[2] = {(uint64_t)pitch_elems * es, (uint64_t)pitch_elems * es * (uint64_t)rows};
+  const uint32_t box[3] = {(uint32_t)(kRowBytes / es), (uint32_t)box_rows, 1};
+  return encode_tiled(map, int8 ? 1 : 0, 3, base, dims, strides, box, nullptr);
+}
+
+// ---- per-device status word written by kernels whose bounded waits gave up --
+int device_status_word(int **status) {
+  static std::mutex m;
+  static int *words[64];
+  int dev = 0;
+  NB_CUDA(cudaGetDevice(&dev));
+  NB_CHECK(dev >= 0 && dev < 64, NB200_EVALUE, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(m);
+  if (words[dev] == nullptr) {
+    NB_CUDA(cudaMalloc(&words[dev], sizeof(int)));
+    NB_CUDA(cudaMemset(words[dev], 0, sizeof(int)));
+  }
+  *status = words[dev];
+  return NB200_OK;
+}
+
+// ---- launch -----------------------------------------------------------------
+template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkip>
+static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, int M, int N, int k_blocks,
+                       const GemmEpilogue &ep, cudaStream_t st) {
+  auto kernel = gemm_tcgen05_kernel<kInt8, PA, PB, BN, STAGES, kSkip, PlainBLoader>;
+  constexpr size_t smem = gemm_smem_bytes<kInt8, PA, PB, BN, STAGES>();
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  static bool configured[64];
+  int dev = 0;
+  NB_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    NB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev & 63] = true;
+  }
+  GemmShape shape;
+  shape.M = M;
+  shape.N = N;
+  shape.k_blocks = k_blocks;
+  shape.m_tiles = (M + kTileM - 1) / kTileM;
+  shape.n_tiles = (N + BN - 1) / BN;
+  int *status = nullptr;
+  NB_TRY(device_status_word(&status));
+  const int tiles = shape.m_tiles * shape.n_tiles;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kernel<<<grid, kGemmThreads, smem, st>>>(ma, mb, shape, ep, PlainBLoader(), status);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+// A: [planes_a][M][pitch_a], B: [planes_b][N][pitch_b], both K-major.
+int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch_a, const void *B, int64_t pitch_b,
+             int M, int N, int K, const GemmEpilogue &ep, cudaStream_t st) {
+  NB_CHECK(M > 0 && N > 0 && K > 0, NB200_EVALUE, "empty contraction (M=%d N=%d K=%d)", M, N, K);
+  const int epb = int8 ? 128 : 64;
+  const int k_blocks = (K + epb - 1) / epb;
+  const int m_tiles = (M + kTileM - 1) / kTileM;
+  // Narrower N tiles when wide ones would leave most SMs idle.
+  const bool narrow = (int64_t)m_tiles * ((N + 127) / 128) < sm_count();
+  CUtensorMap ma, mb;
+  NB_TRY(make_operand_map(&ma, A, int8, K, pitch_a, M, planes_a, kTileM));
+  if (int8) {
+    NB_CHECK(planes_a == 1 && planes_b == 1, NB200_EVALUE, "int8 operands have one plane");
+    const bool wide = (int64_t)m_tiles * ((N + 255) / 256) >= sm_count();
+    if (wide) {
+      NB_TRY(make_operand_map(&mb, B, true, K, pitch_b, N, 1, 256));
+      return launch_gemm<true, 1, 1, 256, 4, false>(ma, mb, M, N, k_blocks, ep, st);
+    }
+    if (!narrow) {
+      NB_TRY(make_operand_map(&mb, B, true, K, pitch_b, N, 1, 128));
+      return launch_gemm<true, 1, 1, 128, 6, false>(ma, mb, M, N, k_blocks, ep, st);
+    }
+    NB_TRY(make_operand_map(&mb, B, true, K, pitch_b, N, 1, 64));
+    return launch_gemm<true, 1, 1, 64, 8, false>(ma, mb, M, N, k_blocks, ep, st);
+  }
+  if (planes_a == 3 && planes_b == 1) {
+    if (!narrow) {
+      NB_TRY(make_operand_map(&mb, B, false, K, pitch_b, N, 1, 128));
+      return launch_gemm<false, 3, 1, 128, 3, false>(ma, mb, M, N, k_blocks, ep, st);
+    }
+    NB_TRY(make_operand_map(&mb, B, false, K, pitch_b, N, 1, 64));
+    return launch_gemm<false, 3, 1, 64, 3, false>(ma, mb, M, N, k_blocks, ep, st);
+  }
+  if (planes_a == 3 && planes_b == 3) {
+    NB_TRY(make_operand_map(&mb, B, false, K, pitch_b, N, 3, 64));
+    return launch_gemm<false, 3, 3, 64, 3, true>(ma, mb, M, N, k_blocks, ep, st);
+  }
+  return fail(NB200_ENOTIMPL, "no kernel for %d x %d operand planes", planes_a, planes_b);
+}
+
+static inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+static bool bf16_exact(float v) {
+  uint32_t b;
+  std::memcpy(&b, &v, 4);
+  return (b & 0xffffu) == 0;
+}
+
+struct AsyncScratch {
+  void *p = nullptr;
+  cudaStream_t st;
+  explicit AsyncScratch(cudaStream_t s) : st(s) {}
+  int alloc(size_t bytes) {
+    NB_CUDA(cudaMallocAsync(&p, bytes, st));
+    return NB200_OK;
+  }
+  ~AsyncScratch() {
+    if (p)
+      cudaFreeAsync(p, st);
+  }
+};
+
+// Shared body of BinaryWeightAffine / BinaryConnectAffine forward.
+static int binary_affine(const float *x, const float *w, float *wb, float *alpha, const float *bias, float *y,
+                         int64_t M, int64_t K, int64_t N, float zero_to, cudaStream_t st) {
+  NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand (M=%lld K=%lld N=%lld)", (long long)M, (long long)K,
+           (long long)N);
+  NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
+  NB_CHECK(x && w && wb && y, NB200_EVALUE, "null data pointer");
+  NB_CHECK(bf16_exact(zero_to), NB200_ENOTIMPL,
+           "quantize_zero_to = %g is not representable in bf16; the exact tensor-core path needs it to be", zero_to);
+  const int64_t Kp = round_up(K, 64);
+  const size_t planes_bytes = (size_t)3 * M * Kp * 2;
+  const size_t side_bytes = (size_t)N * Kp * 2;
+  const size_t partial_bytes = alpha ? (size_t)((K + 63) / 64) * N * 4 : 0;
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc(round_up(planes_bytes, 256) + round_up(side_bytes, 256) + partial_bytes));
+  uint8_t *base = static_cast<uint8_t *>(scratch.p);
+  void *planes = base;
+  void *side = base + round_up(planes_bytes, 256);
+  float *partial = reinterpret_cast<float *>(base + round_up(planes_bytes, 256) + round_up(side_bytes, 256));
+  NB_TRY(binarize_columns(w, (int)K, (int)N, zero_to, wb, alpha, side, Kp, false, partial, st));
+  NB_TRY(split_rows_bf16(x, M, (int)K, Kp, 3, planes, st));
+  GemmEpilogue ep{};
+  ep.y = y;
+  ep.ldy = N;
+  ep.scale = 1.0f;
+  ep.col_scale = alpha;
+  ep.col_bias = bias;
+  return run_gemm(false, 3, 1, planes, Kp, side, Kp, (int)M, (int)N, (int)K, ep, st);
+}
+
+} // namespace nb200
+
+using namespace nb200;
+
+extern "C" {
+
+int nb200_take_device_status(int *code, void *stream) {
+  NB_CHECK(code != nullptr, NB200_EVALUE, "code is NULL");
+  int *word = nullptr;
+  NB_TRY(device_status_word(&word));
+  NB_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  NB_CUDA(cudaMemcpy(code, word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*code != 0)
+    NB_CUDA(cudaMemset(word, 0, sizeof(int)));
+  return NB200_OK;
+}
+
+int nb200_binary_weight_affine_f32(const float *x, const float *w, float *wb, float *alpha, const float *bias,
+                                   float *y, int64_t rows, int64_t w_row, int64_t w_col, float quantize_zero_to,
+                                   void *stream) {
+  NB_CHECK(alpha != nullptr, NB200_EVALUE, "alpha is NULL");
+  return binary_affine(x, w, wb, alpha, bias, y, rows, w_row, w_col, quantize_zero_to, as_stream(stream));
+}
+
+int nb200_binary_connect_affine_f32(const float *x, const float *w, float *wb, const float *bias, float *y,
+                                    int64_t rows, int64_t w_row, int64_t w_col, float quantize_zero_to,
+                                    void *stream) {
+  return binary_affine(x, w, wb, nullptr, bias, y, rows, w_row, w_col, quantize_zero_to, as_stream(stream));
+}
+
+int nb200_affine_codes_i8_f32(const int8_t *x_codes, const int8_t *w_codes, float delta_x, float delta_w,
+                              const float *bias, float *y, int64_t rows, int64_t w_row, int64_t w_col,
+                              void *stream) {
+  const int64_t M = rows, K = w_row, N = w_col;
+  NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand");
+  NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
+  NB_CHECK(x_codes && w_codes && y, NB200_EVALUE, "null data pointer");
+  // |acc| <= K * 127 * 127 must fit int32
+  NB_CHECK(K <= 133000, NB200_ENOTIMPL, "K = %lld could overflow the int32 accumulator", (long long)K);
+  cudaStream_t st = as_stream(stream);
+  const int64_t Kp = round_up(K, 128);
+  const bool x_direct = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(x_codes) & 15) == 0);
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc((size_t)N * Kp + (x_direct ? 0 : (size_t)M * Kp)));
+  int8_t *wt = static_cast<int8_t *>(scratch.p);
+  NB_TRY(transpose_i8(w_codes, (int)K, (int)N, wt, Kp, st));
+  const int8_t *xa = x_codes;
+  int64_t pitch_a = K;
+  if (!x_direct) {
+    int8_t *xc = wt + (size_t)N * Kp;
+    NB_CUDA(cudaMemcpy2DAsync(xc, (size_t)Kp, x_codes, (size_t)K, (size_t)K, (size_t)M, cudaMemcpyDeviceToDevice, st));
+    xa = xc;
+    pitch_a = Kp;
+  }
+  GemmEpilogue ep{};
+  ep.y = y;
+  ep.ldy = N;
+  ep.scale = delta_x * delta_w;
+  ep.col_bias = bias;
+  return run_gemm(true, 1, 1, xa, pitch_a, wt, Kp, (int)M, (int)N, (int)K, ep, st);
+}
+
+int nb200_affine_fxp8_f32(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias, float *y,
+                          int64_t rows, int64_t w_row, int64_t w_col, void *stream) {
+  const int64_t M = rows, K = w_row, N = w_col;
+  NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand");
+  NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
+  NB_CHECK(xq && wq && y, NB200_EVALUE, "null data pointer");
+  NB_CHECK(delta_x > 0.f && delta_w > 0.f, NB200_EVALUE, "step sizes must be positive");
+  NB_CHECK(K <= 133000, NB200_ENOTIMPL, "K = %lld could overflow the int32 accumulator", (long long)K);
+  cudaStream_t st = as_stream(stream);
+  const int64_t Kp = round_up(K, 128);
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc((size_t)(M + N) * Kp + (size_t)K * N));
+  int8_t *xc = static_cast<int8_t *>(scratch.p);
+  int8_t *wt = xc + (size_t)M * Kp;
+  int8_t *wc = wt + (size_t)N * Kp;
+  NB_TRY(codes_rows_i8(xq, M, (int)K, Kp, delta_x, xc, st));
+  NB_TRY(codes_rows_i8(wq, K, (int)N, N, delta_w, wc, st));
+  NB_TRY(transpose_i8(wc, (int)K, (int)N, wt, Kp, st));
+  GemmEpilogue ep{};
+  ep.y = y;
+  ep.ldy = N;
+  ep.scale = delta_x * delta_w;
+  ep.col_bias = bias;
+  return run_gemm(true, 1, 1, xc, Kp, wt, Kp, (int)M, (int)N, (int)K, ep, st);
+}
+
+int nb200_affine_f32(const float *x, const float *w, const float *bias, float *y, int64_t rows, int64_t w_row,
+                     int64_t w_col, void *stream) {
+  const int64_t M = rows, K = w_row, N = w_col;
+  NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand");
+  NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
+  NB_CHECK(x && w && y, NB200_EVALUE, "null data pointer");
+  cudaStream_t st = as_stream(stream);
+  const int64_t Kp = round_up(K, 64);
+  // w [K, N] is transposed through a fp32 staging pass into [N][K] planes.
+  AsyncScratch scratch(st);
+  const size_t xa = round_up((size_t)3 * M * Kp * 2, 256), wa = round_up((size_t)3 * N * Kp * 2, 256);
+  NB_TRY(scratch.alloc(xa + wa + (size_t)N * K * 4));
+  uint8_t *base = static_cast<uint8_t *>(scratch.p);
+  float *wt32 = reinterpret_cast<float *>(base + xa + wa);
+  NB_TRY(transpose_f32(w, (int)K, (int)N, wt32, st));
+  NB_TRY(split_rows_bf16(x, M, (int)K, Kp, 3, base, st));
+  NB_TRY(split_rows_bf16(wt32, N, (int)K, Kp, 3, base + xa, st));
+  GemmEpilogue ep{};
+  ep.y = y;
+  ep.ldy = N;
+  ep.scale = 1.0f;
+  ep.col_bias = bias;
+  return run_gemm(false, 3, 3, base, Kp, base + xa, Kp, (int)M, (int)N, (int)K, ep, st);
+}
+}

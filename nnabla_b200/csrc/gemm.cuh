@@ -1,0 +1,310 @@
+// Persistent, warp-specialised tcgen05 contraction kernel for sm_100a.
+//
+//   D[M, N] = sum over planes (pa, pb) of A_pa[M, K] * B_pb[N, K]^T
+//   y       = D * (scale * row_scale[m] * col_scale[n]) + row_bias[m] + col_bias[n]
+//
+// Both operands are K-major side-band tensors (bf16 or int8) that the prepare
+// kernels write; several "planes" of one operand are the bf16 pieces of an
+// fp32 tensor (x = hi + mid + lo), all multiplied against the same tile of the
+// other operand and accumulated into one fp32 TMEM accumulator, which makes
+// products with +-1 (or small-integer) weights exact. int8 operands accumulate
+// in int32.
+//
+// One CTA per SM, static round-robin over output tiles. Warp 0 feeds a
+// multi-stage shared-memory ring with TMA tiled loads (128-byte swizzle),
+// warp 1 issues tcgen05.mma from one elected thread and owns the TMEM
+// allocation, warps 2-5 drain the double-buffered TMEM accumulator with
+// tcgen05.ld and write y. Every mbarrier wait is time-bounded; a wait that
+// gives up stores a code in *status, raises the CTA's abort flag and all
+// roles fall through to the common teardown (TMEM is always freed).
+//
+// The B operand is fetched by a loader policy so that the same kernel serves
+// plain GEMM (2-D tiles of a [N, K] matrix) and implicit-GEMM convolution
+// (boxes of an NHWC activation tensor shifted by the filter tap).
+#pragma once
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace nb200 {
+
+constexpr int kGemmThreads = 192; // 6 warps: TMA, MMA, 4 x epilogue
+constexpr int kTileM = 128;
+constexpr int kRowBytes = 128; // one swizzle-atom row: 64 bf16 or 128 int8 along K
+
+// Status codes written by a wait that gave up (low byte = role).
+constexpr int kStatusProducerTimeout = 0x101;
+constexpr int kStatusMmaTimeout = 0x102;
+constexpr int kStatusEpilogueTimeout = 0x103;
+
+struct GemmEpilogue {
+  float *y;
+  int64_t ldy;            // elements between consecutive rows of y
+  int64_t y_batch_stride; // conv: elements between images (unused for GEMM)
+  const float *row_scale, *col_scale, *row_bias, *col_bias;
+  float scale;
+};
+
+struct GemmShape {
+  int M, N;     // logical extents of D
+  int k_blocks; // number of 128-byte K blocks
+  int m_tiles, n_tiles;
+};
+
+// Loader for a plain [N, K] K-major B operand: 3-D map (K, N, plane).
+struct PlainBLoader {
+  __device__ __forceinline__ void load(const CUtensorMap *map, void *dst, uint64_t *bar, int kb, int n0, int plane,
+                                       int k_elems_per_block) const {
+    ptx::tma_load_3d(dst, map, bar, kb * k_elems_per_block, n0, plane);
+  }
+};
+
+template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkipSmallPairs, typename BLoader>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        GemmShape shape, GemmEpilogue ep, BLoader bload, int *status) {
+  constexpr int kElemsPerBlock = kInt8 ? 128 : 64; // K elements per 128-byte row
+  constexpr int kUmmaK = kInt8 ? 32 : 16;          // K elements per MMA (32 bytes)
+  constexpr int kMmasPerBlock = kElemsPerBlock / kUmmaK;
+  constexpr uint32_t kABytes = kTileM * kRowBytes;
+  constexpr uint32_t kBBytes = BN * kRowBytes;
+  constexpr uint32_t kStageBytes = PA * kABytes + PB * kBBytes;
+  constexpr uint32_t kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
+  constexpr uint32_t kIdesc = ptx::make_idesc(kInt8 ? 2u : 1u, 1u, kTileM, BN); // S8 and BF16 both encode as 1
+
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle atoms.
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * kStageBytes);
+  uint64_t *full_bar = bars;
+  uint64_t *empty_bar = bars + STAGES;
+  uint64_t *tmem_full = bars + 2 * STAGES;
+  uint64_t *tmem_empty = bars + 2 * STAGES + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = shape.m_tiles * shape.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar + s, 1);
+      ptx::mbar_init(empty_bar + s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(tmem_full + b, 1);
+      ptx::mbar_init(tmem_empty + b, 4);
+    }
+    *abort_flag = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (ptx::elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % shape.m_tiles) * kTileM;
+        const int n0 = (tile / shape.m_tiles) * BN;
+        for (int kb = 0; kb < shape.k_blocks; ++kb) {
+          if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1u, abort_flag)) {
+            if (*abort_flag == 0)
+              atomicCAS(status, 0, kStatusProducerTimeout);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t *st = smem + stage * kStageBytes;
+          ptx::mbar_expect_tx(full_bar + stage, kStageBytes);
+#pragma unroll
+          for (int pa = 0; pa < PA; ++pa)
+            ptx::tma_load_3d(st + pa * kABytes, &map_a, full_bar + stage, kb * kElemsPerBlock, m0, pa);
+#pragma unroll
+          for (int pb = 0; pb < PB; ++pb)
+            bload.load(&map_b, st + PA * kABytes + pb * kBBytes, full_bar + stage, kb, n0, pb, kElemsPerBlock);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (ptx::elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
+        if (!ptx::mbar_wait(tmem_empty + buf, buf_phase ^ 1u, abort_flag)) {
+          if (*abort_flag == 0)
+            atomicCAS(status, 0, kStatusMmaTimeout);
+          *abort_flag = 1;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        uint32_t accumulate = 0;
+        for (int kb = 0; kb < shape.k_blocks; ++kb) {
+          if (!ptx::mbar_wait(full_bar + stage, phase, abort_flag)) {
+            if (*abort_flag == 0)
+              atomicCAS(status, 0, kStatusMmaTimeout);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t st = ptx::smem_u32(smem + stage * kStageBytes);
+#pragma unroll
+          for (int pa = 0; pa < PA; ++pa) {
+#pragma unroll
+            for (int pb = 0; pb < PB; ++pb) {
+              // With both operands split, pieces whose product is below fp32
+              // resolution of the leading term (pa + pb > 2) are skipped.
+              if (kSkipSmallPairs && pa + pb > 2)
+                continue;
+              const uint64_t adesc = ptx::smem_desc_k_sw128(st + pa * kABytes);
+              const uint64_t bdesc = ptx::smem_desc_k_sw128(st + PA * kABytes + pb * kBBytes);
+#pragma unroll
+              for (int k = 0; k < kMmasPerBlock; ++k) {
+                // advancing 32 bytes along K inside the swizzle atom = +2 in the encoded address
+                if (kInt8)
+                  ptx::mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                else
+                  ptx::mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                accumulate = 1;
+              }
+            }
+          }
+          ptx::mma_commit(empty_bar + stage); // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok)
+          ptx::mma_commit(tmem_full + buf);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3; // TMEM lanes [32*quarter, 32*quarter + 32) are visible to this warp
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
+      const int m0 = (tile % shape.m_tiles) * kTileM;
+      const int n0 = (tile / shape.m_tiles) * BN;
+      if (!ptx::mbar_wait(tmem_full + buf, buf_phase, abort_flag)) {
+        if (*abort_flag == 0)
+          atomicCAS(status, 0, kStatusEpilogueTimeout);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < shape.M;
+      const float rs = (ep.row_scale && row_ok) ? ep.row_scale[row] * ep.scale : ep.scale;
+      const float rb = (ep.row_bias && row_ok) ? ep.row_bias[row] : 0.0f;
+      float *yrow = ep.y + (int64_t)row * ep.ldy;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        ptx::tmem_ld_wait();
+        if (row_ok) {
+          const int col0 = n0 + c0;
+          if (col0 + 32 <= shape.N && ((reinterpret_cast<uintptr_t>(yrow + col0) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float o[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const float acc = kInt8 ? (float)(int)r[j + t] : __uint_as_float(r[j + t]);
+                const float s = ep.col_scale ? __fmul_rn(rs, ep.col_scale[col0 + j + t]) : rs;
+                float v = __fmul_rn(acc, s);
+                if (ep.row_bias)
+                  v = __fadd_rn(v, rb);
+                if (ep.col_bias)
+                  v = __fadd_rn(v, ep.col_bias[col0 + j + t]);
+                o[t] = v;
+              }
+              *reinterpret_cast<float4 *>(yrow + col0 + j) = make_float4(o[0], o[1], o[2], o[3]);
+            }
+          } else {
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              if (col < shape.N) {
+                const float acc = kInt8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+                const float s = ep.col_scale ? __fmul_rn(rs, ep.col_scale[col]) : rs;
+                float v = __fmul_rn(acc, s);
+                if (ep.row_bias)
+                  v = __fadd_rn(v, rb);
+                if (ep.col_bias)
+                  v = __fadd_rn(v, ep.col_bias[col]);
+                yrow[col] = v;
+              }
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        ptx::mbar_arrive(tmem_empty + buf);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // Give copies that may still be in flight time to land before the shared
+    // memory and TMEM of this CTA are released.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull)
+      __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <bool kInt8, int PA, int PB, int BN, int STAGES> constexpr size_t gemm_smem_bytes() {
+  return (size_t)STAGES * (PA * kTileM * kRowBytes + PB * BN * kRowBytes) + (2 * STAGES + 4) * 8 + 16 + 1024;
+}
+
+// Host helpers (gemm.cu).
+// Encodes a tiled tensor map over a K-major side-band tensor viewed as
+// (k_extent, rows, planes), rows pitch_elems apart, with a (128 bytes,
+// box_rows, 1) box and the 128-byte swizzle. Reads past k_extent or rows are
+// zero-filled by the copy engine.
+int make_operand_map(CUtensorMap *map, const void *base, bool int8, int64_t k_extent, int64_t pitch_elems,
+                     int64_t rows, int planes, int box_rows);
+int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, const uint64_t *dims,
+                 const uint64_t *strides_bytes, const uint32_t *box, const uint32_t *elem_strides);
+int device_status_word(int **status);
+int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch_a, const void *B, int64_t pitch_b,
+             int M, int N, int K, const GemmEpilogue &ep, cudaStream_t st);
+
+} // namespace nb200

@@ -1,0 +1,324 @@
+// Operand preparation for the tensor-core contractions (all HBM-bound passes):
+//  * weight binarisation fused with the per-output alpha = mean|W| reduction
+//    and with the emission of the K-major +-1 side-band the MMA reads,
+//  * fp32 -> three bf16 planes (hi, mid, lo with hi + mid + lo == x exactly
+//    for normal-range values), optionally with NCHW -> NHWC re-layout,
+//  * int8 code transposition.
+#include <cuda_bf16.h>
+
+#include "prepare.cuh"
+
+namespace nb200 {
+namespace {
+
+__device__ __forceinline__ float sign_of(float w, float zero_to) {
+  // include/nbla/function/sign.hpp:48-50 (+0, -0 and NaN take zero_to)
+  return (w > 0.0f) ? 1.0f : ((w < 0.0f) ? -1.0f : zero_to);
+}
+
+// ---------------------------------------------------------------------------
+// BinaryWeightAffine / BinaryConnectAffine weights: W is [R, C] row-major, one
+// alpha per COLUMN (binary_weight_affine.cpp:83-107). Grid (C/64, R/64);
+// each block handles a 64 x 64 tile: reads W coalesced along c, writes Wb
+// coalesced, transposes the signs through shared memory and writes the
+// side-band [C][Kp] (K = R contiguous) coalesced along r, and stores the
+// tile's column sums of |W| to partial[row_block][c]. A second tiny kernel
+// sums the partials in a fixed order (deterministic) and scales by 1/R.
+// ---------------------------------------------------------------------------
+constexpr int kBT = 64;
+
+template <bool kInt8>
+__global__ void __launch_bounds__(256) binarize_columns_kernel(const float *__restrict__ w, int R, int C,
+                                                               float zero_to, float *__restrict__ wb,
+                                                               void *__restrict__ side, int64_t side_pitch,
+                                                               float *__restrict__ partial) {
+  __shared__ float s_sign[kBT][kBT + 1];
+  __shared__ float s_sum[4][kBT];
+  const int c0 = blockIdx.x * kBT, r0 = blockIdx.y * kBT;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6; // 64 x 4
+  const int c = c0 + tx;
+  float acc = 0.0f;
+  for (int rr = ty; rr < kBT; rr += 4) {
+    const int r = r0 + rr;
+    float s = 0.0f;
+    if (r < R && c < C) {
+      const float v = w[(int64_t)r * C + c];
+      s = sign_of(v, zero_to);
+      wb[(int64_t)r * C + c] = s;
+      acc += fabsf(v);
+    }
+    s_sign[rr][tx] = s;
+  }
+  s_sum[ty][tx] = acc;
+  __syncthreads();
+  if (partial != nullptr && ty == 0 && c < C)
+    partial[(int64_t)blockIdx.y * C + c] = (s_sum[0][tx] + s_sum[1][tx]) + (s_sum[2][tx] + s_sum[3][tx]);
+  // side-band: row = output column c, contiguous index = input row r
+  for (int cc = ty; cc < kBT; cc += 4) {
+    const int oc = c0 + cc, r = r0 + tx;
+    if (oc < C && r < R) {
+      const float s = s_sign[tx][cc];
+      if (kInt8)
+        reinterpret_cast<int8_t *>(side)[(int64_t)oc * side_pitch + r] = (int8_t)(int)s;
+      else
+        reinterpret_cast<__nv_bfloat16 *>(side)[(int64_t)oc * side_pitch + r] = __float2bfloat16_rn(s);
+    }
+  }
+}
+
+__global__ void finalize_alpha_kernel(const float *__restrict__ partial, int blocks, int C, float inv,
+                                      float *__restrict__ alpha) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C)
+    return;
+  float s = 0.0f;
+  for (int b = 0; b < blocks; ++b)
+    s += partial[(int64_t)b * C + c];
+  alpha[c] = __fmul_rn(s, inv);
+}
+
+// ---------------------------------------------------------------------------
+// BinaryWeightConvolution / BinaryConnectConvolution weights: W is
+// [Ko, Cg, kh, kw]; one alpha per output map = mean over its Cg*kh*kw taps
+// (binary_weight_convolution.cpp:81-102). One block per output map; the
+// side-band is [Ko][Kp] with K ordered (ky, kx, c) so that one 128-byte K
+// block is one filter tap over consecutive channels, matching the NHWC
+// activation planes.
+// ---------------------------------------------------------------------------
+template <bool kInt8>
+__global__ void __launch_bounds__(256) binarize_rows_kernel(const float *__restrict__ w, int Cg, int kh, int kw,
+                                                            float zero_to, float inv, float *__restrict__ wb,
+                                                            float *__restrict__ alpha, void *__restrict__ side,
+                                                            int64_t side_pitch, int c_pad) {
+  const int o = blockIdx.x;
+  const int taps = kh * kw, Kd = Cg * taps;
+  const float *wr = w + (int64_t)o * Kd;
+  float acc = 0.0f;
+  for (int k = threadIdx.x; k < Kd; k += 256) {
+    const float v = wr[k];
+    const float s = sign_of(v, zero_to);
+    wb[(int64_t)o * Kd + k] = s;
+    acc += fabsf(v);
+    const int c = k / taps, t = k - c * taps;
+    const int64_t dst = (int64_t)o * side_pitch + (int64_t)t * c_pad + c;
+    if (kInt8)
+      reinterpret_cast<int8_t *>(side)[dst] = (int8_t)(int)s;
+    else
+      reinterpret_cast<__nv_bfloat16 *>(side)[dst] = __float2bfloat16_rn(s);
+  }
+  if (alpha == nullptr)
+    return;
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1)
+    acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  __shared__ float s_part[8];
+  if ((threadIdx.x & 31) == 0)
+    s_part[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.0f;
+    for (int i = 0; i < 8; ++i)
+      s += s_part[i];
+    alpha[o] = __fmul_rn(s, inv);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// fp32 [rows, K] -> bf16 planes [3][rows][Kp]: hi = bf16(x), mid = bf16(x - hi),
+// lo = bf16(x - hi - mid); the two subtractions are exact in fp32.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void split3(float x, __nv_bfloat16 &h, __nv_bfloat16 &m, __nv_bfloat16 &l) {
+  h = __float2bfloat16_rn(x);
+  const float r1 = __fsub_rn(x, __bfloat162float(h));
+  m = __float2bfloat16_rn(r1);
+  const float r2 = __fsub_rn(r1, __bfloat162float(m));
+  l = __float2bfloat16_rn(r2);
+}
+
+__global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict__ x, int64_t rows, int K, int64_t Kp,
+                                                         int planes, __nv_bfloat16 *__restrict__ out) {
+  const int64_t total = rows * Kp;
+  const int64_t plane_stride = rows * Kp;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / Kp;
+    const int k = (int)(i - r * Kp);
+    __nv_bfloat16 h, m, l;
+    const float v = (k < K) ? x[r * K + k] : 0.0f;
+    split3(v, h, m, l);
+    out[i] = h;
+    if (planes > 1)
+      out[plane_stride + i] = m;
+    if (planes > 2)
+      out[2 * plane_stride + i] = l;
+  }
+}
+
+// fp32 NCHW -> planes of NHWC with the channel extent padded to c_pad:
+// out[plane][n][h][w][c_pad]. Tile transpose through shared memory: reads
+// coalesced along w (hw), writes coalesced along c.
+template <typename OutT, int PLANES>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restrict__ x, int C, int HW, int c_pad,
+                                                           OutT *__restrict__ out, int64_t plane_stride,
+                                                           float inv_delta) {
+  __shared__ float tile[32][33];
+  const int n = blockIdx.z;
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
+  for (int cc = ty; cc < 32; cc += 8) {
+    const int c = c0 + cc, p = p0 + tx;
+    tile[cc][tx] = (c < C && p < HW) ? x[((int64_t)n * C + c) * HW + p] : 0.0f;
+  }
+  __syncthreads();
+  for (int pp = ty; pp < 32; pp += 8) {
+    const int p = p0 + pp, c = c0 + tx;
+    if (p < HW && c < c_pad) {
+      const float v = tile[tx][pp];
+      const int64_t dst = ((int64_t)n * HW + p) * c_pad + c;
+      if constexpr (sizeof(OutT) == 1) {
+        out[dst] = (OutT)__float2int_rn(__fmul_rn(v, inv_delta)); // v is k * delta exactly
+      } else {
+        __nv_bfloat16 h, m, l;
+        split3(v, h, m, l);
+        out[dst] = h;
+        if (PLANES > 1)
+          out[plane_stride + dst] = m;
+        if (PLANES > 2)
+          out[2 * plane_stride + dst] = l;
+      }
+    }
+  }
+}
+
+// int8 [R, C] -> [C][pitch] (transpose), tile 64 x 64 through shared memory.
+__global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t *__restrict__ src, int R, int C,
+                                                           int8_t *__restrict__ dst, int64_t pitch) {
+  __shared__ int8_t tile[64][65];
+  const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  for (int rr = ty; rr < 64; rr += 4) {
+    const int r = r0 + rr, c = c0 + tx;
+    tile[rr][tx] = (r < R && c < C) ? src[(int64_t)r * C + c] : (int8_t)0;
+  }
+  __syncthreads();
+  for (int cc = ty; cc < 64; cc += 4) {
+    const int c = c0 + cc, r = r0 + tx;
+    if (c < C && r < R)
+      dst[(int64_t)c * pitch + r] = tile[tx][cc];
+  }
+}
+
+// fp32 [R, C] -> [C][R] (transpose), tile 32 x 32 through shared memory.
+__global__ void __launch_bounds__(256) transpose_f32_kernel(const float *__restrict__ src, int R, int C,
+                                                            float *__restrict__ dst) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int rr = ty; rr < 32; rr += 8) {
+    const int r = r0 + rr, c = c0 + tx;
+    tile[rr][tx] = (r < R && c < C) ? src[(int64_t)r * C + c] : 0.0f;
+  }
+  __syncthreads();
+  for (int cc = ty; cc < 32; cc += 8) {
+    const int c = c0 + cc, r = r0 + tx;
+    if (c < C && r < R)
+      dst[(int64_t)c * R + r] = tile[tx][cc];
+  }
+}
+
+// fp32 values that are integer multiples of delta -> int8 codes, [rows, K] -> [rows][pitch].
+__global__ void __launch_bounds__(256) codes_rows_kernel(const float *__restrict__ x, int64_t rows, int K,
+                                                         int64_t pitch, float inv_delta, int8_t *__restrict__ out) {
+  const int64_t total = rows * pitch;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / pitch;
+    const int k = (int)(i - r * pitch);
+    out[i] = (k < K) ? (int8_t)__float2int_rn(__fmul_rn(x[r * K + k], inv_delta)) : (int8_t)0;
+  }
+}
+
+inline unsigned capped_grid(int64_t items, int threads) {
+  int64_t b = (items + threads - 1) / threads;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (b > cap)
+    b = cap;
+  return (unsigned)(b < 1 ? 1 : b);
+}
+
+} // namespace
+
+int binarize_columns(const float *w, int R, int C, float zero_to, float *wb, float *alpha, void *side,
+                     int64_t side_pitch, bool int8, float *partial_scratch, cudaStream_t st) {
+  const dim3 grid((C + kBT - 1) / kBT, (R + kBT - 1) / kBT);
+  float *partial = alpha ? partial_scratch : nullptr;
+  if (int8)
+    binarize_columns_kernel<true><<<grid, 256, 0, st>>>(w, R, C, zero_to, wb, side, side_pitch, partial);
+  else
+    binarize_columns_kernel<false><<<grid, 256, 0, st>>>(w, R, C, zero_to, wb, side, side_pitch, partial);
+  NB_LAUNCH_CHECK();
+  if (alpha) {
+    const float inv = (float)1 / R; // binary_weight_affine.cpp:68
+    finalize_alpha_kernel<<<(C + 255) / 256, 256, 0, st>>>(partial, (int)grid.y, C, inv, alpha);
+    NB_LAUNCH_CHECK();
+  }
+  return NB200_OK;
+}
+
+int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to, float *wb, float *alpha, void *side,
+                  int64_t side_pitch, int c_pad, bool int8, cudaStream_t st) {
+  const float inv = (float)1 / (Cg * kh * kw); // binary_weight_convolution.cpp:66
+  if (int8)
+    binarize_rows_kernel<true><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
+  else
+    binarize_rows_kernel<false><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st) {
+  split_rows_kernel<<<capped_grid(rows * Kp, 256), 256, 0, st>>>(x, rows, K, Kp, planes,
+                                                                 reinterpret_cast<__nv_bfloat16 *>(out));
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+int nchw_to_nhwc_bf16(const float *x, int N, int C, int HW, int c_pad, int planes, void *out, cudaStream_t st) {
+  const dim3 grid((HW + 31) / 32, (c_pad + 31) / 32, N);
+  const int64_t ps = (int64_t)N * HW * c_pad;
+  __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(out);
+  if (planes == 3)
+    nchw_to_nhwc_kernel<__nv_bfloat16, 3><<<grid, 256, 0, st>>>(x, C, HW, c_pad, o, ps, 0.f);
+  else
+    nchw_to_nhwc_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(x, C, HW, c_pad, o, ps, 0.f);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+int nchw_to_nhwc_i8(const float *x, int N, int C, int HW, int c_pad, float delta, void *out, cudaStream_t st) {
+  const dim3 grid((HW + 31) / 32, (c_pad + 31) / 32, N);
+  nchw_to_nhwc_kernel<int8_t, 1><<<grid, 256, 0, st>>>(x, C, HW, c_pad, reinterpret_cast<int8_t *>(out), 0,
+                                                       1.0f / delta);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+int transpose_i8(const int8_t *src, int R, int C, int8_t *dst, int64_t pitch, cudaStream_t st) {
+  const dim3 grid((C + 63) / 64, (R + 63) / 64);
+  transpose_i8_kernel<<<grid, 256, 0, st>>>(src, R, C, dst, pitch);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+int transpose_f32(const float *src, int R, int C, float *dst, cudaStream_t st) {
+  const dim3 grid((C + 31) / 32, (R + 31) / 32);
+  transpose_f32_kernel<<<grid, 256, 0, st>>>(src, R, C, dst);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+int codes_rows_i8(const float *x, int64_t rows, int K, int64_t pitch, float delta, int8_t *out, cudaStream_t st) {
+  codes_rows_kernel<<<capped_grid(rows * pitch, 256), 256, 0, st>>>(x, rows, K, pitch, 1.0f / delta, out);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+} // namespace nb200

@@ -1,0 +1,28 @@
+// Host-callable operand preparation passes (prepare.cu).
+#pragma once
+#include "common.cuh"
+
+namespace nb200 {
+
+// W [R, C] -> wb (signs, fp32, same layout), alpha[C] = mean_r |W| (NULL to
+// skip, BinaryConnect), side-band [C][side_pitch] (bf16 or int8 signs with
+// K = R contiguous). partial_scratch: ceil(R/64) * C floats (only with alpha).
+int binarize_columns(const float *w, int R, int C, float zero_to, float *wb, float *alpha, void *side,
+                     int64_t side_pitch, bool int8, float *partial_scratch, cudaStream_t st);
+// W [Ko, Cg, kh, kw] -> wb, alpha[Ko] (NULL to skip), side-band [Ko][side_pitch]
+// with K ordered (ky, kx, c) and c padded to c_pad.
+int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to, float *wb, float *alpha, void *side,
+                  int64_t side_pitch, int c_pad, bool int8, cudaStream_t st);
+// fp32 [rows, K] -> bf16 [planes][rows][Kp] (planes = 1 or 3; hi, mid, lo).
+int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st);
+// fp32 NCHW -> bf16 [planes][N][HW][c_pad] / int8 [N][HW][c_pad] (values k*delta -> k).
+int nchw_to_nhwc_bf16(const float *x, int N, int C, int HW, int c_pad, int planes, void *out, cudaStream_t st);
+int nchw_to_nhwc_i8(const float *x, int N, int C, int HW, int c_pad, float delta, void *out, cudaStream_t st);
+// int8 [R, C] -> [C][pitch].
+int transpose_i8(const int8_t *src, int R, int C, int8_t *dst, int64_t pitch, cudaStream_t st);
+// fp32 [R, C] -> [C][R].
+int transpose_f32(const float *src, int R, int C, float *dst, cudaStream_t st);
+// fp32 multiples of delta [rows, K] -> int8 [rows][pitch].
+int codes_rows_i8(const float *x, int64_t rows, int K, int64_t pitch, float delta, int8_t *out, cudaStream_t st);
+
+} // namespace nb200

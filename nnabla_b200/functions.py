@@ -105,3 +105,126 @@ def min_max_quantize(x, qr_min, qr_max, ql_min, ql_max, decay=0.999, x_min_max=F
                int(bool(x_min_max)), int(bool(ema)), C.c_float(eps), C.ptr(y), ctypes.c_void_p(0),
                C.stream_ptr(x.device))
     return y
+
+
+# ---------------------------------------------------------------------------
+# Affine layers
+# ---------------------------------------------------------------------------
+
+def check_device_status(device=None):
+    """Raises if a bounded device-side wait gave up since the last check
+    (synchronises the current stream)."""
+    code = ctypes.c_int(0)
+    C.call("nb200_take_device_status", ctypes.byref(code), C.stream_ptr(device))
+    if code.value != 0:
+        raise C.NB200Error(5, "a device-side wait gave up (status 0x%x); results are incomplete" % code.value)
+
+
+def _affine_dims(x, w, base_axis, bias):
+    """Shape rules of Affine::setup_impl (src/nbla/function/generic/affine.cpp:29-78)."""
+    if w.dim() < 2:
+        raise RuntimeError("Weights(inputs[1]) must be matrix or tensor.")
+    if base_axis < 0:
+        base_axis += x.dim()
+    if not 0 <= base_axis < x.dim():
+        raise RuntimeError("Base_axis must be less than ndim of input data(inputs[0]). base_axis: %d >= ndim of "
+                           "input: %d." % (base_axis, x.dim()))
+    rows = 1
+    for s in x.shape[:base_axis]:
+        rows *= int(s)
+    i_col = x.numel() // max(rows, 1)
+    w_row = int(w.shape[0])
+    w_col = w.numel() // max(w_row, 1)
+    if i_col != w_row:
+        raise RuntimeError("Size of input data(inputs[0]) and weights(inputs[1]) mismatch. size of input: %d != "
+                           "size of weights: %d." % (i_col, w_row))
+    if bias is not None:
+        if bias.dim() != w.dim() - 1 or tuple(bias.shape) != tuple(w.shape[1:]):
+            raise RuntimeError("Shape of bias(inputs[2]) and weights(inputs[1]) mismatch.")
+    out_shape = tuple(x.shape[:base_axis]) + tuple(w.shape[1:])
+    return rows, w_row, w_col, out_shape
+
+
+def _same_shape(a, b, what):
+    if a.dim() != b.dim() or tuple(a.shape) != tuple(b.shape):
+        raise RuntimeError("Binary and float weights must have same size. (%s)" % what)
+
+
+def binary_weight_affine(x, weight, binary_weight, alpha, bias=None, base_axis=1, quantize_zero_to=1.0,
+                         n_outputs=-1, outputs=None):
+    """Binary Weight Affine (function_bases.binary_weight_affine).
+
+    Forward of BinaryWeightAffine (src/nbla/function/generic/binary_weight_affine.cpp:74-122):
+    writes `binary_weight` = sign(weight) and `alpha` = mean |weight| per output,
+    returns x . binary_weight * alpha + bias.
+    """
+    x, weight = _check_input(x), _check_input(weight, "weight")
+    binary_weight, alpha = _check_input(binary_weight, "binary_weight"), _check_input(alpha, "alpha")
+    bias = _check_input(bias, "bias") if bias is not None else None
+    rows, w_row, w_col, out_shape = _affine_dims(x, weight, base_axis, bias)
+    _same_shape(weight, binary_weight, "float vs binary")
+    if alpha.numel() != w_col:
+        raise RuntimeError("Size of alpha must be equal to output size.")
+    y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
+    with torch.cuda.device(x.device):
+        C.call("nb200_binary_weight_affine_f32", C.ptr(x), C.ptr(weight), C.ptr(binary_weight), C.ptr(alpha),
+               C.ptr(bias), C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(w_row), ctypes.c_int64(w_col),
+               C.c_float(quantize_zero_to), C.stream_ptr(x.device))
+    return y
+
+
+def binary_connect_affine(x, weight, binary_weight, bias=None, base_axis=1, quantize_zero_to=1.0, n_outputs=-1,
+                          outputs=None):
+    """Binary Connect Affine (function_bases.binary_connect_affine).
+
+    Forward of BinaryConnectAffine (src/nbla/function/generic/binary_connect_affine.cpp:59-71).
+    """
+    x, weight = _check_input(x), _check_input(weight, "weight")
+    binary_weight = _check_input(binary_weight, "binary_weight")
+    bias = _check_input(bias, "bias") if bias is not None else None
+    rows, w_row, w_col, out_shape = _affine_dims(x, weight, base_axis, bias)
+    _same_shape(weight, binary_weight, "float vs binary")
+    y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
+    with torch.cuda.device(x.device):
+        C.call("nb200_binary_connect_affine_f32", C.ptr(x), C.ptr(weight), C.ptr(binary_weight), C.ptr(bias),
+               C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(w_row), ctypes.c_int64(w_col),
+               C.c_float(quantize_zero_to), C.stream_ptr(x.device))
+    return y
+
+
+def affine(x, weight, bias=None, base_axis=1, n_outputs=-1, outputs=None, fixed_point=None):
+    """Affine (function_bases.affine; src/nbla/function/generic/affine.cpp:80-96).
+
+    fixed_point=(delta_x, delta_w): x and weight are outputs of
+    fixed_point_quantize with n <= 8 and those step sizes; the product then
+    runs on the int8 tensor-core path. Otherwise the fp32-accurate split path.
+    """
+    x, weight = _check_input(x), _check_input(weight, "weight")
+    bias = _check_input(bias, "bias") if bias is not None else None
+    rows, w_row, w_col, out_shape = _affine_dims(x, weight, base_axis, bias)
+    y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
+    with torch.cuda.device(x.device):
+        if fixed_point is not None:
+            dx, dw = fixed_point
+            C.call("nb200_affine_fxp8_f32", C.ptr(x), C.ptr(weight), C.c_float(dx), C.c_float(dw), C.ptr(bias),
+                   C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(w_row), ctypes.c_int64(w_col),
+                   C.stream_ptr(x.device))
+        else:
+            C.call("nb200_affine_f32", C.ptr(x), C.ptr(weight), C.ptr(bias), C.ptr(y), ctypes.c_int64(rows),
+                   ctypes.c_int64(w_row), ctypes.c_int64(w_col), C.stream_ptr(x.device))
+    return y
+
+
+def affine_from_codes(x_codes, w_codes, delta_x, delta_w, bias=None):
+    """Affine on the int8 codes written by fixed_point_quantize_with_codes
+    (x_codes [rows, K], w_codes [K, N])."""
+    rows, K = x_codes.shape
+    K2, N = w_codes.shape
+    if K != K2:
+        raise RuntimeError("Size of input data(inputs[0]) and weights(inputs[1]) mismatch.")
+    y = torch.empty((rows, N), dtype=torch.float32, device=x_codes.device)
+    with torch.cuda.device(x_codes.device):
+        C.call("nb200_affine_codes_i8_f32", C.ptr(x_codes), C.ptr(w_codes), C.c_float(delta_x), C.c_float(delta_w),
+               C.ptr(bias), C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(K), ctypes.c_int64(N),
+               C.stream_ptr(x_codes.device))
+    return y
