@@ -212,10 +212,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
       const int m0 = (tile % shape.m_tiles) * kTileM;
       const int n0 = (tile / shape.m_tiles) * BN;
-      if (!ptx::mbar_wait(tmem_full + buf, buf_phase, abort_flag)) {
-        if (*abort_flag == 0)
-          atomicCAS(status, 0, kStatusEpilogueTimeout);
-        *abort_flag = 1;
+      // All lanes poll; the verdict is made warp-uniform so that the aligned
+      // TMEM loads below always run with the full warp.
+      const bool got = ptx::mbar_wait(tmem_full + buf, buf_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) {
+          if (*abort_flag == 0)
+            atomicCAS(status, 0, kStatusEpilogueTimeout);
+          *abort_flag = 1;
+        }
         ok = false;
         break;
       }

@@ -62,7 +62,12 @@ def test_binary_weight_affine_shapes(F, M, K, N, bias):
     y, wb, al = run_bwa(F, x, w, b, 1, 1.0)
     wy, wwb, wal = oracle.binary_weight_affine(x, w, b, 1, 1.0)
     assert np.array_equal(bits(wb), bits(wwb))
-    np.testing.assert_allclose(al, wal, rtol=1e-6)
+    # alpha: the reference sums |w| with Eigen, the oracle sequentially in fp32
+    # (rounding error grows with K); the GPU sums in a fixed blocked order.
+    # Both must sit within fp32 summation error of the exact mean.
+    exact = np.abs(w.astype(np.float64)).mean(0)
+    np.testing.assert_allclose(al, exact, rtol=1e-6)
+    np.testing.assert_allclose(al, wal, rtol=1e-6 + K * 6e-8)
     assert cases.rel_rms(y, wy) < TOL
 
 
@@ -74,7 +79,8 @@ def test_binary_weight_affine_config1(F):
     w = (0.02 * rng.randn(1024, 4096)).astype(np.float32)
     y, wb, al = run_bwa(F, x, w, np.zeros(4096, np.float32), 1, 1.0)
     assert np.array_equal(sha(wb), g["cfg1/wb_sha"])
-    np.testing.assert_allclose(al, g["cfg1/alpha"], rtol=1e-6)
+    np.testing.assert_allclose(al, np.abs(w.astype(np.float64)).mean(0), rtol=1e-6)
+    np.testing.assert_allclose(al, g["cfg1/alpha"], rtol=1e-6 + 1024 * 6e-8)  # reference sum is sequential fp32
     rms = float(g["cfg1/y_rms"][0])
     err = np.sqrt(np.mean((y[:4].astype(np.float64) - g["cfg1/y_rows"]) ** 2))
     assert err / rms < TOL
