@@ -165,6 +165,38 @@ int nb200_affine_codes_i8_f32(const int8_t *x_codes, const int8_t *w_codes, floa
 int nb200_affine_f32(const float *x, const float *w, const float *bias, float *y, int64_t rows, int64_t w_row,
                      int64_t w_col, void *stream);
 
+/* ---- binary-weight convolutions ------------------------------------------------ */
+
+/* BinaryWeightConvolution<float>::forward_impl
+ * (src/nbla/function/generic/binary_weight_convolution.cpp:72-117, which calls
+ * Convolution<float>::forward_impl, convolution.cpp:160-197). 2-D, NCHW:
+ * x [batch, channels, height, width], w [outmaps, channels/group, kernel_h,
+ * kernel_w], bias [outmaps] or NULL. WRITES wb = sign(w; quantize_zero_to) and
+ * alpha[o] = (sum |w[o,...]|) * float(1/(channels/group*kernel_h*kernel_w))
+ * like the reference writes inputs[2] and inputs[3]; y [batch, outmaps, Ho, Wo]
+ * = conv(x, wb) * alpha[o] + bias[o] with the reference's output-size rule.
+ * The reference unfolds each sample to patches and multiplies per sample;
+ * here the convolution is an implicit GEMM fed by TMA boxes of an NHWC copy
+ * of x (zero padding = out-of-range fill).
+ * activation_delta == 0: x is arbitrary fp32 and is split into three bf16
+ * pieces (exact products with the +-1 weights, fp32 accumulation).
+ * activation_delta > 0: the caller asserts that x holds integer multiples of
+ * activation_delta with |multiple| <= 127 (the output of FixedPointQuantize
+ * with n <= 8); the contraction then runs on the int8 path, exactly. */
+int nb200_binary_weight_convolution_f32(const float *x, const float *w, float *wb, float *alpha, const float *bias,
+                                        float *y, int batch, int channels, int height, int width, int outmaps,
+                                        int kernel_h, int kernel_w, int pad_h, int pad_w, int stride_h, int stride_w,
+                                        int dilation_h, int dilation_w, int group, float quantize_zero_to,
+                                        float activation_delta, void *stream);
+/* BinaryConnectConvolution<float>::forward_impl
+ * (src/nbla/function/generic/binary_connect_convolution.cpp:67-80): as above
+ * without alpha. */
+int nb200_binary_connect_convolution_f32(const float *x, const float *w, float *wb, const float *bias, float *y,
+                                         int batch, int channels, int height, int width, int outmaps, int kernel_h,
+                                         int kernel_w, int pad_h, int pad_w, int stride_h, int stride_w,
+                                         int dilation_h, int dilation_w, int group, float quantize_zero_to,
+                                         float activation_delta, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

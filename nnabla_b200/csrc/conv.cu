@@ -1,0 +1,225 @@
+// Implicit-GEMM convolution on the tcgen05 contraction kernel: host-side
+// planning (pixel boxes, tensor maps) and the C-ABI entry points for
+// BinaryWeightConvolution / BinaryConnectConvolution.
+//
+// Data layout in HBM for one call (scratch, stream-ordered allocation):
+//   activations  [planes][N][H][W][Ctot]  bf16 (3 planes: hi, mid, lo) or int8 codes,
+//                channels of group g at [g * c_pad_g, g * c_pad_g + Cg), zero padded
+//   weights      [Ko][taps][c_slots]      +-1 (or quantize_zero_to) as bf16 / int8,
+//                K ordered tap-major, channel-minor, zero padded per tap
+// D = weights x activations^T with rows = output maps, columns = a box of
+// output pixels; y is written NCHW directly from the epilogue.
+#include <cstring>
+
+#include "gemm.cuh"
+#include "prepare.cuh"
+
+namespace nb200 {
+namespace {
+
+inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+bool bf16_exact(float v) {
+  uint32_t b;
+  std::memcpy(&b, &v, 4);
+  return (b & 0xffffu) == 0;
+}
+
+struct ConvGeometry {
+  int N, C, H, W, Ko, kh, kw, ph, pw, sh, sw, dh, dw, group;
+  int Cg, Kog, Ho, Wo;
+};
+
+// The reference's checks (src/nbla/function/generic/convolution.cpp:40-158).
+int check_geometry(ConvGeometry &g) {
+  NB_CHECK(g.N > 0 && g.C > 0 && g.H > 0 && g.W > 0 && g.Ko > 0 && g.kh > 0 && g.kw > 0, NB200_EVALUE,
+           "empty convolution operand");
+  NB_CHECK(g.group > 0 && g.C % g.group == 0, NB200_EVALUE,
+           "Number of input channel needs to be divisible by group. Input channel: %d, group: %d.", g.C, g.group);
+  NB_CHECK(g.Ko % g.group == 0, NB200_EVALUE,
+           "Number of output channel needs to be divisible by group. Output channel: %d, group: %d.", g.Ko, g.group);
+  NB_CHECK(g.sh > 0 && g.sw > 0 && g.dh > 0 && g.dw > 0 && g.ph >= 0 && g.pw >= 0, NB200_EVALUE,
+           "stride and dilation must be positive, pad non-negative");
+  g.Cg = g.C / g.group;
+  g.Kog = g.Ko / g.group;
+  g.Ho = (g.H + 2 * g.ph - (g.dh * (g.kh - 1) + 1)) / g.sh + 1;
+  g.Wo = (g.W + 2 * g.pw - (g.dw * (g.kw - 1) + 1)) / g.sw + 1;
+  NB_CHECK((g.H + 2 * g.ph - (g.dh * (g.kh - 1) + 1)) >= 0 && (g.W + 2 * g.pw - (g.dw * (g.kw - 1) + 1)) >= 0 &&
+               g.Ho > 0 && g.Wo > 0,
+           NB200_EVALUE, "Invalid configuration of convolution: {input:%dx%d, kernel:%dx%d, pad:%dx%d, stride:%dx%d, "
+                         "dilation:%dx%d}.",
+           g.H, g.W, g.kh, g.kw, g.ph, g.pw, g.sh, g.sw, g.dh, g.dw);
+  return NB200_OK;
+}
+
+// Picks the pixel box: whole output rows, h_box rows of n_box images, at most
+// `bn_max` pixels. Several images share a box only when a whole image fits.
+void plan_box(const ConvGeometry &g, int bn_max, int &h_box, int &n_box) {
+  const int per_img = g.Ho * g.Wo;
+  if (per_img <= bn_max) {
+    h_box = g.Ho;
+    n_box = bn_max / per_img;
+    if (n_box > g.N)
+      n_box = g.N;
+    return;
+  }
+  n_box = 1;
+  int best = bn_max / g.Wo;
+  if (best < 1)
+    best = 1;
+  // Prefer a divisor of Ho (no ragged last box) unless it wastes over a third of the box.
+  for (int h = best; h >= 1; --h)
+    if (g.Ho % h == 0) {
+      if (3 * h >= 2 * best)
+        best = h;
+      break;
+    }
+  h_box = best;
+}
+
+template <bool kInt8, int PA, int PB, int BN, int STAGES>
+int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ctot, const void *wside, int64_t wpitch,
+                int c_pad_g, int cblocks, int h_box, int n_box, const GemmEpilogue &ep, cudaStream_t st) {
+  const int es = kInt8 ? 1 : 2;
+  const int E = kRowBytes / es;
+  CUtensorMap ma, mb;
+  // weights: (K, Ko, 1)
+  NB_TRY(make_operand_map(&ma, wside, kInt8, wpitch, wpitch, g.Ko, 1, kTileM));
+  // activations: (C, W, H, N, planes); the box walks W and H with the convolution stride
+  const uint64_t dims[5] = {(uint64_t)ctot, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N, (uint64_t)planes_b};
+  const uint64_t strides[4] = {(uint64_t)ctot * es, (uint64_t)ctot * es * g.W, (uint64_t)ctot * es * g.W * g.H,
+                               (uint64_t)ctot * es * g.W * g.H * g.N};
+  const uint32_t box[5] = {(uint32_t)E, (uint32_t)(g.Wo * g.sw), (uint32_t)(h_box * g.sh), (uint32_t)n_box, 1};
+  const uint32_t estr[5] = {1, (uint32_t)g.sw, (uint32_t)g.sh, 1, 1};
+  NB_TRY(encode_tiled(&mb, kInt8 ? 1 : 0, 5, act, dims, strides, box, estr));
+  ConvProblem p;
+  p.Nimg = g.N;
+  p.Ko = g.Ko;
+  p.Kog = g.Kog;
+  p.groups = g.group;
+  p.Ho = g.Ho;
+  p.Wo = g.Wo;
+  p.h_box = h_box;
+  p.n_box = n_box;
+  p.tiles_h = (g.Ho + h_box - 1) / h_box;
+  p.tiles_n = (g.N + n_box - 1) / n_box;
+  p.m_tiles_g = (g.Kog + kTileM - 1) / kTileM;
+  p.kw = g.kw;
+  p.taps = g.kh * g.kw;
+  p.cblocks = cblocks;
+  p.sh = g.sh;
+  p.sw = g.sw;
+  p.ph = g.ph;
+  p.pw = g.pw;
+  p.dh = g.dh;
+  p.dw = g.dw;
+  p.c_group_stride = c_pad_g;
+  p.pixels = n_box * h_box * g.Wo;
+  p.n_run = (int)round_up(p.pixels, 16);
+  const int tiles = p.groups * p.m_tiles_g * p.tiles_h * p.tiles_n;
+  return launch_contraction<kInt8, PA, PB, BN, STAGES, false, ConvProblem>(ma, mb, p, tiles, ep, st);
+}
+
+struct AsyncScratch {
+  void *p = nullptr;
+  cudaStream_t st;
+  explicit AsyncScratch(cudaStream_t s) : st(s) {}
+  int alloc(size_t bytes) {
+    NB_CUDA(cudaMallocAsync(&p, bytes, st));
+    return NB200_OK;
+  }
+  ~AsyncScratch() {
+    if (p)
+      cudaFreeAsync(p, st);
+  }
+};
+
+// Shared body of BinaryWeightConvolution / BinaryConnectConvolution forward.
+int binary_convolution(const float *x, const float *w, float *wb, float *alpha, const float *bias, float *y,
+                       ConvGeometry g, float zero_to, float act_delta, cudaStream_t st) {
+  NB_TRY(check_geometry(g));
+  NB_CHECK(x && w && wb && y, NB200_EVALUE, "null data pointer");
+  const bool int8 = act_delta > 0.0f;
+  if (int8)
+    NB_CHECK(zero_to == 1.0f || zero_to == -1.0f || zero_to == 0.0f, NB200_ENOTIMPL,
+             "the int8 path needs quantize_zero_to in {-1, 0, 1} (got %g)", zero_to);
+  else
+    NB_CHECK(bf16_exact(zero_to), NB200_ENOTIMPL,
+             "quantize_zero_to = %g is not representable in bf16; the exact tensor-core path needs it to be", zero_to);
+  NB_CHECK(g.Wo * g.sw <= 256 && g.Wo <= 256, NB200_ENOTIMPL,
+           "output rows wider than 256 pixels (Wo=%d, stride %d) are not supported", g.Wo, g.sw);
+  const int es = int8 ? 1 : 2;
+  const int E = kRowBytes / es;
+  const int c_pad_g = (int)round_up(g.Cg, 16);
+  const int cblocks = (c_pad_g + E - 1) / E;
+  const int c_slots = cblocks * E;
+  int64_t ctot = (int64_t)g.group * c_pad_g;
+  if (ctot < E)
+    ctot = E;
+  const int taps = g.kh * g.kw;
+  const int64_t wpitch = (int64_t)taps * c_slots;
+  const int planes = int8 ? 1 : 3;
+  const size_t act_bytes = (size_t)planes * g.N * g.H * g.W * ctot * es;
+  const size_t side_bytes = (size_t)g.Ko * wpitch * es;
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc(round_up(act_bytes, 1024) + round_up(side_bytes, 1024)));
+  uint8_t *act = static_cast<uint8_t *>(scratch.p);
+  uint8_t *side = act + round_up(act_bytes, 1024);
+  if (c_slots != g.Cg)
+    NB_CUDA(cudaMemsetAsync(side, 0, side_bytes, st));
+  NB_TRY(binarize_rows(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, int8, st));
+  NB_TRY(nchw_to_nhwc_planes(x, g.N, g.C, g.H * g.W, g.group, g.Cg, c_pad_g, (int)ctot, int8 ? 0 : 3, act_delta, act,
+                             st));
+  GemmEpilogue ep{};
+  ep.y = y;
+  ep.scale = int8 ? act_delta : 1.0f;
+  ep.row_scale = alpha;
+  ep.row_bias = bias;
+  // Box selection: prefer the 128-column kernel (deeper pipeline) unless the
+  // 256-column box is better filled.
+  int h128, n128, h256, n256;
+  plan_box(g, 128, h128, n128);
+  plan_box(g, 256, h256, n256);
+  const int px128 = h128 * n128 * g.Wo, px256 = h256 * n256 * g.Wo;
+  const double fill128 = (double)px128 / (double)round_up(px128, 16) * px128 / 128.0;
+  const double fill256 = (double)px256 / (double)round_up(px256, 16) * px256 / 256.0;
+  const bool can128 = px128 <= 128;
+  const bool use256 = !can128 || (int8 && fill256 > fill128 + 0.05);
+  if (int8) {
+    if (use256)
+      return launch_conv<true, 1, 1, 256, 4>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h256, n256, ep, st);
+    return launch_conv<true, 1, 1, 128, 6>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
+  }
+  if (use256)
+    return launch_conv<false, 1, 3, 256, 2>(g, act, 3, ctot, side, wpitch, c_pad_g, cblocks, h256, n256, ep, st);
+  return launch_conv<false, 1, 3, 128, 3>(g, act, 3, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
+}
+
+} // namespace
+} // namespace nb200
+
+using namespace nb200;
+
+extern "C" {
+
+int nb200_binary_weight_convolution_f32(const float *x, const float *w, float *wb, float *alpha, const float *bias,
+                                        float *y, int batch, int channels, int height, int width, int outmaps,
+                                        int kernel_h, int kernel_w, int pad_h, int pad_w, int stride_h, int stride_w,
+                                        int dilation_h, int dilation_w, int group, float quantize_zero_to,
+                                        float activation_delta, void *stream) {
+  NB_CHECK(alpha != nullptr, NB200_EVALUE, "alpha is NULL");
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, group, 0, 0, 0, 0};
+  return binary_convolution(x, w, wb, alpha, bias, y, g, quantize_zero_to, activation_delta, as_stream(stream));
+}
+
+int nb200_binary_connect_convolution_f32(const float *x, const float *w, float *wb, const float *bias, float *y,
+                                         int batch, int channels, int height, int width, int outmaps, int kernel_h,
+                                         int kernel_w, int pad_h, int pad_w, int stride_h, int stride_w,
+                                         int dilation_h, int dilation_w, int group, float quantize_zero_to,
+                                         float activation_delta, void *stream) {
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, group, 0, 0, 0, 0};
+  return binary_convolution(x, w, wb, nullptr, bias, y, g, quantize_zero_to, activation_delta, as_stream(stream));
+}
+}

@@ -83,35 +83,22 @@ int device_status_word(int **status) {
 // ---- launch -----------------------------------------------------------------
 template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkip>
 static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, int M, int N, int k_blocks,
-                       const GemmEpilogue &ep, cudaStream_t st) {
-  auto kernel = gemm_tcgen05_kernel<kInt8, PA, PB, BN, STAGES, kSkip, PlainBLoader>;
-  constexpr size_t smem = gemm_smem_bytes<kInt8, PA, PB, BN, STAGES>();
-  static_assert(smem <= 227 * 1024, "shared memory budget");
-  static bool configured[64];
-  int dev = 0;
-  NB_CUDA(cudaGetDevice(&dev));
-  if (!configured[dev & 63]) {
-    NB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[dev & 63] = true;
-  }
-  GemmShape shape;
-  shape.M = M;
-  shape.N = N;
-  shape.k_blocks = k_blocks;
-  shape.m_tiles = (M + kTileM - 1) / kTileM;
-  shape.n_tiles = (N + BN - 1) / BN;
-  int *status = nullptr;
-  NB_TRY(device_status_word(&status));
-  const int tiles = shape.m_tiles * shape.n_tiles;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  kernel<<<grid, kGemmThreads, smem, st>>>(ma, mb, shape, ep, PlainBLoader(), status);
-  NB_LAUNCH_CHECK();
-  return NB200_OK;
+                       const GemmEpilogue &ep, int64_t ldy, cudaStream_t st) {
+  GemmProblem prob;
+  prob.M = M;
+  prob.N = N;
+  prob.kblocks = k_blocks;
+  prob.m_tiles = (M + kTileM - 1) / kTileM;
+  prob.n_tiles = (N + BN - 1) / BN;
+  prob.bn = BN;
+  prob.ldy = ldy;
+  return launch_contraction<kInt8, PA, PB, BN, STAGES, kSkip, GemmProblem>(ma, mb, prob, prob.m_tiles * prob.n_tiles,
+                                                                           ep, st);
 }
 
 // A: [planes_a][M][pitch_a], B: [planes_b][N][pitch_b], both K-major.
 int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch_a, const void *B, int64_t pitch_b,
-             int M, int N, int K, const GemmEpilogue &ep, cudaStream_t st) {
+             int M, int N, int K, const GemmEpilogue &ep, int64_t ldy, cudaStream_t st) {
   NB_CHECK(M > 0 && N > 0 && K > 0, NB200_EVALUE, "empty contraction (M=%d N=%d K=%d)", M, N, K);
   const int epb = int8 ? 128 : 64;
   const int k_blocks = (K + epb - 1) / epb;
@@ -125,26 +112,26 @@ int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch
     const bool wide = (int64_t)m_tiles * ((N + 255) / 256) >= sm_count();
     if (wide) {
       NB_TRY(make_operand_map(&mb, B, true, K, pitch_b, N, 1, 256));
-      return launch_gemm<true, 1, 1, 256, 4, false>(ma, mb, M, N, k_blocks, ep, st);
+      return launch_gemm<true, 1, 1, 256, 4, false>(ma, mb, M, N, k_blocks, ep, ldy, st);
     }
     if (!narrow) {
       NB_TRY(make_operand_map(&mb, B, true, K, pitch_b, N, 1, 128));
-      return launch_gemm<true, 1, 1, 128, 6, false>(ma, mb, M, N, k_blocks, ep, st);
+      return launch_gemm<true, 1, 1, 128, 6, false>(ma, mb, M, N, k_blocks, ep, ldy, st);
     }
     NB_TRY(make_operand_map(&mb, B, true, K, pitch_b, N, 1, 64));
-    return launch_gemm<true, 1, 1, 64, 8, false>(ma, mb, M, N, k_blocks, ep, st);
+    return launch_gemm<true, 1, 1, 64, 8, false>(ma, mb, M, N, k_blocks, ep, ldy, st);
   }
   if (planes_a == 3 && planes_b == 1) {
     if (!narrow) {
       NB_TRY(make_operand_map(&mb, B, false, K, pitch_b, N, 1, 128));
-      return launch_gemm<false, 3, 1, 128, 3, false>(ma, mb, M, N, k_blocks, ep, st);
+      return launch_gemm<false, 3, 1, 128, 3, false>(ma, mb, M, N, k_blocks, ep, ldy, st);
     }
     NB_TRY(make_operand_map(&mb, B, false, K, pitch_b, N, 1, 64));
-    return launch_gemm<false, 3, 1, 64, 3, false>(ma, mb, M, N, k_blocks, ep, st);
+    return launch_gemm<false, 3, 1, 64, 3, false>(ma, mb, M, N, k_blocks, ep, ldy, st);
   }
   if (planes_a == 3 && planes_b == 3) {
     NB_TRY(make_operand_map(&mb, B, false, K, pitch_b, N, 3, 64));
-    return launch_gemm<false, 3, 3, 64, 3, true>(ma, mb, M, N, k_blocks, ep, st);
+    return launch_gemm<false, 3, 3, 64, 3, true>(ma, mb, M, N, k_blocks, ep, ldy, st);
   }
   return fail(NB200_ENOTIMPL, "no kernel for %d x %d operand planes", planes_a, planes_b);
 }
@@ -194,11 +181,10 @@ static int binary_affine(const float *x, const float *w, float *wb, float *alpha
   NB_TRY(split_rows_bf16(x, M, (int)K, Kp, 3, planes, st));
   GemmEpilogue ep{};
   ep.y = y;
-  ep.ldy = N;
   ep.scale = 1.0f;
   ep.col_scale = alpha;
   ep.col_bias = bias;
-  return run_gemm(false, 3, 1, planes, Kp, side, Kp, (int)M, (int)N, (int)K, ep, st);
+  return run_gemm(false, 3, 1, planes, Kp, side, Kp, (int)M, (int)N, (int)K, ep, N, st);
 }
 
 } // namespace nb200
@@ -257,10 +243,9 @@ int nb200_affine_codes_i8_f32(const int8_t *x_codes, const int8_t *w_codes, floa
   }
   GemmEpilogue ep{};
   ep.y = y;
-  ep.ldy = N;
   ep.scale = delta_x * delta_w;
   ep.col_bias = bias;
-  return run_gemm(true, 1, 1, xa, pitch_a, wt, Kp, (int)M, (int)N, (int)K, ep, st);
+  return run_gemm(true, 1, 1, xa, pitch_a, wt, Kp, (int)M, (int)N, (int)K, ep, N, st);
 }
 
 int nb200_affine_fxp8_f32(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias, float *y,
@@ -283,10 +268,9 @@ int nb200_affine_fxp8_f32(const float *xq, const float *wq, float delta_x, float
   NB_TRY(transpose_i8(wc, (int)K, (int)N, wt, Kp, st));
   GemmEpilogue ep{};
   ep.y = y;
-  ep.ldy = N;
   ep.scale = delta_x * delta_w;
   ep.col_bias = bias;
-  return run_gemm(true, 1, 1, xc, Kp, wt, Kp, (int)M, (int)N, (int)K, ep, st);
+  return run_gemm(true, 1, 1, xc, Kp, wt, Kp, (int)M, (int)N, (int)K, ep, N, st);
 }
 
 int nb200_affine_f32(const float *x, const float *w, const float *bias, float *y, int64_t rows, int64_t w_row,
@@ -308,9 +292,8 @@ int nb200_affine_f32(const float *x, const float *w, const float *bias, float *y
   NB_TRY(split_rows_bf16(wt32, N, (int)K, Kp, 3, base + xa, st));
   GemmEpilogue ep{};
   ep.y = y;
-  ep.ldy = N;
   ep.scale = 1.0f;
   ep.col_bias = bias;
-  return run_gemm(false, 3, 3, base, Kp, base + xa, Kp, (int)M, (int)N, (int)K, ep, st);
+  return run_gemm(false, 3, 3, base, Kp, base + xa, Kp, (int)M, (int)N, (int)K, ep, N, st);
 }
 }

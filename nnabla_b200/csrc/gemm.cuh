@@ -18,9 +18,10 @@
 // gives up stores a code in *status, raises the CTA's abort flag and all
 // roles fall through to the common teardown (TMEM is always freed).
 //
-// The B operand is fetched by a loader policy so that the same kernel serves
-// plain GEMM (2-D tiles of a [N, K] matrix) and implicit-GEMM convolution
-// (boxes of an NHWC activation tensor shifted by the filter tap).
+// A problem policy maps tile indices to operand coordinates and output
+// addresses, so that the same kernel serves plain GEMM (GemmProblem) and
+// implicit-GEMM convolution (ConvProblem: boxes of an NHWC activation tensor
+// shifted by the filter tap).
 #pragma once
 #include "common.cuh"
 #include "ptx.cuh"
@@ -38,30 +39,113 @@ constexpr int kStatusEpilogueTimeout = 0x103;
 
 struct GemmEpilogue {
   float *y;
-  int64_t ldy;            // elements between consecutive rows of y
-  int64_t y_batch_stride; // conv: elements between images (unused for GEMM)
   const float *row_scale, *col_scale, *row_bias, *col_bias;
   float scale;
 };
 
-struct GemmShape {
-  int M, N;     // logical extents of D
-  int k_blocks; // number of 128-byte K blocks
-  int m_tiles, n_tiles;
+// Per-tile coordinates produced by a problem policy.
+struct Tile {
+  int m0;      // first row of D (GEMM: row of x; convolution: output map)
+  int m_end;   // rows >= m_end are not stored
+  int n0;      // GEMM: first column of D; convolution: unused
+  int img0;    // convolution: first image of the pixel box
+  int oy0;     // convolution: first output row of the pixel box
+  int group;   // convolution: group index
 };
 
-// Loader for a plain [N, K] K-major B operand: 3-D map (K, N, plane).
-struct PlainBLoader {
-  __device__ __forceinline__ void load(const CUtensorMap *map, void *dst, uint64_t *bar, int kb, int n0, int plane,
-                                       int k_elems_per_block) const {
-    ptx::tma_load_3d(dst, map, bar, kb * k_elems_per_block, n0, plane);
+// ---- plain GEMM: A [planes][M][K], B [planes][N][K] --------------------------
+struct GemmProblem {
+  int M, N, kblocks, m_tiles, n_tiles, bn;
+  int64_t ldy;
+  __device__ __forceinline__ int num_tiles() const { return m_tiles * n_tiles; }
+  __device__ __forceinline__ int k_blocks() const { return kblocks; }
+  __device__ __forceinline__ uint32_t umma_n() const { return (uint32_t)bn; }
+  __device__ __forceinline__ uint32_t b_tx_bytes() const { return (uint32_t)bn * kRowBytes; }
+  __device__ __forceinline__ void decode(int tile, Tile &t) const {
+    t.m0 = (tile % m_tiles) * kTileM;
+    t.m_end = M;
+    t.n0 = (tile / m_tiles) * bn;
+    t.img0 = t.oy0 = t.group = 0;
+  }
+  __device__ __forceinline__ void load_a(const CUtensorMap *map, void *dst, uint64_t *bar, int kb, const Tile &t,
+                                         int plane, int epb) const {
+    ptx::tma_load_3d(dst, map, bar, kb * epb, t.m0, plane);
+  }
+  __device__ __forceinline__ void load_b(const CUtensorMap *map, void *dst, uint64_t *bar, int kb, const Tile &t,
+                                         int plane, int epb) const {
+    ptx::tma_load_3d(dst, map, bar, kb * epb, t.n0, plane);
+  }
+  // Address of D(row, first column of chunk c0) and the number of valid
+  // columns in the chunk; columns of a chunk are contiguous in y.
+  __device__ __forceinline__ float *chunk_ptr(const GemmEpilogue &ep, const Tile &t, int row, int c0, int &valid,
+                                              int &gcol) const {
+    gcol = t.n0 + c0;
+    valid = N - gcol;
+    return ep.y + (int64_t)row * ldy + gcol;
   }
 };
 
-template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkipSmallPairs, typename BLoader>
+// ---- implicit-GEMM convolution -------------------------------------------------
+// A = weight side-band [planes][Ko][taps * cblocks * E] (K ordered tap-major,
+// channel-minor), B = activation planes [planes][N][H][W][Ctot] (NHWC), D rows
+// = output maps, D columns = a box of n_box images x h_box output rows x Wo
+// output columns. One K block = one filter tap x E consecutive channels; its B
+// tile is one TMA box shifted by the tap (out-of-range rows/columns read as
+// zero = the padding).
+struct ConvProblem {
+  int Nimg, Ko, Kog, groups, Ho, Wo;
+  int h_box, n_box, tiles_h, tiles_n, m_tiles_g;
+  int kw, taps, cblocks;
+  int sh, sw, ph, pw, dh, dw;
+  int c_group_stride; // channel offset between groups in the activation planes
+  int n_run;          // UMMA N: pixels per box rounded up to 16
+  int pixels;         // n_box * h_box * Wo
+  __device__ __forceinline__ int num_tiles() const { return groups * m_tiles_g * tiles_h * tiles_n; }
+  __device__ __forceinline__ int k_blocks() const { return taps * cblocks; }
+  __device__ __forceinline__ uint32_t umma_n() const { return (uint32_t)n_run; }
+  __device__ __forceinline__ uint32_t b_tx_bytes() const { return (uint32_t)pixels * kRowBytes; }
+  __device__ __forceinline__ void decode(int tile, Tile &t) const {
+    const int mt = tile % m_tiles_g;
+    int r = tile / m_tiles_g;
+    const int g = r % groups;
+    r /= groups;
+    t.group = g;
+    t.m0 = g * Kog + mt * kTileM;
+    t.m_end = (g + 1) * Kog;
+    t.oy0 = (r % tiles_h) * h_box;
+    t.img0 = (r / tiles_h) * n_box;
+    t.n0 = 0;
+  }
+  __device__ __forceinline__ void load_a(const CUtensorMap *map, void *dst, uint64_t *bar, int kb, const Tile &t,
+                                         int plane, int epb) const {
+    ptx::tma_load_3d(dst, map, bar, kb * epb, t.m0, plane);
+  }
+  __device__ __forceinline__ void load_b(const CUtensorMap *map, void *dst, uint64_t *bar, int kb, const Tile &t,
+                                         int plane, int epb) const {
+    const int tap = kb / cblocks, cb = kb - tap * cblocks;
+    const int ky = tap / kw, kx = tap - ky * kw;
+    ptx::tma_load_5d(dst, map, bar, t.group * c_group_stride + cb * epb, kx * dw - pw, t.oy0 * sh - ph + ky * dh,
+                     t.img0, plane);
+  }
+  __device__ __forceinline__ float *chunk_ptr(const GemmEpilogue &ep, const Tile &t, int row, int c0, int &valid,
+                                              int &gcol) const {
+    // Columns of one image's box are contiguous in y (full output rows).
+    gcol = 0;
+    const int per_img = h_box * Wo;
+    const int nn = c0 / per_img, q = c0 - nn * per_img;
+    const int img = t.img0 + nn;
+    const int plane_left = (Ho - t.oy0) * Wo - q; // valid elements before the end of this output map
+    int v = per_img - q;                          // ... and before the end of this image's box
+    v = v < plane_left ? v : plane_left;
+    valid = (nn < n_box && img < Nimg) ? v : 0; // columns past the box are padding of the MMA shape
+    return ep.y + ((int64_t)img * Ko + row) * ((int64_t)Ho * Wo) + (int64_t)t.oy0 * Wo + q;
+  }
+};
+
+template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkipSmallPairs, typename Problem>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        GemmShape shape, GemmEpilogue ep, BLoader bload, int *status) {
+                        const Problem prob, const GemmEpilogue ep, int *status) {
   constexpr int kElemsPerBlock = kInt8 ? 128 : 64; // K elements per 128-byte row
   constexpr int kUmmaK = kInt8 ? 32 : 16;          // K elements per MMA (32 bytes)
   constexpr int kMmasPerBlock = kElemsPerBlock / kUmmaK;
@@ -70,7 +154,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   constexpr uint32_t kStageBytes = PA * kABytes + PB * kBBytes;
   constexpr uint32_t kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
-  constexpr uint32_t kIdesc = ptx::make_idesc(kInt8 ? 2u : 1u, 1u, kTileM, BN); // S8 and BF16 both encode as 1
 
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms.
@@ -85,7 +168,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = shape.m_tiles * shape.n_tiles;
+  const int num_tiles = prob.num_tiles();
+  const int k_blocks = prob.k_blocks();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -116,10 +200,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint32_t tx_bytes = PA * kABytes + PB * prob.b_tx_bytes();
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % shape.m_tiles) * kTileM;
-        const int n0 = (tile / shape.m_tiles) * BN;
-        for (int kb = 0; kb < shape.k_blocks; ++kb) {
+        Tile t;
+        prob.decode(tile, t);
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1u, abort_flag)) {
             if (*abort_flag == 0)
               atomicCAS(status, 0, kStatusProducerTimeout);
@@ -128,13 +213,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           uint8_t *st = smem + stage * kStageBytes;
-          ptx::mbar_expect_tx(full_bar + stage, kStageBytes);
+          ptx::mbar_expect_tx(full_bar + stage, tx_bytes);
 #pragma unroll
           for (int pa = 0; pa < PA; ++pa)
-            ptx::tma_load_3d(st + pa * kABytes, &map_a, full_bar + stage, kb * kElemsPerBlock, m0, pa);
+            prob.load_a(&map_a, st + pa * kABytes, full_bar + stage, kb, t, pa, kElemsPerBlock);
 #pragma unroll
           for (int pb = 0; pb < PB; ++pb)
-            bload.load(&map_b, st + PA * kABytes + pb * kBBytes, full_bar + stage, kb, n0, pb, kElemsPerBlock);
+            prob.load_b(&map_b, st + PA * kABytes + pb * kBBytes, full_bar + stage, kb, t, pb, kElemsPerBlock);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -149,6 +234,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
+      const uint32_t idesc = ptx::make_idesc(kInt8 ? 2u : 1u, 1u, kTileM, prob.umma_n()); // S8 and BF16 both encode as 1
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int buf = local & 1;
         const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
@@ -161,7 +247,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         uint32_t accumulate = 0;
-        for (int kb = 0; kb < shape.k_blocks; ++kb) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!ptx::mbar_wait(full_bar + stage, phase, abort_flag)) {
             if (*abort_flag == 0)
               atomicCAS(status, 0, kStatusMmaTimeout);
@@ -185,9 +271,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               for (int k = 0; k < kMmasPerBlock; ++k) {
                 // advancing 32 bytes along K inside the swizzle atom = +2 in the encoded address
                 if (kInt8)
-                  ptx::mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                  ptx::mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accumulate);
                 else
-                  ptx::mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, kIdesc, accumulate);
+                  ptx::mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accumulate);
                 accumulate = 1;
               }
             }
@@ -205,13 +291,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3; // TMEM lanes [32*quarter, 32*quarter + 32) are visible to this warp
+    const int n_cols = (int)prob.umma_n();
     int local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const int buf = local & 1;
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
-      const int m0 = (tile % shape.m_tiles) * kTileM;
-      const int n0 = (tile / shape.m_tiles) * BN;
+      Tile t;
+      prob.decode(tile, t);
       // All lanes poll; the verdict is made warp-uniform so that the aligned
       // TMEM loads below always run with the full warp.
       const bool got = ptx::mbar_wait(tmem_full + buf, buf_phase, abort_flag);
@@ -225,50 +312,60 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         break;
       }
       ptx::tc_fence_after_sync();
-      const int row = m0 + quarter * 32 + lane;
-      const bool row_ok = row < shape.M;
-      const float rs = (ep.row_scale && row_ok) ? ep.row_scale[row] * ep.scale : ep.scale;
+      const int row = t.m0 + quarter * 32 + lane;
+      const bool row_ok = row < t.m_end;
+      const float rs = (ep.row_scale && row_ok) ? __fmul_rn(ep.row_scale[row], ep.scale) : ep.scale;
       const float rb = (ep.row_bias && row_ok) ? ep.row_bias[row] : 0.0f;
-      float *yrow = ep.y + (int64_t)row * ep.ldy;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < n_cols; c0 += 32) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
         ptx::tmem_ld_wait();
-        if (row_ok) {
-          const int col0 = n0 + c0;
-          if (col0 + 32 <= shape.N && ((reinterpret_cast<uintptr_t>(yrow + col0) & 15) == 0)) {
+        if (!row_ok)
+          continue;
+        // A chunk of 32 columns may straddle the boundary between two
+        // contiguous runs of y (two images of a convolution box).
+        int j = 0;
+        while (j < 32) {
+          int valid, gcol;
+          float *dst = prob.chunk_ptr(ep, t, row, c0 + j, valid, gcol);
+          if (valid <= 0)
+            break;
+          const int run = (valid < 32 - j) ? valid : (32 - j);
+          if (run == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
+            for (int q = 0; q < 32; q += 4) {
               float o[4];
 #pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                const float acc = kInt8 ? (float)(int)r[j + t] : __uint_as_float(r[j + t]);
-                const float s = ep.col_scale ? __fmul_rn(rs, ep.col_scale[col0 + j + t]) : rs;
+              for (int u = 0; u < 4; ++u) {
+                const float acc = kInt8 ? (float)(int)r[q + u] : __uint_as_float(r[q + u]);
+                const float s = ep.col_scale ? __fmul_rn(rs, ep.col_scale[gcol + q + u]) : rs;
                 float v = __fmul_rn(acc, s);
                 if (ep.row_bias)
                   v = __fadd_rn(v, rb);
                 if (ep.col_bias)
-                  v = __fadd_rn(v, ep.col_bias[col0 + j + t]);
-                o[t] = v;
+                  v = __fadd_rn(v, ep.col_bias[gcol + q + u]);
+                o[u] = v;
               }
-              *reinterpret_cast<float4 *>(yrow + col0 + j) = make_float4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<float4 *>(dst + q) = make_float4(o[0], o[1], o[2], o[3]);
             }
           } else {
-            for (int j = 0; j < 32; ++j) {
-              const int col = col0 + j;
-              if (col < shape.N) {
-                const float acc = kInt8 ? (float)(int)r[j] : __uint_as_float(r[j]);
-                const float s = ep.col_scale ? __fmul_rn(rs, ep.col_scale[col]) : rs;
+#pragma unroll
+            for (int q = 0; q < 32; ++q) {
+              // static register indexing: q is the position inside the chunk
+              if (q >= j && q < j + run) {
+                const float acc = kInt8 ? (float)(int)r[q] : __uint_as_float(r[q]);
+                const float s = ep.col_scale ? __fmul_rn(rs, ep.col_scale[gcol + q - j]) : rs;
                 float v = __fmul_rn(acc, s);
                 if (ep.row_bias)
                   v = __fadd_rn(v, rb);
                 if (ep.col_bias)
-                  v = __fadd_rn(v, ep.col_bias[col]);
-                yrow[col] = v;
+                  v = __fadd_rn(v, ep.col_bias[gcol + q - j]);
+                dst[q - j] = v;
               }
             }
           }
+          j += run;
         }
       }
       ptx::tc_fence_before_sync();
@@ -310,6 +407,31 @@ int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, c
                  const uint64_t *strides_bytes, const uint32_t *box, const uint32_t *elem_strides);
 int device_status_word(int **status);
 int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch_a, const void *B, int64_t pitch_b,
-             int M, int N, int K, const GemmEpilogue &ep, cudaStream_t st);
+             int M, int N, int K, const GemmEpilogue &ep, int64_t ldy, cudaStream_t st);
+
+
+// Launches the contraction kernel for one problem: one persistent CTA per SM
+// (or per tile when there are fewer tiles than SMs).
+template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkip, typename Problem>
+inline int launch_contraction(const CUtensorMap &ma, const CUtensorMap &mb, const Problem &prob, int tiles,
+                       const GemmEpilogue &ep, cudaStream_t st) {
+  auto kernel = gemm_tcgen05_kernel<kInt8, PA, PB, BN, STAGES, kSkip, Problem>;
+  constexpr size_t smem = gemm_smem_bytes<kInt8, PA, PB, BN, STAGES>();
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  static bool configured[64];
+  int dev = 0;
+  NB_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    NB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev & 63] = true;
+  }
+  int *status = nullptr;
+  NB_TRY(device_status_word(&status));
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kernel<<<grid, kGemmThreads, smem, st>>>(ma, mb, prob, ep, status);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
 
 } // namespace nb200

@@ -153,29 +153,33 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict
   }
 }
 
-// fp32 NCHW -> planes of NHWC with the channel extent padded to c_pad:
-// out[plane][n][h][w][c_pad]. Tile transpose through shared memory: reads
-// coalesced along w (hw), writes coalesced along c.
+// fp32 NCHW -> planes of NHWC: out[plane][n][hw][ctot], where channel c of
+// group g lands at g * c_pad_g + (c - g * Cg) and every other slot is zero.
+// Tile transpose through shared memory: reads coalesced along hw, writes
+// coalesced along the channel slots. OutT = bf16 (PLANES pieces) or int8
+// (codes of values that are multiples of delta).
 template <typename OutT, int PLANES>
-__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restrict__ x, int C, int HW, int c_pad,
-                                                           OutT *__restrict__ out, int64_t plane_stride,
-                                                           float inv_delta) {
+__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restrict__ x, int C, int HW, int groups,
+                                                           int Cg, int c_pad_g, int ctot, OutT *__restrict__ out,
+                                                           int64_t plane_stride, float inv_delta) {
   __shared__ float tile[32][33];
   const int n = blockIdx.z;
-  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int p0 = blockIdx.x * 32, d0 = blockIdx.y * 32; // d = destination channel slot
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
-  for (int cc = ty; cc < 32; cc += 8) {
-    const int c = c0 + cc, p = p0 + tx;
-    tile[cc][tx] = (c < C && p < HW) ? x[((int64_t)n * C + c) * HW + p] : 0.0f;
+  for (int dd = ty; dd < 32; dd += 8) {
+    const int d = d0 + dd, p = p0 + tx;
+    const int g = d / c_pad_g, cc = d - g * c_pad_g;
+    const bool live = d < ctot && g < groups && cc < Cg && p < HW;
+    tile[dd][tx] = live ? x[((int64_t)n * C + (g * Cg + cc)) * HW + p] : 0.0f;
   }
   __syncthreads();
   for (int pp = ty; pp < 32; pp += 8) {
-    const int p = p0 + pp, c = c0 + tx;
-    if (p < HW && c < c_pad) {
+    const int p = p0 + pp, d = d0 + tx;
+    if (p < HW && d < ctot) {
       const float v = tile[tx][pp];
-      const int64_t dst = ((int64_t)n * HW + p) * c_pad + c;
+      const int64_t dst = ((int64_t)n * HW + p) * ctot + d;
       if constexpr (sizeof(OutT) == 1) {
-        out[dst] = (OutT)__float2int_rn(__fmul_rn(v, inv_delta)); // v is k * delta exactly
+        out[dst] = (OutT)__float2int_rn(__fmul_rn(v, inv_delta)); // v is k * delta
       } else {
         __nv_bfloat16 h, m, l;
         split3(v, h, m, l);
@@ -281,22 +285,21 @@ int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes,
   return NB200_OK;
 }
 
-int nchw_to_nhwc_bf16(const float *x, int N, int C, int HW, int c_pad, int planes, void *out, cudaStream_t st) {
-  const dim3 grid((HW + 31) / 32, (c_pad + 31) / 32, N);
-  const int64_t ps = (int64_t)N * HW * c_pad;
-  __nv_bfloat16 *o = reinterpret_cast<__nv_bfloat16 *>(out);
-  if (planes == 3)
-    nchw_to_nhwc_kernel<__nv_bfloat16, 3><<<grid, 256, 0, st>>>(x, C, HW, c_pad, o, ps, 0.f);
-  else
-    nchw_to_nhwc_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(x, C, HW, c_pad, o, ps, 0.f);
-  NB_LAUNCH_CHECK();
-  return NB200_OK;
-}
-
-int nchw_to_nhwc_i8(const float *x, int N, int C, int HW, int c_pad, float delta, void *out, cudaStream_t st) {
-  const dim3 grid((HW + 31) / 32, (c_pad + 31) / 32, N);
-  nchw_to_nhwc_kernel<int8_t, 1><<<grid, 256, 0, st>>>(x, C, HW, c_pad, reinterpret_cast<int8_t *>(out), 0,
-                                                       1.0f / delta);
+int nchw_to_nhwc_planes(const float *x, int N, int C, int HW, int groups, int Cg, int c_pad_g, int ctot, int planes,
+                        float delta, void *out, cudaStream_t st) {
+  const dim3 grid((HW + 31) / 32, (ctot + 31) / 32, N);
+  NB_CHECK(N <= 65535, NB200_ENOTIMPL, "batch larger than 65535");
+  const int64_t ps = (int64_t)N * HW * ctot;
+  if (planes == 0) {
+    nchw_to_nhwc_kernel<int8_t, 1><<<grid, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
+                                                         reinterpret_cast<int8_t *>(out), 0, 1.0f / delta);
+  } else if (planes == 3) {
+    nchw_to_nhwc_kernel<__nv_bfloat16, 3><<<grid, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
+                                                                reinterpret_cast<__nv_bfloat16 *>(out), ps, 0.f);
+  } else {
+    nchw_to_nhwc_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
+                                                                reinterpret_cast<__nv_bfloat16 *>(out), ps, 0.f);
+  }
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }

@@ -15,9 +15,11 @@ int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to,
                   int64_t side_pitch, int c_pad, bool int8, cudaStream_t st);
 // fp32 [rows, K] -> bf16 [planes][rows][Kp] (planes = 1 or 3; hi, mid, lo).
 int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st);
-// fp32 NCHW -> bf16 [planes][N][HW][c_pad] / int8 [N][HW][c_pad] (values k*delta -> k).
-int nchw_to_nhwc_bf16(const float *x, int N, int C, int HW, int c_pad, int planes, void *out, cudaStream_t st);
-int nchw_to_nhwc_i8(const float *x, int N, int C, int HW, int c_pad, float delta, void *out, cudaStream_t st);
+// fp32 NCHW -> NHWC planes [planes][N][HW][ctot] (planes = 3 or 1: bf16 pieces;
+// planes = 0: int8 codes of multiples of delta). Channel c of group g is stored
+// at slot g * c_pad_g + (c - g * Cg); all other slots are zero.
+int nchw_to_nhwc_planes(const float *x, int N, int C, int HW, int groups, int Cg, int c_pad_g, int ctot, int planes,
+                        float delta, void *out, cudaStream_t st);
 // int8 [R, C] -> [C][pitch].
 int transpose_i8(const int8_t *src, int R, int C, int8_t *dst, int64_t pitch, cudaStream_t st);
 // fp32 [R, C] -> [C][R].

@@ -228,3 +228,103 @@ def affine_from_codes(x_codes, w_codes, delta_x, delta_w, bias=None):
                C.ptr(bias), C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(K), ctypes.c_int64(N),
                C.stream_ptr(x_codes.device))
     return y
+
+
+# ---------------------------------------------------------------------------
+# Convolutions
+# ---------------------------------------------------------------------------
+
+def _conv_geometry(x, w, bias, base_axis, pad, stride, dilation, group):
+    """Shape rules of Convolution::setup_impl (src/nbla/function/generic/convolution.cpp:40-158)."""
+    if base_axis < 0:
+        base_axis += x.dim()
+    if not 0 <= base_axis < x.dim() - 1:
+        raise RuntimeError("base_axis must be less than ndim - 1 of inputs[0]. base_axis: %d >= ndim of inputs[0] "
+                           "- 1: %d." % (base_axis, x.dim() - 1))
+    spatial = x.dim() - base_axis - 1
+    if w.dim() != 2 + spatial:
+        raise RuntimeError("Weights must be a tensor more than 3D.")
+    if spatial != 2:
+        raise C.NB200Error(4, "only 2-D convolution is implemented (got %d spatial dims)" % spatial)
+    pad = (0,) * spatial if pad is None else tuple(pad)
+    stride = (1,) * spatial if stride is None else tuple(stride)
+    dilation = (1,) * spatial if dilation is None else tuple(dilation)
+    for name, v in (("pad", pad), ("stride", stride), ("dilation", dilation)):
+        if len(v) != spatial:
+            raise RuntimeError("%s size mismatch. %s size: %d != spatial dims: %d." % (name, name, len(v), spatial))
+    batch = 1
+    for s in x.shape[:base_axis]:
+        batch *= int(s)
+    Cin, H, W = (int(s) for s in x.shape[base_axis:])
+    Ko, Cg, kh, kw = (int(s) for s in w.shape)
+    if Cin % group != 0:
+        raise RuntimeError("Number of input channel needs to be divisible by group. Input channel: %d, group: %d."
+                           % (Cin, group))
+    if Ko % group != 0:
+        raise RuntimeError("Number of output channel needs to be divisible by group. Output channel: %d, group: %d."
+                           % (Ko, group))
+    if Cin // group != Cg:
+        raise RuntimeError("Number of grouped channel mismatch. Input: %d != Weights[1]: %d." % (Cin // group, Cg))
+    if bias is not None and (bias.dim() != 1 or int(bias.shape[0]) != Ko):
+        raise RuntimeError("Shape of bias(inputs[2]) and weights(inputs[1]) mismatch.")
+    outs = []
+    for i, (inp, k) in enumerate(((H, kh), (W, kw))):
+        kk = dilation[i] * (k - 1) + 1
+        o = (inp + 2 * pad[i] - kk) // stride[i] + 1
+        if inp + 2 * pad[i] - kk < 0 or o <= 0:
+            raise RuntimeError("Invalid configuration of convolution at %d-th spatial dimension. {input:%d, "
+                               "kernel:%d, pad:%d, stride:%d, dilation:%d}." % (i, inp, k, pad[i], stride[i],
+                                                                              dilation[i]))
+        outs.append(o)
+    out_shape = tuple(x.shape[:base_axis]) + (Ko, outs[0], outs[1])
+    return batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape
+
+
+def _binary_convolution(entry, x, weight, binary_weight, alpha, bias, base_axis, pad, stride, dilation, group,
+                        quantize_zero_to, outputs, fixed_point_delta):
+    x, weight = _check_input(x), _check_input(weight, "weight")
+    binary_weight = _check_input(binary_weight, "binary_weight")
+    bias = _check_input(bias, "bias") if bias is not None else None
+    batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
+        x, weight, bias, base_axis, pad, stride, dilation, group)
+    _same_shape(weight, binary_weight, "float vs binary")
+    y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
+    args = [C.ptr(x), C.ptr(weight), C.ptr(binary_weight)]
+    if alpha is not None:
+        args.append(C.ptr(alpha))
+    args += [C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1], stride[0], stride[1], dilation[0],
+             dilation[1], int(group), C.c_float(quantize_zero_to), C.c_float(fixed_point_delta or 0.0),
+             C.stream_ptr(x.device)]
+    with torch.cuda.device(x.device):
+        C.call(entry, *args)
+    return y
+
+
+def binary_weight_convolution(x, weight, binary_weight, alpha, bias=None, base_axis=1, pad=None, stride=None,
+                              dilation=None, group=1, quantize_zero_to=1.0, n_outputs=-1, outputs=None,
+                              fixed_point_delta=None):
+    """Binary Weight Convolution (function_bases.binary_weight_convolution).
+
+    Forward of BinaryWeightConvolution
+    (src/nbla/function/generic/binary_weight_convolution.cpp:72-117). Writes
+    `binary_weight` and `alpha`. fixed_point_delta=d declares that x is the
+    output of fixed_point_quantize with step d and n <= 8, which selects the
+    exact int8 contraction.
+    """
+    alpha = _check_input(alpha, "alpha")
+    if alpha.numel() != int(weight.shape[0]):
+        raise RuntimeError("Size of alpha must be equal to the number of output maps.")
+    return _binary_convolution("nb200_binary_weight_convolution_f32", x, weight, binary_weight, alpha, bias,
+                               base_axis, pad, stride, dilation, group, quantize_zero_to, outputs, fixed_point_delta)
+
+
+def binary_connect_convolution(x, weight, binary_weight, bias=None, base_axis=1, pad=None, stride=None,
+                               dilation=None, group=1, quantize_zero_to=1.0, n_outputs=-1, outputs=None,
+                               fixed_point_delta=None):
+    """Binary Connect Convolution (function_bases.binary_connect_convolution).
+
+    Forward of BinaryConnectConvolution
+    (src/nbla/function/generic/binary_connect_convolution.cpp:67-80).
+    """
+    return _binary_convolution("nb200_binary_connect_convolution_f32", x, weight, binary_weight, None, bias,
+                               base_axis, pad, stride, dilation, group, quantize_zero_to, outputs, fixed_point_delta)

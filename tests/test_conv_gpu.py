@@ -1,0 +1,111 @@
+"""GPU parity of the binary convolutions (implicit GEMM on tcgen05) through the
+C ABI: signs bit-exact, alpha to fp32 summation error, outputs within 1e-5 of
+the output RMS of the oracle / the reference's golden outputs."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from golden_util import bits, golden
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a, np.float32)).cuda()
+
+
+@pytest.fixture(scope="module")
+def F():
+    from nnabla_b200 import _capi, functions
+    _capi.call("nb200_check_device")
+    return functions
+
+
+def run_bwc(F, x, w, b, pad, stride, dil, grp, qzt=1.0, delta=None):
+    wb = torch.zeros(w.shape, device="cuda")
+    al = torch.zeros(w.shape[0], device="cuda")
+    y = F.binary_weight_convolution(dev(x), dev(w), wb, al, dev(b) if b is not None else None, 1, pad, stride, dil,
+                                    grp, qzt, fixed_point_delta=delta)
+    F.check_device_status()
+    return y.cpu().numpy(), wb.cpu().numpy(), al.cpu().numpy()
+
+
+@pytest.mark.parametrize("i", range(len(cases.CONV_CASES)))
+def test_binary_convolution_golden(F, i):
+    g = golden()
+    xs, ws, pad, stride, dil, grp = cases.CONV_CASES[i]
+    x, w, b = cases.conv_inputs(xs, ws, with_zeros=True)
+    y, wb, al = run_bwc(F, x, w, b, pad, stride, dil, grp)
+    assert np.array_equal(bits(wb), bits(g[f"bwc{i}/out_wb"]))
+    np.testing.assert_allclose(al, g[f"bwc{i}/out_alpha"], rtol=2e-6)
+    assert y.shape == g[f"bwc{i}/out_y"].shape
+    assert cases.rel_rms(y, g[f"bwc{i}/out_y"]) < TOL
+    wbc = torch.zeros(w.shape, device="cuda")
+    yc = F.binary_connect_convolution(dev(x), dev(w), wbc, dev(b), 1, pad, stride, dil, grp, 1.0)
+    F.check_device_status()
+    assert np.array_equal(bits(wbc.cpu().numpy()), bits(g[f"bcc{i}/out_wb"]))
+    assert cases.rel_rms(yc.cpu().numpy(), g[f"bcc{i}/out_y"]) < TOL
+
+
+RESNET_LIKE = [
+    # N, C, H, W, Ko, k, pad, stride
+    (3, 64, 56, 56, 64, 3, 1, 1),
+    (2, 64, 56, 56, 128, 3, 1, 2),
+    (2, 64, 56, 56, 128, 1, 0, 2),
+    (3, 128, 28, 28, 128, 3, 1, 1),
+    (2, 256, 14, 14, 256, 3, 1, 1),
+    (7, 512, 7, 7, 512, 3, 1, 1),
+    (5, 256, 14, 14, 512, 3, 1, 2),
+    (2, 24, 9, 11, 40, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("N,C,H,W,Ko,k,pad,stride", RESNET_LIKE)
+@pytest.mark.parametrize("int8", [False, True])
+def test_binary_weight_convolution_shapes(F, N, C, H, W, Ko, k, pad, stride, int8):
+    rng = np.random.RandomState(N * 1000 + C + Ko + k)
+    x = np.maximum(rng.randn(N, C, H, W), 0).astype(np.float32)
+    delta = None
+    if int8:
+        delta = 2.0 ** -4
+        x = oracle.fixed_point_quantize(x, True, 8, delta)
+    w = (rng.randn(Ko, C, k, k) * np.sqrt(2.0 / (C * k * k))).astype(np.float32)
+    b = rng.randn(Ko).astype(np.float32)
+    y, wb, al = run_bwc(F, x, w, b, (pad, pad), (stride, stride), (1, 1), 1, 1.0, delta)
+    wy, wwb, wal = oracle.binary_weight_convolution(x, w, b, (pad, pad), (stride, stride), (1, 1), 1, 1.0)
+    assert np.array_equal(bits(wb), bits(wwb))
+    np.testing.assert_allclose(al, np.abs(w.astype(np.float64)).reshape(Ko, -1).mean(1), rtol=1e-6)
+    assert y.shape == wy.shape
+    err = cases.rel_rms(y, wy)
+    print("rel-RMS", err)
+    assert err < TOL
+
+
+def test_binary_weight_convolution_config4_reduced(F):
+    """BASELINE configs[3] with 4 images instead of 128 (same per-image work)."""
+    rng = np.random.RandomState(0)
+    x = np.maximum(rng.randn(4, 256, 28, 28), 0).astype(np.float32)
+    w = (rng.randn(256, 256, 3, 3) * np.sqrt(2.0 / 2304)).astype(np.float32)
+    y, wb, al = run_bwc(F, x, w, np.zeros(256, np.float32), (1, 1), (1, 1), (1, 1), 1)
+    wy, wwb, wal = oracle.binary_weight_convolution(x, w, None, (1, 1), (1, 1), (1, 1), 1, 1.0)
+    assert np.array_equal(bits(wb), bits(wwb))
+    err = cases.rel_rms(y, wy)
+    y64 = oracle.convolution(x, wwb * wal.reshape(-1, 1, 1, 1), None, (1, 1), f64=True)
+    print("config4 rel-RMS vs fp32 oracle %.3g, GPU vs fp64 %.3g, oracle vs fp64 %.3g"
+          % (err, cases.rel_rms(y, y64), cases.rel_rms(wy, y64)))
+    assert err < TOL
+
+
+def test_conv_errors(F):
+    x = torch.zeros(1, 4, 8, 8, device="cuda")
+    w = torch.zeros(6, 4, 3, 3, device="cuda")
+    al = torch.zeros(6, device="cuda")
+    with pytest.raises(RuntimeError, match="divisible by group"):
+        F.binary_weight_convolution(x, w, torch.zeros_like(w), al, group=3)
+    with pytest.raises(RuntimeError, match="Invalid configuration"):
+        F.binary_weight_convolution(x, torch.zeros(6, 4, 9, 9, device="cuda"), torch.zeros(6, 4, 9, 9, device="cuda"), al)
+    with pytest.raises(RuntimeError, match="alpha"):
+        F.binary_weight_convolution(x, w, torch.zeros_like(w), torch.zeros(5, device="cuda"))
