@@ -116,6 +116,28 @@ int nb200_pow2_quantize_f32_host(const float *x, float *y, size_t size, int sign
 int nb200_min_max_quantize_f32(const float *x, const int64_t *x_shape, int ndim, float *qr_min, float *qr_max,
                                const float *ql_min, const float *ql_max, const int64_t *q_shape, float decay,
                                int x_min_max, int ema, float eps, float *y, float *scale, void *stream);
+/* Same computation and arguments as nb200_min_max_quantize_f32, for callers
+ * that must not allocate. It has no counterpart in the reference. Two kinds of
+ * host need it: frameworks that own every byte of device memory through their
+ * own allocator (nnabla's caching allocator is one: a function that goes to the
+ * driver for memory behind its back breaks its accounting and can fail when
+ * the pool has taken the whole device), and serving loops that cannot afford
+ * the locks and device synchronisation an allocation call may bring. This
+ * entry point never calls cudaMalloc, cudaMallocAsync, cudaFree or any other
+ * allocating routine: its scratch (5 floats per quantization range) is a
+ * fixed 80 KiB array inside the library image, so every GPU that loads the
+ * library holds that array until the process exits.
+ *  - Limit: at most 4096 quantization ranges (elements of qr_min) per call;
+ *    more is refused with NB200_EVALUE.
+ *  - The first call on each device looks up the array's device address (the
+ *    device must be current); make that first call before any stream capture.
+ *  - All calls on a device share the one array. Calls that may overlap on the
+ *    GPU (different streams, no ordering between them) race on it; serialise
+ *    them or use nb200_min_max_quantize_f32. */
+int nb200_min_max_quantize_f32_noalloc(const float *x, const int64_t *x_shape, int ndim, float *qr_min,
+                                       float *qr_max, const float *ql_min, const float *ql_max,
+                                       const int64_t *q_shape, float decay, int x_min_max, int ema, float eps,
+                                       float *y, float *scale, void *stream);
 /* Host variant for per-tensor ranges with x_min_max == 0 (q tensors of one
  * element each, host pointers; qr_max is updated by the eps nudge). */
 int nb200_min_max_quantize_f32_host(const float *x, size_t size, float *qr_min, float *qr_max, const float *ql_min,

@@ -658,6 +658,36 @@ int minmax_run(const float *x, const MinMaxView &V, float *qr_min, float *qr_max
   return launch_elementwise(x, y, V.size, op, st);
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant of MinMaxQuantize: the 5*Q floats of scratch live in
+// a fixed array in device global memory that belongs to the library image
+// (every GPU that loads the library carries it until the process exits).
+// Host code must not pass the array's name to a kernel: on the host that name
+// is only a handle. The device address is looked up once per device with
+// cudaGetSymbolAddress while that device is current, and the kernels receive
+// that address.
+// ---------------------------------------------------------------------------
+constexpr size_t kNoAllocMaxRanges = 4096; // quantization ranges (elements of qr_min) per call
+static __device__ __align__(256) float g_minmax_static_scratch[5 * kNoAllocMaxRanges];
+
+std::mutex g_static_scratch_mutex;
+float *g_static_scratch_addr[64];
+
+int static_scratch_for_current_device(float **out) {
+  int dev = 0;
+  NB_CUDA(cudaGetDevice(&dev));
+  NB_CHECK(dev >= 0 && dev < 64, NB200_EVALUE, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void *p = nullptr;
+    NB_CUDA(cudaGetSymbolAddress(&p, g_minmax_static_scratch));
+    NB_CHECK(p != nullptr, NB200_ECUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_scratch_addr[dev] = static_cast<float *>(p);
+  }
+  *out = g_static_scratch_addr[dev];
+  return NB200_OK;
+}
+
 // ---- chunk callbacks of the _host variants ---------------------------------
 struct FxpHostArgs {
   int sign, n;
@@ -737,6 +767,28 @@ int nb200_min_max_quantize_f32(const float *x, const int64_t *x_shape, int ndim,
     return rc;
   NB_CUDA(e);
   return NB200_OK;
+}
+
+int nb200_min_max_quantize_f32_noalloc(const float *x, const int64_t *x_shape, int ndim, float *qr_min,
+                                       float *qr_max, const float *ql_min, const float *ql_max,
+                                       const int64_t *q_shape, float decay, int x_min_max, int ema, float eps,
+                                       float *y, float *scale, void *stream) {
+  NB_CHECK(x_shape && q_shape, NB200_EVALUE, "null shape pointer");
+  MinMaxView V;
+  NB_TRY(minmax_view(x_shape, q_shape, ndim, &V));
+  NB_CHECK(V.Q <= kNoAllocMaxRanges, NB200_EVALUE,
+           "nb200_min_max_quantize_f32_noalloc handles at most %zu quantization ranges per call (got %zu); "
+           "use nb200_min_max_quantize_f32 for more",
+           kNoAllocMaxRanges, V.Q);
+  NB_CHECK(qr_min && qr_max && ql_min && ql_max, NB200_EVALUE, "null range pointer");
+  NB_CHECK(V.size == 0 || (x && y), NB200_EVALUE, "null data pointer");
+  float *scratch = nullptr;
+  NB_TRY(static_scratch_for_current_device(&scratch));
+  // The min/max slots are re-initialised by minmax_run when they are used and
+  // the parameter slots are fully overwritten, so nothing of the previous
+  // call's contents is read.
+  return minmax_run(x, V, qr_min, qr_max, ql_min, ql_max, decay, x_min_max, ema, eps, y, scale, scratch,
+                    as_stream(stream));
 }
 
 int nb200_min_max_quantize_f32_host(const float *x, size_t size, float *qr_min, float *qr_max, const float *ql_min,
