@@ -219,6 +219,39 @@ int nb200_binary_connect_convolution_f32(const float *x, const float *w, float *
                                          int dilation_h, int dilation_w, int group, float quantize_zero_to,
                                          float activation_delta, void *stream);
 
+/* ---- companions: the other functions of a binary-weight ResNet-18 graph ---- */
+/* Needed so the whole graph runs under one context with no CPU fallback
+ * (nnabla's NNP loader also probes a context with ReLU before using it,
+ * python/src/nnabla/utils/load.py:95-103). All bit-identical to the
+ * reference's CPU code for non-NaN input. */
+
+/* BatchNormalization<float>::forward_impl_global
+ * (src/nbla/function/generic/batch_normalization.cpp:228-260), batch_stat =
+ * false, one normalised axis: x viewed as [outer, channels, inner];
+ * y = (x - mean) * gamma / sqrt(var + eps) + beta in that operation order.
+ * beta / gamma may be NULL (no_bias / no_scale). */
+int nb200_batch_normalization_inference_f32(const float *x, const float *beta, const float *gamma, const float *mean,
+                                            const float *var, float *y, int64_t outer, int64_t channels,
+                                            int64_t inner, float eps, void *stream);
+/* ReLU<float>::forward_impl (src/nbla/function/generic/relu.cpp). x == y allowed. */
+int nb200_relu_f32(const float *x, float *y, size_t size, void *stream);
+/* Add2<float>::forward_impl (src/nbla/function/generic/add2.cpp), equal shapes. */
+int nb200_add2_f32(const float *a, const float *b, float *y, size_t size, void *stream);
+/* MaxPooling<float>::forward_impl (src/nbla/function/generic/max_pooling.cpp:140-191),
+ * 2-D, x [maps, height, width]; output extent by base_pooling.cpp:59. */
+int nb200_max_pooling_f32(const float *x, float *y, int64_t maps, int height, int width, int kernel_h, int kernel_w,
+                          int stride_h, int stride_w, int pad_h, int pad_w, int ignore_border, void *stream);
+/* GlobalAveragePooling<float>::forward_impl
+ * (src/nbla/function/generic/global_average_pooling.cpp): x [maps, spatial] -> y [maps]. */
+int nb200_global_average_pooling_f32(const float *x, float *y, int64_t maps, int64_t spatial, void *stream);
+/* Convolution<float>::forward_impl (src/nbla/function/generic/convolution.cpp:160-197)
+ * in full precision for layers with few input channels (the network stem):
+ * direct convolution, products accumulated in the order of the reference's
+ * im2col rows (channel, kernel row, kernel column). group == 1. */
+int nb200_convolution_f32(const float *x, const float *w, const float *bias, float *y, int batch, int channels,
+                          int height, int width, int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w,
+                          int stride_h, int stride_w, int dilation_h, int dilation_w, int group, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

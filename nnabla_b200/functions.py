@@ -328,3 +328,120 @@ def binary_connect_convolution(x, weight, binary_weight, bias=None, base_axis=1,
     """
     return _binary_convolution("nb200_binary_connect_convolution_f32", x, weight, binary_weight, None, bias,
                                base_axis, pad, stride, dilation, group, quantize_zero_to, outputs, fixed_point_delta)
+
+
+# ---------------------------------------------------------------------------
+# Companion functions of a binary-weight ResNet-18 graph
+# ---------------------------------------------------------------------------
+
+def convolution(x, weight, bias=None, base_axis=1, pad=None, stride=None, dilation=None, group=1,
+                channel_last=False, n_outputs=-1, outputs=None):
+    """Convolution (function_bases.convolution; src/nbla/function/generic/convolution.cpp:160-197),
+    full precision, for layers with few input channels (the network stem)."""
+    if channel_last:
+        raise C.NB200Error(4, "channel_last=True is not supported (nor by the reference's CPU Convolution)")
+    x, weight = _check_input(x), _check_input(weight, "weight")
+    bias = _check_input(bias, "bias") if bias is not None else None
+    batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
+        x, weight, bias, base_axis, pad, stride, dilation, group)
+    y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
+    with torch.cuda.device(x.device):
+        C.call("nb200_convolution_f32", C.ptr(x), C.ptr(weight), C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw,
+               pad[0], pad[1], stride[0], stride[1], dilation[0], dilation[1], int(group), C.stream_ptr(x.device))
+    return y
+
+
+def batch_normalization(x, beta, gamma, mean, variance, axes=[1], decay_rate=0.9, eps=1e-05, batch_stat=True,
+                        output_stat=False, n_outputs=None):
+    """Batch normalization (python/src/nnabla/functions.py batch_normalization), inference only:
+    BatchNormalization::forward_impl_global (src/nbla/function/generic/batch_normalization.cpp:228-260)."""
+    if batch_stat:
+        raise C.NB200Error(4, "batch_stat=True (training statistics) is outside the forward inference path")
+    x = _check_input(x)
+    axes = list(axes)
+    if len(axes) != 1:
+        raise C.NB200Error(4, "one normalised axis is supported (got axes=%s)" % (axes,))
+    ax = axes[0] + x.dim() if axes[0] < 0 else axes[0]
+    Cn = int(x.shape[ax])
+    outer = 1
+    for s in x.shape[:ax]:
+        outer *= int(s)
+    inner = x.numel() // max(outer * Cn, 1)
+    params = []
+    for t, nm in ((beta, "beta"), (gamma, "gamma"), (mean, "mean"), (variance, "variance")):
+        if t is None:
+            params.append(None)
+            continue
+        t = _check_input(t, nm)
+        if t.numel() != Cn:
+            raise RuntimeError("%s must have %d elements (shape of the normalised axis)" % (nm, Cn))
+        params.append(t)
+    if params[2] is None or params[3] is None:
+        raise RuntimeError("mean and variance are required")
+    y = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        C.call("nb200_batch_normalization_inference_f32", C.ptr(x), C.ptr(params[0]), C.ptr(params[1]),
+               C.ptr(params[2]), C.ptr(params[3]), C.ptr(y), ctypes.c_int64(outer), ctypes.c_int64(Cn),
+               ctypes.c_int64(inner), C.c_float(eps), C.stream_ptr(x.device))
+    return y
+
+
+def relu(x, inplace=False, n_outputs=-1, outputs=None):
+    """ReLU (function_bases.relu; src/nbla/function/generic/relu.cpp)."""
+    x = _check_input(x)
+    y = x if inplace else _output_like(x, outputs)
+    with torch.cuda.device(x.device):
+        C.call("nb200_relu_f32", C.ptr(x), C.ptr(y), C.size_t(x.numel()), C.stream_ptr(x.device))
+    return y
+
+
+def add2(x0, x1, inplace=False, n_outputs=-1, outputs=None):
+    """Add2 (function_bases.add2; src/nbla/function/generic/add2.cpp), equal shapes."""
+    x0, x1 = _check_input(x0, "x0"), _check_input(x1, "x1")
+    if tuple(x0.shape) != tuple(x1.shape):
+        raise C.NB200Error(4, "broadcasting add2 is not implemented: shapes %s and %s" % (tuple(x0.shape),
+                                                                                         tuple(x1.shape)))
+    y = x0 if inplace else _output_like(x0, outputs)
+    with torch.cuda.device(x0.device):
+        C.call("nb200_add2_f32", C.ptr(x0), C.ptr(x1), C.ptr(y), C.size_t(x0.numel()), C.stream_ptr(x0.device))
+    return y
+
+
+def max_pooling(x, kernel, stride=None, ignore_border=True, pad=None, channel_last=False, n_outputs=-1,
+                outputs=None):
+    """Max pooling (function_bases.max_pooling; src/nbla/function/generic/max_pooling.cpp:140-191), 2-D."""
+    if channel_last:
+        raise C.NB200Error(4, "channel_last=True is not supported (nor by the reference's CPU pooling)")
+    x = _check_input(x)
+    kernel = tuple(kernel)
+    if len(kernel) != 2:
+        raise C.NB200Error(4, "2D Pooling only")
+    stride = kernel if stride is None else tuple(stride)
+    pad = (0, 0) if pad is None else tuple(pad)
+    if len(stride) != 2 or len(pad) != 2:
+        raise RuntimeError("Size of kernel and pad/stride must be same.")
+    H, W = int(x.shape[-2]), int(x.shape[-1])
+    maps = x.numel() // max(H * W, 1)
+    Ho = (H + pad[0] - (kernel[0] - pad[0] if ignore_border else 1)) // stride[0] + 1
+    Wo = (W + pad[1] - (kernel[1] - pad[1] if ignore_border else 1)) // stride[1] + 1
+    y = torch.empty(tuple(x.shape[:-2]) + (Ho, Wo), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        C.call("nb200_max_pooling_f32", C.ptr(x), C.ptr(y), ctypes.c_int64(maps), H, W, kernel[0], kernel[1],
+               stride[0], stride[1], pad[0], pad[1], int(bool(ignore_border)), C.stream_ptr(x.device))
+    return y
+
+
+def global_average_pooling(x, n_outputs=-1, outputs=None):
+    """Global average pooling (function_bases.global_average_pooling;
+    src/nbla/function/generic/global_average_pooling.cpp): [N, C, ...] -> [N, C, 1, 1]."""
+    x = _check_input(x)
+    if x.dim() < 2:
+        raise RuntimeError("GlobalAveragePooling averages across the channel, so the input's shape must have a "
+                           "dimension equal to or larger than 2. actual: %d" % x.dim())
+    N, Cn = int(x.shape[0]), int(x.shape[1])
+    S = x.numel() // max(N * Cn, 1)
+    y = torch.empty((N, Cn, 1, 1), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        C.call("nb200_global_average_pooling_f32", C.ptr(x), C.ptr(y), ctypes.c_int64(N * Cn), ctypes.c_int64(S),
+               C.stream_ptr(x.device))
+    return y

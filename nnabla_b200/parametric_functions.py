@@ -1,0 +1,165 @@
+"""Host-side mirror of `nnabla.parametric_functions` for the quantized-layer path.
+
+Same function names, argument order, defaults and parameter names ("W", "Wb",
+"alpha", "b", "beta", "gamma", "mean", "var" under the scopes "bwn_conv",
+"bwn_affine", "bicon_conv", "bicon_affine", "conv", "affine", "bn") as
+python/src/nnabla/parametric_functions.py:129, :319-485, :563, :946-1117,
+:1815, so a network definition written against `PF.*` reads the same here.
+Parameters live in a scoped registry like nnabla's (parameter.py:260-355) and
+are torch CUDA tensors.
+"""
+import contextlib
+from collections import OrderedDict
+
+import numpy as np
+import torch
+
+from . import functions as F
+
+_parameters = OrderedDict()
+_scope = []
+_device = None
+
+
+def set_device(device):
+    global _device
+    _device = torch.device(device)
+
+
+def _dev():
+    return _device if _device is not None else torch.device("cuda", torch.cuda.current_device())
+
+
+@contextlib.contextmanager
+def parameter_scope(name):
+    _scope.append(name)
+    try:
+        yield
+    finally:
+        _scope.pop()
+
+
+def get_parameters():
+    return _parameters
+
+
+def clear_parameters():
+    _parameters.clear()
+
+
+def get_parameter_or_create(name, shape, initializer):
+    """nnabla.parameter.get_parameter_or_create (parameter.py:260): `initializer`
+    is a numpy array or a callable shape -> numpy array."""
+    key = "/".join(_scope + [name])
+    p = _parameters.get(key)
+    if p is None:
+        a = initializer(shape) if callable(initializer) else np.asarray(initializer)
+        a = np.ascontiguousarray(a, dtype=np.float32).reshape(shape)
+        p = torch.from_numpy(a).to(_dev())
+        _parameters[key] = p
+    elif tuple(p.shape) != tuple(shape):
+        raise ValueError("parameter %s exists with shape %s, requested %s" % (key, tuple(p.shape), tuple(shape)))
+    return p
+
+
+def _glorot_uniform(inmaps, outmaps, kernel, rng):
+    # calc_uniform_lim_glorot (python/src/nnabla/initializer.py:409): b = sqrt(6 / (K (N + M)))
+    lim = np.sqrt(6.0 / (np.prod(kernel) * (inmaps + outmaps)))
+    return lambda shape: rng.uniform(-lim, lim, size=shape)
+
+
+def _zeros(shape):
+    return np.zeros(shape, np.float32)
+
+
+def _rng(rng):
+    return rng if rng is not None else np.random.RandomState(313)
+
+
+def affine(inp, n_outmaps, base_axis=1, w_init=None, b_init=None, fix_parameters=False, rng=None, with_bias=True):
+    n_outmaps = (n_outmaps,) if isinstance(n_outmaps, int) else tuple(n_outmaps)
+    inmaps = int(np.prod(inp.shape[base_axis:]))
+    with parameter_scope("affine"):
+        w = get_parameter_or_create("W", (inmaps,) + n_outmaps,
+                                    w_init or _glorot_uniform(inmaps, int(np.prod(n_outmaps)), (1, 1), _rng(rng)))
+        b = get_parameter_or_create("b", n_outmaps, b_init or _zeros) if with_bias else None
+    return F.affine(inp, w, b, base_axis)
+
+
+def binary_weight_affine(inp, n_outmaps, base_axis=1, quantize_zero_to=1.0, w_init=None, wb_init=None, b_init=None,
+                         fix_parameters=False, rng=None, with_bias=True):
+    n_outmaps = (n_outmaps,) if isinstance(n_outmaps, int) else tuple(n_outmaps)
+    inmaps = int(np.prod(inp.shape[base_axis:]))
+    init = _glorot_uniform(inmaps, int(np.prod(n_outmaps)), (1, 1), _rng(rng))
+    with parameter_scope("bwn_affine"):
+        w = get_parameter_or_create("W", (inmaps,) + n_outmaps, w_init or init)
+        wb = get_parameter_or_create("Wb", (inmaps,) + n_outmaps, wb_init or init)
+        alpha = get_parameter_or_create("alpha", n_outmaps, _zeros)
+        b = get_parameter_or_create("b", n_outmaps, b_init or _zeros) if with_bias else None
+    return F.binary_weight_affine(inp, w, wb, alpha, b, base_axis, quantize_zero_to)
+
+
+def binary_connect_affine(inp, n_outmaps, base_axis=1, quantize_zero_to=1.0, w_init=None, wb_init=None, b_init=None,
+                          fix_parameters=False, rng=None, with_bias=True):
+    n_outmaps = (n_outmaps,) if isinstance(n_outmaps, int) else tuple(n_outmaps)
+    inmaps = int(np.prod(inp.shape[base_axis:]))
+    init = _glorot_uniform(inmaps, int(np.prod(n_outmaps)), (1, 1), _rng(rng))
+    with parameter_scope("bicon_affine"):
+        w = get_parameter_or_create("W", (inmaps,) + n_outmaps, w_init or init)
+        wb = get_parameter_or_create("Wb", (inmaps,) + n_outmaps, wb_init or init)
+        b = get_parameter_or_create("b", n_outmaps, b_init or _zeros) if with_bias else None
+    return F.binary_connect_affine(inp, w, wb, b, base_axis, quantize_zero_to)
+
+
+def convolution(inp, outmaps, kernel, pad=None, stride=None, dilation=None, group=1, channel_last=False,
+                w_init=None, b_init=None, base_axis=1, fix_parameters=False, rng=None, with_bias=True):
+    inmaps = int(inp.shape[base_axis])
+    with parameter_scope("conv"):
+        w = get_parameter_or_create("W", (outmaps, inmaps // group) + tuple(kernel),
+                                    w_init or _glorot_uniform(inmaps, outmaps, tuple(kernel), _rng(rng)))
+        b = get_parameter_or_create("b", (outmaps,), b_init or _zeros) if with_bias else None
+    return F.convolution(inp, w, b, base_axis, pad, stride, dilation, group, channel_last)
+
+
+def binary_weight_convolution(inp, outmaps, kernel, pad=None, stride=None, dilation=None, group=1,
+                              quantize_zero_to=1.0, w_init=None, wb_init=None, b_init=None, base_axis=1,
+                              fix_parameters=False, rng=None, with_bias=True):
+    inmaps = int(inp.shape[base_axis])
+    init = _glorot_uniform(inmaps, outmaps, tuple(kernel), _rng(rng))
+    shape = (outmaps, inmaps // group) + tuple(kernel)
+    with parameter_scope("bwn_conv"):
+        w = get_parameter_or_create("W", shape, w_init or init)
+        wb = get_parameter_or_create("Wb", shape, wb_init or init)
+        alpha = get_parameter_or_create("alpha", (outmaps,), _zeros)
+        b = get_parameter_or_create("b", (outmaps,), b_init or _zeros) if with_bias else None
+    return F.binary_weight_convolution(inp, w, wb, alpha, b, base_axis, pad, stride, dilation, group,
+                                       quantize_zero_to)
+
+
+def binary_connect_convolution(inp, outmaps, kernel, pad=None, stride=None, dilation=None, group=1,
+                               quantize_zero_to=1.0, w_init=None, wb_init=None, b_init=None, base_axis=1,
+                               fix_parameters=False, rng=None, with_bias=True):
+    inmaps = int(inp.shape[base_axis])
+    init = _glorot_uniform(inmaps, outmaps, tuple(kernel), _rng(rng))
+    shape = (outmaps, inmaps // group) + tuple(kernel)
+    with parameter_scope("bicon_conv"):
+        w = get_parameter_or_create("W", shape, w_init or init)
+        wb = get_parameter_or_create("Wb", shape, wb_init or init)
+        b = get_parameter_or_create("b", (outmaps,), b_init or _zeros) if with_bias else None
+    return F.binary_connect_convolution(inp, w, wb, b, base_axis, pad, stride, dilation, group, quantize_zero_to)
+
+
+def batch_normalization(inp, axes=[1], decay_rate=0.9, eps=1e-5, batch_stat=True, output_stat=False,
+                        fix_parameters=False, param_init=None, no_scale=False, no_bias=False):
+    ax = axes[0]
+    shape = [1] * inp.dim()
+    shape[ax] = int(inp.shape[ax])
+    shape = tuple(shape)
+    init = param_init or {}
+    with parameter_scope("bn"):
+        beta = None if no_bias else get_parameter_or_create("beta", shape, init.get("beta", _zeros))
+        gamma = None if no_scale else get_parameter_or_create(
+            "gamma", shape, init.get("gamma", lambda s: np.ones(s, np.float32)))
+        mean = get_parameter_or_create("mean", shape, init.get("mean", _zeros))
+        var = get_parameter_or_create("var", shape, init.get("var", lambda s: np.ones(s, np.float32)))
+    return F.batch_normalization(inp, beta, gamma, mean, var, axes, decay_rate, eps, batch_stat, output_stat)

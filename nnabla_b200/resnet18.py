@@ -1,0 +1,138 @@
+"""Binary-weight ResNet-18 (BASELINE.json configs[4]) written against the F / PF mirrors.
+
+The reference ships no in-tree definition (python/src/nnabla/models/imagenet/resnet.py:59-60
+only loads a downloaded archive); this is the standard 18-layer basic-block
+topology: stem convolution 7x7/2 + BN + ReLU + max-pooling 3x3/2, four stages of
+two basic blocks with 64/128/256/512 maps and 1x1 stride-2 projection
+shortcuts, global average pooling, affine to 1000 classes. The first
+convolution and the final affine are full precision; every other convolution
+is a BinaryWeightConvolution; FixedPointQuantize(sign, n=8, delta=2^-4)
+follows every ReLU; BatchNormalization runs in inference mode on running
+statistics.
+
+`ops` is the function namespace (nnabla_b200.functions on the GPU; the tests
+pass an oracle-backed namespace with the same names), `params` maps parameter
+names to arrays, `trace` (optional list) records every function call for
+per-function parity checks.
+"""
+import numpy as np
+
+DELTA = 2.0 ** -4
+STAGES = [(64, 1), (128, 2), (256, 2), (512, 2)]
+
+
+def init_parameters(rng, num_classes=1000, in_channels=3):
+    """Random initialisation (numpy, seeded): Kaiming-normal convolution weights,
+    random BN running statistics with var > 0, as BASELINE.json configs[4] states."""
+    p = {}
+
+    def conv(name, o, i, k):
+        p[name + "/W"] = (rng.randn(o, i, k, k) * np.sqrt(2.0 / (i * k * k))).astype(np.float32)
+
+    def bn(name, c):
+        p[name + "/beta"] = (0.1 * rng.randn(c)).astype(np.float32)
+        p[name + "/gamma"] = (1.0 + 0.1 * rng.randn(c)).astype(np.float32)
+        p[name + "/mean"] = (0.1 * rng.randn(c)).astype(np.float32)
+        p[name + "/var"] = (0.5 + rng.rand(c)).astype(np.float32)
+
+    conv("stem/conv", 64, in_channels, 7)
+    bn("stem/bn", 64)
+    cin = 64
+    for s, (c, stride) in enumerate(STAGES):
+        for b in range(2):
+            st = stride if b == 0 else 1
+            name = "stage%d/block%d" % (s + 1, b)
+            conv(name + "/conv1", c, cin, 3)
+            bn(name + "/bn1", c)
+            conv(name + "/conv2", c, c, 3)
+            bn(name + "/bn2", c)
+            if st != 1 or cin != c:
+                conv(name + "/shortcut", c, cin, 1)
+                bn(name + "/bn_s", c)
+            cin = c
+    p["head/W"] = (rng.randn(512, num_classes) * np.sqrt(1.0 / 512)).astype(np.float32)
+    p["head/b"] = (0.01 * rng.randn(num_classes)).astype(np.float32)
+    return p
+
+
+class Runner:
+    """Applies the network with a given function namespace and array factory."""
+
+    def __init__(self, ops, params, zeros_like, trace=None, fixed_point_hint=True):
+        self.ops = ops
+        self.p = params
+        self.zeros_like = zeros_like
+        self.trace = trace
+        self.hint = fixed_point_hint
+        self.side = {}  # Wb / alpha buffers, written by the binary layers
+
+    def _rec(self, name, fn, inputs, out, **attrs):
+        if self.trace is not None:
+            self.trace.append({"layer": name, "fn": fn, "inputs": inputs, "output": out, "attrs": attrs})
+        return out
+
+    def bn(self, name, x):
+        p = self.p
+        y = self.ops.batch_normalization(x, p[name + "/beta"], p[name + "/gamma"], p[name + "/mean"],
+                                         p[name + "/var"], [1], 0.9, 1e-5, False)
+        return self._rec(name, "batch_normalization", [x], y)
+
+    def relu_q(self, name, x):
+        y = self._rec(name + "/relu", "relu", [x], self.ops.relu(x))
+        q = self.ops.fixed_point_quantize(y, True, 8, DELTA)
+        return self._rec(name + "/fxp", "fixed_point_quantize", [y], q)
+
+    def bwconv(self, name, x, k, stride):
+        w = self.p[name + "/W"]
+        if name not in self.side:
+            self.side[name] = (self.zeros_like(w), self.zeros_like(w, (w.shape[0],)))
+        wb, alpha = self.side[name]
+        pad = (k // 2, k // 2)
+        kw = {"fixed_point_delta": DELTA} if self.hint else {}
+        y = self.ops.binary_weight_convolution(x, w, wb, alpha, None, 1, pad, (stride, stride), (1, 1), 1, 1.0, **kw)
+        return self._rec(name, "binary_weight_convolution", [x], y, k=k, stride=stride)
+
+    def __call__(self, x):
+        o = self.ops
+        h = o.convolution(x, self.p["stem/conv/W"], None, 1, (3, 3), (2, 2), (1, 1), 1)
+        self._rec("stem/conv", "convolution", [x], h)
+        h = self.relu_q("stem", self.bn("stem/bn", h))
+        h = self._rec("stem/pool", "max_pooling", [h], o.max_pooling(h, (3, 3), (2, 2), True, (1, 1)))
+        cin = 64
+        for s, (c, stride) in enumerate(STAGES):
+            for b in range(2):
+                st = stride if b == 0 else 1
+                name = "stage%d/block%d" % (s + 1, b)
+                r = self.bwconv(name + "/conv1", h, 3, st)
+                r = self.relu_q(name + "/act1", self.bn(name + "/bn1", r))
+                r = self.bn(name + "/bn2", self.bwconv(name + "/conv2", r, 3, 1))
+                if st != 1 or cin != c:
+                    sc = self.bn(name + "/bn_s", self.bwconv(name + "/shortcut", h, 1, st))
+                else:
+                    sc = h
+                a = self._rec(name + "/add", "add2", [r, sc], o.add2(r, sc))
+                h = self.relu_q(name + "/act2", a)
+                cin = c
+        g = self._rec("head/pool", "global_average_pooling", [h], o.global_average_pooling(h))
+        y = o.affine(g, self.p["head/W"], self.p["head/b"], 1)
+        return self._rec("head/affine", "affine", [g], y)
+
+
+def conv_macs_per_image(height=224, width=224, num_classes=1000):
+    """Multiply-accumulates of the convolutions and the affine per image,
+    counted from the layer shapes."""
+    def out(v, k, s, p):
+        return (v + 2 * p - k) // s + 1
+    h, w = out(height, 7, 2, 3), out(width, 7, 2, 3)
+    macs = 64 * 3 * 49 * h * w
+    h, w = (h + 1 - 2) // 2 + 1, (w + 1 - 2) // 2 + 1
+    cin = 64
+    for c, stride in STAGES:
+        for b in range(2):
+            st = stride if b == 0 else 1
+            ho, wo = out(h, 3, st, 1), out(w, 3, st, 1)
+            macs += c * cin * 9 * ho * wo + c * c * 9 * ho * wo
+            if st != 1 or cin != c:
+                macs += c * cin * ho * wo
+            h, w, cin = ho, wo, c
+    return macs + 512 * num_classes

@@ -1,0 +1,49 @@
+"""Function namespace with the names and argument order of nnabla_b200.functions,
+backed by the CPU oracle (numpy arrays). Lets the same network definition run
+on the checker."""
+import numpy as np
+
+from oracle import oracle
+
+
+def convolution(x, w, b=None, base_axis=1, pad=None, stride=None, dilation=None, group=1, channel_last=False):
+    return oracle.convolution(x, w, b, pad or (0, 0), stride or (1, 1), dilation or (1, 1), group)
+
+
+def batch_normalization(x, beta, gamma, mean, var, axes=(1,), decay_rate=0.9, eps=1e-5, batch_stat=True,
+                        output_stat=False):
+    assert not batch_stat
+    return oracle.batch_norm_inference(x, beta, gamma, mean, var, eps)
+
+
+def relu(x, inplace=False):
+    return oracle.relu(x)
+
+
+def add2(a, b, inplace=False):
+    return oracle.add2(a, b)
+
+
+def fixed_point_quantize(x, sign=True, n=8, delta=2 ** -4, quantize=True, ste_fine_grained=True):
+    return oracle.fixed_point_quantize(x, sign, n, delta)
+
+
+def max_pooling(x, kernel, stride=None, ignore_border=True, pad=None, channel_last=False):
+    return oracle.max_pooling(x, kernel, stride or kernel, ignore_border, pad or (0, 0))
+
+
+def global_average_pooling(x):
+    return oracle.global_average_pooling(x)
+
+
+def binary_weight_convolution(x, w, wb, alpha, b=None, base_axis=1, pad=None, stride=None, dilation=None, group=1,
+                              quantize_zero_to=1.0, **kw):
+    y, wb_o, al_o = oracle.binary_weight_convolution(x, w, b, pad or (0, 0), stride or (1, 1), dilation or (1, 1),
+                                                     group, quantize_zero_to)
+    wb[...] = wb_o
+    alpha[...] = al_o
+    return y
+
+
+def affine(x, w, b=None, base_axis=1, **kw):
+    return oracle.affine(x, w, b, base_axis)

@@ -1,0 +1,68 @@
+"""GPU parity of the companion functions (BN inference, ReLU, Add2, max
+pooling, global average pooling, full-precision stem convolution): bit-exact
+against the oracle, which is itself bit-exact against the reference's CPU code."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from golden_util import bits
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a, np.float32)).cuda()
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+@pytest.fixture(scope="module")
+def F():
+    from nnabla_b200 import _capi, functions
+    _capi.call("nb200_check_device")
+    return functions
+
+
+@pytest.mark.parametrize("shape", [(2, 6, 9, 11), (3, 16, 8, 8), (1, 5, 1, 1), (4, 7)])
+def test_batch_normalization_relu_add2(F, shape):
+    rng = np.random.RandomState(sum(shape))
+    x = rng.randn(*shape).astype(np.float32)
+    C = shape[1]
+    pshape = (1, C) + (1,) * (len(shape) - 2)
+    beta, gamma, mean = (rng.randn(*pshape).astype(np.float32) for _ in range(3))
+    var = (rng.rand(*pshape) + 0.1).astype(np.float32)
+    y = F.batch_normalization(dev(x), dev(beta), dev(gamma), dev(mean), dev(var), [1], 0.9, 1e-5, False)
+    x3 = x.reshape(shape[0], C, -1)
+    assert np.array_equal(bits(host(y)).reshape(-1), bits(oracle.batch_norm_inference(x3, beta, gamma, mean, var, 1e-5)).reshape(-1))
+    assert np.array_equal(bits(host(F.relu(dev(x)))), bits(oracle.relu(x)))
+    x2 = rng.randn(*shape).astype(np.float32)
+    assert np.array_equal(bits(host(F.add2(dev(x), dev(x2)))), bits(oracle.add2(x, x2)))
+    with pytest.raises(RuntimeError):
+        F.batch_normalization(dev(x), dev(beta), dev(gamma), dev(mean), dev(var), [1], 0.9, 1e-5, True)
+
+
+@pytest.mark.parametrize("k,s,p,ib", [((3, 3), (2, 2), (1, 1), True), ((2, 2), (2, 2), (0, 0), True),
+                                      ((3, 3), (2, 2), (0, 0), False), ((3, 2), (1, 2), (1, 0), True)])
+def test_pooling(F, k, s, p, ib):
+    rng = np.random.RandomState(7)
+    x = rng.randn(2, 5, 13, 10).astype(np.float32)
+    assert np.array_equal(bits(host(F.max_pooling(dev(x), k, s, ib, p))), bits(oracle.max_pooling(x, k, s, ib, p)))
+    assert np.array_equal(bits(host(F.global_average_pooling(dev(x)))), bits(oracle.global_average_pooling(x)))
+
+
+@pytest.mark.parametrize("xs,ws,pad,stride", [((2, 3, 32, 32), (64, 3, 7, 7), (3, 3), (2, 2)),
+                                              ((1, 3, 17, 19), (20, 3, 3, 3), (1, 1), (1, 1)),
+                                              ((2, 4, 9, 9), (5, 4, 1, 1), (0, 0), (2, 2))])
+def test_full_precision_convolution(F, xs, ws, pad, stride):
+    rng = np.random.RandomState(11)
+    x = rng.randn(*xs).astype(np.float32)
+    w = rng.randn(*ws).astype(np.float32)
+    b = rng.randn(ws[0]).astype(np.float32)
+    y = host(F.convolution(dev(x), dev(w), dev(b), 1, pad, stride))
+    want = oracle.convolution(x, w, b, pad, stride)
+    assert y.shape == want.shape
+    assert np.array_equal(bits(y), bits(want))
