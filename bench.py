@@ -40,6 +40,13 @@ def parse_args():
     ap.add_argument("--size-log2", type=int, default=30)
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other BASELINE configurations")
+    ap.add_argument("--resnet-batch", type=int, default=256, help="images per GPU for the ResNet-18 extra")
+    ap.add_argument("--only-extras", action="store_true",
+                    help="run only the other BASELINE configurations and print their JSON (profiling runs)")
+    ap.add_argument("--small-extras", action="store_true",
+                    help="reduced sizes for the other configurations (ncu captures must stay small)")
     return ap.parse_args()
 
 
@@ -170,6 +177,104 @@ def measured_peaks():
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
+def time_gpu(fn, iters, warm=3):
+    """Mean milliseconds per call of fn, CUDA events on the current stream."""
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_extras(args, rank, world, barrier):
+    """The other BASELINE configurations, timed per rank (inputs resident in
+    HBM, tensors larger than L2 or an L2 flush between iterations is not
+    applied to these short runs: stated per entry)."""
+    import torch
+    import torch.distributed as dist
+    from nnabla_b200 import functions as F
+    from nnabla_b200 import resnet18
+    peaks, _ = measured_peaks()
+    out = {}
+    gen = torch.Generator(device="cuda").manual_seed(99 + rank)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=gen)
+
+    def maxr(ms):
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    # configs[0]: BinaryWeightAffine 256 x 1024 x 4096 (replicated on every rank)
+    M, K, N = 256, 1024, 4096
+    x, w, b = rn(M, K), 0.02 * rn(K, N), torch.zeros(N, device="cuda")
+    wb, al = torch.zeros_like(w), torch.zeros(N, device="cuda")
+    ms = maxr(time_gpu(lambda: F.binary_weight_affine(x, w, wb, al, b), 50))
+    out["configs[0] binary_weight_affine 256x1024x4096"] = {
+        "ms": ms, "tflops_algorithmic": 2 * M * K * N / ms / 1e9, "tflops_issued_bf16x3": 6 * M * K * N / ms / 1e9,
+        "frac_of_bf16_peak_issued": 6 * M * K * N / ms / 1e9 / peaks["bf16_tflops"],
+        "includes": "binarise + alpha + split + GEMM, whole forward_impl", "l2": "working set fits L2 (latency-bound case)"}
+    # configs[2]: 8-bit fixed-point affine, output columns sharded over the ranks
+    M, K, N = (2048, 4096, 2048) if args.small_extras else (8192, 4096, 8192)
+    Ns = N // world
+    x = rn(M, K)
+    w = 0.02 * rn(K, Ns)
+    b = 0.01 * rn(Ns)
+    xq, xc = F.fixed_point_quantize_with_codes(x, True, 8, 2.0 ** -5)
+    wq, wc = F.fixed_point_quantize_with_codes(w, True, 8, 2.0 ** -10)
+    ms_gemm = maxr(time_gpu(lambda: F.affine_from_codes(xc, wc, 2.0 ** -5, 2.0 ** -10, b), 20))
+    entry = {"ms_gemm": ms_gemm, "int8_tops_whole_job": 2 * M * K * N / ms_gemm / 1e9,
+             "columns_per_gpu": Ns, "l2": "operands 32 MiB + 32 MiB/g int8; output 256 MiB/g fp32 exceeds L2"}
+    ms_q = maxr(time_gpu(lambda: (F.fixed_point_quantize_with_codes(x, True, 8, 2.0 ** -5),
+                                  F.fixed_point_quantize_with_codes(w, True, 8, 2.0 ** -10)), 10))
+    entry["ms_quantize_x_and_w"] = ms_q
+    if world > 1:
+        ys = F.affine_from_codes(xc, wc, 2.0 ** -5, 2.0 ** -10, b)
+        stage = torch.empty((world, M, Ns), device="cuda")
+        full = torch.empty((M, N), device="cuda")
+
+        def gemm_and_gather():
+            yy = F.affine_from_codes(xc, wc, 2.0 ** -5, 2.0 ** -10, b)
+            dist.all_gather_into_tensor(stage, yy)
+            full.view(M, world, Ns).copy_(stage.permute(1, 0, 2))
+        entry["ms_gemm_plus_allgather"] = maxr(time_gpu(gemm_and_gather, 10))
+        del ys, stage, full
+    out["configs[2] fixed-point int8 affine %dx%dx%d" % (M, K, N)] = entry
+    del x, w, xq, wq, xc, wc
+    # configs[3]: BinaryWeightConvolution 3x3, 256 -> 256, 28 x 28, batch 128 sharded over the ranks
+    Nb = max(1, (16 if args.small_extras else 128) // world)
+    x = torch.relu(rn(Nb, 256, 28, 28))
+    w = rn(256, 256, 3, 3) * (2.0 / 2304) ** 0.5
+    wb, al, b = torch.zeros_like(w), torch.zeros(256, device="cuda"), torch.zeros(256, device="cuda")
+    ms = maxr(time_gpu(lambda: F.binary_weight_convolution(x, w, wb, al, b, 1, (1, 1), (1, 1)), 10))
+    flops = 2.0 * (Nb * world * 28 * 28) * 256 * 2304
+    out["configs[3] binary_weight_convolution 3x3 256->256 28x28 batch %d" % (Nb * world)] = {
+        "ms": ms, "tflops_algorithmic_whole_job": flops / ms / 1e9, "tflops_issued_bf16x3_whole_job": 3 * flops / ms / 1e9,
+        "frac_of_bf16_peak_issued_per_gpu": 3 * flops / world / ms / 1e9 / peaks["bf16_tflops"],
+        "includes": "binarise + NCHW->NHWC split + implicit GEMM, whole forward_impl", "images_per_gpu": Nb}
+    del x, w
+    # configs[4]: binary-weight ResNet-18, batch sharded over the ranks
+    B = args.resnet_batch
+    Bg = max(1, B // world)
+    params = {k: torch.from_numpy(v).cuda() for k, v in resnet18.init_parameters(np.random.RandomState(0)).items()}
+    x = rn(Bg, 3, 224, 224)
+    gz = lambda t, shape=None: torch.zeros(shape or tuple(t.shape), device="cuda")
+    net = resnet18.Runner(F, params, gz)
+    ms = maxr(time_gpu(lambda: net(x), 5, warm=2))
+    F.check_device_status()
+    out["configs[4] binary-weight ResNet-18 224x224"] = {
+        "ms_per_batch": ms, "images_per_sec_whole_job": Bg * world / ms * 1e3, "batch_per_gpu": Bg,
+        "gmac_per_image": resnet18.conv_macs_per_image() / 1e9}
+    return out
+
+
 def run_b200_arm(args):
     import torch
     import torch.distributed as dist
@@ -188,6 +293,14 @@ def run_b200_arm(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.only_extras:
+        extras = run_extras(args, rank, world, barrier)
+        if rank == 0:
+            print(json.dumps({"other_configs": extras}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     n = 1 << args.size_log2
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
@@ -234,6 +347,8 @@ def run_b200_arm(args):
     # ---- end to end through the host-buffer entry points -------------------
     e2e = None
     try:
+        if args.no_e2e:
+            raise RuntimeError("skipped by --no-e2e")
         hx = torch.empty(n, dtype=torch.float32, pin_memory=True)
         hy = torch.empty(n, dtype=torch.float32, pin_memory=True)
         hx.copy_(x)
@@ -263,6 +378,12 @@ def run_b200_arm(args):
         del hx, hy
     except RuntimeError as exc:  # pinned allocation failure: report, do not fake
         e2e = {"value": None, "unit": "GB/s", "error": str(exc)[:200]}
+
+    del x, y
+    torch.cuda.empty_cache()
+    extras = None
+    if not args.no_extras:
+        extras = run_extras(args, rank, world, barrier)
 
     if rank != 0:
         if world > 1:
@@ -295,6 +416,7 @@ def run_b200_arm(args):
                    "elements_per_gpu": n, "l2": "inputs (4 GiB) larger than L2; no flush needed"},
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
         "gpu_launches": 4 * args.steps,
+        "other_configs": extras,
     }
     print(json.dumps(line))
     if world > 1:
