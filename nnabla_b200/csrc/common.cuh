@@ -45,6 +45,24 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 __device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
 
+// Stream-ordered scratch for one call: allocated from the device's default
+// memory pool (whose release threshold is raised on first use so that the pool
+// keeps its memory across synchronisations instead of returning it to the
+// driver), freed in stream order when the object goes out of scope.
+int scratch_alloc(void **p, size_t bytes, cudaStream_t st);
+struct AsyncScratch {
+  void *p = nullptr;
+  cudaStream_t st;
+  explicit AsyncScratch(cudaStream_t s) : st(s) {}
+  AsyncScratch(const AsyncScratch &) = delete;
+  AsyncScratch &operator=(const AsyncScratch &) = delete;
+  int alloc(size_t bytes) { return scratch_alloc(&p, bytes, st); }
+  ~AsyncScratch() {
+    if (p)
+      cudaFreeAsync(p, st);
+  }
+};
+
 // Host-buffer pipeline shared by the _host entry points: copies `n` floats
 // from hx to the device in chunks, runs `launch(dx, dy, count, offset, stream)`
 // on each chunk and copies the result to hy, overlapping the three stages

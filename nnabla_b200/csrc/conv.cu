@@ -120,20 +120,6 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
   return launch_contraction<kInt8, PA, PB, BN, STAGES, false, ConvProblem>(ma, mb, p, tiles, ep, st);
 }
 
-struct AsyncScratch {
-  void *p = nullptr;
-  cudaStream_t st;
-  explicit AsyncScratch(cudaStream_t s) : st(s) {}
-  int alloc(size_t bytes) {
-    NB_CUDA(cudaMallocAsync(&p, bytes, st));
-    return NB200_OK;
-  }
-  ~AsyncScratch() {
-    if (p)
-      cudaFreeAsync(p, st);
-  }
-};
-
 // Shared body of BinaryWeightConvolution / BinaryConnectConvolution forward.
 int binary_convolution(const float *x, const float *w, float *wb, float *alpha, const float *bias, float *y,
                        ConvGeometry g, float zero_to, float act_delta, cudaStream_t st) {

@@ -144,20 +144,6 @@ static bool bf16_exact(float v) {
   return (b & 0xffffu) == 0;
 }
 
-struct AsyncScratch {
-  void *p = nullptr;
-  cudaStream_t st;
-  explicit AsyncScratch(cudaStream_t s) : st(s) {}
-  int alloc(size_t bytes) {
-    NB_CUDA(cudaMallocAsync(&p, bytes, st));
-    return NB200_OK;
-  }
-  ~AsyncScratch() {
-    if (p)
-      cudaFreeAsync(p, st);
-  }
-};
-
 // Shared body of BinaryWeightAffine / BinaryConnectAffine forward.
 static int binary_affine(const float *x, const float *w, float *wb, float *alpha, const float *bias, float *y,
                          int64_t M, int64_t K, int64_t N, float zero_to, cudaStream_t st) {

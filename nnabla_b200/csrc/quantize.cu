@@ -759,14 +759,10 @@ int nb200_min_max_quantize_f32(const float *x, const int64_t *x_shape, int ndim,
   NB_CHECK(qr_min && qr_max && ql_min && ql_max, NB200_EVALUE, "null range pointer");
   NB_CHECK(V.size == 0 || (x && y), NB200_EVALUE, "null data pointer");
   cudaStream_t st = as_stream(stream);
-  float *scratch = nullptr;
-  NB_CUDA(cudaMallocAsync(&scratch, 5 * V.Q * sizeof(float), st));
-  const int rc = minmax_run(x, V, qr_min, qr_max, ql_min, ql_max, decay, x_min_max, ema, eps, y, scale, scratch, st);
-  cudaError_t e = cudaFreeAsync(scratch, st);
-  if (rc != NB200_OK)
-    return rc;
-  NB_CUDA(e);
-  return NB200_OK;
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc(5 * V.Q * sizeof(float)));
+  return minmax_run(x, V, qr_min, qr_max, ql_min, ql_max, decay, x_min_max, ema, eps, y, scale,
+                    static_cast<float *>(scratch.p), st);
 }
 
 int nb200_min_max_quantize_f32_noalloc(const float *x, const int64_t *x_shape, int ndim, float *qr_min,

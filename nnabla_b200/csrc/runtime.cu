@@ -39,6 +39,31 @@ int sm_count() {
   return cached[dev];
 }
 
+int scratch_alloc(void **p, size_t bytes, cudaStream_t st) {
+  static std::mutex m;
+  static bool pool_ready[64];
+  int dev = 0;
+  NB_CUDA(cudaGetDevice(&dev));
+  NB_CHECK(dev >= 0 && dev < 64, NB200_EVALUE, "device index %d out of range", dev);
+  {
+    std::lock_guard<std::mutex> lock(m);
+    if (!pool_ready[dev]) {
+      cudaMemPool_t pool;
+      NB_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+      uint64_t keep = UINT64_MAX;
+      NB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+      pool_ready[dev] = true;
+    }
+  }
+  cudaError_t e = cudaMallocAsync(p, bytes ? bytes : 1, st);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    return fail(NB200_EMEMORY, "stream-ordered allocation of %zu bytes of scratch failed: out of device memory", bytes);
+  }
+  NB_CUDA(e);
+  return NB200_OK;
+}
+
 // ---- host pipeline ---------------------------------------------------------
 
 namespace {
