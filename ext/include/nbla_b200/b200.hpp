@@ -1,0 +1,101 @@
+// nnabla extension backend "b200": backend singleton, device memory, array
+// classes and registration entry point. Mirrors what the reference's own CPU
+// backend provides (include/nbla/cpu.hpp, include/nbla/memory/cpu_memory.hpp,
+// include/nbla/array/cpu_array.hpp, src/nbla/init.cpp.tmpl:44-111) for a CUDA
+// device driven through the C ABI of libnnabla_b200.so.
+#ifndef NBLA_B200_B200_HPP_
+#define NBLA_B200_B200_HPP_
+
+#include <nbla/array.hpp>
+#include <nbla/backend_base.hpp>
+#include <nbla/context.hpp>
+#include <nbla/memory/allocator.hpp>
+#include <nbla/memory/memory.hpp>
+#include <nbla/singleton_manager.hpp>
+#include <nbla/variable.hpp>
+
+#include <string>
+#include <vector>
+
+namespace nbla {
+
+using std::string;
+using std::vector;
+
+/** Registers the backend, its array classes, synchronizers and functions
+    under "b200:float". Idempotent and thread-safe, like init_cpu(). */
+void init_b200();
+
+/** Context of this backend: Context({"b200:float"}, "B200CachedArray", device_id).
+    There is no "cpu:float" entry: no function falls back to the CPU. */
+Context b200_context(const string &device_id = "0");
+
+/** Raises nbla::Exception for a non-zero status of the C ABI (the message is
+    nb200_last_error()). */
+void nb200_check(int status, const char *what);
+
+/** Device memory block (cudaMalloc through nb200_malloc). Same contract as
+    CpuMemory (src/nbla/memory/cpu_memory.cpp:31-80). */
+class B200Memory : public Memory {
+public:
+  B200Memory(size_t bytes, const string &device_id);
+  B200Memory(size_t bytes, const string &device_id, void *ptr);
+  ~B200Memory();
+
+protected:
+  bool alloc_impl() override;
+  shared_ptr<Memory> divide_impl(size_t second_start) override;
+  void merge_next_impl(Memory *from) override;
+  void merge_prev_impl(Memory *from) override;
+};
+
+/** Backend singleton: array class list and the two allocators. */
+class B200 : public BackendBase {
+public:
+  ~B200();
+  vector<string> array_classes() const override;
+  void _set_array_classes(const vector<string> &a) override;
+  void register_array_class(const string &name) override;
+  shared_ptr<Allocator> caching_allocator() override;
+  shared_ptr<Allocator> naive_allocator() override;
+  void free_unused_host_caches() override;
+  void device_synchronize(const string &device) override;
+  void default_stream_synchronize(const string &device) override;
+  void create_lms_streams(int device = -1) override;
+
+private:
+  friend SingletonManager;
+  B200();
+};
+
+/** Device array allocated from the backend's naive allocator. */
+class B200Array : public Array {
+public:
+  explicit B200Array(const Size_t size, dtypes dtype, const Context &ctx, const AllocatorMemoryPtr mem = nullptr,
+                     const Size_t offset = 0);
+  virtual ~B200Array();
+  virtual void copy_from(const Array *src_array);
+  virtual void zero();
+  virtual void fill(float value);
+  static Context filter_context(const Context &ctx);
+};
+
+/** Device array allocated from the backend's caching allocator. */
+class B200CachedArray : public B200Array {
+public:
+  explicit B200CachedArray(const Size_t size, dtypes dtype, const Context &ctx,
+                           const AllocatorMemoryPtr mem = nullptr, const Size_t offset = 0);
+  virtual ~B200CachedArray();
+  static Context filter_context(const Context &ctx);
+};
+
+/** Fixed-point tags: which device arrays currently hold the output of
+    FixedPointQuantize with at most 8 bits, and with which step size. The
+    contraction functions consult it to take the exact int8 tensor-core path.
+    Keyed by SyncedArray and its modification count
+    (include/nbla/synced_array.hpp:183), so any later write invalidates a tag. */
+void fxp_tag_set(const Variable *v, float delta);
+float fxp_tag_get(const Variable *v); // 0 when untagged or stale
+
+} // namespace nbla
+#endif

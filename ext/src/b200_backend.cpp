@@ -1,0 +1,216 @@
+// Backend, memory and array classes of the "b200" nnabla extension.
+#include <nbla_b200/b200.hpp>
+
+#include <nbla/array/cpu_array.hpp>
+#include <nbla/array_registry.hpp>
+#include <nbla/exception.hpp>
+#include <nbla/memory/caching_allocator_with_buckets.hpp>
+#include <nbla/memory/naive_allocator.hpp>
+#include <nbla/singleton_manager-internal.hpp>
+
+#include <nnabla_b200.h>
+
+#include <map>
+#include <memory>
+#include <mutex>
+
+namespace nbla {
+
+void nb200_check(int status, const char *what) {
+  if (status == NB200_OK)
+    return;
+  const error_code code = status == NB200_EVALUE      ? error_code::value
+                          : status == NB200_EMEMORY   ? error_code::memory
+                          : status == NB200_ENOTIMPL  ? error_code::not_implemented
+                                                      : error_code::target_specific;
+  NBLA_ERROR(code, "%s: %s", what, nb200_last_error());
+}
+
+static size_t bytes_of(Size_t size, dtypes dtype) { return (size_t)size * sizeof_dtype(dtype); }
+
+static int device_index(const string &device_id) { return device_id.empty() ? 0 : std::stoi(device_id); }
+
+static void use_device(const string &device_id) {
+  nb200_check(nb200_set_device(device_index(device_id)), "nb200_set_device");
+}
+
+Context b200_context(const string &device_id) { return Context({"b200:float"}, "B200CachedArray", device_id); }
+
+// ---------------------------------------------------------------- B200Memory
+B200Memory::B200Memory(size_t bytes, const string &device_id) : Memory(bytes, device_id) {}
+B200Memory::B200Memory(size_t bytes, const string &device_id, void *ptr) : Memory(bytes, device_id) { ptr_ = ptr; }
+
+B200Memory::~B200Memory() {
+  if (!ptr_)
+    return;
+  NBLA_FORCE_ASSERT(!prev(), "freeing a device block that was split off another block");
+  nb200_set_device(device_index(this->device_id()));
+  nb200_free(ptr_);
+}
+
+bool B200Memory::alloc_impl() {
+  if (nb200_set_device(device_index(this->device_id())) != NB200_OK)
+    return false;
+  void *p = nullptr;
+  if (nb200_malloc(&p, this->bytes()) != NB200_OK)
+    return false; // the allocator retries after freeing its caches
+  ptr_ = p;
+  return true;
+}
+
+shared_ptr<Memory> B200Memory::divide_impl(size_t second_start) {
+  // The right part starts second_start bytes into this block; this object keeps the left part.
+  void *right = static_cast<void *>(static_cast<uint8_t *>(ptr_) + second_start);
+  return shared_ptr<Memory>(new B200Memory(this->bytes() - second_start, this->device_id(), right));
+}
+
+void B200Memory::merge_next_impl(Memory *from) {} // this block already starts the merged range
+void B200Memory::merge_prev_impl(Memory *from) { ptr_ = from->pointer(); }
+
+// ---------------------------------------------------------------------- B200
+B200::B200() {
+  naive_allocator_ = std::make_shared<NaiveAllocator<B200Memory>>();
+  caching_allocator_ = std::make_shared<CachingAllocatorWithBuckets<B200Memory>>();
+}
+B200::~B200() {}
+vector<string> B200::array_classes() const { return array_classes_; }
+void B200::_set_array_classes(const vector<string> &a) { array_classes_ = a; }
+void B200::register_array_class(const string &name) { array_classes_.push_back(name); }
+shared_ptr<Allocator> B200::caching_allocator() { return caching_allocator_; }
+shared_ptr<Allocator> B200::naive_allocator() { return naive_allocator_; }
+void B200::free_unused_host_caches() {}
+void B200::device_synchronize(const string &device) {
+  use_device(device);
+  nb200_check(nb200_device_synchronize(), "nb200_device_synchronize");
+}
+void B200::default_stream_synchronize(const string &device) {
+  use_device(device);
+  nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+}
+void B200::create_lms_streams(int device) {}
+
+NBLA_INSTANTIATE_SINGLETON(, B200);
+
+// ----------------------------------------------------------------- B200Array
+B200Array::B200Array(const Size_t size, dtypes dtype, const Context &ctx, const AllocatorMemoryPtr mem,
+                     const Size_t offset)
+    : Array(size, dtype, ctx,
+            mem ? mem
+                : SingletonManager::get<B200>()->naive_allocator()->alloc(Array::size_as_bytes(size, dtype),
+                                                                          ctx.device_id),
+            offset) {}
+B200Array::~B200Array() {}
+
+Context B200Array::filter_context(const Context &ctx) { return Context({}, "B200Array", ctx.device_id); }
+
+void B200Array::zero() {
+  use_device(this->ctx_.device_id);
+  nb200_check(nb200_memset_zero(this->pointer<void>(), Array::size_as_bytes(this->size_, this->dtype_), nullptr),
+              "nb200_memset_zero");
+}
+
+void B200Array::fill(float value) {
+  use_device(this->ctx_.device_id);
+  if (this->dtype_ == dtypes::FLOAT) {
+    nb200_check(nb200_fill_f32(this->pointer<float>(), this->size_, value, nullptr), "nb200_fill_f32");
+    return;
+  }
+  // Other element types: fill on the host with the reference's own typed fill, then upload.
+  CpuArray host(this->size_, this->dtype_, Context({"cpu:float"}, "CpuArray", ""));
+  host.fill(value);
+  nb200_check(nb200_memcpy_h2d(this->pointer<void>(), host.const_pointer<void>(),
+                               Array::size_as_bytes(this->size_, this->dtype_), nullptr),
+              "nb200_memcpy_h2d");
+  nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+}
+
+void B200Array::copy_from(const Array *src) {
+  NBLA_CHECK(src->size() == this->size_, error_code::unclassified, "Size mismatch.");
+  NBLA_CHECK(src->dtype() == this->dtype_, error_code::not_implemented,
+             "device-to-device copy with a dtype conversion is not implemented");
+  use_device(this->ctx_.device_id);
+  nb200_check(nb200_memcpy_d2d(this->pointer<void>(), src->const_pointer<void>(),
+                               Array::size_as_bytes(this->size_, this->dtype_), nullptr),
+              "nb200_memcpy_d2d");
+}
+
+B200CachedArray::B200CachedArray(const Size_t size, dtypes dtype, const Context &ctx, const AllocatorMemoryPtr mem,
+                                 const Size_t offset)
+    : B200Array(size, dtype, ctx,
+                mem ? mem
+                    : SingletonManager::get<B200>()->caching_allocator()->alloc(Array::size_as_bytes(size, dtype),
+                                                                                ctx.device_id),
+                offset) {}
+B200CachedArray::~B200CachedArray() {}
+Context B200CachedArray::filter_context(const Context &ctx) { return Context({}, "B200CachedArray", ctx.device_id); }
+
+// ------------------------------------------------------------ synchronizers
+// SyncedArray::sync copies head -> requested array in one call and the two may
+// differ in dtype (src/nbla/synced_array.cpp:372-381): conversions run on the
+// host with the reference's own typed copy, transfers are raw byte copies.
+void synchronizer_cpu_to_b200(Array *src, Array *dst, const int async_flags) {
+  const Array *host = src;
+  std::unique_ptr<CpuArray> converted;
+  if (src->dtype() != dst->dtype()) {
+    converted.reset(new CpuArray(src->size(), dst->dtype(), Context({"cpu:float"}, "CpuArray", "")));
+    converted->copy_from(src);
+    host = converted.get();
+  }
+  use_device(dst->context().device_id);
+  nb200_check(nb200_memcpy_h2d(dst->pointer<void>(), host->const_pointer<void>(),
+                               bytes_of(dst->size(), dst->dtype()), nullptr),
+              "nb200_memcpy_h2d");
+  nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+}
+
+void synchronizer_b200_to_cpu(Array *src, Array *dst, const int async_flags) {
+  use_device(src->context().device_id);
+  if (src->dtype() == dst->dtype()) {
+    nb200_check(nb200_memcpy_d2h(dst->pointer<void>(), src->const_pointer<void>(),
+                                 bytes_of(src->size(), src->dtype()), nullptr),
+                "nb200_memcpy_d2h");
+    nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+    return;
+  }
+  CpuArray staged(src->size(), src->dtype(), Context({"cpu:float"}, "CpuArray", ""));
+  nb200_check(nb200_memcpy_d2h(staged.pointer<void>(), src->const_pointer<void>(),
+                               bytes_of(src->size(), src->dtype()), nullptr),
+              "nb200_memcpy_d2h");
+  nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+  dst->copy_from(&staged);
+}
+
+// -------------------------------------------------------------- fixed-point tags
+namespace {
+struct FxpTag {
+  std::weak_ptr<SyncedArray> owner; // a freed array whose address is reused must not inherit the tag
+  size_t count;
+  float delta;
+};
+std::mutex g_tag_mutex;
+std::map<const SyncedArray *, FxpTag> g_tags;
+} // namespace
+
+void fxp_tag_set(const Variable *v, float delta) {
+  SyncedArrayPtr a = const_cast<Variable *>(v)->data()->array();
+  std::lock_guard<std::mutex> lock(g_tag_mutex);
+  if (g_tags.size() > 1024) {
+    for (auto it = g_tags.begin(); it != g_tags.end();)
+      it = it->second.owner.expired() ? g_tags.erase(it) : std::next(it);
+  }
+  g_tags[a.get()] = FxpTag{a, a->modification_count(), delta};
+}
+
+float fxp_tag_get(const Variable *v) {
+  SyncedArrayPtr a = const_cast<Variable *>(v)->data()->array();
+  std::lock_guard<std::mutex> lock(g_tag_mutex);
+  auto it = g_tags.find(a.get());
+  if (it == g_tags.end())
+    return 0.0f;
+  SyncedArrayPtr owner = it->second.owner.lock();
+  if (owner.get() != a.get() || it->second.count != a->modification_count())
+    return 0.0f;
+  return it->second.delta;
+}
+
+} // namespace nbla

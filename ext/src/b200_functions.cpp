@@ -1,0 +1,582 @@
+// Function implementations of the "b200" nnabla extension and init_b200().
+//
+// Each class derives from the reference's own function class, so name(),
+// copy(), in/out types, argument storage and the gradient-dependency
+// predicates the graph engine reads (src/nbla/computation_graph/variable.cpp:203-273)
+// are the reference's by construction. Overridden: the allowed array classes
+// (device arrays), forward_impl (one call into libnnabla_b200.so) and, for the
+// composites, setup_impl — the reference's setup creates CPU sub-functions
+// through the registry (binary_weight_affine.cpp:35,65-70;
+// min_max_quantize.cpp:97-119; batch_normalization.cpp:119-131), which would
+// look up "b200:float" for each of them and throw, so only the shape checks and
+// the output reshape are repeated here. backward_impl raises not_implemented:
+// this backend is the forward (inference) path.
+#include <nbla_b200/b200.hpp>
+
+#include <nbla/array/cpu_array.hpp>
+#include <nbla/array_registry.hpp>
+#include <nbla/backend_registry.hpp>
+#include <nbla/function/add2.hpp>
+#include <nbla/function/affine.hpp>
+#include <nbla/function/batch_normalization.hpp>
+#include <nbla/function/binary_connect_affine.hpp>
+#include <nbla/function/binary_connect_convolution.hpp>
+#include <nbla/function/binary_weight_affine.hpp>
+#include <nbla/function/binary_weight_convolution.hpp>
+#include <nbla/function/convolution.hpp>
+#include <nbla/function/fixed_point_quantize.hpp>
+#include <nbla/function/global_average_pooling.hpp>
+#include <nbla/function/max_pooling.hpp>
+#include <nbla/function/min_max_quantize.hpp>
+#include <nbla/function/pow2_quantize.hpp>
+#include <nbla/function/relu.hpp>
+#include <nbla/function_registry.hpp>
+#include <nbla/utils/axis_utils.hpp>
+
+#include <nnabla_b200.h>
+
+#include <mutex>
+
+namespace nbla {
+
+void synchronizer_cpu_to_b200(Array *src, Array *dst, const int async_flags);
+void synchronizer_b200_to_cpu(Array *src, Array *dst, const int async_flags);
+
+namespace {
+
+vector<string> device_array_classes() { return SingletonManager::get<B200>()->array_classes(); }
+
+void enter(const Context &ctx) {
+  nb200_check(nb200_set_device(ctx.device_id.empty() ? 0 : std::stoi(ctx.device_id)), "nb200_set_device");
+}
+
+#define B200_NO_BACKWARD(NAME)                                                                                  \
+  virtual void backward_impl(const Variables &, const Variables &, const vector<bool> &, const vector<bool> &) { \
+    NBLA_ERROR(error_code::not_implemented, NAME " backward is not implemented in the b200 backend");            \
+  }
+
+const float *rd(Variable *v, const Context &ctx) { return v->get_data_pointer<float>(ctx); }
+float *wr(Variable *v, const Context &ctx, bool write_only = true) {
+  return v->cast_data_and_get_pointer<float>(ctx, write_only);
+}
+
+// Affine::setup_impl's shape rules (src/nbla/function/generic/affine.cpp:29-78).
+struct AffineDims {
+  Size_t rows, w_row, w_col;
+};
+AffineDims setup_affine_shapes(int &base_axis, Variable *x, Variable *w, Variable *bias, Variable *y) {
+  const Shape_t sx = x->shape(), sw = w->shape();
+  NBLA_CHECK(sw.size() >= 2, error_code::value, "Weights(inputs[1]) must be matrix or tensor.");
+  refine_axis(base_axis, x->ndim());
+  NBLA_CHECK(static_cast<Shape_t::size_type>(base_axis) < sx.size(), error_code::value,
+             "Base_axis must be less than ndim of input data(inputs[0]). base_axis: %d >= ndim of input: %d.",
+             base_axis, (int)sx.size());
+  NBLA_CHECK(x->size(base_axis) == sw[0], error_code::value,
+             "Size of input data(inputs[0]) and weights(inputs[1]) mismatch. size of input: %d != size of weights: %d.",
+             (int)x->size(base_axis), (int)sw[0]);
+  AffineDims d;
+  d.w_row = sw[0];
+  d.w_col = w->size() / d.w_row;
+  d.rows = x->size() / x->size(base_axis);
+  Shape_t so(sx.begin(), sx.begin() + base_axis);
+  so.insert(so.end(), sw.begin() + 1, sw.end());
+  y->reshape(so, true);
+  if (bias) {
+    const Shape_t sb = bias->shape();
+    NBLA_CHECK(sb.size() == sw.size() - 1, error_code::value,
+               "Length of bias(inputs[2]) and weights(inputs[1]) mismatch. bias length: %d != weights length-1: %d.",
+               (int)sb.size(), (int)sw.size() - 1);
+    for (Shape_t::size_type i = 0; i < sb.size(); ++i)
+      NBLA_CHECK(sb[i] == sw[i + 1], error_code::value, "Shape of bias(inputs[2]) and weights(inputs[1]) mismatch.");
+  }
+  return d;
+}
+
+void check_same_shape(Variable *w, Variable *wb) {
+  NBLA_CHECK(w->shape() == wb->shape(), error_code::value, "Binary and float weights must have same size.");
+}
+
+// Convolution::setup_impl's shape rules (src/nbla/function/generic/convolution.cpp:40-158), 2-D NCHW.
+struct ConvDims {
+  int batch, C, H, W, Ko, kh, kw;
+};
+ConvDims setup_conv_shapes(int &base_axis, const vector<int> &pad, const vector<int> &stride,
+                           const vector<int> &dilation, int group, Variable *x, Variable *w, Variable *bias,
+                           Variable *y) {
+  const Shape_t sx = x->shape(), sw = w->shape();
+  refine_axis(base_axis, x->ndim());
+  NBLA_CHECK(static_cast<Shape_t::size_type>(base_axis) < sx.size() - 1, error_code::unclassified,
+             "base_axis must be less than ndim - 1 of inputs[0]. base_axis: %d >= ndim of inputs[0] - 1: %d.",
+             base_axis, (int)sx.size() - 1);
+  const size_t spatial = sx.size() - base_axis - 1;
+  NBLA_CHECK(sw.size() == 2 + spatial, error_code::value, "Weights must be a tensor more than 3D.");
+  NBLA_CHECK(spatial == 2, error_code::not_implemented, "the b200 backend implements 2-D convolution only");
+  NBLA_CHECK(pad.size() == spatial, error_code::value, "pad size mismatch.");
+  NBLA_CHECK(stride.size() == spatial, error_code::value, "stride size mismatch.");
+  NBLA_CHECK(dilation.size() == spatial, error_code::value, "dilation size mismatch.");
+  ConvDims d;
+  d.C = sx[base_axis];
+  d.H = sx[base_axis + 1];
+  d.W = sx[base_axis + 2];
+  d.Ko = sw[0];
+  d.kh = sw[2];
+  d.kw = sw[3];
+  NBLA_CHECK(d.C % group == 0, error_code::value,
+             "Number of input channel needs to be divisible by group. Input channel: %d, group: %d.", d.C, group);
+  NBLA_CHECK(d.Ko % group == 0, error_code::value,
+             "Number of output channel needs to be divisible by group. Output channel: %d, group: %d.", d.Ko, group);
+  NBLA_CHECK(d.C / group == sw[1], error_code::value, "Number of grouped channel mismatch.");
+  Shape_t so(sx.begin(), sx.begin() + base_axis);
+  d.batch = 1;
+  for (int i = 0; i < base_axis; ++i)
+    d.batch *= sx[i];
+  so.push_back(d.Ko);
+  const int in[2] = {d.H, d.W}, k[2] = {d.kh, d.kw};
+  for (int i = 0; i < 2; ++i) {
+    const int kk = dilation[i] * (k[i] - 1) + 1;
+    const int o = (in[i] + 2 * pad[i] - kk) / stride[i] + 1;
+    NBLA_CHECK(in[i] + 2 * pad[i] - kk >= 0 && o > 0, error_code::value,
+               "Invalid configuration of convolution at %d-th spatial dimension.  {input:%d, kernel:%d, pad:%d, "
+               "stride:%d, dilation:%d}.",
+               i, in[i], k[i], pad[i], stride[i], dilation[i]);
+    so.push_back(o);
+  }
+  y->reshape(so, true);
+  if (bias) {
+    NBLA_CHECK(bias->shape().size() == 1, error_code::value, "Bias(inputs[2]) must be a 1d tensor.");
+    NBLA_CHECK(bias->shape()[0] == d.Ko, error_code::value, "Shape of bias(inputs[2]) and weights(inputs[1]) mismatch.");
+  }
+  return d;
+}
+
+// ------------------------------------------------------------- quantizers
+template <typename T> class FixedPointQuantizeB200 : public FixedPointQuantize<T> {
+public:
+  using FixedPointQuantize<T>::FixedPointQuantize;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_);
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_fixed_point_quantize_f32(x, y, in[0]->size(), this->sign_, this->n_, this->delta_, nullptr),
+                "FixedPointQuantize");
+    if ((this->sign_ ? this->n_ - 1 : this->n_) <= 7)
+      fxp_tag_set(out[0], this->delta_);
+  }
+  B200_NO_BACKWARD("FixedPointQuantize")
+};
+
+template <typename T> class Pow2QuantizeB200 : public Pow2Quantize<T> {
+public:
+  using Pow2Quantize<T>::Pow2Quantize;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_);
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_pow2_quantize_f32(x, y, in[0]->size(), this->sign_, this->with_zero_, this->n_, this->m_,
+                                        nullptr),
+                "Pow2Quantize");
+  }
+  B200_NO_BACKWARD("Pow2Quantize")
+};
+
+template <typename T> class MinMaxQuantizeB200 : public MinMaxQuantize<T> {
+public:
+  using MinMaxQuantize<T>::MinMaxQuantize;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) {
+    // Shape rules of min_max_quantize.cpp:54-83.
+    Variable *x = in[0], *q = in[1];
+    for (int i = 2; i <= 4; ++i) {
+      NBLA_CHECK(in[i]->ndim() == q->ndim(), error_code::value, "All input dimensions must be same.");
+      NBLA_CHECK(in[i]->shape() == q->shape(), error_code::value,
+                 "All shapes among ql_min, ql_max, qr_min, and qr_max must be same.");
+    }
+    NBLA_CHECK(q->ndim() == x->ndim(), error_code::value, "x and the quantization ranges must have the same ndim.");
+    for (int a = 0; a < q->ndim(); ++a)
+      NBLA_CHECK(q->shape()[a] == 1 || q->shape()[a] == x->shape()[a], error_code::value,
+                 "x.shape and ql_min.shape must be same except for i-th dimension where ql_min.shape[i] == 1.");
+    out[0]->reshape(x->shape(), true);
+    this->scale_sptr_ = make_shared<Variable>(q->shape());
+  }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const Shape_t sx = in[0]->shape(), sq = in[1]->shape();
+    const float *x = rd(in[0], this->ctx_);
+    float *qr_min = wr(in[1], this->ctx_, false), *qr_max = wr(in[2], this->ctx_, false);
+    const float *ql_min = rd(in[3], this->ctx_), *ql_max = rd(in[4], this->ctx_);
+    float *scale = wr(this->scale_sptr_.get(), this->ctx_);
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_min_max_quantize_f32(x, sx.data(), (int)sx.size(), qr_min, qr_max, ql_min, ql_max, sq.data(),
+                                           this->decay_, this->x_min_max_, this->ema_, this->eps_, y, scale, nullptr),
+                "MinMaxQuantize");
+  }
+  B200_NO_BACKWARD("MinMaxQuantize")
+};
+
+// --------------------------------------------------------- binary affines
+template <typename T> class BinaryWeightAffineB200 : public BinaryWeightAffine<T> {
+  Size_t rows_;
+
+public:
+  using BinaryWeightAffine<T>::BinaryWeightAffine;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) {
+    const AffineDims d = setup_affine_shapes(this->base_axis_, in[0], in[1], in.size() == 5 ? in[4] : nullptr, out[0]);
+    check_same_shape(in[1], in[2]);
+    rows_ = d.rows;
+    this->w_row_ = d.w_row;
+    this->w_col_ = d.w_col;
+    NBLA_CHECK(in[3]->size() == this->w_col_, error_code::value, "Size of alpha must be equal to output size.");
+  }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
+    float *wb = wr(in[2], this->ctx_), *alpha = wr(in[3], this->ctx_);
+    const float *b = in.size() == 5 ? rd(in[4], this->ctx_) : nullptr;
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_binary_weight_affine_f32(x, w, wb, alpha, b, y, rows_, this->w_row_, this->w_col_,
+                                               this->quantize_zero_to_, nullptr),
+                "BinaryWeightAffine");
+  }
+  B200_NO_BACKWARD("BinaryWeightAffine")
+};
+
+template <typename T> class BinaryConnectAffineB200 : public BinaryConnectAffine<T> {
+  AffineDims d_;
+
+public:
+  using BinaryConnectAffine<T>::BinaryConnectAffine;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) {
+    d_ = setup_affine_shapes(this->base_axis_, in[0], in[1], in.size() == 4 ? in[3] : nullptr, out[0]);
+    check_same_shape(in[1], in[2]);
+  }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
+    float *wb = wr(in[2], this->ctx_);
+    const float *b = in.size() == 4 ? rd(in[3], this->ctx_) : nullptr;
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_binary_connect_affine_f32(x, w, wb, b, y, d_.rows, d_.w_row, d_.w_col, this->quantize_zero_to_,
+                                                nullptr),
+                "BinaryConnectAffine");
+  }
+  B200_NO_BACKWARD("BinaryConnectAffine")
+};
+
+// ---------------------------------------------------- binary convolutions
+template <typename T> class BinaryWeightConvolutionB200 : public BinaryWeightConvolution<T> {
+  ConvDims d_;
+
+public:
+  using BinaryWeightConvolution<T>::BinaryWeightConvolution;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) {
+    d_ = setup_conv_shapes(this->base_axis_, this->pad_, this->stride_, this->dilation_, this->group_, in[0], in[1],
+                           in.size() == 5 ? in[4] : nullptr, out[0]);
+    check_same_shape(in[1], in[2]);
+    NBLA_CHECK(in[3]->size() == d_.Ko, error_code::value, "Size of alpha must be equal to the number of output maps.");
+  }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float delta = fxp_tag_get(in[0]);
+    const bool sign_ok = this->quantize_zero_to_ == 1.f || this->quantize_zero_to_ == -1.f ||
+                         this->quantize_zero_to_ == 0.f;
+    const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
+    float *wb = wr(in[2], this->ctx_), *alpha = wr(in[3], this->ctx_);
+    const float *b = in.size() == 5 ? rd(in[4], this->ctx_) : nullptr;
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_binary_weight_convolution_f32(
+                    x, w, wb, alpha, b, y, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
+                    this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1],
+                    this->group_, this->quantize_zero_to_, sign_ok ? delta : 0.0f, nullptr),
+                "BinaryWeightConvolution");
+  }
+  B200_NO_BACKWARD("BinaryWeightConvolution")
+};
+
+template <typename T> class BinaryConnectConvolutionB200 : public BinaryConnectConvolution<T> {
+  ConvDims d_;
+
+public:
+  using BinaryConnectConvolution<T>::BinaryConnectConvolution;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) {
+    d_ = setup_conv_shapes(this->base_axis_, this->pad_, this->stride_, this->dilation_, this->group_, in[0], in[1],
+                           in.size() == 4 ? in[3] : nullptr, out[0]);
+    check_same_shape(in[1], in[2]);
+  }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float delta = fxp_tag_get(in[0]);
+    const bool sign_ok = this->quantize_zero_to_ == 1.f || this->quantize_zero_to_ == -1.f ||
+                         this->quantize_zero_to_ == 0.f;
+    const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
+    float *wb = wr(in[2], this->ctx_);
+    const float *b = in.size() == 4 ? rd(in[3], this->ctx_) : nullptr;
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_binary_connect_convolution_f32(
+                    x, w, wb, b, y, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0], this->pad_[1],
+                    this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1], this->group_,
+                    this->quantize_zero_to_, sign_ok ? delta : 0.0f, nullptr),
+                "BinaryConnectConvolution");
+  }
+  B200_NO_BACKWARD("BinaryConnectConvolution")
+};
+
+// ------------------------------------------------------------- companions
+template <typename T> class AffineB200 : public Affine<T> {
+  AffineDims d_;
+
+public:
+  using Affine<T>::Affine;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) {
+    d_ = setup_affine_shapes(this->base_axis_, in[0], in[1], in.size() == 3 ? in[2] : nullptr, out[0]);
+  }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float dx = fxp_tag_get(in[0]), dw = fxp_tag_get(in[1]);
+    const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
+    const float *b = in.size() == 3 ? rd(in[2], this->ctx_) : nullptr;
+    float *y = wr(out[0], this->ctx_);
+    if (dx > 0.f && dw > 0.f && d_.w_row <= 133000)
+      nb200_check(nb200_affine_fxp8_f32(x, w, dx, dw, b, y, d_.rows, d_.w_row, d_.w_col, nullptr),
+                  "Affine (fixed-point operands)");
+    else
+      nb200_check(nb200_affine_f32(x, w, b, y, d_.rows, d_.w_row, d_.w_col, nullptr), "Affine");
+  }
+  B200_NO_BACKWARD("Affine")
+};
+
+template <typename T> class ConvolutionB200 : public Convolution<T> {
+  ConvDims d_;
+
+public:
+  using Convolution<T>::Convolution;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) {
+    NBLA_CHECK(!this->channel_last_, error_code::not_implemented, "channel_last is not supported");
+    d_ = setup_conv_shapes(this->base_axis_, this->pad_, this->stride_, this->dilation_, this->group_, in[0], in[1],
+                           in.size() == 3 ? in[2] : nullptr, out[0]);
+  }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
+    const float *b = in.size() == 3 ? rd(in[2], this->ctx_) : nullptr;
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_convolution_f32(x, w, b, y, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
+                                      this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0],
+                                      this->dilation_[1], this->group_, nullptr),
+                "Convolution");
+  }
+  B200_NO_BACKWARD("Convolution")
+};
+
+template <typename T> class BatchNormalizationB200 : public BatchNormalization<T> {
+public:
+  using BatchNormalization<T>::BatchNormalization;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) {
+    // Index and size rules of batch_normalization.cpp:31-115 for the inference case.
+    NBLA_CHECK(!this->batch_stat_, error_code::not_implemented,
+               "batch_stat=true (training statistics) is outside the b200 forward path");
+    NBLA_CHECK(this->axes_.size() == 1, error_code::not_implemented, "Specifying axis more than one is not supported");
+    NBLA_CHECK(out.size() == 1, error_code::value,
+               "If batch_stat_ is false, it cannot output batch mean and variance.");
+    const int n = (int)in.size();
+    this->b_idx_ = this->no_bias_ ? -1 : 1;
+    this->g_idx_ = this->no_scale_ ? -1 : (this->no_bias_ ? 1 : 2);
+    this->m_idx_ = n - 2;
+    this->v_idx_ = n - 1;
+    NBLA_CHECK(n == 3 + (this->no_bias_ ? 0 : 1) + (this->no_scale_ ? 0 : 1), error_code::value,
+               "Number of inputs does not match no_scale / no_bias.");
+    const Shape_t sx = in[0]->shape();
+    refine_axis(this->axes_[0], in[0]->ndim());
+    const Size_t size = in[0]->size();
+    const Size_t size_axis = in[0]->size(this->axes_[0]);
+    this->size0_ = size / size_axis;
+    this->size1_ = sx[this->axes_[0]];
+    this->size2_ = size / this->size0_ / this->size1_;
+    this->size12_ = this->size1_ * this->size2_;
+    this->size02_ = this->size0_ * this->size2_;
+    for (int i = 1; i < n; ++i)
+      NBLA_CHECK(in[i]->size() == this->size1_, error_code::value,
+                 "Shape of inputs[%d] does not match the normalised axis (%d elements expected).", i,
+                 (int)this->size1_);
+    out[0]->reshape(sx, true);
+  }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_);
+    const float *beta = this->no_bias_ ? nullptr : rd(in[this->b_idx_], this->ctx_);
+    const float *gamma = this->no_scale_ ? nullptr : rd(in[this->g_idx_], this->ctx_);
+    const float *mean = rd(in[this->m_idx_], this->ctx_), *var = rd(in[this->v_idx_], this->ctx_);
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_batch_normalization_inference_f32(x, beta, gamma, mean, var, y, this->size0_, this->size1_,
+                                                        this->size2_, this->eps_, nullptr),
+                "BatchNormalization");
+  }
+  virtual void recompute_impl(const Variables &in, const Variables &out) { forward_impl(in, out); }
+  B200_NO_BACKWARD("BatchNormalization")
+};
+
+template <typename T> class ReLUB200 : public ReLU<T> {
+public:
+  using ReLU<T>::ReLU;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float tag = fxp_tag_get(in[0]);
+    const float *x = rd(in[0], this->ctx_);
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_relu_f32(x, y, in[0]->size(), nullptr), "ReLU");
+    if (tag > 0.f)
+      fxp_tag_set(out[0], tag); // max(0, k * delta) is still a multiple of delta
+  }
+  B200_NO_BACKWARD("ReLU")
+};
+
+template <typename T> class Add2B200 : public Add2<T> {
+public:
+  using Add2<T>::Add2;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) {
+    NBLA_CHECK(in[0]->shape() == in[1]->shape(), error_code::not_implemented,
+               "broadcasting Add2 is not implemented in the b200 backend");
+    out[0]->reshape(in[0]->shape(), true);
+  }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const float *a = rd(in[0], this->ctx_), *b = rd(in[1], this->ctx_);
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_add2_f32(a, b, y, in[0]->size(), nullptr), "Add2");
+  }
+  B200_NO_BACKWARD("Add2")
+};
+
+template <typename T> class MaxPoolingB200 : public MaxPooling<T> {
+public:
+  using MaxPooling<T>::MaxPooling;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    NBLA_CHECK(!this->channel_last_, error_code::not_implemented, "channel_last is not supported");
+    NBLA_CHECK(this->kernel_.size() == 2, error_code::not_implemented, "the b200 backend implements 2-D pooling only");
+    enter(this->ctx_);
+    const float tag = fxp_tag_get(in[0]);
+    const Shape_t sx = in[0]->shape();
+    const int H = sx[sx.size() - 2], W = sx[sx.size() - 1];
+    const float *x = rd(in[0], this->ctx_);
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_max_pooling_f32(x, y, in[0]->size() / (H * W), H, W, this->kernel_[0], this->kernel_[1],
+                                      this->stride_[0], this->stride_[1], this->pad_[0], this->pad_[1],
+                                      this->ignore_border_, nullptr),
+                "MaxPooling");
+    if (tag > 0.f)
+      fxp_tag_set(out[0], tag); // a maximum of multiples of delta is one of them
+  }
+  B200_NO_BACKWARD("MaxPooling")
+};
+
+template <typename T> class GlobalAveragePoolingB200 : public GlobalAveragePooling<T> {
+public:
+  using GlobalAveragePooling<T>::GlobalAveragePooling;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const Shape_t sx = in[0]->shape();
+    const Size_t maps = sx[0] * sx[1];
+    const float *x = rd(in[0], this->ctx_);
+    float *y = wr(out[0], this->ctx_);
+    nb200_check(nb200_global_average_pooling_f32(x, y, maps, in[0]->size() / maps, nullptr), "GlobalAveragePooling");
+  }
+  B200_NO_BACKWARD("GlobalAveragePooling")
+};
+
+} // namespace
+
+// ------------------------------------------------------------------- init
+void init_b200() {
+  static std::mutex m;
+  std::lock_guard<std::mutex> lock(m);
+  static volatile bool done = false;
+  if (done)
+    return;
+  done = true;
+  init_cpu();
+  nb200_check(nb200_check_device(), "init_b200");
+
+  NBLA_REGISTER_BACKEND("b200", []() { return SingletonManager::get<B200>(); });
+  NBLA_REGISTER_ARRAY_CREATOR(B200Array);
+  SingletonManager::get<B200>()->register_array_class("B200Array");
+  NBLA_REGISTER_ARRAY_CREATOR(B200CachedArray);
+  SingletonManager::get<B200>()->register_array_class("B200CachedArray");
+  // "B200CachedArray" first: Function::setup picks the first allowed class the context names.
+  SingletonManager::get<B200>()->_set_array_classes({"B200CachedArray", "B200Array"});
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(B200Array, B200CachedArray, synchronizer_default);
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(B200CachedArray, B200Array, synchronizer_default);
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(CpuArray, B200Array, synchronizer_cpu_to_b200);
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(CpuArray, B200CachedArray, synchronizer_cpu_to_b200);
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(CpuCachedArray, B200Array, synchronizer_cpu_to_b200);
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(CpuCachedArray, B200CachedArray, synchronizer_cpu_to_b200);
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(B200Array, CpuArray, synchronizer_b200_to_cpu);
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(B200Array, CpuCachedArray, synchronizer_b200_to_cpu);
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(B200CachedArray, CpuArray, synchronizer_b200_to_cpu);
+  NBLA_REGISTER_ARRAY_SYNCHRONIZER(B200CachedArray, CpuCachedArray, synchronizer_b200_to_cpu);
+  NBLA_REGISTER_ARRAY_GROUP(B200Array, b200);
+  NBLA_REGISTER_ARRAY_GROUP(B200CachedArray, b200);
+
+  typedef const vector<int> &ivec;
+#define REG(NAME, ...)                                                                                       \
+  {                                                                                                          \
+    using NAME##_b200_float = NAME##B200<float>;                                                             \
+    NBLA_REGISTER_FUNCTION_IMPL(NAME, NAME##_b200_float, "b200:float", ##__VA_ARGS__);                       \
+  }
+  REG(FixedPointQuantize, bool, int, float, bool);
+  REG(Pow2Quantize, bool, bool, int, int, bool);
+  REG(MinMaxQuantize, float, bool, bool, bool, float);
+  REG(BinaryWeightAffine, int, float);
+  REG(BinaryConnectAffine, int, float);
+  REG(BinaryWeightConvolution, int, ivec, ivec, ivec, int, float);
+  REG(BinaryConnectConvolution, int, ivec, ivec, ivec, int, float);
+  REG(Affine, int);
+  REG(Convolution, int, ivec, ivec, ivec, int, bool);
+  REG(BatchNormalization, ivec, float, float, bool, bool, bool);
+  REG(ReLU, bool);
+  REG(Add2, bool);
+  REG(MaxPooling, ivec, ivec, bool, ivec, bool);
+  REG(GlobalAveragePooling);
+#undef REG
+}
+
+} // namespace nbla

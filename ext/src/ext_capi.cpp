@@ -1,0 +1,183 @@
+// C ABI test harness over the nnabla host library with the b200 extension
+// loaded: creates a function through nnabla's registry for a given backend
+// ("cpu:float" or "b200:float"), feeds it from host buffers through
+// nnabla's own Variable / SyncedArray machinery (so device arrays, the
+// allocator and the synchronizers of the extension are exercised), runs
+// setup + forward and copies inputs (several functions write theirs) and
+// outputs back. The same graph runs on either backend by changing the
+// context only, which is what the tests compare.
+#include <nbla_b200/b200.hpp>
+
+#include <nbla/exception.hpp>
+#include <nbla/function.hpp>
+#include <nbla/variable.hpp>
+
+#include <nbla/function/add2.hpp>
+#include <nbla/function/affine.hpp>
+#include <nbla/function/batch_normalization.hpp>
+#include <nbla/function/binary_connect_affine.hpp>
+#include <nbla/function/binary_connect_convolution.hpp>
+#include <nbla/function/binary_weight_affine.hpp>
+#include <nbla/function/binary_weight_convolution.hpp>
+#include <nbla/function/convolution.hpp>
+#include <nbla/function/fixed_point_quantize.hpp>
+#include <nbla/function/global_average_pooling.hpp>
+#include <nbla/function/max_pooling.hpp>
+#include <nbla/function/min_max_quantize.hpp>
+#include <nbla/function/pow2_quantize.hpp>
+#include <nbla/function/relu.hpp>
+
+#include <chrono>
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+using namespace nbla;
+
+namespace {
+thread_local std::string g_err;
+
+FunctionPtr create(const std::string &name, const Context &ctx, const double *s, int n_s,
+                   const std::vector<std::vector<int>> &ivs) {
+  auto S = [&](int i) -> double {
+    NBLA_CHECK(i < n_s, error_code::value, "missing scalar argument %d", i);
+    return s[i];
+  };
+  auto V = [&](size_t i) -> const std::vector<int> & {
+    NBLA_CHECK(i < ivs.size(), error_code::value, "missing vector argument %d", (int)i);
+    return ivs[i];
+  };
+  if (name == "FixedPointQuantize")
+    return create_FixedPointQuantize(ctx, S(0) != 0, (int)S(1), (float)S(2), S(3) != 0);
+  if (name == "Pow2Quantize")
+    return create_Pow2Quantize(ctx, S(0) != 0, S(1) != 0, (int)S(2), (int)S(3), S(4) != 0);
+  if (name == "MinMaxQuantize")
+    return create_MinMaxQuantize(ctx, (float)S(0), S(1) != 0, S(2) != 0, S(3) != 0, (float)S(4));
+  if (name == "BinaryWeightAffine")
+    return create_BinaryWeightAffine(ctx, (int)S(0), (float)S(1));
+  if (name == "BinaryConnectAffine")
+    return create_BinaryConnectAffine(ctx, (int)S(0), (float)S(1));
+  if (name == "BinaryWeightConvolution")
+    return create_BinaryWeightConvolution(ctx, (int)S(0), V(0), V(1), V(2), (int)S(1), (float)S(2));
+  if (name == "BinaryConnectConvolution")
+    return create_BinaryConnectConvolution(ctx, (int)S(0), V(0), V(1), V(2), (int)S(1), (float)S(2));
+  if (name == "Affine")
+    return create_Affine(ctx, (int)S(0));
+  if (name == "Convolution")
+    return create_Convolution(ctx, (int)S(0), V(0), V(1), V(2), (int)S(1), S(2) != 0);
+  if (name == "BatchNormalization")
+    return create_BatchNormalization(ctx, V(0), (float)S(0), (float)S(1), S(2) != 0, S(3) != 0, S(4) != 0);
+  if (name == "ReLU")
+    return create_ReLU(ctx, S(0) != 0);
+  if (name == "MaxPooling")
+    return create_MaxPooling(ctx, V(0), V(1), S(0) != 0, V(2), S(1) != 0);
+  if (name == "GlobalAveragePooling")
+    return create_GlobalAveragePooling(ctx);
+  if (name == "Add2")
+    return create_Add2(ctx, S(0) != 0);
+  NBLA_ERROR(error_code::value, "unknown function %s", name.c_str());
+}
+} // namespace
+
+extern "C" {
+
+struct nbext_tensor {
+  float *data;
+  int32_t ndim;
+  int64_t shape[8];
+};
+
+const char *nbext_last_error() { return g_err.c_str(); }
+
+int nbext_init() {
+  try {
+    init_b200();
+    return 0;
+  } catch (const std::exception &e) {
+    g_err = e.what();
+    return 1;
+  }
+}
+
+// backend: "cpu:float" or "b200:float". prequant[i] > 0: input i is first
+// passed through FixedPointQuantize(sign, 8, prequant[i]) on the same backend
+// and the function consumes that function's output Variable (this is how the
+// fixed-point tag reaches the contraction functions). Returns the name() of
+// the created function in fname (for the tests' name check).
+int nbext_forward(const char *backend, const char *op, const double *s, int n_s, const int32_t *iv,
+                  const int32_t *iv_len, int n_iv, nbext_tensor *in, int n_in, const float *prequant,
+                  nbext_tensor *out, int n_out, int mode, char *fname, int fname_len) {
+  try {
+    const std::string be(backend);
+    Context ctx = be == "cpu:float" ? Context({"cpu:float"}, "CpuCachedArray", "0") : b200_context("0");
+    if (be != "cpu:float")
+      init_b200();
+    Context cpu({"cpu:float"}, "CpuCachedArray", "0");
+    std::vector<std::vector<int>> ivs;
+    const int32_t *p = iv;
+    for (int i = 0; i < n_iv; ++i) {
+      ivs.emplace_back(p, p + iv_len[i]);
+      p += iv_len[i];
+    }
+    FunctionPtr f = create(op, ctx, s, n_s, ivs);
+    if (fname && fname_len > 0) {
+      std::strncpy(fname, f->name().c_str(), fname_len - 1);
+      fname[fname_len - 1] = 0;
+    }
+    std::vector<VariablePtr> vin, vq, vout;
+    std::vector<FunctionPtr> quantizers;
+    Variables pin, pout;
+    for (int i = 0; i < n_in; ++i) {
+      Shape_t sh(in[i].shape, in[i].shape + in[i].ndim);
+      vin.push_back(std::make_shared<Variable>(sh));
+      if (prequant && prequant[i] > 0.f) {
+        vq.push_back(std::make_shared<Variable>(sh));
+        quantizers.push_back(create_FixedPointQuantize(ctx, true, 8, prequant[i], true));
+        quantizers.back()->setup(Variables{vin.back().get()}, Variables{vq.back().get()});
+        pin.push_back(vq.back().get());
+      } else {
+        vq.push_back(nullptr);
+        quantizers.push_back(nullptr);
+        pin.push_back(vin.back().get());
+      }
+    }
+    for (int i = 0; i < n_out; ++i) {
+      vout.push_back(std::make_shared<Variable>());
+      pout.push_back(vout.back().get());
+    }
+    f->setup(pin, pout);
+    for (int i = 0; i < n_out; ++i) {
+      const Shape_t sh = pout[i]->shape();
+      NBLA_CHECK(sh.size() <= 8, error_code::value, "ndim > 8");
+      out[i].ndim = (int32_t)sh.size();
+      for (size_t d = 0; d < sh.size(); ++d)
+        out[i].shape[d] = sh[d];
+    }
+    if (mode == 0)
+      return 0;
+    // Host data enters through a CPU array; the function's first device read triggers the synchronizer.
+    for (int i = 0; i < n_in; ++i) {
+      float *h = vin[i]->cast_data_and_get_pointer<float>(cpu, true);
+      std::memcpy(h, in[i].data, sizeof(float) * vin[i]->size());
+    }
+    for (int i = 0; i < n_in; ++i)
+      if (quantizers[i])
+        quantizers[i]->forward(Variables{vin[i].get()}, Variables{vq[i].get()});
+    f->forward(pin, pout);
+    for (int i = 0; i < n_in; ++i) {
+      const float *h = pin[i]->get_data_pointer<float>(cpu);
+      std::memcpy(in[i].data, h, sizeof(float) * pin[i]->size());
+    }
+    for (int i = 0; i < n_out; ++i) {
+      const float *h = pout[i]->get_data_pointer<float>(cpu);
+      std::memcpy(out[i].data, h, sizeof(float) * pout[i]->size());
+    }
+    return 0;
+  } catch (const std::exception &e) {
+    g_err = e.what();
+    return 1;
+  }
+}
+}

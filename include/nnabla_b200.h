@@ -69,7 +69,9 @@ int nb200_free_host(void *host_ptr);
 int nb200_memcpy_h2d(void *dev_dst, const void *host_src, size_t bytes, void *stream);
 int nb200_memcpy_d2h(void *host_dst, const void *dev_src, size_t bytes, void *stream);
 int nb200_memcpy_d2d(void *dev_dst, const void *dev_src, size_t bytes, void *stream);
-/* Array::zero / Array::fill (include/nbla/array.hpp:128-140) for fp32 arrays. */
+/* Array::zero / Array::fill (include/nbla/array.hpp:128-140): zero for any
+ * dtype (byte-wise), fill for fp32 arrays. */
+int nb200_memset_zero(void *dev_ptr, size_t bytes, void *stream);
 int nb200_fill_f32(float *dev_ptr, size_t n, float value, void *stream);
 int nb200_stream_create(void **stream);
 int nb200_stream_destroy(void *stream);

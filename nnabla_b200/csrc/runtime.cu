@@ -213,6 +213,12 @@ int nb200_memcpy_d2d(void *dev_dst, const void *dev_src, size_t bytes, void *str
   return NB200_OK;
 }
 
+int nb200_memset_zero(void *dev_ptr, size_t bytes, void *stream) {
+  if (bytes)
+    NB_CUDA(cudaMemsetAsync(dev_ptr, 0, bytes, as_stream(stream)));
+  return NB200_OK;
+}
+
 int nb200_fill_f32(float *dev_ptr, size_t n, float value, void *stream) {
   if (n == 0)
     return NB200_OK;

@@ -1,0 +1,131 @@
+"""The nnabla extension backend "b200:float" against nnabla's own "cpu:float"
+context in the same process: the function is created through nnabla's
+registry, fed through nnabla Variables / SyncedArrays (device arrays, caching
+allocator and synchronizers of the extension), and only the context differs.
+Quantizer outputs, signs and the companions must match bit for bit; alpha to
+fp32 summation error; contraction outputs within 1e-5 of the output RMS."""
+import numpy as np
+import pytest
+
+import cases
+import ext_harness as H
+from golden_util import bits
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not H.available(), reason="extension library not built")]
+CPU, B200 = "cpu:float", "b200:float"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _init():
+    H.init()
+
+
+def both(op, scalars, ivecs, inputs, n_out=1, prequant=None):
+    c = H.forward(CPU, op, scalars, ivecs, inputs, n_out, prequant)
+    g = H.forward(B200, op, scalars, ivecs, inputs, n_out, prequant)
+    assert c[2] == g[2] == op  # name() is the reference's
+    return c, g
+
+
+@pytest.mark.parametrize("sign,n,delta", cases.FXP_GRID)
+def test_fixed_point_quantize(sign, n, delta):
+    n_eff = n - 1 if sign else n
+    x = np.concatenate([cases.fxp_input().ravel(), cases.edge_values_fxp(np.float32(delta), n_eff)])
+    c, g = both("FixedPointQuantize", [sign, n, delta, True], [], [x])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+
+
+@pytest.mark.parametrize("sign,with_zero,n,m", cases.POW2_GRID + [(True, True, 8, 1)])
+def test_pow2_quantize(sign, with_zero, n, m):
+    x = np.concatenate([cases.fxp_input().ravel(), cases.edge_values_pow2()])
+    c, g = both("Pow2Quantize", [sign, with_zero, n, m, True], [], [x])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+
+
+@pytest.mark.parametrize("shapes,decay,x_min_max,ema", cases.MINMAX_GRID)
+def test_min_max_quantize(shapes, decay, x_min_max, ema):
+    ins = list(cases.minmax_inputs(*shapes))
+    c, g = both("MinMaxQuantize", [decay, x_min_max, ema, True, 0.01], [], ins)
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+    assert np.array_equal(bits(g[1][1]), bits(c[1][1]))  # qr_min written back
+    assert np.array_equal(bits(g[1][2]), bits(c[1][2]))  # qr_max written back
+
+
+@pytest.mark.parametrize("xs,ws,base_axis", cases.AFFINE_CASES)
+@pytest.mark.parametrize("qzt", cases.QZT)
+def test_binary_affines(xs, ws, base_axis, qzt):
+    x, w, b = cases.affine_inputs(xs, ws, with_zeros=True)
+    wb = np.zeros_like(w)
+    alpha = np.zeros(int(np.prod(ws[1:])), np.float32)
+    c, g = both("BinaryWeightAffine", [base_axis, qzt], [], [x, w, wb, alpha, b])
+    assert np.array_equal(bits(g[1][2]), bits(c[1][2]))                      # Wb
+    np.testing.assert_allclose(g[1][3], c[1][3], rtol=2e-6)                  # alpha
+    assert g[0][0].shape == c[0][0].shape and cases.rel_rms(g[0][0], c[0][0]) < 1e-5
+    c, g = both("BinaryConnectAffine", [base_axis, qzt], [], [x, w, wb, b])
+    assert np.array_equal(bits(g[1][2]), bits(c[1][2]))
+    assert cases.rel_rms(g[0][0], c[0][0]) < 1e-5
+
+
+@pytest.mark.parametrize("xs,ws,pad,stride,dilation,group", cases.CONV_CASES)
+def test_binary_convolutions(xs, ws, pad, stride, dilation, group):
+    x, w, b = cases.conv_inputs(xs, ws, with_zeros=True)
+    wb, alpha = np.zeros_like(w), np.zeros(ws[0], np.float32)
+    c, g = both("BinaryWeightConvolution", [1, group, 1.0], [pad, stride, dilation], [x, w, wb, alpha, b])
+    assert np.array_equal(bits(g[1][2]), bits(c[1][2]))
+    np.testing.assert_allclose(g[1][3], c[1][3], rtol=2e-6)
+    assert g[0][0].shape == c[0][0].shape and cases.rel_rms(g[0][0], c[0][0]) < 1e-5
+    c, g = both("BinaryConnectConvolution", [1, group, 1.0], [pad, stride, dilation], [x, w, wb, b])
+    assert np.array_equal(bits(g[1][2]), bits(c[1][2]))
+    assert cases.rel_rms(g[0][0], c[0][0]) < 1e-5
+
+
+def test_fixed_point_tag_selects_the_exact_int8_paths():
+    """FixedPointQuantize -> Affine / BinaryWeightConvolution inside nnabla's
+    machinery: the extension recognises the quantizer's output array and runs
+    the int8 contraction; the fixed-point affine then equals the CPU result
+    bit for bit."""
+    rng = np.random.RandomState(0)
+    x = rng.randn(96, 256).astype(np.float32)
+    w = (0.02 * rng.randn(256, 320)).astype(np.float32)
+    b = (0.01 * rng.randn(320)).astype(np.float32)
+    c, g = both("Affine", [1], [], [x, w, b], prequant=[2.0 ** -5, 2.0 ** -10, 0])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+    xc = np.maximum(rng.randn(2, 64, 14, 14), 0).astype(np.float32)
+    wc = (rng.randn(64, 64, 3, 3) * np.sqrt(2.0 / 576)).astype(np.float32)
+    wb, alpha = np.zeros_like(wc), np.zeros(64, np.float32)
+    c, g = both("BinaryWeightConvolution", [1, 1, 1.0], [(1, 1), (1, 1), (1, 1)], [xc, wc, wb, alpha],
+                prequant=[2.0 ** -4, 0, 0, 0])
+    assert cases.rel_rms(g[0][0], c[0][0]) < 2e-6
+
+
+def test_companions_and_full_precision_layers():
+    rng = np.random.RandomState(cases.SEED)
+    x = rng.randn(2, 6, 9, 12).astype(np.float32)
+    beta, gamma, mean = (rng.randn(1, 6, 1, 1).astype(np.float32) for _ in range(3))
+    var = (rng.rand(1, 6, 1, 1) + 0.1).astype(np.float32)
+    c, g = both("BatchNormalization", [0.9, 1e-5, False, False, False], [(1,)], [x, beta, gamma, mean, var])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+    for op, sc, iv, ins in [("ReLU", [False], [], [x]), ("Add2", [False], [], [x, x[::-1].copy()]),
+                            ("MaxPooling", [True, False], [(3, 3), (2, 2), (1, 1)], [x]),
+                            ("GlobalAveragePooling", [], [], [x])]:
+        c, g = both(op, sc, iv, ins)
+        assert np.array_equal(bits(g[0][0]), bits(c[0][0])), op
+    xs = rng.randn(2, 3, 20, 20).astype(np.float32)
+    ws = rng.randn(8, 3, 7, 7).astype(np.float32)
+    c, g = both("Convolution", [1, 1, False], [(3, 3), (2, 2), (1, 1)], [xs, ws])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+    xa, wa, ba = cases.affine_inputs((3, 5, 7), (35, 40))
+    c, g = both("Affine", [1], [], [xa, wa, ba])
+    assert cases.rel_rms(g[0][0], c[0][0]) < 1e-5
+
+
+def test_errors_surface_as_exceptions():
+    x = np.zeros((4, 8), np.float32)
+    with pytest.raises(RuntimeError, match="positive"):
+        H.forward(B200, "FixedPointQuantize", [True, 0, 0.5, True], [], [x])
+    w = np.zeros((9, 3), np.float32)
+    with pytest.raises(RuntimeError, match="mismatch"):
+        H.forward(B200, "BinaryWeightAffine", [1, 1.0], [], [x, w, w.copy(), np.zeros(3, np.float32)])
+    with pytest.raises(RuntimeError, match="not implemented|not_implemented|outside"):
+        H.forward(B200, "BatchNormalization", [0.9, 1e-5, True, False, False], [(1,)],
+                  [x.reshape(4, 8, 1, 1)] + [np.zeros((1, 8, 1, 1), np.float32)] * 4)
