@@ -128,45 +128,58 @@ def run_reference_arm(args):
 
 # --------------------------------------------------------------------------- GPU arm
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while
-    the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the clock-event (throttle) reasons of one GPU
+    through NVML from a background thread while the timed region runs.
+    Read-only: nothing about the GPU's settings is changed."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, index):
-        self.proc = None
+    def __init__(self, cuda_index, period_s=0.002):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self.error = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            props = torch.cuda.get_device_properties(cuda_index)
+            bus_id = "%08x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception as exc:  # NVML missing: report it, do not fake clocks
+            self.error = "%s: %s" % (type(exc).__name__, exc)
+            return
+        self._period = period_s
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except AttributeError:
+                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception as exc:
+                self.error = "%s: %s" % (type(exc).__name__, exc)
+                return
+            time.sleep(self._period)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in out.splitlines():
-            p = [s.strip() for s in ln.split(",")]
-            if len(p) < 6:
-                continue
-            try:
-                sm.append(float(p[0]))
-                mx.append(float(p[1]))
-            except ValueError:
-                continue
-            for nm, v in zip(names, p[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(nm)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        out = {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+               "samples": len(self.samples), "reasons": sorted(self.reasons)}
+        if self.error:
+            out["error"] = self.error
+        return out
 
 
 def measured_peaks():
@@ -222,7 +235,7 @@ def run_extras(args, rank, world, barrier):
         "frac_of_bf16_peak_issued": 6 * M * K * N / ms / 1e9 / peaks["bf16_tflops"],
         "includes": "binarise + alpha + split + GEMM, whole forward_impl", "l2": "working set fits L2 (latency-bound case)"}
     # configs[2]: 8-bit fixed-point affine, output columns sharded over the ranks
-    M, K, N = (2048, 4096, 2048) if args.small_extras else (8192, 4096, 8192)
+    M, K, N = (4096, 4096, 4096) if args.small_extras else (8192, 4096, 8192)
     Ns = N // world
     x = rn(M, K)
     w = 0.02 * rn(K, Ns)
@@ -389,8 +402,14 @@ def run_b200_arm(args):
     value = world * 3 * BYTES_PER_ELEM * n * args.steps / (elapsed_ms / 1e3) / 1e9
     k_dom = int(np.argmax(per_kernel_ms))
     achieved = BYTES_PER_ELEM * n / (per_kernel_ms[k_dom] / 1e3) / 1e9
+    # DRAM traffic per element of the dominant kernel from the committed ncu capture at 2^26 elements
+    # (profiles/quantizers_2p26_full_capture.md), scaled to this launch: traffic grows with the element count.
+    ncu_bytes_per_elem = {"fixed_point_quantize": 489.4e6 / 2 ** 26, "pow2_quantize": 488.3e6 / 2 ** 26,
+                          "min_max_quantize": 488.2e6 / 2 ** 26}
     roofline = {"bound": "hbm", "kernel": QUANTIZERS[k_dom], "achieved": achieved, "peak": peaks["hbm_gbs"],
-                "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                "traffic": ncu_bytes_per_elem[QUANTIZERS[k_dom]] * n, "traffic_unit": "bytes per launch",
+                "algorithmic_bytes_per_launch": BYTES_PER_ELEM * n,
                 "per_kernel_GBps": {QUANTIZERS[k]: BYTES_PER_ELEM * n / (per_kernel_ms[k] / 1e3) / 1e9
                                     for k in range(3)}}
     cpu_baseline = None

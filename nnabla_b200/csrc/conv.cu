@@ -176,8 +176,8 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
       return launch_conv<true, 1, 1, 256, 4>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h256, n256, ep, st);
     return launch_conv<true, 1, 1, 128, 6>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
   }
-  if (use256)
-    return launch_conv<false, 1, 3, 256, 2>(g, act, 3, ctot, side, wpitch, c_pad_g, cblocks, h256, n256, ep, st);
+  NB_CHECK(can128, NB200_ENOTIMPL,
+           "fp32-activation convolution with output rows wider than 128 pixels (Wo=%d) is not supported", g.Wo);
   return launch_conv<false, 1, 3, 128, 3>(g, act, 3, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
 }
 

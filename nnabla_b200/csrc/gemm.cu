@@ -3,7 +3,10 @@
 #include <cstring>
 #include <mutex>
 
+#include <cstdlib>
+
 #include "gemm.cuh"
+#include "gemm2.cuh"
 #include "prepare.cuh"
 
 namespace nb200 {
@@ -29,7 +32,7 @@ static int get_encode_fn(EncodeTiledFn *out) {
   return NB200_OK;
 }
 
-// dtype_code: 0 = bf16, 1 = uint8/int8 bytes
+// dtype_code: 0 = bf16, 1 = uint8/int8 bytes, 2 = float32
 int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, const uint64_t *dims,
                  const uint64_t *strides_bytes, const uint32_t *box, const uint32_t *elem_strides) {
   EncodeTiledFn fn;
@@ -47,7 +50,10 @@ int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, c
     if (i < rank - 1)
       s[i] = strides_bytes[i];
   }
-  const CUresult r = fn(map, dtype_code == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+  const CUtensorMapDataType dt = dtype_code == 0   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : dtype_code == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                                   : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const CUresult r = fn(map, dt,
                         (cuuint32_t)rank, const_cast<void *>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -107,6 +113,22 @@ int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch
   const bool narrow = (int64_t)m_tiles * ((N + 127) / 128) < sm_count();
   CUtensorMap ma, mb;
   NB_TRY(make_operand_map(&ma, A, int8, K, pitch_a, M, planes_a, kTileM));
+  // Large problems: two-SM tiles (256 x 256 per CTA pair) halve the B traffic per SM.
+  // NNABLA_B200_GEMM_PAIR=0 forces the single-CTA kernel (debugging aid).
+  static const bool pair_enabled = []() {
+    const char *e = std::getenv("NNABLA_B200_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  const int64_t pair_tiles = (int64_t)((M + kPairTileM - 1) / kPairTileM) * ((N + kPairTileN - 1) / kPairTileN);
+  // (the bulk stores of its epilogue need a 16-byte aligned y with a row pitch that is a multiple of 16 bytes)
+  const bool y_tma_ok = (reinterpret_cast<uintptr_t>(ep.y) & 15) == 0 && (ldy % 4) == 0;
+  if (pair_enabled && y_tma_ok && planes_b == 1 && pair_tiles >= sm_count() / 2) {
+    NB_TRY(make_operand_map(&mb, B, int8, K, pitch_b, N, 1, kPairTileN / 2));
+    if (int8)
+      return launch_pair_gemm<true, 1, 6>(ma, mb, M, N, k_blocks, ep, ldy, st);
+    if (planes_a == 3)
+      return launch_pair_gemm<false, 3, 3>(ma, mb, M, N, k_blocks, ep, ldy, st);
+  }
   if (int8) {
     NB_CHECK(planes_a == 1 && planes_b == 1, NB200_EVALUE, "int8 operands have one plane");
     const bool wide = (int64_t)m_tiles * ((N + 255) / 256) >= sm_count();
@@ -131,7 +153,7 @@ int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch
   }
   if (planes_a == 3 && planes_b == 3) {
     NB_TRY(make_operand_map(&mb, B, false, K, pitch_b, N, 3, 64));
-    return launch_gemm<false, 3, 3, 64, 3, true>(ma, mb, M, N, k_blocks, ep, ldy, st);
+    return launch_gemm<false, 3, 3, 64, 2, true>(ma, mb, M, N, k_blocks, ep, ldy, st);
   }
   return fail(NB200_ENOTIMPL, "no kernel for %d x %d operand planes", planes_a, planes_b);
 }

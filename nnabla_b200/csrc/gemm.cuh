@@ -31,6 +31,7 @@ namespace nb200 {
 constexpr int kGemmThreads = 192; // 6 warps: TMA, MMA, 4 x epilogue
 constexpr int kTileM = 128;
 constexpr int kRowBytes = 128; // one swizzle-atom row: 64 bf16 or 128 int8 along K
+constexpr int kEpilogueStageBytes = 4 * 32 * 33 * 4; // per-warp transpose buffers of the epilogue
 
 // Status codes written by a wait that gave up (low byte = role).
 constexpr int kStatusProducerTimeout = 0x101;
@@ -75,13 +76,14 @@ struct GemmProblem {
                                          int plane, int epb) const {
     ptx::tma_load_3d(dst, map, bar, kb * epb, t.n0, plane);
   }
-  // Address of D(row, first column of chunk c0) and the number of valid
-  // columns in the chunk; columns of a chunk are contiguous in y.
-  __device__ __forceinline__ float *chunk_ptr(const GemmEpilogue &ep, const Tile &t, int row, int c0, int &valid,
-                                              int &gcol) const {
-    gcol = t.n0 + c0;
-    valid = N - gcol;
-    return ep.y + (int64_t)row * ldy + gcol;
+  // y address of D(row, col) = y + row_offset(row) + column offset; the column
+  // part also says whether the column exists and which global column it is
+  // (index into col_scale / col_bias).
+  __device__ __forceinline__ int64_t row_offset(int row) const { return (int64_t)row * ldy; }
+  __device__ __forceinline__ bool col_offset(const Tile &t, int col, int64_t &off, int &gcol) const {
+    gcol = t.n0 + col;
+    off = gcol;
+    return gcol < N;
   }
 };
 
@@ -127,18 +129,16 @@ struct ConvProblem {
     ptx::tma_load_5d(dst, map, bar, t.group * c_group_stride + cb * epb, kx * dw - pw, t.oy0 * sh - ph + ky * dh,
                      t.img0, plane);
   }
-  __device__ __forceinline__ float *chunk_ptr(const GemmEpilogue &ep, const Tile &t, int row, int c0, int &valid,
-                                              int &gcol) const {
-    // Columns of one image's box are contiguous in y (full output rows).
+  __device__ __forceinline__ int64_t row_offset(int row) const { return (int64_t)row * ((int64_t)Ho * Wo); }
+  __device__ __forceinline__ bool col_offset(const Tile &t, int col, int64_t &off, int &gcol) const {
+    // Column = (image of the box, pixel inside the image's h_box x Wo slab); slabs are whole output rows.
     gcol = 0;
     const int per_img = h_box * Wo;
-    const int nn = c0 / per_img, q = c0 - nn * per_img;
+    const int nn = col / per_img, q = col - nn * per_img;
     const int img = t.img0 + nn;
-    const int plane_left = (Ho - t.oy0) * Wo - q; // valid elements before the end of this output map
-    int v = per_img - q;                          // ... and before the end of this image's box
-    v = v < plane_left ? v : plane_left;
-    valid = (nn < n_box && img < Nimg) ? v : 0; // columns past the box are padding of the MMA shape
-    return ep.y + ((int64_t)img * Ko + row) * ((int64_t)Ho * Wo) + (int64_t)t.oy0 * Wo + q;
+    off = (int64_t)img * Ko * ((int64_t)Ho * Wo) + (int64_t)t.oy0 * Wo + q;
+    // columns past the box are padding of the MMA shape; rows past Ho belong to no image
+    return nn < n_box && img < Nimg && q < (Ho - t.oy0) * Wo;
   }
 };
 
@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t *tmem_empty = bars + 2 * STAGES + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  float *stage_out = reinterpret_cast<float *>(tmem_slot + 4); // 4 epilogue warps x 32 x 33 floats
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -312,61 +313,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         break;
       }
       ptx::tc_fence_after_sync();
-      const int row = t.m0 + quarter * 32 + lane;
-      const bool row_ok = row < t.m_end;
-      const float rs = (ep.row_scale && row_ok) ? __fmul_rn(ep.row_scale[row], ep.scale) : ep.scale;
-      const float rb = (ep.row_bias && row_ok) ? ep.row_bias[row] : 0.0f;
+      // Each thread holds one row of the accumulator; the chunk is transposed
+      // through shared memory so that every store instruction writes one
+      // contiguous run of y (lane = column).
+      float *stg = stage_out + (warp - 2) * (32 * 33);
+      const int row_base = t.m0 + quarter * 32;
 #pragma unroll 1
       for (int c0 = 0; c0 < n_cols; c0 += 32) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
         ptx::tmem_ld_wait();
-        if (!row_ok)
-          continue;
-        // A chunk of 32 columns may straddle the boundary between two
-        // contiguous runs of y (two images of a convolution box).
-        int j = 0;
-        while (j < 32) {
-          int valid, gcol;
-          float *dst = prob.chunk_ptr(ep, t, row, c0 + j, valid, gcol);
-          if (valid <= 0)
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          stg[lane * 33 + j] = kInt8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+        __syncwarp();
+        int64_t coff;
+        int gcol;
+        const bool col_ok = prob.col_offset(t, c0 + lane, coff, gcol);
+        const float cs = (ep.col_scale && col_ok) ? ep.col_scale[gcol] : 1.0f;
+        const float cb = (ep.col_bias && col_ok) ? ep.col_bias[gcol] : 0.0f;
+        float *ycol = ep.y + coff;
+#pragma unroll 4
+        for (int i = 0; i < 32; ++i) {
+          const int row = row_base + i;
+          if (row >= t.m_end)
             break;
-          const int run = (valid < 32 - j) ? valid : (32 - j);
-          if (run == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-            for (int q = 0; q < 32; q += 4) {
-              float o[4];
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const float acc = kInt8 ? (float)(int)r[q + u] : __uint_as_float(r[q + u]);
-                const float s = ep.col_scale ? __fmul_rn(rs, ep.col_scale[gcol + q + u]) : rs;
-                float v = __fmul_rn(acc, s);
-                if (ep.row_bias)
-                  v = __fadd_rn(v, rb);
-                if (ep.col_bias)
-                  v = __fadd_rn(v, ep.col_bias[gcol + q + u]);
-                o[u] = v;
-              }
-              *reinterpret_cast<float4 *>(dst + q) = make_float4(o[0], o[1], o[2], o[3]);
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 32; ++q) {
-              // static register indexing: q is the position inside the chunk
-              if (q >= j && q < j + run) {
-                const float acc = kInt8 ? (float)(int)r[q] : __uint_as_float(r[q]);
-                const float s = ep.col_scale ? __fmul_rn(rs, ep.col_scale[gcol + q - j]) : rs;
-                float v = __fmul_rn(acc, s);
-                if (ep.row_bias)
-                  v = __fadd_rn(v, rb);
-                if (ep.col_bias)
-                  v = __fadd_rn(v, ep.col_bias[gcol + q - j]);
-                dst[q - j] = v;
-              }
-            }
-          }
-          j += run;
+          float s = ep.scale;
+          if (ep.row_scale)
+            s = __fmul_rn(ep.row_scale[row], s);
+          if (ep.col_scale)
+            s = __fmul_rn(s, cs);
+          float v = __fmul_rn(stg[i * 33 + lane], s);
+          if (ep.row_bias)
+            v = __fadd_rn(v, ep.row_bias[row]);
+          if (ep.col_bias)
+            v = __fadd_rn(v, cb);
+          if (col_ok)
+            ycol[prob.row_offset(row)] = v;
         }
+        __syncwarp();
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -393,7 +378,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 }
 
 template <bool kInt8, int PA, int PB, int BN, int STAGES> constexpr size_t gemm_smem_bytes() {
-  return (size_t)STAGES * (PA * kTileM * kRowBytes + PB * BN * kRowBytes) + (2 * STAGES + 4) * 8 + 16 + 1024;
+  return (size_t)STAGES * (PA * kTileM * kRowBytes + PB * BN * kRowBytes) + (2 * STAGES + 4) * 8 + 16 +
+         kEpilogueStageBytes + 1024;
 }
 
 // Host helpers (gemm.cu).

@@ -144,3 +144,30 @@ def test_shape_errors(F):
         F.binary_weight_affine(x, w, torch.zeros_like(w), torch.zeros(4, device="cuda"))
     with pytest.raises(RuntimeError, match="bf16"):
         F.binary_weight_affine(x, w, torch.zeros_like(w), torch.zeros(3, device="cuda"), quantize_zero_to=0.3)
+
+
+@pytest.mark.parametrize("M,K,N", [(2304, 256, 2304), (2500, 200, 2400)])
+def test_large_fixed_point_affine_two_sm_tiles(F, M, K, N):
+    """Large enough for the two-SM (CTA pair) kernel, including ragged edges:
+    exact against integer arithmetic done in float64."""
+    rng = np.random.RandomState(M)
+    xq = oracle.fixed_point_quantize(rng.randn(M, K).astype(np.float32), True, 8, 2.0 ** -5)
+    wq = oracle.fixed_point_quantize((0.02 * rng.randn(K, N)).astype(np.float32), True, 8, 2.0 ** -10)
+    b = (0.01 * rng.randn(N)).astype(np.float32)
+    y = F.affine(dev(xq), dev(wq), dev(b), fixed_point=(2.0 ** -5, 2.0 ** -10))
+    F.check_device_status()
+    exact = (xq.astype(np.float64) @ wq.astype(np.float64)).astype(np.float32) + b  # the product is exact in fp32
+    assert np.array_equal(bits(y.cpu().numpy()), bits(exact))
+
+
+def test_large_binary_weight_affine_two_sm_tiles(F):
+    rng = np.random.RandomState(5)
+    M, K, N = 2304, 192, 2400
+    x = rng.randn(M, K).astype(np.float32)
+    w = (0.02 * rng.randn(K, N)).astype(np.float32)
+    b = rng.randn(N).astype(np.float32)
+    y, wb, al = run_bwa(F, x, w, b, 1, 1.0)
+    sgn = np.where(w > 0, 1.0, np.where(w < 0, -1.0, 1.0))
+    assert np.array_equal(wb, sgn.astype(np.float32))
+    want = (x.astype(np.float64) @ sgn) * np.abs(w.astype(np.float64)).mean(0) + b
+    assert cases.rel_rms(y, want) < TOL
