@@ -224,8 +224,8 @@ int nb200_binary_connect_convolution_f32(const float *x, const float *w, float *
 /* ---- companions: the other functions of a binary-weight ResNet-18 graph ---- */
 /* Needed so the whole graph runs under one context with no CPU fallback
  * (nnabla's NNP loader also probes a context with ReLU before using it,
- * python/src/nnabla/utils/load.py:95-103). All bit-identical to the
- * reference's CPU code for non-NaN input. */
+ * python/src/nnabla/utils/load.py:95-103). Bit-identical to the reference's
+ * CPU code for non-NaN input, except the convolution (fp32 rounding). */
 
 /* BatchNormalization<float>::forward_impl_global
  * (src/nbla/function/generic/batch_normalization.cpp:228-260), batch_stat =
@@ -248,8 +248,9 @@ int nb200_max_pooling_f32(const float *x, float *y, int64_t maps, int height, in
 int nb200_global_average_pooling_f32(const float *x, float *y, int64_t maps, int64_t spatial, void *stream);
 /* Convolution<float>::forward_impl (src/nbla/function/generic/convolution.cpp:160-197)
  * in full precision for layers with few input channels (the network stem):
- * direct convolution, products accumulated in the order of the reference's
- * im2col rows (channel, kernel row, kernel column). group == 1. */
+ * direct convolution, products accumulated with fused multiply-adds in the
+ * order of the reference's im2col rows (channel, kernel row, kernel column).
+ * group == 1. */
 int nb200_convolution_f32(const float *x, const float *w, const float *bias, float *y, int batch, int channels,
                           int height, int width, int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w,
                           int stride_h, int stride_w, int dilation_h, int dilation_w, int group, void *stream);

@@ -2,8 +2,10 @@
 // layers, so that the whole graph runs under one context with no CPU
 // fallback: BatchNormalization (inference), ReLU, Add2, MaxPooling,
 // GlobalAveragePooling and a full-precision Convolution for the network stem.
-// All but the convolution are HBM-bound single passes; arithmetic follows the
-// reference's operation order so results are bit-identical to its CPU code.
+// All but the convolution are HBM-bound single passes whose arithmetic follows
+// the reference's operation order, so their results are bit-identical to its
+// CPU code; the convolution accumulates with fused multiply-adds (tolerance
+// parity, like the other contractions).
 #include "common.cuh"
 
 namespace nb200 {
@@ -135,54 +137,77 @@ __global__ void __launch_bounds__(kThreads) global_average_pooling_kernel(const 
 }
 
 // Full-precision Convolution (src/nbla/function/generic/convolution.cpp:160-197)
-// for the few-channel network stem: direct convolution, one thread per output
-// pixel and OT output maps, weights staged in shared memory, accumulation in
-// the reference's K order (c, ky, kx ascending) with separate multiply and add
-// so the result equals the im2col + natural-order product exactly.
-template <int OT>
+// for the few-channel network stem: direct convolution on the fp32 pipes.
+// Each thread owns PX consecutive output pixels of one output row for OT
+// output maps (OT * PX accumulators in registers); the OT filters are staged
+// in shared memory tap-major so that one 128-bit broadcast load yields four
+// output maps' weights for a tap. Products are accumulated with fused
+// multiply-adds in the order of the reference's im2col rows (channel, kernel
+// row, kernel column), i.e. at least as accurately as its fp32 product.
+template <int OT, int PX>
 __global__ void __launch_bounds__(kThreads) direct_conv_kernel(const float *__restrict__ x, const float *__restrict__ w,
                                                                const float *__restrict__ bias, int C, int H, int W,
                                                                int Ko, int kh, int kw, int ph, int pw, int sh, int sw,
                                                                int dh, int dw, int Ho, int Wo, float *__restrict__ y) {
-  extern __shared__ float s_w[]; // [OT][C*kh*kw]
+  extern __shared__ float4 s_w4[]; // [C*kh*kw][OT/4] float4: weights of OT maps per tap
+  float *s_w = reinterpret_cast<float *>(s_w4);
   const int n = blockIdx.z;
   const int o0 = blockIdx.y * OT;
   const int Kd = C * kh * kw;
   for (int i = threadIdx.x; i < OT * Kd; i += kThreads) {
-    const int o = o0 + i / Kd;
-    s_w[i] = (o < Ko) ? w[(size_t)o * Kd + (i % Kd)] : 0.0f;
+    const int t = i / Kd, k = i - t * Kd; // read filter-major (coalesced), store tap-major
+    s_w[k * OT + t] = (o0 + t < Ko) ? w[(size_t)(o0 + t) * Kd + k] : 0.0f;
   }
   __syncthreads();
-  const int p = blockIdx.x * kThreads + threadIdx.x;
-  if (p >= Ho * Wo)
+  const int groups_x = (Wo + PX - 1) / PX;
+  const int g = blockIdx.x * kThreads + threadIdx.x;
+  if (g >= Ho * groups_x)
     return;
-  const int oy = p / Wo, ox = p - oy * Wo;
-  float acc[OT];
+  const int oy = g / groups_x, ox0 = (g - oy * groups_x) * PX;
+  float acc[OT][PX];
 #pragma unroll
   for (int t = 0; t < OT; ++t)
-    acc[t] = 0.0f;
+#pragma unroll
+    for (int p = 0; p < PX; ++p)
+      acc[t][p] = 0.0f;
   const float *xn = x + (size_t)n * C * H * W;
   int k = 0;
   for (int c = 0; c < C; ++c)
     for (int ky = 0; ky < kh; ++ky) {
       const int iy = oy * sh - ph + ky * dh;
+      const bool row_in = iy >= 0 && iy < H;
+      const float *xrow = xn + ((size_t)c * H + (row_in ? iy : 0)) * W;
       for (int kx = 0; kx < kw; ++kx, ++k) {
-        const int ix = ox * sw - pw + kx * dw;
-        const float v = (iy >= 0 && iy < H && ix >= 0 && ix < W) ? __ldg(xn + ((size_t)c * H + iy) * W + ix) : 0.0f;
+        float v[PX];
 #pragma unroll
-        for (int t = 0; t < OT; ++t)
-          acc[t] = __fadd_rn(acc[t], __fmul_rn(s_w[t * Kd + k], v));
+        for (int p = 0; p < PX; ++p) {
+          const int ix = (ox0 + p) * sw - pw + kx * dw;
+          v[p] = (row_in && ix >= 0 && ix < W) ? __ldg(xrow + ix) : 0.0f;
+        }
+#pragma unroll
+        for (int q = 0; q < OT / 4; ++q) {
+          const float4 wv = s_w4[k * (OT / 4) + q];
+#pragma unroll
+          for (int p = 0; p < PX; ++p) {
+            acc[4 * q + 0][p] = fmaf(wv.x, v[p], acc[4 * q + 0][p]);
+            acc[4 * q + 1][p] = fmaf(wv.y, v[p], acc[4 * q + 1][p]);
+            acc[4 * q + 2][p] = fmaf(wv.z, v[p], acc[4 * q + 2][p]);
+            acc[4 * q + 3][p] = fmaf(wv.w, v[p], acc[4 * q + 3][p]);
+          }
+        }
       }
     }
 #pragma unroll
   for (int t = 0; t < OT; ++t) {
     const int o = o0 + t;
-    if (o < Ko) {
-      float v = acc[t];
-      if (bias)
-        v = __fadd_rn(v, bias[o]);
-      y[(((size_t)n * Ko + o) * Ho + oy) * Wo + ox] = v;
-    }
+    if (o >= Ko)
+      continue;
+    const float b = bias ? bias[o] : 0.0f;
+    float *yo = y + (((size_t)n * Ko + o) * Ho + oy) * Wo + ox0;
+#pragma unroll
+    for (int p = 0; p < PX; ++p)
+      if (ox0 + p < Wo)
+        yo[p] = bias ? __fadd_rn(acc[t][p], b) : acc[t][p];
   }
 }
 
@@ -283,14 +308,15 @@ int nb200_convolution_f32(const float *x, const float *w, const float *bias, flo
   NB_CHECK(eh >= 0 && ew >= 0, NB200_EVALUE, "Invalid configuration of convolution.");
   const int Ho = eh / stride_h + 1, Wo = ew / stride_w + 1;
   NB_CHECK(x && w && y, NB200_EVALUE, "null data pointer");
-  constexpr int OT = 16;
+  constexpr int OT = 16, PX = 4;
   const size_t smem = (size_t)OT * channels * kernel_h * kernel_w * sizeof(float);
   NB_CHECK(smem <= 48 * 1024, NB200_ENOTIMPL,
            "the direct full-precision convolution is meant for few input channels (C*kh*kw = %d is too large)",
            channels * kernel_h * kernel_w);
   NB_CHECK(batch <= 65535 && (outmaps + OT - 1) / OT <= 65535, NB200_ENOTIMPL, "grid extent exceeds 65535");
-  const dim3 grid((Ho * Wo + kThreads - 1) / kThreads, (outmaps + OT - 1) / OT, batch);
-  direct_conv_kernel<OT><<<grid, kThreads, smem, as_stream(stream)>>>(x, w, bias, channels, height, width, outmaps,
+  const int groups = Ho * ((Wo + PX - 1) / PX);
+  const dim3 grid((groups + kThreads - 1) / kThreads, (outmaps + OT - 1) / OT, batch);
+  direct_conv_kernel<OT, PX><<<grid, kThreads, smem, as_stream(stream)>>>(x, w, bias, channels, height, width, outmaps,
                                                                       kernel_h, kernel_w, pad_h, pad_w, stride_h,
                                                                       stride_w, dilation_h, dilation_w, Ho, Wo, y);
   NB_LAUNCH_CHECK();

