@@ -211,6 +211,83 @@ __global__ void __launch_bounds__(kThreads) direct_conv_kernel(const float *__re
   }
 }
 
+// The same convolution specialised at compile time for a KW-wide filter with
+// horizontal stride SW and no dilation (the ResNet stem: 7 x 7, stride 2): the
+// (PX - 1) * SW + KW input values a thread needs from one input row are loaded
+// once into registers and reused by every filter column, so the inner loop is
+// almost purely fused multiply-adds.
+template <int OT, int PX, int KW, int SW>
+__global__ void __launch_bounds__(kThreads) direct_conv_window_kernel(const float *__restrict__ x,
+                                                                      const float *__restrict__ w,
+                                                                      const float *__restrict__ bias, int C, int H,
+                                                                      int W, int Ko, int kh, int ph, int pw, int sh,
+                                                                      int dh, int Ho, int Wo, float *__restrict__ y) {
+  constexpr int WIN = (PX - 1) * SW + KW;
+  extern __shared__ float4 s_w4[]; // [C*kh*KW][OT/4]
+  float *s_w = reinterpret_cast<float *>(s_w4);
+  const int n = blockIdx.z;
+  const int o0 = blockIdx.y * OT;
+  const int Kd = C * kh * KW;
+  for (int i = threadIdx.x; i < OT * Kd; i += kThreads) {
+    const int t = i / Kd, k = i - t * Kd;
+    s_w[k * OT + t] = (o0 + t < Ko) ? w[(size_t)(o0 + t) * Kd + k] : 0.0f;
+  }
+  __syncthreads();
+  const int groups_x = (Wo + PX - 1) / PX;
+  const int g = blockIdx.x * kThreads + threadIdx.x;
+  if (g >= Ho * groups_x)
+    return;
+  const int oy = g / groups_x, ox0 = (g - oy * groups_x) * PX;
+  const int ix0 = ox0 * SW - pw;
+  float acc[OT][PX];
+#pragma unroll
+  for (int t = 0; t < OT; ++t)
+#pragma unroll
+    for (int p = 0; p < PX; ++p)
+      acc[t][p] = 0.0f;
+  const float *xn = x + (size_t)n * C * H * W;
+  int k = 0;
+  for (int c = 0; c < C; ++c)
+    for (int ky = 0; ky < kh; ++ky, k += KW) {
+      const int iy = oy * sh - ph + ky * dh;
+      const bool row_in = iy >= 0 && iy < H;
+      const float *xrow = xn + ((size_t)c * H + (row_in ? iy : 0)) * W;
+      float v[WIN];
+#pragma unroll
+      for (int i = 0; i < WIN; ++i) {
+        const int ix = ix0 + i;
+        v[i] = (row_in && ix >= 0 && ix < W) ? __ldg(xrow + ix) : 0.0f;
+      }
+#pragma unroll
+      for (int kx = 0; kx < KW; ++kx) {
+#pragma unroll
+        for (int q = 0; q < OT / 4; ++q) {
+          const float4 wv = s_w4[(k + kx) * (OT / 4) + q];
+#pragma unroll
+          for (int p = 0; p < PX; ++p) {
+            const float xv = v[p * SW + kx];
+            acc[4 * q + 0][p] = fmaf(wv.x, xv, acc[4 * q + 0][p]);
+            acc[4 * q + 1][p] = fmaf(wv.y, xv, acc[4 * q + 1][p]);
+            acc[4 * q + 2][p] = fmaf(wv.z, xv, acc[4 * q + 2][p]);
+            acc[4 * q + 3][p] = fmaf(wv.w, xv, acc[4 * q + 3][p]);
+          }
+        }
+      }
+    }
+#pragma unroll
+  for (int t = 0; t < OT; ++t) {
+    const int o = o0 + t;
+    if (o >= Ko)
+      continue;
+    const float b = bias ? bias[o] : 0.0f;
+    float *yo = y + (((size_t)n * Ko + o) * Ho + oy) * Wo + ox0;
+#pragma unroll
+    for (int p = 0; p < PX; ++p)
+      if (ox0 + p < Wo)
+        yo[p] = bias ? __fadd_rn(acc[t][p], b) : acc[t][p];
+  }
+}
+
 } // namespace
 } // namespace nb200
 
@@ -316,6 +393,12 @@ int nb200_convolution_f32(const float *x, const float *w, const float *bias, flo
   NB_CHECK(batch <= 65535 && (outmaps + OT - 1) / OT <= 65535, NB200_ENOTIMPL, "grid extent exceeds 65535");
   const int groups = Ho * ((Wo + PX - 1) / PX);
   const dim3 grid((groups + kThreads - 1) / kThreads, (outmaps + OT - 1) / OT, batch);
+  if (kernel_w == 7 && stride_w == 2 && dilation_w == 1) {
+    direct_conv_window_kernel<OT, PX, 7, 2><<<grid, kThreads, smem, as_stream(stream)>>>(
+        x, w, bias, channels, height, width, outmaps, kernel_h, pad_h, pad_w, stride_h, dilation_h, Ho, Wo, y);
+    NB_LAUNCH_CHECK();
+    return NB200_OK;
+  }
   direct_conv_kernel<OT, PX><<<grid, kThreads, smem, as_stream(stream)>>>(x, w, bias, channels, height, width, outmaps,
                                                                       kernel_h, kernel_w, pad_h, pad_w, stride_h,
                                                                       stride_w, dilation_h, dilation_w, Ho, Wo, y);

@@ -77,22 +77,23 @@ void plan_box(const ConvGeometry &g, int bn_max, int &h_box, int &n_box) {
   h_box = best;
 }
 
-template <bool kInt8, int PA, int PB, int BN, int STAGES>
+template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes>
 int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ctot, const void *wside, int64_t wpitch,
                 int c_pad_g, int cblocks, int h_box, int n_box, const GemmEpilogue &ep, cudaStream_t st) {
   const int es = kInt8 ? 1 : 2;
-  const int E = kRowBytes / es;
+  const int E = RB / es;
   CUtensorMap ma, mb;
   // weights: (K, Ko, 1)
-  NB_TRY(make_operand_map(&ma, wside, kInt8, wpitch, wpitch, g.Ko, 1, kTileM));
+  NB_TRY(make_operand_map(&ma, wside, kInt8, wpitch, wpitch, g.Ko, 1, kTileM, RB));
   // activations: (C, W, H, N, planes); the box walks W and H with the convolution stride
   const uint64_t dims[5] = {(uint64_t)ctot, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N, (uint64_t)planes_b};
   const uint64_t strides[4] = {(uint64_t)ctot * es, (uint64_t)ctot * es * g.W, (uint64_t)ctot * es * g.W * g.H,
                                (uint64_t)ctot * es * g.W * g.H * g.N};
   const uint32_t box[5] = {(uint32_t)E, (uint32_t)(g.Wo * g.sw), (uint32_t)(h_box * g.sh), (uint32_t)n_box, 1};
   const uint32_t estr[5] = {1, (uint32_t)g.sw, (uint32_t)g.sh, 1, 1};
-  NB_TRY(encode_tiled(&mb, kInt8 ? 1 : 0, 5, act, dims, strides, box, estr));
+  NB_TRY(encode_tiled(&mb, kInt8 ? 1 : 0, 5, act, dims, strides, box, estr, RB));
   ConvProblem p;
+  p.row_bytes = RB;
   p.Nimg = g.N;
   p.Ko = g.Ko;
   p.Kog = g.Kog;
@@ -117,7 +118,7 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
   p.pixels = n_box * h_box * g.Wo;
   p.n_run = (int)round_up(p.pixels, 16);
   const int tiles = p.groups * p.m_tiles_g * p.tiles_h * p.tiles_n;
-  return launch_contraction<kInt8, PA, PB, BN, STAGES, false, ConvProblem>(ma, mb, p, tiles, ep, st);
+  return launch_contraction<kInt8, PA, PB, BN, STAGES, false, ConvProblem, RB>(ma, mb, p, tiles, ep, st);
 }
 
 // Shared body of BinaryWeightConvolution / BinaryConnectConvolution forward.
@@ -135,8 +136,11 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   NB_CHECK(g.Wo * g.sw <= 256 && g.Wo <= 256, NB200_ENOTIMPL,
            "output rows wider than 256 pixels (Wo=%d, stride %d) are not supported", g.Wo, g.sw);
   const int es = int8 ? 1 : 2;
-  const int E = kRowBytes / es;
   const int c_pad_g = (int)round_up(g.Cg, 16);
+  // One K block is one filter tap over E channel slots. With few channels per
+  // group a 128-byte row would be half zero padding: use 64-byte rows then.
+  const bool narrow_rows = c_pad_g * es <= 64;
+  const int E = (narrow_rows ? 64 : kRowBytes) / es;
   const int cblocks = (c_pad_g + E - 1) / E;
   const int c_slots = cblocks * E;
   int64_t ctot = (int64_t)g.group * c_pad_g;
@@ -172,12 +176,20 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   const bool can128 = px128 <= 128;
   const bool use256 = !can128 || (int8 && fill256 > fill128 + 0.05);
   if (int8) {
+    if (narrow_rows) {
+      if (use256)
+        return launch_conv<true, 1, 1, 256, 8, 64>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h256, n256, ep,
+                                                   st);
+      return launch_conv<true, 1, 1, 128, 10, 64>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
+    }
     if (use256)
       return launch_conv<true, 1, 1, 256, 4>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h256, n256, ep, st);
     return launch_conv<true, 1, 1, 128, 6>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
   }
   NB_CHECK(can128, NB200_ENOTIMPL,
            "fp32-activation convolution with output rows wider than 128 pixels (Wo=%d) is not supported", g.Wo);
+  if (narrow_rows)
+    return launch_conv<false, 1, 3, 128, 6, 64>(g, act, 3, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
   return launch_conv<false, 1, 3, 128, 3>(g, act, 3, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
 }
 

@@ -34,7 +34,8 @@ static int get_encode_fn(EncodeTiledFn *out) {
 
 // dtype_code: 0 = bf16, 1 = uint8/int8 bytes, 2 = float32
 int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, const uint64_t *dims,
-                 const uint64_t *strides_bytes, const uint32_t *box, const uint32_t *elem_strides) {
+                 const uint64_t *strides_bytes, const uint32_t *box, const uint32_t *elem_strides,
+                 int swizzle_bytes) {
   EncodeTiledFn fn;
   NB_TRY(get_encode_fn(&fn));
   NB_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, NB200_EVALUE, "tensor-map base must be 16-byte aligned");
@@ -55,19 +56,20 @@ int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, c
                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   const CUresult r = fn(map, dt,
                         (cuuint32_t)rank, const_cast<void *>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   NB_CHECK(r == CUDA_SUCCESS, NB200_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return NB200_OK;
 }
 
 int make_operand_map(CUtensorMap *map, const void *base, bool int8, int64_t k_extent, int64_t pitch_elems,
-                     int64_t rows, int planes, int box_rows) {
+                     int64_t rows, int planes, int box_rows, int row_bytes) {
   const uint64_t es = int8 ? 1 : 2;
   const uint64_t dims[3] = {(uint64_t)k_extent, (uint64_t)rows, (uint64_t)planes};
   const uint64_t strides[2] = {(uint64_t)pitch_elems * es, (uint64_t)pitch_elems * es * (uint64_t)rows};
-  const uint32_t box[3] = {(uint32_t)(kRowBytes / es), (uint32_t)box_rows, 1};
-  return encode_tiled(map, int8 ? 1 : 0, 3, base, dims, strides, box, nullptr);
+  const uint32_t box[3] = {(uint32_t)(row_bytes / es), (uint32_t)box_rows, 1};
+  return encode_tiled(map, int8 ? 1 : 0, 3, base, dims, strides, box, nullptr, row_bytes);
 }
 
 // ---- per-device status word written by kernels whose bounded waits gave up --
@@ -97,6 +99,7 @@ static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, int M, int 
   prob.m_tiles = (M + kTileM - 1) / kTileM;
   prob.n_tiles = (N + BN - 1) / BN;
   prob.bn = BN;
+  prob.row_bytes = kRowBytes;
   prob.ldy = ldy;
   return launch_contraction<kInt8, PA, PB, BN, STAGES, kSkip, GemmProblem>(ma, mb, prob, prob.m_tiles * prob.n_tiles,
                                                                            ep, st);

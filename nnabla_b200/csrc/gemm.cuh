@@ -57,11 +57,12 @@ struct Tile {
 // ---- plain GEMM: A [planes][M][K], B [planes][N][K] --------------------------
 struct GemmProblem {
   int M, N, kblocks, m_tiles, n_tiles, bn;
+  int row_bytes; // bytes of one K block per operand row (128 or 64)
   int64_t ldy;
   __device__ __forceinline__ int num_tiles() const { return m_tiles * n_tiles; }
   __device__ __forceinline__ int k_blocks() const { return kblocks; }
   __device__ __forceinline__ uint32_t umma_n() const { return (uint32_t)bn; }
-  __device__ __forceinline__ uint32_t b_tx_bytes() const { return (uint32_t)bn * kRowBytes; }
+  __device__ __forceinline__ uint32_t b_tx_bytes() const { return (uint32_t)(bn * row_bytes); }
   __device__ __forceinline__ void decode(int tile, Tile &t) const {
     t.m0 = (tile % m_tiles) * kTileM;
     t.m_end = M;
@@ -100,12 +101,13 @@ struct ConvProblem {
   int kw, taps, cblocks;
   int sh, sw, ph, pw, dh, dw;
   int c_group_stride; // channel offset between groups in the activation planes
+  int row_bytes;      // bytes of one K block per operand row (128, or 64 for few channels)
   int n_run;          // UMMA N: pixels per box rounded up to 16
   int pixels;         // n_box * h_box * Wo
   __device__ __forceinline__ int num_tiles() const { return groups * m_tiles_g * tiles_h * tiles_n; }
   __device__ __forceinline__ int k_blocks() const { return taps * cblocks; }
   __device__ __forceinline__ uint32_t umma_n() const { return (uint32_t)n_run; }
-  __device__ __forceinline__ uint32_t b_tx_bytes() const { return (uint32_t)pixels * kRowBytes; }
+  __device__ __forceinline__ uint32_t b_tx_bytes() const { return (uint32_t)(pixels * row_bytes); }
   __device__ __forceinline__ void decode(int tile, Tile &t) const {
     const int mt = tile % m_tiles_g;
     int r = tile / m_tiles_g;
@@ -142,15 +144,16 @@ struct ConvProblem {
   }
 };
 
-template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkipSmallPairs, typename Problem>
+template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkipSmallPairs, typename Problem, int RB = kRowBytes>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const Problem prob, const GemmEpilogue ep, int *status) {
-  constexpr int kElemsPerBlock = kInt8 ? 128 : 64; // K elements per 128-byte row
-  constexpr int kUmmaK = kInt8 ? 32 : 16;          // K elements per MMA (32 bytes)
+  static_assert(RB == 128 || RB == 64, "operand rows are one 128-byte or 64-byte swizzle span");
+  constexpr int kElemsPerBlock = kInt8 ? RB : RB / 2; // K elements per operand row of one K block
+  constexpr int kUmmaK = kInt8 ? 32 : 16;             // K elements per MMA (32 bytes)
   constexpr int kMmasPerBlock = kElemsPerBlock / kUmmaK;
-  constexpr uint32_t kABytes = kTileM * kRowBytes;
-  constexpr uint32_t kBBytes = BN * kRowBytes;
+  constexpr uint32_t kABytes = kTileM * RB;
+  constexpr uint32_t kBBytes = BN * RB;
   constexpr uint32_t kStageBytes = PA * kABytes + PB * kBBytes;
   constexpr uint32_t kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
@@ -266,8 +269,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               // resolution of the leading term (pa + pb > 2) are skipped.
               if (kSkipSmallPairs && pa + pb > 2)
                 continue;
-              const uint64_t adesc = ptx::smem_desc_k_sw128(st + pa * kABytes);
-              const uint64_t bdesc = ptx::smem_desc_k_sw128(st + PA * kABytes + pb * kBBytes);
+              const uint64_t adesc = ptx::smem_desc_k(st + pa * kABytes, RB);
+              const uint64_t bdesc = ptx::smem_desc_k(st + PA * kABytes + pb * kBBytes, RB);
 #pragma unroll
               for (int k = 0; k < kMmasPerBlock; ++k) {
                 // advancing 32 bytes along K inside the swizzle atom = +2 in the encoded address
@@ -377,8 +380,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 }
 
-template <bool kInt8, int PA, int PB, int BN, int STAGES> constexpr size_t gemm_smem_bytes() {
-  return (size_t)STAGES * (PA * kTileM * kRowBytes + PB * BN * kRowBytes) + (2 * STAGES + 4) * 8 + 16 +
+template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes> constexpr size_t gemm_smem_bytes() {
+  return (size_t)STAGES * (PA * kTileM * RB + PB * BN * RB) + (2 * STAGES + 4) * 8 + 16 +
          kEpilogueStageBytes + 1024;
 }
 
@@ -388,9 +391,10 @@ template <bool kInt8, int PA, int PB, int BN, int STAGES> constexpr size_t gemm_
 // box_rows, 1) box and the 128-byte swizzle. Reads past k_extent or rows are
 // zero-filled by the copy engine.
 int make_operand_map(CUtensorMap *map, const void *base, bool int8, int64_t k_extent, int64_t pitch_elems,
-                     int64_t rows, int planes, int box_rows);
+                     int64_t rows, int planes, int box_rows, int row_bytes = kRowBytes);
 int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, const uint64_t *dims,
-                 const uint64_t *strides_bytes, const uint32_t *box, const uint32_t *elem_strides);
+                 const uint64_t *strides_bytes, const uint32_t *box, const uint32_t *elem_strides,
+                 int swizzle_bytes = 128);
 int device_status_word(int **status);
 int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch_a, const void *B, int64_t pitch_b,
              int M, int N, int K, const GemmEpilogue &ep, int64_t ldy, cudaStream_t st);
@@ -398,11 +402,11 @@ int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch
 
 // Launches the contraction kernel for one problem: one persistent CTA per SM
 // (or per tile when there are fewer tiles than SMs).
-template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkip, typename Problem>
+template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkip, typename Problem, int RB = kRowBytes>
 inline int launch_contraction(const CUtensorMap &ma, const CUtensorMap &mb, const Problem &prob, int tiles,
                        const GemmEpilogue &ep, cudaStream_t st) {
-  auto kernel = gemm_tcgen05_kernel<kInt8, PA, PB, BN, STAGES, kSkip, Problem>;
-  constexpr size_t smem = gemm_smem_bytes<kInt8, PA, PB, BN, STAGES>();
+  auto kernel = gemm_tcgen05_kernel<kInt8, PA, PB, BN, STAGES, kSkip, Problem, RB>;
+  constexpr size_t smem = gemm_smem_bytes<kInt8, PA, PB, BN, STAGES, RB>();
   static_assert(smem <= 227 * 1024, "shared memory budget");
   static bool configured[64];
   int dev = 0;

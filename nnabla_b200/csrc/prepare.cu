@@ -224,6 +224,44 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_i8_kernel(const float *__res
   }
 }
 
+// Same conversion with 128-bit loads (HW a multiple of 4): every thread has
+// four independent float4 loads in flight (4 pixels x 4 channel rows).
+__global__ void __launch_bounds__(256) nchw_to_nhwc_i8_vec_kernel(const float *__restrict__ x, int C, int HW,
+                                                                  int groups, int Cg, int c_pad_g, int ctot,
+                                                                  int8_t *__restrict__ out, float inv_delta) {
+  __shared__ uint32_t tile[64][17];
+  int8_t *tile8 = reinterpret_cast<int8_t *>(&tile[0][0]);
+  const int n = blockIdx.z;
+  const int p0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  const int px4 = threadIdx.x & 15, ch = threadIdx.x >> 4; // 16 pixel quads x 16 channel rows
+  const int p = p0 + 4 * px4;
+  float4 v[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int d = d0 + ch + 16 * r;
+    const int g = d / c_pad_g, cc = d - g * c_pad_g;
+    v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (d < ctot && g < groups && cc < Cg && p < HW)
+      v[r] = __ldcs(reinterpret_cast<const float4 *>(x + ((int64_t)n * C + (g * Cg + cc)) * HW + p));
+  }
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int dd = ch + 16 * r;
+    tile8[(4 * px4 + 0) * 68 + dd] = (int8_t)__float2int_rn(__fmul_rn(v[r].x, inv_delta));
+    tile8[(4 * px4 + 1) * 68 + dd] = (int8_t)__float2int_rn(__fmul_rn(v[r].y, inv_delta));
+    tile8[(4 * px4 + 2) * 68 + dd] = (int8_t)__float2int_rn(__fmul_rn(v[r].z, inv_delta));
+    tile8[(4 * px4 + 3) * 68 + dd] = (int8_t)__float2int_rn(__fmul_rn(v[r].w, inv_delta));
+  }
+  __syncthreads();
+  const int word = threadIdx.x & 15, prow = threadIdx.x >> 4;
+#pragma unroll
+  for (int pp = prow; pp < 64; pp += 16) {
+    const int pix = p0 + pp, d = d0 + 4 * word;
+    if (pix < HW && d < ctot)
+      *reinterpret_cast<uint32_t *>(out + ((int64_t)n * HW + pix) * ctot + d) = tile[pp][word];
+  }
+}
+
 // int8 [R, C] -> [C][pitch] (transpose), tile 64 x 64 through shared memory.
 __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t *__restrict__ src, int R, int C,
                                                            int8_t *__restrict__ dst, int64_t pitch) {
@@ -324,8 +362,12 @@ int nchw_to_nhwc_planes(const float *x, int N, int C, int HW, int groups, int Cg
   if (planes == 0) {
     // ctot is a multiple of 16 (channel slots are padded to 16 per group), so word stores are aligned.
     const dim3 grid8((HW + 63) / 64, (ctot + 63) / 64, N);
-    nchw_to_nhwc_i8_kernel<<<grid8, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
-                                                  reinterpret_cast<int8_t *>(out), 1.0f / delta);
+    if (HW % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
+      nchw_to_nhwc_i8_vec_kernel<<<grid8, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
+                                                        reinterpret_cast<int8_t *>(out), 1.0f / delta);
+    else
+      nchw_to_nhwc_i8_kernel<<<grid8, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
+                                                    reinterpret_cast<int8_t *>(out), 1.0f / delta);
   } else if (planes == 3) {
     nchw_to_nhwc_kernel<__nv_bfloat16, 3><<<grid, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
                                                                 reinterpret_cast<__nv_bfloat16 *>(out), ps, 0.f);

@@ -144,17 +144,19 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 // ---- descriptors ------------------------------------------------------------
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of
-// 128 bytes under the 128-byte swizzle (the layout a TMA load with
-// CU_TENSOR_MAP_SWIZZLE_128B produces): 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) {
+// row_bytes (128 or 64) under the swizzle of the same width (the layout a TMA
+// load with CU_TENSOR_MAP_SWIZZLE_128B / _64B produces): groups of 8 rows are
+// 8 * row_bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k(uint32_t smem_addr, uint32_t row_bytes) {
   uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);       // start address, bits [0,14)
-  d |= (uint64_t)0 << 16;                             // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024u >> 4) << 32;                  // stride byte offset, bits [32,46)
-  d |= (uint64_t)1 << 46;                             // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;                             // layout type: SWIZZLE_128B
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);          // start address, bits [0,14)
+  d |= (uint64_t)0 << 16;                                // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)((8u * row_bytes) >> 4) << 32;          // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                                // descriptor version for sm_100
+  d |= (uint64_t)(row_bytes == 128u ? 2u : 4u) << 61;    // layout type: SWIZZLE_128B = 2, SWIZZLE_64B = 4
   return d;
 }
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) { return smem_desc_k(smem_addr, 128u); }
 
 // Instruction descriptor: dense, D format (1 = f32, 2 = s32), A/B formats,
 // both operands K-major, N at bits [17,23) as N/8, M at bits [24,29) as M/16.

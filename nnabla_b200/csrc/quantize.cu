@@ -289,14 +289,40 @@ Pow2Device g_pow2_dev[64];
 Pow2Tables g_pow2_host;
 int g_pow2_host_state = 0; // 0 = not built, 1 = ok, -1 = unusable
 char g_pow2_why[160];
+// Facts about the tables that allow a lookup-free common case: every pw[k] is
+// exactly 2^k (so it can be assembled from the exponent), and for normal
+// binades every cut lies within g_pow2_margin of kCutCentre.
+constexpr uint32_t kCutCentre = 0x3504f3u; // mantissa field of sqrt(2)
+bool g_pow2_exact_powers = false;
+uint32_t g_pow2_margin = 0;
+
+void analyse_pow2_tables(const Pow2Tables &T) {
+  g_pow2_exact_powers = true;
+  for (int k = kMinExp; k <= 128; ++k) {
+    const float want = (k == 128) ? INFINITY : ldexpf(1.0f, k);
+    if (T.pw[k - kMinExp] != want)
+      g_pow2_exact_powers = false;
+  }
+  uint32_t margin = 0;
+  for (int e = -126; e <= 127; ++e) {
+    const uint32_t c = T.cut[e - kMinExp];
+    const uint32_t d = c > kCutCentre ? c - kCutCentre : kCutCentre - c;
+    if (d > margin)
+      margin = d;
+  }
+  g_pow2_margin = margin + 1;
+}
 
 int pow2_tables_for_current_device(const Pow2Tables **out) {
   int dev = 0;
   NB_CUDA(cudaGetDevice(&dev));
   NB_CHECK(dev >= 0 && dev < 64, NB200_EVALUE, "device index %d out of range", dev);
   std::lock_guard<std::mutex> lock(g_pow2_mutex);
-  if (g_pow2_host_state == 0)
+  if (g_pow2_host_state == 0) {
     g_pow2_host_state = build_pow2_tables(&g_pow2_host, g_pow2_why, sizeof(g_pow2_why)) ? 1 : -1;
+    if (g_pow2_host_state == 1)
+      analyse_pow2_tables(g_pow2_host);
+  }
   NB_CHECK(g_pow2_host_state == 1, NB200_ENOTIMPL, "Pow2Quantize: cannot reproduce the host libm (%s)", g_pow2_why);
   Pow2Device &d = g_pow2_dev[dev];
   if (!d.ready) {
@@ -405,6 +431,62 @@ __global__ void __launch_bounds__(kThreads) pow2_kernel(const float *__restrict_
   }
 }
 
+// Lookup-free common case (used when the host libm's powers of two are exact
+// and its cuts sit close to sqrt(2), which analyse_pow2_tables verified): the
+// snapped exponent of a normal number is decided by comparing its mantissa
+// with kCutCentre -/+ margin, the power of two is assembled from the exponent
+// bits, and only mantissas inside the +-margin window (a few in 10^5) or
+// denormal inputs read the per-binade table from global memory.
+struct Pow2FastOp {
+  static constexpr bool kHasCodes = false;
+  Pow2Params P;
+  uint32_t margin;
+  const Pow2Tables *tables;
+  bool codes_aligned(size_t) const { return true; }
+  __device__ __forceinline__ void store_code(size_t, float) const {}
+  __device__ __forceinline__ void store_codes4(size_t, float, float, float, float) const {}
+  __device__ __forceinline__ float operator()(float x, size_t, float &) const {
+    const float a = fabsf(x);
+    const uint32_t bits = __float_as_uint(a);
+    const uint32_t E = bits >> 23;
+    float q;
+    if (E - 1u < 254u) { // normal number
+      const uint32_t frac = bits & 0x7fffffu;
+      int k = (int)E - 127;
+      if (frac >= kCutCentre + margin) {
+        k += 1;
+      } else if (frac + margin > kCutCentre) {
+        k += (frac > __ldg(&tables->cut[k - kMinExp])) ? 1 : 0;
+      }
+      // 2^k for k in [-126, 128]; k = 128 assembles +inf like powf(2, 128); k = -126 - 1 cannot occur here
+      q = __uint_as_float((uint32_t)(k + 127) << 23);
+    } else if (bits == 0u) {
+      q = 0.0f;
+    } else if (E == 255u) {
+      q = a;
+    } else { // denormal input
+      const int p = 31 - __clz(bits);
+      const int e = p - 149;
+      const uint32_t frac = (bits << (23 - p)) & 0x7fffffu;
+      const int k = e + ((frac > __ldg(&tables->cut[e - kMinExp])) ? 1 : 0);
+      q = __ldg(&tables->pw[k - kMinExp]);
+    }
+    if (q > P.p_max) {
+      q = P.p_max;
+    } else if (q < P.p_min) {
+      q = P.with_zero ? (a < P.prune ? 0.0f : P.p_min) : P.p_min;
+    }
+    const bool neg = x < 0.0f;
+    if (P.sign)
+      q = neg ? -q : q;
+    else if (P.with_zero)
+      q = neg ? 0.0f : q;
+    else
+      q = neg ? P.p_min : q;
+    return q;
+  }
+};
+
 int pow2_params(int sign, int with_zero, int n, int m, Pow2Params *P) {
   // The reference's setup (pow2_quantize.cpp:31-44).
   NB_CHECK(n > 0, NB200_EVALUE, "bit width should be positive.");
@@ -430,6 +512,10 @@ int pow2_launch(const float *x, float *y, size_t size, int sign, int with_zero, 
            "fp32 pointers must be 4-byte aligned");
   const Pow2Tables *tables = nullptr;
   NB_TRY(pow2_tables_for_current_device(&tables));
+  if (g_pow2_exact_powers && g_pow2_margin < 4096u) {
+    Pow2FastOp op{P, g_pow2_margin, tables};
+    return launch_elementwise(x, y, size, op, st);
+  }
   const size_t phase_x = (reinterpret_cast<uintptr_t>(x) & 15) / 4;
   const size_t phase_y = (reinterpret_cast<uintptr_t>(y) & 15) / 4;
   if (phase_x != phase_y) {
