@@ -6,6 +6,7 @@
 // CPU loops; each kernel names the loop it replaces.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -28,13 +29,14 @@ constexpr int kUnroll = 4;
 // Applies op to one float4 group starting at flat element e and stores it;
 // ops with an int8 side-band store their four codes as one 32-bit word.
 template <typename Op>
-__device__ __forceinline__ void apply4(const Op &op, const float4 v, const size_t e, float4 *dst) {
+__device__ __forceinline__ void apply4(const Op &op, const typename Op::State &st, const float4 v, const size_t e,
+                                       float4 *dst) {
   float4 r;
   float k0, k1, k2, k3;
-  r.x = op(v.x, e, k0);
-  r.y = op(v.y, e + 1, k1);
-  r.z = op(v.z, e + 2, k2);
-  r.w = op(v.w, e + 3, k3);
+  r.x = op(v.x, e, k0, st);
+  r.y = op(v.y, e + 1, k1, st);
+  r.z = op(v.z, e + 2, k2, st);
+  r.w = op(v.w, e + 3, k3, st);
   st_stream(dst, r);
   if (Op::kHasCodes)
     op.store_codes4(e, k0, k1, k2, k3);
@@ -47,6 +49,7 @@ __global__ void __launch_bounds__(kThreads) ew_vec_kernel(const float *__restric
   float4 *y4 = reinterpret_cast<float4 *>(y + head);
   const size_t stride = (size_t)gridDim.x * kThreads;
   size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  const typename Op::State st = op.init(); // per-thread constants, loaded once
   for (; i + (kUnroll - 1) * stride < n4; i += kUnroll * stride) {
     float4 v[kUnroll];
 #pragma unroll
@@ -54,17 +57,17 @@ __global__ void __launch_bounds__(kThreads) ew_vec_kernel(const float *__restric
       v[u] = ld_stream(x4 + i + u * stride);
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u)
-      apply4(op, v[u], head + 4 * (i + u * stride), y4 + i + u * stride);
+      apply4(op, st, v[u], head + 4 * (i + u * stride), y4 + i + u * stride);
   }
   for (; i < n4; i += stride)
-    apply4(op, ld_stream(x4 + i), head + 4 * i, y4 + i);
+    apply4(op, st, ld_stream(x4 + i), head + 4 * i, y4 + i);
   if (blockIdx.x == 0) {
     const size_t tail_begin = head + 4 * n4;
     const size_t n_edge = head + (size - tail_begin);
     for (size_t t = threadIdx.x; t < n_edge; t += kThreads) {
       const size_t e = (t < head) ? t : tail_begin + (t - head);
       float k;
-      y[e] = op(x[e], e, k);
+      y[e] = op(x[e], e, k, st);
       if (Op::kHasCodes)
         op.store_code(e, k);
     }
@@ -76,9 +79,10 @@ template <typename Op>
 __global__ void __launch_bounds__(kThreads) ew_scalar_kernel(const float *__restrict__ x, float *__restrict__ y,
                                                              size_t size, Op op) {
   const size_t stride = (size_t)gridDim.x * kThreads;
+  const typename Op::State st = op.init();
   for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < size; i += stride) {
     float k;
-    y[i] = op(x[i], i, k);
+    y[i] = op(x[i], i, k, st);
     if (Op::kHasCodes)
       op.store_code(i, k);
   }
@@ -86,7 +90,13 @@ __global__ void __launch_bounds__(kThreads) ew_scalar_kernel(const float *__rest
 
 inline unsigned grid_for(size_t work_items) {
   size_t blocks = (work_items + kThreads - 1) / kThreads;
-  const size_t cap = (size_t)sm_count() * kBlocksPerSm;
+  // NNABLA_B200_EW_BLOCKS_PER_SM overrides the grid size per SM (tuning aid).
+  static const int per_sm = []() {
+    const char *e = std::getenv("NNABLA_B200_EW_BLOCKS_PER_SM");
+    const int v = e ? std::atoi(e) : 0;
+    return v > 0 ? v : kBlocksPerSm;
+  }();
+  const size_t cap = (size_t)sm_count() * per_sm;
   if (blocks > cap)
     blocks = cap;
   if (blocks == 0)
@@ -137,7 +147,9 @@ template <bool kPow2Delta, bool kCodes> struct FxpOp {
                        (((uint32_t)(int)k2 & 0xffu) << 16) | (((uint32_t)(int)k3 & 0xffu) << 24);
     *reinterpret_cast<uint32_t *>(codes + e) = w;
   }
-  __device__ __forceinline__ float operator()(float x, size_t, float &k) const {
+  struct State {};
+  __device__ __forceinline__ State init() const { return State(); }
+  __device__ __forceinline__ float operator()(float x, size_t, float &k, const State &) const {
     float r;
     if (x > maxv) {
       r = maxv;
@@ -445,7 +457,9 @@ struct Pow2FastOp {
   bool codes_aligned(size_t) const { return true; }
   __device__ __forceinline__ void store_code(size_t, float) const {}
   __device__ __forceinline__ void store_codes4(size_t, float, float, float, float) const {}
-  __device__ __forceinline__ float operator()(float x, size_t, float &) const {
+  struct State {};
+  __device__ __forceinline__ State init() const { return State(); }
+  __device__ __forceinline__ float operator()(float x, size_t, float &, const State &) const {
     const float a = fabsf(x);
     const uint32_t bits = __float_as_uint(a);
     const uint32_t E = bits >> 23;
@@ -665,14 +679,25 @@ struct MinMaxOp {
   bool codes_aligned(size_t) const { return true; }
   __device__ __forceinline__ void store_code(size_t, float) const {}
   __device__ __forceinline__ void store_codes4(size_t, float, float, float, float) const {}
-  __device__ __forceinline__ float operator()(float x, size_t i, float &) const {
-    size_t q = 0;
-    if (Q > 1) {
-      if ((i | inner | Q) >> 32) {
-        q = (i / inner) % Q;
-      } else {
-        q = ((uint32_t)i / (uint32_t)inner) % (uint32_t)Q;
-      }
+  // Per-tensor ranges (Q == 1): the three parameters are read once per thread.
+  struct State {
+    float m, M, s;
+  };
+  __device__ __forceinline__ State init() const {
+    State st;
+    st.m = __ldg(m);
+    st.M = __ldg(M);
+    st.s = __ldg(s);
+    return st;
+  }
+  __device__ __forceinline__ float operator()(float x, size_t i, float &, const State &st) const {
+    if (Q == 1)
+      return minmax_apply_one(x, st.m, st.M, st.s);
+    size_t q;
+    if ((i | inner | Q) >> 32) {
+      q = (i / inner) % Q;
+    } else {
+      q = ((uint32_t)i / (uint32_t)inner) % (uint32_t)Q;
     }
     return minmax_apply_one(x, __ldg(m + q), __ldg(M + q), __ldg(s + q));
   }
