@@ -15,7 +15,7 @@ constexpr int kThreads = 256;
 
 inline unsigned grid_for(size_t items, int per_thread = 1) {
   size_t b = (items + (size_t)kThreads * per_thread - 1) / ((size_t)kThreads * per_thread);
-  const size_t cap = (size_t)sm_count() * 8;
+  const size_t cap = (size_t)sm_count() * 64;
   if (b > cap)
     b = cap;
   return (unsigned)(b < 1 ? 1 : b);

@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(256) codes_rows_kernel(const float *__restrict
 
 inline unsigned capped_grid(int64_t items, int threads) {
   int64_t b = (items + threads - 1) / threads;
-  const int64_t cap = (int64_t)sm_count() * 8;
+  const int64_t cap = (int64_t)sm_count() * 64;
   if (b > cap)
     b = cap;
   return (unsigned)(b < 1 ? 1 : b);

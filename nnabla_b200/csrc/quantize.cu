@@ -16,7 +16,7 @@ namespace nb200 {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kBlocksPerSm = 8;
+constexpr int kBlocksPerSm = 128; // measured: 8 -> 87 %, 32 -> 94 %, 128 -> 99 % of the copy bandwidth at 2^30 elements
 constexpr int kUnroll = 4;
 
 // ---------------------------------------------------------------------------
