@@ -13,7 +13,7 @@
 // One CTA per SM, static round-robin over output tiles. Warp 0 feeds a
 // multi-stage shared-memory ring with TMA tiled loads (128-byte swizzle),
 // warp 1 issues tcgen05.mma from one elected thread and owns the TMEM
-// allocation, warps 2-5 drain the double-buffered TMEM accumulator with
+// allocation, eight epilogue warps drain the double-buffered TMEM accumulator with
 // tcgen05.ld and write y. Every mbarrier wait is time-bounded; a wait that
 // gives up stores a code in *status, raises the CTA's abort flag and all
 // roles fall through to the common teardown (TMEM is always freed).
@@ -23,15 +23,18 @@
 // implicit-GEMM convolution (ConvProblem: boxes of an NHWC activation tensor
 // shifted by the filter tap).
 #pragma once
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
 namespace nb200 {
 
-constexpr int kGemmThreads = 192; // 6 warps: TMA, MMA, 4 x epilogue
+constexpr int kEpilogueWarps = 8;                          // two warps per TMEM lane quarter, alternating column chunks
+constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps); // warps: TMA, MMA, epilogue
 constexpr int kTileM = 128;
 constexpr int kRowBytes = 128; // one swizzle-atom row: 64 bf16 or 128 int8 along K
-constexpr int kEpilogueStageBytes = 4 * 32 * 33 * 4; // per-warp transpose buffers of the epilogue
+constexpr int kEpilogueStageBytes = kEpilogueWarps * 32 * 33 * 4; // per-warp transpose buffers of the epilogue
 
 // Status codes written by a wait that gave up (low byte = role).
 constexpr int kStatusProducerTimeout = 0x101;
@@ -39,6 +42,7 @@ constexpr int kStatusMmaTimeout = 0x102;
 constexpr int kStatusEpilogueTimeout = 0x103;
 
 struct GemmEpilogue {
+  int debug; // timing experiments only (NNABLA_B200_GEMM_DEBUG): 1 = epilogue reads TMEM but neither computes nor stores, 2 = no operand loads after the first ring fill
   float *y;
   const float *row_scale, *col_scale, *row_bias, *col_bias;
   float scale;
@@ -168,7 +172,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t *tmem_empty = bars + 2 * STAGES + 2;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  float *stage_out = reinterpret_cast<float *>(tmem_slot + 4); // 4 epilogue warps x 32 x 33 floats
+  float *stage_out = reinterpret_cast<float *>(tmem_slot + 4); // one 32 x 33 float buffer per epilogue warp
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -182,7 +186,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(tmem_full + b, 1);
-      ptx::mbar_init(tmem_empty + b, 4);
+      ptx::mbar_init(tmem_empty + b, kEpilogueWarps);
     }
     *abort_flag = 0;
     ptx::mbar_fence_init();
@@ -217,13 +221,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           uint8_t *st = smem + stage * kStageBytes;
-          ptx::mbar_expect_tx(full_bar + stage, tx_bytes);
+          if ((ep.debug & 2) && (tile != (int)blockIdx.x || kb >= STAGES)) {
+            ptx::mbar_arrive(full_bar + stage);
+          } else {
+            ptx::mbar_expect_tx(full_bar + stage, tx_bytes);
 #pragma unroll
-          for (int pa = 0; pa < PA; ++pa)
-            prob.load_a(&map_a, st + pa * kABytes, full_bar + stage, kb, t, pa, kElemsPerBlock);
+            for (int pa = 0; pa < PA; ++pa)
+              prob.load_a(&map_a, st + pa * kABytes, full_bar + stage, kb, t, pa, kElemsPerBlock);
 #pragma unroll
-          for (int pb = 0; pb < PB; ++pb)
-            prob.load_b(&map_b, st + PA * kABytes + pb * kBBytes, full_bar + stage, kb, t, pb, kElemsPerBlock);
+            for (int pb = 0; pb < PB; ++pb)
+              prob.load_b(&map_b, st + PA * kABytes + pb * kBBytes, full_bar + stage, kb, t, pb, kElemsPerBlock);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -295,6 +303,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3; // TMEM lanes [32*quarter, 32*quarter + 32) are visible to this warp
+    const int half = (warp - 2) >> 2; // the two warps of a quarter take even / odd 32-column chunks
     const int n_cols = (int)prob.umma_n();
     int local = 0;
     bool ok = true;
@@ -321,38 +330,65 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // contiguous run of y (lane = column).
       float *stg = stage_out + (warp - 2) * (32 * 33);
       const int row_base = t.m0 + quarter * 32;
+      // Row-wise factors are applied by the row's owner before the transpose,
+      // column-wise ones by the column's owner after it: no loads in the loops.
+      const int my_row = row_base + lane;
+      const bool my_row_ok = my_row < t.m_end;
+      const float rs = (ep.row_scale && my_row_ok) ? __fmul_rn(ep.row_scale[my_row], ep.scale) : ep.scale;
+      const float rb = (ep.row_bias && my_row_ok) ? ep.row_bias[my_row] : 0.0f;
+      int rows_here = t.m_end - row_base;
+      rows_here = rows_here < 0 ? 0 : (rows_here > 32 ? 32 : rows_here);
+      const int64_t row_stride = prob.row_offset(1);
 #pragma unroll 1
-      for (int c0 = 0; c0 < n_cols; c0 += 32) {
+      for (int c0 = 32 * half; c0 < n_cols; c0 += 32 * (kEpilogueWarps / 4)) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
         ptx::tmem_ld_wait();
+        if ((ep.debug & 1) || rows_here == 0)
+          continue;
+        if (ep.col_scale) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          stg[lane * 33 + j] = kInt8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+          for (int j = 0; j < 32; ++j)
+            stg[lane * 33 + j] = kInt8 ? (float)(int)r[j] : __uint_as_float(r[j]);
+        } else {
+          // y = acc * (scale * row_scale) (+ row_bias): one rounding per operation, like the reference's
+          // product followed by its bias addition
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = __fmul_rn(kInt8 ? (float)(int)r[j] : __uint_as_float(r[j]), rs);
+            if (ep.row_bias)
+              v = __fadd_rn(v, rb);
+            stg[lane * 33 + j] = v;
+          }
+        }
         __syncwarp();
         int64_t coff;
         int gcol;
         const bool col_ok = prob.col_offset(t, c0 + lane, coff, gcol);
-        const float cs = (ep.col_scale && col_ok) ? ep.col_scale[gcol] : 1.0f;
         const float cb = (ep.col_bias && col_ok) ? ep.col_bias[gcol] : 0.0f;
-        float *ycol = ep.y + coff;
+        float *yp = ep.y + coff + prob.row_offset(row_base);
+        if (ep.col_scale) {
+          const float cs = col_ok ? ep.col_scale[gcol] : 1.0f;
 #pragma unroll 4
-        for (int i = 0; i < 32; ++i) {
-          const int row = row_base + i;
-          if (row >= t.m_end)
-            break;
-          float s = ep.scale;
-          if (ep.row_scale)
-            s = __fmul_rn(ep.row_scale[row], s);
-          if (ep.col_scale)
-            s = __fmul_rn(s, cs);
-          float v = __fmul_rn(stg[i * 33 + lane], s);
-          if (ep.row_bias)
-            v = __fadd_rn(v, ep.row_bias[row]);
-          if (ep.col_bias)
-            v = __fadd_rn(v, cb);
-          if (col_ok)
-            ycol[prob.row_offset(row)] = v;
+          for (int i = 0; i < rows_here; ++i, yp += row_stride) {
+            const float rsi = __shfl_sync(0xffffffffu, rs, i), rbi = __shfl_sync(0xffffffffu, rb, i);
+            float v = __fmul_rn(stg[i * 33 + lane], __fmul_rn(rsi, cs));
+            if (ep.row_bias)
+              v = __fadd_rn(v, rbi);
+            if (ep.col_bias)
+              v = __fadd_rn(v, cb);
+            if (col_ok)
+              *yp = v;
+          }
+        } else {
+#pragma unroll 8
+          for (int i = 0; i < rows_here; ++i, yp += row_stride) {
+            float v = stg[i * 33 + lane];
+            if (ep.col_bias)
+              v = __fadd_rn(v, cb);
+            if (col_ok)
+              *yp = v;
+          }
         }
         __syncwarp();
       }
@@ -418,7 +454,15 @@ inline int launch_contraction(const CUtensorMap &ma, const CUtensorMap &mb, cons
   int *status = nullptr;
   NB_TRY(device_status_word(&status));
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kernel<<<grid, kGemmThreads, smem, st>>>(ma, mb, prob, ep, status);
+  GemmEpilogue epd = ep;
+  {
+    static const int dbg = []() {
+      const char *e = std::getenv("NNABLA_B200_GEMM_DEBUG");
+      return e ? std::atoi(e) : 0;
+    }();
+    epd.debug = dbg;
+  }
+  kernel<<<grid, kGemmThreads, smem, st>>>(ma, mb, prob, epd, status);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }

@@ -116,6 +116,7 @@ __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy
 
 } // namespace ptx
 
+constexpr int kPairThreads = 192; // 6 warps per CTA: TMA, MMA, 4 x epilogue
 constexpr int kPairTileM = 256; // rows of D per CTA pair
 constexpr int kPairTileN = 256; // columns of D per CTA pair
 constexpr int kPairEpilogueBytes = 4 * 2 * 4096; // 4 epilogue warps x 2 swizzled 32 x 32 fp32 boxes
@@ -127,7 +128,7 @@ struct PairGemmProblem {
 };
 
 template <bool kInt8, int PA, int STAGES>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                              const __grid_constant__ CUtensorMap map_y, const PairGemmProblem prob,
                              const GemmEpilogue ep, int *status) {
@@ -418,7 +419,7 @@ inline int launch_pair_gemm(const CUtensorMap &ma, const CUtensorMap &mb, int M,
   int pairs = sm_count() / 2;
   if (pairs > tiles)
     pairs = tiles;
-  kernel<<<2 * pairs, kGemmThreads, smem, st>>>(ma, mb, my, prob, ep, status);
+  kernel<<<2 * pairs, kPairThreads, smem, st>>>(ma, mb, my, prob, ep, status);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }
