@@ -15,7 +15,7 @@
 //                the peer's (two plain commits, one per CTA) when the MMAs that
 //                read stage s have finished.
 //   tmem_full[b] one per CTA, committed the same way after the last K block.
-//   tmem_empty[b] lives in the leader, count 8: the four epilogue warps of both
+//   tmem_empty[b] lives in the leader, count 16: the eight epilogue warps of both
 //                CTAs arrive (the peer's remotely) when they have drained buffer b.
 // The two CTAs synchronise as a cluster after barrier initialisation and
 // before exit, so neither touches the other's shared memory outside that span.
@@ -116,10 +116,11 @@ __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy
 
 } // namespace ptx
 
-constexpr int kPairThreads = 192; // 6 warps per CTA: TMA, MMA, 4 x epilogue
+constexpr int kPairEpilogueWarps = 8;                        // two per TMEM lane quarter, alternating column chunks
+constexpr int kPairThreads = 32 * (2 + kPairEpilogueWarps); // warps per CTA: TMA, MMA, epilogue
 constexpr int kPairTileM = 256; // rows of D per CTA pair
 constexpr int kPairTileN = 256; // columns of D per CTA pair
-constexpr int kPairEpilogueBytes = 4 * 2 * 4096; // 4 epilogue warps x 2 swizzled 32 x 32 fp32 boxes
+constexpr int kPairEpilogueBytes = kPairEpilogueWarps * 4096; // one swizzled 32 x 32 fp32 box per epilogue warp
 
 struct PairGemmProblem {
   int M, N, kblocks, m_tiles, n_tiles;
@@ -166,7 +167,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(tmem_full + b, 1);
-      ptx::mbar_init(tmem_empty + b, 8);
+      ptx::mbar_init(tmem_empty + b, 2 * kPairEpilogueWarps);
     }
     *abort_flag = 0;
     ptx::mbar_fence_init();
@@ -282,6 +283,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs)
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     int local = 0;
     bool ok = true;
     const uint64_t stream_out = ptx::l2_policy_evict_first();
@@ -304,26 +306,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       // Each thread owns one accumulator row. A chunk of 32 columns is scaled,
       // written to a swizzled 32 x 32 box in shared memory with 128-bit stores
       // and handed to the copy engine, which writes full lines of y and clips
-      // at the matrix edges; two boxes per warp keep a store in flight while
-      // the next chunk is prepared.
+      // at the matrix edges. Column factors are fetched one per lane and
+      // broadcast by shuffles, so the inner loop has no memory loads.
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < prob.M;
       const float rs = (ep.row_scale && row_ok) ? __fmul_rn(ep.row_scale[row], ep.scale) : ep.scale;
       const float rb = (ep.row_bias && row_ok) ? ep.row_bias[row] : 0.0f;
-      uint8_t *my_stage = stage_out + (warp - 2) * 8192;
+      uint8_t *box = stage_out + (warp - 2) * 4096;
       const uint32_t sw = (uint32_t)(lane & 7);
 #pragma unroll 1
-      for (int c0 = 0; c0 < kPairTileN; c0 += 32) {
+      for (int c0 = 32 * half; c0 < kPairTileN; c0 += 32 * (kPairEpilogueWarps / 4)) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kPairTileN + c0), r);
         ptx::tmem_ld_wait();
         const int col0 = n0 + c0;
         if (col0 >= prob.N || (prob.debug & 1))
           continue;
-        uint8_t *box = my_stage + ((c0 >> 5) & 1) * 4096;
-        // the store issued two chunks ago from this box must have finished reading it
+        const bool lane_col_ok = col0 + lane < prob.N;
+        const float cs_l = (ep.col_scale && lane_col_ok) ? ep.col_scale[col0 + lane] : 1.0f;
+        const float cb_l = (ep.col_bias && lane_col_ok) ? ep.col_bias[col0 + lane] : 0.0f;
+        // the previous store from this box must have finished reading it
         if (lane == 0)
-          ptx::tma_store_wait_read<1>();
+          ptx::tma_store_wait_read<0>();
         __syncwarp();
         float4 *rowp = reinterpret_cast<float4 *>(box + lane * 128);
 #pragma unroll
@@ -333,13 +337,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           for (int u = 0; u < 4; ++u) {
             const int j = 4 * q + u;
             const float acc = kInt8 ? (float)(int)r[j] : __uint_as_float(r[j]);
-            const int col = col0 + j;
-            const float s = (ep.col_scale && col < prob.N) ? __fmul_rn(rs, ep.col_scale[col]) : rs;
+            float s = rs;
+            if (ep.col_scale)
+              s = __fmul_rn(rs, __shfl_sync(0xffffffffu, cs_l, j));
             float v = __fmul_rn(acc, s);
             if (ep.row_bias)
               v = __fadd_rn(v, rb);
-            if (ep.col_bias && col < prob.N)
-              v = __fadd_rn(v, ep.col_bias[col]);
+            if (ep.col_bias)
+              v = __fadd_rn(v, __shfl_sync(0xffffffffu, cb_l, j));
             o[u] = v;
           }
           rowp[q ^ sw] = make_float4(o[0], o[1], o[2], o[3]);
