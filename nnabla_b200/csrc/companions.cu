@@ -394,8 +394,18 @@ int nb200_convolution_f32(const float *x, const float *w, const float *bias, flo
   const int groups = Ho * ((Wo + PX - 1) / PX);
   const dim3 grid((groups + kThreads - 1) / kThreads, (outmaps + OT - 1) / OT, batch);
   if (kernel_w == 7 && stride_w == 2 && dilation_w == 1) {
-    direct_conv_window_kernel<OT, PX, 7, 2><<<grid, kThreads, smem, as_stream(stream)>>>(
-        x, w, bias, channels, height, width, outmaps, kernel_h, pad_h, pad_w, stride_h, dilation_h, Ho, Wo, y);
+    // Seven pixels per thread when the output width allows it: fewer shared-memory
+    // weight reads per multiply-add (the limiter with four), no idle lanes at Wo = 112.
+    if (Wo % 7 == 0) {
+      constexpr int PX7 = 7;
+      const int groups7 = Ho * (Wo / PX7);
+      const dim3 grid7((groups7 + kThreads - 1) / kThreads, (outmaps + OT - 1) / OT, batch);
+      direct_conv_window_kernel<OT, PX7, 7, 2><<<grid7, kThreads, smem, as_stream(stream)>>>(
+          x, w, bias, channels, height, width, outmaps, kernel_h, pad_h, pad_w, stride_h, dilation_h, Ho, Wo, y);
+    } else {
+      direct_conv_window_kernel<OT, PX, 7, 2><<<grid, kThreads, smem, as_stream(stream)>>>(
+          x, w, bias, channels, height, width, outmaps, kernel_h, pad_h, pad_w, stride_h, dilation_h, Ho, Wo, y);
+    }
     NB_LAUNCH_CHECK();
     return NB200_OK;
   }
