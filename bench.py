@@ -404,8 +404,8 @@ def run_b200_arm(args):
     achieved = BYTES_PER_ELEM * n / (per_kernel_ms[k_dom] / 1e3) / 1e9
     # DRAM traffic per element of the dominant kernel from the committed ncu capture at 2^26 elements
     # (profiles/quantizers_2p26_full_capture.md), scaled to this launch: traffic grows with the element count.
-    ncu_bytes_per_elem = {"fixed_point_quantize": 489.4e6 / 2 ** 26, "pow2_quantize": 488.3e6 / 2 ** 26,
-                          "min_max_quantize": 488.2e6 / 2 ** 26}
+    ncu_bytes_per_elem = {"fixed_point_quantize": 485.1e6 / 2 ** 26, "pow2_quantize": 485.4e6 / 2 ** 26,
+                          "min_max_quantize": 486.9e6 / 2 ** 26}
     roofline = {"bound": "hbm", "kernel": QUANTIZERS[k_dom], "achieved": achieved, "peak": peaks["hbm_gbs"],
                 "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "traffic": ncu_bytes_per_elem[QUANTIZERS[k_dom]] * n, "traffic_unit": "bytes per launch",
