@@ -254,6 +254,17 @@ def run_extras(args, rank, world, barrier):
             return sharding.gather_columns(yy, N)
         entry["ms_gemm_plus_allgather"] = maxr(time_gpu(gemm_and_gather, 10))
         entry["collective"] = "NCCL all-gather of the [8192, N/g] fp32 output slabs + interleave"
+        # the same with the gather fused into the contraction: every rank's epilogue stores its slab into all
+        # ranks' [M, N] results over NVLink (peer mappings), then one tiny all-reduce orders the ranks
+        mats = sharding.PeerMatrices(M, N)
+
+        def gemm_fused_gather():
+            F.affine_from_codes_gather(xc, wc, 2.0 ** -5, 2.0 ** -10, b, mats.ptrs, rank, N, rank * Ns)
+            mats.fence()
+        entry["ms_gemm_fused_gather"] = maxr(time_gpu(gemm_fused_gather, 10))
+        entry["fused_gather_equals_allgather"] = bool(torch.equal(mats.local, gemm_and_gather()))
+        entry["fused_gather_GBps_out_per_gpu"] = (world - 1) * M * Ns * 4 / entry["ms_gemm_fused_gather"] / 1e6
+        mats.close()
     out["configs[2] fixed-point int8 affine %dx%dx%d" % (M, K, N)] = entry
     del x, w, xq, wq, xc, wc
     # configs[3]: BinaryWeightConvolution 3x3, 256 -> 256, 28 x 28, batch 128 sharded over the ranks

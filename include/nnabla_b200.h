@@ -73,6 +73,18 @@ int nb200_memcpy_d2d(void *dev_dst, const void *dev_src, size_t bytes, void *str
  * dtype (byte-wise), fill for fp32 arrays. */
 int nb200_memset_zero(void *dev_ptr, size_t bytes, void *stream);
 int nb200_fill_f32(float *dev_ptr, size_t n, float value, void *stream);
+/* Sharing one GPU's array with the other ranks of the box (one process per
+ * GPU). The reference moves data between devices only through
+ * Communicator::all_gather and friends (include/nbla/communicator.hpp:232-241);
+ * here a rank exports an array it allocated with nb200_malloc as a 64-byte
+ * handle, the other ranks map it with nb200_ipc_open, and the *_gather_f32
+ * contractions below store their results straight into those mappings.
+ * `handle` points at NB200_IPC_HANDLE_BYTES bytes; a mapping is released with
+ * nb200_ipc_close before the owner frees the array. */
+#define NB200_IPC_HANDLE_BYTES 64
+int nb200_ipc_export(const void *dev_ptr, void *handle);
+int nb200_ipc_open(const void *handle, void **peer_ptr);
+int nb200_ipc_close(void *peer_ptr);
 int nb200_stream_create(void **stream);
 int nb200_stream_destroy(void *stream);
 /* BackendBase::device_synchronize (include/nbla/backend_base.hpp:32-91). */
@@ -183,6 +195,24 @@ int nb200_affine_fxp8_f32(const float *xq, const float *wq, float delta_x, float
  * w_codes [w_row, w_col]). */
 int nb200_affine_codes_i8_f32(const int8_t *x_codes, const int8_t *w_codes, float delta_x, float delta_w,
                               const float *bias, float *y, int64_t rows, int64_t w_row, int64_t w_col, void *stream);
+/* Output-column shards of the two contractions above, with the gather of the
+ * shards fused into the kernel: this rank owns columns [col_begin, col_begin +
+ * w_col) of a [w_row, w_col_total] weight (wq / w_codes and bias are its slab)
+ * and stores its [rows, w_col] result into the row-major [rows, w_col_total]
+ * matrix of EVERY rank: y_ranks[rank] is this GPU's own, the other entries are
+ * mappings of the peers' matrices (nb200_ipc_open). When all ranks' calls have
+ * completed, every rank holds the full product; no rank waits on another
+ * inside the kernel, so the caller orders the ranks afterwards (a barrier).
+ * Replaces Affine::forward_impl (affine.cpp:80-96) on a column shard followed
+ * by Communicator::all_gather (include/nbla/communicator.hpp:232-241).
+ * n_ranks <= 8; n_ranks == 1 is the unsharded call. */
+int nb200_affine_fxp8_gather_f32(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias,
+                                 float *const *y_ranks, int n_ranks, int rank, int64_t rows, int64_t w_row,
+                                 int64_t w_col, int64_t w_col_total, int64_t col_begin, void *stream);
+int nb200_affine_codes_i8_gather_f32(const int8_t *x_codes, const int8_t *w_codes, float delta_x, float delta_w,
+                                     const float *bias, float *const *y_ranks, int n_ranks, int rank, int64_t rows,
+                                     int64_t w_row, int64_t w_col, int64_t w_col_total, int64_t col_begin,
+                                     void *stream);
 /* Affine<float>::forward_impl (affine.cpp:80-96) for arbitrary fp32 operands:
  * both are split into bf16 pieces and the six leading piece products are
  * accumulated in fp32 (error of the order of fp32 rounding). */

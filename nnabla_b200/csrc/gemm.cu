@@ -125,7 +125,8 @@ int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch
   const int64_t pair_tiles = (int64_t)((M + kPairTileM - 1) / kPairTileM) * ((N + kPairTileN - 1) / kPairTileN);
   // (the bulk stores of its epilogue need a 16-byte aligned y with a row pitch that is a multiple of 16 bytes)
   const bool y_tma_ok = (reinterpret_cast<uintptr_t>(ep.y) & 15) == 0 && (ldy % 4) == 0;
-  if (pair_enabled && y_tma_ok && planes_b == 1 && pair_tiles >= sm_count() / 2) {
+  // (peer copies of y are written with plain stores, which only the single-CTA kernel's epilogue has)
+  if (pair_enabled && y_tma_ok && ep.n_peers == 0 && planes_b == 1 && pair_tiles >= sm_count() / 2) {
     NB_TRY(make_operand_map(&mb, B, int8, K, pitch_b, N, 1, kPairTileN / 2));
     if (int8)
       return launch_pair_gemm<true, 1, 6>(ma, mb, M, N, k_blocks, ep, ldy, st);
@@ -198,6 +199,83 @@ static int binary_affine(const float *x, const float *w, float *wb, float *alpha
   return run_gemm(false, 3, 1, planes, Kp, side, Kp, (int)M, (int)N, (int)K, ep, N, st);
 }
 
+// Fills the epilogue's destinations for a column slab [col_begin, col_begin + n)
+// of row-major [rows, n_total] matrices, one per rank: y_ranks[rank] is this
+// GPU's own matrix, the others are peer mappings, taken in ring order starting
+// after this rank so that the ranks do not all write to the same peer first.
+static int slab_destinations(GemmEpilogue &ep, float *const *y_ranks, int n_ranks, int rank, int64_t n,
+                             int64_t n_total, int64_t col_begin) {
+  NB_CHECK(y_ranks != nullptr, NB200_EVALUE, "y_ranks is NULL");
+  NB_CHECK(n_ranks >= 1 && n_ranks <= kMaxPeers + 1, NB200_EVALUE, "n_ranks = %d outside [1, %d]", n_ranks,
+           kMaxPeers + 1);
+  NB_CHECK(rank >= 0 && rank < n_ranks, NB200_EVALUE, "rank %d outside [0, %d)", rank, n_ranks);
+  NB_CHECK(col_begin >= 0 && n_total < (1ll << 31) && col_begin + n <= n_total, NB200_EVALUE,
+           "column slab [%lld, %lld) outside [0, %lld)", (long long)col_begin, (long long)(col_begin + n),
+           (long long)n_total);
+  for (int r = 0; r < n_ranks; ++r)
+    NB_CHECK(y_ranks[r] != nullptr, NB200_EVALUE, "y_ranks[%d] is NULL", r);
+  ep.y = y_ranks[rank] + col_begin;
+  ep.n_peers = n_ranks - 1;
+  for (int j = 1; j < n_ranks; ++j)
+    ep.peer_y[j - 1] = y_ranks[(rank + j) % n_ranks] + col_begin;
+  return NB200_OK;
+}
+
+static int affine_codes(const int8_t *x_codes, const int8_t *w_codes, float delta_x, float delta_w, const float *bias,
+                        float *const *y_ranks, int n_ranks, int rank, int64_t rows, int64_t w_row, int64_t w_col,
+                        int64_t n_total, int64_t col_begin, cudaStream_t st) {
+  const int64_t M = rows, K = w_row, N = w_col;
+  NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand");
+  NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
+  NB_CHECK(x_codes && w_codes, NB200_EVALUE, "null data pointer");
+  // |acc| <= K * 127 * 127 must fit int32
+  NB_CHECK(K <= 133000, NB200_ENOTIMPL, "K = %lld could overflow the int32 accumulator", (long long)K);
+  GemmEpilogue ep{};
+  NB_TRY(slab_destinations(ep, y_ranks, n_ranks, rank, N, n_total, col_begin));
+  const int64_t Kp = round_up(K, 128);
+  const bool x_direct = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(x_codes) & 15) == 0);
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc((size_t)N * Kp + (x_direct ? 0 : (size_t)M * Kp)));
+  int8_t *wt = static_cast<int8_t *>(scratch.p);
+  NB_TRY(transpose_i8(w_codes, (int)K, (int)N, wt, Kp, st));
+  const int8_t *xa = x_codes;
+  int64_t pitch_a = K;
+  if (!x_direct) {
+    int8_t *xc = wt + (size_t)N * Kp;
+    NB_CUDA(cudaMemcpy2DAsync(xc, (size_t)Kp, x_codes, (size_t)K, (size_t)K, (size_t)M, cudaMemcpyDeviceToDevice, st));
+    xa = xc;
+    pitch_a = Kp;
+  }
+  ep.scale = delta_x * delta_w;
+  ep.col_bias = bias;
+  return run_gemm(true, 1, 1, xa, pitch_a, wt, Kp, (int)M, (int)N, (int)K, ep, n_total, st);
+}
+
+static int affine_fxp8(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias,
+                       float *const *y_ranks, int n_ranks, int rank, int64_t rows, int64_t w_row, int64_t w_col,
+                       int64_t n_total, int64_t col_begin, cudaStream_t st) {
+  const int64_t M = rows, K = w_row, N = w_col;
+  NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand");
+  NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
+  NB_CHECK(xq && wq, NB200_EVALUE, "null data pointer");
+  NB_CHECK(delta_x > 0.f && delta_w > 0.f, NB200_EVALUE, "step sizes must be positive");
+  NB_CHECK(K <= 133000, NB200_ENOTIMPL, "K = %lld could overflow the int32 accumulator", (long long)K);
+  GemmEpilogue ep{};
+  NB_TRY(slab_destinations(ep, y_ranks, n_ranks, rank, N, n_total, col_begin));
+  const int64_t Kp = round_up(K, 128);
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc((size_t)(M + N) * Kp + (size_t)K * N));
+  int8_t *xc = static_cast<int8_t *>(scratch.p);
+  int8_t *wt = xc + (size_t)M * Kp;
+  int8_t *wc = wt + (size_t)N * Kp;
+  NB_TRY(codes_rows_i8(xq, M, (int)K, Kp, delta_x, xc, st));
+  NB_TRY(codes_rows_i8(wq, K, (int)N, N, delta_w, wc, st));
+  NB_TRY(transpose_i8(wc, (int)K, (int)N, wt, Kp, st));
+  ep.scale = delta_x * delta_w;
+  ep.col_bias = bias;
+  return run_gemm(true, 1, 1, xc, Kp, wt, Kp, (int)M, (int)N, (int)K, ep, n_total, st);
+}
+
 } // namespace nb200
 
 using namespace nb200;
@@ -231,57 +309,32 @@ int nb200_binary_connect_affine_f32(const float *x, const float *w, float *wb, c
 int nb200_affine_codes_i8_f32(const int8_t *x_codes, const int8_t *w_codes, float delta_x, float delta_w,
                               const float *bias, float *y, int64_t rows, int64_t w_row, int64_t w_col,
                               void *stream) {
-  const int64_t M = rows, K = w_row, N = w_col;
-  NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand");
-  NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
-  NB_CHECK(x_codes && w_codes && y, NB200_EVALUE, "null data pointer");
-  // |acc| <= K * 127 * 127 must fit int32
-  NB_CHECK(K <= 133000, NB200_ENOTIMPL, "K = %lld could overflow the int32 accumulator", (long long)K);
-  cudaStream_t st = as_stream(stream);
-  const int64_t Kp = round_up(K, 128);
-  const bool x_direct = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(x_codes) & 15) == 0);
-  AsyncScratch scratch(st);
-  NB_TRY(scratch.alloc((size_t)N * Kp + (x_direct ? 0 : (size_t)M * Kp)));
-  int8_t *wt = static_cast<int8_t *>(scratch.p);
-  NB_TRY(transpose_i8(w_codes, (int)K, (int)N, wt, Kp, st));
-  const int8_t *xa = x_codes;
-  int64_t pitch_a = K;
-  if (!x_direct) {
-    int8_t *xc = wt + (size_t)N * Kp;
-    NB_CUDA(cudaMemcpy2DAsync(xc, (size_t)Kp, x_codes, (size_t)K, (size_t)K, (size_t)M, cudaMemcpyDeviceToDevice, st));
-    xa = xc;
-    pitch_a = Kp;
-  }
-  GemmEpilogue ep{};
-  ep.y = y;
-  ep.scale = delta_x * delta_w;
-  ep.col_bias = bias;
-  return run_gemm(true, 1, 1, xa, pitch_a, wt, Kp, (int)M, (int)N, (int)K, ep, N, st);
+  NB_CHECK(y != nullptr, NB200_EVALUE, "null data pointer");
+  float *const ys[1] = {y};
+  return affine_codes(x_codes, w_codes, delta_x, delta_w, bias, ys, 1, 0, rows, w_row, w_col, w_col, 0,
+                      as_stream(stream));
+}
+
+int nb200_affine_codes_i8_gather_f32(const int8_t *x_codes, const int8_t *w_codes, float delta_x, float delta_w,
+                                     const float *bias, float *const *y_ranks, int n_ranks, int rank, int64_t rows,
+                                     int64_t w_row, int64_t w_col, int64_t w_col_total, int64_t col_begin,
+                                     void *stream) {
+  return affine_codes(x_codes, w_codes, delta_x, delta_w, bias, y_ranks, n_ranks, rank, rows, w_row, w_col,
+                      w_col_total, col_begin, as_stream(stream));
 }
 
 int nb200_affine_fxp8_f32(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias, float *y,
                           int64_t rows, int64_t w_row, int64_t w_col, void *stream) {
-  const int64_t M = rows, K = w_row, N = w_col;
-  NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand");
-  NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
-  NB_CHECK(xq && wq && y, NB200_EVALUE, "null data pointer");
-  NB_CHECK(delta_x > 0.f && delta_w > 0.f, NB200_EVALUE, "step sizes must be positive");
-  NB_CHECK(K <= 133000, NB200_ENOTIMPL, "K = %lld could overflow the int32 accumulator", (long long)K);
-  cudaStream_t st = as_stream(stream);
-  const int64_t Kp = round_up(K, 128);
-  AsyncScratch scratch(st);
-  NB_TRY(scratch.alloc((size_t)(M + N) * Kp + (size_t)K * N));
-  int8_t *xc = static_cast<int8_t *>(scratch.p);
-  int8_t *wt = xc + (size_t)M * Kp;
-  int8_t *wc = wt + (size_t)N * Kp;
-  NB_TRY(codes_rows_i8(xq, M, (int)K, Kp, delta_x, xc, st));
-  NB_TRY(codes_rows_i8(wq, K, (int)N, N, delta_w, wc, st));
-  NB_TRY(transpose_i8(wc, (int)K, (int)N, wt, Kp, st));
-  GemmEpilogue ep{};
-  ep.y = y;
-  ep.scale = delta_x * delta_w;
-  ep.col_bias = bias;
-  return run_gemm(true, 1, 1, xc, Kp, wt, Kp, (int)M, (int)N, (int)K, ep, N, st);
+  NB_CHECK(y != nullptr, NB200_EVALUE, "null data pointer");
+  float *const ys[1] = {y};
+  return affine_fxp8(xq, wq, delta_x, delta_w, bias, ys, 1, 0, rows, w_row, w_col, w_col, 0, as_stream(stream));
+}
+
+int nb200_affine_fxp8_gather_f32(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias,
+                                 float *const *y_ranks, int n_ranks, int rank, int64_t rows, int64_t w_row,
+                                 int64_t w_col, int64_t w_col_total, int64_t col_begin, void *stream) {
+  return affine_fxp8(xq, wq, delta_x, delta_w, bias, y_ranks, n_ranks, rank, rows, w_row, w_col, w_col_total,
+                     col_begin, as_stream(stream));
 }
 
 int nb200_affine_f32(const float *x, const float *w, const float *bias, float *y, int64_t rows, int64_t w_row,

@@ -34,6 +34,7 @@ constexpr int kEpilogueWarps = 8;                          // two warps per TMEM
 constexpr int kGemmThreads = 32 * (2 + kEpilogueWarps); // warps: TMA, MMA, epilogue
 constexpr int kTileM = 128;
 constexpr int kRowBytes = 128; // one swizzle-atom row: 64 bf16 or 128 int8 along K
+constexpr int kMaxPeers = 7;   // other ranks of one 8-GPU box
 constexpr int kEpilogueStageBytes = kEpilogueWarps * 32 * 33 * 4; // per-warp transpose buffers of the epilogue
 
 // Status codes written by a wait that gave up (low byte = role).
@@ -46,6 +47,12 @@ struct GemmEpilogue {
   float *y;
   const float *row_scale, *col_scale, *row_bias, *col_bias;
   float scale;
+  // Copies of y in other GPUs' memory (peer mappings), addressed exactly like
+  // y: every output value is also stored there, so that a column-sharded
+  // contraction leaves the gathered result on every rank without a separate
+  // collective. Plain stores only; no rank waits on another inside the kernel.
+  int n_peers;
+  float *peer_y[kMaxPeers];
 };
 
 // Per-tile coordinates produced by a problem policy.
@@ -366,28 +373,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int gcol;
         const bool col_ok = prob.col_offset(t, c0 + lane, coff, gcol);
         const float cb = (ep.col_bias && col_ok) ? ep.col_bias[gcol] : 0.0f;
-        float *yp = ep.y + coff + prob.row_offset(row_base);
-        if (ep.col_scale) {
-          const float cs = col_ok ? ep.col_scale[gcol] : 1.0f;
+        const int64_t tile_off = coff + prob.row_offset(row_base);
+        // destination 0 is this GPU's y, the others are the peer copies
+#pragma unroll 1
+        for (int d = 0; d <= ep.n_peers; ++d) {
+          float *yp = ep.y; // (selected with constant indices: a variable index would copy the parameters to the stack)
+#pragma unroll
+          for (int q = 0; q < kMaxPeers; ++q)
+            if (d == q + 1)
+              yp = ep.peer_y[q];
+          yp += tile_off;
+          if (ep.col_scale) {
+            const float cs = col_ok ? ep.col_scale[gcol] : 1.0f;
 #pragma unroll 4
-          for (int i = 0; i < rows_here; ++i, yp += row_stride) {
-            const float rsi = __shfl_sync(0xffffffffu, rs, i), rbi = __shfl_sync(0xffffffffu, rb, i);
-            float v = __fmul_rn(stg[i * 33 + lane], __fmul_rn(rsi, cs));
-            if (ep.row_bias)
-              v = __fadd_rn(v, rbi);
-            if (ep.col_bias)
-              v = __fadd_rn(v, cb);
-            if (col_ok)
-              *yp = v;
-          }
-        } else {
+            for (int i = 0; i < rows_here; ++i, yp += row_stride) {
+              const float rsi = __shfl_sync(0xffffffffu, rs, i), rbi = __shfl_sync(0xffffffffu, rb, i);
+              float v = __fmul_rn(stg[i * 33 + lane], __fmul_rn(rsi, cs));
+              if (ep.row_bias)
+                v = __fadd_rn(v, rbi);
+              if (ep.col_bias)
+                v = __fadd_rn(v, cb);
+              if (col_ok)
+                *yp = v;
+            }
+          } else {
 #pragma unroll 8
-          for (int i = 0; i < rows_here; ++i, yp += row_stride) {
-            float v = stg[i * 33 + lane];
-            if (ep.col_bias)
-              v = __fadd_rn(v, cb);
-            if (col_ok)
-              *yp = v;
+            for (int i = 0; i < rows_here; ++i, yp += row_stride) {
+              float v = stg[i * 33 + lane];
+              if (ep.col_bias)
+                v = __fadd_rn(v, cb);
+              if (col_ok)
+                *yp = v;
+            }
           }
         }
         __syncwarp();

@@ -4,6 +4,7 @@
 // include/nnabla_b200.h.
 #include <cstdarg>
 #include <cstdio>
+#include <cstring>
 #include <mutex>
 #include <string>
 
@@ -172,6 +173,31 @@ int nb200_malloc(void **dev_ptr, size_t bytes) {
 int nb200_free(void *dev_ptr) {
   if (dev_ptr)
     NB_CUDA(cudaFree(dev_ptr));
+  return NB200_OK;
+}
+
+static_assert(sizeof(cudaIpcMemHandle_t) == NB200_IPC_HANDLE_BYTES, "handle size of the C ABI");
+
+int nb200_ipc_export(const void *dev_ptr, void *handle) {
+  NB_CHECK(dev_ptr != nullptr && handle != nullptr, NB200_EVALUE, "null pointer");
+  cudaIpcMemHandle_t h;
+  NB_CUDA(cudaIpcGetMemHandle(&h, const_cast<void *>(dev_ptr)));
+  std::memcpy(handle, &h, sizeof(h));
+  return NB200_OK;
+}
+
+int nb200_ipc_open(const void *handle, void **peer_ptr) {
+  NB_CHECK(handle != nullptr && peer_ptr != nullptr, NB200_EVALUE, "null pointer");
+  *peer_ptr = nullptr;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  NB_CUDA(cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return NB200_OK;
+}
+
+int nb200_ipc_close(void *peer_ptr) {
+  if (peer_ptr)
+    NB_CUDA(cudaIpcCloseMemHandle(peer_ptr));
   return NB200_OK;
 }
 

@@ -230,6 +230,47 @@ def affine_from_codes(x_codes, w_codes, delta_x, delta_w, bias=None):
     return y
 
 
+def _rank_pointers(y_ranks):
+    """ctypes array of the per-rank output matrices' device addresses (tensors or plain integers)."""
+    addrs = [int(y.data_ptr()) if hasattr(y, "data_ptr") else int(y) for y in y_ranks]
+    return (ctypes.c_void_p * len(addrs))(*addrs)
+
+
+def affine_from_codes_gather(x_codes, w_codes, delta_x, delta_w, bias, y_ranks, rank, n_total, col_begin):
+    """Column shard of affine_from_codes with the gather fused into the kernel.
+
+    w_codes [K, n] and bias [n] are this rank's slab, columns [col_begin,
+    col_begin + n) of a [K, n_total] weight. y_ranks lists, for every rank, the
+    device address (or tensor) of its row-major [rows, n_total] fp32 result as
+    seen from this process (sharding.PeerMatrices provides them); the slab is
+    stored into all of them. The full result is valid on a rank once every
+    rank's call has completed (PeerMatrices.fence)."""
+    rows, K = x_codes.shape
+    K2, n = w_codes.shape
+    if K != K2:
+        raise RuntimeError("Size of input data(inputs[0]) and weights(inputs[1]) mismatch.")
+    with torch.cuda.device(x_codes.device):
+        C.call("nb200_affine_codes_i8_gather_f32", C.ptr(x_codes), C.ptr(w_codes), C.c_float(delta_x),
+               C.c_float(delta_w), C.ptr(bias), _rank_pointers(y_ranks), int(len(y_ranks)), int(rank),
+               ctypes.c_int64(rows), ctypes.c_int64(K), ctypes.c_int64(n), ctypes.c_int64(n_total),
+               ctypes.c_int64(col_begin), C.stream_ptr(x_codes.device))
+
+
+def affine_fixed_point_gather(xq, wq, delta_x, delta_w, bias, y_ranks, rank, n_total, col_begin):
+    """As affine_from_codes_gather, from the fp32 outputs of fixed_point_quantize
+    (xq [rows, K] multiples of delta_x, wq [K, n] multiples of delta_w)."""
+    xq, wq = _check_input(xq, "xq"), _check_input(wq, "wq")
+    rows, K = xq.shape
+    K2, n = wq.shape
+    if K != K2:
+        raise RuntimeError("Size of input data(inputs[0]) and weights(inputs[1]) mismatch.")
+    with torch.cuda.device(xq.device):
+        C.call("nb200_affine_fxp8_gather_f32", C.ptr(xq), C.ptr(wq), C.c_float(delta_x), C.c_float(delta_w),
+               C.ptr(bias), _rank_pointers(y_ranks), int(len(y_ranks)), int(rank), ctypes.c_int64(rows),
+               ctypes.c_int64(K), ctypes.c_int64(n), ctypes.c_int64(n_total), ctypes.c_int64(col_begin),
+               C.stream_ptr(xq.device))
+
+
 # ---------------------------------------------------------------------------
 # Convolutions
 # ---------------------------------------------------------------------------

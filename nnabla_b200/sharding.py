@@ -4,13 +4,17 @@
 * A single large affine: OUTPUT COLUMNS. Rank r owns W[:, c0:c1] (and for a
   binary-weight layer its own alpha[c0:c1], since alpha is per output column,
   src/nbla/function/generic/binary_weight_affine.cpp:92-98), every rank holds
-  the full x; the only exchange is an all-gather of the [rows, c1-c0] output
-  slabs, interleaved back into the row-major [rows, N] result.
+  the full x; the only exchange is the gather of the [rows, c1-c0] output
+  slabs into the row-major [rows, N] result, either as an all-gather after the
+  contraction (gather_columns) or fused into the contraction's epilogue, which
+  stores each slab straight into every rank's result (PeerMatrices).
 * Convolutions and whole networks: the BATCH; weights replicated; no exchange
   during forward.
 
 torch.distributed is the plumbing (NCCL on GPUs, gloo in the CPU tests).
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -73,3 +77,70 @@ def gather_batch(y_shard, n_total, group=None):
     dist.all_gather_into_tensor(flat, buf, group=group)
     stage = flat.view((world, smax) + tail)
     return torch.cat([stage[r, :e - b] for r, (b, e) in enumerate(sizes)], 0)
+
+
+class _DeviceArray:
+    """A device allocation owned through the C ABI, exposed to torch via the CUDA array interface."""
+
+    def __init__(self, addr, shape):
+        self.addr = addr
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (addr, False),
+                                         "version": 2, "strides": None}
+
+
+class PeerMatrices:
+    """One row-major [rows, cols] fp32 matrix per rank, each mapped into every
+    rank's address space, for contractions that store their output-column slab
+    into all ranks' results (functions.affine_from_codes_gather).
+
+    Collective constructor: every rank of `group` allocates its matrix through
+    the C ABI (nb200_malloc), exports it (nb200_ipc_export), the 64-byte
+    handles are exchanged with all_gather_object, and each rank opens the
+    others' (nb200_ipc_open). `ptrs[r]` is rank r's matrix as seen from this
+    process, `local` a torch view of this rank's own matrix."""
+
+    def __init__(self, rows, cols, group=None, device=None):
+        from . import _capi as C
+        self._C = C
+        self.rows, self.cols, self.group = int(rows), int(cols), group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        nbytes = self.rows * self.cols * 4
+        with torch.cuda.device(self.device):
+            own = ctypes.c_void_p(0)
+            C.call("nb200_malloc", ctypes.byref(own), C.size_t(nbytes))
+            self._own = own.value
+            handle = (ctypes.c_ubyte * 64)()
+            C.call("nb200_ipc_export", ctypes.c_void_p(self._own), handle)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self.ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.ptrs.append(self._own)
+                    continue
+                p = ctypes.c_void_p(0)
+                C.call("nb200_ipc_open", (ctypes.c_ubyte * 64).from_buffer_copy(h), ctypes.byref(p))
+                self.ptrs.append(p.value)
+        self.local = torch.as_tensor(_DeviceArray(self._own, (self.rows, self.cols)), device=self.device)
+        self._flag = torch.zeros(1, device=self.device)
+
+    def fence(self):
+        """Orders the ranks on the current stream: work enqueued after it sees
+        every rank's stores that were enqueued before it."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def close(self):
+        """Collective: unmaps the peers' matrices, then frees this rank's own."""
+        if self._own is None:
+            return
+        C = self._C
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.device(self.device):
+            for r, p in enumerate(self.ptrs):
+                if r != self.rank:
+                    C.call("nb200_ipc_close", ctypes.c_void_p(p))
+            dist.barrier(self.group)  # nobody frees while a peer still has the array mapped
+            self.local = None
+            C.call("nb200_free", ctypes.c_void_p(self._own))
+        self._own, self.ptrs = None, []
