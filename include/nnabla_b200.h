@@ -157,6 +157,31 @@ int nb200_min_max_quantize_f32_noalloc(const float *x, const int64_t *x_shape, i
 int nb200_min_max_quantize_f32_host(const float *x, size_t size, float *qr_min, float *qr_max, const float *ql_min,
                                     const float *ql_max, float eps, float *y);
 
+/* ---- quantizer backward passes (straight-through estimators) -------------------
+ * dx (+)= gradient for n elements; accum != 0 adds to dx (elements that pass no
+ * gradient are left untouched), accum == 0 overwrites (zero where blocked),
+ * exactly like the reference loops. x is not read when ste_fine_grained == 0. */
+/* FixedPointQuantize<float>::backward_impl
+ * (src/nbla/function/generic/fixed_point_quantize.cpp:69-127). */
+int nb200_fixed_point_quantize_backward_f32(const float *x, const float *dy, float *dx, size_t size, int sign, int n,
+                                            float delta, int ste_fine_grained, int accum, void *stream);
+/* Pow2Quantize<float>::backward_impl
+ * (src/nbla/function/generic/pow2_quantize.cpp:84-156). */
+int nb200_pow2_quantize_backward_f32(const float *x, const float *dy, float *dx, size_t size, int sign, int with_zero,
+                                     int n, int m, int ste_fine_grained, int accum, void *stream);
+/* MinMaxQuantize<float>::backward_impl
+ * (src/nbla/function/generic/min_max_quantize.cpp:225-350), called after the
+ * forward: qr_min / qr_max hold the ranges the forward left in place. Shapes
+ * as in nb200_min_max_quantize_f32. propagate_down[3] / accum[3] are the
+ * flags of x, qr_min, qr_max. g_qr_min / g_qr_max (q-shaped) are written only
+ * when neither x_min_max nor ema is set (the reference returns before them,
+ * :300-301). */
+int nb200_min_max_quantize_backward_f32(const float *x, const int64_t *x_shape, int ndim, const float *qr_min,
+                                        const float *qr_max, const float *ql_min, const float *ql_max,
+                                        const int64_t *q_shape, const float *dy, int x_min_max, int ema,
+                                        int ste_fine_grained, const int32_t *propagate_down, const int32_t *accum,
+                                        float *dx, float *g_qr_min, float *g_qr_max, void *stream);
+
 /* ---- binary-weight and fixed-point affine layers ----------------------------- */
 
 /* Device-side waits in the contraction kernels are time-bounded. A wait that

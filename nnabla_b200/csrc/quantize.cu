@@ -799,6 +799,8 @@ int static_scratch_for_current_device(float **out) {
   return NB200_OK;
 }
 
+#include "quantize_backward.cuh"
+
 // ---- chunk callbacks of the _host variants ---------------------------------
 struct FxpHostArgs {
   int sign, n;
@@ -924,5 +926,37 @@ int nb200_min_max_quantize_f32_host(const float *x, size_t size, float *qr_min, 
   } while (0);
   cudaFree(d);
   return rc;
+}
+
+int nb200_fixed_point_quantize_backward_f32(const float *x, const float *dy, float *dx, size_t size, int sign, int n,
+                                            float delta, int ste_fine_grained, int accum, void *stream) {
+  FxpLimits L;
+  NB_TRY(fxp_limits(sign, n, delta, &L));
+  if (ste_fine_grained)
+    return launch_gradient(x, dy, dx, size, accum, FxpGrad{L.maxv, L.minv}, as_stream(stream));
+  return launch_gradient(x, dy, dx, size, accum, PassAllGrad(), as_stream(stream));
+}
+
+int nb200_pow2_quantize_backward_f32(const float *x, const float *dy, float *dx, size_t size, int sign, int with_zero,
+                                     int n, int m, int ste_fine_grained, int accum, void *stream) {
+  Pow2Params P;
+  NB_TRY(pow2_params(sign, with_zero, n, m, &P));
+  if (!ste_fine_grained)
+    return launch_gradient(x, dy, dx, size, accum, PassAllGrad(), as_stream(stream));
+  Pow2Grad op{0u, P.sign};
+  NB_TRY(pow2_gradient_threshold(P, &op.threshold_bits));
+  return launch_gradient(x, dy, dx, size, accum, op, as_stream(stream));
+}
+
+int nb200_min_max_quantize_backward_f32(const float *x, const int64_t *x_shape, int ndim, const float *qr_min,
+                                        const float *qr_max, const float *ql_min, const float *ql_max,
+                                        const int64_t *q_shape, const float *dy, int x_min_max, int ema,
+                                        int ste_fine_grained, const int32_t *propagate_down, const int32_t *accum,
+                                        float *dx, float *g_qr_min, float *g_qr_max, void *stream) {
+  NB_CHECK(x_shape && q_shape && propagate_down && accum, NB200_EVALUE, "null shape or flag pointer");
+  MinMaxView V;
+  NB_TRY(minmax_view(x_shape, q_shape, ndim, &V));
+  return minmax_backward(x, V, qr_min, qr_max, ql_min, ql_max, dy, x_min_max, ema, ste_fine_grained, propagate_down,
+                         accum, dx, g_qr_min, g_qr_max, as_stream(stream));
 }
 }

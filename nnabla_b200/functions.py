@@ -108,6 +108,74 @@ def min_max_quantize(x, qr_min, qr_max, ql_min, ql_max, decay=0.999, x_min_max=F
 
 
 # ---------------------------------------------------------------------------
+# Quantizer backward passes. nnabla reaches these through Function::backward of
+# the graph engine; here they are plain calls: dx receives (accum=False) or
+# accumulates (accum=True) the gradient w.r.t. x given the output gradient dy.
+# ---------------------------------------------------------------------------
+
+def _grad_buffers(x, dy, dx, accum):
+    x, dy = _check_input(x), _check_input(dy, "dy")
+    if dy.shape != x.shape:
+        raise RuntimeError("dy must have x's shape")
+    if dx is None:
+        if accum:
+            raise RuntimeError("accum=True needs the gradient buffer dx to accumulate into")
+        dx = torch.empty_like(x)
+    elif dx.shape != x.shape or dx.dtype != torch.float32 or dx.device != x.device or not dx.is_contiguous():
+        raise RuntimeError("dx must be a contiguous float32 tensor of x's shape and device")
+    return x, dy, dx
+
+
+def fixed_point_quantize_backward(x, dy, sign=True, n=8, delta=2 ** -4, ste_fine_grained=True, accum=False, dx=None):
+    """FixedPointQuantize::backward_impl (src/nbla/function/generic/fixed_point_quantize.cpp:69-127)."""
+    x, dy, dx = _grad_buffers(x, dy, dx, accum)
+    with torch.cuda.device(x.device):
+        C.call("nb200_fixed_point_quantize_backward_f32", C.ptr(x), C.ptr(dy), C.ptr(dx), C.size_t(x.numel()),
+               int(bool(sign)), int(n), C.c_float(delta), int(bool(ste_fine_grained)), int(bool(accum)),
+               C.stream_ptr(x.device))
+    return dx
+
+
+def pow2_quantize_backward(x, dy, sign=True, with_zero=True, n=8, m=1, ste_fine_grained=True, accum=False, dx=None):
+    """Pow2Quantize::backward_impl (src/nbla/function/generic/pow2_quantize.cpp:84-156)."""
+    x, dy, dx = _grad_buffers(x, dy, dx, accum)
+    with torch.cuda.device(x.device):
+        C.call("nb200_pow2_quantize_backward_f32", C.ptr(x), C.ptr(dy), C.ptr(dx), C.size_t(x.numel()),
+               int(bool(sign)), int(bool(with_zero)), int(n), int(m), int(bool(ste_fine_grained)), int(bool(accum)),
+               C.stream_ptr(x.device))
+    return dx
+
+
+def min_max_quantize_backward(x, qr_min, qr_max, ql_min, ql_max, dy, x_min_max=False, ema=False,
+                              ste_fine_grained=True, propagate_down=(True, True, True),
+                              accum=(False, False, False), grads=(None, None, None)):
+    """MinMaxQuantize::backward_impl (src/nbla/function/generic/min_max_quantize.cpp:225-350).
+
+    Call after min_max_quantize: qr_min / qr_max are the ranges the forward
+    left in place. Returns (dx, g_qr_min, g_qr_max); the range gradients are
+    produced only when neither x_min_max nor ema is set."""
+    x, dy, dx = _grad_buffers(x, dy, grads[0], accum[0])
+    qs = [_check_input(t, nm) for t, nm in ((qr_min, "qr_min"), (qr_max, "qr_max"), (ql_min, "ql_min"),
+                                            (ql_max, "ql_max"))]
+    if len({tuple(t.shape) for t in qs}) != 1 or qs[0].dim() != x.dim():
+        raise RuntimeError("All shapes among ql_min, ql_max, qr_min, and qr_max must be same.")
+    gq = []
+    for g, acc in ((grads[1], accum[1]), (grads[2], accum[2])):
+        if g is None:
+            if acc:
+                raise RuntimeError("accum=True needs the gradient buffer to accumulate into")
+            g = torch.zeros_like(qs[0])
+        gq.append(_check_input(g, "range gradient"))
+    with torch.cuda.device(x.device):
+        C.call("nb200_min_max_quantize_backward_f32", C.ptr(x), C.i64_array(x.shape), int(x.dim()), C.ptr(qs[0]),
+               C.ptr(qs[1]), C.ptr(qs[2]), C.ptr(qs[3]), C.i64_array(qs[0].shape), C.ptr(dy), int(bool(x_min_max)),
+               int(bool(ema)), int(bool(ste_fine_grained)), C.i32_array([bool(v) for v in propagate_down]),
+               C.i32_array([bool(v) for v in accum]), C.ptr(dx), C.ptr(gq[0]), C.ptr(gq[1]),
+               C.stream_ptr(x.device))
+    return dx, gq[0], gq[1]
+
+
+# ---------------------------------------------------------------------------
 # Affine layers
 # ---------------------------------------------------------------------------
 

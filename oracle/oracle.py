@@ -249,3 +249,44 @@ def global_average_pooling(x):
     y = np.empty((N, C, 1, 1), np.float32)
     lib().oracle_global_average_pooling(_p(x), ctypes.c_int64(N * C), ctypes.c_int64(S), _p(y))
     return y
+
+
+# Backward passes -------------------------------------------------------------
+
+def fixed_point_quantize_backward(x, dy, sign=True, n=8, delta=2.0 ** -4, ste_fine_grained=True, accum=False,
+                                  dx=None):
+    x, dy = _f(x), _f(dy)
+    g = np.zeros_like(x) if dx is None else _f(dx).copy().reshape(x.shape)
+    lib().oracle_fixed_point_quantize_backward(_p(x), _p(dy), _p(g), ctypes.c_int64(x.size), int(sign), int(n),
+                                               ctypes.c_float(delta), int(ste_fine_grained), int(accum))
+    return g
+
+
+def pow2_quantize_backward(x, dy, sign=True, with_zero=True, n=8, m=1, ste_fine_grained=True, accum=False, dx=None):
+    x, dy = _f(x), _f(dy)
+    g = np.zeros_like(x) if dx is None else _f(dx).copy().reshape(x.shape)
+    lib().oracle_pow2_quantize_backward(_p(x), _p(dy), _p(g), ctypes.c_int64(x.size), int(sign), int(with_zero),
+                                        int(n), int(m), int(ste_fine_grained), int(accum))
+    return g
+
+
+def min_max_quantize_backward(x, qr_min, qr_max, ql_min, ql_max, dy, x_min_max=False, ema=False,
+                              ste_fine_grained=True, propagate_down=(True, True, True),
+                              accum=(False, False, False), grads=(None, None, None)):
+    """qr_min / qr_max are the values the forward left behind. Returns
+    (dx, g_qr_min, g_qr_max)."""
+    x, dy = _f(x), _f(dy)
+    qr_min, qr_max, ql_min, ql_max = _f(qr_min), _f(qr_max), _f(ql_min), _f(ql_max)
+    gx = np.zeros_like(x) if grads[0] is None else _f(grads[0]).copy().reshape(x.shape)
+    gmin = np.zeros_like(qr_min) if grads[1] is None else _f(grads[1]).copy().reshape(qr_min.shape)
+    gmax = np.zeros_like(qr_min) if grads[2] is None else _f(grads[2]).copy().reshape(qr_min.shape)
+    pd = (ctypes.c_int32 * 3)(*[int(bool(v)) for v in propagate_down])
+    ac = (ctypes.c_int32 * 3)(*[int(bool(v)) for v in accum])
+    L = lib()
+    L.oracle_min_max_quantize_backward.restype = ctypes.c_int
+    rc = L.oracle_min_max_quantize_backward(_p(x), _shape(x.shape), x.ndim, _p(qr_min), _p(qr_max), _p(ql_min),
+                                            _p(ql_max), _shape(qr_min.shape), _p(dy), int(x_min_max), int(ema),
+                                            int(ste_fine_grained), pd, ac, _p(gx), _p(gmin), _p(gmax))
+    if rc != 0:
+        raise ValueError("oracle_min_max_quantize_backward: bad shapes")
+    return gx, gmin, gmax

@@ -1,0 +1,158 @@
+/* CPU restatement of the reference's quantizer backward passes (straight-
+ * through estimators), in plain C, one function per reference loop.
+ *
+ * TEST INFRASTRUCTURE ONLY: the checker the CUDA path is compared against.
+ * The product library never links or calls it.
+ *
+ * Parity status: PINNED against the reference's own compiled C++
+ * (oracle/_ref/libnnabla_ref.so, Function::backward) by
+ * tests/test_oracle_vs_reference.py: bit for bit for the input gradients; the
+ * two range gradients of MinMaxQuantize are fp32 sums whose order inside the
+ * reference comes from Eigen (absent), so they are pinned to rounding only.
+ *
+ * Build: gcc -O2 -fno-fast-math -ffp-contract=off, like oracle_quant.c.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+
+/* src/nbla/function/generic/fixed_point_quantize.cpp:69-127. With
+ * ste_fine_grained the gradient passes where min <= x <= max and is zero in
+ * the clipped regions (written only when not accumulating); without it the
+ * gradient passes everywhere. */
+void oracle_fixed_point_quantize_backward(const float *x, const float *dy,
+                                          float *dx, int64_t size, int sign,
+                                          int n, float delta,
+                                          int ste_fine_grained, int accum) {
+  int nn = sign ? n - 1 : n;
+  float max_ = (float)((pow(2, nn) - 1) * delta);
+  float min_ = sign ? -max_ : 0.0f;
+  for (int64_t s = 0; s < size; ++s) {
+    if (ste_fine_grained && (x[s] > max_ || x[s] < min_)) {
+      if (!accum)
+        dx[s] = 0.0f;
+    } else if (accum) {
+      dx[s] = dx[s] + dy[s];
+    } else {
+      dx[s] = dy[s];
+    }
+  }
+}
+
+/* src/nbla/function/generic/pow2_quantize.cpp:84-156. The factor c is 0 where
+ * the snapped power of two exceeds p_max and, for unsigned quantization, where
+ * x is negative; the product c * dy is formed even when c is 0 (so the sign of
+ * a zero gradient and NaN/inf in dy behave like the reference). */
+void oracle_pow2_quantize_backward(const float *x, const float *dy, float *dx,
+                                   int64_t size, int sign, int with_zero,
+                                   int n, int m, int ste_fine_grained,
+                                   int accum) {
+  (void)with_zero;
+  (void)n;
+  float p_max = (float)pow(2., m);
+  for (int64_t s = 0; s < size; ++s) {
+    float c = 1.0f;
+    if (ste_fine_grained) {
+      float x_abs = fabsf(x[s]);
+      float q = powf(2.0f, roundf(log2f(x_abs)));
+      if (q > p_max)
+        c = 0.0f;
+      if (!sign && x[s] < 0.0f)
+        c = 0.0f;
+      float g = c * dy[s];
+      dx[s] = accum ? dx[s] + g : g;
+    } else {
+      dx[s] = accum ? dx[s] + dy[s] : dy[s];
+    }
+  }
+}
+
+/* src/nbla/function/generic/min_max_quantize.cpp:225-350, after a forward
+ * that left the nudged qr_min / qr_max in place. Shapes as in
+ * oracle_min_max_quantize. propagate / accum hold the flags of x, qr_min,
+ * qr_max in that order. The range gradients exist only when neither
+ * x_min_max nor ema is set (:300-301). Returns 0, or -1 on a shape error. */
+int oracle_min_max_quantize_backward(const float *x, const int64_t *xs, int nd,
+                                     const float *qr_min, const float *qr_max,
+                                     const float *ql_min, const float *ql_max,
+                                     const int64_t *qs, const float *dy,
+                                     int x_min_max, int ema,
+                                     int ste_fine_grained,
+                                     const int32_t *propagate,
+                                     const int32_t *accum, float *dx,
+                                     float *g_qr_min, float *g_qr_max) {
+  int64_t xsize = 1, qsize = 1, xstr[8], qstr[8];
+  if (nd > 8)
+    return -1;
+  for (int d = nd - 1; d >= 0; --d) {
+    if (qs[d] != 1 && qs[d] != xs[d])
+      return -1;
+    xstr[d] = xsize;
+    xsize *= xs[d];
+    qstr[d] = (qs[d] == 1) ? 0 : qsize;
+    qsize *= qs[d];
+  }
+  size_t qn = (size_t)(qsize ? qsize : 1);
+  float *m = (float *)malloc(sizeof(float) * qn);
+  float *M = (float *)malloc(sizeof(float) * qn);
+  float *smin = (float *)calloc(qn, sizeof(float));
+  float *smax = (float *)calloc(qn, sizeof(float));
+  if (!m || !M || !smin || !smax)
+    return -1;
+  for (int64_t q = 0; q < qsize; ++q) {
+    /* scale as the forward left it (:184-186), then nudge_qr_min_max (:362-390) */
+    float num = qr_max[q] - qr_min[q];
+    float den = ql_max[q] - ql_min[q];
+    float scale = num / den;
+    float t = qr_min[q] / scale;
+    float zp_from_min = ql_min[q] - t;
+    float zp;
+    if (zp_from_min <= ql_min[q])
+      zp = ql_min[q];
+    else if (zp_from_min >= ql_max[q])
+      zp = ql_max[q];
+    else
+      zp = roundf(zp_from_min);
+    float a = ql_min[q] - zp, b = ql_max[q] - zp;
+    m[q] = a * scale;
+    M[q] = b * scale;
+  }
+  const int ranges = !(x_min_max || ema);
+  for (int64_t i = 0; i < xsize; ++i) {
+    int64_t q = 0, r = i;
+    for (int d = 0; d < nd; ++d) {
+      int64_t c = r / xstr[d];
+      r -= c * xstr[d];
+      q += c * qstr[d];
+    }
+    if (propagate[0]) {
+      float g = dy[i];
+      if (ste_fine_grained) {
+        /* greater_equal * less_equal masks (1 or 0), multiplied with dy */
+        float mask = ((x[i] >= m[q]) ? 1.0f : 0.0f) * ((x[i] <= M[q]) ? 1.0f : 0.0f);
+        g = mask * dy[i];
+      }
+      dx[i] = accum[0] ? g + dx[i] : g;
+    }
+    if (ranges) {
+      /* less / greater masks times dy, summed over the axes where q is 1 */
+      float lo = ((x[i] < m[q]) ? 1.0f : 0.0f) * dy[i];
+      float hi = ((x[i] > M[q]) ? 1.0f : 0.0f) * dy[i];
+      smin[q] = smin[q] + lo;
+      smax[q] = smax[q] + hi;
+    }
+  }
+  if (ranges) {
+    for (int64_t q = 0; q < qsize; ++q) {
+      if (propagate[1])
+        g_qr_min[q] = accum[1] ? g_qr_min[q] + smin[q] : smin[q];
+      if (propagate[2])
+        g_qr_max[q] = accum[2] ? g_qr_max[q] + smax[q] : smax[q];
+    }
+  }
+  free(m);
+  free(M);
+  free(smin);
+  free(smax);
+  return 0;
+}

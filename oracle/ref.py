@@ -79,6 +79,51 @@ def forward(op, scalars, ivecs, inputs, n_out=1, repeat=1):
     return outs, ins, secs.value
 
 
+def backward(op, scalars, ivecs, inputs, out_grads, propagate_down, accum=None, in_grads=None):
+    """Setup + forward + Function::backward of reference function `op`.
+
+    inputs: float32 arrays (no None entries); out_grads: gradient arriving at
+    each output; propagate_down / accum: one flag per input; in_grads: the
+    initial gradient buffers of the inputs (zeros when omitted). Returns
+    (in_grads_after, outputs, inputs_after)."""
+    L = lib()
+    L.nbref_backward.restype = ctypes.c_int
+    ins = [np.ascontiguousarray(a, dtype=np.float32).copy() for a in inputs]
+    n_in = len(ins)
+    accum = [False] * n_in if accum is None else list(accum)
+    if in_grads is None:
+        in_grads = [None] * n_in
+    grads = [np.zeros_like(a) if g is None else np.ascontiguousarray(g, dtype=np.float32).copy().reshape(a.shape)
+             for a, g in zip(ins, in_grads)]
+    s = (ctypes.c_double * max(1, len(scalars)))(*[float(v) for v in scalars])
+    flat = [int(v) for vec in ivecs for v in vec]
+    iv = (ctypes.c_int32 * max(1, len(flat)))(*flat)
+    ivl = (ctypes.c_int32 * max(1, len(ivecs)))(*[len(v) for v in ivecs])
+
+    def tensors(arrays):
+        t = (_Tensor * len(arrays))()
+        for e, a in zip(t, arrays):
+            e.data = a.ctypes.data
+            e.ndim = a.ndim
+            for d, n in enumerate(a.shape):
+                e.shape[d] = n
+        return t
+    n_out = len(out_grads)
+    ogs = [np.ascontiguousarray(g, dtype=np.float32).copy() for g in out_grads]
+    outs = [np.empty(g.shape, dtype=np.float32) for g in ogs]
+    tin, tgin, tout, tgout = tensors(ins), tensors(grads), tensors(outs), tensors(ogs)
+    pd = (ctypes.c_int32 * n_in)(*[int(bool(v)) for v in propagate_down])
+    ac = (ctypes.c_int32 * n_in)(*[int(bool(v)) for v in accum])
+    rc = L.nbref_backward(op.encode(), s, len(scalars), iv, ivl, len(ivecs), tin, tgin, n_in, tout, tgout, n_out,
+                          pd, ac)
+    if rc != 0:
+        raise RuntimeError(L.nbref_last_error().decode())
+    for t, o in zip(tout, outs):
+        if tuple(t.shape[d] for d in range(t.ndim)) != o.shape:
+            raise RuntimeError("out_grads[.] does not have the output's shape")
+    return grads, outs, ins
+
+
 # Convenience wrappers named after the reference functions -------------------
 
 def fixed_point_quantize(x, sign=True, n=8, delta=2.0 ** -4, ste_fine_grained=True, repeat=1, timed=False):
@@ -171,3 +216,26 @@ def average_pooling(x, kernel, stride, ignore_border=True, pad=(0, 0), including
 
 def global_average_pooling(x):
     return forward("GlobalAveragePooling", [], [], [x])[0][0]
+
+
+# Backward passes -------------------------------------------------------------
+
+def fixed_point_quantize_backward(x, dy, sign=True, n=8, delta=2.0 ** -4, ste_fine_grained=True, accum=False, dx=None):
+    g, _, _ = backward("FixedPointQuantize", [sign, n, delta, ste_fine_grained], [], [x], [dy], [True], [accum], [dx])
+    return g[0]
+
+
+def pow2_quantize_backward(x, dy, sign=True, with_zero=True, n=8, m=1, ste_fine_grained=True, accum=False, dx=None):
+    g, _, _ = backward("Pow2Quantize", [sign, with_zero, n, m, ste_fine_grained], [], [x], [dy], [True], [accum], [dx])
+    return g[0]
+
+
+def min_max_quantize_backward(x, qr_min, qr_max, ql_min, ql_max, dy, decay=0.999, x_min_max=False, ema=False,
+                              ste_fine_grained=True, eps=0.01, propagate_down=(True, True, True),
+                              accum=(False, False, False), grads=(None, None, None)):
+    """Returns (dx, g_qr_min, g_qr_max) after forward + backward."""
+    pd = list(propagate_down) + [False, False]
+    ac = list(accum) + [False, False]
+    g, _, _ = backward("MinMaxQuantize", [decay, x_min_max, ema, ste_fine_grained, eps], [],
+                       [x, qr_min, qr_max, ql_min, ql_max], [dy], pd, ac, list(grads) + [None, None])
+    return g[0], g[1], g[2]

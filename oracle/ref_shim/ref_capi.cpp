@@ -41,6 +41,81 @@
 
 using namespace nbla;
 
+static std::vector<std::vector<int>> split_vectors(const int32_t *iv,
+                                                    const int32_t *iv_len,
+                                                    int n_iv) {
+  std::vector<std::vector<int>> ivs;
+  const int32_t *p = iv;
+  for (int i = 0; i < n_iv; ++i) {
+    ivs.emplace_back(p, p + iv_len[i]);
+    p += iv_len[i];
+  }
+  return ivs;
+}
+
+// Creates function `op` through the reference's registry. s: scalar arguments
+// in the order of the reference constructor, each as a double (bool/int/float
+// alike); ivs: the vector<int> arguments in constructor order.
+static FunctionPtr make_function(const Context &ctx, const char *op,
+                                 const double *s, int n_s,
+                                 const std::vector<std::vector<int>> &ivs) {
+  const int n_iv = (int)ivs.size();
+  auto S = [&](int i) -> double {
+    NBLA_CHECK(i < n_s, error_code::value, "missing scalar argument %d", i);
+    return s[i];
+  };
+  auto V = [&](int i) -> const std::vector<int> & {
+    NBLA_CHECK(i < n_iv, error_code::value, "missing vector argument %d", i);
+    return ivs[i];
+  };
+  const std::string name(op);
+  FunctionPtr f;
+  if (name == "FixedPointQuantize")
+    f = create_FixedPointQuantize(ctx, S(0) != 0, (int)S(1), (float)S(2),
+                                  S(3) != 0);
+  else if (name == "Pow2Quantize")
+    f = create_Pow2Quantize(ctx, S(0) != 0, S(1) != 0, (int)S(2), (int)S(3),
+                            S(4) != 0);
+  else if (name == "MinMaxQuantize")
+    f = create_MinMaxQuantize(ctx, (float)S(0), S(1) != 0, S(2) != 0,
+                              S(3) != 0, (float)S(4));
+  else if (name == "BinaryWeightAffine")
+    f = create_BinaryWeightAffine(ctx, (int)S(0), (float)S(1));
+  else if (name == "BinaryConnectAffine")
+    f = create_BinaryConnectAffine(ctx, (int)S(0), (float)S(1));
+  else if (name == "BinaryWeightConvolution")
+    f = create_BinaryWeightConvolution(ctx, (int)S(0), V(0), V(1), V(2),
+                                       (int)S(1), (float)S(2));
+  else if (name == "BinaryConnectConvolution")
+    f = create_BinaryConnectConvolution(ctx, (int)S(0), V(0), V(1), V(2),
+                                        (int)S(1), (float)S(2));
+  else if (name == "Sign")
+    f = create_Sign(ctx, (float)S(0));
+  else if (name == "Affine")
+    f = create_Affine(ctx, (int)S(0));
+  else if (name == "Convolution")
+    f = create_Convolution(ctx, (int)S(0), V(0), V(1), V(2), (int)S(1),
+                           S(2) != 0);
+  else if (name == "BatchNormalization")
+    f = create_BatchNormalization(ctx, V(0), (float)S(0), (float)S(1),
+                                  S(2) != 0, S(3) != 0, S(4) != 0);
+  else if (name == "ReLU")
+    f = create_ReLU(ctx, S(0) != 0);
+  else if (name == "MaxPooling")
+    f = create_MaxPooling(ctx, V(0), V(1), S(0) != 0, V(2), S(1) != 0);
+  else if (name == "AveragePooling")
+    f = create_AveragePooling(ctx, V(0), V(1), S(0) != 0, V(2), S(1) != 0,
+                              S(2) != 0);
+  else if (name == "GlobalAveragePooling")
+    f = create_GlobalAveragePooling(ctx);
+  else if (name == "Add2")
+    f = create_Add2(ctx, S(0) != 0);
+  else
+    NBLA_ERROR(error_code::value, "unknown function %s", op);
+
+  return f;
+}
+
 extern "C" {
 
 struct nbref_tensor {
@@ -65,66 +140,8 @@ int nbref_forward(const char *op, const double *s, int n_s, const int32_t *iv,
                   double *forward_seconds) {
   try {
     Context ctx({"cpu:float"}, "CpuCachedArray", "0");
-    std::vector<std::vector<int>> ivs;
-    {
-      const int32_t *p = iv;
-      for (int i = 0; i < n_iv; ++i) {
-        ivs.emplace_back(p, p + iv_len[i]);
-        p += iv_len[i];
-      }
-    }
-    auto S = [&](int i) -> double {
-      NBLA_CHECK(i < n_s, error_code::value, "missing scalar argument %d", i);
-      return s[i];
-    };
-    auto V = [&](int i) -> const std::vector<int> & {
-      NBLA_CHECK(i < n_iv, error_code::value, "missing vector argument %d", i);
-      return ivs[i];
-    };
-    const std::string name(op);
-    FunctionPtr f;
-    if (name == "FixedPointQuantize")
-      f = create_FixedPointQuantize(ctx, S(0) != 0, (int)S(1), (float)S(2),
-                                    S(3) != 0);
-    else if (name == "Pow2Quantize")
-      f = create_Pow2Quantize(ctx, S(0) != 0, S(1) != 0, (int)S(2), (int)S(3),
-                              S(4) != 0);
-    else if (name == "MinMaxQuantize")
-      f = create_MinMaxQuantize(ctx, (float)S(0), S(1) != 0, S(2) != 0,
-                                S(3) != 0, (float)S(4));
-    else if (name == "BinaryWeightAffine")
-      f = create_BinaryWeightAffine(ctx, (int)S(0), (float)S(1));
-    else if (name == "BinaryConnectAffine")
-      f = create_BinaryConnectAffine(ctx, (int)S(0), (float)S(1));
-    else if (name == "BinaryWeightConvolution")
-      f = create_BinaryWeightConvolution(ctx, (int)S(0), V(0), V(1), V(2),
-                                         (int)S(1), (float)S(2));
-    else if (name == "BinaryConnectConvolution")
-      f = create_BinaryConnectConvolution(ctx, (int)S(0), V(0), V(1), V(2),
-                                          (int)S(1), (float)S(2));
-    else if (name == "Sign")
-      f = create_Sign(ctx, (float)S(0));
-    else if (name == "Affine")
-      f = create_Affine(ctx, (int)S(0));
-    else if (name == "Convolution")
-      f = create_Convolution(ctx, (int)S(0), V(0), V(1), V(2), (int)S(1),
-                             S(2) != 0);
-    else if (name == "BatchNormalization")
-      f = create_BatchNormalization(ctx, V(0), (float)S(0), (float)S(1),
-                                    S(2) != 0, S(3) != 0, S(4) != 0);
-    else if (name == "ReLU")
-      f = create_ReLU(ctx, S(0) != 0);
-    else if (name == "MaxPooling")
-      f = create_MaxPooling(ctx, V(0), V(1), S(0) != 0, V(2), S(1) != 0);
-    else if (name == "AveragePooling")
-      f = create_AveragePooling(ctx, V(0), V(1), S(0) != 0, V(2), S(1) != 0,
-                                S(2) != 0);
-    else if (name == "GlobalAveragePooling")
-      f = create_GlobalAveragePooling(ctx);
-    else if (name == "Add2")
-      f = create_Add2(ctx, S(0) != 0);
-    else
-      NBLA_ERROR(error_code::value, "unknown function %s", op);
+    const std::vector<std::vector<int>> ivs = split_vectors(iv, iv_len, n_iv);
+    FunctionPtr f = make_function(ctx, op, s, n_s, ivs);
 
     std::vector<VariablePtr> vin, vout;
     Variables pin, pout;
@@ -165,6 +182,74 @@ int nbref_forward(const char *op, const double *s, int n_s, const int32_t *iv,
     for (int i = 0; i < n_in; ++i) {
       const float *p = pin[i]->get_data_pointer<float>(ctx);
       std::memcpy(in[i].data, p, sizeof(float) * pin[i]->size());
+    }
+    for (int i = 0; i < n_out; ++i) {
+      const float *p = pout[i]->get_data_pointer<float>(ctx);
+      std::memcpy(out[i].data, p, sizeof(float) * pout[i]->size());
+    }
+    return 0;
+  } catch (const std::exception &e) {
+    g_err = e.what();
+    return 1;
+  }
+}
+// Setup + forward + backward. in[i].data / out[j].data as in nbref_forward
+// (inputs and outputs are copied back after the forward); out_grad[j] is the
+// gradient arriving at output j; in_grad[i] holds the initial gradient of
+// input i (read when accum[i] != 0, otherwise the buffer is pre-filled with it
+// anyway so that elements the reference leaves untouched are visible) and
+// receives the gradient after Function::backward (src/nbla/function.cpp:125-
+// 160) ran with the given propagate_down / accum flags.
+int nbref_backward(const char *op, const double *s, int n_s, const int32_t *iv,
+                   const int32_t *iv_len, int n_iv, nbref_tensor *in,
+                   nbref_tensor *in_grad, int n_in, nbref_tensor *out,
+                   nbref_tensor *out_grad, int n_out,
+                   const int32_t *propagate_down, const int32_t *accum) {
+  try {
+    Context ctx({"cpu:float"}, "CpuCachedArray", "0");
+    const std::vector<std::vector<int>> ivs = split_vectors(iv, iv_len, n_iv);
+    FunctionPtr f = make_function(ctx, op, s, n_s, ivs);
+    std::vector<VariablePtr> vin, vout;
+    Variables pin, pout;
+    for (int i = 0; i < n_in; ++i) {
+      Shape_t sh(in[i].shape, in[i].shape + in[i].ndim);
+      vin.push_back(std::make_shared<Variable>(sh));
+      pin.push_back(vin.back().get());
+    }
+    for (int i = 0; i < n_out; ++i) {
+      vout.push_back(std::make_shared<Variable>());
+      pout.push_back(vout.back().get());
+    }
+    f->setup(pin, pout);
+    for (int i = 0; i < n_out; ++i) {
+      const Shape_t sh = pout[i]->shape();
+      NBLA_CHECK(sh.size() <= 8, error_code::value, "ndim > 8");
+      out[i].ndim = (int32_t)sh.size();
+      for (size_t d = 0; d < sh.size(); ++d)
+        out[i].shape[d] = sh[d];
+    }
+    for (int i = 0; i < n_in; ++i) {
+      float *p = pin[i]->cast_data_and_get_pointer<float>(ctx, true);
+      std::memcpy(p, in[i].data, sizeof(float) * pin[i]->size());
+      float *g = pin[i]->cast_grad_and_get_pointer<float>(ctx, true);
+      std::memcpy(g, in_grad[i].data, sizeof(float) * pin[i]->size());
+    }
+    f->forward(pin, pout);
+    for (int i = 0; i < n_out; ++i) {
+      float *g = pout[i]->cast_grad_and_get_pointer<float>(ctx, true);
+      std::memcpy(g, out_grad[i].data, sizeof(float) * pout[i]->size());
+    }
+    std::vector<bool> pd(n_in), ac(n_in);
+    for (int i = 0; i < n_in; ++i) {
+      pd[i] = propagate_down[i] != 0;
+      ac[i] = accum[i] != 0;
+    }
+    f->backward(pin, pout, pd, ac);
+    for (int i = 0; i < n_in; ++i) {
+      const float *p = pin[i]->get_data_pointer<float>(ctx);
+      std::memcpy(in[i].data, p, sizeof(float) * pin[i]->size());
+      const float *g = pin[i]->get_grad_pointer<float>(ctx);
+      std::memcpy(in_grad[i].data, g, sizeof(float) * pin[i]->size());
     }
     for (int i = 0; i < n_out; ++i) {
       const float *p = pout[i]->get_data_pointer<float>(ctx);

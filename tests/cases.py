@@ -50,6 +50,34 @@ def edge_values_pow2():
     return np.concatenate([v, -v])
 
 
+def pow2_backward_edges(m):
+    """Inputs around the only place where Pow2Quantize's gradient factor changes
+    (the snap from 2^m to 2^(m+1)), plus NaNs, whose factor stays 1."""
+    c = np.array([np.sqrt(2.0) * 2.0 ** m], np.float32).view(np.uint32)[0]
+    near = f32(np.arange(int(c) - 300, int(c) + 301, dtype=np.int64).astype(np.uint32))
+    v = np.concatenate([near, np.array([np.nan, 2.0 ** m, 2.0 ** (m + 1), 2.0 ** (m + 1) * 0.99999], np.float32)])
+    return np.concatenate([v, -v]).astype(np.float32)
+
+
+def grad_inputs(x, seed=7):
+    """Output gradient (with zeros and sign flips) and an initial input gradient for backward cases."""
+    rng = np.random.RandomState(seed)
+    dy = rng.randn(*x.shape).astype(np.float32)
+    dy.reshape(-1)[::13] = 0.0
+    dy.reshape(-1)[5::17] *= -1.0
+    dx0 = rng.randn(*x.shape).astype(np.float32)
+    return dy, dx0
+
+
+def fxp_backward_input(delta, n_eff):
+    x = np.concatenate([fxp_input((2, 3, 50)).ravel(), edge_values_fxp(np.float32(delta), n_eff)])
+    return x[~np.isnan(x)]
+
+
+def pow2_backward_input(m):
+    return np.concatenate([fxp_input((2, 3, 50)).ravel(), edge_values_pow2(), pow2_backward_edges(m)])
+
+
 FXP_GRID = list(itertools.product([False, True], [3, 8], [2.0 ** -7, 0.005]))   # sign, n, delta
 POW2_GRID = list(itertools.product([False, True], [False, True], [3, 5], [0, 1]))  # sign, with_zero, n, m
 MINMAX_SHAPES = [((4, 8, 16, 16), (1, 1, 1, 1)), ((4, 8, 16, 16), (1, 8, 1, 1)), ((16, 8, 3, 3), (16, 1, 1, 1))]

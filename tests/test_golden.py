@@ -74,3 +74,25 @@ def test_baseline_config_digests():
     assert np.array_equal(sha(oracle.fixed_point_quantize(x, True, 8, 2.0 ** -4)), g["cfg2_fxp/sha"])
     assert np.array_equal(sha(oracle.pow2_quantize(x, True, True, 8, 1)), g["cfg2_pow2/sha"])
     assert np.array_equal(sha(oracle.min_max_quantize(x, one(-4), one(4), one(0), one(255))[0]), g["cfg2_minmax/sha"])
+
+
+# ---- quantizer backward passes against golden_backward.npz -----------------
+import backward_cases  # noqa: E402
+
+
+@pytest.mark.parametrize("i", range(len(cases.FXP_GRID)))
+@pytest.mark.parametrize("fine,accum", backward_cases.FLAGS)
+def test_fxp_backward(i, fine, accum):
+    backward_cases.check_fxp(oracle, i, fine, accum)
+
+
+@pytest.mark.parametrize("i", range(len(backward_cases.POW2_CASES)))
+@pytest.mark.parametrize("fine,accum", backward_cases.FLAGS)
+def test_pow2_backward(i, fine, accum):
+    backward_cases.check_pow2(oracle, i, fine, accum)
+
+
+@pytest.mark.parametrize("i", range(len(cases.MINMAX_GRID)))
+@pytest.mark.parametrize("fine,accum", backward_cases.FLAGS)
+def test_minmax_backward(i, fine, accum):
+    backward_cases.check_minmax(oracle, i, fine, accum)
