@@ -267,6 +267,26 @@ def run_extras(args, rank, world, barrier):
         mats.close()
     out["configs[2] fixed-point int8 affine %dx%dx%d" % (M, K, N)] = entry
     del x, w, xq, wq, xc, wc
+    # quantizer backward passes (straight-through estimators) on the configs[1] parameters, per rank
+    nb = 1 << (22 if args.small_extras else 28)
+    gx = torch.rand(nb, device="cuda", generator=gen) * 9 - 4.5
+    gdy = rn(nb)
+    gdx = torch.empty_like(gx)
+    one = lambda v: torch.tensor([v], device="cuda")
+    qa, qb, la, lb = one(-4.0), one(4.0), one(0.0), one(255.0)
+    F.min_max_quantize(gx, qa, qb, la, lb)
+    bw = {}
+    for name, fn, bpe in (
+            ("fixed_point", lambda: F.fixed_point_quantize_backward(gx, gdy, True, 8, 2.0 ** -4, True, False, gdx), 12),
+            ("pow2", lambda: F.pow2_quantize_backward(gx, gdy, True, True, 8, 1, True, False, gdx), 12),
+            ("min_max_dx_and_ranges", lambda: F.min_max_quantize_backward(gx, qa, qb, la, lb, gdy, grads=(gdx, None, None)), 12),
+            ("fixed_point_accum", lambda: F.fixed_point_quantize_backward(gx, gdy, True, 8, 2.0 ** -4, True, True, gdx), 16),
+            ("coarse_ste_copy", lambda: F.fixed_point_quantize_backward(gx, gdy, True, 8, 2.0 ** -4, False, False, gdx), 8)):
+        ms = maxr(time_gpu(fn, 10))
+        bw[name] = {"ms": ms, "GBps_per_gpu": bpe * nb / ms / 1e6, "bytes_per_element": bpe,
+                    "frac_of_hbm_peak": bpe * nb / ms / 1e6 / peaks["hbm_gbs"]}
+    out["quantizer backward, 2^%d elements per GPU" % (22 if args.small_extras else 28)] = bw
+    del gx, gdy, gdx
     # configs[3]: BinaryWeightConvolution 3x3, 256 -> 256, 28 x 28, batch 128 sharded over the ranks
     Nb = max(1, (16 if args.small_extras else 128) // world)
     x = torch.relu(rn(Nb, 256, 28, 28))

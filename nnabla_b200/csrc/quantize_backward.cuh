@@ -243,28 +243,53 @@ __device__ __forceinline__ float masked(bool on, float g) { return __fmul_rn(on 
 // (x < m) * dy, g_qr_max[q] = sum of (x > M) * dy. grid = (splits, Q); block
 // (s, q) reduces its share to one pair of partial sums, a second kernel adds
 // the partials of each q in a fixed order (deterministic).
+// kDx: 0 = range sums only; 1 / 2 = per-tensor ranges (Q == 1, 16-byte aligned
+// buffers) also write / accumulate the gradient w.r.t. x in the same pass
+// (kFine: masked by m <= x <= M), so x and dy are read once.
+template <int kDx, bool kFine>
 __global__ void __launch_bounds__(kThreads) minmax_range_grad_kernel(const float *__restrict__ x,
                                                                      const float *__restrict__ dy, MinMaxView V,
                                                                      const float *__restrict__ m,
-                                                                     const float *__restrict__ M, float *partial) {
+                                                                     const float *__restrict__ M, float *partial,
+                                                                     float *__restrict__ dx) {
   const size_t q = blockIdx.y;
   const size_t per_q = V.outer * V.inner;
   const float lo = __ldg(m + q), hi = __ldg(M + q);
   float s_lo = 0.0f, s_hi = 0.0f;
   const size_t stride = (size_t)gridDim.x * kThreads;
-  if (V.Q == 1 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0) {
+  if (kDx != 0 || (V.Q == 1 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0)) {
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     const float4 *g4 = reinterpret_cast<const float4 *>(dy);
+    float4 *d4 = reinterpret_cast<float4 *>(dx);
     const size_t n4 = per_q / 4;
+    // gradient w.r.t. x of one element: (x >= m) * (x <= M) * dy, or dy itself
+    auto gx = [&](float a, float g, float d) {
+      const float v = __fmul_rn(a >= lo ? 1.0f : 0.0f, a <= hi ? 1.0f : 0.0f);
+      const float r = kFine ? __fmul_rn(v, g) : g;
+      return kDx == 2 ? __fadd_rn(r, d) : r;
+    };
     for (size_t t = (size_t)blockIdx.x * kThreads + threadIdx.x; t < n4; t += stride) {
       const float4 a = ld_stream(x4 + t), g = ld_stream(g4 + t);
       s_lo += masked(a.x < lo, g.x) + masked(a.y < lo, g.y) + masked(a.z < lo, g.z) + masked(a.w < lo, g.w);
       s_hi += masked(a.x > hi, g.x) + masked(a.y > hi, g.y) + masked(a.z > hi, g.z) + masked(a.w > hi, g.w);
+      if (kDx != 0) {
+        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (kDx == 2)
+          d = ld_stream(d4 + t);
+        float4 r;
+        r.x = gx(a.x, g.x, d.x);
+        r.y = gx(a.y, g.y, d.y);
+        r.z = gx(a.z, g.z, d.z);
+        r.w = gx(a.w, g.w, d.w);
+        st_stream(d4 + t, r);
+      }
     }
     if (blockIdx.x == 0)
       for (size_t t = 4 * n4 + threadIdx.x; t < per_q; t += kThreads) {
         s_lo += masked(x[t] < lo, dy[t]);
         s_hi += masked(x[t] > hi, dy[t]);
+        if (kDx != 0)
+          dx[t] = gx(x[t], dy[t], kDx == 2 ? dx[t] : 0.0f);
       }
   } else {
     for (size_t t = (size_t)blockIdx.x * kThreads + threadIdx.x; t < per_q; t += stride) {
@@ -347,7 +372,11 @@ int minmax_backward(const float *x, const MinMaxView &V, const float *qr_min, co
     minmax_nudged_kernel<<<(unsigned)((V.Q + 255) / 256), 256, 0, st>>>(V.Q, qr_min, qr_max, ql_min, ql_max, m, M);
     NB_LAUNCH_CHECK();
   }
-  if (prop[0]) {
+  // Per-tensor ranges with aligned buffers: one pass produces dx and the range sums.
+  const bool fused = ranges && prop[0] && V.Q == 1 && V.size > 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) |
+                       reinterpret_cast<uintptr_t>(dx)) & 15) == 0;
+  if (prop[0] && !fused) {
     if (fine) {
       MinMaxGrad op{m, M, V.Q, V.inner};
       NB_TRY(launch_gradient(x, dy, dx, V.size, accum[0], op, st));
@@ -358,7 +387,20 @@ int minmax_backward(const float *x, const MinMaxView &V, const float *qr_min, co
   if (ranges) {
     NB_CHECK((!prop[1] || g_min) && (!prop[2] || g_max), NB200_EVALUE, "null range-gradient pointer");
     NB_CHECK(V.size == 0 || (x && dy), NB200_EVALUE, "null data pointer");
-    minmax_range_grad_kernel<<<dim3((unsigned)splits, (unsigned)V.Q), kThreads, 0, st>>>(x, dy, V, m, M, partial);
+    const dim3 grid((unsigned)splits, (unsigned)V.Q);
+    if (!fused) {
+      minmax_range_grad_kernel<0, false><<<grid, kThreads, 0, st>>>(x, dy, V, m, M, partial, nullptr);
+    } else {
+      NB_CHECK(dx != nullptr, NB200_EVALUE, "null data pointer");
+      if (fine && accum[0])
+        minmax_range_grad_kernel<2, true><<<grid, kThreads, 0, st>>>(x, dy, V, m, M, partial, dx);
+      else if (fine)
+        minmax_range_grad_kernel<1, true><<<grid, kThreads, 0, st>>>(x, dy, V, m, M, partial, dx);
+      else if (accum[0])
+        minmax_range_grad_kernel<2, false><<<grid, kThreads, 0, st>>>(x, dy, V, m, M, partial, dx);
+      else
+        minmax_range_grad_kernel<1, false><<<grid, kThreads, 0, st>>>(x, dy, V, m, M, partial, dx);
+    }
     NB_LAUNCH_CHECK();
     minmax_range_finish_kernel<<<(unsigned)V.Q, kThreads, 0, st>>>(partial, (unsigned)splits, g_min, g_max, prop[1],
                                                                    prop[2], accum[1], accum[2]);
