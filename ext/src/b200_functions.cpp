@@ -165,7 +165,19 @@ protected:
     if ((this->sign_ ? this->n_ - 1 : this->n_) <= 7)
       fxp_tag_set(out[0], this->delta_);
   }
-  B200_NO_BACKWARD("FixedPointQuantize")
+  // fixed_point_quantize.cpp:103-127
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &propagate_down,
+                             const vector<bool> &accum) {
+    if (!propagate_down[0])
+      return;
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_);
+    float *dx = in[0]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[0]);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    nb200_check(nb200_fixed_point_quantize_backward_f32(x, dy, dx, in[0]->size(), this->sign_, this->n_, this->delta_,
+                                                        this->ste_fine_grained_, accum[0], nullptr),
+                "FixedPointQuantize backward");
+  }
 };
 
 template <typename T> class Pow2QuantizeB200 : public Pow2Quantize<T> {
@@ -182,7 +194,19 @@ protected:
                                         nullptr),
                 "Pow2Quantize");
   }
-  B200_NO_BACKWARD("Pow2Quantize")
+  // pow2_quantize.cpp:127-156
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &propagate_down,
+                             const vector<bool> &accum) {
+    if (!propagate_down[0])
+      return;
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_);
+    float *dx = in[0]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[0]);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    nb200_check(nb200_pow2_quantize_backward_f32(x, dy, dx, in[0]->size(), this->sign_, this->with_zero_, this->n_,
+                                                 this->m_, this->ste_fine_grained_, accum[0], nullptr),
+                "Pow2Quantize backward");
+  }
 };
 
 template <typename T> class MinMaxQuantizeB200 : public MinMaxQuantize<T> {
@@ -218,7 +242,31 @@ protected:
                                            this->decay_, this->x_min_max_, this->ema_, this->eps_, y, scale, nullptr),
                 "MinMaxQuantize");
   }
-  B200_NO_BACKWARD("MinMaxQuantize")
+  // min_max_quantize.cpp:225-350
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &propagate_down,
+                             const vector<bool> &accum) {
+    NBLA_CHECK(!(propagate_down[3] || propagate_down[4]), error_code::value,
+               "Backward to x(inputs[0]), qr_min(inputs[1]), and/or qr_max(inputs[2])"
+               "are only allowed.");
+    enter(this->ctx_);
+    const bool ranges = !(this->x_min_max_ || this->ema_);
+    const int32_t pd[3] = {propagate_down[0], ranges && propagate_down[1], ranges && propagate_down[2]};
+    const int32_t ac[3] = {accum[0], accum[1], accum[2]};
+    if (!(pd[0] || pd[1] || pd[2]))
+      return;
+    const Shape_t sx = in[0]->shape(), sq = in[1]->shape();
+    const float *x = rd(in[0], this->ctx_);
+    const float *qr_min = rd(in[1], this->ctx_), *qr_max = rd(in[2], this->ctx_);
+    const float *ql_min = rd(in[3], this->ctx_), *ql_max = rd(in[4], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dx = pd[0] ? in[0]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[0]) : nullptr;
+    float *g_min = pd[1] ? in[1]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[1]) : nullptr;
+    float *g_max = pd[2] ? in[2]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[2]) : nullptr;
+    nb200_check(nb200_min_max_quantize_backward_f32(x, sx.data(), (int)sx.size(), qr_min, qr_max, ql_min, ql_max,
+                                                    sq.data(), dy, this->x_min_max_, this->ema_,
+                                                    this->ste_fine_grained_, pd, ac, dx, g_min, g_max, nullptr),
+                "MinMaxQuantize backward");
+  }
 };
 
 // --------------------------------------------------------- binary affines

@@ -180,4 +180,71 @@ int nbext_forward(const char *backend, const char *op, const double *s, int n_s,
     return 1;
   }
 }
+
+// Setup + forward + Function::backward on `backend`. in_grad[i] holds the
+// initial gradient of input i and receives it after the backward; out_grad[j]
+// is the gradient arriving at output j. Host data enters and leaves through
+// CPU arrays, the device arrays are reached through the synchronizers.
+int nbext_backward(const char *backend, const char *op, const double *s, int n_s, const int32_t *iv,
+                   const int32_t *iv_len, int n_iv, nbext_tensor *in, nbext_tensor *in_grad, int n_in,
+                   nbext_tensor *out, nbext_tensor *out_grad, int n_out, const int32_t *propagate_down,
+                   const int32_t *accum) {
+  try {
+    const std::string be(backend);
+    Context ctx = be == "cpu:float" ? Context({"cpu:float"}, "CpuCachedArray", "0") : b200_context("0");
+    if (be != "cpu:float")
+      init_b200();
+    Context cpu({"cpu:float"}, "CpuCachedArray", "0");
+    std::vector<std::vector<int>> ivs;
+    const int32_t *p = iv;
+    for (int i = 0; i < n_iv; ++i) {
+      ivs.emplace_back(p, p + iv_len[i]);
+      p += iv_len[i];
+    }
+    FunctionPtr f = create(op, ctx, s, n_s, ivs);
+    std::vector<VariablePtr> vin, vout;
+    Variables pin, pout;
+    for (int i = 0; i < n_in; ++i) {
+      Shape_t sh(in[i].shape, in[i].shape + in[i].ndim);
+      vin.push_back(std::make_shared<Variable>(sh));
+      pin.push_back(vin.back().get());
+    }
+    for (int i = 0; i < n_out; ++i) {
+      vout.push_back(std::make_shared<Variable>());
+      pout.push_back(vout.back().get());
+    }
+    f->setup(pin, pout);
+    for (int i = 0; i < n_in; ++i) {
+      float *h = pin[i]->cast_data_and_get_pointer<float>(cpu, true);
+      std::memcpy(h, in[i].data, sizeof(float) * pin[i]->size());
+      float *g = pin[i]->cast_grad_and_get_pointer<float>(cpu, true);
+      std::memcpy(g, in_grad[i].data, sizeof(float) * pin[i]->size());
+    }
+    f->forward(pin, pout);
+    for (int i = 0; i < n_out; ++i) {
+      float *g = pout[i]->cast_grad_and_get_pointer<float>(cpu, true);
+      std::memcpy(g, out_grad[i].data, sizeof(float) * pout[i]->size());
+    }
+    std::vector<bool> pd(n_in), ac(n_in);
+    for (int i = 0; i < n_in; ++i) {
+      pd[i] = propagate_down[i] != 0;
+      ac[i] = accum[i] != 0;
+    }
+    f->backward(pin, pout, pd, ac);
+    for (int i = 0; i < n_in; ++i) {
+      const float *h = pin[i]->get_data_pointer<float>(cpu);
+      std::memcpy(in[i].data, h, sizeof(float) * pin[i]->size());
+      const float *g = pin[i]->get_grad_pointer<float>(cpu);
+      std::memcpy(in_grad[i].data, g, sizeof(float) * pin[i]->size());
+    }
+    for (int i = 0; i < n_out; ++i) {
+      const float *h = pout[i]->get_data_pointer<float>(cpu);
+      std::memcpy(out[i].data, h, sizeof(float) * pout[i]->size());
+    }
+    return 0;
+  } catch (const std::exception &e) {
+    g_err = e.what();
+    return 1;
+  }
+}
 }

@@ -65,3 +65,31 @@ def forward(backend, op, scalars, ivecs, inputs, n_out=1, prequant=None):
         outs.append(a)
     call(1)
     return outs, ins, name.value.decode()
+
+
+def backward(backend, op, scalars, ivecs, inputs, out_grads, propagate_down, accum, in_grads):
+    """Setup + forward + Function::backward on `backend`. Returns (in_grads_after, outputs, inputs_after)."""
+    L = lib()
+    ins = [np.ascontiguousarray(a, dtype=np.float32).copy() for a in inputs]
+    grads = [np.ascontiguousarray(g, dtype=np.float32).copy().reshape(a.shape) for a, g in zip(ins, in_grads)]
+    ogs = [np.ascontiguousarray(g, dtype=np.float32).copy() for g in out_grads]
+    outs = [np.empty(g.shape, dtype=np.float32) for g in ogs]
+    s = (ctypes.c_double * max(1, len(scalars)))(*[float(v) for v in scalars])
+    flat = [int(v) for vec in ivecs for v in vec]
+    iv = (ctypes.c_int32 * max(1, len(flat)))(*flat)
+    ivl = (ctypes.c_int32 * max(1, len(ivecs)))(*[len(v) for v in ivecs])
+
+    def tensors(arrays):
+        t = (_Tensor * len(arrays))()
+        for e, a in zip(t, arrays):
+            e.data, e.ndim = a.ctypes.data, a.ndim
+            for d, n in enumerate(a.shape):
+                e.shape[d] = n
+        return t
+    pd = (ctypes.c_int32 * len(ins))(*[int(bool(v)) for v in propagate_down])
+    ac = (ctypes.c_int32 * len(ins))(*[int(bool(v)) for v in accum])
+    rc = L.nbext_backward(backend.encode(), op.encode(), s, len(scalars), iv, ivl, len(ivecs), tensors(ins),
+                          tensors(grads), len(ins), tensors(outs), tensors(ogs), len(outs), pd, ac)
+    if rc != 0:
+        raise RuntimeError(L.nbext_last_error().decode())
+    return grads, outs, ins

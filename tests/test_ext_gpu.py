@@ -129,3 +129,52 @@ def test_errors_surface_as_exceptions():
     with pytest.raises(RuntimeError, match="not implemented|not_implemented|outside"):
         H.forward(B200, "BatchNormalization", [0.9, 1e-5, True, False, False], [(1,)],
                   [x.reshape(4, 8, 1, 1)] + [np.zeros((1, 8, 1, 1), np.float32)] * 4)
+
+
+# ---- backward passes of the quantizers through Function::backward -----------
+
+def both_backward(op, scalars, inputs, dy, pd, ac, g0):
+    c = H.backward(CPU, op, scalars, [], inputs, [dy], pd, ac, g0)
+    g = H.backward(B200, op, scalars, [], inputs, [dy], pd, ac, g0)
+    return c, g
+
+
+@pytest.mark.parametrize("sign,n,delta", cases.FXP_GRID[:4])
+@pytest.mark.parametrize("fine", [True, False])
+@pytest.mark.parametrize("accum", [False, True])
+def test_fixed_point_quantize_backward(sign, n, delta, fine, accum):
+    x = cases.fxp_backward_input(delta, n - 1 if sign else n)
+    dy, dx0 = cases.grad_inputs(x)
+    c, g = both_backward("FixedPointQuantize", [sign, n, delta, fine], [x], dy, [True], [accum], [dx0])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+
+
+@pytest.mark.parametrize("sign,with_zero,n,m", cases.POW2_GRID[::3] + [(True, True, 8, 1)])
+@pytest.mark.parametrize("fine", [True, False])
+@pytest.mark.parametrize("accum", [False, True])
+def test_pow2_quantize_backward(sign, with_zero, n, m, fine, accum):
+    x = cases.pow2_backward_input(m)
+    dy, dx0 = cases.grad_inputs(x)
+    c, g = both_backward("Pow2Quantize", [sign, with_zero, n, m, fine], [x], dy, [True], [accum], [dx0])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+
+
+@pytest.mark.parametrize("shapes,decay,x_min_max,ema", cases.MINMAX_GRID[::2])
+@pytest.mark.parametrize("fine", [True, False])
+@pytest.mark.parametrize("accum", [False, True])
+def test_min_max_quantize_backward(shapes, decay, x_min_max, ema, fine, accum):
+    ins = list(cases.minmax_inputs(*shapes))
+    dy, dx0 = cases.grad_inputs(ins[0])
+    rng = np.random.RandomState(3)
+    g0 = [dx0] + [rng.randn(*ins[1].shape).astype(np.float32) for _ in range(4)]
+    ranges = not (x_min_max or ema)
+    pd = [True, ranges, ranges, False, False]
+    c, g = both_backward("MinMaxQuantize", [decay, x_min_max, ema, fine, 0.01], ins, dy, pd, [accum] * 5, g0)
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+    per_q = ins[0].size // ins[1].size
+    tol = 1e-6 * per_q ** 0.5 * (np.abs(dy).max() + 1)
+    for k in (1, 2):
+        if ranges:
+            assert np.allclose(g[0][k], c[0][k], rtol=1e-5, atol=tol)
+        else:
+            assert np.array_equal(bits(g[0][k]), bits(c[0][k]))
