@@ -244,6 +244,32 @@ int nb200_affine_codes_i8_gather_f32(const int8_t *x_codes, const int8_t *w_code
 int nb200_affine_f32(const float *x, const float *w, const float *bias, float *y, int64_t rows, int64_t w_row,
                      int64_t w_col, void *stream);
 
+/* ---- affine backward passes ------------------------------------------------------
+ * Affine<float>::backward_impl (src/nbla/function/generic/affine.cpp:98-138)
+ * for row-major x [rows, w_row], w [w_row, w_col], dy [rows, w_col]:
+ *   dx (+)= dy . w^T,   dw (+)= x^T . dy,   db (+)= column sums of dy.
+ * A NULL dx / dw / db is not computed (propagate_down false); accum_* != 0
+ * adds to the buffer. Operands are split into bf16 pieces and accumulated in
+ * fp32 in tensor memory (error of the order of fp32 rounding). */
+int nb200_affine_backward_f32(const float *x, const float *w, const float *dy, float *dx, float *dw, float *db,
+                              int64_t rows, int64_t w_row, int64_t w_col, int accum_dx, int accum_dw, int accum_db,
+                              void *stream);
+/* BinaryWeightAffine<float>::backward_impl
+ * (src/nbla/function/generic/binary_weight_affine.cpp:124-146): the affine
+ * backward against the scaled binary weights wb * alpha, with the gradient of
+ * those weights passed straight through Sign to the float weights
+ * (include/nbla/function/sign.hpp:48-50), so dw is the gradient of inputs[1].
+ * wb / alpha are what the forward wrote. The products dy * alpha * (+-1) are
+ * the reference's own, rounding for rounding. */
+int nb200_binary_weight_affine_backward_f32(const float *x, const float *wb, const float *alpha, const float *dy,
+                                            float *dx, float *dw, float *db, int64_t rows, int64_t w_row,
+                                            int64_t w_col, int accum_dx, int accum_dw, int accum_db, void *stream);
+/* BinaryConnectAffine<float>::backward_impl
+ * (src/nbla/function/generic/binary_connect_affine.cpp:73-93). */
+int nb200_binary_connect_affine_backward_f32(const float *x, const float *wb, const float *dy, float *dx, float *dw,
+                                             float *db, int64_t rows, int64_t w_row, int64_t w_col, int accum_dx,
+                                             int accum_dw, int accum_db, void *stream);
+
 /* ---- binary-weight convolutions ------------------------------------------------ */
 
 /* BinaryWeightConvolution<float>::forward_impl

@@ -125,8 +125,8 @@ int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch
   const int64_t pair_tiles = (int64_t)((M + kPairTileM - 1) / kPairTileM) * ((N + kPairTileN - 1) / kPairTileN);
   // (the bulk stores of its epilogue need a 16-byte aligned y with a row pitch that is a multiple of 16 bytes)
   const bool y_tma_ok = (reinterpret_cast<uintptr_t>(ep.y) & 15) == 0 && (ldy % 4) == 0;
-  // (peer copies of y are written with plain stores, which only the single-CTA kernel's epilogue has)
-  if (pair_enabled && y_tma_ok && ep.n_peers == 0 && planes_b == 1 && pair_tiles >= sm_count() / 2) {
+  // (peer copies of y and accumulation into y need the plain stores of the single-CTA kernel's epilogue)
+  if (pair_enabled && y_tma_ok && ep.n_peers == 0 && !ep.accumulate && planes_b == 1 && pair_tiles >= sm_count() / 2) {
     NB_TRY(make_operand_map(&mb, B, int8, K, pitch_b, N, 1, kPairTileN / 2));
     if (int8)
       return launch_pair_gemm<true, 1, 6>(ma, mb, M, N, k_blocks, ep, ldy, st);
@@ -276,6 +276,69 @@ static int affine_fxp8(const float *xq, const float *wq, float delta_x, float de
   return run_gemm(true, 1, 1, xc, Kp, wt, Kp, (int)M, (int)N, (int)K, ep, n_total, st);
 }
 
+// Backward of y = x . W (+ b) for row-major x [M, K], W [K, N], dy [M, N]
+// (Affine::backward_impl, src/nbla/function/generic/affine.cpp:98-138):
+//   dx (+)= dy . W^T     A = dy [M][N], B = W [K][N]: both already contraction-major
+//   dW (+)= x^T . dy     A = x^T [K][M], B = dy^T [N][M]: two fp32 transposes first
+//   db (+)= column sums of dy
+// `w_exact_bf16`: W holds values that are exact in bf16 (the +-1 / zero_to
+// weights of the binary layers); it is then used as one bf16 plane and
+// `w_col_scale` (alpha, per column of W, may be NULL) is folded into dy before
+// the split, which reproduces the reference's products dy * (wb * alpha)
+// rounding for rounding. Otherwise W is split into three pieces like x.
+static int affine_backward(const float *x, const float *w, const float *w_col_scale, bool w_exact_bf16,
+                           const float *dy, float *dx, float *dw, float *db, int64_t M, int64_t K, int64_t N,
+                           int accum_dx, int accum_dw, int accum_db, cudaStream_t st) {
+  NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand (M=%lld K=%lld N=%lld)", (long long)M, (long long)K,
+           (long long)N);
+  NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
+  NB_CHECK(dy != nullptr, NB200_EVALUE, "dy is NULL");
+  if (dx) {
+    NB_CHECK(w != nullptr, NB200_EVALUE, "the gradient w.r.t. x needs the weights");
+    const int64_t Np = round_up(N, 64);
+    const int planes_w = w_exact_bf16 ? 1 : 3;
+    const size_t a_bytes = round_up((size_t)3 * M * Np * 2, 256), b_bytes = (size_t)planes_w * K * Np * 2;
+    AsyncScratch scratch(st);
+    NB_TRY(scratch.alloc(a_bytes + b_bytes));
+    uint8_t *base = static_cast<uint8_t *>(scratch.p);
+    NB_TRY(split_rows_bf16(dy, M, (int)N, Np, 3, base, st, w_col_scale));
+    NB_TRY(split_rows_bf16(w, K, (int)N, Np, planes_w, base + a_bytes, st));
+    GemmEpilogue ep{};
+    ep.y = dx;
+    ep.scale = 1.0f;
+    ep.accumulate = accum_dx;
+    NB_TRY(run_gemm(false, 3, planes_w, base, Np, base + a_bytes, Np, (int)M, (int)K, (int)N, ep, K, st));
+  }
+  if (dw) {
+    NB_CHECK(x != nullptr, NB200_EVALUE, "the gradient w.r.t. the weights needs x");
+    const int64_t Mp = round_up(M, 64);
+    const size_t xt_bytes = round_up((size_t)K * M * 4, 256), dyt_bytes = round_up((size_t)N * M * 4, 256);
+    const size_t a_bytes = round_up((size_t)3 * K * Mp * 2, 256), b_bytes = round_up((size_t)3 * N * Mp * 2, 256);
+    AsyncScratch scratch(st);
+    NB_TRY(scratch.alloc(xt_bytes + dyt_bytes + a_bytes + b_bytes));
+    uint8_t *base = static_cast<uint8_t *>(scratch.p);
+    float *xt = reinterpret_cast<float *>(base), *dyt = reinterpret_cast<float *>(base + xt_bytes);
+    uint8_t *pa = base + xt_bytes + dyt_bytes, *pb = pa + a_bytes;
+    NB_TRY(transpose_f32(x, (int)M, (int)K, xt, st));
+    NB_TRY(transpose_f32(dy, (int)M, (int)N, dyt, st));
+    NB_TRY(split_rows_bf16(xt, K, (int)M, Mp, 3, pa, st));
+    NB_TRY(split_rows_bf16(dyt, N, (int)M, Mp, 3, pb, st));
+    GemmEpilogue ep{};
+    ep.y = dw;
+    ep.scale = 1.0f;
+    ep.accumulate = accum_dw;
+    NB_TRY(run_gemm(false, 3, 3, pa, Mp, pb, Mp, (int)K, (int)N, (int)M, ep, N, st));
+  }
+  if (db) {
+    int splits = (int)((M + 255) / 256);
+    splits = splits > 64 ? 64 : splits;
+    AsyncScratch scratch(st);
+    NB_TRY(scratch.alloc((size_t)splits * N * 4));
+    NB_TRY(column_sums(dy, M, (int)N, db, accum_db, static_cast<float *>(scratch.p), splits, st));
+  }
+  return NB200_OK;
+}
+
 } // namespace nb200
 
 using namespace nb200;
@@ -359,5 +422,27 @@ int nb200_affine_f32(const float *x, const float *w, const float *bias, float *y
   ep.scale = 1.0f;
   ep.col_bias = bias;
   return run_gemm(false, 3, 3, base, Kp, base + xa, Kp, (int)M, (int)N, (int)K, ep, N, st);
+}
+
+int nb200_affine_backward_f32(const float *x, const float *w, const float *dy, float *dx, float *dw, float *db,
+                              int64_t rows, int64_t w_row, int64_t w_col, int accum_dx, int accum_dw, int accum_db,
+                              void *stream) {
+  return affine_backward(x, w, nullptr, false, dy, dx, dw, db, rows, w_row, w_col, accum_dx, accum_dw, accum_db,
+                         as_stream(stream));
+}
+
+int nb200_binary_weight_affine_backward_f32(const float *x, const float *wb, const float *alpha, const float *dy,
+                                            float *dx, float *dw, float *db, int64_t rows, int64_t w_row,
+                                            int64_t w_col, int accum_dx, int accum_dw, int accum_db, void *stream) {
+  NB_CHECK(alpha != nullptr || dx == nullptr, NB200_EVALUE, "alpha is NULL");
+  return affine_backward(x, wb, alpha, true, dy, dx, dw, db, rows, w_row, w_col, accum_dx, accum_dw, accum_db,
+                         as_stream(stream));
+}
+
+int nb200_binary_connect_affine_backward_f32(const float *x, const float *wb, const float *dy, float *dx, float *dw,
+                                             float *db, int64_t rows, int64_t w_row, int64_t w_col, int accum_dx,
+                                             int accum_dw, int accum_db, void *stream) {
+  return affine_backward(x, wb, nullptr, true, dy, dx, dw, db, rows, w_row, w_col, accum_dx, accum_dw, accum_db,
+                         as_stream(stream));
 }
 }

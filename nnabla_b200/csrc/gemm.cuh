@@ -53,6 +53,7 @@ struct GemmEpilogue {
   // collective. Plain stores only; no rank waits on another inside the kernel.
   int n_peers;
   float *peer_y[kMaxPeers];
+  int accumulate; // y += value instead of y = value (gradient accumulation); single-CTA kernel only
 };
 
 // Per-tile coordinates produced by a problem policy.
@@ -394,7 +395,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               if (ep.col_bias)
                 v = __fadd_rn(v, cb);
               if (col_ok)
-                *yp = v;
+                *yp = ep.accumulate ? __fadd_rn(*yp, v) : v;
             }
           } else {
 #pragma unroll 8
@@ -403,7 +404,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               if (ep.col_bias)
                 v = __fadd_rn(v, cb);
               if (col_ok)
-                *yp = v;
+                *yp = ep.accumulate ? __fadd_rn(*yp, v) : v;
             }
           }
         }

@@ -136,14 +136,17 @@ __device__ __forceinline__ void split3(float x, __nv_bfloat16 &h, __nv_bfloat16 
 }
 
 __global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict__ x, int64_t rows, int K, int64_t Kp,
-                                                         int planes, __nv_bfloat16 *__restrict__ out) {
+                                                         int planes, const float *__restrict__ col_scale,
+                                                         __nv_bfloat16 *__restrict__ out) {
   const int64_t total = rows * Kp;
   const int64_t plane_stride = rows * Kp;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / Kp;
     const int k = (int)(i - r * Kp);
     __nv_bfloat16 h, m, l;
-    const float v = (k < K) ? x[r * K + k] : 0.0f;
+    float v = (k < K) ? x[r * K + k] : 0.0f;
+    if (col_scale != nullptr && k < K)
+      v = __fmul_rn(v, col_scale[k]);
     split3(v, h, m, l);
     out[i] = h;
     if (planes > 1)
@@ -151,6 +154,40 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict
     if (planes > 2)
       out[2 * plane_stride + i] = l;
   }
+}
+
+// Column sums of a row-major [rows, C] matrix (bias gradient, affine.cpp:130-137):
+// block (cx, s) adds its share of the rows for 256 columns (coalesced along the
+// columns), a second kernel adds the `splits` partials of each column in order.
+__global__ void __launch_bounds__(256) column_partial_sums_kernel(const float *__restrict__ a, int64_t rows, int C,
+                                                                  float *__restrict__ partial) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= C)
+    return;
+  const int64_t per = (rows + gridDim.y - 1) / gridDim.y;
+  const int64_t r0 = blockIdx.y * per, r1 = (r0 + per < rows) ? r0 + per : rows;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int64_t r = r0;
+  for (; r + 3 < r1; r += 4) {
+    s0 += a[r * C + c];
+    s1 += a[(r + 1) * C + c];
+    s2 += a[(r + 2) * C + c];
+    s3 += a[(r + 3) * C + c];
+  }
+  for (; r < r1; ++r)
+    s0 += a[r * C + c];
+  partial[(int64_t)blockIdx.y * C + c] = (s0 + s1) + (s2 + s3);
+}
+
+__global__ void __launch_bounds__(256) column_finish_kernel(const float *__restrict__ partial, int C, int splits,
+                                                            float *__restrict__ out, int accumulate) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= C)
+    return;
+  float s = 0.f;
+  for (int k = 0; k < splits; ++k)
+    s += partial[(int64_t)k * C + c];
+  out[c] = accumulate ? __fadd_rn(out[c], s) : s;
 }
 
 // fp32 NCHW -> planes of NHWC: out[plane][n][hw][ctot], where channel c of
@@ -347,8 +384,9 @@ int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to,
   return NB200_OK;
 }
 
-int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st) {
-  split_rows_kernel<<<capped_grid(rows * Kp, 256), 256, 0, st>>>(x, rows, K, Kp, planes,
+int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st,
+                    const float *col_scale) {
+  split_rows_kernel<<<capped_grid(rows * Kp, 256), 256, 0, st>>>(x, rows, K, Kp, planes, col_scale,
                                                                  reinterpret_cast<__nv_bfloat16 *>(out));
   NB_LAUNCH_CHECK();
   return NB200_OK;
@@ -375,6 +413,16 @@ int nchw_to_nhwc_planes(const float *x, int N, int C, int HW, int groups, int Cg
     nchw_to_nhwc_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
                                                                 reinterpret_cast<__nv_bfloat16 *>(out), ps, 0.f);
   }
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+int column_sums(const float *a, int64_t rows, int C, float *out, int accumulate, float *partial, int splits,
+                cudaStream_t st) {
+  const dim3 grid((C + 255) / 256, splits);
+  column_partial_sums_kernel<<<grid, 256, 0, st>>>(a, rows, C, partial);
+  NB_LAUNCH_CHECK();
+  column_finish_kernel<<<(C + 255) / 256, 256, 0, st>>>(partial, C, splits, out, accumulate);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }

@@ -14,7 +14,12 @@ int binarize_columns(const float *w, int R, int C, float zero_to, float *wb, flo
 int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to, float *wb, float *alpha, void *side,
                   int64_t side_pitch, int c_pad, bool int8, cudaStream_t st);
 // fp32 [rows, K] -> bf16 [planes][rows][Kp] (planes = 1 or 3; hi, mid, lo).
-int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st);
+// col_scale (K floats or NULL): x[r, k] is multiplied by col_scale[k] first.
+int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st,
+                    const float *col_scale = nullptr);
+// out[c] (+)= sum over rows of a[rows, C]; partial: splits * C floats of scratch.
+int column_sums(const float *a, int64_t rows, int C, float *out, int accumulate, float *partial, int splits,
+                cudaStream_t st);
 // fp32 NCHW -> NHWC planes [planes][N][HW][ctot] (planes = 3 or 1: bf16 pieces;
 // planes = 0: int8 codes of multiples of delta). Channel c of group g is stored
 // at slot g * c_pad_g + (c - g * Cg); all other slots are zero.

@@ -298,6 +298,60 @@ def affine_from_codes(x_codes, w_codes, delta_x, delta_w, bias=None):
     return y
 
 
+def _affine_backward(entry, x, w, alpha, dy, base_axis, propagate_down, accum, grads):
+    """Shared driver of the affine backward entry points. Returns (dx, dw, db);
+    an entry whose propagate_down flag is false is returned as passed in."""
+    x, w, dy = _check_input(x), _check_input(w, "weight"), _check_input(dy, "dy")
+    rows, w_row, w_col, out_shape = _affine_dims(x, w, base_axis, None)
+    if tuple(dy.shape) != tuple(out_shape):
+        raise RuntimeError("dy must have the output's shape")
+    shapes = (x.shape, w.shape, w.shape[1:])
+    out = []
+    for g, shape, pd, ac in zip(grads, shapes, propagate_down, accum):
+        if not pd:
+            out.append(g)
+            continue
+        if g is None:
+            if ac:
+                raise RuntimeError("accum=True needs the gradient buffer to accumulate into")
+            g = torch.empty(tuple(shape), dtype=torch.float32, device=x.device)
+        elif tuple(g.shape) != tuple(shape) or g.dtype != torch.float32 or not g.is_cuda or not g.is_contiguous():
+            raise RuntimeError("gradient buffers must be contiguous float32 CUDA tensors of their input's shape")
+        out.append(g)
+    p = [C.ptr(g) if pd else ctypes.c_void_p(0) for g, pd in zip(out, propagate_down)]
+    args = [C.ptr(x), C.ptr(w)] + ([C.ptr(alpha)] if alpha is not None else []) + [C.ptr(dy)] + p + [
+        ctypes.c_int64(rows), ctypes.c_int64(w_row), ctypes.c_int64(w_col), int(bool(accum[0])), int(bool(accum[1])),
+        int(bool(accum[2])), C.stream_ptr(x.device)]
+    with torch.cuda.device(x.device):
+        C.call(entry, *args)
+    return tuple(out)
+
+
+def affine_backward(x, weight, dy, base_axis=1, propagate_down=(True, True, True), accum=(False, False, False),
+                    grads=(None, None, None)):
+    """Affine::backward_impl (src/nbla/function/generic/affine.cpp:98-138): returns (dx, dw, db)."""
+    return _affine_backward("nb200_affine_backward_f32", x, weight, None, dy, base_axis, propagate_down, accum, grads)
+
+
+def binary_weight_affine_backward(x, binary_weight, alpha, dy, base_axis=1, propagate_down=(True, True, True),
+                                  accum=(False, False, False), grads=(None, None, None)):
+    """BinaryWeightAffine::backward_impl (src/nbla/function/generic/binary_weight_affine.cpp:124-146).
+
+    binary_weight / alpha are what the forward wrote; dw is the gradient of the
+    FLOAT weights (the gradient of the scaled binary weights passes straight
+    through Sign). Returns (dx, dw, db)."""
+    alpha = _check_input(alpha, "alpha")
+    return _affine_backward("nb200_binary_weight_affine_backward_f32", x, binary_weight, alpha, dy, base_axis,
+                            propagate_down, accum, grads)
+
+
+def binary_connect_affine_backward(x, binary_weight, dy, base_axis=1, propagate_down=(True, True, True),
+                                   accum=(False, False, False), grads=(None, None, None)):
+    """BinaryConnectAffine::backward_impl (src/nbla/function/generic/binary_connect_affine.cpp:73-93)."""
+    return _affine_backward("nb200_binary_connect_affine_backward_f32", x, binary_weight, None, dy, base_axis,
+                            propagate_down, accum, grads)
+
+
 def _rank_pointers(y_ranks):
     """ctypes array of the per-rank output matrices' device addresses (tensors or plain integers)."""
     addrs = [int(y.data_ptr()) if hasattr(y, "data_ptr") else int(y) for y in y_ranks]

@@ -290,3 +290,33 @@ def min_max_quantize_backward(x, qr_min, qr_max, ql_min, ql_max, dy, x_min_max=F
     if rc != 0:
         raise ValueError("oracle_min_max_quantize_backward: bad shapes")
     return gx, gmin, gmax
+
+
+def affine_backward(x, w, dy, base_axis=1, propagate_down=(True, True, True), accum=(False, False, False),
+                    grads=(None, None, None), f64=False):
+    """Affine::backward_impl (affine.cpp:98-138). Returns (dx, dw, db); entries
+    whose propagate_down flag is false come back as the initial buffers."""
+    x, w, dy = _f(x), _f(w), _f(dy)
+    M = int(np.prod(x.shape[:base_axis]))
+    K = x.size // M
+    N = w.size // w.shape[0]
+    shapes = (x.shape, w.shape, w.shape[1:])
+    g = [np.zeros(s, np.float32) if b is None else _f(b).copy().reshape(s) for s, b in zip(shapes, grads)]
+    lib().oracle_affine_backward(_p(x), _p(w), _p(dy), _p(g[0]) if propagate_down[0] else None,
+                                 _p(g[1]) if propagate_down[1] else None, _p(g[2]) if propagate_down[2] else None,
+                                 ctypes.c_int64(M), ctypes.c_int64(K), ctypes.c_int64(N), int(accum[0]),
+                                 int(accum[1]), int(accum[2]), int(f64))
+    return tuple(g)
+
+
+def binary_weight_affine_backward(x, w, dy, base_axis=1, quantize_zero_to=1.0, **kw):
+    """binary_weight_affine.cpp:124-146: affine backward against wb * alpha; the
+    weight gradient passes straight through Sign to the float weights."""
+    w = _f(w)
+    _, _, sc = binarize_columns(w.reshape(w.shape[0], -1), quantize_zero_to)
+    return affine_backward(x, sc.reshape(w.shape), dy, base_axis, **kw)
+
+
+def binary_connect_affine_backward(x, w, dy, base_axis=1, quantize_zero_to=1.0, **kw):
+    """binary_connect_affine.cpp:73-93."""
+    return affine_backward(x, sign(_f(w), quantize_zero_to), dy, base_axis, **kw)

@@ -1,14 +1,16 @@
-/* CPU restatement of the reference's quantizer backward passes (straight-
- * through estimators), in plain C, one function per reference loop.
+/* CPU restatement of the reference's backward passes on the quantized-layer
+ * path (the quantizers' straight-through estimators and the affine backward
+ * the binary layers call), in plain C, one function per reference loop.
  *
  * TEST INFRASTRUCTURE ONLY: the checker the CUDA path is compared against.
  * The product library never links or calls it.
  *
  * Parity status: PINNED against the reference's own compiled C++
  * (oracle/_ref/libnnabla_ref.so, Function::backward) by
- * tests/test_oracle_vs_reference.py: bit for bit for the input gradients; the
- * two range gradients of MinMaxQuantize are fp32 sums whose order inside the
- * reference comes from Eigen (absent), so they are pinned to rounding only.
+ * tests/test_oracle_backward_vs_reference.py: bit for bit for the input gradients; the
+ * two range gradients of MinMaxQuantize and the affine backward are fp32 sums
+ * whose order inside the reference comes from Eigen (absent), so they are
+ * pinned to rounding only.
  *
  * Build: gcc -O2 -fno-fast-math -ffp-contract=off, like oracle_quant.c.
  */
@@ -155,4 +157,51 @@ int oracle_min_max_quantize_backward(const float *x, const int64_t *xs, int nd,
   free(smin);
   free(smax);
   return 0;
+}
+
+/* src/nbla/function/generic/affine.cpp:98-138 for row-major x [M,K], w [K,N],
+ * dy [M,N]: dx (+)= dy . w^T, dw (+)= x^T . dy, db (+)= column sums of dy. A
+ * NULL dx / dw / db is skipped. Each product is summed completely (fp32, or
+ * double when f64 != 0 — the error yardstick) before it is added to the
+ * buffer, like the reference's `mdx += mdy * mw.transpose()`. Summation order
+ * inside the reference is Eigen's (absent): pinned to rounding only. */
+void oracle_affine_backward(const float *x, const float *w, const float *dy,
+                            float *dx, float *dw, float *db, int64_t M,
+                            int64_t K, int64_t N, int accum_dx, int accum_dw,
+                            int accum_db, int f64) {
+  if (dx)
+    for (int64_t i = 0; i < M; ++i)
+      for (int64_t k = 0; k < K; ++k) {
+        float s = 0.f;
+        double d = 0.;
+        for (int64_t j = 0; j < N; ++j) {
+          s += dy[i * N + j] * w[k * N + j];
+          d += (double)dy[i * N + j] * (double)w[k * N + j];
+        }
+        float v = f64 ? (float)d : s;
+        dx[i * K + k] = accum_dx ? dx[i * K + k] + v : v;
+      }
+  if (dw)
+    for (int64_t k = 0; k < K; ++k)
+      for (int64_t j = 0; j < N; ++j) {
+        float s = 0.f;
+        double d = 0.;
+        for (int64_t i = 0; i < M; ++i) {
+          s += x[i * K + k] * dy[i * N + j];
+          d += (double)x[i * K + k] * (double)dy[i * N + j];
+        }
+        float v = f64 ? (float)d : s;
+        dw[k * N + j] = accum_dw ? dw[k * N + j] + v : v;
+      }
+  if (db)
+    for (int64_t j = 0; j < N; ++j) {
+      float s = 0.f;
+      double d = 0.;
+      for (int64_t i = 0; i < M; ++i) {
+        s += dy[i * N + j];
+        d += (double)dy[i * N + j];
+      }
+      float v = f64 ? (float)d : s;
+      db[j] = accum_db ? db[j] + v : v;
+    }
 }

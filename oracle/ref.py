@@ -239,3 +239,38 @@ def min_max_quantize_backward(x, qr_min, qr_max, ql_min, ql_max, dy, decay=0.999
     g, _, _ = backward("MinMaxQuantize", [decay, x_min_max, ema, ste_fine_grained, eps], [],
                        [x, qr_min, qr_max, ql_min, ql_max], [dy], pd, ac, list(grads) + [None, None])
     return g[0], g[1], g[2]
+
+
+def affine_backward(x, w, b, dy, base_axis=1, propagate_down=(True, True, True), accum=(False, False, False),
+                    grads=(None, None, None)):
+    """Returns (dx, dw, db) from Affine::backward (b may be None)."""
+    ins = [x, w] + ([b] if b is not None else [])
+    n = len(ins)
+    g, _, _ = backward("Affine", [base_axis], [], ins, [dy], list(propagate_down)[:n], list(accum)[:n],
+                       list(grads)[:n])
+    return tuple(g) + (None,) * (3 - n)
+
+
+def binary_weight_affine_backward(x, w, b, dy, base_axis=1, quantize_zero_to=1.0, propagate_down=(True, True, True),
+                                  accum=(False, False, False), grads=(None, None, None)):
+    """Returns (dx, dw, db) from BinaryWeightAffine::backward; inputs are [x, w, wb, alpha, b?]."""
+    wb = np.zeros_like(w, dtype=np.float32)
+    alpha = np.zeros(int(np.prod(w.shape[1:])), dtype=np.float32)
+    ins = [x, w, wb, alpha] + ([b] if b is not None else [])
+    pd = [propagate_down[0], propagate_down[1], False, False] + ([propagate_down[2]] if b is not None else [])
+    ac = [accum[0], accum[1], False, False] + ([accum[2]] if b is not None else [])
+    g0 = [grads[0], grads[1], None, None] + ([grads[2]] if b is not None else [])
+    g, _, _ = backward("BinaryWeightAffine", [base_axis, quantize_zero_to], [], ins, [dy], pd, ac, g0)
+    return g[0], g[1], (g[4] if b is not None else None)
+
+
+def binary_connect_affine_backward(x, w, b, dy, base_axis=1, quantize_zero_to=1.0, propagate_down=(True, True, True),
+                                   accum=(False, False, False), grads=(None, None, None)):
+    """Returns (dx, dw, db) from BinaryConnectAffine::backward; inputs are [x, w, wb, b?]."""
+    wb = np.zeros_like(w, dtype=np.float32)
+    ins = [x, w, wb] + ([b] if b is not None else [])
+    pd = [propagate_down[0], propagate_down[1], False] + ([propagate_down[2]] if b is not None else [])
+    ac = [accum[0], accum[1], False] + ([accum[2]] if b is not None else [])
+    g0 = [grads[0], grads[1], None] + ([grads[2]] if b is not None else [])
+    g, _, _ = backward("BinaryConnectAffine", [base_axis, quantize_zero_to], [], ins, [dy], pd, ac, g0)
+    return g[0], g[1], (g[3] if b is not None else None)

@@ -68,3 +68,41 @@ def test_min_max_quantize_backward(shapes, decay, x_min_max, ema, fine, accum):
         assert np.allclose(ggmax, wgmax, rtol=1e-5, atol=tol)
     else:
         assert np.array_equal(bits(ggmin), bits(g0[1])) and np.array_equal(bits(ggmax), bits(g0[2]))
+
+
+def affine_grad_case(xs, ws, base_axis):
+    x, w, b = cases.affine_inputs(xs, ws, with_zeros=True)
+    rng = np.random.RandomState(1)
+    dy = rng.randn(*(tuple(xs[:base_axis]) + tuple(ws[1:]))).astype(np.float32)
+    g0 = [rng.randn(*xs).astype(np.float32), rng.randn(*ws).astype(np.float32),
+          rng.randn(*ws[1:]).astype(np.float32)]
+    return x, w, b, dy, g0
+
+
+@pytest.mark.parametrize("xs,ws,base_axis", cases.AFFINE_CASES)
+@pytest.mark.parametrize("accum", [False, True])
+def test_affine_backward_family(xs, ws, base_axis, accum):
+    x, w, b, dy, g0 = affine_grad_case(xs, ws, base_axis)
+    ac = (accum,) * 3
+    pairs = [
+        (ref.affine_backward(x, w, b, dy, base_axis, accum=ac, grads=g0),
+         oracle.affine_backward(x, w, dy, base_axis, accum=ac, grads=g0)),
+        (ref.binary_weight_affine_backward(x, w, b, dy, base_axis, 1.0, accum=ac, grads=g0),
+         oracle.binary_weight_affine_backward(x, w, dy, base_axis, 1.0, accum=ac, grads=g0)),
+        (ref.binary_connect_affine_backward(x, w, b, dy, base_axis, 0.0, accum=ac, grads=g0),
+         oracle.binary_connect_affine_backward(x, w, dy, base_axis, 0.0, accum=ac, grads=g0)),
+    ]
+    for want, got in pairs:
+        for a, c in zip(got, want):
+            assert cases.rel_rms(a, c) < 1e-6
+
+
+def test_binary_weight_affine_backward_without_bias_and_partial_propagation():
+    xs, ws, base_axis = cases.AFFINE_CASES[2]
+    x, w, _, dy, g0 = affine_grad_case(xs, ws, base_axis)
+    want = ref.binary_weight_affine_backward(x, w, None, dy, base_axis, 1.0, propagate_down=(True, False, False),
+                                             grads=g0)
+    got = oracle.binary_weight_affine_backward(x, w, dy, base_axis, 1.0, propagate_down=(True, False, False),
+                                               grads=g0)
+    assert cases.rel_rms(got[0], want[0]) < 1e-6
+    assert np.array_equal(got[1], g0[1]) and np.array_equal(want[1], g0[1])  # weight gradient untouched
