@@ -56,6 +56,10 @@ void enter(const Context &ctx) {
   }
 
 const float *rd(Variable *v, const Context &ctx) { return v->get_data_pointer<float>(ctx); }
+// Gradient buffer of an input for backward: NULL when nothing propagates to it.
+float *grad_wr(Variable *v, const Context &ctx, bool propagate, bool accum) {
+  return propagate ? v->cast_grad_and_get_pointer<float>(ctx, !accum) : nullptr;
+}
 float *wr(Variable *v, const Context &ctx, bool write_only = true) {
   return v->cast_data_and_get_pointer<float>(ctx, write_only);
 }
@@ -296,7 +300,21 @@ protected:
                                                this->quantize_zero_to_, nullptr),
                 "BinaryWeightAffine");
   }
-  B200_NO_BACKWARD("BinaryWeightAffine")
+  // binary_weight_affine.cpp:124-146; inputs [x, w, wb, alpha, b?]
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    const bool has_b = in.size() == 5;
+    if (!(pd[0] || pd[1] || (has_b && pd[4])))
+      return;
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_), *alpha = rd(in[3], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]), *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
+    float *db = has_b ? grad_wr(in[4], this->ctx_, pd[4], accum[4]) : nullptr;
+    nb200_check(nb200_binary_weight_affine_backward_f32(x, wb, alpha, dy, dx, dw, db, rows_, this->w_row_,
+                                                        this->w_col_, accum[0], accum[1], has_b && accum[4], nullptr),
+                "BinaryWeightAffine backward");
+  }
 };
 
 template <typename T> class BinaryConnectAffineB200 : public BinaryConnectAffine<T> {
@@ -321,7 +339,32 @@ protected:
                                                 nullptr),
                 "BinaryConnectAffine");
   }
-  B200_NO_BACKWARD("BinaryConnectAffine")
+  // binary_connect_affine.cpp:73-93; inputs [x, w, wb, b?]
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    const bool has_b = in.size() == 4;
+    if (!(pd[0] || pd[1] || (has_b && pd[3])))
+      return;
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]);
+    // Like the reference, the weight gradient is first written to the gradient of the BINARY weights
+    // (inputs[2], overwritten) and from there passed through Sign to the float weights' gradient.
+    float *dwb = grad_wr(in[2], this->ctx_, pd[1], false);
+    float *db = has_b ? grad_wr(in[3], this->ctx_, pd[3], accum[3]) : nullptr;
+    nb200_check(nb200_binary_connect_affine_backward_f32(x, wb, dy, dx, dwb, db, d_.rows, d_.w_row, d_.w_col, accum[0],
+                                                         0, has_b && accum[3], nullptr),
+                "BinaryConnectAffine backward");
+    if (pd[1]) {
+      float *dw = grad_wr(in[1], this->ctx_, true, accum[1]);
+      const size_t n = in[1]->size();
+      if (accum[1])
+        nb200_check(nb200_add2_f32(dw, dwb, dw, n, nullptr), "BinaryConnectAffine backward (accumulate)");
+      else
+        nb200_check(nb200_memcpy_d2d(dw, dwb, n * sizeof(float), nullptr), "BinaryConnectAffine backward (copy)");
+    }
+  }
 };
 
 // ---------------------------------------------------- binary convolutions
@@ -412,7 +455,21 @@ protected:
     else
       nb200_check(nb200_affine_f32(x, w, b, y, d_.rows, d_.w_row, d_.w_col, nullptr), "Affine");
   }
-  B200_NO_BACKWARD("Affine")
+  // affine.cpp:98-138; inputs [x, w, b?]
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    const bool has_b = in.size() == 3;
+    if (!(pd[0] || pd[1] || (has_b && pd[2])))
+      return;
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]), *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
+    float *db = has_b ? grad_wr(in[2], this->ctx_, pd[2], accum[2]) : nullptr;
+    nb200_check(nb200_affine_backward_f32(x, w, dy, dx, dw, db, d_.rows, d_.w_row, d_.w_col, accum[0], accum[1],
+                                          has_b && accum[2], nullptr),
+                "Affine backward");
+  }
 };
 
 template <typename T> class ConvolutionB200 : public Convolution<T> {

@@ -178,3 +178,28 @@ def test_min_max_quantize_backward(shapes, decay, x_min_max, ema, fine, accum):
             assert np.allclose(g[0][k], c[0][k], rtol=1e-5, atol=tol)
         else:
             assert np.array_equal(bits(g[0][k]), bits(c[0][k]))
+
+
+@pytest.mark.parametrize("xs,ws,base_axis", cases.AFFINE_CASES)
+@pytest.mark.parametrize("accum", [False, True])
+def test_affine_family_backward(xs, ws, base_axis, accum):
+    x, w, b = cases.affine_inputs(xs, ws, with_zeros=True)
+    rng = np.random.RandomState(1)
+    dy = rng.randn(*(tuple(xs[:base_axis]) + tuple(ws[1:]))).astype(np.float32)
+    gx, gw, gb = (rng.randn(*s).astype(np.float32) for s in (xs, ws, ws[1:]))
+    wb, alpha = np.zeros_like(w), np.zeros(int(np.prod(ws[1:])), np.float32)
+    runs = [
+        ("Affine", [base_axis], [x, w, b], [True, True, True], [gx, gw, gb]),
+        ("BinaryWeightAffine", [base_axis, 1.0], [x, w, wb, alpha, b], [True, True, False, False, True],
+         [gx, gw, wb, alpha, gb]),
+        ("BinaryConnectAffine", [base_axis, 0.0], [x, w, wb, b], [True, True, False, True], [gx, gw, wb, gb]),
+    ]
+    for op, scalars, ins, pd, g0 in runs:
+        c = H.backward(CPU, op, scalars, [], ins, [dy], pd, [accum] * len(ins), g0)
+        g = H.backward(B200, op, scalars, [], ins, [dy], pd, [accum] * len(ins), g0)
+        for i, p in enumerate(pd):
+            # (the reference leaves the weight gradient in the BINARY weights' gradient too, binary_connect_affine.cpp:77-92)
+            if p or (op == "BinaryConnectAffine" and i == 2):
+                assert cases.rel_rms(g[0][i], c[0][i]) < 1e-5, (op, i)
+            else:
+                assert np.array_equal(bits(g[0][i]), bits(c[0][i])), (op, i)
