@@ -157,6 +157,32 @@ int nb200_min_max_quantize_f32_noalloc(const float *x, const int64_t *x_shape, i
 int nb200_min_max_quantize_f32_host(const float *x, size_t size, float *qr_min, float *qr_max, const float *ql_min,
                                     const float *ql_max, float eps, float *y);
 
+/* ---- binary convolution backward passes ------------------------------------------
+ * Convolution<float>::backward_impl
+ * (src/nbla/function/generic/convolution.cpp:199-300) as the binary layers
+ * call it (binary_weight_convolution.cpp:119-146 with wb * alpha,
+ * binary_connect_convolution.cpp:82-104 with wb), geometry as in the forward:
+ *   dx (+)= transposed convolution of dy with the weights,
+ *   dw (+)= correlation of x with dy (the gradient of the FLOAT weights: it
+ *           passes straight through Sign),
+ *   db (+)= sums of dy over batch and pixels.
+ * NULL dx / dw / db is not computed. wb / alpha are what the forward wrote.
+ * activation_delta > 0 declares x to hold multiples of that step with codes
+ * in [-127, 127] (then x is exact in one bf16 piece). Both gradients run on
+ * the forward's implicit-GEMM tensor-core kernel. */
+int nb200_binary_weight_convolution_backward_f32(const float *x, const float *wb, const float *alpha, const float *dy,
+                                                 float *dx, float *dw, float *db, int batch, int channels, int height,
+                                                 int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                                 int pad_w, int stride_h, int stride_w, int dilation_h,
+                                                 int dilation_w, int group, int accum_dx, int accum_dw, int accum_db,
+                                                 float activation_delta, void *stream);
+int nb200_binary_connect_convolution_backward_f32(const float *x, const float *wb, const float *dy, float *dx,
+                                                  float *dw, float *db, int batch, int channels, int height,
+                                                  int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                                  int pad_w, int stride_h, int stride_w, int dilation_h,
+                                                  int dilation_w, int group, int accum_dx, int accum_dw,
+                                                  int accum_db, float activation_delta, void *stream);
+
 /* ---- quantizer backward passes (straight-through estimators) -------------------
  * dx (+)= gradient for n elements; accum != 0 adds to dx (elements that pass no
  * gradient are left untouched), accum == 0 overwrites (zero where blocked),

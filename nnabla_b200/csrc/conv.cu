@@ -77,14 +77,14 @@ void plan_box(const ConvGeometry &g, int bn_max, int &h_box, int &n_box) {
   h_box = best;
 }
 
-template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes>
+template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes, bool kSkip = false>
 int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ctot, const void *wside, int64_t wpitch,
                 int c_pad_g, int cblocks, int h_box, int n_box, const GemmEpilogue &ep, cudaStream_t st) {
   const int es = kInt8 ? 1 : 2;
   const int E = RB / es;
   CUtensorMap ma, mb;
-  // weights: (K, Ko, 1)
-  NB_TRY(make_operand_map(&ma, wside, kInt8, wpitch, wpitch, g.Ko, 1, kTileM, RB));
+  // weights: (K, Ko, planes)
+  NB_TRY(make_operand_map(&ma, wside, kInt8, wpitch, wpitch, g.Ko, PA, kTileM, RB));
   // activations: (C, W, H, N, planes); the box walks W and H with the convolution stride
   const uint64_t dims[5] = {(uint64_t)ctot, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N, (uint64_t)planes_b};
   const uint64_t strides[4] = {(uint64_t)ctot * es, (uint64_t)ctot * es * g.W, (uint64_t)ctot * es * g.W * g.H,
@@ -94,6 +94,7 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
   NB_TRY(encode_tiled(&mb, kInt8 ? 1 : 0, 5, act, dims, strides, box, estr, RB));
   ConvProblem p;
   p.row_bytes = RB;
+  p.chunk_blocks = kInt8 ? 0 : k_chunk_blocks((kSkip ? 6 : PA * PB) * (RB / 32));
   p.Nimg = g.N;
   p.Ko = g.Ko;
   p.Kog = g.Kog;
@@ -118,7 +119,7 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
   p.pixels = n_box * h_box * g.Wo;
   p.n_run = (int)round_up(p.pixels, 16);
   const int tiles = p.groups * p.m_tiles_g * p.tiles_h * p.tiles_n;
-  return launch_contraction<kInt8, PA, PB, BN, STAGES, false, ConvProblem, RB>(ma, mb, p, tiles, ep, st);
+  return launch_contraction<kInt8, PA, PB, BN, STAGES, kSkip, ConvProblem, RB>(ma, mb, p, tiles, ep, st);
 }
 
 // Shared body of BinaryWeightConvolution / BinaryConnectConvolution forward.
@@ -193,6 +194,149 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   return launch_conv<false, 1, 3, 128, 3>(g, act, 3, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
 }
 
+// ---------------------------------------------------------------------------
+// Backward (Convolution::backward_impl, src/nbla/function/generic/convolution.cpp:199-300,
+// called by the binary convolutions with their binarised weights,
+// binary_weight_convolution.cpp:119-146, binary_connect_convolution.cpp:82-104).
+// Both gradients run on the forward's implicit-GEMM kernel:
+//
+//  dx = convolution of dy (each map scaled by alpha, pixels spread by the
+//       forward stride over a zeroed grid) with the flipped, transposed +-1
+//       weights: stride 1, same dilation, padding d * (k - 1) - p.
+//  dW[o, c, ky, kx] = sum over (n, oy, ox) of dy[n, o, oy, ox] * x[n, c, oy*s - p + ky*d, ox*s - p + kx*d]
+//       = a convolution whose "images" are the input channels, whose channel
+//       axis is the batch, whose filter is dy^T (kernel size Ho x Wo) and whose
+//       stride / dilation are the forward's dilation / stride; its Ho' x Wo'
+//       output is the kh x kw filter window. One launch per group.
+//  db = sums of dy over batch and pixels.
+// ---------------------------------------------------------------------------
+int conv_input_grad(const float *wb, const float *alpha, const float *dy, float *dx, const ConvGeometry &g,
+                    int accum, cudaStream_t st) {
+  // geometry of the equivalent forward convolution
+  ConvGeometry b = g;
+  b.C = g.Ko;
+  b.Ko = g.C;
+  b.Cg = g.Kog;
+  b.Kog = g.Cg;
+  b.H = g.H + 2 * g.ph - g.dh * (g.kh - 1); // stuffed dy grid, padded so that the output is exactly H x W
+  b.W = g.W + 2 * g.pw - g.dw * (g.kw - 1);
+  b.sh = b.sw = 1;
+  b.ph = g.dh * (g.kh - 1) - g.ph;
+  b.pw = g.dw * (g.kw - 1) - g.pw;
+  b.Ho = g.H;
+  b.Wo = g.W;
+  NB_CHECK(b.Wo <= 128, NB200_ENOTIMPL, "input gradient for images wider than 128 pixels (W=%d) is not supported",
+           b.Wo);
+  const int k_pad_g = (int)round_up(b.Cg, 16);
+  const bool narrow_rows = k_pad_g * 2 <= 64;
+  const int E = (narrow_rows ? 64 : kRowBytes) / 2;
+  const int cblocks = (k_pad_g + E - 1) / E;
+  const int k_slots = cblocks * E;
+  int64_t ctot = (int64_t)g.group * k_pad_g;
+  if (ctot < E)
+    ctot = E;
+  const int taps = g.kh * g.kw;
+  const int64_t wpitch = (int64_t)taps * k_slots;
+  const size_t act_bytes = (size_t)3 * g.N * b.H * b.W * ctot * 2;
+  const size_t side_bytes = (size_t)g.C * wpitch * 2;
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc(round_up(act_bytes, 1024) + round_up(side_bytes, 1024)));
+  uint8_t *act = static_cast<uint8_t *>(scratch.p);
+  uint8_t *side = act + round_up(act_bytes, 1024);
+  NB_CUDA(cudaMemsetAsync(act, 0, round_up(act_bytes, 1024) + side_bytes, st));
+  NB_TRY(dy_to_nhwc_stuffed(dy, g.N, g.Ko, g.Ho, g.Wo, g.group, g.Kog, k_pad_g, (int)ctot, b.H, b.W, g.sh, g.sw, alpha,
+                            act, st));
+  NB_TRY(flip_transpose_weights(wb, g.Ko, g.Cg, g.kh, g.kw, g.group, k_slots, side, st));
+  GemmEpilogue ep{};
+  ep.y = dx;
+  ep.scale = 1.0f;
+  ep.accumulate = accum;
+  int h_box, n_box;
+  plan_box(b, 128, h_box, n_box);
+  if (narrow_rows)
+    return launch_conv<false, 1, 3, 128, 6, 64>(b, act, 3, ctot, side, wpitch, k_pad_g, cblocks, h_box, n_box, ep, st);
+  return launch_conv<false, 1, 3, 128, 3>(b, act, 3, ctot, side, wpitch, k_pad_g, cblocks, h_box, n_box, ep, st);
+}
+
+int conv_weight_grad(const float *x, const float *dy, float *dw, const ConvGeometry &g, int accum, float act_delta,
+                     cudaStream_t st) {
+  NB_CHECK(g.kw * g.dw <= 256 && g.kh * g.kw <= 64, NB200_ENOTIMPL,
+           "weight gradient for a %d x %d filter (dilation %d) is not supported", g.kh, g.kw, g.dw);
+  NB_CHECK((int64_t)g.Ho * g.Wo <= (1 << 20), NB200_ENOTIMPL, "output maps larger than 2^20 pixels");
+  // activations that are multiples of act_delta with |code| <= 127 are exact in one bf16 piece
+  const int planes_x = act_delta > 0.0f ? 1 : 3;
+  const int E = kRowBytes / 2;
+  const int Np = (int)round_up(g.N, E);
+  const int cblocks = Np / E;
+  const int taps_f = g.Ho * g.Wo;          // filter taps of the equivalent convolution
+  const int taps_w = g.kh * g.kw;          // its output pixels per image
+  const int64_t wpitch = (int64_t)taps_f * Np;
+  const int64_t Rx = (int64_t)g.Cg * g.H * g.W, Rdy = (int64_t)g.Kog * taps_f;
+  const size_t x_bytes = round_up((size_t)planes_x * Rx * Np * 2, 1024);
+  const size_t dy_bytes = round_up((size_t)3 * Rdy * Np * 2, 1024);
+  const size_t out_bytes = round_up((size_t)g.Cg * g.Kog * taps_w * 4, 1024);
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc(x_bytes + dy_bytes + out_bytes));
+  uint8_t *xt = static_cast<uint8_t *>(scratch.p);
+  uint8_t *dyt = xt + x_bytes;
+  float *staged = reinterpret_cast<float *>(dyt + dy_bytes);
+  ConvGeometry b = g;
+  b.N = g.Cg;   // images = input channels of the group
+  b.C = g.N;    // channel axis = batch
+  b.Cg = g.N;
+  b.Ko = g.Kog; // output maps = maps of the group
+  b.Kog = g.Kog;
+  b.group = 1;
+  b.kh = g.Ho;
+  b.kw = g.Wo;
+  b.sh = g.dh;
+  b.sw = g.dw;
+  b.dh = g.sh;
+  b.dw = g.sw;
+  b.Ho = g.kh;
+  b.Wo = g.kw;
+  int h_box, n_box;
+  plan_box(b, 64, h_box, n_box);
+  for (int grp = 0; grp < g.group; ++grp) {
+    if (g.N != Np)
+      NB_CUDA(cudaMemsetAsync(xt, 0, x_bytes + dy_bytes, st));
+    NB_TRY(batch_to_inner(x + (int64_t)grp * Rx, g.N, Rx, (int64_t)g.C * g.H * g.W, Np, planes_x, xt, st));
+    NB_TRY(batch_to_inner(dy + (int64_t)grp * Rdy, g.N, Rdy, (int64_t)g.Ko * taps_f, Np, 3, dyt, st));
+    GemmEpilogue ep{};
+    ep.y = staged;
+    ep.scale = 1.0f;
+    if (planes_x == 3)
+      NB_TRY((launch_conv<false, 3, 3, 64, 2, kRowBytes, true>(b, xt, 3, Np, dyt, wpitch, Np, cblocks, h_box, n_box, ep,
+                                                               st)));
+    else
+      NB_TRY((launch_conv<false, 3, 1, 64, 3>(b, xt, 1, Np, dyt, wpitch, Np, cblocks, h_box, n_box, ep, st)));
+    NB_TRY(permute_weight_grad(staged, g.Cg, g.Kog, taps_w, dw + (int64_t)grp * g.Kog * g.Cg * taps_w, accum, st));
+  }
+  return NB200_OK;
+}
+
+int convolution_backward(const float *x, const float *w_exact, const float *alpha, const float *dy, float *dx,
+                         float *dw, float *db, ConvGeometry g, int accum_dx, int accum_dw, int accum_db,
+                         float act_delta, cudaStream_t st) {
+  NB_TRY(check_geometry(g));
+  NB_CHECK(dy != nullptr, NB200_EVALUE, "dy is NULL");
+  if (dx) {
+    NB_CHECK(w_exact != nullptr, NB200_EVALUE, "the gradient w.r.t. x needs the binary weights");
+    NB_TRY(conv_input_grad(w_exact, alpha, dy, dx, g, accum_dx, st));
+  }
+  if (dw) {
+    NB_CHECK(x != nullptr, NB200_EVALUE, "the gradient w.r.t. the weights needs x");
+    NB_TRY(conv_weight_grad(x, dy, dw, g, accum_dw, act_delta, st));
+  }
+  if (db) {
+    int splits = g.N < 32 ? g.N : 32;
+    AsyncScratch scratch(st);
+    NB_TRY(scratch.alloc((size_t)splits * g.Ko * 4));
+    NB_TRY(channel_sums(dy, g.N, g.Ko, g.Ho * g.Wo, db, accum_db, static_cast<float *>(scratch.p), splits, st));
+  }
+  return NB200_OK;
+}
+
 } // namespace
 } // namespace nb200
 
@@ -219,5 +363,30 @@ int nb200_binary_connect_convolution_f32(const float *x, const float *w, float *
   ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
                  dilation_h, dilation_w, group, 0, 0, 0, 0};
   return binary_convolution(x, w, wb, nullptr, bias, y, g, quantize_zero_to, activation_delta, as_stream(stream));
+}
+
+int nb200_binary_weight_convolution_backward_f32(const float *x, const float *wb, const float *alpha, const float *dy,
+                                                 float *dx, float *dw, float *db, int batch, int channels, int height,
+                                                 int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                                 int pad_w, int stride_h, int stride_w, int dilation_h,
+                                                 int dilation_w, int group, int accum_dx, int accum_dw, int accum_db,
+                                                 float activation_delta, void *stream) {
+  NB_CHECK(alpha != nullptr || dx == nullptr, NB200_EVALUE, "alpha is NULL");
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, group, 0, 0, 0, 0};
+  return convolution_backward(x, wb, alpha, dy, dx, dw, db, g, accum_dx, accum_dw, accum_db, activation_delta,
+                              as_stream(stream));
+}
+
+int nb200_binary_connect_convolution_backward_f32(const float *x, const float *wb, const float *dy, float *dx,
+                                                  float *dw, float *db, int batch, int channels, int height,
+                                                  int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                                  int pad_w, int stride_h, int stride_w, int dilation_h,
+                                                  int dilation_w, int group, int accum_dx, int accum_dw,
+                                                  int accum_db, float activation_delta, void *stream) {
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, group, 0, 0, 0, 0};
+  return convolution_backward(x, wb, nullptr, dy, dx, dw, db, g, accum_dx, accum_dw, accum_db, activation_delta,
+                              as_stream(stream));
 }
 }

@@ -100,6 +100,7 @@ static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, int M, int 
   prob.n_tiles = (N + BN - 1) / BN;
   prob.bn = BN;
   prob.row_bytes = kRowBytes;
+  prob.chunk_blocks = kInt8 ? 0 : k_chunk_blocks((kSkip ? 6 : PA * PB) * 4);
   prob.ldy = ldy;
   return launch_contraction<kInt8, PA, PB, BN, STAGES, kSkip, GemmProblem>(ma, mb, prob, prob.m_tiles * prob.n_tiles,
                                                                            ep, st);

@@ -32,4 +32,22 @@ int transpose_f32(const float *src, int R, int C, float *dst, cudaStream_t st);
 // fp32 multiples of delta [rows, K] -> int8 [rows][pitch].
 int codes_rows_i8(const float *x, int64_t rows, int K, int64_t pitch, float delta, int8_t *out, cudaStream_t st);
 
+// ---- convolution backward (prepare_backward.cu) ------------------------------
+// dy [N][Ko][Ho][Wo] -> 3 bf16 planes [N][Hs][Ws][ctot] (pre-zeroed by the caller):
+// pixel (oy, ox) at (oy * sh, ox * sw), map o of group g at slot g * k_pad_g + o - g * Kog,
+// multiplied by chan_scale[o] first when given.
+int dy_to_nhwc_stuffed(const float *dy, int N, int Ko, int Ho, int Wo, int groups, int Kog, int k_pad_g, int ctot,
+                       int Hs, int Ws, int sh, int sw, const float *chan_scale, void *out, cudaStream_t st);
+// wb [Ko][Cg][kh][kw] -> side [C][kh * kw][k_slots] bf16 (pre-zeroed), taps flipped, maps innermost.
+int flip_transpose_weights(const float *wb, int Ko, int Cg, int kh, int kw, int groups, int k_slots, void *side,
+                           cudaStream_t st);
+// N rows of R fp32 values (rows src_row_stride apart) -> bf16 [planes][R][Np] (pre-zeroed), batch innermost.
+int batch_to_inner(const float *src, int N, int64_t R, int64_t src_row_stride, int Np, int planes, void *out,
+                   cudaStream_t st);
+// out[o] (+)= sum over n and pixels of dy [N][Ko][HW]; partial: splits * Ko floats.
+int channel_sums(const float *dy, int N, int Ko, int HW, float *out, int accumulate, float *partial, int splits,
+                 cudaStream_t st);
+// staged [Cg][Kog][taps] -> dw [Kog][Cg][taps] (overwrite or add).
+int permute_weight_grad(const float *staged, int Cg, int Kog, int taps, float *dw, int accumulate, cudaStream_t st);
+
 } // namespace nb200

@@ -493,6 +493,59 @@ def binary_connect_convolution(x, weight, binary_weight, bias=None, base_axis=1,
                                base_axis, pad, stride, dilation, group, quantize_zero_to, outputs, fixed_point_delta)
 
 
+def _binary_convolution_backward(entry, x, binary_weight, alpha, dy, base_axis, pad, stride, dilation, group,
+                                 propagate_down, accum, grads, fixed_point_delta):
+    x, w, dy = _check_input(x), _check_input(binary_weight, "binary_weight"), _check_input(dy, "dy")
+    batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
+        x, w, None, base_axis, pad, stride, dilation, group)
+    if tuple(dy.shape) != tuple(out_shape):
+        raise RuntimeError("dy must have the output's shape")
+    shapes = (x.shape, w.shape, (Ko,))
+    out = []
+    for g, shape, pd, ac in zip(grads, shapes, propagate_down, accum):
+        if not pd:
+            out.append(g)
+            continue
+        if g is None:
+            if ac:
+                raise RuntimeError("accum=True needs the gradient buffer to accumulate into")
+            g = torch.empty(tuple(shape), dtype=torch.float32, device=x.device)
+        elif tuple(g.shape) != tuple(shape) or g.dtype != torch.float32 or not g.is_cuda or not g.is_contiguous():
+            raise RuntimeError("gradient buffers must be contiguous float32 CUDA tensors of their input's shape")
+        out.append(g)
+    p = [C.ptr(g) if pd else ctypes.c_void_p(0) for g, pd in zip(out, propagate_down)]
+    args = [C.ptr(x), C.ptr(w)] + ([C.ptr(alpha)] if alpha is not None else []) + [C.ptr(dy)] + p + [
+        batch, Cin, H, W, Ko, kh, kw, int(pad[0]), int(pad[1]), int(stride[0]), int(stride[1]), int(dilation[0]),
+        int(dilation[1]), int(group), int(bool(accum[0])), int(bool(accum[1])), int(bool(accum[2])),
+        C.c_float(fixed_point_delta or 0.0), C.stream_ptr(x.device)]
+    with torch.cuda.device(x.device):
+        C.call(entry, *args)
+    return tuple(out)
+
+
+def binary_weight_convolution_backward(x, binary_weight, alpha, dy, base_axis=1, pad=None, stride=None, dilation=None,
+                                       group=1, propagate_down=(True, True, True), accum=(False, False, False),
+                                       grads=(None, None, None), fixed_point_delta=None):
+    """BinaryWeightConvolution::backward_impl
+    (src/nbla/function/generic/binary_weight_convolution.cpp:119-146): returns
+    (dx, dw, db); binary_weight / alpha are what the forward wrote, dw is the
+    gradient of the float weights. fixed_point_delta as in the forward."""
+    alpha = _check_input(alpha, "alpha")
+    return _binary_convolution_backward("nb200_binary_weight_convolution_backward_f32", x, binary_weight, alpha, dy,
+                                        base_axis, pad, stride, dilation, group, propagate_down, accum, grads,
+                                        fixed_point_delta)
+
+
+def binary_connect_convolution_backward(x, binary_weight, dy, base_axis=1, pad=None, stride=None, dilation=None,
+                                        group=1, propagate_down=(True, True, True), accum=(False, False, False),
+                                        grads=(None, None, None), fixed_point_delta=None):
+    """BinaryConnectConvolution::backward_impl
+    (src/nbla/function/generic/binary_connect_convolution.cpp:82-104)."""
+    return _binary_convolution_backward("nb200_binary_connect_convolution_backward_f32", x, binary_weight, None, dy,
+                                        base_axis, pad, stride, dilation, group, propagate_down, accum, grads,
+                                        fixed_point_delta)
+
+
 # ---------------------------------------------------------------------------
 # Companion functions of a binary-weight ResNet-18 graph
 # ---------------------------------------------------------------------------

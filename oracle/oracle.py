@@ -320,3 +320,38 @@ def binary_weight_affine_backward(x, w, dy, base_axis=1, quantize_zero_to=1.0, *
 def binary_connect_affine_backward(x, w, dy, base_axis=1, quantize_zero_to=1.0, **kw):
     """binary_connect_affine.cpp:73-93."""
     return affine_backward(x, sign(_f(w), quantize_zero_to), dy, base_axis, **kw)
+
+
+def convolution_backward(x, w, dy, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1,
+                         propagate_down=(True, True, True), accum=(False, False, False), grads=(None, None, None),
+                         f64=False):
+    """Convolution::backward_impl (convolution.cpp:199-300), 2-D NCHW. Returns (dx, dw, db)."""
+    x, w, dy = _f(x), _f(w), _f(dy)
+    N, C, H, W = x.shape
+    Ko, _, kh, kw = w.shape
+    shapes = (x.shape, w.shape, (Ko,))
+    g = [np.zeros(s, np.float32) if b is None else _f(b).copy().reshape(s) for s, b in zip(shapes, grads)]
+    L = lib()
+    L.oracle_convolution_backward.restype = ctypes.c_int
+    rc = L.oracle_convolution_backward(_p(x), _p(w), _p(dy), _p(g[0]) if propagate_down[0] else None,
+                                       _p(g[1]) if propagate_down[1] else None,
+                                       _p(g[2]) if propagate_down[2] else None, N, C, H, W, Ko, kh, kw, pad[0],
+                                       pad[1], stride[0], stride[1], dilation[0], dilation[1], group, int(accum[0]),
+                                       int(accum[1]), int(accum[2]), int(f64))
+    if rc != 0:
+        raise ValueError("oracle_convolution_backward: invalid configuration")
+    return tuple(g)
+
+
+def binary_weight_convolution_backward(x, w, dy, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1,
+                                       quantize_zero_to=1.0, **kw):
+    """binary_weight_convolution.cpp:119-146: convolution backward against wb * alpha."""
+    w = _f(w)
+    _, _, sc = binarize_rows(w.reshape(w.shape[0], -1), quantize_zero_to)
+    return convolution_backward(x, sc.reshape(w.shape), dy, pad, stride, dilation, group, **kw)
+
+
+def binary_connect_convolution_backward(x, w, dy, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1,
+                                        quantize_zero_to=1.0, **kw):
+    """binary_connect_convolution.cpp:82-104."""
+    return convolution_backward(x, sign(_f(w), quantize_zero_to), dy, pad, stride, dilation, group, **kw)

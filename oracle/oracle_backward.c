@@ -205,3 +205,102 @@ void oracle_affine_backward(const float *x, const float *w, const float *dy,
       db[j] = accum_db ? db[j] + v : v;
     }
 }
+
+/* src/nbla/function/generic/convolution.cpp:199-300 (2-D, NCHW), as direct
+ * sums instead of the reference's per-sample im2col + GEMM (same terms; the
+ * order of the fp32 additions is Eigen's in the reference and not pinned):
+ *   dx[n,c,iy,ix] (+)= sum_{o,ky,kx} dy[n,o,oy,ox] * w[o,c,ky,kx], iy = oy*sh - ph + ky*dh
+ *   dw[o,c,ky,kx] (+)= sum_{n,oy,ox} dy[n,o,oy,ox] * x[n,c,iy,ix]
+ *   db[o]         (+)= sum_{n,oy,ox} dy[n,o,oy,ox]
+ * w has shape [Ko][C/group][kh][kw]. f64 != 0 accumulates in double (the error
+ * yardstick). A NULL dx / dw / db is skipped. Returns 0, -1 on a bad shape. */
+int oracle_convolution_backward(const float *x, const float *w, const float *dy,
+                                float *dx, float *dw, float *db, int N, int C,
+                                int H, int W, int Ko, int kh, int kw, int ph,
+                                int pw, int sh, int sw, int dh, int dw_, int group,
+                                int accum_dx, int accum_dw, int accum_db, int f64) {
+  if (group <= 0 || C % group || Ko % group)
+    return -1;
+  const int Cg = C / group, Kog = Ko / group;
+  const int Ho = (H + 2 * ph - (dh * (kh - 1) + 1)) / sh + 1;
+  const int Wo = (W + 2 * pw - (dw_ * (kw - 1) + 1)) / sw + 1;
+  if (Ho <= 0 || Wo <= 0)
+    return -1;
+  if (dx) {
+    double *acc = (double *)calloc((size_t)N * C * H * W, sizeof(double));
+    float *accf = (float *)calloc((size_t)N * C * H * W, sizeof(float));
+    if (!acc || !accf)
+      return -1;
+    for (int n = 0; n < N; ++n)
+      for (int o = 0; o < Ko; ++o) {
+        const int g = o / Kog;
+        for (int oy = 0; oy < Ho; ++oy)
+          for (int ox = 0; ox < Wo; ++ox) {
+            const float gy = dy[(((int64_t)n * Ko + o) * Ho + oy) * Wo + ox];
+            for (int c = 0; c < Cg; ++c)
+              for (int ky = 0; ky < kh; ++ky) {
+                const int iy = oy * sh - ph + ky * dh;
+                if (iy < 0 || iy >= H)
+                  continue;
+                for (int kx = 0; kx < kw; ++kx) {
+                  const int ix = ox * sw - pw + kx * dw_;
+                  if (ix < 0 || ix >= W)
+                    continue;
+                  const float wv = w[(((int64_t)o * Cg + c) * kh + ky) * kw + kx];
+                  const int64_t i = (((int64_t)n * C + g * Cg + c) * H + iy) * W + ix;
+                  acc[i] += (double)gy * (double)wv;
+                  accf[i] += gy * wv;
+                }
+              }
+          }
+      }
+    for (int64_t i = 0; i < (int64_t)N * C * H * W; ++i) {
+      const float v = f64 ? (float)acc[i] : accf[i];
+      dx[i] = accum_dx ? dx[i] + v : v;
+    }
+    free(acc);
+    free(accf);
+  }
+  if (dw)
+    for (int o = 0; o < Ko; ++o) {
+      const int g = o / Kog;
+      for (int c = 0; c < Cg; ++c)
+        for (int ky = 0; ky < kh; ++ky)
+          for (int kx = 0; kx < kw; ++kx) {
+            double d = 0.;
+            float s = 0.f;
+            for (int n = 0; n < N; ++n)
+              for (int oy = 0; oy < Ho; ++oy) {
+                const int iy = oy * sh - ph + ky * dh;
+                if (iy < 0 || iy >= H)
+                  continue;
+                for (int ox = 0; ox < Wo; ++ox) {
+                  const int ix = ox * sw - pw + kx * dw_;
+                  if (ix < 0 || ix >= W)
+                    continue;
+                  const float gy = dy[(((int64_t)n * Ko + o) * Ho + oy) * Wo + ox];
+                  const float xv = x[(((int64_t)n * C + g * Cg + c) * H + iy) * W + ix];
+                  d += (double)gy * (double)xv;
+                  s += gy * xv;
+                }
+              }
+            const int64_t i = (((int64_t)o * Cg + c) * kh + ky) * kw + kx;
+            const float v = f64 ? (float)d : s;
+            dw[i] = accum_dw ? dw[i] + v : v;
+          }
+    }
+  if (db)
+    for (int o = 0; o < Ko; ++o) {
+      double d = 0.;
+      float s = 0.f;
+      for (int n = 0; n < N; ++n)
+        for (int p = 0; p < Ho * Wo; ++p) {
+          const float gy = dy[((int64_t)n * Ko + o) * Ho * Wo + p];
+          d += (double)gy;
+          s += gy;
+        }
+      const float v = f64 ? (float)d : s;
+      db[o] = accum_db ? db[o] + v : v;
+    }
+  return 0;
+}

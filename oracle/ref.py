@@ -274,3 +274,37 @@ def binary_connect_affine_backward(x, w, b, dy, base_axis=1, quantize_zero_to=1.
     g0 = [grads[0], grads[1], None] + ([grads[2]] if b is not None else [])
     g, _, _ = backward("BinaryConnectAffine", [base_axis, quantize_zero_to], [], ins, [dy], pd, ac, g0)
     return g[0], g[1], (g[3] if b is not None else None)
+
+
+def _conv_backward(op, scalars, ivecs, x, w, extra, b, dy, propagate_down, accum, grads):
+    ins = [x, w] + extra + ([b] if b is not None else [])
+    ne = len(extra)
+    pd = [propagate_down[0], propagate_down[1]] + [False] * ne + ([propagate_down[2]] if b is not None else [])
+    ac = [accum[0], accum[1]] + [False] * ne + ([accum[2]] if b is not None else [])
+    g0 = [grads[0], grads[1]] + [None] * ne + ([grads[2]] if b is not None else [])
+    g, _, _ = backward(op, scalars, ivecs, ins, [dy], pd, ac, g0)
+    return g[0], g[1], (g[2 + ne] if b is not None else None)
+
+
+def convolution_backward(x, w, b, dy, base_axis=1, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1,
+                         propagate_down=(True, True, True), accum=(False, False, False), grads=(None, None, None)):
+    """Returns (dx, dw, db) from Convolution::backward."""
+    return _conv_backward("Convolution", [base_axis, group, False], [pad, stride, dilation], x, w, [], b, dy,
+                          propagate_down, accum, grads)
+
+
+def binary_weight_convolution_backward(x, w, b, dy, base_axis=1, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1,
+                                       quantize_zero_to=1.0, propagate_down=(True, True, True),
+                                       accum=(False, False, False), grads=(None, None, None)):
+    wb = np.zeros_like(w, dtype=np.float32)
+    alpha = np.zeros(w.shape[0], dtype=np.float32)
+    return _conv_backward("BinaryWeightConvolution", [base_axis, group, quantize_zero_to], [pad, stride, dilation], x,
+                          w, [wb, alpha], b, dy, propagate_down, accum, grads)
+
+
+def binary_connect_convolution_backward(x, w, b, dy, base_axis=1, pad=(0, 0), stride=(1, 1), dilation=(1, 1),
+                                        group=1, quantize_zero_to=1.0, propagate_down=(True, True, True),
+                                        accum=(False, False, False), grads=(None, None, None)):
+    wb = np.zeros_like(w, dtype=np.float32)
+    return _conv_backward("BinaryConnectConvolution", [base_axis, group, quantize_zero_to], [pad, stride, dilation],
+                          x, w, [wb], b, dy, propagate_down, accum, grads)

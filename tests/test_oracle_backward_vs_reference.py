@@ -106,3 +106,24 @@ def test_binary_weight_affine_backward_without_bias_and_partial_propagation():
                                                grads=g0)
     assert cases.rel_rms(got[0], want[0]) < 1e-6
     assert np.array_equal(got[1], g0[1]) and np.array_equal(want[1], g0[1])  # weight gradient untouched
+
+
+@pytest.mark.parametrize("xs,ws,pad,stride,dil,grp", cases.CONV_CASES)
+@pytest.mark.parametrize("accum", [False, True])
+def test_convolution_backward_family(xs, ws, pad, stride, dil, grp, accum):
+    x, w, b = cases.conv_inputs(xs, ws, with_zeros=True)
+    rng = np.random.RandomState(2)
+    dy = rng.randn(*oracle.conv_out_shape(xs, ws, pad, stride, dil)).astype(np.float32)
+    g0 = [rng.randn(*xs).astype(np.float32), rng.randn(*ws).astype(np.float32), rng.randn(ws[0]).astype(np.float32)]
+    ac = (accum,) * 3
+    pairs = [
+        (ref.convolution_backward(x, w, b, dy, 1, pad, stride, dil, grp, accum=ac, grads=g0),
+         oracle.convolution_backward(x, w, dy, pad, stride, dil, grp, accum=ac, grads=g0)),
+        (ref.binary_weight_convolution_backward(x, w, b, dy, 1, pad, stride, dil, grp, 1.0, accum=ac, grads=g0),
+         oracle.binary_weight_convolution_backward(x, w, dy, pad, stride, dil, grp, 1.0, accum=ac, grads=g0)),
+        (ref.binary_connect_convolution_backward(x, w, b, dy, 1, pad, stride, dil, grp, 0.0, accum=ac, grads=g0),
+         oracle.binary_connect_convolution_backward(x, w, dy, pad, stride, dil, grp, 0.0, accum=ac, grads=g0)),
+    ]
+    for want, got in pairs:
+        for a, c in zip(got, want):
+            assert cases.rel_rms(a, c) < 1e-6
