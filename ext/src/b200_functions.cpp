@@ -397,7 +397,24 @@ protected:
                     this->group_, this->quantize_zero_to_, sign_ok ? delta : 0.0f, nullptr),
                 "BinaryWeightConvolution");
   }
-  B200_NO_BACKWARD("BinaryWeightConvolution")
+  // binary_weight_convolution.cpp:119-146; inputs [x, w, wb, alpha, b?]
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    const bool has_b = in.size() == 5;
+    if (!(pd[0] || pd[1] || (has_b && pd[4])))
+      return;
+    enter(this->ctx_);
+    const float delta = fxp_tag_get(in[0]);
+    const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_), *alpha = rd(in[3], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]), *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
+    float *db = has_b ? grad_wr(in[4], this->ctx_, pd[4], accum[4]) : nullptr;
+    nb200_check(nb200_binary_weight_convolution_backward_f32(
+                    x, wb, alpha, dy, dx, dw, db, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
+                    this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1],
+                    this->group_, accum[0], accum[1], has_b && accum[4], delta, nullptr),
+                "BinaryWeightConvolution backward");
+  }
 };
 
 template <typename T> class BinaryConnectConvolutionB200 : public BinaryConnectConvolution<T> {
@@ -428,7 +445,34 @@ protected:
                     this->quantize_zero_to_, sign_ok ? delta : 0.0f, nullptr),
                 "BinaryConnectConvolution");
   }
-  B200_NO_BACKWARD("BinaryConnectConvolution")
+  // binary_connect_convolution.cpp:82-104; inputs [x, w, wb, b?]. Like the reference, the weight gradient
+  // is first written to the gradient of the binary weights (inputs[2]) and passed through Sign from there.
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    const bool has_b = in.size() == 4;
+    if (!(pd[0] || pd[1] || (has_b && pd[3])))
+      return;
+    enter(this->ctx_);
+    const float delta = fxp_tag_get(in[0]);
+    const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]);
+    float *dwb = grad_wr(in[2], this->ctx_, pd[1], false);
+    float *db = has_b ? grad_wr(in[3], this->ctx_, pd[3], accum[3]) : nullptr;
+    nb200_check(nb200_binary_connect_convolution_backward_f32(
+                    x, wb, dy, dx, dwb, db, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
+                    this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1],
+                    this->group_, accum[0], 0, has_b && accum[3], delta, nullptr),
+                "BinaryConnectConvolution backward");
+    if (pd[1]) {
+      float *dw = grad_wr(in[1], this->ctx_, true, accum[1]);
+      const size_t n = in[1]->size();
+      if (accum[1])
+        nb200_check(nb200_add2_f32(dw, dwb, dw, n, nullptr), "BinaryConnectConvolution backward (accumulate)");
+      else
+        nb200_check(nb200_memcpy_d2d(dw, dwb, n * sizeof(float), nullptr), "BinaryConnectConvolution backward (copy)");
+    }
+  }
 };
 
 // ------------------------------------------------------------- companions

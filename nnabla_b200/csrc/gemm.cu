@@ -131,7 +131,9 @@ int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch
     NB_TRY(make_operand_map(&mb, B, int8, K, pitch_b, N, 1, kPairTileN / 2));
     if (int8)
       return launch_pair_gemm<true, 1, 6>(ma, mb, M, N, k_blocks, ep, ldy, st);
-    if (planes_a == 3)
+    // (the two-SM kernel accumulates a whole tile in tensor memory; long floating-point K loops go to the
+    // single-CTA kernel, whose chunked accumulation bounds the truncation error)
+    if (planes_a == 3 && k_blocks * 12 <= 384)
       return launch_pair_gemm<false, 3, 3>(ma, mb, M, N, k_blocks, ep, ldy, st);
   }
   if (int8) {

@@ -203,3 +203,27 @@ def test_affine_family_backward(xs, ws, base_axis, accum):
                 assert cases.rel_rms(g[0][i], c[0][i]) < 1e-5, (op, i)
             else:
                 assert np.array_equal(bits(g[0][i]), bits(c[0][i])), (op, i)
+
+
+@pytest.mark.parametrize("xs,ws,pad,stride,dil,grp", cases.CONV_CASES)
+@pytest.mark.parametrize("accum", [False, True])
+def test_binary_convolutions_backward(xs, ws, pad, stride, dil, grp, accum):
+    from oracle import oracle
+    x, w, b = cases.conv_inputs(xs, ws, with_zeros=True)
+    rng = np.random.RandomState(2)
+    dy = rng.randn(*oracle.conv_out_shape(xs, ws, pad, stride, dil)).astype(np.float32)
+    gx, gw, gb = (rng.randn(*s).astype(np.float32) for s in (xs, ws, (ws[0],)))
+    wb, alpha = np.zeros_like(w), np.zeros(ws[0], np.float32)
+    runs = [
+        ("BinaryWeightConvolution", [1, grp, 1.0], [x, w, wb, alpha, b], [True, True, False, False, True],
+         [gx, gw, wb, alpha, gb]),
+        ("BinaryConnectConvolution", [1, grp, 0.0], [x, w, wb, b], [True, True, False, True], [gx, gw, wb, gb]),
+    ]
+    for op, scalars, ins, pd, g0 in runs:
+        c = H.backward(CPU, op, scalars, [pad, stride, dil], ins, [dy], pd, [accum] * len(ins), g0)
+        g = H.backward(B200, op, scalars, [pad, stride, dil], ins, [dy], pd, [accum] * len(ins), g0)
+        for i, p in enumerate(pd):
+            if p or (op == "BinaryConnectConvolution" and i == 2):
+                assert cases.rel_rms(g[0][i], c[0][i]) < 1e-5, (op, i)
+            else:
+                assert np.array_equal(bits(g[0][i]), bits(c[0][i])), (op, i)
