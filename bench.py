@@ -298,7 +298,18 @@ def run_extras(args, rank, world, barrier):
         "ms": ms, "tflops_algorithmic_whole_job": flops / ms / 1e9, "tflops_issued_bf16x3_whole_job": 3 * flops / ms / 1e9,
         "frac_of_bf16_peak_issued_per_gpu": 3 * flops / world / ms / 1e9 / peaks["bf16_tflops"],
         "includes": "binarise + NCHW->NHWC split + implicit GEMM, whole forward_impl", "images_per_gpu": Nb}
-    del x, w
+    # backward of the same layer (straight-through weight gradient), per rank
+    dyc = rn(Nb, 256, 28, 28)
+    gxc, gwc, gbc = torch.empty_like(x), torch.empty_like(w), torch.empty(256, device="cuda")
+    ms_dx = maxr(time_gpu(lambda: F.binary_weight_convolution_backward(
+        x, wb, al, dyc, 1, (1, 1), (1, 1), propagate_down=(True, False, False), grads=(gxc, None, None)), 10))
+    ms_dw = maxr(time_gpu(lambda: F.binary_weight_convolution_backward(
+        x, wb, al, dyc, 1, (1, 1), (1, 1), propagate_down=(False, True, True), grads=(None, gwc, gbc)), 10))
+    out["configs[3] backward (dx | dw + db), batch %d" % (Nb * world)] = {
+        "ms_dx": ms_dx, "ms_dw_db": ms_dw, "tflops_algorithmic_dx_whole_job": flops / ms_dx / 1e9,
+        "tflops_algorithmic_dw_whole_job": flops / ms_dw / 1e9,
+        "includes": "operand re-layout (stuffing / batch-innermost transposes, bf16 pieces) + implicit GEMM"}
+    del x, w, dyc, gxc
     # configs[4]: binary-weight ResNet-18, batch sharded over the ranks
     B = args.resnet_batch
     Bg = max(1, B // world)

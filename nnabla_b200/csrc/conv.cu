@@ -79,7 +79,8 @@ void plan_box(const ConvGeometry &g, int bn_max, int &h_box, int &n_box) {
 
 template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes, bool kSkip = false>
 int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ctot, const void *wside, int64_t wpitch,
-                int c_pad_g, int cblocks, int h_box, int n_box, const GemmEpilogue &ep, cudaStream_t st) {
+                int c_pad_g, int cblocks, int h_box, int n_box, const GemmEpilogue &ep, cudaStream_t st,
+                int k_splits = 1, int64_t split_stride = 0) {
   const int es = kInt8 ? 1 : 2;
   const int E = RB / es;
   CUtensorMap ma, mb;
@@ -118,7 +119,9 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
   p.c_group_stride = c_pad_g;
   p.pixels = n_box * h_box * g.Wo;
   p.n_run = (int)round_up(p.pixels, 16);
-  const int tiles = p.groups * p.m_tiles_g * p.tiles_h * p.tiles_n;
+  p.k_splits = k_splits;
+  p.split_stride = split_stride;
+  const int tiles = k_splits * p.groups * p.m_tiles_g * p.tiles_h * p.tiles_n;
   return launch_contraction<kInt8, PA, PB, BN, STAGES, kSkip, ConvProblem, RB>(ma, mb, p, tiles, ep, st);
 }
 
@@ -274,12 +277,6 @@ int conv_weight_grad(const float *x, const float *dy, float *dw, const ConvGeome
   const int64_t Rx = (int64_t)g.Cg * g.H * g.W, Rdy = (int64_t)g.Kog * taps_f;
   const size_t x_bytes = round_up((size_t)planes_x * Rx * Np * 2, 1024);
   const size_t dy_bytes = round_up((size_t)3 * Rdy * Np * 2, 1024);
-  const size_t out_bytes = round_up((size_t)g.Cg * g.Kog * taps_w * 4, 1024);
-  AsyncScratch scratch(st);
-  NB_TRY(scratch.alloc(x_bytes + dy_bytes + out_bytes));
-  uint8_t *xt = static_cast<uint8_t *>(scratch.p);
-  uint8_t *dyt = xt + x_bytes;
-  float *staged = reinterpret_cast<float *>(dyt + dy_bytes);
   ConvGeometry b = g;
   b.N = g.Cg;   // images = input channels of the group
   b.C = g.N;    // channel axis = batch
@@ -297,6 +294,25 @@ int conv_weight_grad(const float *x, const float *dy, float *dw, const ConvGeome
   b.Wo = g.kw;
   int h_box, n_box;
   plan_box(b, 64, h_box, n_box);
+  // The output is small and K (batch x output pixels) is long: cut K over the SMs that the
+  // output tiles alone would leave idle; each split writes its own staged result.
+  const int base_tiles = ((g.Kog + kTileM - 1) / kTileM) * ((g.Cg + n_box - 1) / n_box) * ((b.Ho + h_box - 1) / h_box);
+  const int kb_all = taps_f * cblocks;
+  int k_splits = sm_count() / base_tiles;
+  k_splits = k_splits > 32 ? 32 : k_splits;
+  k_splits = k_splits > kb_all / 8 ? kb_all / 8 : k_splits;
+  k_splits = k_splits < 1 ? 1 : k_splits;
+  {
+    const int per = (kb_all + k_splits - 1) / k_splits;
+    k_splits = (kb_all + per - 1) / per; // no empty split
+  }
+  const int64_t split_stride = (int64_t)g.Cg * g.Kog * taps_w;
+  const size_t out_bytes = round_up((size_t)k_splits * split_stride * 4, 1024);
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc(x_bytes + dy_bytes + out_bytes));
+  uint8_t *xt = static_cast<uint8_t *>(scratch.p);
+  uint8_t *dyt = xt + x_bytes;
+  float *staged = reinterpret_cast<float *>(dyt + dy_bytes);
   for (int grp = 0; grp < g.group; ++grp) {
     if (g.N != Np)
       NB_CUDA(cudaMemsetAsync(xt, 0, x_bytes + dy_bytes, st));
@@ -307,10 +323,12 @@ int conv_weight_grad(const float *x, const float *dy, float *dw, const ConvGeome
     ep.scale = 1.0f;
     if (planes_x == 3)
       NB_TRY((launch_conv<false, 3, 3, 64, 2, kRowBytes, true>(b, xt, 3, Np, dyt, wpitch, Np, cblocks, h_box, n_box, ep,
-                                                               st)));
+                                                               st, k_splits, split_stride)));
     else
-      NB_TRY((launch_conv<false, 3, 1, 64, 3>(b, xt, 1, Np, dyt, wpitch, Np, cblocks, h_box, n_box, ep, st)));
-    NB_TRY(permute_weight_grad(staged, g.Cg, g.Kog, taps_w, dw + (int64_t)grp * g.Kog * g.Cg * taps_w, accum, st));
+      NB_TRY((launch_conv<false, 3, 1, 64, 3>(b, xt, 1, Np, dyt, wpitch, Np, cblocks, h_box, n_box, ep, st, k_splits,
+                                              split_stride)));
+    NB_TRY(permute_weight_grad(staged, k_splits, g.Cg, g.Kog, taps_w, dw + (int64_t)grp * g.Kog * g.Cg * taps_w, accum,
+                               st));
   }
   return NB200_OK;
 }

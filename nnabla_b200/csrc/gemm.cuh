@@ -71,6 +71,8 @@ struct Tile {
   int img0;    // convolution: first image of the pixel box
   int oy0;     // convolution: first output row of the pixel box
   int group;   // convolution: group index
+  int kb0, kb1; // K blocks [kb0, kb1) of the contraction that this tile accumulates (split K)
+  int64_t y_off; // offset of this tile's partial result in y (split K: one staged result per split)
 };
 
 // ---- plain GEMM: A [planes][M][K], B [planes][N][K] --------------------------
@@ -89,6 +91,9 @@ struct GemmProblem {
     t.m_end = M;
     t.n0 = (tile / m_tiles) * bn;
     t.img0 = t.oy0 = t.group = 0;
+    t.kb0 = 0;
+    t.kb1 = kblocks;
+    t.y_off = 0;
   }
   __device__ __forceinline__ void load_a(const CUtensorMap *map, void *dst, uint64_t *bar, int kb, const Tile &t,
                                          int plane, int epb) const {
@@ -126,12 +131,20 @@ struct ConvProblem {
   int chunk_blocks;   // K blocks accumulated in tensor memory before the fp32 registers take over (0 = all)
   int n_run;          // UMMA N: pixels per box rounded up to 16
   int pixels;         // n_box * h_box * Wo
+  int k_splits;       // the K loop is cut into this many tiles, each writing its own partial result
+  int64_t split_stride; // elements between the partial results of consecutive splits in y
   __device__ __forceinline__ int k_chunk() const { return chunk_blocks; }
-  __device__ __forceinline__ int num_tiles() const { return groups * m_tiles_g * tiles_h * tiles_n; }
+  __device__ __forceinline__ int num_tiles() const { return k_splits * groups * m_tiles_g * tiles_h * tiles_n; }
   __device__ __forceinline__ int k_blocks() const { return taps * cblocks; }
   __device__ __forceinline__ uint32_t umma_n() const { return (uint32_t)n_run; }
   __device__ __forceinline__ uint32_t b_tx_bytes() const { return (uint32_t)(pixels * row_bytes); }
   __device__ __forceinline__ void decode(int tile, Tile &t) const {
+    const int split = tile % k_splits;
+    tile /= k_splits;
+    const int kb_all = taps * cblocks, per = (kb_all + k_splits - 1) / k_splits;
+    t.kb0 = split * per;
+    t.kb1 = (t.kb0 + per < kb_all) ? t.kb0 + per : kb_all;
+    t.y_off = (int64_t)split * split_stride;
     const int mt = tile % m_tiles_g;
     int r = tile / m_tiles_g;
     const int g = r % groups;
@@ -196,10 +209,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = prob.num_tiles();
-  const int k_blocks = prob.k_blocks();
   // K blocks per TMEM accumulation (int8 accumulation is exact: never chunked)
-  const int chunk = (!kInt8 && prob.k_chunk() > 0 && prob.k_chunk() < k_blocks) ? prob.k_chunk() : k_blocks;
-  const int n_chunks = (k_blocks + chunk - 1) / chunk;
+  const int chunk_cfg = (!kInt8 && prob.k_chunk() > 0) ? prob.k_chunk() : 0x3fffffff;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -234,7 +245,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         Tile t;
         prob.decode(tile, t);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = t.kb0; kb < t.kb1; ++kb) {
           if (!ptx::mbar_wait(empty_bar + stage, phase ^ 1u, abort_flag)) {
             if (*abort_flag == 0)
               atomicCAS(status, 0, kStatusProducerTimeout);
@@ -243,7 +254,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           uint8_t *st = smem + stage * kStageBytes;
-          if ((ep.debug & 2) && (tile != (int)blockIdx.x || kb >= STAGES)) {
+          if ((ep.debug & 2) && (tile != (int)blockIdx.x || kb - t.kb0 >= STAGES)) {
             ptx::mbar_arrive(full_bar + stage);
           } else {
             ptx::mbar_expect_tx(full_bar + stage, tx_bytes);
@@ -270,7 +281,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       bool ok = true;
       const uint32_t idesc = ptx::make_idesc(kInt8 ? 2u : 1u, 1u, kTileM, prob.umma_n()); // S8 and BF16 both encode as 1
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += chunk, ++local) {
+        Tile t;
+        prob.decode(tile, t);
+        const int k_blocks = t.kb1, chunk = chunk_cfg;
+        for (int kb0 = t.kb0; kb0 < k_blocks && ok; kb0 += chunk, ++local) {
           const int buf = local & 1;
           const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
           if (!ptx::mbar_wait(tmem_empty + buf, buf_phase ^ 1u, abort_flag)) {
@@ -283,7 +297,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           ptx::tc_fence_after_sync();
           const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
           uint32_t accumulate = 0;
-          const int kb1 = (kb0 + chunk < k_blocks) ? kb0 + chunk : k_blocks;
+          const int kb1 = (k_blocks - kb0 > chunk) ? kb0 + chunk : k_blocks;
           for (int kb = kb0; kb < kb1; ++kb) {
             if (!ptx::mbar_wait(full_bar + stage, phase, abort_flag)) {
               if (*abort_flag == 0)
@@ -352,6 +366,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int rows_here = t.m_end - row_base;
       rows_here = rows_here < 0 ? 0 : (rows_here > 32 ? 32 : rows_here);
       const int64_t row_stride = prob.row_offset(1);
+      const int n_kb = t.kb1 - t.kb0;
+      const int n_chunks = (n_kb <= chunk_cfg) ? 1 : (n_kb + chunk_cfg - 1) / chunk_cfg;
       for (int kc = 0; kc < n_chunks && ok; ++kc, ++local) {
         const int buf = local & 1;
         const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
@@ -419,7 +435,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           int gcol;
           const bool col_ok = prob.col_offset(t, c0 + lane, coff, gcol);
           const float cb = (ep.col_bias && col_ok) ? ep.col_bias[gcol] : 0.0f;
-          const int64_t tile_off = coff + prob.row_offset(row_base);
+          const int64_t tile_off = coff + prob.row_offset(row_base) + t.y_off;
           // destination 0 is this GPU's y, the others are the peer copies
 #pragma unroll 1
           for (int d = 0; d <= ep.n_peers; ++d) {

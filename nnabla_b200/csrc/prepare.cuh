@@ -47,7 +47,8 @@ int batch_to_inner(const float *src, int N, int64_t R, int64_t src_row_stride, i
 // out[o] (+)= sum over n and pixels of dy [N][Ko][HW]; partial: splits * Ko floats.
 int channel_sums(const float *dy, int N, int Ko, int HW, float *out, int accumulate, float *partial, int splits,
                  cudaStream_t st);
-// staged [Cg][Kog][taps] -> dw [Kog][Cg][taps] (overwrite or add).
-int permute_weight_grad(const float *staged, int Cg, int Kog, int taps, float *dw, int accumulate, cudaStream_t st);
+// staged [splits][Cg][Kog][taps] -> dw [Kog][Cg][taps] = sum over the splits (overwrite or add).
+int permute_weight_grad(const float *staged, int splits, int Cg, int Kog, int taps, float *dw, int accumulate,
+                        cudaStream_t st);
 
 } // namespace nb200

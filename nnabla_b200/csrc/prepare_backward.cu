@@ -151,16 +151,19 @@ __global__ void channel_finish_kernel(const float *__restrict__ partial, int Ko,
   out[o] = accumulate ? __fadd_rn(out[o], s) : s;
 }
 
-// staged [Cg][Kog][taps] (the contraction's NCHW-shaped output with the input
-// channel as the image axis) -> dW[o0 + o][c][taps], overwriting or adding.
-__global__ void permute_weight_grad_kernel(const float *__restrict__ staged, int Cg, int Kog, int taps,
+// staged [splits][Cg][Kog][taps] (the contraction's NCHW-shaped output with the
+// input channel as the image axis, one partial result per K split) ->
+// dW[o][c][taps]: the splits are added in order, then dW is overwritten or added to.
+__global__ void permute_weight_grad_kernel(const float *__restrict__ staged, int splits, int Cg, int Kog, int taps,
                                            float *__restrict__ dw, int accumulate) {
   const int64_t total = (int64_t)Cg * Kog * taps;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int t = (int)(i % taps);
     const int c = (int)((i / taps) % Cg);
     const int o = (int)(i / ((int64_t)taps * Cg));
-    const float v = staged[((int64_t)c * Kog + o) * taps + t];
+    float v = 0.0f;
+    for (int k = 0; k < splits; ++k)
+      v = __fadd_rn(v, staged[k * total + ((int64_t)c * Kog + o) * taps + t]);
     dw[i] = accumulate ? __fadd_rn(dw[i], v) : v;
   }
 }
@@ -216,8 +219,9 @@ int channel_sums(const float *dy, int N, int Ko, int HW, float *out, int accumul
   return NB200_OK;
 }
 
-int permute_weight_grad(const float *staged, int Cg, int Kog, int taps, float *dw, int accumulate, cudaStream_t st) {
-  permute_weight_grad_kernel<<<capped((int64_t)Cg * Kog * taps, 256), 256, 0, st>>>(staged, Cg, Kog, taps, dw,
+int permute_weight_grad(const float *staged, int splits, int Cg, int Kog, int taps, float *dw, int accumulate,
+                        cudaStream_t st) {
+  permute_weight_grad_kernel<<<capped((int64_t)Cg * Kog * taps, 256), 256, 0, st>>>(staged, splits, Cg, Kog, taps, dw,
                                                                                       accumulate);
   NB_LAUNCH_CHECK();
   return NB200_OK;
