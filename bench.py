@@ -47,6 +47,8 @@ def parse_args():
                     help="run only the other BASELINE configurations and print their JSON (profiling runs)")
     ap.add_argument("--small-extras", action="store_true",
                     help="reduced sizes for the other configurations (ncu captures must stay small)")
+    ap.add_argument("--backward-log2", type=int, default=0,
+                    help="log2 of the element count of the quantizer-backward entry (default 28, 22 with --small-extras)")
     return ap.parse_args()
 
 
@@ -268,7 +270,7 @@ def run_extras(args, rank, world, barrier):
     out["configs[2] fixed-point int8 affine %dx%dx%d" % (M, K, N)] = entry
     del x, w, xq, wq, xc, wc
     # quantizer backward passes (straight-through estimators) on the configs[1] parameters, per rank
-    nb = 1 << (22 if args.small_extras else 28)
+    nb = 1 << (args.backward_log2 or (22 if args.small_extras else 28))
     gx = torch.rand(nb, device="cuda", generator=gen) * 9 - 4.5
     gdy = rn(nb)
     gdx = torch.empty_like(gx)
@@ -285,7 +287,7 @@ def run_extras(args, rank, world, barrier):
         ms = maxr(time_gpu(fn, 10))
         bw[name] = {"ms": ms, "GBps_per_gpu": bpe * nb / ms / 1e6, "bytes_per_element": bpe,
                     "frac_of_hbm_peak": bpe * nb / ms / 1e6 / peaks["hbm_gbs"]}
-    out["quantizer backward, 2^%d elements per GPU" % (22 if args.small_extras else 28)] = bw
+    out["quantizer backward, 2^%d elements per GPU" % (nb.bit_length() - 1)] = bw
     del gx, gdy, gdx
     # configs[3]: BinaryWeightConvolution 3x3, 256 -> 256, 28 x 28, batch 128 sharded over the ranks
     Nb = max(1, (16 if args.small_extras else 128) // world)
