@@ -157,6 +157,22 @@ int nb200_min_max_quantize_f32_noalloc(const float *x, const int64_t *x_shape, i
 int nb200_min_max_quantize_f32_host(const float *x, size_t size, float *qr_min, float *qr_max, const float *ql_min,
                                     const float *ql_max, float eps, float *y);
 
+/* ---- inference-time fusion ---------------------------------------------------------
+ * y = FixedPointQuantize(ReLU(BN_a(a) [+ BN_b(b) | + b])) over [outer, channels, inner]
+ * tensors in one pass: BatchNormalization::forward_impl_global
+ * (src/nbla/function/generic/batch_normalization.cpp:228-260), Add2 (add2.cpp),
+ * ReLU (relu.cpp) and FixedPointQuantize (fixed_point_quantize.cpp:45-66),
+ * bit-identical to calling them one after the other (the reference's own fused
+ * form of the first three is FusedBatchNormalization,
+ * fused_batch_normalization.cpp). b == NULL: no second operand; mean_b == NULL:
+ * b is added as it is (a residual); beta / gamma may be NULL (0 / 1).
+ * relu / quantize switch those two stages on. */
+int nb200_bn_add_relu_fxp_f32(const float *a, const float *beta_a, const float *gamma_a, const float *mean_a,
+                              const float *var_a, const float *b, const float *beta_b, const float *gamma_b,
+                              const float *mean_b, const float *var_b, float *y, int64_t outer, int64_t channels,
+                              int64_t inner, float eps, int relu, int quantize, int sign, int n, float delta,
+                              void *stream);
+
 /* ---- binary convolution backward passes ------------------------------------------
  * Convolution<float>::backward_impl
  * (src/nbla/function/generic/convolution.cpp:199-300) as the binary layers

@@ -661,3 +661,49 @@ def global_average_pooling(x, n_outputs=-1, outputs=None):
         C.call("nb200_global_average_pooling_f32", C.ptr(x), C.ptr(y), ctypes.c_int64(N * Cn), ctypes.c_int64(S),
                C.stream_ptr(x.device))
     return y
+
+
+def bn_add_relu_fixed_point(a, bn_a, b=None, bn_b=None, eps=1e-05, relu=True, quantize=True, sign=True, n=8,
+                            delta=2 ** -4, outputs=None):
+    """Inference-time fusion: fixed_point_quantize(relu(batch_normalization(a) [+ batch_normalization(b) | + b]))
+    in one pass, bit-identical to the separate functions.
+
+    bn_a / bn_b are (beta, gamma, mean, variance) tuples over axis 1 (bn_b=None
+    adds b as it is, b=None leaves the second term out). The reference's fused
+    form of the first three stages is FusedBatchNormalization
+    (src/nbla/function/generic/fused_batch_normalization.cpp)."""
+    a = _check_input(a, "a")
+    if a.dim() < 2:
+        raise RuntimeError("the normalised axis is axis 1")
+    Cn = int(a.shape[1])
+    outer, inner = int(a.shape[0]), a.numel() // max(int(a.shape[0]) * Cn, 1)
+
+    def params(t4, what):
+        out = []
+        for t, nm in zip(t4, ("beta", "gamma", "mean", "variance")):
+            if t is None:
+                if nm in ("mean", "variance"):
+                    raise RuntimeError("mean and variance are required (%s)" % what)
+                out.append(None)
+                continue
+            t = _check_input(t, nm)
+            if t.numel() != Cn:
+                raise RuntimeError("%s must have %d elements (shape of the normalised axis)" % (nm, Cn))
+            out.append(t)
+        return out
+    pa = params(bn_a, "a")
+    pb = [None] * 4
+    if b is not None:
+        b = _check_input(b, "b")
+        _same_shape(a, b, "a vs b")
+        if bn_b is not None:
+            pb = params(bn_b, "b")
+    elif bn_b is not None:
+        raise RuntimeError("bn_b without b")
+    y = _output_like(a, outputs)
+    with torch.cuda.device(a.device):
+        C.call("nb200_bn_add_relu_fxp_f32", C.ptr(a), C.ptr(pa[0]), C.ptr(pa[1]), C.ptr(pa[2]), C.ptr(pa[3]),
+               C.ptr(b), C.ptr(pb[0]), C.ptr(pb[1]), C.ptr(pb[2]), C.ptr(pb[3]), C.ptr(y), ctypes.c_int64(outer),
+               ctypes.c_int64(Cn), ctypes.c_int64(inner), C.c_float(eps), int(bool(relu)), int(bool(quantize)),
+               int(bool(sign)), int(n), C.c_float(delta), C.stream_ptr(a.device))
+    return y

@@ -58,7 +58,11 @@ def init_parameters(rng, num_classes=1000, in_channels=3):
 class Runner:
     """Applies the network with a given function namespace and array factory."""
 
-    def __init__(self, ops, params, zeros_like, trace=None, fixed_point_hint=True):
+    def __init__(self, ops, params, zeros_like, trace=None, fixed_point_hint=True, fused=False):
+        """fused=True applies BN (+ residual) + ReLU + FixedPointQuantize as one
+        function (ops.bn_add_relu_fixed_point), which is bit-identical to the
+        separate functions and reads / writes each activation once."""
+        self.fused = fused
         self.ops = ops
         self.p = params
         self.zeros_like = zeros_like
@@ -82,6 +86,16 @@ class Runner:
         q = self.ops.fixed_point_quantize(y, True, 8, DELTA)
         return self._rec(name + "/fxp", "fixed_point_quantize", [y], q)
 
+    def bn_params(self, name):
+        p = self.p
+        return (p[name + "/beta"], p[name + "/gamma"], p[name + "/mean"], p[name + "/var"])
+
+    def fused_act(self, name, a, bn_a, b=None, bn_b=None):
+        y = self.ops.bn_add_relu_fixed_point(a, self.bn_params(bn_a), b, self.bn_params(bn_b) if bn_b else None, 1e-5,
+                                             True, True, True, 8, DELTA)
+        return self._rec(name, "bn_add_relu_fixed_point", [a] + ([b] if b is not None else []), y, bn_a=bn_a,
+                         bn_b=bn_b)
+
     def bwconv(self, name, x, k, stride):
         w = self.p[name + "/W"]
         if name not in self.side:
@@ -96,7 +110,7 @@ class Runner:
         o = self.ops
         h = o.convolution(x, self.p["stem/conv/W"], None, 1, (3, 3), (2, 2), (1, 1), 1)
         self._rec("stem/conv", "convolution", [x], h)
-        h = self.relu_q("stem", self.bn("stem/bn", h))
+        h = self.fused_act("stem/act", h, "stem/bn") if self.fused else self.relu_q("stem", self.bn("stem/bn", h))
         h = self._rec("stem/pool", "max_pooling", [h], o.max_pooling(h, (3, 3), (2, 2), True, (1, 1)))
         cin = 64
         for s, (c, stride) in enumerate(STAGES):
@@ -104,6 +118,16 @@ class Runner:
                 st = stride if b == 0 else 1
                 name = "stage%d/block%d" % (s + 1, b)
                 r = self.bwconv(name + "/conv1", h, 3, st)
+                if self.fused:
+                    r = self.fused_act(name + "/act1", r, name + "/bn1")
+                    r = self.bwconv(name + "/conv2", r, 3, 1)
+                    if st != 1 or cin != c:
+                        sc = self.bwconv(name + "/shortcut", h, 1, st)
+                        h = self.fused_act(name + "/act2", r, name + "/bn2", sc, name + "/bn_s")
+                    else:
+                        h = self.fused_act(name + "/act2", r, name + "/bn2", h)
+                    cin = c
+                    continue
                 r = self.relu_q(name + "/act1", self.bn(name + "/bn1", r))
                 r = self.bn(name + "/bn2", self.bwconv(name + "/conv2", r, 3, 1))
                 if st != 1 or cin != c:

@@ -47,3 +47,15 @@ def binary_weight_convolution(x, w, wb, alpha, b=None, base_axis=1, pad=None, st
 
 def affine(x, w, b=None, base_axis=1, **kw):
     return oracle.affine(x, w, b, base_axis)
+
+
+def bn_add_relu_fixed_point(a, bn_a, b=None, bn_b=None, eps=1e-5, relu_on=True, quantize=True, sign=True, n=8,
+                            delta=2 ** -4):
+    """The unfused chain the fused function must reproduce bit for bit."""
+    v = oracle.batch_norm_inference(a, bn_a[0], bn_a[1], bn_a[2], bn_a[3], eps)
+    if b is not None:
+        w = oracle.batch_norm_inference(b, bn_b[0], bn_b[1], bn_b[2], bn_b[3], eps) if bn_b is not None else b
+        v = oracle.add2(v, w)
+    if relu_on:
+        v = oracle.relu(v)
+    return oracle.fixed_point_quantize(v, sign, n, delta) if quantize else v
