@@ -128,3 +128,41 @@ def test_one_process_per_gpu():
     results = mp.Manager().dict()
     mp.spawn(_rank_main, args=(world, port, results), nprocs=world, join=True)
     assert [results[r] for r in range(world)] == [True] * world
+
+
+def _comm_main(rank, world, port, results):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch.distributed as dist
+    from nnabla_b200 import communicators as C
+    comm = C.MultiProcessDataParallelCommunicator()
+    try:
+        comm.init("nccl")
+        dev_ = torch.device("cuda", rank)
+        grads = [torch.full((n,), float(rank + 1), device=dev_) for n in (1000, 77, 4096, 5)]
+        comm.all_reduce(grads, division=True, inplace=False)
+        mean = sum(range(1, world + 1)) / world
+        ok = all(bool(torch.allclose(g, torch.full_like(g, mean))) for g in grads)
+        grads = [torch.full((n,), float(rank + 1), device=dev_) for n in (300000, 70000, 5)]
+        comm.all_reduce_callback(grads, pack_size=100000, division=False)()
+        ok = ok and all(bool(torch.equal(g, torch.full_like(g, float(sum(range(1, world + 1)))))) for g in grads)
+        out = [torch.zeros(3, device=dev_) for _ in range(world)]
+        comm.all_gather(torch.full((3,), float(rank), device=dev_), out)
+        ok = ok and all(bool(torch.equal(out[r], torch.full((3,), float(r), device=dev_))) for r in range(world))
+        torch.cuda.synchronize()
+        results[rank] = ok
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_communicator_over_nccl():
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 8)
+    port = 29650 + os.getpid() % 200
+    results = mp.Manager().dict()
+    mp.spawn(_comm_main, args=(world, port, results), nprocs=world, join=True)
+    assert [results[r] for r in range(world)] == [True] * world
