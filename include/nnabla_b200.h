@@ -157,6 +157,36 @@ int nb200_min_max_quantize_f32_noalloc(const float *x, const int64_t *x_shape, i
 int nb200_min_max_quantize_f32_host(const float *x, size_t size, float *qr_min, float *qr_max, const float *ql_min,
                                     const float *ql_max, float eps, float *y);
 
+/* ---- sibling quantization functions (forward and backward) ----------------------- */
+/* BinarySigmoid / BinaryTanh (include/nbla/function/binary_sigmoid.hpp:50-52,
+ * binary_tanh.hpp:51-52): y = x > 0 ? 1 : 0 (or -1); gradient |x| >= 1 ? 0 :
+ * dy * 0.5 (or dy), combined as (accum ? dx : 0) + g
+ * (include/nbla/function/utils/base_transform_unary.hpp:104-110). */
+int nb200_binary_sigmoid_f32(const float *x, float *y, size_t size, void *stream);
+int nb200_binary_tanh_f32(const float *x, float *y, size_t size, void *stream);
+int nb200_binary_sigmoid_backward_f32(const float *x, const float *dy, float *dx, size_t size, int accum,
+                                      void *stream);
+int nb200_binary_tanh_backward_f32(const float *x, const float *dy, float *dx, size_t size, int accum, void *stream);
+/* QuantizeLinear<float>::forward_impl (src/nbla/function/generic/quantize_linear.cpp:103-122):
+ * y = saturate(round(x / scale) + zero_point). scale and zero_point broadcast
+ * over x (every extent 1 or x's); zero_point is ROUNDED AND SATURATED IN PLACE
+ * first, as the reference does. round_mode 0 = HALF_AWAY_FROM_ZERO, 1 =
+ * HALF_TO_EVEN; dtype 1 = BYTE, 2 = UBYTE (include/nbla/dtypes.hpp:32-35). */
+int nb200_quantize_linear_f32(const float *x, const int64_t *x_shape, int ndim, const float *scale,
+                              const int64_t *scale_shape, float *zero_point, const int64_t *zero_point_shape, float *y,
+                              int round_mode, int narrow_range, int dtype, void *stream);
+/* DequantizeLinear<float>::forward_impl (dequantize_linear.cpp:60-71): y = (x - zero_point) * scale. */
+int nb200_dequantize_linear_f32(const float *x, const int64_t *x_shape, int ndim, const float *scale,
+                                const int64_t *scale_shape, const float *zero_point, const int64_t *zero_point_shape,
+                                float *y, void *stream);
+/* Their gradients w.r.t. x: dx (+)= dy / scale (quantize_linear.cpp:137-147),
+ * dx (+)= dy * scale (dequantize_linear.cpp:92-102). The reference has no
+ * gradient w.r.t. scale or zero point. */
+int nb200_quantize_linear_backward_f32(const float *dy, const int64_t *x_shape, int ndim, const float *scale,
+                                       const int64_t *scale_shape, float *dx, int accum, void *stream);
+int nb200_dequantize_linear_backward_f32(const float *dy, const int64_t *x_shape, int ndim, const float *scale,
+                                         const int64_t *scale_shape, float *dx, int accum, void *stream);
+
 /* ---- inference-time fusion ---------------------------------------------------------
  * y = FixedPointQuantize(ReLU(BN_a(a) [+ BN_b(b) | + b])) over [outer, channels, inner]
  * tensors in one pass: BatchNormalization::forward_impl_global

@@ -800,6 +800,7 @@ int static_scratch_for_current_device(float **out) {
 }
 
 #include "quantize_backward.cuh"
+#include "quantize_siblings.cuh"
 
 // ---- chunk callbacks of the _host variants ---------------------------------
 struct FxpHostArgs {
@@ -958,5 +959,73 @@ int nb200_min_max_quantize_backward_f32(const float *x, const int64_t *x_shape, 
   NB_TRY(minmax_view(x_shape, q_shape, ndim, &V));
   return minmax_backward(x, V, qr_min, qr_max, ql_min, ql_max, dy, x_min_max, ema, ste_fine_grained, propagate_down,
                          accum, dx, g_qr_min, g_qr_max, as_stream(stream));
+}
+
+int nb200_binary_sigmoid_f32(const float *x, float *y, size_t size, void *stream) {
+  return launch_elementwise(x, y, size, BinaryActOp<false>(), as_stream(stream));
+}
+int nb200_binary_tanh_f32(const float *x, float *y, size_t size, void *stream) {
+  return launch_elementwise(x, y, size, BinaryActOp<true>(), as_stream(stream));
+}
+int nb200_binary_sigmoid_backward_f32(const float *x, const float *dy, float *dx, size_t size, int accum,
+                                      void *stream) {
+  return launch_gradient(x, dy, dx, size, accum, BinaryActGrad<false>(), as_stream(stream));
+}
+int nb200_binary_tanh_backward_f32(const float *x, const float *dy, float *dx, size_t size, int accum, void *stream) {
+  return launch_gradient(x, dy, dx, size, accum, BinaryActGrad<true>(), as_stream(stream));
+}
+
+int nb200_quantize_linear_f32(const float *x, const int64_t *x_shape, int ndim, const float *scale,
+                              const int64_t *scale_shape, float *zero_point, const int64_t *zero_point_shape, float *y,
+                              int round_mode, int narrow_range, int dtype, void *stream) {
+  NB_CHECK(x_shape && scale_shape && zero_point_shape, NB200_EVALUE, "null shape pointer");
+  NB_CHECK(round_mode == 0 || round_mode == 1, NB200_EVALUE,
+           "round_mode must be 0 (HALF_AWAY_FROM_ZERO) or 1 (HALF_TO_EVEN)");
+  QuantizeLinearOp op{};
+  size_t size = 0;
+  NB_TRY(broadcast_view(x_shape, scale_shape, ndim, &op.vs, &size));
+  NB_TRY(broadcast_view(x_shape, zero_point_shape, ndim, &op.vz, nullptr));
+  NB_TRY(quantize_linear_range(narrow_range, dtype, &op.lo, &op.hi));
+  NB_CHECK(scale && zero_point, NB200_EVALUE, "null parameter pointer");
+  op.scale = scale;
+  op.zp = zero_point;
+  op.half_to_even = round_mode;
+  cudaStream_t st = as_stream(stream);
+  ql_zero_point_kernel<<<(unsigned)((op.vz.Q + 255) / 256), 256, 0, st>>>(zero_point, op.vz.Q, round_mode, op.lo,
+                                                                           op.hi);
+  NB_LAUNCH_CHECK();
+  return launch_elementwise(x, y, size, op, st);
+}
+
+int nb200_dequantize_linear_f32(const float *x, const int64_t *x_shape, int ndim, const float *scale,
+                                const int64_t *scale_shape, const float *zero_point, const int64_t *zero_point_shape,
+                                float *y, void *stream) {
+  NB_CHECK(x_shape && scale_shape && zero_point_shape, NB200_EVALUE, "null shape pointer");
+  DequantizeLinearOp op{};
+  size_t size = 0;
+  NB_TRY(broadcast_view(x_shape, scale_shape, ndim, &op.vs, &size));
+  NB_TRY(broadcast_view(x_shape, zero_point_shape, ndim, &op.vz, nullptr));
+  NB_CHECK(scale && zero_point, NB200_EVALUE, "null parameter pointer");
+  op.scale = scale;
+  op.zp = zero_point;
+  return launch_elementwise(x, y, size, op, as_stream(stream));
+}
+
+int nb200_quantize_linear_backward_f32(const float *dy, const int64_t *x_shape, int ndim, const float *scale,
+                                       const int64_t *scale_shape, float *dx, int accum, void *stream) {
+  NB_CHECK(x_shape && scale_shape && scale, NB200_EVALUE, "null pointer");
+  LinearScaleGrad<true> op{scale, {}};
+  size_t size = 0;
+  NB_TRY(broadcast_view(x_shape, scale_shape, ndim, &op.vs, &size));
+  return launch_gradient(nullptr, dy, dx, size, accum, op, as_stream(stream));
+}
+
+int nb200_dequantize_linear_backward_f32(const float *dy, const int64_t *x_shape, int ndim, const float *scale,
+                                         const int64_t *scale_shape, float *dx, int accum, void *stream) {
+  NB_CHECK(x_shape && scale_shape && scale, NB200_EVALUE, "null pointer");
+  LinearScaleGrad<false> op{scale, {}};
+  size_t size = 0;
+  NB_TRY(broadcast_view(x_shape, scale_shape, ndim, &op.vs, &size));
+  return launch_gradient(nullptr, dy, dx, size, accum, op, as_stream(stream));
 }
 }

@@ -23,6 +23,8 @@ __device__ __forceinline__ float grad_combine(const Op &op, const typename Op::S
   const bool pass = op(x, dy, i, g, st);
   if (kAccum)
     return pass ? __fadd_rn(dx, g) : dx;
+  if (Op::kZeroPlus) // functions defined as (accum ? dx : 0) + g: a negative zero becomes +0
+    return pass ? __fadd_rn(0.0f, g) : 0.0f;
   return pass ? g : 0.0f;
 }
 
@@ -117,6 +119,7 @@ int launch_gradient(const float *x, const float *dy, float *dx, size_t size, int
 // min_max_quantize.cpp:288-294.
 struct PassAllGrad {
   static constexpr bool kNeedsX = false;
+  static constexpr bool kZeroPlus = false;
   struct State {};
   __device__ __forceinline__ State init() const { return State(); }
   __device__ __forceinline__ bool operator()(float, float dy, size_t, float &g, const State &) const {
@@ -128,6 +131,7 @@ struct PassAllGrad {
 // fixed_point_quantize.cpp:81-101: the gradient passes inside [min, max].
 struct FxpGrad {
   static constexpr bool kNeedsX = true;
+  static constexpr bool kZeroPlus = false;
   float maxv, minv;
   struct State {};
   __device__ __forceinline__ State init() const { return State(); }
@@ -144,6 +148,7 @@ struct FxpGrad {
 // (NaN inputs keep c = 1 like the reference, whose comparison with NaN fails).
 struct Pow2Grad {
   static constexpr bool kNeedsX = true;
+  static constexpr bool kZeroPlus = false;
   uint32_t threshold_bits; // c = 0 for threshold_bits < bits(|x|) <= bits(inf)
   int sign;
   struct State {};
@@ -212,6 +217,7 @@ __global__ void minmax_nudged_kernel(size_t Q, const float *qr_min, const float 
 // Gradient w.r.t. x with ste_fine_grained (:268-287): (x >= m) * (x <= M) * dy.
 struct MinMaxGrad {
   static constexpr bool kNeedsX = true;
+  static constexpr bool kZeroPlus = false;
   const float *m, *M;
   size_t Q, inner;
   struct State {

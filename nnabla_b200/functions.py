@@ -707,3 +707,102 @@ def bn_add_relu_fixed_point(a, bn_a, b=None, bn_b=None, eps=1e-05, relu=True, qu
                ctypes.c_int64(Cn), ctypes.c_int64(inner), C.c_float(eps), int(bool(relu)), int(bool(quantize)),
                int(bool(sign)), int(n), C.c_float(delta), C.stream_ptr(a.device))
     return y
+
+
+# ---------------------------------------------------------------------------
+# Sibling quantization functions
+# ---------------------------------------------------------------------------
+
+def _unary(entry, x, outputs):
+    x = _check_input(x)
+    y = _output_like(x, outputs)
+    with torch.cuda.device(x.device):
+        C.call(entry, C.ptr(x), C.ptr(y), C.size_t(x.numel()), C.stream_ptr(x.device))
+    return y
+
+
+def binary_sigmoid(x, n_outputs=-1, outputs=None):
+    """Element-wise binary sigmoid, 1 where x > 0 and 0 elsewhere
+    (python/src/nnabla/functions.py binary_sigmoid; include/nbla/function/binary_sigmoid.hpp:50-52)."""
+    return _unary("nb200_binary_sigmoid_f32", x, outputs)
+
+
+def binary_tanh(x, n_outputs=-1, outputs=None):
+    """Element-wise binary tanh, 1 where x > 0 and -1 elsewhere (include/nbla/function/binary_tanh.hpp:51-52)."""
+    return _unary("nb200_binary_tanh_f32", x, outputs)
+
+
+def _unary_backward(entry, x, dy, accum, dx):
+    x, dy, dx = _grad_buffers(x, dy, dx, accum)
+    with torch.cuda.device(x.device):
+        C.call(entry, C.ptr(x), C.ptr(dy), C.ptr(dx), C.size_t(x.numel()), int(bool(accum)), C.stream_ptr(x.device))
+    return dx
+
+
+def binary_sigmoid_backward(x, dy, accum=False, dx=None):
+    return _unary_backward("nb200_binary_sigmoid_backward_f32", x, dy, accum, dx)
+
+
+def binary_tanh_backward(x, dy, accum=False, dx=None):
+    return _unary_backward("nb200_binary_tanh_backward_f32", x, dy, accum, dx)
+
+
+_ROUND_MODES = {"HALF_AWAY_FROM_ZERO": 0, "HALF_TO_EVEN": 1}
+_QL_DTYPES = {1: 1, 2: 2, "int8": 1, "uint8": 2, torch.int8: 1, torch.uint8: 2}
+
+
+def _linear_params(x, scale, zero_point):
+    x, scale = _check_input(x), _check_input(scale, "scale")
+    zero_point = _check_input(zero_point, "zero_point") if zero_point is not None else None
+    for t in (scale, zero_point):
+        if t is not None and t.dim() != x.dim():
+            raise RuntimeError("Dimensions of inputs must be same (%d, %d)." % (x.dim(), t.dim()))
+    return x, scale, zero_point
+
+
+def quantize_linear(x, scale, zero_point, round_mode="HALF_AWAY_FROM_ZERO", narrow_range=False, dtype=1, n_outputs=-1,
+                    outputs=None):
+    """saturate(round(x / scale) + zero_point) (python/src/nnabla/functions.py quantize_linear;
+    src/nbla/function/generic/quantize_linear.cpp:103-122). As in the reference
+    zero_point is rounded and saturated IN PLACE. dtype: 1 / "int8" = BYTE, 2 / "uint8" = UBYTE."""
+    x, scale, zero_point = _linear_params(x, scale, zero_point)
+    if round_mode not in _ROUND_MODES:
+        raise RuntimeError("round_mode must be HALF_AWAY_FROM_ZERO or HALF_TO_EVEN")
+    if dtype not in _QL_DTYPES:
+        raise C.NB200Error(4, "dtype must be int8 (BYTE) or uint8 (UBYTE)")
+    y = _output_like(x, outputs)
+    with torch.cuda.device(x.device):
+        C.call("nb200_quantize_linear_f32", C.ptr(x), C.i64_array(x.shape), int(x.dim()), C.ptr(scale),
+               C.i64_array(scale.shape), C.ptr(zero_point), C.i64_array(zero_point.shape), C.ptr(y),
+               _ROUND_MODES[round_mode], int(bool(narrow_range)), _QL_DTYPES[dtype], C.stream_ptr(x.device))
+    return y
+
+
+def dequantize_linear(x, scale, zero_point, n_outputs=-1, outputs=None):
+    """(x - zero_point) * scale (src/nbla/function/generic/dequantize_linear.cpp:60-71)."""
+    x, scale, zero_point = _linear_params(x, scale, zero_point)
+    y = _output_like(x, outputs)
+    with torch.cuda.device(x.device):
+        C.call("nb200_dequantize_linear_f32", C.ptr(x), C.i64_array(x.shape), int(x.dim()), C.ptr(scale),
+               C.i64_array(scale.shape), C.ptr(zero_point), C.i64_array(zero_point.shape), C.ptr(y),
+               C.stream_ptr(x.device))
+    return y
+
+
+def _linear_backward(entry, dy, scale, accum, dx):
+    dy, scale, _ = _linear_params(dy, scale, None)
+    _, dy, dx = _grad_buffers(dy, dy, dx, accum)
+    with torch.cuda.device(dy.device):
+        C.call(entry, C.ptr(dy), C.i64_array(dy.shape), int(dy.dim()), C.ptr(scale), C.i64_array(scale.shape),
+               C.ptr(dx), int(bool(accum)), C.stream_ptr(dy.device))
+    return dx
+
+
+def quantize_linear_backward(dy, scale, accum=False, dx=None):
+    """dx (+)= dy / scale (quantize_linear.cpp:137-147); the reference has no gradient for scale or zero point."""
+    return _linear_backward("nb200_quantize_linear_backward_f32", dy, scale, accum, dx)
+
+
+def dequantize_linear_backward(dy, scale, accum=False, dx=None):
+    """dx (+)= dy * scale (dequantize_linear.cpp:92-102)."""
+    return _linear_backward("nb200_dequantize_linear_backward_f32", dy, scale, accum, dx)

@@ -355,3 +355,72 @@ def binary_connect_convolution_backward(x, w, dy, pad=(0, 0), stride=(1, 1), dil
                                         quantize_zero_to=1.0, **kw):
     """binary_connect_convolution.cpp:82-104."""
     return convolution_backward(x, sign(_f(w), quantize_zero_to), dy, pad, stride, dilation, group, **kw)
+
+
+# Sibling quantization functions -------------------------------------------------
+
+def binary_sigmoid(x):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().oracle_binary_act(_p(x), _p(y), ctypes.c_int64(x.size), 0)
+    return y
+
+
+def binary_tanh(x):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().oracle_binary_act(_p(x), _p(y), ctypes.c_int64(x.size), 1)
+    return y
+
+
+def _binary_act_backward(x, dy, tanh_like, accum, dx):
+    x, dy = _f(x), _f(dy)
+    g = np.zeros_like(x) if dx is None else _f(dx).copy().reshape(x.shape)
+    lib().oracle_binary_act_backward(_p(x), _p(dy), _p(g), ctypes.c_int64(x.size), int(tanh_like), int(accum))
+    return g
+
+
+def binary_sigmoid_backward(x, dy, accum=False, dx=None):
+    return _binary_act_backward(x, dy, False, accum, dx)
+
+
+def binary_tanh_backward(x, dy, accum=False, dx=None):
+    return _binary_act_backward(x, dy, True, accum, dx)
+
+
+def quantize_linear(x, scale, zero_point, round_mode="HALF_AWAY_FROM_ZERO", narrow_range=False, dtype=1):
+    """Returns (y, zero_point_after)."""
+    x, scale, zp = _f(x), _f(scale), _f(zero_point).copy()
+    y = np.empty_like(x)
+    L = lib()
+    L.oracle_quantize_linear.restype = ctypes.c_int
+    rc = L.oracle_quantize_linear(_p(x), _shape(x.shape), x.ndim, _p(scale), _shape(scale.shape), _p(zp),
+                                  _shape(zp.shape), _p(y), int(round_mode == "HALF_TO_EVEN"), int(narrow_range),
+                                  int(dtype))
+    if rc != 0:
+        raise ValueError("oracle_quantize_linear: dtype must be 1 (BYTE) or 2 (UBYTE)")
+    return y, zp
+
+
+def dequantize_linear(x, scale, zero_point):
+    x, scale, zp = _f(x), _f(scale), _f(zero_point)
+    y = np.empty_like(x)
+    lib().oracle_dequantize_linear(_p(x), _shape(x.shape), x.ndim, _p(scale), _shape(scale.shape), _p(zp),
+                                   _shape(zp.shape), _p(y))
+    return y
+
+
+def _linear_scale_backward(dy, scale, divide, accum, dx):
+    dy, scale = _f(dy), _f(scale)
+    g = np.zeros_like(dy) if dx is None else _f(dx).copy().reshape(dy.shape)
+    lib().oracle_linear_scale_backward(_p(dy), _shape(dy.shape), dy.ndim, _p(scale), _shape(scale.shape), _p(g),
+                                       int(divide), int(accum))
+    return g
+
+
+def quantize_linear_backward(dy, scale, accum=False, dx=None):
+    return _linear_scale_backward(dy, scale, True, accum, dx)
+
+
+def dequantize_linear_backward(dy, scale, accum=False, dx=None):
+    return _linear_scale_backward(dy, scale, False, accum, dx)

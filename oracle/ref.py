@@ -308,3 +308,45 @@ def binary_connect_convolution_backward(x, w, b, dy, base_axis=1, pad=(0, 0), st
     wb = np.zeros_like(w, dtype=np.float32)
     return _conv_backward("BinaryConnectConvolution", [base_axis, group, quantize_zero_to], [pad, stride, dilation],
                           x, w, [wb], b, dy, propagate_down, accum, grads)
+
+
+# Sibling quantization functions -------------------------------------------------
+
+def binary_sigmoid(x):
+    return forward("BinarySigmoid", [], [], [x])[0][0]
+
+
+def binary_tanh(x):
+    return forward("BinaryTanh", [], [], [x])[0][0]
+
+
+def binary_sigmoid_backward(x, dy, accum=False, dx=None):
+    return backward("BinarySigmoid", [], [], [x], [dy], [True], [accum], [dx])[0][0]
+
+
+def binary_tanh_backward(x, dy, accum=False, dx=None):
+    return backward("BinaryTanh", [], [], [x], [dy], [True], [accum], [dx])[0][0]
+
+
+def quantize_linear(x, scale, zero_point, round_mode="HALF_AWAY_FROM_ZERO", narrow_range=False, dtype=1):
+    """Returns (y, zero_point_after)."""
+    o, i, _ = forward("QuantizeLinear", [round_mode == "HALF_TO_EVEN", narrow_range, dtype], [],
+                      [x, scale, zero_point])
+    return o[0], i[2]
+
+
+def dequantize_linear(x, scale, zero_point):
+    return forward("DequantizeLinear", [], [], [x, scale, zero_point])[0][0]
+
+
+def quantize_linear_backward(x, scale, zero_point, dy, round_mode="HALF_AWAY_FROM_ZERO", narrow_range=False, dtype=1,
+                             accum=False, dx=None):
+    g, _, _ = backward("QuantizeLinear", [round_mode == "HALF_TO_EVEN", narrow_range, dtype], [],
+                       [x, scale, zero_point], [dy], [True, False, False], [accum, False, False], [dx, None, None])
+    return g[0]
+
+
+def dequantize_linear_backward(x, scale, zero_point, dy, accum=False, dx=None):
+    g, _, _ = backward("DequantizeLinear", [], [], [x, scale, zero_point], [dy], [True, False, False],
+                       [accum, False, False], [dx, None, None])
+    return g[0]

@@ -27,7 +27,12 @@
 #include <nbla/function/fixed_point_quantize.hpp>
 #include <nbla/function/global_average_pooling.hpp>
 #include <nbla/function/max_pooling.hpp>
+#include <nbla/function/binary_sigmoid.hpp>
+#include <nbla/function/binary_tanh.hpp>
+#include <nbla/function/dequantize_linear.hpp>
 #include <nbla/function/min_max_quantize.hpp>
+#include <nbla/function/prune.hpp>
+#include <nbla/function/quantize_linear.hpp>
 #include <nbla/function/pow2_quantize.hpp>
 #include <nbla/function/relu.hpp>
 #include <nbla/function/sign.hpp>
@@ -110,6 +115,16 @@ static FunctionPtr make_function(const Context &ctx, const char *op,
     f = create_GlobalAveragePooling(ctx);
   else if (name == "Add2")
     f = create_Add2(ctx, S(0) != 0);
+  else if (name == "BinarySigmoid")
+    f = create_BinarySigmoid(ctx);
+  else if (name == "BinaryTanh")
+    f = create_BinaryTanh(ctx);
+  else if (name == "QuantizeLinear") // scalars: round mode (0 = HALF_AWAY_FROM_ZERO, 1 = HALF_TO_EVEN), narrow_range, dtype
+    f = create_QuantizeLinear(ctx, S(0) != 0 ? "HALF_TO_EVEN" : "HALF_AWAY_FROM_ZERO", S(1) != 0, (int)S(2));
+  else if (name == "DequantizeLinear")
+    f = create_DequantizeLinear(ctx);
+  else if (name == "Prune")
+    f = create_Prune(ctx, (float)S(0));
   else
     NBLA_ERROR(error_code::value, "unknown function %s", op);
 

@@ -139,3 +139,28 @@ def rel_rms(a, b):
     a = np.asarray(a, np.float64)
     b = np.asarray(b, np.float64)
     return float(np.sqrt(np.mean((a - b) ** 2)) / max(np.sqrt(np.mean(b ** 2)), 1e-30))
+
+
+# ---- sibling quantization functions ---------------------------------------------
+def binary_act_input():
+    rng = np.random.RandomState(SEED)
+    x = (rng.randn(2, 3, 4, 37) * 1.5).astype(np.float32)
+    edges = np.array([0.0, -0.0, 1.0, -1.0, 0.99999994, -0.99999994, 1.0000001, np.inf, -np.inf, np.nan, 1e-45, -1e-45],
+                     np.float32)
+    return np.concatenate([x.ravel(), edges])
+
+
+# (x shape, scale shape, zero-point shape)
+QL_SHAPES = [((4, 6, 5, 5), (1, 1, 1, 1), (1, 1, 1, 1)), ((4, 6, 5, 5), (1, 6, 1, 1), (1, 1, 1, 1)),
+             ((4, 6, 5, 5), (1, 6, 1, 1), (1, 6, 1, 1)), ((8, 33), (8, 1), (1, 1))]
+QL_GRID = list(itertools.product(QL_SHAPES, ["HALF_AWAY_FROM_ZERO", "HALF_TO_EVEN"], [False, True], [1, 2]))
+
+
+def quantize_linear_inputs(xs, ss, zs):
+    rng = np.random.RandomState(SEED)
+    x = (rng.randn(*xs) * 40).astype(np.float32)
+    x.reshape(-1)[::7] = np.round(x.reshape(-1)[::7]) + 0.5      # exact halves after division by a power of two
+    scale = (2.0 ** rng.randint(-2, 2, size=ss)).astype(np.float32)
+    scale.reshape(-1)[::2] *= np.float32(1.3)
+    zp = (rng.randn(*zs) * 100 + 0.5 * rng.randint(0, 2, size=zs)).astype(np.float32)
+    return x, scale, zp

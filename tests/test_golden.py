@@ -96,3 +96,24 @@ def test_pow2_backward(i, fine, accum):
 @pytest.mark.parametrize("fine,accum", backward_cases.FLAGS)
 def test_minmax_backward(i, fine, accum):
     backward_cases.check_minmax(oracle, i, fine, accum)
+
+
+# ---- sibling quantization functions against golden_siblings.npz ------------
+import sibling_cases  # noqa: E402
+
+
+@pytest.mark.parametrize("name", ["binary_sigmoid", "binary_tanh"])
+@pytest.mark.parametrize("accum", [False, True])
+def test_sibling_binary(name, accum):
+    sibling_cases.check_binary(oracle, name, accum)
+
+
+@pytest.mark.parametrize("i", range(len(cases.QL_GRID)))
+def test_sibling_quantize_linear(i):
+    sibling_cases.check_quantize_linear(oracle, i)
+
+
+@pytest.mark.parametrize("i", range(len(cases.QL_SHAPES)))
+@pytest.mark.parametrize("accum", [False, True])
+def test_sibling_linear_rest(i, accum):
+    sibling_cases.check_linear_rest(oracle, i, accum)
