@@ -37,7 +37,11 @@
 #include <nbla/function/max_pooling.hpp>
 #include <nbla/function/maximum2.hpp>
 #include <nbla/function/min.hpp>
+#include <nbla/function/binary_sigmoid.hpp>
+#include <nbla/function/binary_tanh.hpp>
+#include <nbla/function/dequantize_linear.hpp>
 #include <nbla/function/min_max_quantize.hpp>
+#include <nbla/function/quantize_linear.hpp>
 #include <nbla/function/minimum2.hpp>
 #include <nbla/function/mul2.hpp>
 #include <nbla/function/mul_scalar.hpp>
@@ -120,6 +124,10 @@ void init_cpu() {
   REG(MaxPooling, ivec, ivec, bool, ivec, bool);
   REG(AveragePooling, ivec, ivec, bool, ivec, bool, bool);
   REG(GlobalAveragePooling);
+  REG(BinarySigmoid);
+  REG(BinaryTanh);
+  REG(QuantizeLinear, const string &, bool, int);
+  REG(DequantizeLinear);
 }
 
 void clear_cpu_memory_cache() {

@@ -27,7 +27,11 @@
 #include <nbla/function/fixed_point_quantize.hpp>
 #include <nbla/function/global_average_pooling.hpp>
 #include <nbla/function/max_pooling.hpp>
+#include <nbla/function/binary_sigmoid.hpp>
+#include <nbla/function/binary_tanh.hpp>
+#include <nbla/function/dequantize_linear.hpp>
 #include <nbla/function/min_max_quantize.hpp>
+#include <nbla/function/quantize_linear.hpp>
 #include <nbla/function/pow2_quantize.hpp>
 #include <nbla/function/relu.hpp>
 #include <nbla/function_registry.hpp>
@@ -270,6 +274,130 @@ protected:
                                                     sq.data(), dy, this->x_min_max_, this->ema_,
                                                     this->ste_fine_grained_, pd, ac, dx, g_min, g_max, nullptr),
                 "MinMaxQuantize backward");
+  }
+};
+
+// ------------------------------------------- sibling quantization functions
+template <typename T> class BinarySigmoidB200 : public BinarySigmoid<T> {
+public:
+  using BinarySigmoid<T>::BinarySigmoid;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    nb200_check(nb200_binary_sigmoid_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), nullptr),
+                "BinarySigmoid");
+  }
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    if (!pd[0])
+      return;
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_), *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    nb200_check(nb200_binary_sigmoid_backward_f32(x, dy, grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(),
+                                                  accum[0], nullptr),
+                "BinarySigmoid backward");
+  }
+};
+
+template <typename T> class BinaryTanhB200 : public BinaryTanh<T> {
+public:
+  using BinaryTanh<T>::BinaryTanh;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    nb200_check(nb200_binary_tanh_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), nullptr),
+                "BinaryTanh");
+  }
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    if (!pd[0])
+      return;
+    enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_), *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    nb200_check(nb200_binary_tanh_backward_f32(x, dy, grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(),
+                                               accum[0], nullptr),
+                "BinaryTanh backward");
+  }
+};
+
+// Shape rules shared by QuantizeLinear / DequantizeLinear (quantize_linear.cpp:27-48).
+void setup_linear_shapes(const Variables &in, const Variables &out) {
+  NBLA_CHECK(in[0]->ndim() == in[1]->ndim() && in[0]->ndim() == in[2]->ndim(), error_code::value,
+             "Dimensions of inputs must be same (%d, %d, %d).", in[0]->ndim(), in[1]->ndim(), in[2]->ndim());
+  for (int i = 0; i < in[0]->ndim(); ++i)
+    for (int k = 1; k <= 2; ++k)
+      NBLA_CHECK(in[k]->shape()[i] == 1 || in[k]->shape()[i] == in[0]->shape()[i], error_code::value,
+                 "Size at %d-th dimension of inputs[%d] (%d) should be 1 or match the size at %d-th dimension of "
+                 "inputs[0] (%d).",
+                 i, k, (int)in[k]->shape()[i], i, (int)in[0]->shape()[i]);
+  out[0]->reshape(in[0]->shape(), true);
+}
+
+template <typename T> class QuantizeLinearB200 : public QuantizeLinear<T> {
+public:
+  using QuantizeLinear<T>::QuantizeLinear;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) { setup_linear_shapes(in, out); }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    NBLA_CHECK(this->round_mode_ == "HALF_AWAY_FROM_ZERO" || this->round_mode_ == "HALF_TO_EVEN", error_code::value,
+               "unknown round_mode %s", this->round_mode_.c_str());
+    const Shape_t sx = in[0]->shape(), ss = in[1]->shape(), sz = in[2]->shape();
+    const float *x = rd(in[0], this->ctx_), *scale = rd(in[1], this->ctx_);
+    float *zp = wr(in[2], this->ctx_, false);
+    nb200_check(nb200_quantize_linear_f32(x, sx.data(), (int)sx.size(), scale, ss.data(), zp, sz.data(),
+                                          wr(out[0], this->ctx_), this->round_mode_ == "HALF_TO_EVEN",
+                                          this->narrow_range_, this->dtype_, nullptr),
+                "QuantizeLinear");
+  }
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    if (!(pd[0] || pd[1] || pd[2]))
+      return;
+    NBLA_CHECK(!pd[1], error_code::not_implemented, "Backward w.r.t. the scale is not supported now.");
+    NBLA_CHECK(!pd[2], error_code::not_implemented, "Backward w.r.t. the zero point is not supported now.");
+    enter(this->ctx_);
+    const Shape_t sx = in[0]->shape(), ss = in[1]->shape();
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_), *scale = rd(in[1], this->ctx_);
+    nb200_check(nb200_quantize_linear_backward_f32(dy, sx.data(), (int)sx.size(), scale, ss.data(),
+                                                   grad_wr(in[0], this->ctx_, true, accum[0]), accum[0], nullptr),
+                "QuantizeLinear backward");
+  }
+};
+
+template <typename T> class DequantizeLinearB200 : public DequantizeLinear<T> {
+public:
+  using DequantizeLinear<T>::DequantizeLinear;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void setup_impl(const Variables &in, const Variables &out) { setup_linear_shapes(in, out); }
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    const Shape_t sx = in[0]->shape(), ss = in[1]->shape(), sz = in[2]->shape();
+    nb200_check(nb200_dequantize_linear_f32(rd(in[0], this->ctx_), sx.data(), (int)sx.size(), rd(in[1], this->ctx_),
+                                            ss.data(), rd(in[2], this->ctx_), sz.data(), wr(out[0], this->ctx_),
+                                            nullptr),
+                "DequantizeLinear");
+  }
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    if (!(pd[0] || pd[1] || pd[2]))
+      return;
+    NBLA_CHECK(!pd[1], error_code::not_implemented, "Backward w.r.t. the scale is not supported now.");
+    NBLA_CHECK(!pd[2], error_code::not_implemented, "Backward w.r.t. the zero point is not supported now.");
+    enter(this->ctx_);
+    const Shape_t sx = in[0]->shape(), ss = in[1]->shape();
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_), *scale = rd(in[1], this->ctx_);
+    nb200_check(nb200_dequantize_linear_backward_f32(dy, sx.data(), (int)sx.size(), scale, ss.data(),
+                                                     grad_wr(in[0], this->ctx_, true, accum[0]), accum[0], nullptr),
+                "DequantizeLinear backward");
   }
 };
 
@@ -712,6 +840,10 @@ void init_b200() {
     NBLA_REGISTER_FUNCTION_IMPL(NAME, NAME##_b200_float, "b200:float", ##__VA_ARGS__);                       \
   }
   REG(FixedPointQuantize, bool, int, float, bool);
+  REG(BinarySigmoid);
+  REG(BinaryTanh);
+  REG(QuantizeLinear, const string &, bool, int);
+  REG(DequantizeLinear);
   REG(Pow2Quantize, bool, bool, int, int, bool);
   REG(MinMaxQuantize, float, bool, bool, bool, float);
   REG(BinaryWeightAffine, int, float);

@@ -23,7 +23,11 @@
 #include <nbla/function/fixed_point_quantize.hpp>
 #include <nbla/function/global_average_pooling.hpp>
 #include <nbla/function/max_pooling.hpp>
+#include <nbla/function/binary_sigmoid.hpp>
+#include <nbla/function/binary_tanh.hpp>
+#include <nbla/function/dequantize_linear.hpp>
 #include <nbla/function/min_max_quantize.hpp>
+#include <nbla/function/quantize_linear.hpp>
 #include <nbla/function/pow2_quantize.hpp>
 #include <nbla/function/relu.hpp>
 
@@ -77,6 +81,14 @@ FunctionPtr create(const std::string &name, const Context &ctx, const double *s,
     return create_GlobalAveragePooling(ctx);
   if (name == "Add2")
     return create_Add2(ctx, S(0) != 0);
+  if (name == "BinarySigmoid")
+    return create_BinarySigmoid(ctx);
+  if (name == "BinaryTanh")
+    return create_BinaryTanh(ctx);
+  if (name == "QuantizeLinear") // scalars: round mode (0 = HALF_AWAY_FROM_ZERO, 1 = HALF_TO_EVEN), narrow_range, dtype
+    return create_QuantizeLinear(ctx, S(0) != 0 ? "HALF_TO_EVEN" : "HALF_AWAY_FROM_ZERO", S(1) != 0, (int)S(2));
+  if (name == "DequantizeLinear")
+    return create_DequantizeLinear(ctx);
   NBLA_ERROR(error_code::value, "unknown function %s", name.c_str());
 }
 } // namespace

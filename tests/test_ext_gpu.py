@@ -227,3 +227,37 @@ def test_binary_convolutions_backward(xs, ws, pad, stride, dil, grp, accum):
                 assert cases.rel_rms(g[0][i], c[0][i]) < 1e-5, (op, i)
             else:
                 assert np.array_equal(bits(g[0][i]), bits(c[0][i])), (op, i)
+
+
+# ---- sibling quantization functions through nnabla's registry ---------------
+
+@pytest.mark.parametrize("op", ["BinarySigmoid", "BinaryTanh"])
+@pytest.mark.parametrize("accum", [False, True])
+def test_binary_activations(op, accum):
+    x = cases.binary_act_input()
+    dy, dx0 = cases.grad_inputs(x)
+    c, g = both(op, [], [], [x])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+    c, g = both_backward(op, [], [x], dy, [True], [accum], [dx0])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+
+
+@pytest.mark.parametrize("shapes,round_mode,narrow,dtype", cases.QL_GRID[::3])
+def test_quantize_linear(shapes, round_mode, narrow, dtype):
+    x, scale, zp = cases.quantize_linear_inputs(*shapes)
+    c, g = both("QuantizeLinear", [round_mode == "HALF_TO_EVEN", narrow, dtype], [], [x, scale, zp])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+    assert np.array_equal(bits(g[1][2]), bits(c[1][2]))  # zero point rounded and saturated in place
+
+
+@pytest.mark.parametrize("shapes", cases.QL_SHAPES)
+@pytest.mark.parametrize("accum", [False, True])
+def test_linear_backward_and_dequantize(shapes, accum):
+    x, scale, zp = cases.quantize_linear_inputs(*shapes)
+    dy, dx0 = cases.grad_inputs(x)
+    c, g = both("DequantizeLinear", [], [], [x, scale, zp])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+    g0 = [dx0, np.zeros_like(scale), np.zeros_like(zp)]
+    for op, scalars in (("QuantizeLinear", [0, 0, 1]), ("DequantizeLinear", [])):
+        c, g = both_backward(op, scalars, [x, scale, zp], dy, [True, False, False], [accum, False, False], g0)
+        assert np.array_equal(bits(g[0][0]), bits(c[0][0])), op
