@@ -187,6 +187,13 @@ int nb200_quantize_linear_backward_f32(const float *dy, const int64_t *x_shape, 
 int nb200_dequantize_linear_backward_f32(const float *dy, const int64_t *x_shape, int ndim, const float *scale,
                                          const int64_t *scale_shape, float *dx, int accum, void *stream);
 
+/* Prune<float>::forward_impl (src/nbla/function/generic/prune.cpp:38-72): y = |x| < t ? 0 : x
+ * with t the (int)((size - 1) * rate)-th smallest |x| (+ 1 when rate == 1),
+ * found by a radix select on the device instead of the reference's sort.
+ * backward (prune.cpp:74-88): the gradient passes unchanged. */
+int nb200_prune_f32(const float *x, float *y, size_t size, float rate, void *stream);
+int nb200_prune_backward_f32(const float *dy, float *dx, size_t size, int accum, void *stream);
+
 /* ---- inference-time fusion ---------------------------------------------------------
  * y = FixedPointQuantize(ReLU(BN_a(a) [+ BN_b(b) | + b])) over [outer, channels, inner]
  * tensors in one pass: BatchNormalization::forward_impl_global

@@ -1028,4 +1028,12 @@ int nb200_dequantize_linear_backward_f32(const float *dy, const int64_t *x_shape
   NB_TRY(broadcast_view(x_shape, scale_shape, ndim, &op.vs, &size));
   return launch_gradient(nullptr, dy, dx, size, accum, op, as_stream(stream));
 }
+
+int nb200_prune_f32(const float *x, float *y, size_t size, float rate, void *stream) {
+  return prune_forward(x, y, size, rate, as_stream(stream));
+}
+
+int nb200_prune_backward_f32(const float *dy, float *dx, size_t size, int accum, void *stream) {
+  return launch_gradient(nullptr, dy, dx, size, accum, PassAllGrad(), as_stream(stream));
+}
 }

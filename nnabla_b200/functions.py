@@ -806,3 +806,22 @@ def quantize_linear_backward(dy, scale, accum=False, dx=None):
 def dequantize_linear_backward(dy, scale, accum=False, dx=None):
     """dx (+)= dy * scale (dequantize_linear.cpp:92-102)."""
     return _linear_backward("nb200_dequantize_linear_backward_f32", dy, scale, accum, dx)
+
+
+def prune(x, rate=0.9, n_outputs=-1, outputs=None):
+    """Prune the input: values whose magnitude is below the rate-quantile of
+    |x| become zero (python/src/nnabla/functions.py prune; src/nbla/function/generic/prune.cpp:38-72)."""
+    x = _check_input(x)
+    y = _output_like(x, outputs)
+    with torch.cuda.device(x.device):
+        C.call("nb200_prune_f32", C.ptr(x), C.ptr(y), C.size_t(x.numel()), C.c_float(rate), C.stream_ptr(x.device))
+    return y
+
+
+def prune_backward(dy, accum=False, dx=None):
+    """Prune::backward_impl (prune.cpp:74-88): the gradient passes unchanged."""
+    _, dy, dx = _grad_buffers(dy, dy, dx, accum)
+    with torch.cuda.device(dy.device):
+        C.call("nb200_prune_backward_f32", C.ptr(dy), C.ptr(dx), C.size_t(dy.numel()), int(bool(accum)),
+               C.stream_ptr(dy.device))
+    return dx

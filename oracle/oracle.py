@@ -424,3 +424,10 @@ def quantize_linear_backward(dy, scale, accum=False, dx=None):
 
 def dequantize_linear_backward(dy, scale, accum=False, dx=None):
     return _linear_scale_backward(dy, scale, False, accum, dx)
+
+
+def prune(x, rate=0.9):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().oracle_prune(_p(x), _p(y), ctypes.c_int64(x.size), ctypes.c_float(rate))
+    return y

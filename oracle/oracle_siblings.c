@@ -115,3 +115,28 @@ void oracle_linear_scale_backward(const float *dy, const int64_t *xs, int nd, co
     dx[i] = accum ? dx[i] + g : g;
   }
 }
+
+/* src/nbla/function/generic/prune.cpp:38-72: the threshold is the
+ * (int)((n - 1) * rate)-th smallest magnitude (+ 1 when rate == 1). */
+#include <stdlib.h>
+#include <string.h>
+static int cmp_abs(const void *a, const void *b) {
+  float x = fabsf(*(const float *)a), y = fabsf(*(const float *)b);
+  return (x > y) - (x < y);
+}
+int oracle_prune(const float *x, float *y, int64_t n, float rate) {
+  if (n == 0)
+    return 0;
+  float *buf = (float *)malloc(sizeof(float) * (size_t)n);
+  if (!buf)
+    return -1;
+  memcpy(buf, x, sizeof(float) * (size_t)n);
+  qsort(buf, (size_t)n, sizeof(float), cmp_abs);
+  int idx = (int)(((int)n - 1) * rate);
+  float t = fabsf(buf[idx]);
+  t += rate == 1.0 ? 1.0 : 0.0;
+  free(buf);
+  for (int64_t i = 0; i < n; ++i)
+    y[i] = (fabsf(x[i]) < t) ? 0.0f : x[i];
+  return 0;
+}

@@ -350,3 +350,7 @@ def dequantize_linear_backward(x, scale, zero_point, dy, accum=False, dx=None):
     g, _, _ = backward("DequantizeLinear", [], [], [x, scale, zero_point], [dy], [True, False, False],
                        [accum, False, False], [dx, None, None])
     return g[0]
+
+
+def prune(x, rate=0.9):
+    return forward("Prune", [rate], [], [x])[0][0]

@@ -44,3 +44,15 @@ def test_linear_backward_and_dequantize(shapes, accum):
     assert np.array_equal(bits(oracle.quantize_linear_backward(dy, scale, accum, dx0)), bits(want))
     want = ref.dequantize_linear_backward(x, scale, zp, dy, accum=accum, dx=dx0)
     assert np.array_equal(bits(oracle.dequantize_linear_backward(dy, scale, accum, dx0)), bits(want))
+
+
+@pytest.mark.parametrize("rate", [0.0, 0.3, 0.9, 0.999, 1.0])
+@pytest.mark.parametrize("n", [1, 2, 1000, 4097])
+def test_prune(rate, n):
+    rng = np.random.RandomState(n)
+    x = rng.randn(n).astype(np.float32)
+    x[::5] = -np.abs(x[::5])
+    if n > 10:
+        x[3] = x[7] = 0.0          # ties and zeros
+        x[9] = -x[8]
+    assert np.array_equal(bits(oracle.prune(x, rate)), bits(ref.prune(x, rate)))

@@ -104,3 +104,28 @@ def test_sibling_argument_errors(F):
         F.quantize_linear(x, torch.ones(1, device="cuda"), s.clone())
     with pytest.raises(RuntimeError):
         F.quantize_linear(x, torch.ones(2, 2, device="cuda"), s.clone())
+
+
+@pytest.mark.parametrize("rate", [0.0, 0.3, 0.9, 0.999, 1.0])
+@pytest.mark.parametrize("n", [1, 2, 1000, 4097, 1 << 20])
+def test_prune(F, rate, n):
+    rng = np.random.RandomState(n)
+    x = rng.randn(n).astype(np.float32)
+    x[::5] = -np.abs(x[::5])
+    if n > 10:
+        x[3] = x[7] = 0.0
+        x[9] = -x[8]
+    got = F.prune(dev(x), rate)
+    assert np.array_equal(bits(host(got)), bits(oracle.prune(x, rate)))
+
+
+def test_prune_special_values_and_backward(F):
+    x = np.array([0.0, -0.0, 1e-45, -1e-45, 3e38, -3e38, np.inf, -np.inf, 1.0, -1.0, 0.5, 2.0], np.float32)
+    for rate in (0.2, 0.5, 0.95):
+        assert np.array_equal(bits(host(F.prune(dev(x), rate))), bits(oracle.prune(x, rate)))
+    dy = np.arange(12, dtype=np.float32)
+    dx0 = np.ones(12, np.float32)
+    assert np.array_equal(host(F.prune_backward(dev(dy))), dy)
+    assert np.array_equal(host(F.prune_backward(dev(dy), True, dev(dx0))), dy + 1)
+    with pytest.raises(RuntimeError):
+        F.prune(dev(x), 1.5)
