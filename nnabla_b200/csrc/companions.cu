@@ -121,6 +121,52 @@ __global__ void __launch_bounds__(kThreads) max_pooling_kernel(const float *__re
   }
 }
 
+// The same for the 3 x 3 window, stride 2, padding 1 of residual networks when
+// W and Wo are multiples of 4 (16-byte aligned rows): one thread produces four
+// adjacent outputs from nine input columns per row (one scalar + two 128-bit
+// loads), scanning every window in the reference's order (rows outer, columns
+// inner, first maximum wins) so that ties between +0 and -0 resolve alike.
+__global__ void __launch_bounds__(kThreads) max_pooling_3x3s2_kernel(const float *__restrict__ x, size_t maps, int H,
+                                                                     int W, int Ho, int Wo, float *__restrict__ y) {
+  const int Wo4 = Wo / 4;
+  const size_t total = maps * Ho * Wo4;
+  const size_t stride = (size_t)gridDim.x * kThreads;
+  for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
+    const int ox4 = (int)(i % Wo4);
+    const int oy = (int)((i / Wo4) % Ho);
+    const size_t m = i / ((size_t)Wo4 * Ho);
+    const int y0 = max(2 * oy - 1, 0), y1 = min(2 * oy + 2, H);
+    const float *xm = x + m * (size_t)H * W + 8 * ox4;
+    float best[4];
+    bool first = true;
+    for (int iy = y0; iy < y1; ++iy) {
+      const float *row = xm + (size_t)iy * W;
+      float r[9];
+      r[0] = ox4 > 0 ? __ldg(row - 1) : 0.0f;
+      const float4 a = __ldcs(reinterpret_cast<const float4 *>(row));
+      const float4 b = __ldcs(reinterpret_cast<const float4 *>(row) + 1);
+      r[1] = a.x, r[2] = a.y, r[3] = a.z, r[4] = a.w, r[5] = b.x, r[6] = b.y, r[7] = b.z, r[8] = b.w;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int t = 0; t < 3; ++t) {
+          if (j == 0 && t == 0 && ox4 == 0)
+            continue; // column -1 is padding
+          const float v = r[2 * j + t];
+          // the first element of a window initialises it (for j = 0 at the left edge that is t = 1)
+          const bool starts = first && (t == 0 || (j == 0 && t == 1 && ox4 == 0));
+          if (starts)
+            best[j] = v;
+          else if (best[j] < v)
+            best[j] = v;
+        }
+      }
+      first = false;
+    }
+    __stcs(reinterpret_cast<float4 *>(y + (m * Ho + oy) * (size_t)Wo) + ox4, make_float4(best[0], best[1], best[2], best[3]));
+  }
+}
+
 // GlobalAveragePooling (src/nbla/function/generic/global_average_pooling.cpp):
 // std::accumulate in ascending order, then one division; one thread per map
 // keeps that order.
@@ -288,6 +334,126 @@ __global__ void __launch_bounds__(kThreads) direct_conv_window_kernel(const floa
   }
 }
 
+// Tile-staged form of the window kernel for a whole output-row band: the block
+// first copies the input rows its band needs into shared memory with coalesced
+// loads and explicit zero padding (so the inner loop has no bounds checks and
+// no scattered global loads: with per-thread windows the 14-float stride
+// between lanes made every load touch 32 sectors and the load/store unit, not
+// the FMA pipes, set the pace), then loops over the output maps OT at a time,
+// reusing the staged input for all of them. Threads are (band row, pixel
+// phase): a thread's PX pixels are Wo / PX apart so that a warp's store covers
+// runs of consecutive pixels; weights of all maps sit in shared memory as
+// [map group][k][OT].
+template <int OT, int PX, int KW, int SW, bool kPairs>
+__global__ void __launch_bounds__(kThreads) direct_conv_tile_kernel(const float *__restrict__ x,
+                                                                    const float *__restrict__ w,
+                                                                    const float *__restrict__ bias, int C, int H, int W,
+                                                                    int Ko, int kh, int ph, int pw, int sh, int Ho,
+                                                                    int Wo, int rows, int in_rows, int Wp,
+                                                                    float *__restrict__ y) {
+  constexpr int kLeft = 4;
+  extern __shared__ float4 s_all4[];
+  float *s_w = reinterpret_cast<float *>(s_all4);   // [Ko / OT][C * kh * KW][OT]
+  const int Kd = C * kh * KW;
+  const int o_groups = (Ko + OT - 1) / OT;
+  float *s_x = s_w + (size_t)o_groups * Kd * OT;     // [C][in_rows][Wp]
+  const int n = blockIdx.z;
+  const int oy0 = blockIdx.x * rows;
+  for (int i = threadIdx.x; i < o_groups * OT * Kd; i += blockDim.x) {
+    const int o = i / Kd, k = i - o * Kd;
+    s_w[((size_t)(o / OT) * Kd + k) * OT + (o % OT)] = (o < Ko) ? w[(size_t)o * Kd + k] : 0.0f;
+  }
+  // Input band: image column ix sits at shared column ix + kLeft (kLeft = 4 keeps the
+  // 128-bit stores aligned; Wp is a multiple of 4); everything outside the image is zero.
+  const float *xn = x + (size_t)n * C * H * W;
+  const int iy_base = oy0 * sh - ph;
+  const int W4 = W / 4, edge = Wp - kLeft - W; // zero columns right of the image
+  for (int i = threadIdx.x; i < C * in_rows * (kLeft + edge); i += blockDim.x) {
+    const int e = i % (kLeft + edge), rr = i / (kLeft + edge);
+    s_x[(size_t)rr * Wp + (e < kLeft ? e : W + e)] = 0.0f;
+  }
+#pragma unroll 4
+  for (int i = threadIdx.x; i < C * in_rows * W4; i += blockDim.x) {
+    const int q = i % W4, rr = i / W4;
+    const int r = rr % in_rows, c = rr / in_rows;
+    const int iy = iy_base + r;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (iy >= 0 && iy < H)
+      v = __ldg(reinterpret_cast<const float4 *>(xn + ((size_t)c * H + iy) * W) + q);
+    *reinterpret_cast<float4 *>(s_x + (size_t)rr * Wp + kLeft + 4 * q) = v;
+  }
+  __syncthreads();
+  // A thread owns the pixels gx, gx + groups_x, gx + 2 groups_x, ... of its row, so
+  // that neighbouring lanes store neighbouring pixels (whole sectors per store).
+  const int groups_x = Wo / PX;
+  const int row_local = threadIdx.x / groups_x, gx = threadIdx.x - row_local * groups_x;
+  const int oy = oy0 + row_local;
+  if (row_local >= rows || oy >= Ho)
+    return;
+  for (int og = 0; og < o_groups; ++og) {
+    float acc[OT][PX];
+#pragma unroll
+    for (int t = 0; t < OT; ++t)
+#pragma unroll
+      for (int p = 0; p < PX; ++p)
+        acc[t][p] = 0.0f;
+    const float4 *wg = reinterpret_cast<const float4 *>(s_w + (size_t)og * Kd * OT);
+    int k = 0;
+    for (int c = 0; c < C; ++c)
+      for (int ky = 0; ky < kh; ++ky, k += KW) {
+        // first input column of pixel ox is ox * SW - pw, i.e. shared column ox * SW + kLeft - pw
+        const float *srow = s_x + ((size_t)c * in_rows + row_local * sh + ky) * Wp + gx * SW + (kLeft - pw);
+        float v[PX][KW];
+#pragma unroll
+        for (int p = 0; p < PX; ++p) {
+          const float *sp = srow + p * groups_x * SW;
+          if (kPairs) {
+            // (kLeft - pw) odd and SW even: sp + 1 is 8-byte aligned, so taps 1.. load in pairs
+            v[p][0] = sp[0];
+#pragma unroll
+            for (int kx = 1; kx + 1 < KW; kx += 2) {
+              const float2 t2 = *reinterpret_cast<const float2 *>(sp + kx);
+              v[p][kx] = t2.x;
+              v[p][kx + 1] = t2.y;
+            }
+            if (KW % 2 == 0)
+              v[p][KW - 1] = sp[KW - 1];
+          } else {
+#pragma unroll
+            for (int kx = 0; kx < KW; ++kx)
+              v[p][kx] = sp[kx];
+          }
+        }
+#pragma unroll
+        for (int kx = 0; kx < KW; ++kx) {
+#pragma unroll
+          for (int q = 0; q < OT / 4; ++q) {
+            const float4 wv = wg[(k + kx) * (OT / 4) + q];
+#pragma unroll
+            for (int p = 0; p < PX; ++p) {
+              const float xv = v[p][kx];
+              acc[4 * q + 0][p] = fmaf(wv.x, xv, acc[4 * q + 0][p]);
+              acc[4 * q + 1][p] = fmaf(wv.y, xv, acc[4 * q + 1][p]);
+              acc[4 * q + 2][p] = fmaf(wv.z, xv, acc[4 * q + 2][p]);
+              acc[4 * q + 3][p] = fmaf(wv.w, xv, acc[4 * q + 3][p]);
+            }
+          }
+        }
+      }
+#pragma unroll
+    for (int t = 0; t < OT; ++t) {
+      const int o = og * OT + t;
+      if (o >= Ko)
+        continue;
+      const float b = bias ? bias[o] : 0.0f;
+      float *yo = y + (((size_t)n * Ko + o) * Ho + oy) * Wo + gx;
+#pragma unroll
+      for (int p = 0; p < PX; ++p)
+        yo[p * groups_x] = bias ? __fadd_rn(acc[t][p], b) : acc[t][p];
+    }
+  }
+}
+
 } // namespace
 } // namespace nb200
 
@@ -355,8 +521,15 @@ int nb200_max_pooling_f32(const float *x, float *y, int64_t maps, int height, in
   if (total == 0)
     return NB200_OK;
   NB_CHECK(x && y, NB200_EVALUE, "null data pointer");
-  max_pooling_kernel<<<grid_for(total, 2), kThreads, 0, as_stream(stream)>>>(
-      x, (size_t)maps, height, width, Ho, Wo, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, y);
+  const bool fast = kernel_h == 3 && kernel_w == 3 && stride_h == 2 && stride_w == 2 && pad_h == 1 && pad_w == 1 &&
+                    width % 4 == 0 && Wo % 4 == 0 && 2 * Wo == width &&
+                    ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  if (fast)
+    max_pooling_3x3s2_kernel<<<grid_for(total / 4, 1), kThreads, 0, as_stream(stream)>>>(x, (size_t)maps, height,
+                                                                                         width, Ho, Wo, y);
+  else
+    max_pooling_kernel<<<grid_for(total, 2), kThreads, 0, as_stream(stream)>>>(
+        x, (size_t)maps, height, width, Ho, Wo, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, y);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }
@@ -396,6 +569,45 @@ int nb200_convolution_f32(const float *x, const float *w, const float *bias, flo
   if (kernel_w == 7 && stride_w == 2 && dilation_w == 1) {
     // Seven pixels per thread when the output width allows it: fewer shared-memory
     // weight reads per multiply-add (the limiter with four), no idle lanes at Wo = 112.
+    // Whole bands of output rows per block with the input staged in shared memory, when
+    // the pixel groups of a band fill the block and the staged rows fit.
+    if (Wo % 7 == 0 && dilation_h == 1 && Wo / 7 <= kThreads) {
+      constexpr int PX7 = 7;
+      const int groups_x = Wo / PX7;
+      // (128-thread blocks, two per SM, were slower: every block stages all the weights again)
+      const int block_threads = kThreads;
+      int rows = block_threads / groups_x;
+      rows = rows > Ho ? Ho : rows;
+      const int in_rows = (rows - 1) * stride_h + kernel_h;
+      // shared row: 4 zero columns, the image row, then zeros up to the last column any window reads
+      int Wp = 4 + width;
+      if (Wp < (Wo - 1) * 2 + 7 + 4 - pad_w)
+        Wp = (Wo - 1) * 2 + 7 + 4 - pad_w;
+      Wp = (Wp + 3) / 4 * 4;
+      const int o_groups = (outmaps + OT - 1) / OT;
+      const size_t tile_smem = ((size_t)o_groups * OT * channels * kernel_h * 7 + (size_t)channels * in_rows * Wp) *
+                               sizeof(float);
+      // (weights take o_groups * OT * C * kh * 7 floats, a multiple of 4: the band stays 16-byte aligned)
+      if (tile_smem <= 200 * 1024 && (Ho + rows - 1) / rows <= 65535 && pad_w <= 4 && width % 4 == 0 &&
+          (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        // taps pair up into 64-bit shared loads when the first tap of every pixel sits at an odd column
+        const bool pairs = ((4 - pad_w) & 1) == 1;
+        auto kernel = pairs ? direct_conv_tile_kernel<OT, PX7, 7, 2, true> : direct_conv_tile_kernel<OT, PX7, 7, 2, false>;
+        static bool configured[64][2];
+        int dev = 0;
+        NB_CUDA(cudaGetDevice(&dev));
+        if (!configured[dev & 63][pairs]) {
+          NB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+          configured[dev & 63][pairs] = true;
+        }
+        const dim3 grid_t((Ho + rows - 1) / rows, 1, batch);
+        kernel<<<grid_t, block_threads, tile_smem, as_stream(stream)>>>(x, w, bias, channels, height, width, outmaps,
+                                                                  kernel_h, pad_h, pad_w, stride_h, Ho, Wo, rows,
+                                                                  in_rows, Wp, y);
+        NB_LAUNCH_CHECK();
+        return NB200_OK;
+      }
+    }
     if (Wo % 7 == 0) {
       constexpr int PX7 = 7;
       const int groups7 = Ho * (Wo / PX7);

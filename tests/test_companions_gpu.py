@@ -55,6 +55,11 @@ def test_pooling(F, k, s, p, ib):
 
 
 @pytest.mark.parametrize("xs,ws,pad,stride", [((2, 3, 32, 32), (64, 3, 7, 7), (3, 3), (2, 2)),
+                                              ((2, 3, 56, 56), (64, 3, 7, 7), (3, 3), (2, 2)),   # band kernel, one band
+                                              ((1, 3, 224, 224), (64, 3, 7, 7), (3, 3), (2, 2)),  # band kernel, 7 bands
+                                              ((2, 2, 30, 28), (20, 2, 5, 7), (2, 3), (3, 2)),    # ragged maps and rows
+                                              ((1, 3, 27, 29), (8, 3, 7, 7), (3, 1), (2, 2)),     # 7 does not divide Wo
+
                                               ((1, 3, 17, 19), (20, 3, 3, 3), (1, 1), (1, 1)),
                                               ((2, 4, 9, 9), (5, 4, 1, 1), (0, 0), (2, 2))])
 def test_full_precision_convolution(F, xs, ws, pad, stride):
@@ -66,3 +71,17 @@ def test_full_precision_convolution(F, xs, ws, pad, stride):
     want = oracle.convolution(x, w, b, pad, stride)
     assert y.shape == want.shape
     assert cases.rel_rms(y, want) < 1e-6  # fused multiply-adds: fp32 rounding differs from the separate mul/add of the oracle
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 16, 16), (1, 4, 13, 24), (3, 2, 8, 8), (1, 1, 56, 112)])
+@pytest.mark.parametrize("ib", [True, False])
+def test_pooling_3x3_stride2_vector_path(F, shape, ib):
+    """Widths that take the four-outputs-per-thread kernel; zeros of both signs
+    and repeated values make the first-maximum-wins rule visible."""
+    rng = np.random.RandomState(sum(shape))
+    x = rng.randn(*shape).astype(np.float32)
+    x[rng.rand(*shape) < 0.3] = 0.0
+    x[rng.rand(*shape) < 0.2] = -0.0
+    x = np.minimum(x, 0.0) if shape[0] == 3 else x          # all windows hold only zeros and negatives
+    got = F.max_pooling(dev(x), (3, 3), (2, 2), ib, (1, 1))
+    assert np.array_equal(bits(host(got)), bits(oracle.max_pooling(x, (3, 3), (2, 2), ib, (1, 1))))
