@@ -250,6 +250,14 @@ def run_extras(args, rank, world, barrier):
     ms_q = maxr(time_gpu(lambda: (F.fixed_point_quantize_with_codes(x, True, 8, 2.0 ** -5),
                                   F.fixed_point_quantize_with_codes(w, True, 8, 2.0 ** -10)), 10))
     entry["ms_quantize_x_and_w"] = ms_q
+    try:  # the library's int8 GEMM on the same codes, for context only (int32 output, no scaling, no bias)
+        wct = wc.t().contiguous().t()  # column-major B, the layout the library wants
+        ms_lib = maxr(time_gpu(lambda: torch._int_mm(xc, wct), 20))
+        entry["library_int8_gemm_ms"] = ms_lib
+        entry["library_int8_tops_whole_job"] = 2 * M * K * N / ms_lib / 1e9
+    except Exception as e:  # noqa: BLE001 - the comparison is optional
+        entry["library_int8_gemm_ms"] = None
+        entry["library_int8_note"] = str(e)[:100]
     if world > 1:
         def gemm_and_gather():
             yy = F.affine_from_codes(xc, wc, 2.0 ** -5, 2.0 ** -10, b)
