@@ -41,6 +41,7 @@
 #include <nbla/function/binary_tanh.hpp>
 #include <nbla/function/dequantize_linear.hpp>
 #include <nbla/function/min_max_quantize.hpp>
+#include <nbla/function/prune.hpp>
 #include <nbla/function/quantize_linear.hpp>
 #include <nbla/function/minimum2.hpp>
 #include <nbla/function/mul2.hpp>
@@ -128,6 +129,7 @@ void init_cpu() {
   REG(BinaryTanh);
   REG(QuantizeLinear, const string &, bool, int);
   REG(DequantizeLinear);
+  REG(Prune, float);
 }
 
 void clear_cpu_memory_cache() {

@@ -31,6 +31,7 @@
 #include <nbla/function/binary_tanh.hpp>
 #include <nbla/function/dequantize_linear.hpp>
 #include <nbla/function/min_max_quantize.hpp>
+#include <nbla/function/prune.hpp>
 #include <nbla/function/quantize_linear.hpp>
 #include <nbla/function/pow2_quantize.hpp>
 #include <nbla/function/relu.hpp>
@@ -321,6 +322,28 @@ protected:
     nb200_check(nb200_binary_tanh_backward_f32(x, dy, grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(),
                                                accum[0], nullptr),
                 "BinaryTanh backward");
+  }
+};
+
+template <typename T> class PruneB200 : public Prune<T> {
+public:
+  using Prune<T>::Prune;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    enter(this->ctx_);
+    nb200_check(nb200_prune_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), this->rate_, nullptr),
+                "Prune");
+  }
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    if (!pd[0])
+      return;
+    enter(this->ctx_);
+    nb200_check(nb200_prune_backward_f32(out[0]->get_grad_pointer<float>(this->ctx_),
+                                         grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(), accum[0], nullptr),
+                "Prune backward");
   }
 };
 
@@ -844,6 +867,7 @@ void init_b200() {
   REG(BinaryTanh);
   REG(QuantizeLinear, const string &, bool, int);
   REG(DequantizeLinear);
+  REG(Prune, float);
   REG(Pow2Quantize, bool, bool, int, int, bool);
   REG(MinMaxQuantize, float, bool, bool, bool, float);
   REG(BinaryWeightAffine, int, float);

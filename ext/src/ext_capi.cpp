@@ -27,6 +27,7 @@
 #include <nbla/function/binary_tanh.hpp>
 #include <nbla/function/dequantize_linear.hpp>
 #include <nbla/function/min_max_quantize.hpp>
+#include <nbla/function/prune.hpp>
 #include <nbla/function/quantize_linear.hpp>
 #include <nbla/function/pow2_quantize.hpp>
 #include <nbla/function/relu.hpp>
@@ -89,6 +90,8 @@ FunctionPtr create(const std::string &name, const Context &ctx, const double *s,
     return create_QuantizeLinear(ctx, S(0) != 0 ? "HALF_TO_EVEN" : "HALF_AWAY_FROM_ZERO", S(1) != 0, (int)S(2));
   if (name == "DequantizeLinear")
     return create_DequantizeLinear(ctx);
+  if (name == "Prune")
+    return create_Prune(ctx, (float)S(0));
   NBLA_ERROR(error_code::value, "unknown function %s", name.c_str());
 }
 } // namespace

@@ -261,3 +261,16 @@ def test_linear_backward_and_dequantize(shapes, accum):
     for op, scalars in (("QuantizeLinear", [0, 0, 1]), ("DequantizeLinear", [])):
         c, g = both_backward(op, scalars, [x, scale, zp], dy, [True, False, False], [accum, False, False], g0)
         assert np.array_equal(bits(g[0][0]), bits(c[0][0])), op
+
+
+@pytest.mark.parametrize("rate", [0.0, 0.5, 0.9, 1.0])
+def test_prune(rate):
+    rng = np.random.RandomState(5)
+    x = rng.randn(3, 7, 11).astype(np.float32)
+    x.reshape(-1)[::9] = 0.0
+    dy, dx0 = cases.grad_inputs(x)
+    c, g = both("Prune", [rate], [], [x])
+    assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
+    for accum in (False, True):
+        c, g = both_backward("Prune", [rate], [x], dy, [True], [accum], [dx0])
+        assert np.array_equal(bits(g[0][0]), bits(c[0][0]))
