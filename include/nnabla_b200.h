@@ -255,6 +255,15 @@ int nb200_binary_connect_convolution_backward_f32(const float *x, const float *w
                                                   int dilation_w, int group, int accum_dx, int accum_dw,
                                                   int accum_db, float activation_delta, void *stream);
 
+/* Weight and bias gradients of the full-precision Convolution (the network
+ * stem; convolution.cpp:199-300): dw (+)= correlation of x with dy, db (+)=
+ * sums of dy. The gradient w.r.t. x of a full-precision convolution is not
+ * provided (a first layer does not need it). */
+int nb200_convolution_backward_f32(const float *x, const float *dy, float *dw, float *db, int batch, int channels,
+                                   int height, int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                   int pad_w, int stride_h, int stride_w, int dilation_h, int dilation_w, int group,
+                                   int accum_dw, int accum_db, void *stream);
+
 /* ---- quantizer backward passes (straight-through estimators) -------------------
  * dx (+)= gradient for n elements; accum != 0 adds to dx (elements that pass no
  * gradient are left untouched), accum == 0 overwrites (zero where blocked),

@@ -457,4 +457,14 @@ int nb200_binary_weight_convolution_fused_f32(const float *x, const float *w, fl
                  dilation_h, dilation_w, group, 0, 0, 0, 0};
   return binary_convolution(x, w, wb, alpha, bias, y, g, quantize_zero_to, activation_delta, as_stream(stream), &post);
 }
+
+int nb200_convolution_backward_f32(const float *x, const float *dy, float *dw, float *db, int batch, int channels,
+                                   int height, int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                   int pad_w, int stride_h, int stride_w, int dilation_h, int dilation_w, int group,
+                                   int accum_dw, int accum_db, void *stream) {
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, group, 0, 0, 0, 0};
+  return convolution_backward(x, nullptr, nullptr, dy, nullptr, dw, db, g, 0, accum_dw, accum_db, 0.0f,
+                              as_stream(stream));
+}
 }

@@ -103,3 +103,21 @@ def test_partial_propagation(F):
     want = oracle.binary_weight_convolution_backward(x, w, dy, pad, stride, dil, grp, 1.0,
                                                      propagate_down=(True, False, False), grads=g0)
     assert cases.rel_rms(out[0].cpu().numpy(), want[0]) < TOL
+
+
+@pytest.mark.parametrize("xs,ws,pad,stride", [((4, 3, 32, 32), (16, 3, 7, 7), (3, 3), (2, 2)),
+                                              ((3, 5, 12, 10), (8, 5, 3, 3), (1, 1), (1, 1))])
+@pytest.mark.parametrize("accum", [False, True])
+def test_full_precision_convolution_weight_gradient(F, xs, ws, pad, stride, accum):
+    x, w, b, dy, g0 = grad_case(xs, ws, pad, stride, (1, 1))
+    ac = (False, accum, accum)
+    got = F.convolution_backward(dev(x), ws, dev(dy), 1, pad, stride, accum=ac, grads=[None, dev(g0[1]), dev(g0[2])])
+    F.check_device_status()
+    want = oracle.convolution_backward(x, w, dy, pad, stride, propagate_down=(False, True, True), accum=ac, grads=g0)
+    exact = oracle.convolution_backward(x, w, dy, pad, stride, propagate_down=(False, True, True), accum=ac, grads=g0,
+                                        f64=True)
+    for k in (1, 2):
+        assert cases.rel_rms(got[k].cpu().numpy(), want[k]) < TOL
+        assert cases.rel_rms(got[k].cpu().numpy(), exact[k]) < TOL
+    with pytest.raises(RuntimeError):
+        F.convolution_backward(dev(x), ws, dev(dy), 1, pad, stride, propagate_down=(True, True, True))
