@@ -338,11 +338,6 @@ def run_extras(args, rank, world, barrier):
         "ms_per_batch_fused_activations": ms_fused,
         "images_per_sec_whole_job_fused_activations": Bg * world / ms_fused * 1e3,
         "fused": "BN (+ residual) + ReLU + FixedPointQuantize as one pass, bit-identical logits"}
-    net_ep = resnet18.Runner(F, params, gz, fused="epilogue")
-    ms_ep = maxr(time_gpu(lambda: net_ep(x), 5, warm=2))
-    F.check_device_status()
-    out["configs[4] binary-weight ResNet-18 224x224"]["ms_per_batch_fused_epilogue"] = ms_ep
-    out["configs[4] binary-weight ResNet-18 224x224"]["images_per_sec_whole_job_fused_epilogue"] = Bg * world / ms_ep * 1e3
     return out
 
 

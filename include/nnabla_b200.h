@@ -210,25 +210,6 @@ int nb200_bn_add_relu_fxp_f32(const float *a, const float *beta_a, const float *
                               int64_t inner, float eps, int relu, int quantize, int sign, int n, float delta,
                               void *stream);
 
-/* BinaryWeightConvolution with the elementwise chain that follows it fused into
- * the contraction's epilogue:
- *   y = FixedPointQuantize(ReLU(BN(conv(x, wb * alpha) + bias) [+ BN_r(residual) | + residual]))
- * (binary_weight_convolution.cpp:72-117, then batch_normalization.cpp:228-260,
- * add2.cpp, relu.cpp, fixed_point_quantize.cpp:45-66), bit-identical to the
- * separate calls; the convolution's own output never goes to memory. bn_mean
- * == NULL: no BN; residual == NULL: no second operand; res_mean == NULL: the
- * residual is added as it is. The other arguments are those of
- * nb200_binary_weight_convolution_f32 and nb200_bn_add_relu_fxp_f32. */
-int nb200_binary_weight_convolution_fused_f32(const float *x, const float *w, float *wb, float *alpha,
-                                              const float *bias, float *y, int batch, int channels, int height,
-                                              int width, int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w,
-                                              int stride_h, int stride_w, int dilation_h, int dilation_w, int group,
-                                              float quantize_zero_to, float activation_delta, const float *bn_beta,
-                                              const float *bn_gamma, const float *bn_mean, const float *bn_var,
-                                              const float *residual, const float *res_beta, const float *res_gamma,
-                                              const float *res_mean, const float *res_var, float eps, int relu,
-                                              int quantize, int sign, int n, float delta, void *stream);
-
 /* ---- binary convolution backward passes ------------------------------------------
  * Convolution<float>::backward_impl
  * (src/nbla/function/generic/convolution.cpp:199-300) as the binary layers

@@ -9,7 +9,6 @@
 //                K ordered tap-major, channel-minor, zero padded per tap
 // D = weights x activations^T with rows = output maps, columns = a box of
 // output pixels; y is written NCHW directly from the epilogue.
-#include <cmath>
 #include <cstring>
 
 #include "gemm.cuh"
@@ -128,8 +127,7 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
 
 // Shared body of BinaryWeightConvolution / BinaryConnectConvolution forward.
 int binary_convolution(const float *x, const float *w, float *wb, float *alpha, const float *bias, float *y,
-                       ConvGeometry g, float zero_to, float act_delta, cudaStream_t st,
-                       const PostOp *post = nullptr) {
+                       ConvGeometry g, float zero_to, float act_delta, cudaStream_t st) {
   NB_TRY(check_geometry(g));
   NB_CHECK(x && w && wb && y, NB200_EVALUE, "null data pointer");
   const bool int8 = act_delta > 0.0f;
@@ -171,8 +169,6 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   ep.scale = int8 ? act_delta : 1.0f;
   ep.row_scale = alpha;
   ep.row_bias = bias;
-  if (post)
-    ep.post = *post;
   // Box selection: prefer the 128-column kernel (deeper pipeline) unless the
   // 256-column box is better filled.
   int h128, n128, h256, n256;
@@ -410,52 +406,6 @@ int nb200_binary_connect_convolution_backward_f32(const float *x, const float *w
                  dilation_h, dilation_w, group, 0, 0, 0, 0};
   return convolution_backward(x, wb, nullptr, dy, dx, dw, db, g, accum_dx, accum_dw, accum_db, activation_delta,
                               as_stream(stream));
-}
-
-int nb200_binary_weight_convolution_fused_f32(const float *x, const float *w, float *wb, float *alpha,
-                                              const float *bias, float *y, int batch, int channels, int height,
-                                              int width, int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w,
-                                              int stride_h, int stride_w, int dilation_h, int dilation_w, int group,
-                                              float quantize_zero_to, float activation_delta, const float *bn_beta,
-                                              const float *bn_gamma, const float *bn_mean, const float *bn_var,
-                                              const float *residual, const float *res_beta, const float *res_gamma,
-                                              const float *res_mean, const float *res_var, float eps, int relu,
-                                              int quantize, int sign, int n, float delta, void *stream) {
-  NB_CHECK(alpha != nullptr, NB200_EVALUE, "alpha is NULL");
-  NB_CHECK((bn_mean == nullptr) == (bn_var == nullptr), NB200_EVALUE, "mean and variance go together");
-  NB_CHECK(res_mean == nullptr || (residual != nullptr && res_var != nullptr), NB200_EVALUE,
-           "statistics of the second operand without the operand");
-  PostOp post{};
-  post.enabled = 1;
-  post.beta = bn_beta;
-  post.gamma = bn_gamma;
-  post.mean = bn_mean;
-  post.var = bn_var;
-  post.res = residual;
-  post.res_beta = res_beta;
-  post.res_gamma = res_gamma;
-  post.res_mean = res_mean;
-  post.res_var = res_var;
-  post.eps = eps;
-  post.relu = relu;
-  post.quantize = quantize;
-  post.delta = 1.0f;
-  if (quantize) {
-    // the reference's setup (fixed_point_quantize.cpp:31-42)
-    NB_CHECK(n > 0 && delta > 0.f, NB200_EVALUE, "Both bit width and delta should be positive.");
-    const int nn = sign ? n - 1 : n;
-    NB_CHECK(nn > 0, NB200_EVALUE, "bit width should be positive when considering sign (1bit).");
-    post.maxv = (float)((std::pow(2, nn) - 1) * delta);
-    post.minv = sign ? -post.maxv : 0.0f;
-    post.delta = delta;
-    int ex = 0;
-    const float mant = std::frexp(delta, &ex);
-    post.pow2_delta = (mant == 0.5f) && ex > -120 && ex < 120;
-    post.inv_delta = post.pow2_delta ? 1.0f / delta : 0.0f;
-  }
-  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
-                 dilation_h, dilation_w, group, 0, 0, 0, 0};
-  return binary_convolution(x, w, wb, alpha, bias, y, g, quantize_zero_to, activation_delta, as_stream(stream), &post);
 }
 
 int nb200_convolution_backward_f32(const float *x, const float *dy, float *dw, float *db, int batch, int channels,

@@ -49,37 +49,6 @@ constexpr int kStatusProducerTimeout = 0x101;
 constexpr int kStatusMmaTimeout = 0x102;
 constexpr int kStatusEpilogueTimeout = 0x103;
 
-// Optional per-row post-processing of a convolution's output (rows = output
-// maps), fused into the epilogue: y = fxp(relu(BN(y) [+ BN_r(res) | + res])),
-// every operation rounded like the separate functions (batch_normalization.cpp:228-260,
-// add2.cpp, relu.cpp, fixed_point_quantize.cpp:53-65).
-struct PostOp {
-  int enabled;
-  const float *beta, *gamma, *mean, *var;                 // BN of the output; mean == NULL: none
-  const float *res;                                       // second operand, addressed like y; NULL: none
-  const float *res_beta, *res_gamma, *res_mean, *res_var; // its own BN; res_mean == NULL: added as it is
-  float eps;
-  int relu, quantize;
-  float maxv, minv, delta, inv_delta; // FixedPointQuantize limits and step
-  int pow2_delta;
-};
-
-__device__ __forceinline__ float post_bn(float v, float m, float g, float sd, float b) {
-  return __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(v, m), g), sd), b);
-}
-__device__ __forceinline__ float post_fxp(float x, const PostOp &P) {
-  if (x > P.maxv)
-    return P.maxv;
-  if (x < P.minv)
-    return P.minv;
-  const float a = fabsf(x);
-  const float q = P.pow2_delta ? __fmul_rn(a, P.inv_delta) : __fdiv_rn(a, P.delta);
-  const float t = floorf(q);
-  const float k = t + ((__fsub_rn(q, t) >= 0.5f) ? 1.0f : 0.0f);
-  const float r = __fmul_rn(k, P.delta);
-  return x < 0.0f ? -r : r;
-}
-
 struct GemmEpilogue {
   int debug; // timing experiments only (NNABLA_B200_GEMM_DEBUG): 1 = epilogue reads TMEM but neither computes nor stores, 2 = no operand loads after the first ring fill
   float *y;
@@ -92,7 +61,6 @@ struct GemmEpilogue {
   int n_peers;
   float *peer_y[kMaxPeers];
   int accumulate; // y += value instead of y = value (gradient accumulation); single-CTA kernel only
-  PostOp post;    // single-CTA kernel, no column factors, no peers, no accumulation
 };
 
 // Per-tile coordinates produced by a problem policy.
@@ -395,22 +363,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const bool my_row_ok = my_row < t.m_end;
       const float rs = (ep.row_scale && my_row_ok) ? __fmul_rn(ep.row_scale[my_row], ep.scale) : ep.scale;
       const float rb = (ep.row_bias && my_row_ok) ? ep.row_bias[my_row] : 0.0f;
-      // constants of this thread's row for the fused post-processing
-      float pm = 0.f, pg = 1.f, psd = 1.f, pb = 0.f, qm = 0.f, qg = 1.f, qsd = 1.f, qb = 0.f;
-      if (ep.post.enabled && my_row_ok) {
-        if (ep.post.mean) {
-          pm = ep.post.mean[my_row];
-          psd = __fsqrt_rn(__fadd_rn(ep.post.var[my_row], ep.post.eps));
-          pg = ep.post.gamma ? ep.post.gamma[my_row] : 1.0f;
-          pb = ep.post.beta ? ep.post.beta[my_row] : 0.0f;
-        }
-        if (ep.post.res_mean) {
-          qm = ep.post.res_mean[my_row];
-          qsd = __fsqrt_rn(__fadd_rn(ep.post.res_var[my_row], ep.post.eps));
-          qg = ep.post.res_gamma ? ep.post.res_gamma[my_row] : 1.0f;
-          qb = ep.post.res_beta ? ep.post.res_beta[my_row] : 0.0f;
-        }
-      }
       int rows_here = t.m_end - row_base;
       rows_here = rows_here < 0 ? 0 : (rows_here > 32 ? 32 : rows_here);
       const int64_t row_stride = prob.row_offset(1);
@@ -475,8 +427,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               float v = __fmul_rn(kInt8 ? (float)(int)r[j] : __uint_as_float(r[j]), rs);
               if (ep.row_bias)
                 v = __fadd_rn(v, rb);
-              if (ep.post.enabled && ep.post.mean)
-                v = post_bn(v, pm, pg, psd, pb);
               stg[lane * 33 + j] = v;
             }
           }
@@ -495,27 +445,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               if (d == q + 1)
                 yp = ep.peer_y[q];
             yp += tile_off;
-            if (ep.post.enabled) {
-              // fused tail: (+ second operand, through its own BN if it has one) -> ReLU -> quantizer
-              const float *rp = ep.post.res ? ep.post.res + tile_off : nullptr;
-#pragma unroll 4
-              for (int i = 0; i < rows_here; ++i, yp += row_stride) {
-                float v = stg[i * 33 + lane];
-                if (rp) {
-                  float w = col_ok ? __ldcs(rp + (int64_t)i * row_stride) : 0.0f;
-                  if (ep.post.res_mean)
-                    w = post_bn(w, __shfl_sync(0xffffffffu, qm, i), __shfl_sync(0xffffffffu, qg, i),
-                                __shfl_sync(0xffffffffu, qsd, i), __shfl_sync(0xffffffffu, qb, i));
-                  v = __fadd_rn(v, w);
-                }
-                if (ep.post.relu)
-                  v = v > 0.0f ? v : 0.0f;
-                if (ep.post.quantize)
-                  v = post_fxp(v, ep.post);
-                if (col_ok)
-                  *yp = v;
-              }
-            } else if (ep.accumulate) {
+            if (ep.accumulate) {
               // gradient accumulation: y += value (kept out of the plain store loops, whose
               // stores must stay independent of any load from y)
               const float cs = (ep.col_scale && col_ok) ? ep.col_scale[gcol] : 1.0f;

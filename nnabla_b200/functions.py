@@ -481,59 +481,6 @@ def binary_weight_convolution(x, weight, binary_weight, alpha, bias=None, base_a
                                base_axis, pad, stride, dilation, group, quantize_zero_to, outputs, fixed_point_delta)
 
 
-def binary_weight_convolution_fused(x, weight, binary_weight, alpha, bias=None, base_axis=1, pad=None, stride=None,
-                                    dilation=None, group=1, quantize_zero_to=1.0, fixed_point_delta=None, bn=None,
-                                    residual=None, bn_residual=None, eps=1e-05, relu=True, quantize=True, sign=True,
-                                    n=8, delta=2 ** -4, outputs=None):
-    """binary_weight_convolution with the chain that follows it fused into the
-    contraction's epilogue, bit-identical to the separate functions:
-
-        fixed_point_quantize(relu(batch_normalization(conv) [+ batch_normalization(residual) | + residual]))
-
-    bn / bn_residual are (beta, gamma, mean, variance) tuples over the output
-    maps (None: that normalisation is left out); residual has the output's shape."""
-    x, weight = _check_input(x), _check_input(weight, "weight")
-    binary_weight, alpha = _check_input(binary_weight, "binary_weight"), _check_input(alpha, "alpha")
-    bias = _check_input(bias, "bias") if bias is not None else None
-    batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
-        x, weight, bias, base_axis, pad, stride, dilation, group)
-    _same_shape(weight, binary_weight, "float vs binary")
-    if alpha.numel() != Ko:
-        raise RuntimeError("Size of alpha must be equal to the number of output maps.")
-
-    def params(t4, what):
-        if t4 is None:
-            return [None] * 4
-        out = []
-        for t, nm in zip(t4, ("beta", "gamma", "mean", "variance")):
-            if t is None:
-                if nm in ("mean", "variance"):
-                    raise RuntimeError("mean and variance are required (%s)" % what)
-                out.append(None)
-                continue
-            t = _check_input(t, nm)
-            if t.numel() != Ko:
-                raise RuntimeError("%s must have %d elements (the output maps)" % (nm, Ko))
-            out.append(t)
-        return out
-    pa, pr = params(bn, "bn"), params(bn_residual, "bn_residual")
-    if residual is not None:
-        residual = _check_input(residual, "residual")
-        if tuple(residual.shape) != tuple(out_shape):
-            raise RuntimeError("residual must have the output's shape")
-    elif bn_residual is not None:
-        raise RuntimeError("bn_residual without residual")
-    y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
-    with torch.cuda.device(x.device):
-        C.call("nb200_binary_weight_convolution_fused_f32", C.ptr(x), C.ptr(weight), C.ptr(binary_weight), C.ptr(alpha),
-               C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1], stride[0], stride[1], dilation[0],
-               dilation[1], int(group), C.c_float(quantize_zero_to), C.c_float(fixed_point_delta or 0.0),
-               C.ptr(pa[0]), C.ptr(pa[1]), C.ptr(pa[2]), C.ptr(pa[3]), C.ptr(residual), C.ptr(pr[0]), C.ptr(pr[1]),
-               C.ptr(pr[2]), C.ptr(pr[3]), C.c_float(eps), int(bool(relu)), int(bool(quantize)), int(bool(sign)),
-               int(n), C.c_float(delta), C.stream_ptr(x.device))
-    return y
-
-
 def binary_connect_convolution(x, weight, binary_weight, bias=None, base_axis=1, pad=None, stride=None,
                                dilation=None, group=1, quantize_zero_to=1.0, n_outputs=-1, outputs=None,
                                fixed_point_delta=None):

@@ -61,11 +61,7 @@ class Runner:
     def __init__(self, ops, params, zeros_like, trace=None, fixed_point_hint=True, fused=False):
         """fused=True applies BN (+ residual) + ReLU + FixedPointQuantize as one
         function (ops.bn_add_relu_fixed_point), which is bit-identical to the
-        separate functions and reads / writes each activation once.
-        fused="epilogue" goes further: inside the residual blocks that chain runs
-        in the epilogue of the binary-weight convolution that produces its input
-        (ops.binary_weight_convolution_fused), so the convolution's own output
-        never goes to memory; still bit-identical."""
+        separate functions and reads / writes each activation once."""
         self.fused = fused
         self.ops = ops
         self.p = params
@@ -100,18 +96,6 @@ class Runner:
         return self._rec(name, "bn_add_relu_fixed_point", [a] + ([b] if b is not None else []), y, bn_a=bn_a,
                          bn_b=bn_b)
 
-    def bwconv_fused(self, name, x, k, stride, bn, residual=None, bn_residual=None):
-        w = self.p[name + "/W"]
-        if name not in self.side:
-            self.side[name] = (self.zeros_like(w), self.zeros_like(w, (w.shape[0],)))
-        wb, alpha = self.side[name]
-        y = self.ops.binary_weight_convolution_fused(
-            x, w, wb, alpha, None, 1, (k // 2, k // 2), (stride, stride), (1, 1), 1, 1.0,
-            DELTA if self.hint else None, self.bn_params(bn), residual,
-            self.bn_params(bn_residual) if bn_residual else None, 1e-5, True, True, True, 8, DELTA)
-        return self._rec(name, "binary_weight_convolution_fused", [x] + ([residual] if residual is not None else []),
-                         y, k=k, stride=stride, bn=bn, bn_residual=bn_residual)
-
     def bwconv(self, name, x, k, stride):
         w = self.p[name + "/W"]
         if name not in self.side:
@@ -133,15 +117,6 @@ class Runner:
             for b in range(2):
                 st = stride if b == 0 else 1
                 name = "stage%d/block%d" % (s + 1, b)
-                if self.fused == "epilogue":
-                    r = self.bwconv_fused(name + "/conv1", h, 3, st, name + "/bn1")
-                    if st != 1 or cin != c:
-                        sc = self.bwconv(name + "/shortcut", h, 1, st)
-                        h = self.bwconv_fused(name + "/conv2", r, 3, 1, name + "/bn2", sc, name + "/bn_s")
-                    else:
-                        h = self.bwconv_fused(name + "/conv2", r, 3, 1, name + "/bn2", h)
-                    cin = c
-                    continue
                 r = self.bwconv(name + "/conv1", h, 3, st)
                 if self.fused:
                     r = self.fused_act(name + "/act1", r, name + "/bn1")

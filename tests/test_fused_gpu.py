@@ -66,44 +66,3 @@ def test_fused_resnet_equals_unfused(F):
     fused = resnet18.Runner(F, gp, gz, fused=True)(x)
     F.check_device_status()
     assert torch.equal(plain, fused)
-
-
-@pytest.mark.parametrize("case", [((2, 8, 12, 12), (16, 8, 3, 3), (1, 1), (1, 1)), ((3, 16, 9, 9), (32, 16, 3, 3), (1, 1), (2, 2)),
-                                  ((2, 64, 14, 14), (64, 64, 3, 3), (1, 1), (1, 1)), ((2, 8, 10, 10), (150, 8, 1, 1), (0, 0), (1, 1))])
-@pytest.mark.parametrize("second", ["none", "residual", "bn"])
-@pytest.mark.parametrize("int8", [False, True])
-def test_convolution_with_fused_tail_equals_the_separate_functions(F, case, second, int8):
-    xs, ws, pad, stride = case
-    rng = np.random.RandomState(sum(xs) + sum(ws))
-    x = rng.randn(*xs).astype(np.float32)
-    if int8:
-        from oracle import oracle
-        x = oracle.fixed_point_quantize(x, True, 8, 2.0 ** -4)
-    w = rng.randn(*ws).astype(np.float32)
-    pa, pr = bn_set(rng, ws[0]), bn_set(rng, ws[0])
-    hint = 2.0 ** -4 if int8 else None
-    wb, al = torch.zeros(ws, device="cuda"), torch.zeros(ws[0], device="cuda")
-    y = F.binary_weight_convolution(dev(x), dev(w), wb, al, None, 1, pad, stride, fixed_point_delta=hint)
-    res = dev(rng.randn(*y.shape).astype(np.float32)) if second != "none" else None
-    da = [dev(t) for t in pa]
-    dr = [dev(t) for t in pr] if second == "bn" else None
-    want = F.bn_add_relu_fixed_point(y, da, res, dr)
-    wb2, al2 = torch.zeros(ws, device="cuda"), torch.zeros(ws[0], device="cuda")
-    got = F.binary_weight_convolution_fused(dev(x), dev(w), wb2, al2, None, 1, pad, stride, fixed_point_delta=hint,
-                                            bn=da, residual=res, bn_residual=dr)
-    F.check_device_status()
-    assert torch.equal(got, want)
-    assert torch.equal(wb2, wb) and torch.equal(al2, al)
-
-
-def test_epilogue_fused_resnet_equals_unfused(F):
-    from nnabla_b200 import resnet18
-    rng = np.random.RandomState(0)
-    params = resnet18.init_parameters(rng, num_classes=100)
-    x = dev(rng.randn(2, 3, 64, 64).astype(np.float32))
-    gp = {k: dev(v) for k, v in params.items()}
-    gz = lambda w, shape=None: torch.zeros(shape or tuple(w.shape), device="cuda")
-    plain = resnet18.Runner(F, gp, gz)(x)
-    fused = resnet18.Runner(F, gp, gz, fused="epilogue")(x)
-    F.check_device_status()
-    assert torch.equal(plain, fused)
