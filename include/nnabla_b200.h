@@ -308,6 +308,15 @@ int nb200_affine_fxp8_f32(const float *xq, const float *wq, float delta_x, float
  * w_codes [w_row, w_col]). */
 int nb200_affine_codes_i8_f32(const int8_t *x_codes, const int8_t *w_codes, float delta_x, float delta_w,
                               const float *bias, float *y, int64_t rows, int64_t w_row, int64_t w_col, void *stream);
+/* The same with the weight codes already in the layout the tensor core reads
+ * (K-major: [w_col][w_pitch], w_pitch >= w_row a multiple of 16, padding zero),
+ * which nb200_transpose_codes_i8 produces: weights are parameters, so this
+ * re-layout is done once per weight update instead of once per call. */
+int nb200_transpose_codes_i8(const int8_t *w_codes, int8_t *w_codes_kmajor, int64_t w_row, int64_t w_col,
+                             int64_t pitch, void *stream);
+int nb200_affine_codes_i8_kmajor_f32(const int8_t *x_codes, const int8_t *w_codes_kmajor, int64_t w_pitch,
+                                     float delta_x, float delta_w, const float *bias, float *y, int64_t rows,
+                                     int64_t w_row, int64_t w_col, void *stream);
 /* Output-column shards of the two contractions above, with the gather of the
  * shards fused into the kernel: this rank owns columns [col_begin, col_begin +
  * w_col) of a [w_row, w_col_total] weight (wq / w_codes and bias are its slab)

@@ -77,7 +77,8 @@ void plan_box(const ConvGeometry &g, int bn_max, int &h_box, int &n_box) {
   h_box = best;
 }
 
-template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes, bool kSkip = false>
+template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes, bool kSkip = false,
+          bool kResidentA = false>
 int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ctot, const void *wside, int64_t wpitch,
                 int c_pad_g, int cblocks, int h_box, int n_box, const GemmEpilogue &ep, cudaStream_t st,
                 int k_splits = 1, int64_t split_stride = 0) {
@@ -122,7 +123,8 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
   p.k_splits = k_splits;
   p.split_stride = split_stride;
   const int tiles = k_splits * p.groups * p.m_tiles_g * p.tiles_h * p.tiles_n;
-  return launch_contraction<kInt8, PA, PB, BN, STAGES, kSkip, ConvProblem, RB>(ma, mb, p, tiles, ep, st);
+  return launch_contraction<kInt8, PA, PB, BN, STAGES, kSkip, ConvProblem, RB, kResidentA>(ma, mb, p, tiles, ep, st,
+                                                                                            p.taps * p.cblocks);
 }
 
 // Shared body of BinaryWeightConvolution / BinaryConnectConvolution forward.
@@ -180,6 +182,18 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   const bool can128 = px128 <= 128;
   const bool use256 = !can128 || (int8 && fill256 > fill128 + 0.05);
   if (int8) {
+    // All tiles share the weights when the output maps fit one M tile: keep them in shared
+    // memory for the whole launch if their K blocks fit beside the ring (64-byte rows only:
+    // there the copy engine's request rate, one request per row, bounds the kernel).
+    const bool resident = narrow_rows && g.group == 1 && g.Ko <= kTileM &&
+                          (size_t)taps * cblocks * kTileM * 64 <= 72 * 1024;
+    if (resident) {
+      if (use256)
+        return launch_conv<true, 1, 1, 256, 6, 64, false, true>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h256,
+                                                                n256, ep, st);
+      return launch_conv<true, 1, 1, 128, 10, 64, false, true>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h128,
+                                                               n128, ep, st);
+    }
     if (narrow_rows) {
       if (use256)
         return launch_conv<true, 1, 1, 256, 8, 64>(g, act, 1, ctot, side, wpitch, c_pad_g, cblocks, h256, n256, ep,

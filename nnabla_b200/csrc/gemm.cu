@@ -224,9 +224,12 @@ static int slab_destinations(GemmEpilogue &ep, float *const *y_ranks, int n_rank
   return NB200_OK;
 }
 
+// w_kmajor: w_codes already holds the K-major layout [w_col][w_pitch] (nb200_transpose_codes_i8), so the
+// re-layout pass is skipped (weights are parameters: their codes can be laid out once and reused).
 static int affine_codes(const int8_t *x_codes, const int8_t *w_codes, float delta_x, float delta_w, const float *bias,
                         float *const *y_ranks, int n_ranks, int rank, int64_t rows, int64_t w_row, int64_t w_col,
-                        int64_t n_total, int64_t col_begin, cudaStream_t st) {
+                        int64_t n_total, int64_t col_begin, cudaStream_t st, bool w_kmajor = false,
+                        int64_t w_pitch = 0) {
   const int64_t M = rows, K = w_row, N = w_col;
   NB_CHECK(M > 0 && K > 0 && N > 0, NB200_EVALUE, "empty operand");
   NB_CHECK(M < (1ll << 31) && K < (1ll << 31) && N < (1ll << 31), NB200_EVALUE, "extent exceeds 2^31");
@@ -237,21 +240,31 @@ static int affine_codes(const int8_t *x_codes, const int8_t *w_codes, float delt
   NB_TRY(slab_destinations(ep, y_ranks, n_ranks, rank, N, n_total, col_begin));
   const int64_t Kp = round_up(K, 128);
   const bool x_direct = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(x_codes) & 15) == 0);
+  if (w_kmajor)
+    NB_CHECK(w_pitch >= K && w_pitch % 16 == 0 && (reinterpret_cast<uintptr_t>(w_codes) & 15) == 0, NB200_EVALUE,
+             "K-major weight codes need a 16-byte aligned base and a pitch >= w_row that is a multiple of 16 (got %lld)",
+             (long long)w_pitch);
   AsyncScratch scratch(st);
-  NB_TRY(scratch.alloc((size_t)N * Kp + (x_direct ? 0 : (size_t)M * Kp)));
+  NB_TRY(scratch.alloc((w_kmajor ? 0 : (size_t)N * Kp) + (x_direct ? 0 : (size_t)M * Kp) + 16));
   int8_t *wt = static_cast<int8_t *>(scratch.p);
-  NB_TRY(transpose_i8(w_codes, (int)K, (int)N, wt, Kp, st));
+  const int8_t *wk = w_codes;
+  int64_t pitch_b = w_pitch;
+  if (!w_kmajor) {
+    NB_TRY(transpose_i8(w_codes, (int)K, (int)N, wt, Kp, st));
+    wk = wt;
+    pitch_b = Kp;
+  }
   const int8_t *xa = x_codes;
   int64_t pitch_a = K;
   if (!x_direct) {
-    int8_t *xc = wt + (size_t)N * Kp;
+    int8_t *xc = wt + (w_kmajor ? 0 : (size_t)N * Kp);
     NB_CUDA(cudaMemcpy2DAsync(xc, (size_t)Kp, x_codes, (size_t)K, (size_t)K, (size_t)M, cudaMemcpyDeviceToDevice, st));
     xa = xc;
     pitch_a = Kp;
   }
   ep.scale = delta_x * delta_w;
   ep.col_bias = bias;
-  return run_gemm(true, 1, 1, xa, pitch_a, wt, Kp, (int)M, (int)N, (int)K, ep, n_total, st);
+  return run_gemm(true, 1, 1, xa, pitch_a, wk, pitch_b, (int)M, (int)N, (int)K, ep, n_total, st);
 }
 
 static int affine_fxp8(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias,
@@ -447,5 +460,24 @@ int nb200_binary_connect_affine_backward_f32(const float *x, const float *wb, co
                                              int accum_dw, int accum_db, void *stream) {
   return affine_backward(x, wb, nullptr, true, dy, dx, dw, db, rows, w_row, w_col, accum_dx, accum_dw, accum_db,
                          as_stream(stream));
+}
+
+int nb200_transpose_codes_i8(const int8_t *w_codes, int8_t *w_codes_kmajor, int64_t w_row, int64_t w_col,
+                             int64_t pitch, void *stream) {
+  NB_CHECK(w_codes && w_codes_kmajor, NB200_EVALUE, "null data pointer");
+  NB_CHECK(w_row > 0 && w_col > 0 && w_row < (1ll << 31) && w_col < (1ll << 31), NB200_EVALUE, "bad extents");
+  NB_CHECK(pitch >= w_row, NB200_EVALUE, "pitch %lld is smaller than w_row %lld", (long long)pitch, (long long)w_row);
+  if (pitch > w_row) // the padding must read as zero codes
+    NB_CUDA(cudaMemsetAsync(w_codes_kmajor, 0, (size_t)w_col * pitch, as_stream(stream)));
+  return transpose_i8(w_codes, (int)w_row, (int)w_col, w_codes_kmajor, pitch, as_stream(stream));
+}
+
+int nb200_affine_codes_i8_kmajor_f32(const int8_t *x_codes, const int8_t *w_codes_kmajor, int64_t w_pitch,
+                                     float delta_x, float delta_w, const float *bias, float *y, int64_t rows,
+                                     int64_t w_row, int64_t w_col, void *stream) {
+  NB_CHECK(y != nullptr, NB200_EVALUE, "null data pointer");
+  float *const ys[1] = {y};
+  return affine_codes(x_codes, w_codes_kmajor, delta_x, delta_w, bias, ys, 1, 0, rows, w_row, w_col, w_col, 0,
+                      as_stream(stream), true, w_pitch);
 }
 }

@@ -180,7 +180,13 @@ struct ConvProblem {
   }
 };
 
-template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkipSmallPairs, typename Problem, int RB = kRowBytes>
+// kResidentA: every tile of the launch uses the same A operand (a convolution
+// whose output maps fit one M tile) and all its K blocks fit in shared memory
+// beside the ring: A is loaded once per CTA and only the B tiles stream. With
+// few channels the copy engine's request rate bounds the kernel (one request
+// per 64-byte row), and A was half of the requests.
+template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkipSmallPairs, typename Problem, int RB = kRowBytes,
+          bool kResidentA = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const Problem prob, const GemmEpilogue ep, int *status) {
@@ -190,19 +196,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   constexpr int kMmasPerBlock = kElemsPerBlock / kUmmaK;
   constexpr uint32_t kABytes = kTileM * RB;
   constexpr uint32_t kBBytes = BN * RB;
-  constexpr uint32_t kStageBytes = PA * kABytes + PB * kBBytes;
+  constexpr uint32_t kStageA = kResidentA ? 0u : PA * kABytes; // bytes of A inside a ring stage
+  constexpr uint32_t kStageBytes = kStageA + PB * kBBytes;
   constexpr uint32_t kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
 
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms.
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * kStageBytes);
+  // resident A (kResidentA): [k block][plane][kTileM rows] behind the ring
+  const uint32_t resident_bytes = kResidentA ? (uint32_t)prob.k_blocks() * PA * kABytes : 0u;
+  uint8_t *a_resident = smem + STAGES * kStageBytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * kStageBytes + resident_bytes);
   uint64_t *full_bar = bars;
   uint64_t *empty_bar = bars + STAGES;
   uint64_t *tmem_full = bars + 2 * STAGES;
   uint64_t *tmem_empty = bars + 2 * STAGES + 2;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  uint64_t *a_full = bars + 2 * STAGES + 4;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   float *stage_out = reinterpret_cast<float *>(tmem_slot + 4); // one 32 x 33 float buffer per epilogue warp
 
@@ -221,6 +232,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       ptx::mbar_init(tmem_full + b, 1);
       ptx::mbar_init(tmem_empty + b, kEpilogueWarps);
     }
+    ptx::mbar_init(a_full, 1);
     *abort_flag = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tensormap(&map_a);
@@ -241,7 +253,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      const uint32_t tx_bytes = PA * kABytes + PB * prob.b_tx_bytes();
+      const uint32_t tx_bytes = kStageA + PB * prob.b_tx_bytes();
+      if (kResidentA && (int)blockIdx.x < num_tiles) {
+        Tile t0;
+        prob.decode(blockIdx.x, t0);
+        ptx::mbar_expect_tx(a_full, resident_bytes);
+        for (int kb = 0; kb < prob.k_blocks(); ++kb)
+#pragma unroll
+          for (int pa = 0; pa < PA; ++pa)
+            prob.load_a(&map_a, a_resident + (size_t)(kb * PA + pa) * kABytes, a_full, kb, t0, pa, kElemsPerBlock);
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         Tile t;
         prob.decode(tile, t);
@@ -258,12 +279,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             ptx::mbar_arrive(full_bar + stage);
           } else {
             ptx::mbar_expect_tx(full_bar + stage, tx_bytes);
+            if (!kResidentA) {
 #pragma unroll
-            for (int pa = 0; pa < PA; ++pa)
-              prob.load_a(&map_a, st + pa * kABytes, full_bar + stage, kb, t, pa, kElemsPerBlock);
+              for (int pa = 0; pa < PA; ++pa)
+                prob.load_a(&map_a, st + pa * kABytes, full_bar + stage, kb, t, pa, kElemsPerBlock);
+            }
 #pragma unroll
             for (int pb = 0; pb < PB; ++pb)
-              prob.load_b(&map_b, st + PA * kABytes + pb * kBBytes, full_bar + stage, kb, t, pb, kElemsPerBlock);
+              prob.load_b(&map_b, st + kStageA + pb * kBBytes, full_bar + stage, kb, t, pb, kElemsPerBlock);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -280,6 +303,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       int local = 0;
       bool ok = true;
       const uint32_t idesc = ptx::make_idesc(kInt8 ? 2u : 1u, 1u, kTileM, prob.umma_n()); // S8 and BF16 both encode as 1
+      if (kResidentA && (int)blockIdx.x < num_tiles) {
+        if (!ptx::mbar_wait(a_full, 0u, abort_flag)) {
+          if (*abort_flag == 0)
+            atomicCAS(status, 0, kStatusMmaTimeout);
+          *abort_flag = 1;
+          ok = false;
+        }
+        ptx::tc_fence_after_sync();
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         Tile t;
         prob.decode(tile, t);
@@ -316,8 +348,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 // resolution of the leading term (pa + pb > 2) are skipped.
                 if (kSkipSmallPairs && pa + pb > 2)
                   continue;
-                const uint64_t adesc = ptx::smem_desc_k(st + pa * kABytes, RB);
-                const uint64_t bdesc = ptx::smem_desc_k(st + PA * kABytes + pb * kBBytes, RB);
+                const uint64_t adesc =
+                    kResidentA ? ptx::smem_desc_k(ptx::smem_u32(a_resident) + (uint32_t)(kb * PA + pa) * kABytes, RB)
+                               : ptx::smem_desc_k(st + pa * kABytes, RB);
+                const uint64_t bdesc = ptx::smem_desc_k(st + kStageA + pb * kBBytes, RB);
 #pragma unroll
                 for (int k = 0; k < kMmasPerBlock; ++k) {
                   // advancing 32 bytes along K inside the swizzle atom = +2 in the encoded address
@@ -514,8 +548,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 }
 
-template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes> constexpr size_t gemm_smem_bytes() {
-  return (size_t)STAGES * (PA * kTileM * RB + PB * BN * RB) + (2 * STAGES + 4) * 8 + 16 +
+template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes, bool kResidentA = false>
+constexpr size_t gemm_smem_bytes() {
+  return (size_t)STAGES * ((kResidentA ? 0 : PA * kTileM * RB) + PB * BN * RB) + (2 * STAGES + 5) * 8 + 16 +
          kEpilogueStageBytes + 1024;
 }
 
@@ -553,17 +588,22 @@ int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch
 
 // Launches the contraction kernel for one problem: one persistent CTA per SM
 // (or per tile when there are fewer tiles than SMs).
-template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkip, typename Problem, int RB = kRowBytes>
+template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkip, typename Problem, int RB = kRowBytes,
+          bool kResidentA = false>
 inline int launch_contraction(const CUtensorMap &ma, const CUtensorMap &mb, const Problem &prob, int tiles,
-                       const GemmEpilogue &ep, cudaStream_t st) {
-  auto kernel = gemm_tcgen05_kernel<kInt8, PA, PB, BN, STAGES, kSkip, Problem, RB>;
-  constexpr size_t smem = gemm_smem_bytes<kInt8, PA, PB, BN, STAGES, RB>();
-  static_assert(smem <= 227 * 1024, "shared memory budget");
+                       const GemmEpilogue &ep, cudaStream_t st, int resident_k_blocks = 0) {
+  auto kernel = gemm_tcgen05_kernel<kInt8, PA, PB, BN, STAGES, kSkip, Problem, RB, kResidentA>;
+  constexpr size_t smem_fixed = gemm_smem_bytes<kInt8, PA, PB, BN, STAGES, RB, kResidentA>();
+  static_assert(smem_fixed <= 227 * 1024, "shared memory budget");
+  // a resident A operand adds its K blocks; the attribute is set to the device maximum once
+  const size_t smem = smem_fixed + (kResidentA ? (size_t)resident_k_blocks * PA * kTileM * RB : 0);
+  NB_CHECK(smem <= 227 * 1024, NB200_EVALUE, "resident operand does not fit in shared memory");
   static bool configured[64];
   int dev = 0;
   NB_CUDA(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    NB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kResidentA ? 227 * 1024 : (int)smem));
     configured[dev & 63] = true;
   }
   int *status = nullptr;

@@ -352,6 +352,33 @@ def binary_connect_affine_backward(x, binary_weight, dy, base_axis=1, propagate_
                             propagate_down, accum, grads)
 
 
+def transpose_codes(w_codes):
+    """K-major copy [N][Kp] (Kp = K rounded up to 16, zero padded) of int8 weight
+    codes [K, N]: the layout affine_from_codes(..., w_kmajor=True) reads without
+    a re-layout pass. Done once per weight update."""
+    K, N = w_codes.shape
+    Kp = (K + 15) // 16 * 16
+    out = torch.empty((N, Kp), dtype=torch.int8, device=w_codes.device)
+    with torch.cuda.device(w_codes.device):
+        C.call("nb200_transpose_codes_i8", C.ptr(w_codes.contiguous()), C.ptr(out), ctypes.c_int64(K),
+               ctypes.c_int64(N), ctypes.c_int64(Kp), C.stream_ptr(w_codes.device))
+    return out
+
+
+def affine_from_kmajor_codes(x_codes, w_codes_kmajor, w_row, delta_x, delta_w, bias=None):
+    """affine_from_codes with weight codes prepared by transpose_codes ([N][Kp])."""
+    rows, K = x_codes.shape
+    N, Kp = w_codes_kmajor.shape
+    if K != w_row or Kp < K:
+        raise RuntimeError("Size of input data(inputs[0]) and weights(inputs[1]) mismatch.")
+    y = torch.empty((rows, N), dtype=torch.float32, device=x_codes.device)
+    with torch.cuda.device(x_codes.device):
+        C.call("nb200_affine_codes_i8_kmajor_f32", C.ptr(x_codes), C.ptr(w_codes_kmajor), ctypes.c_int64(Kp),
+               C.c_float(delta_x), C.c_float(delta_w), C.ptr(bias), C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(K),
+               ctypes.c_int64(N), C.stream_ptr(x_codes.device))
+    return y
+
+
 def _rank_pointers(y_ranks):
     """ctypes array of the per-rank output matrices' device addresses (tensors or plain integers)."""
     addrs = [int(y.data_ptr()) if hasattr(y, "data_ptr") else int(y) for y in y_ranks]

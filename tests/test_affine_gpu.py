@@ -171,3 +171,18 @@ def test_large_binary_weight_affine_two_sm_tiles(F):
     assert np.array_equal(wb, sgn.astype(np.float32))
     want = (x.astype(np.float64) @ sgn) * np.abs(w.astype(np.float64)).mean(0) + b
     assert cases.rel_rms(y, want) < TOL
+
+
+@pytest.mark.parametrize("M,K,N", [(384, 512, 640), (70, 200, 333), (2304, 256, 2304)])
+def test_affine_from_prepared_kmajor_codes(F, M, K, N):
+    rng = np.random.RandomState(M + N)
+    x = rng.randn(M, K).astype(np.float32)
+    w = (0.02 * rng.randn(K, N)).astype(np.float32)
+    b = (0.01 * rng.randn(N)).astype(np.float32)
+    _, xc = F.fixed_point_quantize_with_codes(dev(x), True, 8, 2.0 ** -5)
+    _, wc = F.fixed_point_quantize_with_codes(dev(w), True, 8, 2.0 ** -10)
+    want = F.affine_from_codes(xc, wc, 2.0 ** -5, 2.0 ** -10, dev(b))
+    wk = F.transpose_codes(wc)
+    got = F.affine_from_kmajor_codes(xc, wk, K, 2.0 ** -5, 2.0 ** -10, dev(b))
+    F.check_device_status()
+    assert torch.equal(got, want)
