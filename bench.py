@@ -326,6 +326,20 @@ def run_extras(args, rank, world, barrier):
         "tflops_algorithmic_dw_whole_job": flops / ms_dw / 1e9,
         "includes": "operand re-layout (stuffing / batch-innermost transposes, bf16 pieces) + implicit GEMM"}
     del x, w, dyc, gxc
+    # data-parallel gradient all-reduce of the ResNet-18 parameter set through the communicator (N > 1 only)
+    if world > 1:
+        from nnabla_b200 import communicators
+        comm = communicators.MultiProcessDataParallelCommunicator()
+        comm.init()
+        shapes = [tuple(v.shape) for v in resnet18.init_parameters(np.random.RandomState(0)).values()]
+        grads = [torch.ones(sh, device="cuda") for sh in shapes]
+        n_par = sum(g.numel() for g in grads)
+        cb = comm.all_reduce_callback(grads, pack_size=8 << 20, division=True)
+        ms_ar = maxr(time_gpu(cb, 10))
+        out["gradient all-reduce, ResNet-18 parameters"] = {
+            "ms": ms_ar, "parameters": n_par, "arrays": len(grads), "bucket_values": 8 << 20,
+            "bus_GBps": 2 * (world - 1) / world * n_par * 4 / ms_ar / 1e6,
+            "correct": bool(all(torch.allclose(g, torch.ones_like(g)) for g in grads))}
     # configs[4]: binary-weight ResNet-18, batch sharded over the ranks
     B = args.resnet_batch
     Bg = max(1, B // world)
