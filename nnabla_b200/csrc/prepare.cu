@@ -135,19 +135,21 @@ __device__ __forceinline__ void split3(float x, __nv_bfloat16 &h, __nv_bfloat16 
   l = __float2bfloat16_rn(r2);
 }
 
+// Block = 64 columns x 4 rows (Kp is a multiple of 64): coalesced along K, no
+// 64-bit divisions.
 __global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict__ x, int64_t rows, int K, int64_t Kp,
                                                          int planes, const float *__restrict__ col_scale,
                                                          __nv_bfloat16 *__restrict__ out) {
-  const int64_t total = rows * Kp;
+  const int k = blockIdx.x * 64 + threadIdx.x;
   const int64_t plane_stride = rows * Kp;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / Kp;
-    const int k = (int)(i - r * Kp);
-    __nv_bfloat16 h, m, l;
+  const float cs = (col_scale != nullptr && k < K) ? col_scale[k] : 1.0f;
+  for (int64_t r = (int64_t)blockIdx.y * 4 + threadIdx.y; r < rows; r += (int64_t)gridDim.y * 4) {
     float v = (k < K) ? x[r * K + k] : 0.0f;
-    if (col_scale != nullptr && k < K)
-      v = __fmul_rn(v, col_scale[k]);
+    if (col_scale != nullptr)
+      v = __fmul_rn(v, cs);
+    __nv_bfloat16 h, m, l;
     split3(v, h, m, l);
+    const int64_t i = r * Kp + k;
     out[i] = h;
     if (planes > 1)
       out[plane_stride + i] = m;
@@ -386,8 +388,13 @@ int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to,
 
 int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st,
                     const float *col_scale) {
-  split_rows_kernel<<<capped_grid(rows * Kp, 256), 256, 0, st>>>(x, rows, K, Kp, planes, col_scale,
-                                                                 reinterpret_cast<__nv_bfloat16 *>(out));
+  NB_CHECK(Kp % 64 == 0 && Kp / 64 < (1ll << 31), NB200_EVALUE, "the padded K extent must be a multiple of 64");
+  int64_t gy = (rows + 3) / 4;
+  const int64_t cap = (int64_t)sm_count() * 64;
+  gy = gy > cap ? cap : (gy < 1 ? 1 : gy);
+  gy = gy > 65535 ? 65535 : gy;
+  split_rows_kernel<<<dim3((unsigned)(Kp / 64), (unsigned)gy), dim3(64, 4), 0, st>>>(
+      x, rows, K, Kp, planes, col_scale, reinterpret_cast<__nv_bfloat16 *>(out));
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }
