@@ -110,19 +110,14 @@ class Communicator:
     # ---- packing ---------------------------------------------------------------------
     @staticmethod
     def _pack(arrays):
-        flat = torch.empty(sum(a.numel() for a in arrays), dtype=arrays[0].dtype, device=arrays[0].device)
-        off = 0
-        for a in arrays:
-            flat[off:off + a.numel()].copy_(a.reshape(-1))
-            off += a.numel()
-        return flat
+        """One flat buffer holding the arrays back to back (a single gather kernel)."""
+        return torch.cat([a.reshape(-1) for a in arrays])
 
     @staticmethod
     def _unpack(flat, arrays):
-        off = 0
-        for a in arrays:
-            a.copy_(flat[off:off + a.numel()].view_as(a))
-            off += a.numel()
+        """Copies the flat buffer back into the arrays (one multi-tensor copy)."""
+        views = [v.view_as(a) for v, a in zip(flat.split([a.numel() for a in arrays]), arrays)]
+        torch._foreach_copy_(list(arrays), views)
 
     def _run(self, arrays, inplace, fn):
         """Applies collective `fn(tensor)` to each array (inplace) or once to the packed arrays."""

@@ -186,3 +186,28 @@ def test_affine_from_prepared_kmajor_codes(F, M, K, N):
     got = F.affine_from_kmajor_codes(xc, wk, K, 2.0 ** -5, 2.0 ** -10, dev(b))
     F.check_device_status()
     assert torch.equal(got, want)
+
+
+def test_fixed_point_affine_full_baseline_size(F):
+    """BASELINE configs[2] at its full size (8192 x 4096 x 8192): every partial sum is an
+    integer below 2^24 times a power of two, so the result is exact and must equal, bit for
+    bit, an independent integer product (the library's int8 GEMM, used here as a checker only)
+    scaled and biased with one rounding each; a window of rows is also checked against the
+    oracle."""
+    M, K, N = 8192, 4096, 8192
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(M, K, device="cuda", generator=gen)
+    w = 0.02 * torch.randn(K, N, device="cuda", generator=gen)
+    b = 0.01 * torch.randn(N, device="cuda", generator=gen)
+    xq, xc = F.fixed_point_quantize_with_codes(x, True, 8, 2.0 ** -5)
+    wq, wc = F.fixed_point_quantize_with_codes(w, True, 8, 2.0 ** -10)
+    y = F.affine_from_codes(xc, wc, 2.0 ** -5, 2.0 ** -10, b)
+    y2 = F.affine_from_kmajor_codes(xc, F.transpose_codes(wc), K, 2.0 ** -5, 2.0 ** -10, b)
+    F.check_device_status()
+    assert torch.equal(y, y2)
+    acc = torch._int_mm(xc, wc.t().contiguous().t())
+    want = acc.float().mul_(2.0 ** -15).add_(b)
+    assert torch.equal(y, want)
+    rows = slice(4000, 4016)
+    ref_rows = oracle.affine(xq[rows].cpu().numpy(), wq.cpu().numpy(), b.cpu().numpy())
+    assert np.array_equal(bits(y[rows].cpu().numpy()), bits(ref_rows))

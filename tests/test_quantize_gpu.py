@@ -139,16 +139,37 @@ def test_minmax_cfg_digest_tails_and_errors(F):
 
 
 def test_large_tensor_properties(F):
-    """2^28 elements (1 GiB): idempotence of the quantizers and a chunked
-    comparison with the oracle on two windows."""
-    n = 1 << 28
+    """The headline size, 2^30 elements (4 GiB per tensor, byte offsets beyond
+    2^32): idempotence of the three quantizers, their backward passes against
+    masks computed from the forward's own definition, and a comparison with the
+    oracle on windows at the start, across the 2^32-byte boundary and at the
+    very end."""
+    n = 1 << 30
     gen = torch.Generator(device="cuda").manual_seed(0)
-    x = (torch.rand(n, device="cuda", generator=gen) * 8 - 4)
+    x = (torch.rand(n, device="cuda", generator=gen) * 9 - 4.5)
+    one = lambda v: torch.tensor([v], device="cuda")
     y = F.fixed_point_quantize(x, True, 8, 2.0 ** -4)
     assert torch.equal(F.fixed_point_quantize(y, True, 8, 2.0 ** -4), y)
     p = F.pow2_quantize(x, True, True, 8, 1)
     assert torch.equal(F.pow2_quantize(p, True, True, 8, 1), p)
-    for lo in (0, n - (1 << 20) - 3):
-        w = x[lo:lo + (1 << 20)].cpu().numpy()
-        assert np.array_equal(bits(host(y[lo:lo + (1 << 20)])), bits(oracle.fixed_point_quantize(w, True, 8, 2.0 ** -4)))
-        assert np.array_equal(bits(host(p[lo:lo + (1 << 20)])), bits(oracle.pow2_quantize(w, True, True, 8, 1)))
+    qmin, qmax = one(-4.0), one(4.0)
+    m = F.min_max_quantize(x, qmin, qmax, one(0.0), one(255.0))
+    assert torch.equal(F.min_max_quantize(m, qmin, qmax, one(0.0), one(255.0)), m)
+    W = 1 << 20
+    for lo in (0, (1 << 29) - W // 2, (1 << 30) - W - 3, n - W):
+        w = x[lo:lo + W].cpu().numpy()
+        assert np.array_equal(bits(host(y[lo:lo + W])), bits(oracle.fixed_point_quantize(w, True, 8, 2.0 ** -4)))
+        assert np.array_equal(bits(host(p[lo:lo + W])), bits(oracle.pow2_quantize(w, True, True, 8, 1)))
+        assert np.array_equal(bits(host(m[lo:lo + W])), bits(oracle.min_max_quantize(w, [-4], [4], [0], [255])[0]))
+    del p, m
+    # backward at the same size: the gradient passes exactly where the forward did not clip
+    # (step 2^-5: the clip limits +-127 * 2^-5 = +-3.97 lie inside the data range; dy := y, any tensor will do)
+    dx = F.fixed_point_quantize_backward(x, y, True, 8, 2.0 ** -5, True, False)
+    limit = (2.0 ** 7 - 1) * 2.0 ** -5
+    inside = (x <= limit) & (x >= -limit)
+    assert int((~inside).sum()) > 0
+    assert torch.equal(dx, torch.where(inside, y, torch.zeros_like(y)))
+    for lo in ((1 << 30) - W - 3, n - W):
+        want = oracle.fixed_point_quantize_backward(x[lo:lo + W].cpu().numpy(), y[lo:lo + W].cpu().numpy(), True, 8,
+                                                    2.0 ** -5)
+        assert np.array_equal(bits(host(dx[lo:lo + W])), bits(want))
