@@ -210,6 +210,18 @@ int nb200_bn_add_relu_fxp_f32(const float *a, const float *beta_a, const float *
                               int64_t inner, float eps, int relu, int quantize, int sign, int n, float delta,
                               void *stream);
 
+/* Convolution<float>::forward_impl (src/nbla/function/generic/convolution.cpp:160-197)
+ * for operands that are outputs of FixedPointQuantize with at most 8 bits (what
+ * fixed_point_quantized_convolution builds, python/src/nnabla/parametric_functions.py:2411-):
+ * xq multiples of delta_x, wq [outmaps, channels / group, kh, kw] multiples of
+ * delta_w, |code| <= 127. int8 tensor-core path with int32 accumulation:
+ * y = float(acc) * (delta_x * delta_w) + bias, exact whenever the reference's
+ * fp32 result is. */
+int nb200_convolution_fxp8_f32(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias,
+                               float *y, int batch, int channels, int height, int width, int outmaps, int kernel_h,
+                               int kernel_w, int pad_h, int pad_w, int stride_h, int stride_w, int dilation_h,
+                               int dilation_w, int group, void *stream);
+
 /* ---- binary convolution backward passes ------------------------------------------
  * Convolution<float>::backward_impl
  * (src/nbla/function/generic/convolution.cpp:199-300) as the binary layers

@@ -128,12 +128,19 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
 }
 
 // Shared body of BinaryWeightConvolution / BinaryConnectConvolution forward.
+// weight_delta > 0: w itself holds multiples of weight_delta (a fixed-point convolution of two
+// 8-bit operands: no binarisation, wb / alpha unused, int8 path only).
 int binary_convolution(const float *x, const float *w, float *wb, float *alpha, const float *bias, float *y,
-                       ConvGeometry g, float zero_to, float act_delta, cudaStream_t st) {
+                       ConvGeometry g, float zero_to, float act_delta, cudaStream_t st, float weight_delta = 0.0f) {
   NB_TRY(check_geometry(g));
-  NB_CHECK(x && w && wb && y, NB200_EVALUE, "null data pointer");
+  const bool fxp_weights = weight_delta > 0.0f;
+  NB_CHECK(x && w && (wb || fxp_weights) && y, NB200_EVALUE, "null data pointer");
   const bool int8 = act_delta > 0.0f;
-  if (int8)
+  NB_CHECK(int8 || !fxp_weights, NB200_EVALUE, "fixed-point weights need fixed-point activations");
+  if (fxp_weights) {
+    // |acc| <= taps * Cg * 127 * 127 must fit int32
+    NB_CHECK((int64_t)g.Cg * g.kh * g.kw <= 133000, NB200_ENOTIMPL, "the int32 accumulator could overflow");
+  } else if (int8)
     NB_CHECK(zero_to == 1.0f || zero_to == -1.0f || zero_to == 0.0f, NB200_ENOTIMPL,
              "the int8 path needs quantize_zero_to in {-1, 0, 1} (got %g)", zero_to);
   else
@@ -163,13 +170,16 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   uint8_t *side = act + round_up(act_bytes, 1024);
   if (c_slots != g.Cg)
     NB_CUDA(cudaMemsetAsync(side, 0, side_bytes, st));
-  NB_TRY(binarize_rows(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, int8, st));
+  if (fxp_weights)
+    NB_TRY(codes_conv_weights(w, g.Ko, g.Cg, g.kh, g.kw, weight_delta, side, wpitch, c_slots, st));
+  else
+    NB_TRY(binarize_rows(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, int8, st));
   NB_TRY(nchw_to_nhwc_planes(x, g.N, g.C, g.H * g.W, g.group, g.Cg, c_pad_g, (int)ctot, int8 ? 0 : 3, act_delta, act,
                              st));
   GemmEpilogue ep{};
   ep.y = y;
-  ep.scale = int8 ? act_delta : 1.0f;
-  ep.row_scale = alpha;
+  ep.scale = fxp_weights ? act_delta * weight_delta : (int8 ? act_delta : 1.0f);
+  ep.row_scale = fxp_weights ? nullptr : alpha;
   ep.row_bias = bias;
   // Box selection: prefer the 128-column kernel (deeper pipeline) unless the
   // 256-column box is better filled.
@@ -430,5 +440,15 @@ int nb200_convolution_backward_f32(const float *x, const float *dy, float *dw, f
                  dilation_h, dilation_w, group, 0, 0, 0, 0};
   return convolution_backward(x, nullptr, nullptr, dy, nullptr, dw, db, g, 0, accum_dw, accum_db, 0.0f,
                               as_stream(stream));
+}
+
+int nb200_convolution_fxp8_f32(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias,
+                               float *y, int batch, int channels, int height, int width, int outmaps, int kernel_h,
+                               int kernel_w, int pad_h, int pad_w, int stride_h, int stride_w, int dilation_h,
+                               int dilation_w, int group, void *stream) {
+  NB_CHECK(delta_x > 0.f && delta_w > 0.f, NB200_EVALUE, "step sizes must be positive");
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, group, 0, 0, 0, 0};
+  return binary_convolution(xq, wq, nullptr, nullptr, bias, y, g, 1.0f, delta_x, as_stream(stream), delta_w);
 }
 }

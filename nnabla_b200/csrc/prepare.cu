@@ -123,6 +123,20 @@ __global__ void __launch_bounds__(256) binarize_rows_kernel(const float *__restr
   }
 }
 
+// Fixed-point convolution weights: wq [Ko, Cg, kh, kw] holds multiples of delta
+// (|code| <= 127); the int8 codes go to the same tap-major side-band layout.
+__global__ void __launch_bounds__(256) codes_conv_weights_kernel(const float *__restrict__ wq, int Cg, int kh, int kw,
+                                                                 float inv_delta, int8_t *__restrict__ side,
+                                                                 int64_t side_pitch, int c_pad) {
+  const int o = blockIdx.x;
+  const int taps = kh * kw, Kd = Cg * taps;
+  const float *wr = wq + (int64_t)o * Kd;
+  for (int k = threadIdx.x; k < Kd; k += 256) {
+    const int c = k / taps, t = k - c * taps;
+    side[(int64_t)o * side_pitch + (int64_t)t * c_pad + c] = (int8_t)__float2int_rn(__fmul_rn(wr[k], inv_delta));
+  }
+}
+
 // ---------------------------------------------------------------------------
 // fp32 [rows, K] -> bf16 planes [3][rows][Kp]: hi = bf16(x), mid = bf16(x - hi),
 // lo = bf16(x - hi - mid); the two subtractions are exact in fp32.
@@ -382,6 +396,14 @@ int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to,
     binarize_rows_kernel<true><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
   else
     binarize_rows_kernel<false><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+int codes_conv_weights(const float *wq, int Ko, int Cg, int kh, int kw, float delta, void *side, int64_t side_pitch,
+                       int c_pad, cudaStream_t st) {
+  codes_conv_weights_kernel<<<Ko, 256, 0, st>>>(wq, Cg, kh, kw, 1.0f / delta, reinterpret_cast<int8_t *>(side),
+                                                side_pitch, c_pad);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }

@@ -13,6 +13,9 @@ int binarize_columns(const float *w, int R, int C, float zero_to, float *wb, flo
 // with K ordered (ky, kx, c) and c padded to c_pad.
 int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to, float *wb, float *alpha, void *side,
                   int64_t side_pitch, int c_pad, bool int8, cudaStream_t st);
+// wq [Ko, Cg, kh, kw] multiples of delta -> int8 codes in the side-band layout of binarize_rows.
+int codes_conv_weights(const float *wq, int Ko, int Cg, int kh, int kw, float delta, void *side, int64_t side_pitch,
+                       int c_pad, cudaStream_t st);
 // fp32 [rows, K] -> bf16 [planes][rows][Kp] (planes = 1 or 3; hi, mid, lo).
 // col_scale (K floats or NULL): x[r, k] is multiplied by col_scale[k] first.
 int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st,

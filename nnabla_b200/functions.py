@@ -606,9 +606,13 @@ def convolution_backward(x, weight_shape, dy, base_axis=1, pad=None, stride=None
 # ---------------------------------------------------------------------------
 
 def convolution(x, weight, bias=None, base_axis=1, pad=None, stride=None, dilation=None, group=1,
-                channel_last=False, n_outputs=-1, outputs=None):
-    """Convolution (function_bases.convolution; src/nbla/function/generic/convolution.cpp:160-197),
-    full precision, for layers with few input channels (the network stem)."""
+                channel_last=False, n_outputs=-1, outputs=None, fixed_point=None):
+    """Convolution (function_bases.convolution; src/nbla/function/generic/convolution.cpp:160-197).
+
+    fixed_point=(delta_x, delta_w): x and weight are outputs of
+    fixed_point_quantize with n <= 8 and those step sizes; the convolution then
+    runs on the int8 tensor-core path (exact). Otherwise full precision, for
+    layers with few input channels (the network stem)."""
     if channel_last:
         raise C.NB200Error(4, "channel_last=True is not supported (nor by the reference's CPU Convolution)")
     x, weight = _check_input(x), _check_input(weight, "weight")
@@ -616,6 +620,12 @@ def convolution(x, weight, bias=None, base_axis=1, pad=None, stride=None, dilati
     batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
         x, weight, bias, base_axis, pad, stride, dilation, group)
     y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
+    if fixed_point is not None:
+        with torch.cuda.device(x.device):
+            C.call("nb200_convolution_fxp8_f32", C.ptr(x), C.ptr(weight), C.c_float(fixed_point[0]),
+                   C.c_float(fixed_point[1]), C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1],
+                   stride[0], stride[1], dilation[0], dilation[1], int(group), C.stream_ptr(x.device))
+        return y
     with torch.cuda.device(x.device):
         C.call("nb200_convolution_f32", C.ptr(x), C.ptr(weight), C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw,
                pad[0], pad[1], stride[0], stride[1], dilation[0], dilation[1], int(group), C.stream_ptr(x.device))

@@ -163,3 +163,106 @@ def batch_normalization(inp, axes=[1], decay_rate=0.9, eps=1e-5, batch_stat=True
         mean = get_parameter_or_create("mean", shape, init.get("mean", _zeros))
         var = get_parameter_or_create("var", shape, init.get("var", lambda s: np.ones(s, np.float32)))
     return F.batch_normalization(inp, beta, gamma, mean, var, axes, decay_rate, eps, batch_stat, output_stat)
+
+
+def fixed_point_quantized_affine(inp, n_outmaps, base_axis=1, w_init=None, b_init=None, fix_parameters=False, rng=None,
+                                 with_bias=True, quantize_w=True, sign_w=True, n_w=8, delta_w=2 ** -4,
+                                 ste_fine_grained_w=True, quantize_b=True, sign_b=True, n_b=8, delta_b=2 ** -4,
+                                 ste_fine_grained_b=True, input_delta=None):
+    """Fixed-Point Quantized Affine (python/src/nnabla/parametric_functions.py:2296-2408):
+    y = x . Q(W) + Q(b), with the quantized copies kept as parameters W_q / b_q.
+    input_delta=d declares that inp holds multiples of d with at most 8 bits
+    (the output of fixed_point_quantize); with 8-bit weights the product then
+    runs on the exact int8 tensor-core path."""
+    n_outmaps = (n_outmaps,) if isinstance(n_outmaps, int) else tuple(n_outmaps)
+    inmaps = int(np.prod(inp.shape[base_axis:]))
+    with parameter_scope("fp_quantized_affine"):
+        w = get_parameter_or_create("W", (inmaps,) + n_outmaps,
+                                    w_init or _glorot_uniform(inmaps, int(np.prod(n_outmaps)), (1, 1), _rng(rng)))
+        real_w = w
+        if quantize_w:
+            w_q = get_parameter_or_create("W_q", (inmaps,) + n_outmaps, _zeros)
+            real_w = F.fixed_point_quantize(w, sign_w, n_w, delta_w, True, ste_fine_grained_w, outputs=[w_q])
+        real_b = None
+        if with_bias:
+            b = get_parameter_or_create("b", n_outmaps, b_init or _zeros)
+            real_b = b
+            if quantize_b:
+                b_q = get_parameter_or_create("b_q", n_outmaps, _zeros)
+                real_b = F.fixed_point_quantize(b, sign_b, n_b, delta_b, True, ste_fine_grained_b, outputs=[b_q])
+    exact = input_delta is not None and quantize_w and (n_w - (1 if sign_w else 0)) <= 7
+    return F.affine(inp, real_w, real_b, base_axis, fixed_point=(input_delta, delta_w) if exact else None)
+
+
+def fixed_point_quantized_convolution(inp, outmaps, kernel, pad=None, stride=None, dilation=None, group=1,
+                                      channel_last=False, w_init=None, b_init=None, base_axis=1, fix_parameters=False,
+                                      rng=None, with_bias=True, quantize_w=True, sign_w=True, n_w=8, delta_w=2 ** -4,
+                                      ste_fine_grained_w=True, quantize_b=True, sign_b=True, n_b=8, delta_b=2 ** -4,
+                                      ste_fine_grained_b=True, input_delta=None):
+    """Fixed-Point Quantized Convolution (python/src/nnabla/parametric_functions.py:2411-2530).
+    With input_delta and 8-bit weights the convolution is the exact int8 one;
+    without them only few-channel inputs are supported (the full-precision stem kernel)."""
+    inmaps = int(inp.shape[base_axis])
+    with parameter_scope("fp_quantized_conv"):
+        w = get_parameter_or_create("W", (outmaps, inmaps // group) + tuple(kernel),
+                                    w_init or _glorot_uniform(inmaps, outmaps, tuple(kernel), _rng(rng)))
+        real_w = w
+        if quantize_w:
+            w_q = get_parameter_or_create("W_q", (outmaps, inmaps // group) + tuple(kernel), _zeros)
+            real_w = F.fixed_point_quantize(w, sign_w, n_w, delta_w, True, ste_fine_grained_w, outputs=[w_q])
+        real_b = None
+        if with_bias:
+            b = get_parameter_or_create("b", (outmaps,), b_init or _zeros)
+            real_b = b
+            if quantize_b:
+                b_q = get_parameter_or_create("b_q", (outmaps,), _zeros)
+                real_b = F.fixed_point_quantize(b, sign_b, n_b, delta_b, True, ste_fine_grained_b, outputs=[b_q])
+    exact = input_delta is not None and quantize_w and (n_w - (1 if sign_w else 0)) <= 7
+    return F.convolution(inp, real_w, real_b, base_axis, pad, stride, dilation, group, channel_last,
+                         fixed_point=(input_delta, delta_w) if exact else None)
+
+
+def pow2_quantized_affine(inp, n_outmaps, base_axis=1, w_init=None, b_init=None, fix_parameters=False, rng=None,
+                          with_bias=True, quantize_w=True, sign_w=True, with_zero_w=False, n_w=8, m_w=2,
+                          ste_fine_grained_w=True, quantize_b=True, sign_b=True, with_zero_b=False, n_b=8, m_b=2,
+                          ste_fine_grained_b=True):
+    """Pow2 Quantized Affine (python/src/nnabla/parametric_functions.py:2533-2645)."""
+    n_outmaps = (n_outmaps,) if isinstance(n_outmaps, int) else tuple(n_outmaps)
+    inmaps = int(np.prod(inp.shape[base_axis:]))
+    with parameter_scope("pow2_quantized_affine"):
+        w = get_parameter_or_create("W", (inmaps,) + n_outmaps,
+                                    w_init or _glorot_uniform(inmaps, int(np.prod(n_outmaps)), (1, 1), _rng(rng)))
+        real_w = w
+        if quantize_w:
+            w_q = get_parameter_or_create("W_q", (inmaps,) + n_outmaps, _zeros)
+            real_w = F.pow2_quantize(w, sign_w, with_zero_w, n_w, m_w, True, ste_fine_grained_w, outputs=[w_q])
+        real_b = None
+        if with_bias:
+            b = get_parameter_or_create("b", n_outmaps, b_init or _zeros)
+            real_b = b
+            if quantize_b:
+                b_q = get_parameter_or_create("b_q", n_outmaps, _zeros)
+                real_b = F.pow2_quantize(b, sign_b, with_zero_b, n_b, m_b, True, ste_fine_grained_b, outputs=[b_q])
+    return F.affine(inp, real_w, real_b, base_axis)
+
+
+def pruned_affine(inp, n_outmaps, base_axis=1, w_init=None, b_init=None, fix_parameters=False, rng=None,
+                  with_bias=True, prune_w=True, rate_w=0.9, prune_b=True, rate_b=0.9):
+    """Pruned Affine (python/src/nnabla/parametric_functions.py:2765-2864)."""
+    n_outmaps = (n_outmaps,) if isinstance(n_outmaps, int) else tuple(n_outmaps)
+    inmaps = int(np.prod(inp.shape[base_axis:]))
+    with parameter_scope("pruned_affine"):
+        w = get_parameter_or_create("W", (inmaps,) + n_outmaps,
+                                    w_init or _glorot_uniform(inmaps, int(np.prod(n_outmaps)), (1, 1), _rng(rng)))
+        real_w = w
+        if prune_w:
+            w_q = get_parameter_or_create("W_q", (inmaps,) + n_outmaps, _zeros)
+            real_w = F.prune(w, rate_w, outputs=[w_q])
+        real_b = None
+        if with_bias:
+            b = get_parameter_or_create("b", n_outmaps, b_init or _zeros)
+            real_b = b
+            if prune_b:
+                b_q = get_parameter_or_create("b_q", n_outmaps, _zeros)
+                real_b = F.prune(b, rate_b, outputs=[b_q])
+    return F.affine(inp, real_w, real_b, base_axis)

@@ -109,3 +109,50 @@ def test_conv_errors(F):
         F.binary_weight_convolution(x, torch.zeros(6, 4, 9, 9, device="cuda"), torch.zeros(6, 4, 9, 9, device="cuda"), al)
     with pytest.raises(RuntimeError, match="alpha"):
         F.binary_weight_convolution(x, w, torch.zeros_like(w), torch.zeros(5, device="cuda"))
+
+
+@pytest.mark.parametrize("xs,ws,pad,stride,dil,grp", cases.CONV_CASES + [((2, 64, 14, 14), (64, 64, 3, 3), (1, 1), (1, 1), (1, 1), 1)])
+def test_fixed_point_convolution_is_exact(F, xs, ws, pad, stride, dil, grp):
+    """Both operands 8-bit fixed point: every partial sum is an integer below 2^24 times a
+    power of two, so the int8 path must reproduce the fp32 oracle bit for bit."""
+    x, w, b = cases.conv_inputs(xs, ws)
+    xq = oracle.fixed_point_quantize(x, True, 8, 2.0 ** -5)
+    wq = oracle.fixed_point_quantize(0.1 * w, True, 8, 2.0 ** -9)
+    y = F.convolution(dev(xq), dev(wq), dev(b), 1, pad, stride, dil, grp, fixed_point=(2.0 ** -5, 2.0 ** -9))
+    F.check_device_status()
+    want = oracle.convolution(xq, wq, b, pad, stride, dil, grp)
+    assert np.array_equal(bits(y.cpu().numpy()), bits(want))
+
+
+def test_quantized_parametric_layers(F):
+    """fixed_point_quantized_affine / _convolution, pow2_quantized_affine and pruned_affine
+    (parametric_functions.py:2296-2864) are the quantizer followed by the plain layer; the
+    quantized copies are kept as parameters."""
+    from nnabla_b200 import parametric_functions as PF
+    PF.clear_parameters()
+    rng = np.random.RandomState(4)
+    x = oracle.fixed_point_quantize(rng.randn(6, 32).astype(np.float32), True, 8, 2.0 ** -4)
+    with PF.parameter_scope("a"):
+        y = PF.fixed_point_quantized_affine(dev(x), 24, rng=rng, delta_w=2.0 ** -6, input_delta=2.0 ** -4)
+    p = PF.get_parameters()
+    w, wq, bq = (p["a/fp_quantized_affine/" + k].cpu().numpy() for k in ("W", "W_q", "b_q"))
+    assert np.array_equal(bits(wq), bits(oracle.fixed_point_quantize(w, True, 8, 2.0 ** -6)))
+    assert np.array_equal(bits(y.cpu().numpy()), bits(oracle.affine(x, wq, bq)))
+    xc = oracle.fixed_point_quantize(rng.randn(2, 16, 9, 9).astype(np.float32), True, 8, 2.0 ** -4)
+    with PF.parameter_scope("c"):
+        yc = PF.fixed_point_quantized_convolution(dev(xc), 32, (3, 3), pad=(1, 1), rng=rng, delta_w=2.0 ** -6,
+                                                  input_delta=2.0 ** -4)
+    p = PF.get_parameters()
+    wq, bq = (p["c/fp_quantized_conv/" + k].cpu().numpy() for k in ("W_q", "b_q"))
+    assert np.array_equal(bits(yc.cpu().numpy()), bits(oracle.convolution(xc, wq, bq, (1, 1))))
+    with PF.parameter_scope("p"):
+        yp = PF.pow2_quantized_affine(dev(x), 24, rng=rng)
+        yr = PF.pruned_affine(dev(x), 24, rng=rng, rate_w=0.5)
+    p = PF.get_parameters()
+    w, wq = (p["p/pow2_quantized_affine/" + k].cpu().numpy() for k in ("W", "W_q"))
+    assert np.array_equal(bits(wq), bits(oracle.pow2_quantize(w, True, False, 8, 2)))
+    assert cases.rel_rms(yp.cpu().numpy(), oracle.affine(x, wq, p["p/pow2_quantized_affine/b_q"].cpu().numpy())) < 1e-5
+    w, wq = (p["p/pruned_affine/" + k].cpu().numpy() for k in ("W", "W_q"))
+    assert np.array_equal(bits(wq), bits(oracle.prune(w, 0.5)))
+    assert cases.rel_rms(yr.cpu().numpy(), oracle.affine(x, wq, p["p/pruned_affine/b_q"].cpu().numpy())) < 1e-5
+    PF.clear_parameters()
