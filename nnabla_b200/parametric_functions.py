@@ -266,3 +266,57 @@ def pruned_affine(inp, n_outmaps, base_axis=1, w_init=None, b_init=None, fix_par
                 b_q = get_parameter_or_create("b_q", n_outmaps, _zeros)
                 real_b = F.prune(b, rate_b, outputs=[b_q])
     return F.affine(inp, real_w, real_b, base_axis)
+
+
+def _constant(value):
+    return lambda shape: np.full(shape, value, np.float32)
+
+
+def min_max_quantize(x, ql_min=0, ql_max=255, decay=0.999, x_min_max=False, ema=False, ste_fine_grained=True,
+                     eps=0.01, qr_min_init=None, qr_max_init=None, fix_parameters=False, outputs=None,
+                     name="min_max_quantize"):
+    """Min-max quantization with its ranges kept as parameters
+    (python/src/nnabla/parametric_functions.py:2971-3097): scalar quantization
+    levels become (1, ..., 1)-shaped parameters ql_min / ql_max, the ranges
+    qr_min / qr_max start at -6 / 6 unless initialisers are given."""
+    with parameter_scope(name):
+        ones = (1,) * x.dim()
+        if isinstance(ql_min, (int, float)):
+            ql_min = get_parameter_or_create("ql_min", ones, _constant(ql_min))
+        if isinstance(ql_max, (int, float)):
+            ql_max = get_parameter_or_create("ql_max", ones, _constant(ql_max))
+        shape = tuple(ql_min.shape)
+        qr_min = get_parameter_or_create("qr_min", shape, qr_min_init or _constant(-6.0))
+        qr_max = get_parameter_or_create("qr_max", shape, qr_max_init or _constant(6.0))
+    return F.min_max_quantize(x, qr_min, qr_max, ql_min, ql_max, decay, x_min_max, ema, ste_fine_grained, eps,
+                              outputs=outputs)
+
+
+def min_max_quantized_affine(inp, n_outmaps, base_axis=1, w_init=None, b_init=None, fix_parameters=False, rng=None,
+                             with_bias=True, quantize_w=True, ql_min_w=0, ql_max_w=255, w_min_max=False,
+                             qr_min_w_init=None, qr_max_w_init=None, ste_fine_grained_w=True, quantize_b=True,
+                             ql_min_b=0, ql_max_b=255, b_min_max=False, qr_min_b_init=None, qr_max_b_init=None,
+                             ste_fine_grained_b=True, eps=0.01):
+    """Min-max Quantized Affine (python/src/nnabla/parametric_functions.py:3110-3256):
+    weight ranges start at -2 / 2, bias ranges at -6 / 6."""
+    n_outmaps = (n_outmaps,) if isinstance(n_outmaps, int) else tuple(n_outmaps)
+    inmaps = int(np.prod(inp.shape[base_axis:]))
+    with parameter_scope("min_max_quantized_affine"):
+        w = get_parameter_or_create("W", (inmaps,) + n_outmaps,
+                                    w_init or _glorot_uniform(inmaps, int(np.prod(n_outmaps)), (1, 1), _rng(rng)))
+        real_w = w
+        if quantize_w:
+            w_q = get_parameter_or_create("W_q", (inmaps,) + n_outmaps, _zeros)
+            real_w = min_max_quantize(w, ql_min_w, ql_max_w, 0.999, w_min_max, False, ste_fine_grained_w, eps,
+                                      qr_min_w_init or _constant(-2.0), qr_max_w_init or _constant(2.0),
+                                      fix_parameters, outputs=[w_q], name="min_max_quantize_w")
+        real_b = None
+        if with_bias:
+            b = get_parameter_or_create("b", n_outmaps, b_init or _zeros)
+            real_b = b
+            if quantize_b:
+                b_q = get_parameter_or_create("b_q", n_outmaps, _zeros)
+                real_b = min_max_quantize(b, ql_min_b, ql_max_b, 0.999, b_min_max, False, ste_fine_grained_b, eps,
+                                          qr_min_b_init or _constant(-6.0), qr_max_b_init or _constant(6.0),
+                                          fix_parameters, outputs=[b_q], name="min_max_quantize_b")
+    return F.affine(inp, real_w, real_b, base_axis)

@@ -155,4 +155,14 @@ def test_quantized_parametric_layers(F):
     w, wq = (p["p/pruned_affine/" + k].cpu().numpy() for k in ("W", "W_q"))
     assert np.array_equal(bits(wq), bits(oracle.prune(w, 0.5)))
     assert cases.rel_rms(yr.cpu().numpy(), oracle.affine(x, wq, p["p/pruned_affine/b_q"].cpu().numpy())) < 1e-5
+    with PF.parameter_scope("m"):
+        ym = PF.min_max_quantized_affine(dev(x), 24, rng=rng)
+    p = PF.get_parameters()
+    pre = "m/min_max_quantized_affine/"
+    w, wq = p[pre + "W"].cpu().numpy(), p[pre + "W_q"].cpu().numpy()
+    one = lambda v: np.full((1, 1), v, np.float32)
+    want_wq, _, qmax_after, _ = oracle.min_max_quantize(w, one(-2), one(2), one(0), one(255))
+    assert np.array_equal(bits(wq), bits(want_wq))
+    assert np.array_equal(bits(p[pre + "min_max_quantize_w/qr_max"].cpu().numpy()), bits(qmax_after))
+    assert cases.rel_rms(ym.cpu().numpy(), oracle.affine(x, wq, p[pre + "b_q"].cpu().numpy())) < 1e-5
     PF.clear_parameters()
