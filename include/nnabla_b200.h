@@ -210,6 +210,50 @@ int nb200_bn_add_relu_fxp_f32(const float *a, const float *beta_a, const float *
                               int64_t inner, float eps, int relu, int quantize, int sign, int n, float delta,
                               void *stream);
 
+/* ---- activations kept as 8-bit codes between the layers -----------------------------
+ * An output of FixedPointQuantize with n - sign <= 7 is k * delta with an integer
+ * |k| <= 127 (fixed_point_quantize.cpp:53-65): the int8 code k carries the whole
+ * value. Between the layers of a quantized network the codes can replace the
+ * fp32 tensor: 1 byte per activation instead of 4, already in the channel-last
+ * layout that the int8 convolution reads, and the residual of a block is
+ * code * delta exactly. A "codes_nhwc" tensor is int8 [batch, inner, slots]
+ * (inner = height * width); channel c of group g = c / (channels / group) sits in
+ * slot g * pad16(channels / group) + c % (channels / group), the other slots
+ * hold 0. Results are bit-identical to the fp32 chain (a -0.0 of the chain is a
+ * +0.0 here; with the ReLU in front of the quantizer none occurs). */
+
+/* Slots per pixel of a codes_nhwc tensor (>= channels, a multiple of 16). */
+int64_t nb200_codes_nhwc_slots(int64_t channels, int group);
+/* xq [batch, channels, inner] fp32 multiples of delta, |multiple| <= 127 -> codes_nhwc. */
+int nb200_fixed_point_codes_nhwc(const float *xq, int8_t *codes, int64_t batch, int64_t channels, int64_t inner,
+                                 int group, float delta, void *stream);
+/* codes_nhwc -> y [batch, channels, inner] fp32 = code * delta. */
+int nb200_codes_nhwc_to_f32(const int8_t *codes, float *y, int64_t batch, int64_t channels, int64_t inner, int group,
+                            float delta, void *stream);
+/* nb200_bn_add_relu_fxp_f32 whose result is written as codes_nhwc (the
+ * quantizer is always applied; n - sign <= 7). The second operand is either
+ * b (fp32 [batch, channels, inner], with or without its own normalisation) or
+ * b_codes (codes_nhwc of the same shape and group, value code * b_delta), not both. */
+int nb200_bn_add_relu_fxp_codes_nhwc(const float *a, const float *beta_a, const float *gamma_a, const float *mean_a,
+                                     const float *var_a, const float *b, const float *beta_b, const float *gamma_b,
+                                     const float *mean_b, const float *var_b, const int8_t *b_codes, float b_delta,
+                                     int8_t *y_codes, int64_t batch, int64_t channels, int64_t inner, int group,
+                                     float eps, int relu, int sign, int n, float delta, void *stream);
+/* MaxPooling<float>::forward_impl (src/nbla/function/generic/max_pooling.cpp:140-191,
+ * output extent base_pooling.cpp:59) on a codes_nhwc tensor [batch, height * width,
+ * slots] -> [batch, Ho * Wo, slots]: the maximum of the codes is the code of the maximum. */
+int nb200_max_pooling_codes_nhwc(const int8_t *codes, int8_t *y_codes, int64_t batch, int64_t channels, int height,
+                                 int width, int group, int kernel_h, int kernel_w, int stride_h, int stride_w,
+                                 int pad_h, int pad_w, int ignore_border, void *stream);
+/* nb200_binary_weight_convolution_f32 / nb200_binary_connect_convolution_f32
+ * (alpha == NULL) on x given as codes_nhwc [batch, height * width, slots] with
+ * step activation_delta > 0; y is fp32 NCHW as usual. */
+int nb200_binary_convolution_codes_f32(const int8_t *x_codes, const float *w, float *wb, float *alpha,
+                                       const float *bias, float *y, int batch, int channels, int height, int width,
+                                       int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w, int stride_h,
+                                       int stride_w, int dilation_h, int dilation_w, int group,
+                                       float quantize_zero_to, float activation_delta, void *stream);
+
 /* Convolution<float>::forward_impl (src/nbla/function/generic/convolution.cpp:160-197)
  * for operands that are outputs of FixedPointQuantize with at most 8 bits (what
  * fixed_point_quantized_convolution builds, python/src/nnabla/parametric_functions.py:2411-):

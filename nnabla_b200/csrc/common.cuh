@@ -45,6 +45,27 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 __device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
 
+// Channel of a grid-stride walker over an [outer, C, S] tensor (item i belongs
+// to channel (i / S) % C): two 64-bit divisions when the walk starts, additions
+// afterwards (a 64-bit division per item costs more than the item's arithmetic).
+struct ChannelWalk {
+  unsigned off, c, ds, dc, S, C;
+  __device__ __forceinline__ ChannelWalk(size_t first, size_t stride, unsigned S_, unsigned C_) : S(S_), C(C_) {
+    const size_t plane = first / S_, dplane = stride / S_;
+    off = (unsigned)(first - plane * S_);
+    c = (unsigned)(plane % C_);
+    ds = (unsigned)(stride - dplane * S_);
+    dc = (unsigned)(dplane % C_);
+  }
+  __device__ __forceinline__ void next() {
+    off += ds;
+    const unsigned carry = off >= S ? 1u : 0u;
+    off -= carry ? S : 0u;
+    c += dc + carry;
+    c -= c >= C ? C : 0u;
+  }
+};
+
 // Stream-ordered scratch for one call: allocated from the device's default
 // memory pool (whose release threshold is raised on first use so that the pool
 // keeps its memory across synchronisations instead of returning it to the

@@ -34,8 +34,10 @@ __global__ void __launch_bounds__(kThreads) bn_inference_kernel(const float *__r
   if (kVec) {
     const size_t total4 = total / 4;
     const int S4 = S / 4;
-    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total4; i += stride) {
-      const int c = (int)((i / S4) % C);
+    const size_t first = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    ChannelWalk walk(first, stride, (unsigned)S4, (unsigned)C);
+    for (size_t i = first; i < total4; i += stride, walk.next()) {
+      const int c = (int)walk.c;
       const float m = __ldg(mean + c);
       const float sd = __fsqrt_rn(__fadd_rn(__ldg(var + c), eps));
       const float g = gamma ? __ldg(gamma + c) : 1.0f;
@@ -49,8 +51,10 @@ __global__ void __launch_bounds__(kThreads) bn_inference_kernel(const float *__r
       __stcs(reinterpret_cast<float4 *>(y) + i, r);
     }
   } else {
-    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
-      const int c = (int)((i / S) % C);
+    const size_t first = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    ChannelWalk walk(first, stride, (unsigned)S, (unsigned)C);
+    for (size_t i = first; i < total; i += stride, walk.next()) {
+      const int c = (int)walk.c;
       const float sd = __fsqrt_rn(__fadd_rn(var[c], eps));
       const float g = gamma ? gamma[c] : 1.0f;
       const float b = beta ? beta[c] : 0.0f;

@@ -130,12 +130,16 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
 // Shared body of BinaryWeightConvolution / BinaryConnectConvolution forward.
 // weight_delta > 0: w itself holds multiples of weight_delta (a fixed-point convolution of two
 // 8-bit operands: no binarisation, wb / alpha unused, int8 path only).
+// x_codes != NULL: the activations arrive as int8 channel-last codes in the layout below
+// (x unused, act_delta > 0 required) and the re-layout pass is skipped.
 int binary_convolution(const float *x, const float *w, float *wb, float *alpha, const float *bias, float *y,
-                       ConvGeometry g, float zero_to, float act_delta, cudaStream_t st, float weight_delta = 0.0f) {
+                       ConvGeometry g, float zero_to, float act_delta, cudaStream_t st, float weight_delta = 0.0f,
+                       const int8_t *x_codes = nullptr) {
   NB_TRY(check_geometry(g));
   const bool fxp_weights = weight_delta > 0.0f;
-  NB_CHECK(x && w && (wb || fxp_weights) && y, NB200_EVALUE, "null data pointer");
+  NB_CHECK((x || x_codes) && w && (wb || fxp_weights) && y, NB200_EVALUE, "null data pointer");
   const bool int8 = act_delta > 0.0f;
+  NB_CHECK(int8 || !x_codes, NB200_EVALUE, "activation codes need their step (activation_delta > 0)");
   NB_CHECK(int8 || !fxp_weights, NB200_EVALUE, "fixed-point weights need fixed-point activations");
   if (fxp_weights) {
     // |acc| <= taps * Cg * 127 * 127 must fit int32
@@ -159,23 +163,26 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   int64_t ctot = (int64_t)g.group * c_pad_g;
   if (ctot < E)
     ctot = E;
+  NB_CHECK(!int8 || ctot == codes_slots(g.C, g.group), NB200_EVALUE, "activation code layout mismatch");
   const int taps = g.kh * g.kw;
   const int64_t wpitch = (int64_t)taps * c_slots;
   const int planes = int8 ? 1 : 3;
-  const size_t act_bytes = (size_t)planes * g.N * g.H * g.W * ctot * es;
+  const size_t act_bytes = x_codes ? 0 : (size_t)planes * g.N * g.H * g.W * ctot * es;
   const size_t side_bytes = (size_t)g.Ko * wpitch * es;
   AsyncScratch scratch(st);
   NB_TRY(scratch.alloc(round_up(act_bytes, 1024) + round_up(side_bytes, 1024)));
-  uint8_t *act = static_cast<uint8_t *>(scratch.p);
-  uint8_t *side = act + round_up(act_bytes, 1024);
+  const uint8_t *act = x_codes ? reinterpret_cast<const uint8_t *>(x_codes) : static_cast<uint8_t *>(scratch.p);
+  uint8_t *side = static_cast<uint8_t *>(scratch.p) + round_up(act_bytes, 1024);
+  NB_CHECK((reinterpret_cast<uintptr_t>(act) & 15) == 0, NB200_EVALUE, "activation codes must be 16-byte aligned");
   if (c_slots != g.Cg)
     NB_CUDA(cudaMemsetAsync(side, 0, side_bytes, st));
   if (fxp_weights)
     NB_TRY(codes_conv_weights(w, g.Ko, g.Cg, g.kh, g.kw, weight_delta, side, wpitch, c_slots, st));
   else
     NB_TRY(binarize_rows(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, int8, st));
-  NB_TRY(nchw_to_nhwc_planes(x, g.N, g.C, g.H * g.W, g.group, g.Cg, c_pad_g, (int)ctot, int8 ? 0 : 3, act_delta, act,
-                             st));
+  if (!x_codes)
+    NB_TRY(nchw_to_nhwc_planes(x, g.N, g.C, g.H * g.W, g.group, g.Cg, c_pad_g, (int)ctot, int8 ? 0 : 3, act_delta,
+                               static_cast<uint8_t *>(scratch.p), st));
   GemmEpilogue ep{};
   ep.y = y;
   ep.scale = fxp_weights ? act_delta * weight_delta : (int8 ? act_delta : 1.0f);
@@ -405,6 +412,38 @@ int nb200_binary_connect_convolution_f32(const float *x, const float *w, float *
   ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
                  dilation_h, dilation_w, group, 0, 0, 0, 0};
   return binary_convolution(x, w, wb, nullptr, bias, y, g, quantize_zero_to, activation_delta, as_stream(stream));
+}
+
+int64_t nb200_codes_nhwc_slots(int64_t channels, int group) {
+  if (channels <= 0 || group <= 0 || channels % group != 0)
+    return 0;
+  return codes_slots(channels, group);
+}
+
+int nb200_fixed_point_codes_nhwc(const float *xq, int8_t *codes, int64_t batch, int64_t channels, int64_t inner,
+                                 int group, float delta, void *stream) {
+  NB_CHECK(batch >= 0 && channels > 0 && inner > 0 && group > 0 && channels % group == 0, NB200_EVALUE, "bad extents");
+  NB_CHECK(delta > 0.f, NB200_EVALUE, "delta should be positive");
+  NB_CHECK(channels < (1 << 30) && inner < (1 << 30), NB200_EVALUE, "extent exceeds 2^30");
+  if (batch == 0)
+    return NB200_OK;
+  NB_CHECK(xq && codes, NB200_EVALUE, "null data pointer");
+  const int Cg = (int)(channels / group);
+  return nchw_to_nhwc_planes(xq, (int)batch, (int)channels, (int)inner, group, Cg, (Cg + 15) / 16 * 16,
+                             (int)codes_slots(channels, group), 0, delta, codes, as_stream(stream));
+}
+
+int nb200_binary_convolution_codes_f32(const int8_t *x_codes, const float *w, float *wb, float *alpha,
+                                       const float *bias, float *y, int batch, int channels, int height, int width,
+                                       int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w, int stride_h,
+                                       int stride_w, int dilation_h, int dilation_w, int group,
+                                       float quantize_zero_to, float activation_delta, void *stream) {
+  NB_CHECK(x_codes != nullptr, NB200_EVALUE, "x_codes is NULL");
+  NB_CHECK(activation_delta > 0.f, NB200_EVALUE, "activation_delta should be positive");
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, group, 0, 0, 0, 0};
+  return binary_convolution(nullptr, w, wb, alpha, bias, y, g, quantize_zero_to, activation_delta, as_stream(stream),
+                            0.0f, x_codes);
 }
 
 int nb200_binary_weight_convolution_backward_f32(const float *x, const float *wb, const float *alpha, const float *dy,

@@ -16,6 +16,14 @@ int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to,
 // wq [Ko, Cg, kh, kw] multiples of delta -> int8 codes in the side-band layout of binarize_rows.
 int codes_conv_weights(const float *wq, int Ko, int Cg, int kh, int kw, float delta, void *side, int64_t side_pitch,
                        int c_pad, cudaStream_t st);
+// Channel slots per pixel of the int8 channel-last activation layout: every group padded to a
+// multiple of 16, the whole row at least one K block (64 slots when a group fits 64, else 128).
+inline int64_t codes_slots(int64_t channels, int group) {
+  const int64_t c_pad_g = (channels / group + 15) / 16 * 16;
+  const int64_t E = c_pad_g <= 64 ? 64 : 128;
+  const int64_t ctot = (int64_t)group * c_pad_g;
+  return ctot < E ? E : ctot;
+}
 // fp32 [rows, K] -> bf16 [planes][rows][Kp] (planes = 1 or 3; hi, mid, lo).
 // col_scale (K floats or NULL): x[r, k] is multiplied by col_scale[k] first.
 int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes, void *out, cudaStream_t st,

@@ -775,6 +775,165 @@ def bn_add_relu_fixed_point(a, bn_a, b=None, bn_b=None, eps=1e-05, relu=True, qu
 
 
 # ---------------------------------------------------------------------------
+# Activations kept as int8 channel-last codes between layers
+# ---------------------------------------------------------------------------
+
+def codes_nhwc_slots(channels, group=1):
+    """Slots per pixel of a codes tensor for `channels` channels in `group` groups."""
+    fn = C.lib().nb200_codes_nhwc_slots
+    fn.restype = ctypes.c_int64
+    n = int(fn(ctypes.c_int64(int(channels)), int(group)))
+    if n <= 0:
+        raise RuntimeError("Number of input channel needs to be divisible by group. Input channel: %d, group: %d."
+                           % (channels, group))
+    return n
+
+
+def _nchw_extents(x):
+    if x.dim() < 2:
+        raise RuntimeError("the channel axis is axis 1")
+    batch, ch = int(x.shape[0]), int(x.shape[1])
+    return batch, ch, x.numel() // max(batch * ch, 1)
+
+
+def fixed_point_codes_nhwc(xq, delta=2 ** -4, group=1):
+    """xq [batch, channels, ...] (an output of fixed_point_quantize with step
+    `delta` and n <= 8) -> int8 codes [batch, inner, slots], channel-last."""
+    xq = _check_input(xq, "xq")
+    batch, ch, inner = _nchw_extents(xq)
+    codes = torch.empty((batch, inner, codes_nhwc_slots(ch, group)), dtype=torch.int8, device=xq.device)
+    with torch.cuda.device(xq.device):
+        C.call("nb200_fixed_point_codes_nhwc", C.ptr(xq), C.ptr(codes), ctypes.c_int64(batch), ctypes.c_int64(ch),
+               ctypes.c_int64(inner), int(group), C.c_float(delta), C.stream_ptr(xq.device))
+    return codes
+
+
+def _check_codes(codes, batch, inner, channels, group, name="codes"):
+    if not isinstance(codes, torch.Tensor) or not codes.is_cuda or codes.dtype != torch.int8:
+        raise TypeError("%s must be an int8 torch.Tensor on a CUDA device" % name)
+    want = (batch, inner, codes_nhwc_slots(channels, group))
+    if tuple(codes.shape) != want or not codes.is_contiguous():
+        raise RuntimeError("%s must be a contiguous [batch, inner, slots] = %s tensor, got %s"
+                           % (name, want, tuple(codes.shape)))
+    return codes
+
+
+def codes_nhwc_to_float(codes, shape, delta=2 ** -4, group=1):
+    """codes [batch, inner, slots] -> fp32 tensor of `shape` = [batch, channels, ...] holding code * delta."""
+    shape = tuple(int(v) for v in shape)
+    batch, ch = shape[0], shape[1]
+    inner = 1
+    for v in shape[2:]:
+        inner *= v
+    codes = _check_codes(codes, batch, inner, ch, group)
+    y = torch.empty(shape, dtype=torch.float32, device=codes.device)
+    with torch.cuda.device(codes.device):
+        C.call("nb200_codes_nhwc_to_f32", C.ptr(codes), C.ptr(y), ctypes.c_int64(batch), ctypes.c_int64(ch),
+               ctypes.c_int64(inner), int(group), C.c_float(delta), C.stream_ptr(codes.device))
+    return y
+
+
+def bn_add_relu_fixed_point_codes(a, bn_a, b=None, bn_b=None, b_codes=None, b_delta=None, eps=1e-05, relu=True,
+                                  sign=True, n=8, delta=2 ** -4, group=1):
+    """bn_add_relu_fixed_point whose result is returned as int8 channel-last
+    codes (value = code * delta). The second operand is b (fp32, shaped like
+    a, normalised with bn_b when given) or b_codes (codes of a tensor shaped
+    like a, step b_delta, default delta)."""
+    a = _check_input(a, "a")
+    batch, Cn, inner = _nchw_extents(a)
+
+    def params(t4, what):
+        out = []
+        for t, nm in zip(t4, ("beta", "gamma", "mean", "variance")):
+            if t is None:
+                if nm in ("mean", "variance"):
+                    raise RuntimeError("mean and variance are required (%s)" % what)
+                out.append(None)
+                continue
+            t = _check_input(t, nm)
+            if t.numel() != Cn:
+                raise RuntimeError("%s must have %d elements (shape of the normalised axis)" % (nm, Cn))
+            out.append(t)
+        return out
+    pa = params(bn_a, "a")
+    pb = [None] * 4
+    if b is not None and b_codes is not None:
+        raise RuntimeError("the second operand is either b or b_codes")
+    if b is not None:
+        b = _check_input(b, "b")
+        _same_shape(a, b, "a vs b")
+        if bn_b is not None:
+            pb = params(bn_b, "b")
+    elif bn_b is not None:
+        raise RuntimeError("bn_b without b")
+    if b_codes is not None:
+        b_codes = _check_codes(b_codes, batch, inner, Cn, group, "b_codes")
+    y = torch.empty((batch, inner, codes_nhwc_slots(Cn, group)), dtype=torch.int8, device=a.device)
+    with torch.cuda.device(a.device):
+        C.call("nb200_bn_add_relu_fxp_codes_nhwc", C.ptr(a), C.ptr(pa[0]), C.ptr(pa[1]), C.ptr(pa[2]), C.ptr(pa[3]),
+               C.ptr(b), C.ptr(pb[0]), C.ptr(pb[1]), C.ptr(pb[2]), C.ptr(pb[3]), C.ptr(b_codes),
+               C.c_float(delta if b_delta is None else b_delta), C.ptr(y), ctypes.c_int64(batch), ctypes.c_int64(Cn),
+               ctypes.c_int64(inner), int(group), C.c_float(eps), int(bool(relu)), int(bool(sign)), int(n),
+               C.c_float(delta), C.stream_ptr(a.device))
+    return y
+
+
+def max_pooling_codes(codes, shape, kernel, stride=None, ignore_border=True, pad=None, group=1):
+    """max_pooling on int8 channel-last codes of a tensor of `shape` = (batch,
+    channels, height, width); returns (codes [batch, Ho * Wo, slots], pooled shape).
+    The maximum of the codes is the code of the maximum (python/src/nnabla/functions.py max_pooling;
+    src/nbla/function/generic/max_pooling.cpp:140-191)."""
+    shape = tuple(int(v) for v in shape)
+    if len(shape) != 4:
+        raise C.NB200Error(4, "only [batch, channels, height, width] tensors are implemented")
+    batch, Cn, H, W = shape
+    codes = _check_codes(codes, batch, H * W, Cn, group)
+    kernel = tuple(kernel)
+    stride = kernel if stride is None else tuple(stride)
+    pad = (0, 0) if pad is None else tuple(pad)
+    Ho = (H + pad[0] - (kernel[0] - pad[0] if ignore_border else 1)) // stride[0] + 1
+    Wo = (W + pad[1] - (kernel[1] - pad[1] if ignore_border else 1)) // stride[1] + 1
+    if Ho <= 0 or Wo <= 0:
+        raise RuntimeError("pooling output would be empty")
+    y = torch.empty((batch, Ho * Wo, codes.shape[2]), dtype=torch.int8, device=codes.device)
+    with torch.cuda.device(codes.device):
+        C.call("nb200_max_pooling_codes_nhwc", C.ptr(codes), C.ptr(y), ctypes.c_int64(batch), ctypes.c_int64(Cn), H, W,
+               int(group), int(kernel[0]), int(kernel[1]), int(stride[0]), int(stride[1]), int(pad[0]), int(pad[1]),
+               int(bool(ignore_border)), C.stream_ptr(codes.device))
+    return y, (batch, Cn, Ho, Wo)
+
+
+def binary_weight_convolution_from_codes(x_codes, x_shape, weight, binary_weight, alpha, bias=None, pad=None,
+                                         stride=None, dilation=None, group=1, quantize_zero_to=1.0,
+                                         activation_delta=2 ** -4, outputs=None):
+    """binary_weight_convolution (binary_connect_convolution when alpha is
+    None) on activations given as int8 channel-last codes of a tensor of shape
+    x_shape = (batch, channels, height, width) with step activation_delta."""
+    weight = _check_input(weight, "weight")
+    binary_weight = _check_input(binary_weight, "binary_weight")
+    bias = _check_input(bias, "bias") if bias is not None else None
+    x_shape = tuple(int(v) for v in x_shape)
+    if len(x_shape) != 4:
+        raise C.NB200Error(4, "only 2-D convolution with one batch axis is implemented for code tensors")
+    like = torch.empty(x_shape, dtype=torch.float32, device="meta")
+    batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
+        like, weight, bias, 1, pad, stride, dilation, group)
+    x_codes = _check_codes(x_codes, batch, H * W, Cin, group, "x_codes")
+    _same_shape(weight, binary_weight, "float vs binary")
+    if alpha is not None:
+        alpha = _check_input(alpha, "alpha")
+        if alpha.numel() != Ko:
+            raise RuntimeError("Size of alpha must be equal to the number of output maps.")
+    y = torch.empty(out_shape, dtype=torch.float32, device=weight.device) if outputs is None else outputs[0]
+    with torch.cuda.device(weight.device):
+        C.call("nb200_binary_convolution_codes_f32", C.ptr(x_codes), C.ptr(weight), C.ptr(binary_weight),
+               C.ptr(alpha), C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1], stride[0],
+               stride[1], dilation[0], dilation[1], int(group), C.c_float(quantize_zero_to),
+               C.c_float(activation_delta), C.stream_ptr(weight.device))
+    return y
+
+
+# ---------------------------------------------------------------------------
 # Sibling quantization functions
 # ---------------------------------------------------------------------------
 

@@ -61,7 +61,11 @@ class Runner:
     def __init__(self, ops, params, zeros_like, trace=None, fixed_point_hint=True, fused=False):
         """fused=True applies BN (+ residual) + ReLU + FixedPointQuantize as one
         function (ops.bn_add_relu_fixed_point), which is bit-identical to the
-        separate functions and reads / writes each activation once."""
+        separate functions and reads / writes each activation once.
+        fused="codes" additionally keeps the quantized activations between the
+        binary-weight layers as int8 channel-last codes (1 byte per value, the
+        layout the int8 convolution reads; the residual is code * delta): the
+        same logits, bit for bit."""
         self.fused = fused
         self.ops = ops
         self.p = params
@@ -106,7 +110,42 @@ class Runner:
         y = self.ops.binary_weight_convolution(x, w, wb, alpha, None, 1, pad, (stride, stride), (1, 1), 1, 1.0, **kw)
         return self._rec(name, "binary_weight_convolution", [x], y, k=k, stride=stride)
 
+    def bwconv_codes(self, name, codes, shape, k, stride):
+        w = self.p[name + "/W"]
+        if name not in self.side:
+            self.side[name] = (self.zeros_like(w), self.zeros_like(w, (w.shape[0],)))
+        wb, alpha = self.side[name]
+        return self.ops.binary_weight_convolution_from_codes(codes, shape, w, wb, alpha, None, (k // 2, k // 2),
+                                                             (stride, stride), (1, 1), 1, 1.0, DELTA)
+
+    def act_codes(self, a, bn_a, b=None, bn_b=None, b_codes=None):
+        return self.ops.bn_add_relu_fixed_point_codes(a, self.bn_params(bn_a), b, self.bn_params(bn_b) if bn_b else None,
+                                                      b_codes, DELTA, 1e-5, True, True, 8, DELTA)
+
+    def _call_codes(self, x):
+        o = self.ops
+        h = o.convolution(x, self.p["stem/conv/W"], None, 1, (3, 3), (2, 2), (1, 1), 1)
+        hc, shape = o.max_pooling_codes(self.act_codes(h, "stem/bn"), tuple(h.shape), (3, 3), (2, 2), True, (1, 1))
+        cin = 64
+        for s, (c, stride) in enumerate(STAGES):
+            for b in range(2):
+                st = stride if b == 0 else 1
+                name = "stage%d/block%d" % (s + 1, b)
+                r = self.bwconv_codes(name + "/conv1", hc, shape, 3, st)
+                out_shape = tuple(r.shape)
+                r = self.bwconv_codes(name + "/conv2", self.act_codes(r, name + "/bn1"), out_shape, 3, 1)
+                if st != 1 or cin != c:
+                    sc = self.bwconv_codes(name + "/shortcut", hc, shape, 1, st)
+                    hc = self.act_codes(r, name + "/bn2", sc, name + "/bn_s")
+                else:
+                    hc = self.act_codes(r, name + "/bn2", b_codes=hc)
+                shape, cin = out_shape, c
+        g = o.global_average_pooling(o.codes_nhwc_to_float(hc, shape, DELTA))
+        return o.affine(g, self.p["head/W"], self.p["head/b"], 1)
+
     def __call__(self, x):
+        if self.fused == "codes":
+            return self._call_codes(x)
         o = self.ops
         h = o.convolution(x, self.p["stem/conv/W"], None, 1, (3, 3), (2, 2), (1, 1), 1)
         self._rec("stem/conv", "convolution", [x], h)
