@@ -7,6 +7,7 @@
 // CPU code; the convolution accumulates with fused multiply-adds (tolerance
 // parity, like the other contractions).
 #include "common.cuh"
+#include "narrow_conv.cuh"
 
 namespace nb200 {
 namespace {
@@ -562,6 +563,10 @@ int nb200_convolution_f32(const float *x, const float *w, const float *bias, flo
   NB_CHECK(eh >= 0 && ew >= 0, NB200_EVALUE, "Invalid configuration of convolution.");
   const int Ho = eh / stride_h + 1, Wo = ew / stride_w + 1;
   NB_CHECK(x && w && y, NB200_EVALUE, "null data pointer");
+  if (narrow_conv_applies(x, channels, height, width, outmaps, kernel_h, kernel_w, pad_w, stride_w, dilation_h,
+                          dilation_w, group, Wo))
+    return narrow_conv_tc(x, w, bias, y, batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w,
+                          stride_h, stride_w, Ho, Wo, as_stream(stream));
   constexpr int OT = 16, PX = 4;
   const size_t smem = (size_t)OT * channels * kernel_h * kernel_w * sizeof(float);
   NB_CHECK(smem <= 48 * 1024, NB200_ENOTIMPL,

@@ -56,7 +56,9 @@ int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, c
                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   const CUresult r = fn(map, dt,
                         (cuuint32_t)rank, const_cast<void *>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        swizzle_bytes == 0    ? CU_TENSOR_MAP_SWIZZLE_NONE
+                        : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                              : CU_TENSOR_MAP_SWIZZLE_128B,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   NB_CHECK(r == CUDA_SUCCESS, NB200_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);

@@ -68,6 +68,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
   }
 }
 
+// The same for warps whose polling would take issue slots from warps that do
+// arithmetic on the same SM: sleeps `sleep_ns` between polls.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity, volatile int *abort,
+                                                  uint32_t sleep_ns, uint64_t limit_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity))
+    return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t polls = 0;
+  while (true) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity))
+      return true;
+    if ((++polls & 15u) == 0) {
+      if (*abort != 0)
+        return false;
+      if (globaltimer_ns() - t0 > limit_ns)
+        return false;
+    }
+  }
+}
+
 // ---- TMA --------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -78,6 +99,13 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
                "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *m, uint64_t *bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
+               "r"(c2), "r"(c3)
                : "memory");
 }
 __device__ __forceinline__ void tma_load_5d(void *smem_dst, const CUtensorMap *m, uint64_t *bar, int c0, int c1,
