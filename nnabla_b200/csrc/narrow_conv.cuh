@@ -6,7 +6,7 @@ namespace nb200 {
 
 // Whether the geometry fits the kernel: group 1, no dilation, kernel_w * channels <= 24,
 // kernel_h <= 7, at most 64 output maps and 112 output columns, an even stride_w * channels,
-// rows of x that a TMA box can fetch (16-byte aligned, width a multiple of 4, at most 256).
+// padded rows of at most 704 values (channels * (width + 2 * pad_w)).
 // NNABLA_B200_DIRECT_CONV=1 switches the path off (the CUDA-core kernel then runs).
 bool narrow_conv_applies(const float *x, int channels, int height, int width, int outmaps, int kernel_h,
                          int kernel_w, int pad_w, int stride_w, int dilation_h, int dilation_w, int group, int Wo);

@@ -60,6 +60,9 @@ def test_pooling(F, k, s, p, ib):
                                               ((2, 2, 30, 28), (20, 2, 5, 7), (2, 3), (3, 2)),    # ragged maps and rows
                                               ((1, 3, 27, 29), (8, 3, 7, 7), (3, 1), (2, 2)),     # 7 does not divide Wo
 
+                                              ((3, 3, 224, 224), (64, 3, 7, 7), (3, 3), (2, 2)),  # tensor cores, 3 tiles per SM
+                                              ((2, 1, 64, 100), (48, 1, 6, 24), (2, 11), (2, 2)), # one channel, 24-wide filter rows
+                                              ((2, 4, 40, 36), (64, 4, 3, 5), (1, 2), (1, 1)),    # 4 channels, stride 1
                                               ((1, 3, 17, 19), (20, 3, 3, 3), (1, 1), (1, 1)),
                                               ((2, 4, 9, 9), (5, 4, 1, 1), (0, 0), (2, 2))])
 def test_full_precision_convolution(F, xs, ws, pad, stride):
@@ -70,7 +73,10 @@ def test_full_precision_convolution(F, xs, ws, pad, stride):
     y = host(F.convolution(dev(x), dev(w), dev(b), 1, pad, stride))
     want = oracle.convolution(x, w, b, pad, stride)
     assert y.shape == want.shape
-    assert cases.rel_rms(y, want) < 1e-6  # fused multiply-adds: fp32 rounding differs from the separate mul/add of the oracle
+    # fp32 rounding differs from the oracle's separate mul / add: fused multiply-adds in the CUDA-core
+    # kernel (about 1e-7), truncating fp32 accumulation of bf16 piece products on the tensor cores
+    # (about 6e-7 of the output RMS); the bar for contractions is 1e-5 of the output RMS
+    assert cases.rel_rms(y, want) < 2e-6
 
 
 @pytest.mark.parametrize("shape", [(2, 3, 16, 16), (1, 4, 13, 24), (3, 2, 8, 8), (1, 1, 56, 112)])
