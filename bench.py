@@ -103,6 +103,59 @@ def cpu_inputs(threads):
     return [x[i * per:(i + 1) * per] for i in range(threads)], per * threads
 
 
+def cpu_contraction_samples():
+    """CPU times of the GEMM / convolution configurations on bounded samples, beside the GPU
+    numbers of `other_configs`. The reference multiplies through Eigen, which its build downloads
+    and which is not in its tree; the contraction is therefore timed with the host's BLAS (NumPy)
+    under the reference's control flow (sign / alpha passes, one unfold + one GEMM per sample,
+    src/nbla/function/generic/convolution.cpp:160-197), once on 1 thread (the reference's CPU
+    build is single-threaded) and once on all cores."""
+    try:
+        from threadpoolctl import threadpool_limits
+    except ImportError:  # pragma: no cover - optional
+        return {"unavailable": "threadpoolctl is missing"}
+    rng = np.random.RandomState(0)
+    f32 = np.float32
+    out = {"blas": "NumPy's BLAS in place of Eigen (not vendored in the reference)"}
+
+    def best_ms(fn, reps=2):
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return 1e3 * min(ts)
+    x0, w0 = rng.randn(256, 1024).astype(f32), (0.02 * rng.randn(1024, 4096)).astype(f32)
+
+    def bwa():
+        alpha = np.abs(w0).sum(0) * f32(1.0 / 1024)
+        return x0 @ (np.where(w0 > 0, f32(1), f32(-1)) * alpha)
+    rows = 512  # of 8192
+    x2 = (np.rint(rng.randn(rows, 4096) * 32).clip(-127, 127) * f32(2.0 ** -5)).astype(f32)
+    w2 = (np.rint(rng.randn(4096, 8192) * 20).clip(-127, 127) * f32(2.0 ** -10)).astype(f32)
+    imgs = 4  # of 128
+    x3 = np.maximum(rng.randn(imgs, 256, 28, 28), 0).astype(f32)
+    w3 = (rng.randn(256, 2304) * np.sqrt(2.0 / 2304)).astype(f32)
+
+    def bwc():
+        alpha = np.abs(w3).sum(1) * f32(1.0 / 2304)
+        wb = np.where(w3 > 0, f32(1), f32(-1)) * alpha[:, None]
+        for i in range(imgs):
+            xp = np.pad(x3[i], ((0, 0), (1, 1), (1, 1)))
+            col = np.lib.stride_tricks.sliding_window_view(xp, (3, 3), axis=(1, 2))  # [256, 28, 28, 3, 3]
+            col = np.ascontiguousarray(col.transpose(0, 3, 4, 1, 2)).reshape(2304, 784)
+            wb @ col
+    for label, threads in (("1_thread", 1), ("all_cores", os.cpu_count() or 1)):
+        with threadpool_limits(limits=threads):
+            out[label] = {
+                "threads": threads,
+                "configs[0] binary_weight_affine 256x1024x4096 ms": best_ms(bwa),
+                "configs[2] affine 8192x4096x8192 ms (512 of 8192 rows timed, scaled x16)": 16 * best_ms(lambda: x2 @ w2),
+                "configs[3] binary_weight_convolution batch 128 ms (4 images timed, scaled x32)": 32 * best_ms(bwc),
+            }
+    return out
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -507,6 +560,8 @@ def run_b200_arm(args):
         cpu_baseline = {"value": 3 * BYTES_PER_ELEM * ncpu / sum(secs.values()) / 1e9, "unit": "GB/s", "cores": 1,
                         "kind": kind, "sample": "3 quantizers over 2^%d elements, 1 thread" % CPU_SAMPLE_LOG2,
                         "per_function_GBps": {k: BYTES_PER_ELEM * ncpu / v / 1e9 for k, v in secs.items()}}
+        if not args.no_extras and rank == 0:
+            cpu_baseline["other_configs"] = cpu_contraction_samples()
     line = {
         "metric": "quantizer_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
