@@ -409,6 +409,10 @@ def run_extras(args, rank, world, barrier):
     ms_codes = maxr(time_gpu(lambda: net_codes(x), 5, warm=2))
     F.check_device_status()
     same = bool(torch.equal(net_codes(x), net(x)))
+    net_prep = resnet18.Runner(F, params, gz, fused="codes", prepared_weights=True)
+    ms_prep = maxr(time_gpu(lambda: net_prep(x), 5, warm=2))
+    F.check_device_status()
+    same = same and bool(torch.equal(net_prep(x), net(x)))
     out["configs[4] binary-weight ResNet-18 224x224"] = {
         "ms_per_batch": ms, "images_per_sec_whole_job": Bg * world / ms * 1e3, "batch_per_gpu": Bg,
         "gmac_per_image": resnet18.conv_macs_per_image() / 1e9,
@@ -419,6 +423,10 @@ def run_extras(args, rank, world, barrier):
         "images_per_sec_whole_job_int8_activations": Bg * world / ms_codes * 1e3,
         "int8_activations": "the fused pass writes int8 channel-last codes that the next convolution reads directly "
                             "(1 byte per activation between layers, residual = code * delta)",
+        "ms_per_batch_int8_activations_prepared_weights": ms_prep,
+        "images_per_sec_whole_job_int8_activations_prepared_weights": Bg * world / ms_prep * 1e3,
+        "prepared_weights": "weights binarised once (inference: they do not change between calls) instead of in "
+                            "every forward pass as the reference's forward_impl does",
         "int8_activations_logits_equal_unfused": same}
     return out
 

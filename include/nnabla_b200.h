@@ -210,6 +210,19 @@ int nb200_bn_add_relu_fxp_f32(const float *a, const float *beta_a, const float *
                               int64_t inner, float eps, int relu, int quantize, int sign, int n, float delta,
                               void *stream);
 
+/* ---- binary weights prepared once per weight update -----------------------------------
+ * The binary convolutions re-derive sign(w), alpha and the tensor core's int8 side-band
+ * from w on every call, as the reference's forward_impl does
+ * (binary_weight_convolution.cpp:72-117). For inference, where w does not change between
+ * calls, they can be made once (what a cache keyed on SyncedArray::modification_count,
+ * include/nbla/synced_array.hpp:183, would hold) and passed to
+ * nb200_binary_convolution_codes_prepared_f32. side: int8, nb200_binary_weights_side_bytes
+ * bytes, 16-byte aligned; wb and alpha (NULL for BinaryConnect) are written as by the
+ * convolution itself. */
+int64_t nb200_binary_weights_side_bytes(int outmaps, int channels, int kernel_h, int kernel_w, int group);
+int nb200_binary_weights_prepare_i8(const float *w, float *wb, float *alpha, int8_t *side, int outmaps, int channels,
+                                    int kernel_h, int kernel_w, int group, float quantize_zero_to, void *stream);
+
 /* ---- activations kept as 8-bit codes between the layers -----------------------------
  * An output of FixedPointQuantize with n - sign <= 7 is k * delta with an integer
  * |k| <= 127 (fixed_point_quantize.cpp:53-65): the int8 code k carries the whole
@@ -253,6 +266,12 @@ int nb200_binary_convolution_codes_f32(const int8_t *x_codes, const float *w, fl
                                        int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w, int stride_h,
                                        int stride_w, int dilation_h, int dilation_w, int group,
                                        float quantize_zero_to, float activation_delta, void *stream);
+/* The same with weights prepared by nb200_binary_weights_prepare_i8 (alpha == NULL: BinaryConnect). */
+int nb200_binary_convolution_codes_prepared_f32(const int8_t *x_codes, const int8_t *side, const float *alpha,
+                                                const float *bias, float *y, int batch, int channels, int height,
+                                                int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                                int pad_w, int stride_h, int stride_w, int dilation_h,
+                                                int dilation_w, int group, float activation_delta, void *stream);
 
 /* Convolution<float>::forward_impl (src/nbla/function/generic/convolution.cpp:160-197)
  * for operands that are outputs of FixedPointQuantize with at most 8 bits (what

@@ -134,10 +134,15 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
 // (x unused, act_delta > 0 required) and the re-layout pass is skipped.
 int binary_convolution(const float *x, const float *w, float *wb, float *alpha, const float *bias, float *y,
                        ConvGeometry g, float zero_to, float act_delta, cudaStream_t st, float weight_delta = 0.0f,
-                       const int8_t *x_codes = nullptr) {
+                       const int8_t *x_codes = nullptr, const int8_t *prepared_side = nullptr) {
+  // prepared_side != NULL: the weights' int8 side-band (and alpha) were made once by
+  // nb200_binary_weights_prepare_i8; w / wb are unused and nothing is binarised here.
   NB_TRY(check_geometry(g));
   const bool fxp_weights = weight_delta > 0.0f;
-  NB_CHECK((x || x_codes) && w && (wb || fxp_weights) && y, NB200_EVALUE, "null data pointer");
+  NB_CHECK((x || x_codes) && (w || prepared_side) && (wb || fxp_weights || prepared_side) && y, NB200_EVALUE,
+           "null data pointer");
+  NB_CHECK(!prepared_side || (act_delta > 0.0f && !fxp_weights), NB200_EVALUE,
+           "prepared weights are for the int8 path (activation_delta > 0)");
   const bool int8 = act_delta > 0.0f;
   NB_CHECK(int8 || !x_codes, NB200_EVALUE, "activation codes need their step (activation_delta > 0)");
   NB_CHECK(int8 || !fxp_weights, NB200_EVALUE, "fixed-point weights need fixed-point activations");
@@ -168,18 +173,22 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   const int64_t wpitch = (int64_t)taps * c_slots;
   const int planes = int8 ? 1 : 3;
   const size_t act_bytes = x_codes ? 0 : (size_t)planes * g.N * g.H * g.W * ctot * es;
-  const size_t side_bytes = (size_t)g.Ko * wpitch * es;
+  const size_t side_bytes = prepared_side ? 0 : (size_t)g.Ko * wpitch * es;
   AsyncScratch scratch(st);
   NB_TRY(scratch.alloc(round_up(act_bytes, 1024) + round_up(side_bytes, 1024)));
   const uint8_t *act = x_codes ? reinterpret_cast<const uint8_t *>(x_codes) : static_cast<uint8_t *>(scratch.p);
-  uint8_t *side = static_cast<uint8_t *>(scratch.p) + round_up(act_bytes, 1024);
-  NB_CHECK((reinterpret_cast<uintptr_t>(act) & 15) == 0, NB200_EVALUE, "activation codes must be 16-byte aligned");
-  if (c_slots != g.Cg)
-    NB_CUDA(cudaMemsetAsync(side, 0, side_bytes, st));
-  if (fxp_weights)
-    NB_TRY(codes_conv_weights(w, g.Ko, g.Cg, g.kh, g.kw, weight_delta, side, wpitch, c_slots, st));
-  else
-    NB_TRY(binarize_rows(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, int8, st));
+  uint8_t *side = prepared_side ? const_cast<uint8_t *>(reinterpret_cast<const uint8_t *>(prepared_side))
+                                : static_cast<uint8_t *>(scratch.p) + round_up(act_bytes, 1024);
+  NB_CHECK(((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(side)) & 15) == 0, NB200_EVALUE,
+           "activation codes and prepared weights must be 16-byte aligned");
+  if (!prepared_side) {
+    if (c_slots != g.Cg)
+      NB_CUDA(cudaMemsetAsync(side, 0, side_bytes, st));
+    if (fxp_weights)
+      NB_TRY(codes_conv_weights(w, g.Ko, g.Cg, g.kh, g.kw, weight_delta, side, wpitch, c_slots, st));
+    else
+      NB_TRY(binarize_rows(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, int8, st));
+  }
   if (!x_codes)
     NB_TRY(nchw_to_nhwc_planes(x, g.N, g.C, g.H * g.W, g.group, g.Cg, c_pad_g, (int)ctot, int8 ? 0 : 3, act_delta,
                                static_cast<uint8_t *>(scratch.p), st));
@@ -444,6 +453,57 @@ int nb200_binary_convolution_codes_f32(const int8_t *x_codes, const float *w, fl
                  dilation_h, dilation_w, group, 0, 0, 0, 0};
   return binary_convolution(nullptr, w, wb, alpha, bias, y, g, quantize_zero_to, activation_delta, as_stream(stream),
                             0.0f, x_codes);
+}
+
+namespace {
+// slots per filter tap and row pitch of the int8 weight side-band [outmaps][taps * c_slots]
+void int8_side_layout(int Cg, int taps, int &c_slots, int64_t &wpitch) {
+  const int c_pad_g = (int)round_up(Cg, 16);
+  const int E = c_pad_g <= 64 ? 64 : kRowBytes;
+  c_slots = (c_pad_g + E - 1) / E * E;
+  wpitch = (int64_t)taps * c_slots;
+}
+} // namespace
+
+int64_t nb200_binary_weights_side_bytes(int outmaps, int channels, int kernel_h, int kernel_w, int group) {
+  if (outmaps <= 0 || channels <= 0 || kernel_h <= 0 || kernel_w <= 0 || group <= 0 || channels % group != 0)
+    return 0;
+  int c_slots;
+  int64_t wpitch;
+  int8_side_layout(channels / group, kernel_h * kernel_w, c_slots, wpitch);
+  return (int64_t)outmaps * wpitch;
+}
+
+int nb200_binary_weights_prepare_i8(const float *w, float *wb, float *alpha, int8_t *side, int outmaps, int channels,
+                                    int kernel_h, int kernel_w, int group, float quantize_zero_to, void *stream) {
+  NB_CHECK(outmaps > 0 && channels > 0 && kernel_h > 0 && kernel_w > 0 && group > 0 && channels % group == 0 &&
+               outmaps % group == 0,
+           NB200_EVALUE, "bad weight shape");
+  NB_CHECK(w && wb && side, NB200_EVALUE, "null data pointer");
+  NB_CHECK(quantize_zero_to == 1.0f || quantize_zero_to == -1.0f || quantize_zero_to == 0.0f, NB200_ENOTIMPL,
+           "the int8 path needs quantize_zero_to in {-1, 0, 1} (got %g)", quantize_zero_to);
+  NB_CHECK((reinterpret_cast<uintptr_t>(side) & 15) == 0, NB200_EVALUE, "the side-band must be 16-byte aligned");
+  const int Cg = channels / group;
+  int c_slots;
+  int64_t wpitch;
+  int8_side_layout(Cg, kernel_h * kernel_w, c_slots, wpitch);
+  cudaStream_t st = as_stream(stream);
+  if (c_slots != Cg)
+    NB_CUDA(cudaMemsetAsync(side, 0, (size_t)outmaps * wpitch, st));
+  return binarize_rows(w, outmaps, Cg, kernel_h, kernel_w, quantize_zero_to, wb, alpha, side, wpitch, c_slots, true, st);
+}
+
+int nb200_binary_convolution_codes_prepared_f32(const int8_t *x_codes, const int8_t *side, const float *alpha,
+                                                const float *bias, float *y, int batch, int channels, int height,
+                                                int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                                int pad_w, int stride_h, int stride_w, int dilation_h,
+                                                int dilation_w, int group, float activation_delta, void *stream) {
+  NB_CHECK(x_codes != nullptr && side != nullptr, NB200_EVALUE, "null data pointer");
+  NB_CHECK(activation_delta > 0.f, NB200_EVALUE, "activation_delta should be positive");
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, group, 0, 0, 0, 0};
+  return binary_convolution(nullptr, nullptr, nullptr, const_cast<float *>(alpha), bias, y, g, 1.0f, activation_delta,
+                            as_stream(stream), 0.0f, x_codes, side);
 }
 
 int nb200_binary_weight_convolution_backward_f32(const float *x, const float *wb, const float *alpha, const float *dy,

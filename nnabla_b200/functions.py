@@ -933,6 +933,60 @@ def binary_weight_convolution_from_codes(x_codes, x_shape, weight, binary_weight
     return y
 
 
+class PreparedBinaryWeights:
+    """sign(w), alpha and the int8 side-band of a binary convolution, made once
+    per weight update (prepare_binary_weights)."""
+
+    def __init__(self, shape, group, binary_weight, alpha, side):
+        self.shape, self.group = tuple(shape), int(group)
+        self.binary_weight, self.alpha, self.side = binary_weight, alpha, side
+
+
+def prepare_binary_weights(weight, group=1, quantize_zero_to=1.0, with_alpha=True):
+    """Binarises `weight` [outmaps, channels / group, kh, kw] once: what the binary
+    convolutions otherwise redo on every call (binary_weight_convolution.cpp:72-117).
+    with_alpha=False gives BinaryConnect weights (no scaling)."""
+    weight = _check_input(weight, "weight")
+    if weight.dim() != 4:
+        raise C.NB200Error(4, "only 2-D convolution weights are implemented")
+    Ko, Cg, kh, kw = (int(v) for v in weight.shape)
+    fn = C.lib().nb200_binary_weights_side_bytes
+    fn.restype = ctypes.c_int64
+    nbytes = int(fn(Ko, Cg * int(group), kh, kw, int(group)))
+    if nbytes <= 0 or Ko % group != 0:
+        raise RuntimeError("Number of output channel needs to be divisible by group. Output channel: %d, group: %d."
+                           % (Ko, group))
+    wb = torch.empty_like(weight)
+    alpha = torch.empty((Ko,), dtype=torch.float32, device=weight.device) if with_alpha else None
+    side = torch.empty((nbytes,), dtype=torch.int8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        C.call("nb200_binary_weights_prepare_i8", C.ptr(weight), C.ptr(wb), C.ptr(alpha), C.ptr(side), Ko,
+               Cg * int(group), kh, kw, int(group), C.c_float(quantize_zero_to), C.stream_ptr(weight.device))
+    return PreparedBinaryWeights(weight.shape, group, wb, alpha, side)
+
+
+def binary_convolution_from_codes_prepared(x_codes, x_shape, prepared, bias=None, pad=None, stride=None,
+                                           dilation=None, activation_delta=2 ** -4, outputs=None):
+    """binary_weight_convolution_from_codes with weights from prepare_binary_weights."""
+    bias = _check_input(bias, "bias") if bias is not None else None
+    x_shape = tuple(int(v) for v in x_shape)
+    if len(x_shape) != 4:
+        raise C.NB200Error(4, "only 2-D convolution with one batch axis is implemented for code tensors")
+    like_x = torch.empty(x_shape, dtype=torch.float32, device="meta")
+    like_w = torch.empty(prepared.shape, dtype=torch.float32, device="meta")
+    batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
+        like_x, like_w, bias, 1, pad, stride, dilation, prepared.group)
+    x_codes = _check_codes(x_codes, batch, H * W, Cin, prepared.group, "x_codes")
+    dev = x_codes.device
+    y = torch.empty(out_shape, dtype=torch.float32, device=dev) if outputs is None else outputs[0]
+    with torch.cuda.device(dev):
+        C.call("nb200_binary_convolution_codes_prepared_f32", C.ptr(x_codes), C.ptr(prepared.side),
+               C.ptr(prepared.alpha), C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1], stride[0],
+               stride[1], dilation[0], dilation[1], int(prepared.group), C.c_float(activation_delta),
+               C.stream_ptr(dev))
+    return y
+
+
 # ---------------------------------------------------------------------------
 # Sibling quantization functions
 # ---------------------------------------------------------------------------

@@ -58,7 +58,8 @@ def init_parameters(rng, num_classes=1000, in_channels=3):
 class Runner:
     """Applies the network with a given function namespace and array factory."""
 
-    def __init__(self, ops, params, zeros_like, trace=None, fixed_point_hint=True, fused=False):
+    def __init__(self, ops, params, zeros_like, trace=None, fixed_point_hint=True, fused=False,
+                 prepared_weights=False):
         """fused=True applies BN (+ residual) + ReLU + FixedPointQuantize as one
         function (ops.bn_add_relu_fixed_point), which is bit-identical to the
         separate functions and reads / writes each activation once.
@@ -66,6 +67,10 @@ class Runner:
         binary-weight layers as int8 channel-last codes (1 byte per value, the
         layout the int8 convolution reads; the residual is code * delta): the
         same logits, bit for bit."""
+        # prepared_weights (with fused="codes"): binarise every weight once, at its first use,
+        # instead of in every forward pass; for inference with weights that do not change
+        self.prepared_weights = prepared_weights
+        self.prepared = {}
         self.fused = fused
         self.ops = ops
         self.p = params
@@ -112,6 +117,11 @@ class Runner:
 
     def bwconv_codes(self, name, codes, shape, k, stride):
         w = self.p[name + "/W"]
+        if self.prepared_weights:
+            if name not in self.prepared:
+                self.prepared[name] = self.ops.prepare_binary_weights(w, 1, 1.0)
+            return self.ops.binary_convolution_from_codes_prepared(codes, shape, self.prepared[name], None,
+                                                                   (k // 2, k // 2), (stride, stride), (1, 1), DELTA)
         if name not in self.side:
             self.side[name] = (self.zeros_like(w), self.zeros_like(w, (w.shape[0],)))
         wb, alpha = self.side[name]

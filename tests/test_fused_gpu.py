@@ -182,6 +182,30 @@ def test_convolution_from_codes_equals_hinted_convolution(F, case):
     assert torch.equal(got_c, want_c)
 
 
+def test_prepared_weights_equal_per_call_binarisation(F):
+    rng = np.random.RandomState(21)
+    delta = 2.0 ** -4
+    for xs, ko, k, g, stride in (((2, 64, 14, 14), 64, 3, 1, 1), ((2, 48, 9, 9), 24, 3, 3, 2), ((1, 160, 8, 8), 200, 1, 1, 1)):
+        xq = oracle_ops.fixed_point_quantize(np.maximum(rng.randn(*xs), 0).astype(np.float32) * 2, True, 8, delta)
+        w = (rng.randn(ko, xs[1] // g, k, k) * 0.1).astype(np.float32)
+        w[0, 0, 0, 0] = 0.0
+        bias = (0.1 * rng.randn(ko)).astype(np.float32)
+        codes = F.fixed_point_codes_nhwc(dev(xq), delta, g)
+        pad, st = (k // 2, k // 2), (stride, stride)
+        wb = torch.zeros(*w.shape, device="cuda")
+        al = torch.zeros(ko, device="cuda")
+        want = F.binary_weight_convolution_from_codes(codes, xs, dev(w), wb, al, dev(bias), pad, st, (1, 1), g, 1.0, delta)
+        prep = F.prepare_binary_weights(dev(w), g, 1.0)
+        got = F.binary_convolution_from_codes_prepared(codes, xs, prep, dev(bias), pad, st, (1, 1), delta)
+        F.check_device_status()
+        assert torch.equal(got, want) and torch.equal(prep.binary_weight, wb) and torch.equal(prep.alpha, al)
+        # BinaryConnect: no alpha
+        wbc = torch.zeros(*w.shape, device="cuda")
+        want_c = F.binary_weight_convolution_from_codes(codes, xs, dev(w), wbc, None, None, pad, st, (1, 1), g, 1.0, delta)
+        prep_c = F.prepare_binary_weights(dev(w), g, 1.0, with_alpha=False)
+        assert torch.equal(F.binary_convolution_from_codes_prepared(codes, xs, prep_c, None, pad, st, (1, 1), delta), want_c)
+
+
 def test_codes_resnet_equals_unfused(F):
     from nnabla_b200 import resnet18
     rng = np.random.RandomState(0)
@@ -193,6 +217,9 @@ def test_codes_resnet_equals_unfused(F):
     codes = resnet18.Runner(F, gp, gz, fused="codes")(x)
     F.check_device_status()
     assert torch.equal(plain, codes)
+    net = resnet18.Runner(F, gp, gz, fused="codes", prepared_weights=True)
+    assert torch.equal(plain, net(x)) and torch.equal(plain, net(x))  # first call prepares, second reuses
+    F.check_device_status()
 
 
 def test_normalisation_with_extreme_statistics(F):
