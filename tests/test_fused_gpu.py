@@ -246,3 +246,22 @@ def test_normalisation_with_extreme_statistics(F):
         return np.array_equal(np.isnan(got), nan) and np.array_equal(bits(got)[~nan], bits(want)[~nan])
     assert same(F.bn_add_relu_fixed_point(dev(a), [dev(t) for t in pa], relu=False, quantize=False))
     assert same(F.batch_normalization(dev(a), *[dev(t) for t in pa], axes=[1], eps=1e-5, batch_stat=False))
+
+
+def test_forward_captured_as_cuda_graph(F):
+    """The library's calls are stream-ordered, so a whole forward can be recorded into a CUDA graph
+    and replayed: same logits, also for new inputs."""
+    from nnabla_b200 import graphs, resnet18
+    rng = np.random.RandomState(5)
+    params = resnet18.init_parameters(rng, num_classes=100)
+    gp = {k: dev(v) for k, v in params.items()}
+    gz = lambda w, shape=None: torch.zeros(shape or tuple(w.shape), device="cuda")
+    x = dev(rng.randn(2, 3, 64, 64).astype(np.float32))
+    net = resnet18.Runner(F, gp, gz, fused="codes", prepared_weights=True)
+    want = net(x).clone()
+    captured = graphs.Captured(net, x)
+    assert torch.equal(captured(x), want)
+    x2 = dev(rng.randn(2, 3, 64, 64).astype(np.float32))
+    assert torch.equal(captured(x2), net(x2))
+    assert torch.equal(captured(x), want)
+    F.check_device_status()
