@@ -415,10 +415,15 @@ def run_extras(args, rank, world, barrier):
     same = same and bool(torch.equal(net_prep(x), net(x)))
     # the same forward captured once as a CUDA graph and replayed (one launch instead of about 130 calls)
     from nnabla_b200 import graphs
-    captured = graphs.Captured(net_prep, x)
-    ms_graph = maxr(time_gpu(lambda: captured(x), 5, warm=2))
+    graph_note = "the int8-activations forward with prepared weights, captured once and replayed"
+    try:
+        captured = graphs.Captured(net_prep, x)
+        ms_graph = time_gpu(lambda: captured(x), 5, warm=2)
+        same = same and bool(torch.equal(captured(x), net(x)))
+    except RuntimeError as e:  # a capture that another thread's CUDA call interrupted: report, do not fail the run
+        ms_graph, graph_note = ms_prep, "capture failed (%s): eager time reported" % str(e)[:80]
+    ms_graph = maxr(ms_graph)
     F.check_device_status()
-    same = same and bool(torch.equal(captured(x), net(x)))
     out["configs[4] binary-weight ResNet-18 224x224"] = {
         "ms_per_batch": ms, "images_per_sec_whole_job": Bg * world / ms * 1e3, "batch_per_gpu": Bg,
         "gmac_per_image": resnet18.conv_macs_per_image() / 1e9,
@@ -433,7 +438,7 @@ def run_extras(args, rank, world, barrier):
         "images_per_sec_whole_job_int8_activations_prepared_weights": Bg * world / ms_prep * 1e3,
         "ms_per_batch_cuda_graph": ms_graph,
         "images_per_sec_whole_job_cuda_graph": Bg * world / ms_graph * 1e3,
-        "cuda_graph": "the int8-activations forward with prepared weights, captured once and replayed",
+        "cuda_graph": graph_note,
         "prepared_weights": "weights binarised once (inference: they do not change between calls) instead of in "
                             "every forward pass as the reference's forward_impl does",
         "int8_activations_logits_equal_unfused": same}
