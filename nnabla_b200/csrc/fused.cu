@@ -62,7 +62,9 @@ __device__ __forceinline__ float bn_value(float v, const ChannelConsts &k) {
 }
 
 // kSecond: 0 = one term, 1 = plain second operand, 2 = second operand with its own BN.
-template <bool kVec, int kSecond>
+// kFast: ReLU on, quantizer on, power-of-two delta: the value is non-negative and the quantizer is
+// (floor(v * 2 / delta) + 1) >> 1 capped at the largest code, times delta (same bits, fewer operations).
+template <bool kVec, int kSecond, bool kFast = false>
 __global__ void __launch_bounds__(kThreads) bn_add_relu_fxp_kernel(BnTerm A, BnTerm B, size_t total, int C, int S,
                                                                    float eps, int relu, int quantize, FxpParams P,
                                                                    int cached, float *__restrict__ y) {
@@ -82,7 +84,13 @@ __global__ void __launch_bounds__(kThreads) bn_add_relu_fxp_kernel(BnTerm A, BnT
     return cached ? consts[which * C + c] : load_consts(t, c, eps);
   };
   const size_t stride = (size_t)gridDim.x * kThreads;
+  const float two_inv = __fmul_rn(P.inv_delta, 2.0f), cap = __fmul_rn(__fmul_rn(P.maxv, P.inv_delta), 2.0f) + 0.5f;
   auto finish = [&](float v) {
+    if (kFast) {
+      v = fmaxf(v, 0.0f); // ReLU; a NaN becomes 0 as below
+      const int k = (__float2int_rd(fminf(__fmul_rn(v, two_inv), cap)) + 1) >> 1;
+      return __fmul_rn((float)k, P.delta);
+    }
     if (relu)
       v = v > 0.0f ? v : 0.0f;
     return quantize ? fxp_value(v, P) : v;
@@ -161,7 +169,12 @@ int launch(const BnTerm &A, const BnTerm &B, size_t total, int C, int S, float e
     const unsigned few = (unsigned)sm_count() * 16;
     grid = grid > few ? few : grid;
   }
-  if (vec)
+  // the largest code must be exact in fp32 arithmetic for the short form (codes below 2^22: twice the code plus one half is exact)
+  const bool fast = vec && relu && quantize && P.pow2 && P.maxv * P.inv_delta < 4194304.0f;
+  if (fast)
+    bn_add_relu_fxp_kernel<true, kSecond, true><<<grid, kThreads, cached ? smem : 0, st>>>(A, B, total, C, S, eps, relu,
+                                                                                            quantize, P, cached, y);
+  else if (vec)
     bn_add_relu_fxp_kernel<true, kSecond><<<grid, kThreads, cached ? smem : 0, st>>>(A, B, total, C, S, eps, relu,
                                                                                       quantize, P, cached, y);
   else
@@ -201,7 +214,10 @@ struct CodesLayout {
 
 // kSecond: 0 = one term, 1 = plain fp32 second operand, 2 = fp32 second operand with its own BN,
 // 3 = second operand given as codes (value = code * b_delta).
-template <bool kVec, int kSecond>
+// kFast: the common case of a residual network (ReLU on, power-of-two delta, every slot holds a
+// channel): the value is non-negative, so the code is (floor(v * 2 / delta) + 1) >> 1 capped at
+// kmax, six operations instead of the general quantizer's fourteen; same codes.
+template <bool kVec, int kSecond, bool kFast = false>
 __global__ void __launch_bounds__(256) bn_add_relu_fxp_codes_kernel(BnTerm A, BnTerm B,
                                                                     const int8_t *__restrict__ b_codes, float b_delta,
                                                                     CodesLayout L, float eps, int relu, FxpParams P,
@@ -299,15 +315,22 @@ __global__ void __launch_bounds__(256) bn_add_relu_fxp_codes_kernel(BnTerm A, Bn
     if (kSecond == 3)
       res = __ldcs(reinterpret_cast<const unsigned int *>(b_codes + o));
     uint32_t packed = 0;
+    const float two_inv = __fmul_rn(P.inv_delta, 2.0f), cap = (float)(2 * kmax) + 0.5f;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float v = tile[pp * kTilePitch + 4 * word + k];
       if (kSecond == 3)
         v = __fadd_rn(v, __fmul_rn((float)(int)(int8_t)((res >> (8 * k)) & 0xffu), b_delta));
-      if (relu)
-        v = v > 0.0f ? v : 0.0f;
-      const int code = live[k] ? fxp_code(v, P, kmax, kmin) : 0;
-      packed |= ((uint32_t)code & 0xffu) << (8 * k);
+      if (kFast) {
+        v = fmaxf(v, 0.0f); // ReLU; a NaN becomes 0 as in the general form
+        const int code = (__float2int_rd(fminf(__fmul_rn(v, two_inv), cap)) + 1) >> 1;
+        packed |= (uint32_t)code << (8 * k);
+      } else {
+        if (relu)
+          v = v > 0.0f ? v : 0.0f;
+        const int code = live[k] ? fxp_code(v, P, kmax, kmin) : 0;
+        packed |= ((uint32_t)code & 0xffu) << (8 * k);
+      }
     }
     *reinterpret_cast<uint32_t *>(out + o) = packed;
   }
@@ -476,6 +499,18 @@ extern "C" int nb200_bn_add_relu_fxp_codes_nhwc(const float *a, const float *bet
   const int second = b_codes ? 3 : (b == nullptr ? 0 : (mean_b == nullptr ? 1 : 2));
 #define NB_LAUNCH_CODES(V, S)                                                                                          \
   bn_add_relu_fxp_codes_kernel<V, S><<<grid, 256, 0, st>>>(A, B, b_codes, b_delta, L, eps, relu, P, kmax, kmin, y_codes)
+#define NB_LAUNCH_CODES_FAST(S)                                                                                        \
+  bn_add_relu_fxp_codes_kernel<true, S, true><<<grid, 256, 0, st>>>(A, B, b_codes, b_delta, L, eps, relu, P, kmax,     \
+                                                                    kmin, y_codes)
+  const bool fast = vec && relu && P.pow2 && group == 1 && L.slots == L.C && kmin <= 0;
+  if (fast) {
+    switch (second) {
+    case 0: NB_LAUNCH_CODES_FAST(0); break;
+    case 1: NB_LAUNCH_CODES_FAST(1); break;
+    case 2: NB_LAUNCH_CODES_FAST(2); break;
+    default: NB_LAUNCH_CODES_FAST(3); break;
+    }
+  } else
   switch (second * 2 + (vec ? 1 : 0)) {
   case 0: NB_LAUNCH_CODES(false, 0); break;
   case 1: NB_LAUNCH_CODES(true, 0); break;
@@ -487,6 +522,7 @@ extern "C" int nb200_bn_add_relu_fxp_codes_nhwc(const float *a, const float *bet
   default: NB_LAUNCH_CODES(true, 3); break;
   }
 #undef NB_LAUNCH_CODES
+#undef NB_LAUNCH_CODES_FAST
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }
