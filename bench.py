@@ -289,6 +289,15 @@ def run_extras(args, rank, world, barrier):
         "ms": ms, "tflops_algorithmic": 2 * M * K * N / ms / 1e9, "tflops_issued_bf16x3": 6 * M * K * N / ms / 1e9,
         "frac_of_bf16_peak_issued": 6 * M * K * N / ms / 1e9 / peaks["bf16_tflops"],
         "includes": "binarise + alpha + split + GEMM, whole forward_impl", "l2": "working set fits L2 (latency-bound case)"}
+    try:  # the same forward_impl recorded once as a CUDA graph: its five dependent launches replay as one
+        from nnabla_b200 import graphs
+        cap0 = graphs.Captured(lambda xx: F.binary_weight_affine(xx, w, wb, al, b), x)
+        out["configs[0] binary_weight_affine 256x1024x4096"]["ms_cuda_graph"] = maxr(
+            time_gpu(lambda: cap0.graph.replay(), 50))
+        del cap0
+    except RuntimeError as e:
+        out["configs[0] binary_weight_affine 256x1024x4096"]["ms_cuda_graph"] = None
+        out["configs[0] binary_weight_affine 256x1024x4096"]["cuda_graph_note"] = str(e)[:80]
     # configs[2]: 8-bit fixed-point affine, output columns sharded over the ranks
     M, K, N = (4096, 4096, 4096) if args.small_extras else (8192, 4096, 8192)
     Ns = N // world
