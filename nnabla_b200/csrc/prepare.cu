@@ -66,6 +66,70 @@ __global__ void __launch_bounds__(256) binarize_columns_kernel(const float *__re
   }
 }
 
+// The same with 128-bit accesses (C a multiple of 4, 16-byte aligned W / Wb, side-band rows
+// aligned to 8 bytes): a thread handles four columns of a row, and four rows of a side-band row.
+template <bool kInt8>
+__global__ void __launch_bounds__(256) binarize_columns_vec_kernel(const float *__restrict__ w, int R, int C,
+                                                                   float zero_to, float *__restrict__ wb,
+                                                                   void *__restrict__ side, int64_t side_pitch,
+                                                                   float *__restrict__ partial) {
+  __shared__ float s_sign[kBT][kBT + 1];
+  __shared__ float s_sum[16][kBT];
+  const int c0 = blockIdx.x * kBT, r0 = blockIdx.y * kBT;
+  const int tx4 = threadIdx.x & 15, ty = threadIdx.x >> 4; // 16 column quads x 16 rows
+  const int c = c0 + 4 * tx4;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int rr = ty + 16 * it, r = r0 + rr;
+    float4 sg = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < R && c < C) { // C % 4 == 0: the quad is inside or outside as a whole
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(w + (int64_t)r * C + c));
+      sg = make_float4(sign_of(v.x, zero_to), sign_of(v.y, zero_to), sign_of(v.z, zero_to), sign_of(v.w, zero_to));
+      *reinterpret_cast<float4 *>(wb + (int64_t)r * C + c) = sg;
+      acc[0] += fabsf(v.x), acc[1] += fabsf(v.y), acc[2] += fabsf(v.z), acc[3] += fabsf(v.w);
+    }
+    s_sign[rr][4 * tx4 + 0] = sg.x;
+    s_sign[rr][4 * tx4 + 1] = sg.y;
+    s_sign[rr][4 * tx4 + 2] = sg.z;
+    s_sign[rr][4 * tx4 + 3] = sg.w;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    s_sum[ty][4 * tx4 + i] = acc[i];
+  __syncthreads();
+  if (partial != nullptr && threadIdx.x < kBT && c0 + threadIdx.x < C) {
+    float t = 0.0f; // fixed order: deterministic
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+      t += s_sum[k][threadIdx.x];
+    partial[(int64_t)blockIdx.y * C + c0 + threadIdx.x] = t;
+  }
+  // side-band: row = output column, contiguous index = input row; four input rows per thread
+  const int r = r0 + 4 * tx4;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int cc = ty + 16 * it, oc = c0 + cc;
+    if (oc >= C || r >= R)
+      continue;
+    float sv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      sv[i] = (r + i < R) ? s_sign[4 * tx4 + i][cc] : 0.0f;
+    if (kInt8) {
+      const uint32_t packed = ((uint32_t)(uint8_t)(int8_t)(int)sv[0]) | ((uint32_t)(uint8_t)(int8_t)(int)sv[1] << 8) |
+                              ((uint32_t)(uint8_t)(int8_t)(int)sv[2] << 16) | ((uint32_t)(uint8_t)(int8_t)(int)sv[3] << 24);
+      *reinterpret_cast<uint32_t *>(reinterpret_cast<int8_t *>(side) + (int64_t)oc * side_pitch + r) = packed;
+    } else {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(sv[0], sv[1]), hi = __floats2bfloat162_rn(sv[2], sv[3]);
+      uint2 out;
+      out.x = *reinterpret_cast<const uint32_t *>(&lo);
+      out.y = *reinterpret_cast<const uint32_t *>(&hi);
+      *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(side) + (int64_t)oc * side_pitch + r) = out;
+    }
+  }
+}
+
 __global__ void finalize_alpha_kernel(const float *__restrict__ partial, int blocks, int C, float inv,
                                       float *__restrict__ alpha) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -376,7 +440,15 @@ int binarize_columns(const float *w, int R, int C, float zero_to, float *wb, flo
                      int64_t side_pitch, bool int8, float *partial_scratch, cudaStream_t st) {
   const dim3 grid((C + kBT - 1) / kBT, (R + kBT - 1) / kBT);
   float *partial = alpha ? partial_scratch : nullptr;
-  if (int8)
+  // the side-band rows hold K padded to a multiple of 64 values: four rows past R stay inside a row
+  const bool vec = C % 4 == 0 && side_pitch % 4 == 0 && side_pitch >= (int64_t)(R + 3) / 4 * 4 &&
+                   ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(wb)) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(side) & 7) == 0;
+  if (vec && int8)
+    binarize_columns_vec_kernel<true><<<grid, 256, 0, st>>>(w, R, C, zero_to, wb, side, side_pitch, partial);
+  else if (vec)
+    binarize_columns_vec_kernel<false><<<grid, 256, 0, st>>>(w, R, C, zero_to, wb, side, side_pitch, partial);
+  else if (int8)
     binarize_columns_kernel<true><<<grid, 256, 0, st>>>(w, R, C, zero_to, wb, side, side_pitch, partial);
   else
     binarize_columns_kernel<false><<<grid, 256, 0, st>>>(w, R, C, zero_to, wb, side, side_pitch, partial);
