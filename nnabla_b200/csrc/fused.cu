@@ -373,34 +373,32 @@ struct PoolGeom {
 };
 
 __global__ void __launch_bounds__(256) max_pooling_codes_kernel(const int8_t *__restrict__ in, int slots, PoolGeom G,
-                                                                size_t total, int8_t *__restrict__ out) {
+                                                                int8_t *__restrict__ out) {
+  // grid = (chunks of an output row, output rows, samples): no wide divisions per item
   const int vecs = slots / 16; // 16-slot groups per pixel
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const unsigned v = (unsigned)(i % (unsigned)vecs);
-    const size_t pix = i / (unsigned)vecs;
-    const unsigned ox = (unsigned)(pix % (unsigned)G.Wo);
-    const size_t t = pix / (unsigned)G.Wo;
-    const unsigned oy = (unsigned)(t % (unsigned)G.Ho);
-    const size_t n = t / (unsigned)G.Ho;
-    // window clipped to the input (max_pooling.cpp:140-191): padding never takes part
-    int y0 = (int)oy * G.sh - G.ph, x0 = (int)ox * G.sw - G.pw;
-    int y1 = min(min(y0 + G.kh, G.H + G.ph), G.H), x1 = min(min(x0 + G.kw, G.W + G.pw), G.W);
-    y0 = max(y0, 0);
-    x0 = max(x0, 0);
-    uint4 best = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
-    for (int iy = y0; iy < y1; ++iy) {
-      const uint4 *row = reinterpret_cast<const uint4 *>(in + ((n * G.H + iy) * (size_t)G.W) * slots) + v;
-      for (int ix = x0; ix < x1; ++ix) {
-        const uint4 q = __ldg(row + (size_t)ix * vecs);
-        best.x = __vmaxs4(best.x, q.x);
-        best.y = __vmaxs4(best.y, q.y);
-        best.z = __vmaxs4(best.z, q.z);
-        best.w = __vmaxs4(best.w, q.w);
-      }
+  const int item = blockIdx.x * 256 + threadIdx.x;
+  if (item >= G.Wo * vecs)
+    return;
+  const int ox = item / vecs, v = item - ox * vecs;
+  const int oy = blockIdx.y;
+  const size_t n = blockIdx.z;
+  // window clipped to the input (max_pooling.cpp:140-191): padding never takes part
+  int y0 = oy * G.sh - G.ph, x0 = ox * G.sw - G.pw;
+  const int y1 = min(min(y0 + G.kh, G.H + G.ph), G.H), x1 = min(min(x0 + G.kw, G.W + G.pw), G.W);
+  y0 = max(y0, 0);
+  x0 = max(x0, 0);
+  uint4 best = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+  for (int iy = y0; iy < y1; ++iy) {
+    const uint4 *row = reinterpret_cast<const uint4 *>(in + ((n * G.H + iy) * (size_t)G.W) * slots) + v;
+    for (int ix = x0; ix < x1; ++ix) {
+      const uint4 q = __ldg(row + (size_t)ix * vecs);
+      best.x = __vmaxs4(best.x, q.x);
+      best.y = __vmaxs4(best.y, q.y);
+      best.z = __vmaxs4(best.z, q.z);
+      best.w = __vmaxs4(best.w, q.w);
     }
-    reinterpret_cast<uint4 *>(out)[i] = best;
   }
+  reinterpret_cast<uint4 *>(out)[((n * G.Ho + oy) * (size_t)G.Wo + ox) * vecs + v] = best;
 }
 
 int fill_fxp(FxpParams &P, int sign, int n, float delta) {
@@ -564,11 +562,9 @@ extern "C" int nb200_max_pooling_codes_nhwc(const int8_t *codes, int8_t *y_codes
   NB_CHECK(((reinterpret_cast<uintptr_t>(codes) | reinterpret_cast<uintptr_t>(y_codes)) & 15) == 0, NB200_EVALUE,
            "code tensors must be 16-byte aligned");
   const int slots = (int)codes_slots(channels, group);
-  const size_t total = (size_t)batch * G.Ho * G.Wo * (slots / 16);
-  size_t blocks = (total + 255) / 256;
-  const size_t cap = (size_t)sm_count() * 64;
-  blocks = blocks > cap ? cap : blocks;
-  max_pooling_codes_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(codes, slots, G, total, y_codes);
+  NB_CHECK(batch <= 65535 && G.Ho <= 65535, NB200_ENOTIMPL, "more than 65535 samples or output rows");
+  const dim3 grid((unsigned)((G.Wo * (slots / 16) + 255) / 256), (unsigned)G.Ho, (unsigned)batch);
+  max_pooling_codes_kernel<<<grid, 256, 0, as_stream(stream)>>>(codes, slots, G, y_codes);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }
