@@ -31,6 +31,7 @@
 // shifted by the filter tap).
 #pragma once
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -470,6 +471,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const bool col_ok = prob.col_offset(t, c0 + lane, coff, gcol);
           const float cb = (ep.col_bias && col_ok) ? ep.col_bias[gcol] : 0.0f;
           const int64_t tile_off = coff + prob.row_offset(row_base) + t.y_off;
+          if constexpr (kInt8 && std::is_same<Problem, ConvProblem>::value) {
+            // Convolution tiles whose columns are consecutive pixels of y (whole rows of one
+            // image): 128-bit stores, four rows of eight column quads per instruction, instead of
+            // one 32-column row per instruction.
+            if (prob.n_box == 1 && ep.n_peers == 0 && !ep.accumulate && !ep.col_scale && !ep.col_bias) {
+              const int rows_left = prob.Ho - t.oy0;
+              const int nvalid = (rows_left < prob.h_box ? rows_left : prob.h_box) * prob.Wo - c0;
+              const int nv = nvalid < 0 ? 0 : (nvalid > 32 ? 32 : nvalid);
+              const int64_t plane = (int64_t)prob.Ho * prob.Wo;
+              const int64_t off0 = (int64_t)t.img0 * prob.Ko * plane + (int64_t)t.oy0 * prob.Wo + c0 +
+                                   prob.row_offset(row_base) + t.y_off;
+              if ((nv & 3) == 0 && (plane & 3) == 0 && (off0 & 3) == 0 &&
+                  (reinterpret_cast<uintptr_t>(ep.y) & 15) == 0) {
+                const int q4 = 4 * (lane & 7), rr = lane >> 3;
+                float *yq = ep.y + off0 + q4;
+#pragma unroll 4
+                for (int i0 = 0; i0 < rows_here; i0 += 4) {
+                  const int i = i0 + rr;
+                  if (i < rows_here && q4 < nv) {
+                    const float *sp = stg + i * 33 + q4;
+                    *reinterpret_cast<float4 *>(yq + (int64_t)i * plane) = make_float4(sp[0], sp[1], sp[2], sp[3]);
+                  }
+                }
+                __syncwarp();
+                continue;
+              }
+            }
+          }
           // destination 0 is this GPU's y, the others are the peer copies
 #pragma unroll 1
           for (int d = 0; d <= ep.n_peers; ++d) {
