@@ -9,8 +9,8 @@
 // through the registry (binary_weight_affine.cpp:35,65-70;
 // min_max_quantize.cpp:97-119; batch_normalization.cpp:119-131), which would
 // look up "b200:float" for each of them and throw, so only the shape checks and
-// the output reshape are repeated here. backward_impl raises not_implemented:
-// this backend is the forward (inference) path.
+// the output reshape are repeated here. backward_impl is implemented for the
+// quantizers, their siblings, the affine family and the binary convolutions.
 #include <nbla_b200/b200.hpp>
 
 #include <nbla/array/cpu_array.hpp>

@@ -90,6 +90,12 @@ int nb200_stream_destroy(void *stream);
 /* BackendBase::device_synchronize (include/nbla/backend_base.hpp:32-91). */
 int nb200_stream_synchronize(void *stream);
 int nb200_device_synchronize(void);
+/* Bytes of the current device's stream-ordered scratch pool (the pool every
+ * entry point's temporary side-band tensors come from) in use now, and the
+ * high-water mark since it was last reset (reset_high != 0 resets it first).
+ * Either pointer may be NULL. The counterpart of the caching allocator's
+ * usage queries (include/nbla/memory/allocator.hpp:209-251). */
+int nb200_scratch_pool_stats(int64_t *used_now, int64_t *used_high, int reset_high);
 
 /* ---- elementwise quantizers ------------------------------------------------ */
 
@@ -138,13 +144,16 @@ int nb200_min_max_quantize_f32(const float *x, const int64_t *x_shape, int ndim,
  * the pool has taken the whole device), and serving loops that cannot afford
  * the locks and device synchronisation an allocation call may bring. This
  * entry point never calls cudaMalloc, cudaMallocAsync, cudaFree or any other
- * allocating routine: its scratch (5 floats per quantization range) is a
- * fixed 80 KiB array inside the library image, so every GPU that loads the
+ * allocating routine: its scratch (28 bytes per quantization range) is a
+ * fixed 112 KiB array inside the library image, so every GPU that loads the
  * library holds that array until the process exits.
  *  - Limit: at most 4096 quantization ranges (elements of qr_min) per call;
  *    more is refused with NB200_EVALUE.
  *  - The first call on each device looks up the array's device address (the
  *    device must be current); make that first call before any stream capture.
+ *    The address is kept for the life of the process: a host that tears the
+ *    device's primary context down (cudaDeviceReset) and goes on must not
+ *    call this entry point again afterwards.
  *  - All calls on a device share the one array. Calls that may overlap on the
  *    GPU (different streams, no ordering between them) race on it; serialise
  *    them or use nb200_min_max_quantize_f32. */

@@ -125,7 +125,7 @@ constexpr int kPairEpilogueBytes = kPairEpilogueWarps * 4096; // one swizzled 32
 struct PairGemmProblem {
   int M, N, kblocks, m_tiles, n_tiles;
   int64_t ldy;
-  int debug; // timing experiments only (NNABLA_B200_GEMM_DEBUG): 1 = no global stores, 2 = no operand loads after the first ring fill
+  int debug; // timing-knob builds only (-DNB200_GEMM_TIMING_KNOBS): 1 = no global stores, 2 = no operand loads after the first ring fill; always 0 otherwise
 };
 
 template <bool kInt8, int PA, int STAGES>
@@ -205,7 +205,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
           }
           uint8_t *st = smem + stage * kStageBytes;
           const uint32_t leader_full = ptx::map_to_cta(ptx::smem_u32(full_bar + stage), 0);
-          if ((prob.debug & 2) && (tile != pair_id || kb >= STAGES)) {
+          if (kTimingKnobs && (prob.debug & 2) && (tile != pair_id || kb >= STAGES)) {
             if (rank == 0)
               ptx::mbar_arrive(full_bar + stage);
           } else {
@@ -320,7 +320,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kPairTileN + c0), r);
         ptx::tmem_ld_wait();
         const int col0 = n0 + c0;
-        if (col0 >= prob.N || (prob.debug & 1))
+        if (col0 >= prob.N || (kTimingKnobs && (prob.debug & 1)))
           continue;
         const bool lane_col_ok = col0 + lane < prob.N;
         const float cs_l = (ep.col_scale && lane_col_ok) ? ep.col_scale[col0 + lane] : 1.0f;
@@ -351,7 +351,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         }
         ptx::fence_async_shared();
         __syncwarp();
-        if (lane == 0 && !(prob.debug & 4)) {
+        if (lane == 0 && !(kTimingKnobs && (prob.debug & 4))) {
           ptx::tma_store_2d(&map_y, box, col0, m0 + quarter * 32, stream_out);
           ptx::tma_store_commit();
         }
@@ -414,10 +414,13 @@ inline int launch_pair_gemm(const CUtensorMap &ma, const CUtensorMap &mb, int M,
   prob.m_tiles = (M + kPairTileM - 1) / kPairTileM;
   prob.n_tiles = (N + kPairTileN - 1) / kPairTileN;
   prob.ldy = ldy;
+  prob.debug = 0;
+#ifdef NB200_GEMM_TIMING_KNOBS
   {
     const char *e = std::getenv("NNABLA_B200_GEMM_DEBUG");
     prob.debug = e ? std::atoi(e) : 0;
   }
+#endif
   int *status = nullptr;
   NB_TRY(device_status_word(&status));
   const int tiles = prob.m_tiles * prob.n_tiles;

@@ -552,69 +552,93 @@ int pow2_launch(const float *x, float *y, size_t size, int sign, int with_zero, 
 // apply pass. The q tensors broadcast over x; the supported (and fast) case
 // is a q shape whose non-1 extents form one contiguous run of axes, so that
 // x is viewed as [outer, Q, inner] and the q index of flat element i is
-// (i / inner) % Q. Scratch per call: 5*Q floats (min, max, m, M, scale).
+// (i / inner) % Q. Scratch per call: 7*Q words (min and max keys, m, M, scale).
 // ---------------------------------------------------------------------------
 struct MinMaxView {
   size_t outer, Q, inner, size;
 };
+constexpr size_t kMinMaxScratchWords = 7; // per range: two 64-bit keys (min, max), m, M, scale
 
-// Order-preserving float min/max through integer atomics (no NaN handling:
-// the reference's Min/Max on NaN input is order-dependent).
-__device__ __forceinline__ void atomic_min_f32(float *addr, float v) {
-  if (v >= 0.0f)
-    atomicMin(reinterpret_cast<int *>(addr), __float_as_int(v));
-  else
-    atomicMax(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
+// Min / Max of the reference (src/nbla/function/generic/max.cpp:44-61, min.cpp): a serial scan that
+// starts from -1e8 (Max) / +1e8 (Min) and replaces the running value only on a strict comparison,
+// so among equal values the FIRST one in scan order wins. That matters for zeros: -0.0 == +0.0
+// compares equal, the first one's sign ends up in qr_min / qr_max (which are written back), and a
+// NaN never wins. Each candidate is packed into a 64-bit key whose unsigned order is that rule:
+//   high word: the value as an order-preserving integer, both zeros mapped to the same code
+//              (complemented for Min, so that one atomicMax serves both);
+//   low word:  (2^31 - 1 - t) << 1 | sign bit, t = position in the reference's scan order: for
+//              equal values the earlier one has the larger key, and the zero's sign survives.
+// The starting value has the largest low word: an element equal to it never replaces it.
+__device__ __forceinline__ uint32_t ordered_bits(float v) {
+  const uint32_t u = (v == 0.0f) ? 0u : __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
-__device__ __forceinline__ void atomic_max_f32(float *addr, float v) {
-  if (v >= 0.0f)
-    atomicMax(reinterpret_cast<int *>(addr), __float_as_int(v));
-  else
-    atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
+__device__ __forceinline__ unsigned long long extremum_key(float v, uint32_t t, bool is_min) {
+  const uint32_t hi = is_min ? ~ordered_bits(v) : ordered_bits(v);
+  const uint32_t lo = ((0x7fffffffu - t) << 1) | (__float_as_uint(v) >> 31);
+  return ((unsigned long long)hi << 32) | lo;
+}
+__device__ __forceinline__ unsigned long long extremum_start(bool is_min) {
+  const float v = is_min ? 1e8f : -1e8f;
+  const uint32_t hi = is_min ? ~ordered_bits(v) : ordered_bits(v);
+  return ((unsigned long long)hi << 32) | 0xfffffffeu | (__float_as_uint(v) >> 31);
+}
+__device__ __forceinline__ float extremum_value(unsigned long long key, bool is_min) {
+  uint32_t o = (uint32_t)(key >> 32);
+  if (is_min)
+    o = ~o;
+  const uint32_t u = (o & 0x80000000u) ? (o & 0x7fffffffu) : ~o;
+  return __uint_as_float(u == 0u ? ((uint32_t)key & 1u) << 31 : u);
 }
 
-__global__ void minmax_init_kernel(float *mn, float *mx, size_t Q) {
+__global__ void minmax_init_kernel(unsigned long long *mn, unsigned long long *mx, size_t Q) {
   const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   if (i < Q) {
-    mn[i] = __int_as_float(0x7f800000);  // +inf
-    mx[i] = __int_as_float(0xff800000);  // -inf
+    mn[i] = extremum_start(true);
+    mx[i] = extremum_start(false);
   }
 }
 
 // grid = (splits, Q). Block (s, q) reduces its share of the outer*inner
-// elements that belong to q, then one atomic pair per block.
+// elements that belong to q, then one atomic pair per block. t = o * inner + j
+// is the element's position in the reference's scan over the reduced axes.
 __global__ void __launch_bounds__(kThreads) minmax_reduce_kernel(const float *__restrict__ x, MinMaxView V,
-                                                                 float *mn, float *mx) {
+                                                                 unsigned long long *mn, unsigned long long *mx) {
   const size_t q = blockIdx.y;
   const size_t per_q = V.outer * V.inner;
-  float lo = __int_as_float(0x7f800000), hi = __int_as_float(0xff800000);
+  float lo = 1e8f, hi = -1e8f;
+  uint32_t t_lo = 0xffffffffu, t_hi = 0xffffffffu; // position of the thread's extremum; none yet
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t t = (size_t)blockIdx.x * kThreads + threadIdx.x; t < per_q; t += stride) {
     const size_t o = t / V.inner, j = t - o * V.inner;
     const float v = x[(o * V.Q + q) * V.inner + j];
-    lo = v < lo ? v : lo;
-    hi = v > hi ? v : hi;
+    if (v < lo)
+      lo = v, t_lo = (uint32_t)t;
+    if (v > hi)
+      hi = v, t_hi = (uint32_t)t;
   }
+  unsigned long long klo = t_lo == 0xffffffffu ? extremum_start(true) : extremum_key(lo, t_lo, true);
+  unsigned long long khi = t_hi == 0xffffffffu ? extremum_start(false) : extremum_key(hi, t_hi, false);
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) {
-    const float lo2 = __shfl_xor_sync(0xffffffffu, lo, d), hi2 = __shfl_xor_sync(0xffffffffu, hi, d);
-    lo = lo2 < lo ? lo2 : lo;
-    hi = hi2 > hi ? hi2 : hi;
+    const unsigned long long lo2 = __shfl_xor_sync(0xffffffffu, klo, d), hi2 = __shfl_xor_sync(0xffffffffu, khi, d);
+    klo = lo2 > klo ? lo2 : klo;
+    khi = hi2 > khi ? hi2 : khi;
   }
-  __shared__ float s_lo[kThreads / 32], s_hi[kThreads / 32];
+  __shared__ unsigned long long s_lo[kThreads / 32], s_hi[kThreads / 32];
   if ((threadIdx.x & 31) == 0) {
-    s_lo[threadIdx.x >> 5] = lo;
-    s_hi[threadIdx.x >> 5] = hi;
+    s_lo[threadIdx.x >> 5] = klo;
+    s_hi[threadIdx.x >> 5] = khi;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int w = 1; w < kThreads / 32; ++w) {
-      lo = s_lo[w] < lo ? s_lo[w] : lo;
-      hi = s_hi[w] > hi ? s_hi[w] : hi;
+      klo = s_lo[w] > klo ? s_lo[w] : klo;
+      khi = s_hi[w] > khi ? s_hi[w] : khi;
     }
     if (per_q > 0) {
-      atomic_min_f32(mn + q, lo);
-      atomic_max_f32(mx + q, hi);
+      atomicMax(mn + q, klo);
+      atomicMax(mx + q, khi);
     }
   }
 }
@@ -623,7 +647,8 @@ __global__ void __launch_bounds__(kThreads) minmax_reduce_kernel(const float *__
 // (:352-361), the scale (:184-186) and nudge_qr_min_max (:362-390), with every
 // fp32 operation rounded on its own.
 __global__ void minmax_params_kernel(size_t Q, float *qr_min, float *qr_max, const float *ql_min, const float *ql_max,
-                                     const float *mn, const float *mx, int x_min_max, int ema, float decay_f,
+                                     const unsigned long long *mn_key, const unsigned long long *mx_key,
+                                     int x_min_max, int ema, float decay_f,
                                      float one_minus_decay_f, float eps, float *m_out, float *M_out, float *s_out,
                                      float *scale_user) {
   const size_t q = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
@@ -631,12 +656,13 @@ __global__ void minmax_params_kernel(size_t Q, float *qr_min, float *qr_max, con
     return;
   float rmin = qr_min[q], rmax = qr_max[q];
   if (x_min_max) {
+    const float mn = extremum_value(mn_key[q], true), mx = extremum_value(mx_key[q], false);
     if (ema) {
-      rmin = __fadd_rn(__fmul_rn(rmin, decay_f), __fmul_rn(mn[q], one_minus_decay_f));
-      rmax = __fadd_rn(__fmul_rn(rmax, decay_f), __fmul_rn(mx[q], one_minus_decay_f));
+      rmin = __fadd_rn(__fmul_rn(rmin, decay_f), __fmul_rn(mn, one_minus_decay_f));
+      rmax = __fadd_rn(__fmul_rn(rmax, decay_f), __fmul_rn(mx, one_minus_decay_f));
     } else {
-      rmin = mn[q];
-      rmax = mx[q];
+      rmin = mn;
+      rmax = mx;
     }
     qr_min[q] = rmin;
   }
@@ -739,11 +765,13 @@ int minmax_view(const int64_t *xs, const int64_t *qs, int ndim, MinMaxView *V) {
   return NB200_OK;
 }
 
-// Runs the three steps on device buffers. `scratch` holds 5*Q floats.
+// Runs the three steps on device buffers. `scratch` (8-byte aligned) holds kMinMaxScratchWords
+// 32-bit words per range: two 64-bit extremum keys, then m, M and the scale.
 int minmax_run(const float *x, const MinMaxView &V, float *qr_min, float *qr_max, const float *ql_min,
                const float *ql_max, float decay, int x_min_max, int ema, float eps, float *y, float *scale,
                float *scratch, cudaStream_t st) {
-  float *mn = scratch, *mx = scratch + V.Q, *m = scratch + 2 * V.Q, *M = scratch + 3 * V.Q, *s = scratch + 4 * V.Q;
+  unsigned long long *mn = reinterpret_cast<unsigned long long *>(scratch), *mx = mn + V.Q;
+  float *m = scratch + 4 * V.Q, *M = scratch + 5 * V.Q, *s = scratch + 6 * V.Q;
   const unsigned qblocks = (unsigned)((V.Q + 255) / 256);
   if (x_min_max) {
     NB_CHECK(V.size > 0, NB200_EVALUE, "min/max of an empty tensor");
@@ -751,6 +779,8 @@ int minmax_run(const float *x, const MinMaxView &V, float *qr_min, float *qr_max
     NB_LAUNCH_CHECK();
     NB_CHECK(V.Q <= 65535, NB200_ENOTIMPL, "more than 65535 quantization ranges");
     const size_t per_q = V.outer * V.inner;
+    // the reference scans with an int index (max.cpp:51); positions are kept in 31 bits here
+    NB_CHECK(per_q < (1ull << 31), NB200_ENOTIMPL, "min/max over 2^31 or more elements per range");
     size_t splits = (per_q + (size_t)kThreads * 16 - 1) / ((size_t)kThreads * 16);
     const size_t cap = ((size_t)sm_count() * kBlocksPerSm + V.Q - 1) / V.Q;
     if (splits > cap)
@@ -770,7 +800,7 @@ int minmax_run(const float *x, const MinMaxView &V, float *qr_min, float *qr_max
 }
 
 // ---------------------------------------------------------------------------
-// Allocation-free variant of MinMaxQuantize: the 5*Q floats of scratch live in
+// Allocation-free variant of MinMaxQuantize: the 7*Q words of scratch live in
 // a fixed array in device global memory that belongs to the library image
 // (every GPU that loads the library carries it until the process exits).
 // Host code must not pass the array's name to a kernel: on the host that name
@@ -779,7 +809,7 @@ int minmax_run(const float *x, const MinMaxView &V, float *qr_min, float *qr_max
 // that address.
 // ---------------------------------------------------------------------------
 constexpr size_t kNoAllocMaxRanges = 4096; // quantization ranges (elements of qr_min) per call
-static __device__ __align__(256) float g_minmax_static_scratch[5 * kNoAllocMaxRanges];
+static __device__ __align__(256) float g_minmax_static_scratch[kMinMaxScratchWords * kNoAllocMaxRanges];
 
 std::mutex g_static_scratch_mutex;
 float *g_static_scratch_addr[64];
@@ -874,7 +904,7 @@ int nb200_min_max_quantize_f32(const float *x, const int64_t *x_shape, int ndim,
   NB_CHECK(V.size == 0 || (x && y), NB200_EVALUE, "null data pointer");
   cudaStream_t st = as_stream(stream);
   AsyncScratch scratch(st);
-  NB_TRY(scratch.alloc(5 * V.Q * sizeof(float)));
+  NB_TRY(scratch.alloc(kMinMaxScratchWords * V.Q * sizeof(float)));
   return minmax_run(x, V, qr_min, qr_max, ql_min, ql_max, decay, x_min_max, ema, eps, y, scale,
                     static_cast<float *>(scratch.p), st);
 }

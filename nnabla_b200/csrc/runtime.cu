@@ -280,6 +280,26 @@ int nb200_stream_synchronize(void *stream) {
   return NB200_OK;
 }
 
+int nb200_scratch_pool_stats(int64_t *used_now, int64_t *used_high, int reset_high) {
+  int dev = 0;
+  NB_CUDA(cudaGetDevice(&dev));
+  cudaMemPool_t pool;
+  NB_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+  uint64_t v = 0;
+  if (reset_high) {
+    NB_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrUsedMemHigh, &v)); // the watermark can only be set to 0
+  }
+  if (used_now) {
+    NB_CUDA(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemCurrent, &v));
+    *used_now = (int64_t)v;
+  }
+  if (used_high) {
+    NB_CUDA(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemHigh, &v));
+    *used_high = (int64_t)v;
+  }
+  return NB200_OK;
+}
+
 int nb200_device_synchronize(void) {
   NB_CUDA(cudaDeviceSynchronize());
   return NB200_OK;

@@ -1,4 +1,4 @@
-"""Binary-weight ResNet-18 (BASELINE.json configs[4]) written against the F / PF mirrors.
+"""Binary-weight ResNet-18 on 224 x 224 inputs with 1000 classes, written against the F / PF mirrors.
 
 The reference ships no in-tree definition (python/src/nnabla/models/imagenet/resnet.py:59-60
 only loads a downloaded archive); this is the standard 18-layer basic-block
@@ -23,7 +23,7 @@ STAGES = [(64, 1), (128, 2), (256, 2), (512, 2)]
 
 def init_parameters(rng, num_classes=1000, in_channels=3):
     """Random initialisation (numpy, seeded): Kaiming-normal convolution weights,
-    random BN running statistics with var > 0, as BASELINE.json configs[4] states."""
+    random BN running statistics with var > 0."""
     p = {}
 
     def conv(name, o, i, k):

@@ -163,23 +163,24 @@ int oracle_min_max_quantize(const float *x, const int64_t *xs, int nd,
     /* Min / Max over the axes where the q shape is 1 (:97-98, :159-178). */
     mn = (float *)malloc(sizeof(float) * (size_t)qsize);
     mx = (float *)malloc(sizeof(float) * (size_t)qsize);
-    char *seen = (char *)calloc((size_t)qsize, 1);
-    if (!mn || !mx || !seen)
+    if (!mn || !mx)
       return -1;
+    /* Min / Max scan from +1e8 / -1e8 and replace on a strict comparison
+     * (src/nbla/function/generic/max.cpp:49-57, min.cpp): the first of equal
+     * values stays (this decides the sign of a zero extremum), a NaN never
+     * wins, and values beyond 1e8 in magnitude on the wrong side are ignored. */
+    for (int64_t q = 0; q < qsize; ++q) {
+      mn[q] = 1e+8;
+      mx[q] = -1e+8;
+    }
     for (int64_t i = 0; i < xsize; ++i) {
       int64_t q;
       QIDX(i, q);
-      if (!seen[q]) {
-        seen[q] = 1;
-        mn[q] = mx[q] = x[i];
-      } else {
-        if (x[i] < mn[q])
-          mn[q] = x[i];
-        if (x[i] > mx[q])
-          mx[q] = x[i];
-      }
+      if (x[i] < mn[q])
+        mn[q] = x[i];
+      if (x[i] > mx[q])
+        mx[q] = x[i];
     }
-    free(seen);
     float d1 = (float)decay, d2 = (float)(1.0 - decay); /* :105-106 */
     for (int64_t q = 0; q < qsize; ++q) {
       if (ema) {

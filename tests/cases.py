@@ -90,6 +90,38 @@ def fxp_input(shape=(2, 3, 4, 33)):
     return (rng.randn(*shape) * 2).astype(np.float32)
 
 
+def minmax_zero_sign_cases():
+    """Inputs whose min or max is a zero, or lies outside the +-1e8 start values of the
+    reference's Min / Max scans (src/nbla/function/generic/max.cpp:49-57): (name, x, q_shape).
+    The sign of a zero extremum is that of the FIRST zero in scan order, and it is written
+    back into qr_min / qr_max. Sizes span one block and several blocks of the device reduction."""
+    f32 = np.float32
+    rng = np.random.RandomState(SEED + 1)
+    out = []
+    for n in (64, 70000):
+        neg = -np.abs(rng.randn(n)).astype(f32) - f32(0.25)
+        pos = np.abs(rng.randn(n)).astype(f32) + f32(0.25)
+        a = neg.copy(); a[n // 3] = f32(-0.0)                     # max is -0.0 alone
+        b = neg.copy(); b[n // 3] = f32(-0.0); b[n // 3 + 7] = f32(0.0)   # -0.0 first, then +0.0
+        c = neg.copy(); c[n // 3] = f32(0.0); c[n - 2] = f32(-0.0)        # +0.0 first
+        d = pos.copy(); d[n // 2] = f32(-0.0)                     # min is -0.0 alone
+        e = pos.copy(); e[5] = f32(0.0); e[n - 1] = f32(-0.0)     # min: +0.0 first
+        g = pos.copy(); g[n - 1] = f32(0.0); g[3] = f32(-0.0)     # min: -0.0 first
+        h = np.concatenate([pos[: n // 2], neg[: n // 2]]); h[1] = f32(-0.0)  # zero inside the range
+        for name, x in (("max-0", a), ("max-0+0", b), ("max+0-0", c), ("min-0", d), ("min+0-0", e), ("min-0+0", g),
+                        ("mixed", h)):
+            out.append(("%s/%d" % (name, n), x.reshape(1, -1), (1, 1)))
+    # per-channel ranges: channel 0 all non-positive with -0.0, channel 1 all non-negative with -0.0 late
+    x = rng.randn(3, 4, 50).astype(f32)
+    x[:, 0] = -np.abs(x[:, 0]) - f32(0.5); x[2, 0, 7] = f32(-0.0)
+    x[:, 1] = np.abs(x[:, 1]) + f32(0.5); x[0, 1, 9] = f32(0.0); x[1, 1, 0] = f32(-0.0)
+    out.append(("per-channel", x, (1, 4, 1)))
+    # beyond the scan's start values: all below -1e8 (max stays -1e8), all above +1e8 (min stays +1e8)
+    out.append(("below-1e8", np.array([[-3e8, -2e8, -5e8]], f32), (1, 1)))
+    out.append(("above+1e8", np.array([[3e8, 2e8, 5e8]], f32), (1, 1)))
+    return out
+
+
 def minmax_inputs(x_shape, q_shape):
     rng = np.random.RandomState(SEED)
     x = rng.randn(*x_shape).astype(np.float32)

@@ -1,6 +1,6 @@
 """GPU parity of the affine layers (tcgen05 contractions) through the C ABI:
 signs bit-exact, alpha to 1e-6, outputs within 1e-5 of the output RMS of the
-oracle (the tolerance BASELINE.json states for GEMM outputs)."""
+oracle (1e-5 of the output RMS, the tolerance the benchmark definition states for GEMM outputs)."""
 import numpy as np
 import pytest
 import torch

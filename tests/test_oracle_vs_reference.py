@@ -58,6 +58,19 @@ def test_min_max_quantize(shapes, decay, x_min_max, ema):
     assert np.array_equal(bits(gy), bits(wy))
 
 
+@pytest.mark.parametrize("case", cases.minmax_zero_sign_cases(), ids=lambda c: c[0])
+@pytest.mark.parametrize("ema", [False, True])
+def test_min_max_quantize_zero_extrema(case, ema):
+    """Signed zeros as the minimum / maximum (first one in scan order wins) and the +-1e8 start values."""
+    _, x, qs = case
+    q = lambda v: np.full(qs, v, np.float32)
+    wy, wmin, wmax = ref.min_max_quantize(x, q(-0.5), q(0.5), q(0), q(255), 0.9, True, ema, True, 0.01)
+    gy, gmin, gmax, _ = oracle.min_max_quantize(x, q(-0.5), q(0.5), q(0), q(255), 0.9, True, ema, 0.01)
+    assert np.array_equal(bits(gmin), bits(wmin))
+    assert np.array_equal(bits(gmax), bits(wmax))
+    assert np.array_equal(bits(gy), bits(wy))
+
+
 def test_min_max_quantize_config_and_eps_nudge():
     rng = np.random.RandomState(0)
     x = rng.uniform(-4, 4, (1 << 18,)).astype(np.float32)

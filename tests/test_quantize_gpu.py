@@ -119,6 +119,22 @@ def test_minmax_golden(F, i):
     assert np.array_equal(sha(host(y)), g[f"minmax{i}/out_sha"])
 
 
+@pytest.mark.parametrize("case", cases.minmax_zero_sign_cases(), ids=lambda c: c[0])
+@pytest.mark.parametrize("ema", [False, True])
+def test_minmax_zero_extrema(F, case, ema):
+    """x_min_max with a signed zero as the extremum: the first zero in the reference's scan order
+    gives qr_min / qr_max its sign (one block and several blocks of the device reduction), and the
+    scans start from +-1e8 as the reference's Min / Max do."""
+    _, x, qs = case
+    q = lambda v: np.full(qs, v, np.float32)
+    dmin, dmax = dev(q(-0.5)), dev(q(0.5))
+    y = F.min_max_quantize(dev(x), dmin, dmax, dev(q(0)), dev(q(255)), 0.9, True, ema, True, 0.01)
+    wy, wmin, wmax, _ = oracle.min_max_quantize(x, q(-0.5), q(0.5), q(0), q(255), 0.9, True, ema, 0.01)
+    assert np.array_equal(bits(host(dmin)), bits(wmin))
+    assert np.array_equal(bits(host(dmax)), bits(wmax))
+    assert np.array_equal(bits(host(y)), bits(wy))
+
+
 def test_minmax_cfg_digest_tails_and_errors(F):
     g = golden()
     rng = np.random.RandomState(0)

@@ -58,6 +58,38 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert torch.equal(nmax.view(torch.int32), rmax.view(torch.int32))
 
 
+def _pool_high(reset):
+    from nnabla_b200 import _capi as C
+    high = ctypes.c_int64(0)
+    C.call("nb200_scratch_pool_stats", None, ctypes.byref(high), int(reset))
+    return high.value
+
+
+def test_noalloc_takes_nothing_from_the_scratch_pool():
+    """What the entry point is for: between a reset of the scratch pool's high-water mark and the
+    end of the call the mark does not move, while the regular entry point (which takes its 28 bytes
+    per range from the pool) moves it. torch's own allocator is not involved in either call: every
+    tensor is made before the mark is reset."""
+    from nnabla_b200 import _capi as C
+    torch.cuda.set_device(0)
+    x, qmin, qmax, lmin, lmax = _inputs(5, (4, 8, 16, 16), (1, 8, 1, 1))
+    y, scale = torch.empty_like(x), torch.empty_like(qmin)
+
+    def run(entry):
+        C.call(entry, C.ptr(x), C.i64_array(x.shape), x.dim(), C.ptr(qmin), C.ptr(qmax), C.ptr(lmin), C.ptr(lmax),
+               C.i64_array(qmin.shape), C.c_float(0.9), 1, 1, C.c_float(0.01), C.ptr(y), C.ptr(scale),
+               C.stream_ptr(x.device))
+        torch.cuda.synchronize()
+    run("nb200_min_max_quantize_f32_noalloc")  # first call on the device: address lookup, tables
+    torch.cuda.synchronize()
+    before = _pool_high(reset=True)
+    run("nb200_min_max_quantize_f32_noalloc")
+    assert _pool_high(reset=False) == before
+    before = _pool_high(reset=True)
+    run("nb200_min_max_quantize_f32")
+    assert _pool_high(reset=False) > before
+
+
 def test_noalloc_refuses_more_ranges_than_its_array_holds():
     from nnabla_b200 import _capi as C
     torch.cuda.set_device(0)
