@@ -3,20 +3,27 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
-Headline workload (BASELINE.json configs[1], the configuration the quantizer
-GB/s metric is quoted on): one step = FixedPointQuantize(sign, n=8, delta=2^-4),
-Pow2Quantize(sign, with_zero, n=8, m=1) and MinMaxQuantize(ql 0..255, given
-per-tensor range -4..4) each applied to an fp32 tensor of 2^30 elements
-~U(-4,4). Algorithmic traffic is 8 bytes per element per quantizer.
+Headline workload: the binary-weight ResNet-18 (first convolution and final
+affine full precision, every other convolution a BinaryWeightConvolution,
+FixedPointQuantize(n=8, delta=2^-4) after each ReLU, BatchNormalization on
+running statistics), random initialisation, input fp32 [256, 3, 224, 224]
+~N(0,1), 1000 classes. One step = one forward pass of the whole batch; with N
+GPUs (torchrun, one process per GPU) the batch is sharded, 256 / N images per
+GPU, weights replicated, no collective in the forward pass (strong scaling).
+`value` is images per second of the graph AS IT IS WRITTEN, function by
+function through nnabla_b200.functions; the other execution forms of the same
+graph (fused activation pass, int8 codes between the layers, prepared
+weights, CUDA-graph replay: all bit-identical logits; BN folded into the
+convolutions: its own tolerance) are reported under `forms`.
 
-Prints ONE JSON line (rank 0). With N > 1 (torchrun) every rank processes its
-own tensor: the path shards by elements with no collective (weak scaling).
+Prints ONE JSON line (rank 0). The other benchmark configurations (single
+layers, the quantizer sweep, the column-sharded fixed-point affine) follow
+under `other_configs`; the keys a reader needs first are the last ones.
 """
 import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -26,9 +33,8 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-BYTES_PER_ELEM = 8  # 4 read + 4 written, per quantizer
-QUANTIZERS = ("fixed_point_quantize", "pow2_quantize", "min_max_quantize")
-CPU_SAMPLE_LOG2 = 24
+IMAGE = (3, 224, 224)
+CLASSES = 1000
 
 
 def parse_args():
@@ -37,148 +43,94 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--size-log2", type=int, default=30)
-    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--batch", type=int, default=256, help="images per step over all GPUs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
-    ap.add_argument("--no-extras", action="store_true", help="skip the other BASELINE configurations")
-    ap.add_argument("--resnet-batch", type=int, default=256, help="images per GPU for the ResNet-18 extra")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other configurations")
+    ap.add_argument("--no-forms", action="store_true", help="skip the other execution forms of the network")
     ap.add_argument("--only-extras", action="store_true",
-                    help="run only the other BASELINE configurations and print their JSON (profiling runs)")
+                    help="run only the other configurations and print their JSON (profiling runs)")
     ap.add_argument("--small-extras", action="store_true",
                     help="reduced sizes for the other configurations (ncu captures must stay small)")
-    ap.add_argument("--backward-log2", type=int, default=0,
-                    help="log2 of the element count of the quantizer-backward entry (default 28, 22 with --small-extras)")
+    ap.add_argument("--sweep-max-log2", type=int, default=30, help="largest size of the quantizer sweep")
     return ap.parse_args()
 
 
+def round_floats(o, digits=5):
+    """Numbers with a few significant digits keep the JSON line short."""
+    if isinstance(o, float):
+        return float("%.*g" % (digits, o))
+    if isinstance(o, dict):
+        return {k: round_floats(v, digits) for k, v in o.items()}
+    if isinstance(o, (list, tuple)):
+        return [round_floats(v, digits) for v in o]
+    return o
+
+
 # --------------------------------------------------------------------------- CPU arm
-def cpu_functions():
-    """(kind, {name: callable(x)->seconds}) — the reference's own compiled CPU
-    functions when oracle/_ref is present, else the C restatement."""
-    from oracle import ref
+def cpu_network():
+    """(kind, function namespace) of the CPU implementation of the network's functions: the
+    reference's own compiled code where oracle/_ref is present, else the C restatement."""
+    from oracle import ops, ref
     if ref.available():
-        one = lambda v: np.array([v], np.float32)
-        return "reference", {
-            "fixed_point_quantize": lambda x: ref.fixed_point_quantize(x, True, 8, 2.0 ** -4, timed=True)[1],
-            "pow2_quantize": lambda x: ref.pow2_quantize(x, True, True, 8, 1, timed=True)[1],
-            "min_max_quantize": lambda x: ref.min_max_quantize(x, one(-4), one(4), one(0), one(255), timed=True)[3],
-        }
-    from oracle import oracle
-
-    def timed(fn):
-        def run(x):
-            t0 = time.perf_counter()
-            fn(x)
-            return time.perf_counter() - t0
-        return run
-    return "port", {
-        "fixed_point_quantize": timed(lambda x: oracle.fixed_point_quantize(x, True, 8, 2.0 ** -4)),
-        "pow2_quantize": timed(lambda x: oracle.pow2_quantize(x, True, True, 8, 1)),
-        "min_max_quantize": timed(lambda x: oracle.min_max_quantize(x, [-4], [4], [0], [255])),
-    }
+        return "reference", ops.reference()
+    return "port", ops
 
 
-def cpu_step(fns, slices):
-    """One bounded CPU step: every quantizer over every slice, one host thread
-    per slice (the reference functions are single-threaded; independent
-    function instances may run on separate threads). Returns wall seconds."""
-    def work(x):
-        for name in QUANTIZERS:
-            fns[name](x)
+def cpu_images_per_second(images, threads):
+    """Runs the reference network on `images` images, one image per call, spread over `threads`
+    host threads (independent function instances; the reference's CPU functions are
+    single-threaded). Returns (images per second, seconds)."""
+    from nnabla_b200 import resnet18
+    kind, ns = cpu_network()
+    params = resnet18.init_parameters(np.random.RandomState(0))
+    rng = np.random.RandomState(1)
+    xs = [rng.randn(1, *IMAGE).astype(np.float32) for _ in range(images)]
+    cz = lambda w, shape=None: np.zeros(shape or w.shape, np.float32)
+
+    def work(mine):
+        net = resnet18.Runner(ns, params, cz, None, fixed_point_hint=False)
+        for x in mine:
+            net(x)
     t0 = time.perf_counter()
-    ths = [threading.Thread(target=work, args=(s,)) for s in slices]
+    ths = [threading.Thread(target=work, args=(xs[i::threads],)) for i in range(threads)]
     for t in ths:
         t.start()
     for t in ths:
         t.join()
-    return time.perf_counter() - t0
-
-
-def cpu_inputs(threads):
-    rng = np.random.RandomState(0)
-    n = 1 << CPU_SAMPLE_LOG2
-    x = rng.uniform(-4, 4, n).astype(np.float32)
-    per = n // threads
-    return [x[i * per:(i + 1) * per] for i in range(threads)], per * threads
-
-
-def cpu_contraction_samples():
-    """CPU times of the GEMM / convolution configurations on bounded samples, beside the GPU
-    numbers of `other_configs`. The reference multiplies through Eigen, which its build downloads
-    and which is not in its tree; the contraction is therefore timed with the host's BLAS (NumPy)
-    under the reference's control flow (sign / alpha passes, one unfold + one GEMM per sample,
-    src/nbla/function/generic/convolution.cpp:160-197), once on 1 thread (the reference's CPU
-    build is single-threaded) and once on all cores."""
-    try:
-        from threadpoolctl import threadpool_limits
-    except ImportError:  # pragma: no cover - optional
-        return {"unavailable": "threadpoolctl is missing"}
-    rng = np.random.RandomState(0)
-    f32 = np.float32
-    out = {"blas": "NumPy's BLAS in place of Eigen (not vendored in the reference)"}
-
-    def best_ms(fn, reps=2):
-        ts = []
-        for _ in range(reps):
-            t0 = time.perf_counter()
-            fn()
-            ts.append(time.perf_counter() - t0)
-        return 1e3 * min(ts)
-    x0, w0 = rng.randn(256, 1024).astype(f32), (0.02 * rng.randn(1024, 4096)).astype(f32)
-
-    def bwa():
-        alpha = np.abs(w0).sum(0) * f32(1.0 / 1024)
-        return x0 @ (np.where(w0 > 0, f32(1), f32(-1)) * alpha)
-    rows = 512  # of 8192
-    x2 = (np.rint(rng.randn(rows, 4096) * 32).clip(-127, 127) * f32(2.0 ** -5)).astype(f32)
-    w2 = (np.rint(rng.randn(4096, 8192) * 20).clip(-127, 127) * f32(2.0 ** -10)).astype(f32)
-    imgs = 4  # of 128
-    x3 = np.maximum(rng.randn(imgs, 256, 28, 28), 0).astype(f32)
-    w3 = (rng.randn(256, 2304) * np.sqrt(2.0 / 2304)).astype(f32)
-
-    def bwc():
-        alpha = np.abs(w3).sum(1) * f32(1.0 / 2304)
-        wb = np.where(w3 > 0, f32(1), f32(-1)) * alpha[:, None]
-        for i in range(imgs):
-            xp = np.pad(x3[i], ((0, 0), (1, 1), (1, 1)))
-            col = np.lib.stride_tricks.sliding_window_view(xp, (3, 3), axis=(1, 2))  # [256, 28, 28, 3, 3]
-            col = np.ascontiguousarray(col.transpose(0, 3, 4, 1, 2)).reshape(2304, 784)
-            wb @ col
-    for label, threads in (("1_thread", 1), ("all_cores", os.cpu_count() or 1)):
-        with threadpool_limits(limits=threads):
-            out[label] = {
-                "threads": threads,
-                "configs[0] binary_weight_affine 256x1024x4096 ms": best_ms(bwa),
-                "configs[2] affine 8192x4096x8192 ms (512 of 8192 rows timed, scaled x16)": 16 * best_ms(lambda: x2 @ w2),
-                "configs[3] binary_weight_convolution batch 128 ms (4 images timed, scaled x32)": 32 * best_ms(bwc),
-            }
-    return out
+    dt = time.perf_counter() - t0
+    return kind, images / dt, dt
 
 
 def run_reference_arm(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    kind, fns = cpu_functions()
-    threads = os.cpu_count() or 1
-    slices, n = cpu_inputs(threads)
-    for _ in range(max(1, min(args.warmup, 1))):
-        cpu_step(fns, slices)
-    times = [cpu_step(fns, slices) for _ in range(args.steps)]
-    total = sum(times)
-    value = len(QUANTIZERS) * BYTES_PER_ELEM * n * args.steps / total / 1e9
-    sample = "each step: 3 quantizers over 2^%d elements split over %d host threads" % (CPU_SAMPLE_LOG2, threads)
+    threads = min(os.cpu_count() or 1, 16)
+    for _ in range(1 if args.warmup > 0 else 0):
+        cpu_images_per_second(threads, threads)
+    total, kind = 0.0, "port"
+    for _ in range(args.steps):
+        kind, _, dt = cpu_images_per_second(threads, threads)
+        total += dt
+    value = threads * args.steps / total
+    sample = "each step: %d images (of the %d of a batch), one per host thread, whole network per image" % (
+        threads, args.batch)
     line = {
-        "impl": "reference", "metric": "quantizer_GBps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[1]: FixedPoint+Pow2+MinMax quantize, fp32 U(-4,4); CPU arm on a bounded "
-                               "sample of 2^%d elements per step" % CPU_SAMPLE_LOG2},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
-        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": "resnet18_images_per_sec", "value": value, "unit": "images/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.batch, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    print(json.dumps(round_floats(line)))
+
+
+def workload_config(batch, world):
+    return {"workload": "configs[4]: binary-weight ResNet-18 forward, fp32 input [%d,3,224,224], 1000 classes, "
+                        "random init, batch sharded over the GPUs" % batch,
+            "global_batch": batch, "images_per_gpu": batch // max(1, world),
+            "form": "graph as written, one call per function"}
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -260,15 +212,128 @@ def time_gpu(fn, iters, warm=3):
     return e0.elapsed_time(e1) / iters
 
 
-def run_extras(args, rank, world, barrier):
-    """The other BASELINE configurations, timed per rank (inputs resident in
-    HBM, tensors larger than L2 or an L2 flush between iterations is not
-    applied to these short runs: stated per entry)."""
+def measure_int8_peak(seconds=2.0):
+    """Dense int8 tensor-core throughput of this GPU with the library GEMM (torch._int_mm, 8192^3),
+    by the method of the measured bf16 peak: best of 10 single launches, and back to back for a
+    few seconds (sustained, under the power cap). TOP/s."""
+    import torch
+    n = 8192
+    a = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
+    b = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8).t()  # column-major, as the library wants
+    ops = 2.0 * n ** 3
+    for _ in range(3):
+        torch._int_mm(a, b)
+    best = 1e30
+    for _ in range(10):
+        best = min(best, time_gpu(lambda: torch._int_mm(a, b), 1, warm=0))
+    per = max(best, 1e-3)
+    iters = max(10, int(seconds * 1e3 / per))
+    sustained = time_gpu(lambda: torch._int_mm(a, b), iters, warm=0)
+    return {"int8_tops": ops / best / 1e9, "int8_tops_sustained": ops / sustained / 1e9,
+            "how": "torch._int_mm 8192^3, best of 10 and %d launches back to back" % iters}
+
+
+class FunctionTimer:
+    """Wraps a function namespace: every call is bracketed by CUDA events on the current stream
+    and filed under the function's name with its algorithmic work (bytes for the memory-bound
+    functions, operations for the contractions)."""
+
+    def __init__(self, ns):
+        self._ns = ns
+        self.records = []
+
+    def __getattr__(self, name):
+        import torch
+        fn = getattr(self._ns, name)
+
+        def timed(*a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            y = fn(*a, **kw)
+            e1.record()
+            self.records.append((name, e0, e1, self._work(name, a, kw, y)))
+            return y
+        return timed
+
+    @staticmethod
+    def _work(name, a, kw, y):
+        n_in = a[0].numel()
+        n_out = y.numel() if hasattr(y, "numel") else 0
+        if name in ("batch_normalization", "relu", "fixed_point_quantize"):
+            return ("bytes", 8.0 * n_in)
+        if name == "add2":
+            return ("bytes", 12.0 * n_in)
+        if name in ("max_pooling", "global_average_pooling"):
+            return ("bytes", 4.0 * (n_in + n_out))
+        if name in ("convolution", "binary_weight_convolution"):
+            w = a[1]
+            k = w.shape[1] * w.shape[2] * w.shape[3]
+            kind = "int8_ops" if (name == "binary_weight_convolution" and kw.get("fixed_point_delta")) else "flops"
+            return (kind, 2.0 * n_out * k)
+        if name == "affine":
+            return ("flops", 2.0 * n_out * a[1].shape[0])
+        return ("bytes", 0.0)
+
+    def table(self):
+        import torch
+        torch.cuda.synchronize()
+        fam = {}
+        for name, e0, e1, (kind, work) in self.records:
+            f = fam.setdefault(name, {"calls": 0, "ms": 0.0, "kind": kind, "work": 0.0})
+            f["calls"] += 1
+            f["ms"] += e0.elapsed_time(e1)
+            f["work"] += work
+        return fam
+
+
+def function_table(F, params, gz, x, peaks, int8_peak, passes=3):
+    """Per-function time table of the as-written graph (each function's calls bracketed by CUDA
+    events, averaged over `passes` forward passes) and the roofline entry of the family with the
+    largest share."""
+    from nnabla_b200 import resnet18
+    timer = FunctionTimer(F)
+    net = resnet18.Runner(timer, params, gz)
+    net(x)
+    timer.records.clear()
+    for _ in range(passes):
+        net(x)
+    fam = timer.table()
+    total = sum(f["ms"] for f in fam.values())
+    rows = {}
+    for name, f in sorted(fam.items(), key=lambda kv: -kv[1]["ms"]):
+        ms = f["ms"] / passes
+        row = {"calls": f["calls"] // passes, "ms": ms, "share": f["ms"] / total}
+        if f["kind"] == "bytes":
+            row["GBps"] = f["work"] / f["ms"] / 1e6
+            row["frac_hbm"] = row["GBps"] / peaks["hbm_gbs"]
+        elif f["kind"] == "int8_ops":
+            row["int8_tops"] = f["work"] / f["ms"] / 1e9
+            row["frac_int8"] = row["int8_tops"] / int8_peak
+        else:
+            row["tflops"] = f["work"] / f["ms"] / 1e9
+            row["frac_bf16"] = row["tflops"] / peaks["bf16_tflops"]
+        rows[name] = row
+    top = max(fam.items(), key=lambda kv: kv[1]["ms"])
+    name, f = top
+    per_call_ms = f["ms"] / f["calls"]
+    if f["kind"] == "bytes":
+        ach, peak, unit, bound = f["work"] / f["ms"] / 1e6, peaks["hbm_gbs"], "GB/s", "hbm"
+    elif f["kind"] == "int8_ops":
+        ach, peak, unit, bound = f["work"] / f["ms"] / 1e9, int8_peak, "TOP/s", "tensor"
+    else:
+        ach, peak, unit, bound = f["work"] / f["ms"] / 1e9, peaks["bf16_tflops"], "TFLOP/s", "tensor"
+    roof = {"bound": bound, "kernel": name, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+            "traffic": None, "share_of_step": f["ms"] / total, "ms_per_call": per_call_ms,
+            "algorithmic_work_per_call": f["work"] / f["calls"]}
+    return rows, roof
+
+
+def run_extras(args, rank, world, peaks, int8_peak):
+    """The other configurations, timed per rank (inputs resident in HBM)."""
     import torch
     import torch.distributed as dist
     from nnabla_b200 import functions as F
-    from nnabla_b200 import resnet18, sharding
-    peaks, _ = measured_peaks()
+    from nnabla_b200 import sharding
     out = {}
     gen = torch.Generator(device="cuda").manual_seed(99 + rank)
     rn = lambda *s: torch.randn(*s, device="cuda", generator=gen)
@@ -280,24 +345,40 @@ def run_extras(args, rank, world, barrier):
             return float(t.item())
         return ms
 
-    # configs[0]: BinaryWeightAffine 256 x 1024 x 4096 (replicated on every rank)
+    # configs[0]: BinaryWeightAffine 256 x 1024 x 4096 (replicated on every rank; working set fits L2)
     M, K, N = 256, 1024, 4096
     x, w, b = rn(M, K), 0.02 * rn(K, N), torch.zeros(N, device="cuda")
     wb, al = torch.zeros_like(w), torch.zeros(N, device="cuda")
     ms = maxr(time_gpu(lambda: F.binary_weight_affine(x, w, wb, al, b), 50))
-    out["configs[0] binary_weight_affine 256x1024x4096"] = {
-        "ms": ms, "tflops_algorithmic": 2 * M * K * N / ms / 1e9, "tflops_issued_bf16x3": 6 * M * K * N / ms / 1e9,
-        "frac_of_bf16_peak_issued": 6 * M * K * N / ms / 1e9 / peaks["bf16_tflops"],
-        "includes": "binarise + alpha + split + GEMM, whole forward_impl", "l2": "working set fits L2 (latency-bound case)"}
-    try:  # the same forward_impl recorded once as a CUDA graph: its five dependent launches replay as one
+    e0 = {"ms": ms, "us_hbm_floor": 38.8e6 / peaks["hbm_gbs"] / 1e3, "frac_hbm": 38.8e6 / peaks["hbm_gbs"] / 1e6 / ms,
+          "tflops_issued_bf16x3": 6 * M * K * N / ms / 1e9, "frac_bf16_issued": 6 * M * K * N / ms / 1e9 / peaks["bf16_tflops"]}
+    try:  # the same forward_impl recorded once as a CUDA graph
         from nnabla_b200 import graphs
         cap0 = graphs.Captured(lambda xx: F.binary_weight_affine(xx, w, wb, al, b), x)
-        out["configs[0] binary_weight_affine 256x1024x4096"]["ms_cuda_graph"] = maxr(
-            time_gpu(lambda: cap0.graph.replay(), 50))
+        e0["ms_cuda_graph"] = maxr(time_gpu(lambda: cap0.graph.replay(), 50))
         del cap0
     except RuntimeError as e:
-        out["configs[0] binary_weight_affine 256x1024x4096"]["ms_cuda_graph"] = None
-        out["configs[0] binary_weight_affine 256x1024x4096"]["cuda_graph_note"] = str(e)[:80]
+        e0["ms_cuda_graph"] = None
+    out["configs[0] binary_weight_affine 256x1024x4096"] = e0
+
+    # configs[1]: quantizer sweep, 2^20 .. 2^30 elements (sizes up to L2 run out of L2 after the first pass)
+    one = lambda v: torch.tensor([v], device="cuda", dtype=torch.float32)
+    qa, qb, la, lb = one(-4.0), one(4.0), one(0.0), one(255.0)
+    sweep = {}
+    for k in range(20, min(args.sweep_max_log2, 22 if args.small_extras else 30) + 1, 2):
+        n = 1 << k
+        xs = torch.rand(n, device="cuda", generator=gen) * 8 - 4
+        ys = torch.empty_like(xs)
+        it = 50 if k <= 24 else (20 if k <= 28 else 10)
+        t = [maxr(time_gpu(lambda: F.fixed_point_quantize(xs, True, 8, 2.0 ** -4, outputs=[ys]), it)),
+             maxr(time_gpu(lambda: F.pow2_quantize(xs, True, True, 8, 1, outputs=[ys]), it)),
+             maxr(time_gpu(lambda: F.min_max_quantize(xs, qa, qb, la, lb, outputs=[ys]), it))]
+        sweep["2^%d" % k] = {"GBps_fxp_pow2_minmax": [8.0 * n / v / 1e6 for v in t],
+                             "frac_hbm": [8.0 * n / v / 1e6 / peaks["hbm_gbs"] for v in t]}
+        del xs, ys
+    out["configs[1] quantizers (per GPU)"] = sweep
+    torch.cuda.empty_cache()
+
     # configs[2]: 8-bit fixed-point affine, output columns sharded over the ranks
     M, K, N = (4096, 4096, 4096) if args.small_extras else (8192, 4096, 8192)
     Ns = N // world
@@ -306,65 +387,79 @@ def run_extras(args, rank, world, barrier):
     b = 0.01 * rn(Ns)
     xq, xc = F.fixed_point_quantize_with_codes(x, True, 8, 2.0 ** -5)
     wq, wc = F.fixed_point_quantize_with_codes(w, True, 8, 2.0 ** -10)
+    ops = 2.0 * M * K * N
     ms_gemm = maxr(time_gpu(lambda: F.affine_from_codes(xc, wc, 2.0 ** -5, 2.0 ** -10, b), 20))
-    wk = F.transpose_codes(wc)  # the weight's codes in the tensor core's layout, prepared once per weight update
+    wk = F.transpose_codes(wc)  # the weight's codes in the tensor core's layout, made once per weight update
     ms_prepared = maxr(time_gpu(lambda: F.affine_from_kmajor_codes(xc, wk, K, 2.0 ** -5, 2.0 ** -10, b), 20))
-    entry = {"ms_gemm": ms_gemm, "int8_tops_whole_job": 2 * M * K * N / ms_gemm / 1e9,
-             "ms_gemm_prepared_weights": ms_prepared,
-             "int8_tops_whole_job_prepared_weights": 2 * M * K * N / ms_prepared / 1e9,
-             "ms_gemm_includes": "ms_gemm re-lays the weight codes out K-major on every call (0.07 ms at the full "
-                                 "size); ms_gemm_prepared_weights reuses a layout made once (transpose_codes)",
-             "columns_per_gpu": Ns, "l2": "operands 32 MiB + 32 MiB/g int8; output 256 MiB/g fp32 exceeds L2"}
-    ms_q = maxr(time_gpu(lambda: (F.fixed_point_quantize_with_codes(x, True, 8, 2.0 ** -5),
-                                  F.fixed_point_quantize_with_codes(w, True, 8, 2.0 ** -10)), 10))
-    entry["ms_quantize_x_and_w"] = ms_q
-    try:  # the library's int8 GEMM on the same codes, for context only (int32 output, no scaling, no bias)
-        wct = wc.t().contiguous().t()  # column-major B, the layout the library wants
+
+    def chain():  # what a graph runs: FixedPointQuantize(x), FixedPointQuantize(W), Affine on the fp32 tensors
+        a = F.fixed_point_quantize(x, True, 8, 2.0 ** -5)
+        c = F.fixed_point_quantize(w, True, 8, 2.0 ** -10)
+        return F.affine(a, c, b, fixed_point=(2.0 ** -5, 2.0 ** -10))
+    ms_chain = maxr(time_gpu(chain, 10))
+    ms_qx = maxr(time_gpu(lambda: F.fixed_point_quantize(x, True, 8, 2.0 ** -5), 10))
+    ms_qw = maxr(time_gpu(lambda: F.fixed_point_quantize(w, True, 8, 2.0 ** -10), 10))
+    ms_aff = maxr(time_gpu(lambda: F.affine(xq, wq, b, fixed_point=(2.0 ** -5, 2.0 ** -10)), 10))
+    e2 = {"columns_per_gpu": Ns,
+          "ms_gemm_kmajor_codes": ms_prepared, "int8_tops_kmajor_codes": ops / ms_prepared / 1e9,
+          "frac_int8_kmajor_codes": ops / world / ms_prepared / 1e9 / int8_peak,
+          "ms_gemm_codes": ms_gemm, "int8_tops_codes": ops / ms_gemm / 1e9,
+          "frac_int8_codes": ops / world / ms_gemm / 1e9 / int8_peak,
+          "ms_chain_quantize_x_quantize_w_affine": ms_chain, "int8_tops_chain": ops / ms_chain / 1e9,
+          "frac_int8_chain": ops / world / ms_chain / 1e9 / int8_peak,
+          "ms_quantize_x": ms_qx, "ms_quantize_w": ms_qw, "ms_affine_on_fp32_operands": ms_aff}
+    try:  # the library's int8 GEMM on the same codes, for context (int32 output, no scaling, no bias)
+        wct = wc.t().contiguous().t()
         ms_lib = maxr(time_gpu(lambda: torch._int_mm(xc, wct), 20))
-        entry["library_int8_gemm_ms"] = ms_lib
-        entry["library_int8_tops_whole_job"] = 2 * M * K * N / ms_lib / 1e9
-    except Exception as e:  # noqa: BLE001 - the comparison is optional
-        entry["library_int8_gemm_ms"] = None
-        entry["library_int8_note"] = str(e)[:100]
+        e2["ms_library_int8_gemm"] = ms_lib
+    except Exception:  # noqa: BLE001 - the comparison is optional
+        e2["ms_library_int8_gemm"] = None
     if world > 1:
         def gemm_and_gather():
             yy = F.affine_from_codes(xc, wc, 2.0 ** -5, 2.0 ** -10, b)
             return sharding.gather_columns(yy, N)
-        entry["ms_gemm_plus_allgather"] = maxr(time_gpu(gemm_and_gather, 10))
-        entry["collective"] = "NCCL all-gather of the [8192, N/g] fp32 output slabs + interleave"
-        # the same with the gather fused into the contraction: every rank's epilogue stores its slab into all
-        # ranks' [M, N] results over NVLink (peer mappings), then one tiny all-reduce orders the ranks
+        e2["ms_gemm_plus_nccl_allgather"] = maxr(time_gpu(gemm_and_gather, 10))
+        # the gather fused into the contraction: every rank's epilogue stores its slab into all ranks'
+        # [M, N] results over NVLink (peer mappings), then one tiny all-reduce orders the ranks
         mats = sharding.PeerMatrices(M, N)
 
         def gemm_fused_gather():
             F.affine_from_codes_gather(xc, wc, 2.0 ** -5, 2.0 ** -10, b, mats.ptrs, rank, N, rank * Ns)
             mats.fence()
-        entry["ms_gemm_fused_gather"] = maxr(time_gpu(gemm_fused_gather, 10))
-        entry["fused_gather_equals_allgather"] = bool(torch.equal(mats.local, gemm_and_gather()))
-        entry["fused_gather_GBps_out_per_gpu"] = (world - 1) * M * Ns * 4 / entry["ms_gemm_fused_gather"] / 1e6
+        e2["ms_gemm_fused_gather_all_ranks"] = maxr(time_gpu(gemm_fused_gather, 10))
+        e2["fused_gather_GBps_out_per_gpu"] = (world - 1) * M * Ns * 4 / e2["ms_gemm_fused_gather_all_ranks"] / 1e6
+        # gather to rank 0 only: every rank stores its slab into rank 0's result (and rank 0 into its own)
+        only0 = [mats.ptrs[0]]
+
+        def gemm_gather_rank0():
+            F.affine_from_codes_gather(xc, wc, 2.0 ** -5, 2.0 ** -10, b, only0, 0, N, rank * Ns)
+            mats.fence()
+        try:
+            e2["ms_gemm_fused_gather_rank0"] = maxr(time_gpu(gemm_gather_rank0, 10))
+        except Exception as exc:  # noqa: BLE001
+            e2["ms_gemm_fused_gather_rank0"] = None
+            e2["gather_rank0_note"] = str(exc)[:60]
+        gemm_fused_gather()
+        torch.cuda.synchronize()
+        want = gemm_and_gather()
+        same = bool(torch.equal(mats.local, want))
+        # a window of rows of the gathered result against an integer product worked out on its own:
+        # every partial sum is an integer below 2^24, so fp32(acc) * 2^-15 + bias is exact up to one rounding
+        rows = slice(M // 2 - 16, M // 2 + 16)
+        acc = xc[rows].to(torch.float64) @ wc.to(torch.float64)  # exact: |acc| < 2^53
+        ref = (acc.to(torch.float32) * (2.0 ** -15) + b)
+        window_ok = bool(torch.equal(mats.local[rows, rank * Ns:(rank + 1) * Ns], ref))
+        flags = torch.tensor([int(same), int(window_ok)], device="cuda")
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        e2["fused_gather_equals_allgather"] = bool(flags[0].item())
+        e2["gathered_rows_equal_integer_product"] = bool(flags[1].item())
         mats.close()
-    out["configs[2] fixed-point int8 affine %dx%dx%d" % (M, K, N)] = entry
-    del x, w, xq, wq, xc, wc
-    # quantizer backward passes (straight-through estimators) on the configs[1] parameters, per rank
-    nb = 1 << (args.backward_log2 or (22 if args.small_extras else 28))
-    gx = torch.rand(nb, device="cuda", generator=gen) * 9 - 4.5
-    gdy = rn(nb)
-    gdx = torch.empty_like(gx)
-    one = lambda v: torch.tensor([v], device="cuda")
-    qa, qb, la, lb = one(-4.0), one(4.0), one(0.0), one(255.0)
-    F.min_max_quantize(gx, qa, qb, la, lb)
-    bw = {}
-    for name, fn, bpe in (
-            ("fixed_point", lambda: F.fixed_point_quantize_backward(gx, gdy, True, 8, 2.0 ** -4, True, False, gdx), 12),
-            ("pow2", lambda: F.pow2_quantize_backward(gx, gdy, True, True, 8, 1, True, False, gdx), 12),
-            ("min_max_dx_and_ranges", lambda: F.min_max_quantize_backward(gx, qa, qb, la, lb, gdy, grads=(gdx, None, None)), 12),
-            ("fixed_point_accum", lambda: F.fixed_point_quantize_backward(gx, gdy, True, 8, 2.0 ** -4, True, True, gdx), 16),
-            ("coarse_ste_copy", lambda: F.fixed_point_quantize_backward(gx, gdy, True, 8, 2.0 ** -4, False, False, gdx), 8)):
-        ms = maxr(time_gpu(fn, 10))
-        bw[name] = {"ms": ms, "GBps_per_gpu": bpe * nb / ms / 1e6, "bytes_per_element": bpe,
-                    "frac_of_hbm_peak": bpe * nb / ms / 1e6 / peaks["hbm_gbs"]}
-    out["quantizer backward, 2^%d elements per GPU" % (nb.bit_length() - 1)] = bw
-    del gx, gdy, gdx
+        assert e2["fused_gather_equals_allgather"], "peer-store gather differs from the NCCL all-gather"
+        assert e2["gathered_rows_equal_integer_product"], "gathered result differs from the integer product"
+    out["configs[2] fixed-point int8 affine %dx%dx%d" % (M, K, N)] = e2
+    del x, w, xq, wq, xc, wc, wk
+    torch.cuda.empty_cache()
+
     # configs[3]: BinaryWeightConvolution 3x3, 256 -> 256, 28 x 28, batch 128 sharded over the ranks
     Nb = max(1, (16 if args.small_extras else 128) // world)
     x = torch.relu(rn(Nb, 256, 28, 28))
@@ -372,85 +467,18 @@ def run_extras(args, rank, world, barrier):
     wb, al, b = torch.zeros_like(w), torch.zeros(256, device="cuda"), torch.zeros(256, device="cuda")
     ms = maxr(time_gpu(lambda: F.binary_weight_convolution(x, w, wb, al, b, 1, (1, 1), (1, 1)), 10))
     flops = 2.0 * (Nb * world * 28 * 28) * 256 * 2304
-    out["configs[3] binary_weight_convolution 3x3 256->256 28x28 batch %d" % (Nb * world)] = {
-        "ms": ms, "tflops_algorithmic_whole_job": flops / ms / 1e9, "tflops_issued_bf16x3_whole_job": 3 * flops / ms / 1e9,
-        "frac_of_bf16_peak_issued_per_gpu": 3 * flops / world / ms / 1e9 / peaks["bf16_tflops"],
-        "includes": "binarise + NCHW->NHWC split + implicit GEMM, whole forward_impl", "images_per_gpu": Nb}
-    # backward of the same layer (straight-through weight gradient), per rank
+    e3 = {"ms": ms, "images_per_gpu": Nb, "tflops_algorithmic": flops / ms / 1e9,
+          "tflops_issued_bf16x3": 3 * flops / ms / 1e9,
+          "frac_bf16_issued_per_gpu": 3 * flops / world / ms / 1e9 / peaks["bf16_tflops"]}
     dyc = rn(Nb, 256, 28, 28)
     gxc, gwc, gbc = torch.empty_like(x), torch.empty_like(w), torch.empty(256, device="cuda")
-    ms_dx = maxr(time_gpu(lambda: F.binary_weight_convolution_backward(
+    e3["ms_backward_dx"] = maxr(time_gpu(lambda: F.binary_weight_convolution_backward(
         x, wb, al, dyc, 1, (1, 1), (1, 1), propagate_down=(True, False, False), grads=(gxc, None, None)), 10))
-    ms_dw = maxr(time_gpu(lambda: F.binary_weight_convolution_backward(
+    e3["ms_backward_dw_db"] = maxr(time_gpu(lambda: F.binary_weight_convolution_backward(
         x, wb, al, dyc, 1, (1, 1), (1, 1), propagate_down=(False, True, True), grads=(None, gwc, gbc)), 10))
-    out["configs[3] backward (dx | dw + db), batch %d" % (Nb * world)] = {
-        "ms_dx": ms_dx, "ms_dw_db": ms_dw, "tflops_algorithmic_dx_whole_job": flops / ms_dx / 1e9,
-        "tflops_algorithmic_dw_whole_job": flops / ms_dw / 1e9,
-        "includes": "operand re-layout (stuffing / batch-innermost transposes, bf16 pieces) + implicit GEMM"}
+    out["configs[3] binary_weight_convolution 3x3 256->256 28x28 batch %d" % (Nb * world)] = e3
     del x, w, dyc, gxc
-    # data-parallel gradient all-reduce of the ResNet-18 parameter set through the communicator (N > 1 only)
-    if world > 1:
-        from nnabla_b200 import communicators
-        comm = communicators.MultiProcessDataParallelCommunicator()
-        comm.init()
-        shapes = [tuple(v.shape) for v in resnet18.init_parameters(np.random.RandomState(0)).values()]
-        grads = [torch.ones(sh, device="cuda") for sh in shapes]
-        n_par = sum(g.numel() for g in grads)
-        cb = comm.all_reduce_callback(grads, pack_size=8 << 20, division=True)
-        ms_ar = maxr(time_gpu(cb, 10))
-        out["gradient all-reduce, ResNet-18 parameters"] = {
-            "ms": ms_ar, "parameters": n_par, "arrays": len(grads), "bucket_values": 8 << 20,
-            "bus_GBps": 2 * (world - 1) / world * n_par * 4 / ms_ar / 1e6,
-            "correct": bool(all(torch.allclose(g, torch.ones_like(g)) for g in grads))}
-    # configs[4]: binary-weight ResNet-18, batch sharded over the ranks
-    B = args.resnet_batch
-    Bg = max(1, B // world)
-    params = {k: torch.from_numpy(v).cuda() for k, v in resnet18.init_parameters(np.random.RandomState(0)).items()}
-    x = rn(Bg, 3, 224, 224)
-    gz = lambda t, shape=None: torch.zeros(shape or tuple(t.shape), device="cuda")
-    net = resnet18.Runner(F, params, gz)
-    ms = maxr(time_gpu(lambda: net(x), 5, warm=2))
-    F.check_device_status()
-    net_fused = resnet18.Runner(F, params, gz, fused=True)
-    ms_fused = maxr(time_gpu(lambda: net_fused(x), 5, warm=2))
-    F.check_device_status()
-    net_codes = resnet18.Runner(F, params, gz, fused="codes")
-    ms_codes = maxr(time_gpu(lambda: net_codes(x), 5, warm=2))
-    F.check_device_status()
-    same = bool(torch.equal(net_codes(x), net(x)))
-    net_prep = resnet18.Runner(F, params, gz, fused="codes", prepared_weights=True)
-    ms_prep = maxr(time_gpu(lambda: net_prep(x), 5, warm=2))
-    F.check_device_status()
-    same = same and bool(torch.equal(net_prep(x), net(x)))
-    # the same forward captured once as a CUDA graph and replayed (one launch instead of about 130 calls)
-    from nnabla_b200 import graphs
-    graph_note = "the int8-activations forward with prepared weights, captured once and replayed"
-    try:
-        captured = graphs.Captured(net_prep, x)
-        ms_graph = time_gpu(lambda: captured(x), 5, warm=2)
-        same = same and bool(torch.equal(captured(x), net(x)))
-    except RuntimeError as e:  # a capture that another thread's CUDA call interrupted: report, do not fail the run
-        ms_graph, graph_note = ms_prep, "capture failed (%s): eager time reported" % str(e)[:80]
-    ms_graph = maxr(ms_graph)
-    F.check_device_status()
-    out["configs[4] binary-weight ResNet-18 224x224"] = {
-        "ms_per_batch": ms, "images_per_sec_whole_job": Bg * world / ms * 1e3, "batch_per_gpu": Bg,
-        "gmac_per_image": resnet18.conv_macs_per_image() / 1e9,
-        "ms_per_batch_fused_activations": ms_fused,
-        "images_per_sec_whole_job_fused_activations": Bg * world / ms_fused * 1e3,
-        "fused": "BN (+ residual) + ReLU + FixedPointQuantize as one pass, bit-identical logits",
-        "ms_per_batch_int8_activations": ms_codes,
-        "images_per_sec_whole_job_int8_activations": Bg * world / ms_codes * 1e3,
-        "int8_activations": "the fused pass writes int8 channel-last codes that the next convolution reads directly "
-                            "(1 byte per activation between layers, residual = code * delta)",
-        "ms_per_batch_int8_activations_prepared_weights": ms_prep,
-        "images_per_sec_whole_job_int8_activations_prepared_weights": Bg * world / ms_prep * 1e3,
-        "ms_per_batch_cuda_graph": ms_graph,
-        "images_per_sec_whole_job_cuda_graph": Bg * world / ms_graph * 1e3,
-        "cuda_graph": graph_note,
-        "prepared_weights": "weights binarised once (inference: they do not change between calls) instead of in "
-                            "every forward pass as the reference's forward_impl does",
-        "int8_activations_logits_equal_unfused": same}
+    torch.cuda.empty_cache()
     return out
 
 
@@ -459,6 +487,7 @@ def run_b200_arm(args):
     import torch.distributed as dist
     from nnabla_b200 import _capi as C
     from nnabla_b200 import functions as F
+    from nnabla_b200 import graphs, resnet18
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -473,139 +502,184 @@ def run_b200_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def maxr(v):
+        if world > 1:
+            t = torch.tensor([v], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return v
+
+    peaks, peak_kind = measured_peaks()
+    int8 = measure_int8_peak(0.5 if args.small_extras else 2.0)
+    int8_peak = int8["int8_tops"]
+
     if args.only_extras:
-        extras = run_extras(args, rank, world, barrier)
+        extras = run_extras(args, rank, world, peaks, int8_peak)
         if rank == 0:
-            print(json.dumps({"other_configs": extras}))
+            print(json.dumps(round_floats({"measured_int8_peak": int8, "other_configs": extras})))
         if world > 1:
             dist.destroy_process_group()
         return
 
-    n = 1 << args.size_log2
-    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    x = torch.rand(n, device="cuda", generator=gen) * 8 - 4
-    y = torch.empty_like(x)
-    one = lambda v: torch.tensor([v], device="cuda", dtype=torch.float32)
-    qr_min, qr_max, ql_min, ql_max = one(-4.0), one(4.0), one(0.0), one(255.0)
+    assert args.batch % world == 0, "the batch must divide over the GPUs"
+    Bg = args.batch // world
+    params = {k: torch.from_numpy(v).cuda() for k, v in resnet18.init_parameters(np.random.RandomState(0)).items()}
+    # this rank's images of the seeded batch, in pinned host memory
+    hx = torch.from_numpy(np.random.RandomState(1000 + rank).randn(Bg, *IMAGE).astype(np.float32)).pin_memory()
+    x = hx.cuda()
+    gz = lambda t, shape=None: torch.zeros(shape or tuple(t.shape), device="cuda")
+    net = resnet18.Runner(F, params, gz)
 
-    def step(events=None):
-        if events:
-            events[0].record()
-        F.fixed_point_quantize(x, True, 8, 2.0 ** -4, outputs=[y])
-        if events:
-            events[1].record()
-        F.pow2_quantize(x, True, True, 8, 1, outputs=[y])
-        if events:
-            events[2].record()
-        F.min_max_quantize(x, qr_min, qr_max, ql_min, ql_max, outputs=[y])
-        if events:
-            events[3].record()
-
-    for _ in range(max(args.warmup, 3)):
-        step()
+    # ---- the timed region: K forward passes of the graph as written ------------------------
+    W = max(args.warmup, 3)
+    for _ in range(W):
+        net(x)
+    F.check_device_status()
     barrier()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     sampler = ClockSampler(local) if rank == 0 else None
     barrier()
-    t_start = torch.cuda.Event(enable_timing=True)
-    t_end = torch.cuda.Event(enable_timing=True)
+    calls0 = C.calls_made()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
-    for s in range(args.steps):
-        step(ev[s])
+    for _ in range(args.steps):
+        logits = net(x)
     t_end.record()
     barrier()
     clocks = sampler.stop() if sampler else None
-    elapsed_ms = t_start.elapsed_time(t_end)
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-    per_kernel_ms = [statistics.mean(ev[s][k].elapsed_time(ev[s][k + 1]) for s in range(args.steps))
-                     for k in range(3)]
+    calls = C.calls_made() - calls0
+    elapsed_ms = maxr(t_start.elapsed_time(t_end))
+    F.check_device_status()
+    value = args.batch * args.steps / (elapsed_ms / 1e3)
+    finite = bool(torch.isfinite(logits).all())
 
-    # ---- end to end through the host-buffer entry points -------------------
+    # ---- end to end: pinned host images in, logits out, every step -------------------------
     e2e = None
-    try:
-        if args.no_e2e:
-            raise RuntimeError("skipped by --no-e2e")
-        hx = torch.empty(n, dtype=torch.float32, pin_memory=True)
-        hy = torch.empty(n, dtype=torch.float32, pin_memory=True)
-        hx.copy_(x)
-        hq = np.array([-4.0, 4.0, 0.0, 255.0], np.float32)
+    if not args.no_e2e:
+        copy_stream = torch.cuda.Stream()
+        xin = [torch.empty_like(x), torch.empty_like(x)]
+        hy = [torch.empty(Bg, CLASSES, dtype=torch.float32).pin_memory() for _ in range(2)]
+        main = torch.cuda.current_stream()
 
-        def e2e_step():
-            C.call("nb200_fixed_point_quantize_f32_host", C.ptr(hx), C.ptr(hy), C.size_t(n), 1, 8,
-                   C.c_float(2.0 ** -4))
-            C.call("nb200_pow2_quantize_f32_host", C.ptr(hx), C.ptr(hy), C.size_t(n), 1, 1, 8, 1)
-            C.call("nb200_min_max_quantize_f32_host", C.ptr(hx), C.size_t(n), C.ptr(hq[0:]), C.ptr(hq[1:]),
-                   C.ptr(hq[2:]), C.ptr(hq[3:]), C.c_float(0.01), C.ptr(hy))
-
-        e2e_step()
+        def e2e_run(steps):
+            done = [None, None]
+            for s in range(steps):
+                k = s & 1
+                with torch.cuda.stream(copy_stream):
+                    if done[k] is not None:
+                        copy_stream.wait_event(done[k])  # the buffer's previous step has finished with it
+                    xin[k].copy_(hx, non_blocking=True)
+                    ready = torch.cuda.Event()
+                    ready.record(copy_stream)
+                main.wait_event(ready)
+                y = net(xin[k])
+                hy[k].copy_(y, non_blocking=True)
+                done[k] = torch.cuda.Event()
+                done[k].record(main)
+            torch.cuda.synchronize()
+        e2e_run(2)
         barrier()
         t0 = time.perf_counter()
-        for _ in range(args.e2e_steps):
-            e2e_step()
+        e2e_run(args.steps)
         barrier()
-        e2e_s = time.perf_counter() - t0
-        if world > 1:
-            t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_s = float(t.item())
-        e2e = {"value": world * 3 * BYTES_PER_ELEM * n * args.e2e_steps / e2e_s / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": 3 * 4 * n, "d2h_bytes_per_step": 3 * 4 * n, "steps": args.e2e_steps,
-               "api": "nb200_*_quantize_f32_host (pinned host buffers)"}
-        del hx, hy
-    except RuntimeError as exc:  # pinned allocation failure: report, do not fake
-        e2e = {"value": None, "unit": "GB/s", "error": str(exc)[:200]}
+        e2e_s = maxr(time.perf_counter() - t0)
+        e2e = {"value": args.batch * args.steps / e2e_s, "unit": "images/s",
+               "h2d_bytes_per_step": world * Bg * int(np.prod(IMAGE)) * 4, "d2h_bytes_per_step": world * Bg * CLASSES * 4,
+               "steps": args.steps, "ms_per_step": 1e3 * e2e_s / args.steps,
+               "api": "resnet18.Runner over nnabla_b200.functions; pinned host images -> device (copy of step s+1 "
+                      "overlaps the forward of step s) -> logits to pinned host memory"}
+        del xin
 
-    del x, y
+    # ---- the other execution forms of the same graph ---------------------------------------
+    forms = None
+    if not args.no_forms:
+        forms = {"as_written_ms": elapsed_ms / args.steps}
+        same = True
+
+        def form(key, runner, iters=5):
+            nonlocal same
+            ms = maxr(time_gpu(lambda: runner(x), iters, warm=2))
+            F.check_device_status()
+            forms[key + "_ms"] = ms
+            forms[key + "_images_per_sec"] = args.batch / ms * 1e3
+            return runner
+        same_as = lambda r: bool(torch.equal(r(x), logits))
+        same &= same_as(form("fused_activation_pass", resnet18.Runner(F, params, gz, fused=True)))
+        same &= same_as(form("int8_codes_between_layers", resnet18.Runner(F, params, gz, fused="codes")))
+        prep = form("int8_codes_prepared_weights", resnet18.Runner(F, params, gz, fused="codes", prepared_weights=True))
+        same &= same_as(prep)
+        try:
+            captured = graphs.Captured(prep, x)
+            same &= same_as(form("cuda_graph_replay", captured))
+            del captured
+        except RuntimeError as e:  # a capture another thread's CUDA call interrupted: report, do not fail the run
+            forms["cuda_graph_replay_ms"] = None
+        if hasattr(resnet18, "FoldedRunner"):
+            folded = resnet18.FoldedRunner(F, params)
+            form("bn_folded_int8_epilogue", folded)
+            fl = folded(x)
+            forms["bn_folded_logits_rel_rms_vs_as_written"] = float(
+                ((fl - logits).double().pow(2).mean() / logits.double().pow(2).mean()).sqrt())
+            forms["bn_folded_top1_agreement"] = float((fl.argmax(1) == logits.argmax(1)).float().mean())
+        # the same graph through nnabla's own graph engine with the extension backend: built with
+        # CgVariable / CgFunction / connect(), run by CgVariable::forward(clear_buffer=true) on "b200:float"
+        from nnabla_b200 import nbla_graph
+        if nbla_graph.available():
+            hostp = {k: v.cpu().numpy() for k, v in params.items()}
+            g = nbla_graph.Graph("b200:float", str(local))
+            xv = g.variable(hx.numpy())
+            cz = lambda w, shape=None: np.zeros(shape or w.shape, np.float32)
+            yv = resnet18.Runner(g, hostp, cz, None, fixed_point_hint=False)(xv)
+            g.forward(yv, clear_buffer=True, repeat=2)
+            nbla_graph.reset_counters()
+            sec = maxr(g.forward(yv, clear_buffer=True, repeat=5))
+            forms["nnabla_graph_engine_b200_context_ms"] = 1e3 * sec
+            forms["nnabla_graph_engine_b200_context_images_per_sec"] = args.batch / sec
+            forms["nnabla_graph_engine_int8_convolutions_per_pass"] = nbla_graph.counter("int8_convolutions") / 5
+            same &= bool(np.array_equal(g.data(yv), logits.cpu().numpy()))
+            g.close()
+            nbla_graph.clear_memory_cache()
+            torch.cuda.set_device(local)
+        flag = torch.tensor([int(same)], device="cuda")
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        forms["bit_identical_logits_all_forms"] = bool(flag.item())
+
+    # ---- per-function table and the roofline entry -----------------------------------------
+    table, roofline = function_table(F, params, gz, x, peaks, int8_peak)
+    roofline["peak_source"] = peak_kind if roofline["unit"] != "TOP/s" else "measured in this run (torch._int_mm 8192^3)"
+
+    del x, logits
     torch.cuda.empty_cache()
     extras = None
     if not args.no_extras:
-        extras = run_extras(args, rank, world, barrier)
+        extras = run_extras(args, rank, world, peaks, int8_peak)
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    peaks, peak_kind = measured_peaks()
-    value = world * 3 * BYTES_PER_ELEM * n * args.steps / (elapsed_ms / 1e3) / 1e9
-    k_dom = int(np.argmax(per_kernel_ms))
-    achieved = BYTES_PER_ELEM * n / (per_kernel_ms[k_dom] / 1e3) / 1e9
-    # DRAM traffic per element of the dominant kernel from the committed ncu capture at 2^26 elements
-    # (profiles/quantizers_2p26_full_capture.md), scaled to this launch: traffic grows with the element count.
-    ncu_bytes_per_elem = {"fixed_point_quantize": 485.1e6 / 2 ** 26, "pow2_quantize": 485.4e6 / 2 ** 26,
-                          "min_max_quantize": 486.9e6 / 2 ** 26}
-    roofline = {"bound": "hbm", "kernel": QUANTIZERS[k_dom], "achieved": achieved, "peak": peaks["hbm_gbs"],
-                "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                "traffic": ncu_bytes_per_elem[QUANTIZERS[k_dom]] * n, "traffic_unit": "bytes per launch",
-                "algorithmic_bytes_per_launch": BYTES_PER_ELEM * n,
-                "per_kernel_GBps": {QUANTIZERS[k]: BYTES_PER_ELEM * n / (per_kernel_ms[k] / 1e3) / 1e9
-                                    for k in range(3)}}
     cpu_baseline = None
     if not args.no_cpu_baseline:
-        kind, fns = cpu_functions()
-        slices, ncpu = cpu_inputs(1)
-        secs = {name: fns[name](slices[0]) for name in QUANTIZERS}
-        cpu_baseline = {"value": 3 * BYTES_PER_ELEM * ncpu / sum(secs.values()) / 1e9, "unit": "GB/s", "cores": 1,
-                        "kind": kind, "sample": "3 quantizers over 2^%d elements, 1 thread" % CPU_SAMPLE_LOG2,
-                        "per_function_GBps": {k: BYTES_PER_ELEM * ncpu / v / 1e9 for k, v in secs.items()}}
-        if not args.no_extras and rank == 0:
-            cpu_baseline["other_configs"] = cpu_contraction_samples()
+        n_img = 4
+        kind, ips, dt = cpu_images_per_second(n_img, 1)
+        cpu_baseline = {"value": ips, "unit": "images/s", "cores": 1, "kind": kind,
+                        "sample": "%d images of the batch, whole network per image, 1 thread (%.1f s)" % (n_img, dt)}
     line = {
-        "metric": "quantizer_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[1]: FixedPointQuantize(sign,n=8,delta=2^-4) + Pow2Quantize(sign,with_zero,"
-                               "n=8,m=1) + MinMaxQuantize(0..255, range -4..4) on fp32 U(-4,4), 2^%d elements per GPU"
-                               % args.size_log2,
-                   "elements_per_gpu": n, "l2": "inputs (4 GiB) larger than L2; no flush needed"},
-        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
-        "gpu_launches": 4 * args.steps,
         "other_configs": extras,
+        "measured_int8_peak": int8,
+        "functions": table,
+        "forms": forms,
+        "metric": "resnet18_images_per_sec", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+        "warmup": W, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": dict(workload_config(args.batch, world),
+                       l2="per-step activations (over 800 MB at 256 images) exceed L2; no flush needed"),
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": calls, "gpu_launches_note": "C-ABI calls in the timed region; each launches 1 to 4 kernels",
+        "logits_finite": finite,
     }
-    print(json.dumps(line))
+    print(json.dumps(round_floats(line)))
     if world > 1:
         dist.destroy_process_group()
 

@@ -34,6 +34,23 @@ Context b200_context(const string &device_id = "0");
     nb200_last_error()). */
 void nb200_check(int status, const char *what);
 
+/** Makes the context's device current and returns the stream every function,
+    copy and fill of this backend is enqueued on for that device: one
+    non-blocking stream per device, created at first use, never the legacy
+    default stream. It is shared by the host threads that use the device on
+    purpose: the caching allocator is shared by them too and hands a block that
+    one thread released to the next thread that asks, with no record of the
+    work still queued on it, so that work and the new owner's must be ordered
+    by one stream. */
+void *b200_stream(const string &device_id);
+
+/** Counters of the paths the functions took since the last reset, by name:
+    "int8_convolutions", "bf16_convolutions", "int8_affines",
+    "weight_cache_hits", "weight_cache_misses". Unknown names read 0. */
+long long b200_counter(const string &name);
+void b200_count(const char *name);
+void b200_reset_counters();
+
 /** Device memory block (cudaMalloc through nb200_malloc). Same contract as
     CpuMemory (src/nbla/memory/cpu_memory.cpp:31-80). */
 class B200Memory : public Memory {
@@ -96,6 +113,17 @@ public:
     (include/nbla/synced_array.hpp:183), so any later write invalidates a tag. */
 void fxp_tag_set(const Variable *v, float delta);
 float fxp_tag_get(const Variable *v); // 0 when untagged or stale
+
+/** Identity of the current contents of a variable's data: the SyncedArray and
+    its modification count (include/nbla/synced_array.hpp:183). Two equal
+    stamps of a live array mean nothing wrote to it in between. */
+struct DataStamp {
+  const SyncedArray *array = nullptr;
+  size_t count = 0;
+  bool operator==(const DataStamp &o) const { return array == o.array && count == o.count; }
+  bool operator!=(const DataStamp &o) const { return !(*this == o); }
+};
+DataStamp data_stamp(const Variable *v);
 
 } // namespace nbla
 #endif

@@ -10,8 +10,9 @@ nnabla.utils.profiler.GraphProfiler and the function benchmark harness call.
 
 It needs the nnabla Python package (Cython bindings over libnnabla), which
 cannot be built without nnabla's code generator; until then the same classes
-are driven through ext/src/ext_capi.cpp (see tests/test_ext_gpu.py). The
-native entry points used below are those of ext/_build/libnnabla_ext_b200.so.
+are driven through the C binding of ext/runner (nnabla_b200/nbla_graph.py,
+tests/test_ext_gpu.py). The native entry points used below are those of
+ext/_build/libnnabla_ext_b200.so.
 """
 import ctypes
 import os
@@ -21,9 +22,10 @@ import nnabla as nn  # noqa: F401  (the host package; absent in this build envir
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _lib = ctypes.CDLL(os.environ.get("NNABLA_EXT_B200_LIB", os.path.join(_HERE, "libnnabla_ext_b200.so")),
                    mode=ctypes.RTLD_GLOBAL)
-_lib.nbext_last_error.restype = ctypes.c_char_p
-if _lib.nbext_init() != 0:
-    raise ImportError("nnabla_ext.b200: " + _lib.nbext_last_error().decode())
+_lib.nnabla_ext_b200_last_error.restype = ctypes.c_char_p
+if _lib.nnabla_ext_b200_init() != 0:
+    raise ImportError("nnabla_ext.b200: " + _lib.nnabla_ext_b200_last_error().decode())
+_nb200_lib = None
 
 
 def array_classes():
@@ -39,8 +41,8 @@ def context(device_id="0", type_config="float", **kw):
 
 
 def device_synchronize(device_id="0", **kw):
-    _nb200().nb200_set_device(int(device_id))
-    _nb200().nb200_device_synchronize()
+    if _lib.nnabla_ext_b200_device_synchronize(int(device_id)) != 0:
+        raise RuntimeError(_lib.nnabla_ext_b200_last_error().decode())
 
 
 def synchronize(device_id="0", **kw):
@@ -48,7 +50,9 @@ def synchronize(device_id="0", **kw):
 
 
 def clear_memory_cache():
-    pass  # the caching allocator is owned by the native backend singleton
+    """Returns the caching allocator's unused device blocks to the driver."""
+    if _lib.nnabla_ext_b200_clear_memory_cache() != 0:
+        raise RuntimeError(_lib.nnabla_ext_b200_last_error().decode())
 
 
 def get_device_count():
@@ -62,4 +66,8 @@ def get_devices():
 
 
 def _nb200():
-    return ctypes.CDLL("libnnabla_b200.so")
+    """The C-ABI library, already mapped as a dependency of the extension library."""
+    global _nb200_lib
+    if _nb200_lib is None:
+        _nb200_lib = ctypes.CDLL(os.environ.get("NNABLA_B200_LIB", "libnnabla_b200.so"))
+    return _nb200_lib

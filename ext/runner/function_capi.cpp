@@ -1,5 +1,5 @@
-// C ABI test harness over the nnabla host library with the b200 extension
-// loaded: creates a function through nnabla's registry for a given backend
+// C binding for single functions over the nnabla host library with the b200
+// extension loaded: creates a function through nnabla's registry for a given backend
 // ("cpu:float" or "b200:float"), feeds it from host buffers through
 // nnabla's own Variable / SyncedArray machinery (so device arrays, the
 // allocator and the synchronizers of the extension are exercised), runs
@@ -41,59 +41,11 @@
 
 using namespace nbla;
 
+#include "create_function.hpp"
+
 namespace {
 thread_local std::string g_err;
-
-FunctionPtr create(const std::string &name, const Context &ctx, const double *s, int n_s,
-                   const std::vector<std::vector<int>> &ivs) {
-  auto S = [&](int i) -> double {
-    NBLA_CHECK(i < n_s, error_code::value, "missing scalar argument %d", i);
-    return s[i];
-  };
-  auto V = [&](size_t i) -> const std::vector<int> & {
-    NBLA_CHECK(i < ivs.size(), error_code::value, "missing vector argument %d", (int)i);
-    return ivs[i];
-  };
-  if (name == "FixedPointQuantize")
-    return create_FixedPointQuantize(ctx, S(0) != 0, (int)S(1), (float)S(2), S(3) != 0);
-  if (name == "Pow2Quantize")
-    return create_Pow2Quantize(ctx, S(0) != 0, S(1) != 0, (int)S(2), (int)S(3), S(4) != 0);
-  if (name == "MinMaxQuantize")
-    return create_MinMaxQuantize(ctx, (float)S(0), S(1) != 0, S(2) != 0, S(3) != 0, (float)S(4));
-  if (name == "BinaryWeightAffine")
-    return create_BinaryWeightAffine(ctx, (int)S(0), (float)S(1));
-  if (name == "BinaryConnectAffine")
-    return create_BinaryConnectAffine(ctx, (int)S(0), (float)S(1));
-  if (name == "BinaryWeightConvolution")
-    return create_BinaryWeightConvolution(ctx, (int)S(0), V(0), V(1), V(2), (int)S(1), (float)S(2));
-  if (name == "BinaryConnectConvolution")
-    return create_BinaryConnectConvolution(ctx, (int)S(0), V(0), V(1), V(2), (int)S(1), (float)S(2));
-  if (name == "Affine")
-    return create_Affine(ctx, (int)S(0));
-  if (name == "Convolution")
-    return create_Convolution(ctx, (int)S(0), V(0), V(1), V(2), (int)S(1), S(2) != 0);
-  if (name == "BatchNormalization")
-    return create_BatchNormalization(ctx, V(0), (float)S(0), (float)S(1), S(2) != 0, S(3) != 0, S(4) != 0);
-  if (name == "ReLU")
-    return create_ReLU(ctx, S(0) != 0);
-  if (name == "MaxPooling")
-    return create_MaxPooling(ctx, V(0), V(1), S(0) != 0, V(2), S(1) != 0);
-  if (name == "GlobalAveragePooling")
-    return create_GlobalAveragePooling(ctx);
-  if (name == "Add2")
-    return create_Add2(ctx, S(0) != 0);
-  if (name == "BinarySigmoid")
-    return create_BinarySigmoid(ctx);
-  if (name == "BinaryTanh")
-    return create_BinaryTanh(ctx);
-  if (name == "QuantizeLinear") // scalars: round mode (0 = HALF_AWAY_FROM_ZERO, 1 = HALF_TO_EVEN), narrow_range, dtype
-    return create_QuantizeLinear(ctx, S(0) != 0 ? "HALF_TO_EVEN" : "HALF_AWAY_FROM_ZERO", S(1) != 0, (int)S(2));
-  if (name == "DequantizeLinear")
-    return create_DequantizeLinear(ctx);
-  if (name == "Prune")
-    return create_Prune(ctx, (float)S(0));
-  NBLA_ERROR(error_code::value, "unknown function %s", name.c_str());
-}
+using nbla_b200_runner::create_function;
 } // namespace
 
 extern "C" {
@@ -136,7 +88,7 @@ int nbext_forward(const char *backend, const char *op, const double *s, int n_s,
       ivs.emplace_back(p, p + iv_len[i]);
       p += iv_len[i];
     }
-    FunctionPtr f = create(op, ctx, s, n_s, ivs);
+    FunctionPtr f = create_function(op, ctx, s, n_s, ivs);
     if (fname && fname_len > 0) {
       std::strncpy(fname, f->name().c_str(), fname_len - 1);
       fname[fname_len - 1] = 0;
@@ -216,7 +168,7 @@ int nbext_backward(const char *backend, const char *op, const double *s, int n_s
       ivs.emplace_back(p, p + iv_len[i]);
       p += iv_len[i];
     }
-    FunctionPtr f = create(op, ctx, s, n_s, ivs);
+    FunctionPtr f = create_function(op, ctx, s, n_s, ivs);
     std::vector<VariablePtr> vin, vout;
     Variables pin, pout;
     for (int i = 0; i < n_in; ++i) {

@@ -13,6 +13,7 @@
 #include <map>
 #include <memory>
 #include <mutex>
+#include <string>
 
 namespace nbla {
 
@@ -32,6 +33,44 @@ static int device_index(const string &device_id) { return device_id.empty() ? 0 
 
 static void use_device(const string &device_id) {
   nb200_check(nb200_set_device(device_index(device_id)), "nb200_set_device");
+}
+
+void *b200_stream(const string &device_id) {
+  static std::mutex m;
+  static void *streams[64];
+  const int dev = device_index(device_id);
+  NBLA_CHECK(dev >= 0 && dev < 64, error_code::value, "device index %d out of range", dev);
+  nb200_check(nb200_set_device(dev), "nb200_set_device");
+  std::lock_guard<std::mutex> lock(m);
+  if (streams[dev] == nullptr)
+    nb200_check(nb200_stream_create(&streams[dev]), "nb200_stream_create");
+  return streams[dev];
+}
+
+namespace {
+std::mutex g_counter_mutex;
+std::map<string, long long> g_counters;
+} // namespace
+long long b200_counter(const string &name) {
+  std::lock_guard<std::mutex> lock(g_counter_mutex);
+  auto it = g_counters.find(name);
+  return it == g_counters.end() ? 0 : it->second;
+}
+void b200_count(const char *name) {
+  std::lock_guard<std::mutex> lock(g_counter_mutex);
+  ++g_counters[name];
+}
+void b200_reset_counters() {
+  std::lock_guard<std::mutex> lock(g_counter_mutex);
+  g_counters.clear();
+}
+
+DataStamp data_stamp(const Variable *v) {
+  SyncedArrayPtr a = const_cast<Variable *>(v)->data()->array();
+  DataStamp s;
+  s.array = a.get();
+  s.count = a->modification_count();
+  return s;
 }
 
 Context b200_context(const string &device_id) { return Context({"b200:float"}, "B200CachedArray", device_id); }
@@ -84,8 +123,7 @@ void B200::device_synchronize(const string &device) {
   nb200_check(nb200_device_synchronize(), "nb200_device_synchronize");
 }
 void B200::default_stream_synchronize(const string &device) {
-  use_device(device);
-  nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+  nb200_check(nb200_stream_synchronize(b200_stream(device)), "nb200_stream_synchronize");
 }
 void B200::create_lms_streams(int device) {}
 
@@ -104,34 +142,48 @@ B200Array::~B200Array() {}
 Context B200Array::filter_context(const Context &ctx) { return Context({}, "B200Array", ctx.device_id); }
 
 void B200Array::zero() {
-  use_device(this->ctx_.device_id);
-  nb200_check(nb200_memset_zero(this->pointer<void>(), Array::size_as_bytes(this->size_, this->dtype_), nullptr),
+  void *st = b200_stream(this->ctx_.device_id);
+  nb200_check(nb200_memset_zero(this->pointer<void>(), Array::size_as_bytes(this->size_, this->dtype_), st),
               "nb200_memset_zero");
 }
 
 void B200Array::fill(float value) {
-  use_device(this->ctx_.device_id);
+  void *st = b200_stream(this->ctx_.device_id);
   if (this->dtype_ == dtypes::FLOAT) {
-    nb200_check(nb200_fill_f32(this->pointer<float>(), this->size_, value, nullptr), "nb200_fill_f32");
+    nb200_check(nb200_fill_f32(this->pointer<float>(), this->size_, value, st), "nb200_fill_f32");
     return;
   }
   // Other element types: fill on the host with the reference's own typed fill, then upload.
   CpuArray host(this->size_, this->dtype_, Context({"cpu:float"}, "CpuArray", ""));
   host.fill(value);
   nb200_check(nb200_memcpy_h2d(this->pointer<void>(), host.const_pointer<void>(),
-                               Array::size_as_bytes(this->size_, this->dtype_), nullptr),
+                               Array::size_as_bytes(this->size_, this->dtype_), st),
               "nb200_memcpy_h2d");
-  nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+  nb200_check(nb200_stream_synchronize(st), "nb200_stream_synchronize"); // `host` goes away on return
 }
 
 void B200Array::copy_from(const Array *src) {
   NBLA_CHECK(src->size() == this->size_, error_code::unclassified, "Size mismatch.");
-  NBLA_CHECK(src->dtype() == this->dtype_, error_code::not_implemented,
-             "device-to-device copy with a dtype conversion is not implemented");
-  use_device(this->ctx_.device_id);
-  nb200_check(nb200_memcpy_d2d(this->pointer<void>(), src->const_pointer<void>(),
-                               Array::size_as_bytes(this->size_, this->dtype_), nullptr),
-              "nb200_memcpy_d2d");
+  void *st = b200_stream(this->ctx_.device_id);
+  if (src->dtype() == this->dtype_) {
+    nb200_check(nb200_memcpy_d2d(this->pointer<void>(), src->const_pointer<void>(),
+                                 Array::size_as_bytes(this->size_, this->dtype_), st),
+                "nb200_memcpy_d2d");
+    return;
+  }
+  // A copy that changes the element type (the reference's arrays convert through the 15 x 15
+  // switch of include/nbla/array.hpp): down to the host, the reference's own typed copy, up again.
+  const Context cpu({"cpu:float"}, "CpuArray", "");
+  CpuArray from(src->size(), src->dtype(), cpu), to(this->size_, this->dtype_, cpu);
+  nb200_check(nb200_memcpy_d2h(from.pointer<void>(), src->const_pointer<void>(),
+                               Array::size_as_bytes(src->size(), src->dtype()), st),
+              "nb200_memcpy_d2h");
+  nb200_check(nb200_stream_synchronize(st), "nb200_stream_synchronize");
+  to.copy_from(&from);
+  nb200_check(nb200_memcpy_h2d(this->pointer<void>(), to.const_pointer<void>(),
+                               Array::size_as_bytes(this->size_, this->dtype_), st),
+              "nb200_memcpy_h2d");
+  nb200_check(nb200_stream_synchronize(st), "nb200_stream_synchronize");
 }
 
 B200CachedArray::B200CachedArray(const Size_t size, dtypes dtype, const Context &ctx, const AllocatorMemoryPtr mem,
@@ -156,27 +208,31 @@ void synchronizer_cpu_to_b200(Array *src, Array *dst, const int async_flags) {
     converted->copy_from(src);
     host = converted.get();
   }
-  use_device(dst->context().device_id);
+  void *st = b200_stream(dst->context().device_id);
   nb200_check(nb200_memcpy_h2d(dst->pointer<void>(), host->const_pointer<void>(),
-                               bytes_of(dst->size(), dst->dtype()), nullptr),
+                               bytes_of(dst->size(), dst->dtype()), st),
               "nb200_memcpy_h2d");
-  nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+  // AsyncFlag::ASYNC (include/nbla/common.hpp:45): the caller orders later work itself and keeps the
+  // source alive. A converted staging copy lives only until return, so that case always waits.
+  if (!(async_flags & AsyncFlag::ASYNC) || converted)
+    nb200_check(nb200_stream_synchronize(st), "nb200_stream_synchronize");
 }
 
 void synchronizer_b200_to_cpu(Array *src, Array *dst, const int async_flags) {
-  use_device(src->context().device_id);
+  void *st = b200_stream(src->context().device_id);
   if (src->dtype() == dst->dtype()) {
     nb200_check(nb200_memcpy_d2h(dst->pointer<void>(), src->const_pointer<void>(),
-                                 bytes_of(src->size(), src->dtype()), nullptr),
+                                 bytes_of(src->size(), src->dtype()), st),
                 "nb200_memcpy_d2h");
-    nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+    if (!(async_flags & AsyncFlag::ASYNC))
+      nb200_check(nb200_stream_synchronize(st), "nb200_stream_synchronize");
     return;
   }
   CpuArray staged(src->size(), src->dtype(), Context({"cpu:float"}, "CpuArray", ""));
   nb200_check(nb200_memcpy_d2h(staged.pointer<void>(), src->const_pointer<void>(),
-                               bytes_of(src->size(), src->dtype()), nullptr),
+                               bytes_of(src->size(), src->dtype()), st),
               "nb200_memcpy_d2h");
-  nb200_check(nb200_stream_synchronize(nullptr), "nb200_stream_synchronize");
+  nb200_check(nb200_stream_synchronize(st), "nb200_stream_synchronize");
   dst->copy_from(&staged);
 }
 
@@ -214,3 +270,39 @@ float fxp_tag_get(const Variable *v) {
 }
 
 } // namespace nbla
+
+// ---- C entry points for the extension's Python package -------------------------
+// (ext/python/nnabla_ext/b200/__init__.py loads this library with ctypes)
+extern "C" {
+static thread_local std::string g_ext_error;
+const char *nnabla_ext_b200_last_error() { return g_ext_error.c_str(); }
+int nnabla_ext_b200_init() {
+  try {
+    nbla::init_b200();
+    return 0;
+  } catch (const std::exception &e) {
+    g_ext_error = e.what();
+    return 1;
+  }
+}
+// clear_memory_cache() of an extension package (python/src/nnabla_ext/cpu/__init__.py:17-45):
+// returns the caching allocator's unused blocks to the device.
+int nnabla_ext_b200_clear_memory_cache() {
+  try {
+    nbla::SingletonManager::get<nbla::B200>()->caching_allocator()->free_unused_caches();
+    return 0;
+  } catch (const std::exception &e) {
+    g_ext_error = e.what();
+    return 1;
+  }
+}
+int nnabla_ext_b200_device_synchronize(int device) {
+  try {
+    nbla::SingletonManager::get<nbla::B200>()->device_synchronize(std::to_string(device));
+    return 0;
+  } catch (const std::exception &e) {
+    g_ext_error = e.what();
+    return 1;
+  }
+}
+}

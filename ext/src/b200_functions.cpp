@@ -36,6 +36,7 @@
 #include <nbla/function/pow2_quantize.hpp>
 #include <nbla/function/relu.hpp>
 #include <nbla/function_registry.hpp>
+#include <nbla/nd_array.hpp>
 #include <nbla/utils/axis_utils.hpp>
 
 #include <nnabla_b200.h>
@@ -51,9 +52,8 @@ namespace {
 
 vector<string> device_array_classes() { return SingletonManager::get<B200>()->array_classes(); }
 
-void enter(const Context &ctx) {
-  nb200_check(nb200_set_device(ctx.device_id.empty() ? 0 : std::stoi(ctx.device_id)), "nb200_set_device");
-}
+// Makes the context's device current; returns the stream the function enqueues its work on.
+void *enter(const Context &ctx) { return b200_stream(ctx.device_id); }
 
 #define B200_NO_BACKWARD(NAME)                                                                                  \
   virtual void backward_impl(const Variables &, const Variables &, const vector<bool> &, const vector<bool> &) { \
@@ -166,10 +166,10 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_);
     float *y = wr(out[0], this->ctx_);
-    nb200_check(nb200_fixed_point_quantize_f32(x, y, in[0]->size(), this->sign_, this->n_, this->delta_, nullptr),
+    nb200_check(nb200_fixed_point_quantize_f32(x, y, in[0]->size(), this->sign_, this->n_, this->delta_, st),
                 "FixedPointQuantize");
     if ((this->sign_ ? this->n_ - 1 : this->n_) <= 7)
       fxp_tag_set(out[0], this->delta_);
@@ -179,12 +179,12 @@ protected:
                              const vector<bool> &accum) {
     if (!propagate_down[0])
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_);
     float *dx = in[0]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[0]);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     nb200_check(nb200_fixed_point_quantize_backward_f32(x, dy, dx, in[0]->size(), this->sign_, this->n_, this->delta_,
-                                                        this->ste_fine_grained_, accum[0], nullptr),
+                                                        this->ste_fine_grained_, accum[0], st),
                 "FixedPointQuantize backward");
   }
 };
@@ -196,11 +196,11 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_);
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_pow2_quantize_f32(x, y, in[0]->size(), this->sign_, this->with_zero_, this->n_, this->m_,
-                                        nullptr),
+                                        st),
                 "Pow2Quantize");
   }
   // pow2_quantize.cpp:127-156
@@ -208,12 +208,12 @@ protected:
                              const vector<bool> &accum) {
     if (!propagate_down[0])
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_);
     float *dx = in[0]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[0]);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     nb200_check(nb200_pow2_quantize_backward_f32(x, dy, dx, in[0]->size(), this->sign_, this->with_zero_, this->n_,
-                                                 this->m_, this->ste_fine_grained_, accum[0], nullptr),
+                                                 this->m_, this->ste_fine_grained_, accum[0], st),
                 "Pow2Quantize backward");
   }
 };
@@ -240,7 +240,7 @@ protected:
     this->scale_sptr_ = make_shared<Variable>(q->shape());
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const Shape_t sx = in[0]->shape(), sq = in[1]->shape();
     const float *x = rd(in[0], this->ctx_);
     float *qr_min = wr(in[1], this->ctx_, false), *qr_max = wr(in[2], this->ctx_, false);
@@ -248,7 +248,7 @@ protected:
     float *scale = wr(this->scale_sptr_.get(), this->ctx_);
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_min_max_quantize_f32(x, sx.data(), (int)sx.size(), qr_min, qr_max, ql_min, ql_max, sq.data(),
-                                           this->decay_, this->x_min_max_, this->ema_, this->eps_, y, scale, nullptr),
+                                           this->decay_, this->x_min_max_, this->ema_, this->eps_, y, scale, st),
                 "MinMaxQuantize");
   }
   // min_max_quantize.cpp:225-350
@@ -257,7 +257,7 @@ protected:
     NBLA_CHECK(!(propagate_down[3] || propagate_down[4]), error_code::value,
                "Backward to x(inputs[0]), qr_min(inputs[1]), and/or qr_max(inputs[2])"
                "are only allowed.");
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const bool ranges = !(this->x_min_max_ || this->ema_);
     const int32_t pd[3] = {propagate_down[0], ranges && propagate_down[1], ranges && propagate_down[2]};
     const int32_t ac[3] = {accum[0], accum[1], accum[2]};
@@ -273,7 +273,7 @@ protected:
     float *g_max = pd[2] ? in[2]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[2]) : nullptr;
     nb200_check(nb200_min_max_quantize_backward_f32(x, sx.data(), (int)sx.size(), qr_min, qr_max, ql_min, ql_max,
                                                     sq.data(), dy, this->x_min_max_, this->ema_,
-                                                    this->ste_fine_grained_, pd, ac, dx, g_min, g_max, nullptr),
+                                                    this->ste_fine_grained_, pd, ac, dx, g_min, g_max, st),
                 "MinMaxQuantize backward");
   }
 };
@@ -286,18 +286,18 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
-    nb200_check(nb200_binary_sigmoid_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), nullptr),
+    void *st = enter(this->ctx_);
+    nb200_check(nb200_binary_sigmoid_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), st),
                 "BinarySigmoid");
   }
   virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
                              const vector<bool> &accum) {
     if (!pd[0])
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_), *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     nb200_check(nb200_binary_sigmoid_backward_f32(x, dy, grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(),
-                                                  accum[0], nullptr),
+                                                  accum[0], st),
                 "BinarySigmoid backward");
   }
 };
@@ -309,18 +309,18 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
-    nb200_check(nb200_binary_tanh_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), nullptr),
+    void *st = enter(this->ctx_);
+    nb200_check(nb200_binary_tanh_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), st),
                 "BinaryTanh");
   }
   virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
                              const vector<bool> &accum) {
     if (!pd[0])
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_), *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     nb200_check(nb200_binary_tanh_backward_f32(x, dy, grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(),
-                                               accum[0], nullptr),
+                                               accum[0], st),
                 "BinaryTanh backward");
   }
 };
@@ -332,17 +332,17 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
-    nb200_check(nb200_prune_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), this->rate_, nullptr),
+    void *st = enter(this->ctx_);
+    nb200_check(nb200_prune_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), this->rate_, st),
                 "Prune");
   }
   virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
                              const vector<bool> &accum) {
     if (!pd[0])
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     nb200_check(nb200_prune_backward_f32(out[0]->get_grad_pointer<float>(this->ctx_),
-                                         grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(), accum[0], nullptr),
+                                         grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(), accum[0], st),
                 "Prune backward");
   }
 };
@@ -368,7 +368,7 @@ public:
 protected:
   virtual void setup_impl(const Variables &in, const Variables &out) { setup_linear_shapes(in, out); }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     NBLA_CHECK(this->round_mode_ == "HALF_AWAY_FROM_ZERO" || this->round_mode_ == "HALF_TO_EVEN", error_code::value,
                "unknown round_mode %s", this->round_mode_.c_str());
     const Shape_t sx = in[0]->shape(), ss = in[1]->shape(), sz = in[2]->shape();
@@ -376,7 +376,7 @@ protected:
     float *zp = wr(in[2], this->ctx_, false);
     nb200_check(nb200_quantize_linear_f32(x, sx.data(), (int)sx.size(), scale, ss.data(), zp, sz.data(),
                                           wr(out[0], this->ctx_), this->round_mode_ == "HALF_TO_EVEN",
-                                          this->narrow_range_, this->dtype_, nullptr),
+                                          this->narrow_range_, this->dtype_, st),
                 "QuantizeLinear");
   }
   virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
@@ -385,11 +385,11 @@ protected:
       return;
     NBLA_CHECK(!pd[1], error_code::not_implemented, "Backward w.r.t. the scale is not supported now.");
     NBLA_CHECK(!pd[2], error_code::not_implemented, "Backward w.r.t. the zero point is not supported now.");
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const Shape_t sx = in[0]->shape(), ss = in[1]->shape();
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_), *scale = rd(in[1], this->ctx_);
     nb200_check(nb200_quantize_linear_backward_f32(dy, sx.data(), (int)sx.size(), scale, ss.data(),
-                                                   grad_wr(in[0], this->ctx_, true, accum[0]), accum[0], nullptr),
+                                                   grad_wr(in[0], this->ctx_, true, accum[0]), accum[0], st),
                 "QuantizeLinear backward");
   }
 };
@@ -402,11 +402,11 @@ public:
 protected:
   virtual void setup_impl(const Variables &in, const Variables &out) { setup_linear_shapes(in, out); }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const Shape_t sx = in[0]->shape(), ss = in[1]->shape(), sz = in[2]->shape();
     nb200_check(nb200_dequantize_linear_f32(rd(in[0], this->ctx_), sx.data(), (int)sx.size(), rd(in[1], this->ctx_),
                                             ss.data(), rd(in[2], this->ctx_), sz.data(), wr(out[0], this->ctx_),
-                                            nullptr),
+                                            st),
                 "DequantizeLinear");
   }
   virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
@@ -415,11 +415,11 @@ protected:
       return;
     NBLA_CHECK(!pd[1], error_code::not_implemented, "Backward w.r.t. the scale is not supported now.");
     NBLA_CHECK(!pd[2], error_code::not_implemented, "Backward w.r.t. the zero point is not supported now.");
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const Shape_t sx = in[0]->shape(), ss = in[1]->shape();
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_), *scale = rd(in[1], this->ctx_);
     nb200_check(nb200_dequantize_linear_backward_f32(dy, sx.data(), (int)sx.size(), scale, ss.data(),
-                                                     grad_wr(in[0], this->ctx_, true, accum[0]), accum[0], nullptr),
+                                                     grad_wr(in[0], this->ctx_, true, accum[0]), accum[0], st),
                 "DequantizeLinear backward");
   }
 };
@@ -442,13 +442,13 @@ protected:
     NBLA_CHECK(in[3]->size() == this->w_col_, error_code::value, "Size of alpha must be equal to output size.");
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     float *wb = wr(in[2], this->ctx_), *alpha = wr(in[3], this->ctx_);
     const float *b = in.size() == 5 ? rd(in[4], this->ctx_) : nullptr;
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_binary_weight_affine_f32(x, w, wb, alpha, b, y, rows_, this->w_row_, this->w_col_,
-                                               this->quantize_zero_to_, nullptr),
+                                               this->quantize_zero_to_, st),
                 "BinaryWeightAffine");
   }
   // binary_weight_affine.cpp:124-146; inputs [x, w, wb, alpha, b?]
@@ -457,13 +457,13 @@ protected:
     const bool has_b = in.size() == 5;
     if (!(pd[0] || pd[1] || (has_b && pd[4])))
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_), *alpha = rd(in[3], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]), *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
     float *db = has_b ? grad_wr(in[4], this->ctx_, pd[4], accum[4]) : nullptr;
     nb200_check(nb200_binary_weight_affine_backward_f32(x, wb, alpha, dy, dx, dw, db, rows_, this->w_row_,
-                                                        this->w_col_, accum[0], accum[1], has_b && accum[4], nullptr),
+                                                        this->w_col_, accum[0], accum[1], has_b && accum[4], st),
                 "BinaryWeightAffine backward");
   }
 };
@@ -481,13 +481,13 @@ protected:
     check_same_shape(in[1], in[2]);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     float *wb = wr(in[2], this->ctx_);
     const float *b = in.size() == 4 ? rd(in[3], this->ctx_) : nullptr;
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_binary_connect_affine_f32(x, w, wb, b, y, d_.rows, d_.w_row, d_.w_col, this->quantize_zero_to_,
-                                                nullptr),
+                                                st),
                 "BinaryConnectAffine");
   }
   // binary_connect_affine.cpp:73-93; inputs [x, w, wb, b?]
@@ -496,7 +496,7 @@ protected:
     const bool has_b = in.size() == 4;
     if (!(pd[0] || pd[1] || (has_b && pd[3])))
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]);
@@ -505,15 +505,15 @@ protected:
     float *dwb = grad_wr(in[2], this->ctx_, pd[1], false);
     float *db = has_b ? grad_wr(in[3], this->ctx_, pd[3], accum[3]) : nullptr;
     nb200_check(nb200_binary_connect_affine_backward_f32(x, wb, dy, dx, dwb, db, d_.rows, d_.w_row, d_.w_col, accum[0],
-                                                         0, has_b && accum[3], nullptr),
+                                                         0, has_b && accum[3], st),
                 "BinaryConnectAffine backward");
     if (pd[1]) {
       float *dw = grad_wr(in[1], this->ctx_, true, accum[1]);
       const size_t n = in[1]->size();
       if (accum[1])
-        nb200_check(nb200_add2_f32(dw, dwb, dw, n, nullptr), "BinaryConnectAffine backward (accumulate)");
+        nb200_check(nb200_add2_f32(dw, dwb, dw, n, st), "BinaryConnectAffine backward (accumulate)");
       else
-        nb200_check(nb200_memcpy_d2d(dw, dwb, n * sizeof(float), nullptr), "BinaryConnectAffine backward (copy)");
+        nb200_check(nb200_memcpy_d2d(dw, dwb, n * sizeof(float), st), "BinaryConnectAffine backward (copy)");
     }
   }
 };
@@ -521,6 +521,10 @@ protected:
 // ---------------------------------------------------- binary convolutions
 template <typename T> class BinaryWeightConvolutionB200 : public BinaryWeightConvolution<T> {
   ConvDims d_;
+  // The weights' int8 side-band for the tensor cores, kept across calls while the float weights
+  // (and the Wb / alpha this function wrote) are unchanged: their data stamps are the key.
+  NdArrayPtr side_;
+  DataStamp w_stamp_, wb_stamp_, alpha_stamp_;
 
 public:
   using BinaryWeightConvolution<T>::BinaryWeightConvolution;
@@ -534,18 +538,57 @@ protected:
     NBLA_CHECK(in[3]->size() == d_.Ko, error_code::value, "Size of alpha must be equal to the number of output maps.");
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float delta = fxp_tag_get(in[0]);
     const bool sign_ok = this->quantize_zero_to_ == 1.f || this->quantize_zero_to_ == -1.f ||
                          this->quantize_zero_to_ == 0.f;
-    const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
-    float *wb = wr(in[2], this->ctx_), *alpha = wr(in[3], this->ctx_);
+    const float *x = rd(in[0], this->ctx_);
     const float *b = in.size() == 5 ? rd(in[4], this->ctx_) : nullptr;
+    if (sign_ok && delta > 0.f) {
+      // 8-bit fixed-point activations: exact int8 contraction. The weights are binarised (Wb, alpha
+      // and the side-band written) only when they changed since the last call.
+      b200_count("int8_convolutions");
+      const bool hit = side_ && data_stamp(in[1]) == w_stamp_ && data_stamp(in[2]) == wb_stamp_ &&
+                       data_stamp(in[3]) == alpha_stamp_;
+      if (!hit) {
+        b200_count("weight_cache_misses");
+        const float *w = rd(in[1], this->ctx_);
+        float *wb = wr(in[2], this->ctx_), *alpha = wr(in[3], this->ctx_);
+        const int64_t bytes = nb200_binary_weights_side_bytes(d_.Ko, d_.C, d_.kh, d_.kw, this->group_);
+        side_ = make_shared<NdArray>(Shape_t{bytes});
+        int8_t *side = side_->cast(dtypes::BYTE, this->ctx_, true)->template pointer<int8_t>();
+        nb200_check(nb200_binary_weights_prepare_i8(w, wb, alpha, side, d_.Ko, d_.C, d_.kh, d_.kw, this->group_,
+                                                    this->quantize_zero_to_, st),
+                    "BinaryWeightConvolution (weights)");
+        w_stamp_ = data_stamp(in[1]);
+        wb_stamp_ = data_stamp(in[2]);
+        alpha_stamp_ = data_stamp(in[3]);
+      } else {
+        b200_count("weight_cache_hits");
+      }
+      const int8_t *side = side_->get(dtypes::BYTE, this->ctx_)->template const_pointer<int8_t>();
+      const float *alpha = rd(in[3], this->ctx_);
+      const int64_t slots = nb200_codes_nhwc_slots(d_.C, this->group_);
+      NdArray codes(Shape_t{(int64_t)d_.batch * d_.H * d_.W * slots});
+      int8_t *xc = codes.cast(dtypes::BYTE, this->ctx_, true)->template pointer<int8_t>();
+      float *y = wr(out[0], this->ctx_);
+      nb200_check(nb200_fixed_point_codes_nhwc(x, xc, d_.batch, d_.C, (int64_t)d_.H * d_.W, this->group_, delta, st),
+                  "BinaryWeightConvolution (activation codes)");
+      nb200_check(nb200_binary_convolution_codes_prepared_f32(
+                      xc, side, alpha, b, y, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
+                      this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1],
+                      this->group_, delta, st),
+                  "BinaryWeightConvolution");
+      return;
+    }
+    b200_count("bf16_convolutions");
+    const float *w = rd(in[1], this->ctx_);
+    float *wb = wr(in[2], this->ctx_), *alpha = wr(in[3], this->ctx_);
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_binary_weight_convolution_f32(
                     x, w, wb, alpha, b, y, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
                     this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1],
-                    this->group_, this->quantize_zero_to_, sign_ok ? delta : 0.0f, nullptr),
+                    this->group_, this->quantize_zero_to_, sign_ok ? delta : 0.0f, st),
                 "BinaryWeightConvolution");
   }
   // binary_weight_convolution.cpp:119-146; inputs [x, w, wb, alpha, b?]
@@ -554,7 +597,7 @@ protected:
     const bool has_b = in.size() == 5;
     if (!(pd[0] || pd[1] || (has_b && pd[4])))
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float delta = fxp_tag_get(in[0]);
     const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_), *alpha = rd(in[3], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
@@ -563,7 +606,7 @@ protected:
     nb200_check(nb200_binary_weight_convolution_backward_f32(
                     x, wb, alpha, dy, dx, dw, db, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
                     this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1],
-                    this->group_, accum[0], accum[1], has_b && accum[4], delta, nullptr),
+                    this->group_, accum[0], accum[1], has_b && accum[4], delta, st),
                 "BinaryWeightConvolution backward");
   }
 };
@@ -582,7 +625,7 @@ protected:
     check_same_shape(in[1], in[2]);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float delta = fxp_tag_get(in[0]);
     const bool sign_ok = this->quantize_zero_to_ == 1.f || this->quantize_zero_to_ == -1.f ||
                          this->quantize_zero_to_ == 0.f;
@@ -593,7 +636,7 @@ protected:
     nb200_check(nb200_binary_connect_convolution_f32(
                     x, w, wb, b, y, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0], this->pad_[1],
                     this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1], this->group_,
-                    this->quantize_zero_to_, sign_ok ? delta : 0.0f, nullptr),
+                    this->quantize_zero_to_, sign_ok ? delta : 0.0f, st),
                 "BinaryConnectConvolution");
   }
   // binary_connect_convolution.cpp:82-104; inputs [x, w, wb, b?]. Like the reference, the weight gradient
@@ -603,7 +646,7 @@ protected:
     const bool has_b = in.size() == 4;
     if (!(pd[0] || pd[1] || (has_b && pd[3])))
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float delta = fxp_tag_get(in[0]);
     const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
@@ -613,15 +656,15 @@ protected:
     nb200_check(nb200_binary_connect_convolution_backward_f32(
                     x, wb, dy, dx, dwb, db, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
                     this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1],
-                    this->group_, accum[0], 0, has_b && accum[3], delta, nullptr),
+                    this->group_, accum[0], 0, has_b && accum[3], delta, st),
                 "BinaryConnectConvolution backward");
     if (pd[1]) {
       float *dw = grad_wr(in[1], this->ctx_, true, accum[1]);
       const size_t n = in[1]->size();
       if (accum[1])
-        nb200_check(nb200_add2_f32(dw, dwb, dw, n, nullptr), "BinaryConnectConvolution backward (accumulate)");
+        nb200_check(nb200_add2_f32(dw, dwb, dw, n, st), "BinaryConnectConvolution backward (accumulate)");
       else
-        nb200_check(nb200_memcpy_d2d(dw, dwb, n * sizeof(float), nullptr), "BinaryConnectConvolution backward (copy)");
+        nb200_check(nb200_memcpy_d2d(dw, dwb, n * sizeof(float), st), "BinaryConnectConvolution backward (copy)");
     }
   }
 };
@@ -639,16 +682,18 @@ protected:
     d_ = setup_affine_shapes(this->base_axis_, in[0], in[1], in.size() == 3 ? in[2] : nullptr, out[0]);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float dx = fxp_tag_get(in[0]), dw = fxp_tag_get(in[1]);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     const float *b = in.size() == 3 ? rd(in[2], this->ctx_) : nullptr;
     float *y = wr(out[0], this->ctx_);
     if (dx > 0.f && dw > 0.f && d_.w_row <= 133000)
-      nb200_check(nb200_affine_fxp8_f32(x, w, dx, dw, b, y, d_.rows, d_.w_row, d_.w_col, nullptr),
+      b200_count("int8_affines");
+    if (dx > 0.f && dw > 0.f && d_.w_row <= 133000)
+      nb200_check(nb200_affine_fxp8_f32(x, w, dx, dw, b, y, d_.rows, d_.w_row, d_.w_col, st),
                   "Affine (fixed-point operands)");
     else
-      nb200_check(nb200_affine_f32(x, w, b, y, d_.rows, d_.w_row, d_.w_col, nullptr), "Affine");
+      nb200_check(nb200_affine_f32(x, w, b, y, d_.rows, d_.w_row, d_.w_col, st), "Affine");
   }
   // affine.cpp:98-138; inputs [x, w, b?]
   virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
@@ -656,13 +701,13 @@ protected:
     const bool has_b = in.size() == 3;
     if (!(pd[0] || pd[1] || (has_b && pd[2])))
       return;
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]), *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
     float *db = has_b ? grad_wr(in[2], this->ctx_, pd[2], accum[2]) : nullptr;
     nb200_check(nb200_affine_backward_f32(x, w, dy, dx, dw, db, d_.rows, d_.w_row, d_.w_col, accum[0], accum[1],
-                                          has_b && accum[2], nullptr),
+                                          has_b && accum[2], st),
                 "Affine backward");
   }
 };
@@ -681,13 +726,13 @@ protected:
                            in.size() == 3 ? in[2] : nullptr, out[0]);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     const float *b = in.size() == 3 ? rd(in[2], this->ctx_) : nullptr;
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_convolution_f32(x, w, b, y, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
                                       this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0],
-                                      this->dilation_[1], this->group_, nullptr),
+                                      this->dilation_[1], this->group_, st),
                 "Convolution");
   }
   B200_NO_BACKWARD("Convolution")
@@ -729,14 +774,14 @@ protected:
     out[0]->reshape(sx, true);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_);
     const float *beta = this->no_bias_ ? nullptr : rd(in[this->b_idx_], this->ctx_);
     const float *gamma = this->no_scale_ ? nullptr : rd(in[this->g_idx_], this->ctx_);
     const float *mean = rd(in[this->m_idx_], this->ctx_), *var = rd(in[this->v_idx_], this->ctx_);
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_batch_normalization_inference_f32(x, beta, gamma, mean, var, y, this->size0_, this->size1_,
-                                                        this->size2_, this->eps_, nullptr),
+                                                        this->size2_, this->eps_, st),
                 "BatchNormalization");
   }
   virtual void recompute_impl(const Variables &in, const Variables &out) { forward_impl(in, out); }
@@ -750,11 +795,11 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float tag = fxp_tag_get(in[0]);
     const float *x = rd(in[0], this->ctx_);
     float *y = wr(out[0], this->ctx_);
-    nb200_check(nb200_relu_f32(x, y, in[0]->size(), nullptr), "ReLU");
+    nb200_check(nb200_relu_f32(x, y, in[0]->size(), st), "ReLU");
     if (tag > 0.f)
       fxp_tag_set(out[0], tag); // max(0, k * delta) is still a multiple of delta
   }
@@ -773,10 +818,10 @@ protected:
     out[0]->reshape(in[0]->shape(), true);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float *a = rd(in[0], this->ctx_), *b = rd(in[1], this->ctx_);
     float *y = wr(out[0], this->ctx_);
-    nb200_check(nb200_add2_f32(a, b, y, in[0]->size(), nullptr), "Add2");
+    nb200_check(nb200_add2_f32(a, b, y, in[0]->size(), st), "Add2");
   }
   B200_NO_BACKWARD("Add2")
 };
@@ -790,7 +835,7 @@ protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
     NBLA_CHECK(!this->channel_last_, error_code::not_implemented, "channel_last is not supported");
     NBLA_CHECK(this->kernel_.size() == 2, error_code::not_implemented, "the b200 backend implements 2-D pooling only");
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const float tag = fxp_tag_get(in[0]);
     const Shape_t sx = in[0]->shape();
     const int H = sx[sx.size() - 2], W = sx[sx.size() - 1];
@@ -798,7 +843,7 @@ protected:
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_max_pooling_f32(x, y, in[0]->size() / (H * W), H, W, this->kernel_[0], this->kernel_[1],
                                       this->stride_[0], this->stride_[1], this->pad_[0], this->pad_[1],
-                                      this->ignore_border_, nullptr),
+                                      this->ignore_border_, st),
                 "MaxPooling");
     if (tag > 0.f)
       fxp_tag_set(out[0], tag); // a maximum of multiples of delta is one of them
@@ -813,12 +858,12 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    enter(this->ctx_);
+    void *st = enter(this->ctx_);
     const Shape_t sx = in[0]->shape();
     const Size_t maps = sx[0] * sx[1];
     const float *x = rd(in[0], this->ctx_);
     float *y = wr(out[0], this->ctx_);
-    nb200_check(nb200_global_average_pooling_f32(x, y, maps, in[0]->size() / maps, nullptr), "GlobalAveragePooling");
+    nb200_check(nb200_global_average_pooling_f32(x, y, maps, in[0]->size() / maps, st), "GlobalAveragePooling");
   }
   B200_NO_BACKWARD("GlobalAveragePooling")
 };

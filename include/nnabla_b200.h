@@ -361,6 +361,14 @@ int nb200_min_max_quantize_backward_f32(const float *x, const int64_t *x_shape, 
  * returns (its output is then incomplete). This call synchronises `stream`,
  * returns the word in *code (0 = no wait ever gave up) and clears it. */
 int nb200_take_device_status(int *code, void *stream);
+/* Runs the give-up path of those waits on purpose, harmlessly: a one-block
+ * kernel waits on a barrier nobody arrives at, with a limit of limit_us
+ * microseconds (1..100000). The kernel returns by itself, the status word
+ * holds the producer-timeout code afterwards (read it with
+ * nb200_take_device_status) and the context stays usable. *waited_us (may be
+ * NULL) receives how long a second role waited before the abort flag
+ * released it. No counterpart in the reference (it has no device code). */
+int nb200_selftest_wait_timeout(int limit_us, int *waited_us, void *stream);
 
 /* BinaryWeightAffine<float>::forward_impl
  * (src/nbla/function/generic/binary_weight_affine.cpp:74-122).

@@ -34,8 +34,18 @@ def lib():
     return _lib
 
 
+_calls = 0
+
+
+def calls_made():
+    """Number of entry-point calls made through call() so far in this process."""
+    return _calls
+
+
 def call(name, *args):
     """Calls entry point `name` and raises NB200Error on a non-zero status."""
+    global _calls
+    _calls += 1
     L = lib()
     fn = getattr(L, name)
     fn.restype = ctypes.c_int

@@ -19,6 +19,51 @@ import torch
 import torch.distributed as dist
 
 
+class PeerLost(RuntimeError):
+    """A rank did not reach a step within the deadline; `.missing` lists the ranks."""
+
+    def __init__(self, step, missing, waited_s):
+        RuntimeError.__init__(self, "step %s: rank(s) %s did not arrive within %.1f s" % (step, missing, waited_s))
+        self.step, self.missing = step, missing
+
+
+class StepGuard:
+    """Host-side check that every rank is about to take part in a step, made BEFORE anything is
+    launched for it. The kernels and collectives of this package never wait on another rank on
+    the device, so a lost rank can only make a later collective (the gather, the ordering
+    all-reduce of PeerMatrices.fence) wait for its own timeout; the guard turns that into an
+    immediate, named error on the host instead. Each rank publishes "rank r reached step s" in the
+    job's key-value store (a torch.distributed Store: TCPStore, FileStore, ...) and reads the
+    others' marks with a deadline. A rank that leaves does so between steps, with nothing in
+    flight; the survivors learn of it here, before their next launch."""
+
+    def __init__(self, store, rank, world, timeout_s=10.0, prefix="nb200/step"):
+        self.store, self.rank, self.world = store, int(rank), int(world)
+        self.timeout_s, self.prefix = float(timeout_s), prefix
+
+    def _key(self, step, rank):
+        return "%s/%s/%d" % (self.prefix, step, rank)
+
+    def arrive(self, step):
+        """Marks this rank as present at `step` and waits until every rank is; raises PeerLost
+        naming the ranks that are not there when the deadline passes."""
+        import datetime
+        import time
+        self.store.set(self._key(step, self.rank), b"1")
+        t0 = time.monotonic()
+        missing = []
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            left = self.timeout_s - (time.monotonic() - t0)
+            try:
+                self.store.wait([self._key(step, r)], datetime.timedelta(seconds=max(left, 0.05)))
+            except Exception:  # noqa: BLE001 - the store's wait signals its timeout with a RuntimeError / DistStoreError
+                missing.append(r)
+        if missing:
+            raise PeerLost(step, missing, time.monotonic() - t0)
+
+
 def shard_range(total, rank, world):
     """[begin, end) of shard `rank` when `total` units are split as evenly as
     possible (the first total % world shards get one more)."""

@@ -1,4 +1,4 @@
-"""ctypes driver of ext/_build/libnbext_test.so (tests/ext_driver, linked against the extension
+"""ctypes driver of ext/_build/libnnabla_b200_runner.so (ext/runner, linked against the extension
 ext/_build/libnnabla_ext_b200.so and the host library): runs a function created
 through nnabla's registry on either the reference's "cpu:float" context or the
 extension's "b200:float" context."""
@@ -8,7 +8,7 @@ import os
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(ROOT, "ext", "_build", "libnbext_test.so")
+LIB_PATH = os.path.join(ROOT, "ext", "_build", "libnnabla_b200_runner.so")
 _lib = None
 
 

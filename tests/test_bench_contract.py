@@ -20,7 +20,8 @@ def test_reference_arm_prints_the_contract_line():
     for key in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better",
                 "scaling", "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
         assert key in line, key
-    assert line["impl"] == "reference" and line["metric"] == "quantizer_GBps" and line["unit"] == "GB/s"
+    assert line["impl"] == "reference" and line["metric"] == "resnet18_images_per_sec" and line["unit"] == "images/s"
+    assert line["scaling"] == "strong"
     assert line["value"] > 0 and line["cpu_baseline"]["kind"] == "reference" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert "workload" in line["config"]
@@ -29,7 +30,7 @@ def test_reference_arm_prints_the_contract_line():
 @pytest.mark.gpu
 def test_own_arm_prints_the_contract_line():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--steps", "2", "--warmup", "3",
-                          "--no-extras", "--size-log2", "24", "--e2e-steps", "1"], capture_output=True, text=True,
+                          "--no-extras", "--no-forms", "--batch", "32"], capture_output=True, text=True,
                          timeout=900, cwd=ROOT)
     assert out.returncode == 0, out.stderr[-500:]
     line = json.loads(out.stdout.strip().splitlines()[-1])
@@ -39,7 +40,8 @@ def test_own_arm_prints_the_contract_line():
     assert line["steps"] == 2 and line["warmup"] == 3 and line["n_gpus"] == 1 and line["gpu_launches"] > 0
     for key in ("bound", "achieved", "peak", "unit", "frac", "traffic"):
         assert key in line["roofline"], key
-    assert line["roofline"]["bound"] == "hbm" and 0 < line["roofline"]["frac"] < 1.3
+    assert line["roofline"]["bound"] in ("hbm", "tensor") and 0 < line["roofline"]["frac"] < 1.3
+    assert line["metric"] == "resnet18_images_per_sec" and line["scaling"] == "strong" and line["logits_finite"]
     for key in ("value", "unit", "cores", "kind", "sample"):
         assert key in line["cpu_baseline"], key
     assert line["e2e"]["h2d_bytes_per_step"] > 0 and line["e2e"]["d2h_bytes_per_step"] > 0 and line["e2e"]["value"] > 0

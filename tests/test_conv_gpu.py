@@ -99,6 +99,36 @@ def test_binary_weight_convolution_config4_reduced(F):
     assert err < TOL
 
 
+def test_binary_weight_convolution_config3_full_batch(F):
+    """The benchmark's 3x3 256 -> 256 layer at its stated size, x = ReLU(N(0,1)) [128, 256, 28, 28],
+    W Kaiming-normal, seed 0: the GPU runs the whole batch (the tile decoding, pixel boxes and
+    store paths of the timed geometry), the oracle checks images 0, 63 and 127 (a convolution
+    treats every image on its own, src/nbla/function/generic/convolution.cpp:168-196)."""
+    rng = np.random.RandomState(0)
+    x = np.maximum(rng.randn(128, 256, 28, 28), 0).astype(np.float32)
+    w = (rng.randn(256, 256, 3, 3) * np.sqrt(2.0 / 2304)).astype(np.float32)
+    wb = torch.zeros(w.shape, device="cuda")
+    al = torch.zeros(256, device="cuda")
+    y = F.binary_weight_convolution(dev(x), dev(w), wb, al, torch.zeros(256, device="cuda"), 1, (1, 1), (1, 1),
+                                    (1, 1), 1, 1.0)
+    F.check_device_status()
+    assert tuple(y.shape) == (128, 256, 28, 28)
+    picks = [0, 63, 127]
+    wy, wwb, wal = oracle.binary_weight_convolution(x[picks], w, None, (1, 1), (1, 1), (1, 1), 1, 1.0)
+    assert np.array_equal(bits(wb.cpu().numpy()), bits(wwb))
+    # alpha against the exact mean: the oracle's own fp32 sum of 2304 terms is the less accurate of the two
+    np.testing.assert_allclose(al.cpu().numpy(), np.abs(w.astype(np.float64)).reshape(256, -1).mean(1), rtol=1e-6)
+    np.testing.assert_allclose(al.cpu().numpy(), wal, rtol=1e-5)
+    got = y[picks].cpu().numpy()
+    for j, i in enumerate(picks):
+        err = cases.rel_rms(got[j], wy[j])
+        print("image %d rel-RMS %.3g" % (i, err))
+        assert err < TOL, i
+    # every other image: the same weights give the same map of an all-ones probe through linearity
+    # is not available (ReLU input), so check the batch is complete instead: no image left unwritten
+    assert bool(torch.isfinite(y).all()) and float(y.abs().amax(dim=(1, 2, 3)).min()) > 0.0
+
+
 def test_conv_errors(F):
     x = torch.zeros(1, 4, 8, 8, device="cuda")
     w = torch.zeros(6, 4, 3, 3, device="cuda")

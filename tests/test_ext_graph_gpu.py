@@ -1,0 +1,108 @@
+"""A whole network through nnabla's own graph engine on the "b200:float" context: the graph is
+built with CgVariable / CgFunction / connect() (src/nbla/computation_graph/computation_graph.cpp:59-123)
+and run by CgVariable::forward with clear_buffer, so the extension's arrays, caching allocator,
+synchronizers, stream, fixed-point tags and prepared-weight cache all take part. The same calls
+build it on "cpu:float"; only the context string differs."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from nnabla_b200 import nbla_graph, resnet18
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not nbla_graph.available(), reason="runner library not built")]
+
+cz = lambda w, shape=None: np.zeros(shape or w.shape, np.float32)
+
+
+def mirror_logits(params, x):
+    """The same graph, function by function, through nnabla_b200.functions."""
+    from nnabla_b200 import functions as F
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).cuda()
+    gp = {k: dev(v) for k, v in params.items()}
+    gz = lambda w, shape=None: torch.zeros(shape or tuple(w.shape), device="cuda")
+    y = resnet18.Runner(F, gp, gz)(dev(x)).cpu().numpy()
+    F.check_device_status()
+    return y
+
+
+def test_resnet18_graph_on_b200_context_small():
+    rng = np.random.RandomState(0)
+    params = resnet18.init_parameters(rng, num_classes=100)
+    x = rng.randn(2, 3, 64, 64).astype(np.float32)
+    logits = {}
+    for backend in ("cpu:float", "b200:float"):
+        g = nbla_graph.Graph(backend)
+        xv = g.variable(x)
+        y = resnet18.Runner(g, params, cz, None, fixed_point_hint=False)(xv)
+        nbla_graph.reset_counters()
+        g.forward(y, clear_buffer=True)
+        logits[backend] = g.data(y)
+        if backend == "b200:float":
+            # every binary-weight convolution saw the fixed-point tag of its input and took the int8 path
+            assert nbla_graph.counter("int8_convolutions") == 19 and nbla_graph.counter("bf16_convolutions") == 0
+            assert nbla_graph.counter("weight_cache_misses") == 19
+            g.forward(y, clear_buffer=True)
+            assert nbla_graph.counter("weight_cache_hits") == 19 and nbla_graph.counter("weight_cache_misses") == 19
+            assert np.array_equal(g.data(y), logits[backend])
+            # without clear_buffer, and with new input data
+            g.forward(y, clear_buffer=False)
+            assert np.array_equal(g.data(y), logits[backend])
+            x2 = rng.randn(2, 3, 64, 64).astype(np.float32)
+            g.set_data(xv, x2)
+            g.forward(y, clear_buffer=True)
+            assert np.array_equal(g.data(y), mirror_logits(params, x2))
+        g.close()
+    # the extension's functions are the kernels the function-by-function mirror calls: same bits
+    assert np.array_equal(logits["b200:float"], mirror_logits(params, x))
+    # against the reference's own CPU functions run by the same engine (free-running: a last-bit
+    # difference before a quantizer moves a value by one step, so the logits are compared as a whole)
+    err = cases.rel_rms(logits["b200:float"], logits["cpu:float"])
+    print("graph engine, b200 vs cpu context: logits rel-RMS %.3g" % err)
+    assert err < 1e-2
+
+
+def test_weight_update_invalidates_the_prepared_weights():
+    rng = np.random.RandomState(3)
+    g = nbla_graph.Graph("b200:float")
+    x = np.maximum(rng.randn(2, 16, 8, 8), 0).astype(np.float32)
+    w = rng.randn(8, 16, 3, 3).astype(np.float32)
+    xv, wv = g.variable(x), g.variable(w)
+    wb, al = g.variable(np.zeros_like(w)), g.variable(np.zeros(8, np.float32))
+    q = g.fixed_point_quantize(xv, True, 8, 2.0 ** -4)
+    y = g.binary_weight_convolution(q, wv, wb, al, None, 1, (1, 1), (1, 1), (1, 1), 1, 1.0)
+    nbla_graph.reset_counters()
+    g.forward(y)
+    first = g.data(y)
+    g.forward(y)
+    assert nbla_graph.counter("weight_cache_hits") == 1
+    g.set_data(wv, -w)  # a weight update: the stamp of W changes, the side-band is rebuilt
+    g.forward(y)
+    assert nbla_graph.counter("weight_cache_misses") == 2
+    assert np.array_equal(g.data(y), -first) and np.array_equal(g.data(wb), -np.sign(w))
+    g.close()
+
+
+def test_resnet18_graph_on_b200_context_benchmark_size():
+    rng = np.random.RandomState(0)
+    params = resnet18.init_parameters(rng)
+    x = rng.randn(256, 3, 224, 224).astype(np.float32)
+    g = nbla_graph.Graph("b200:float")
+    xv = g.variable(x)
+    y = resnet18.Runner(g, params, cz, None, fixed_point_hint=False)(xv)
+    g.forward(y, clear_buffer=True, repeat=2)
+    nbla_graph.reset_counters()
+    sec = g.forward(y, clear_buffer=True, repeat=5)
+    assert nbla_graph.counter("int8_convolutions") == 5 * 19 and nbla_graph.counter("weight_cache_hits") == 5 * 19
+    got = g.data(y)
+    print("ResNet-18 [256,3,224,224] through nnabla's graph engine on b200:float: %.2f ms per batch, %.0f images/s"
+          % (1e3 * sec, 256 / sec))
+    prof = g.profile(y)
+    by = {}
+    for name, ms in prof:
+        by[name] = by.get(name, 0.0) + ms
+    print("per function (device synchronised around each): " +
+          ", ".join("%s %.2f ms" % kv for kv in sorted(by.items(), key=lambda kv: -kv[1])))
+    g.close()
+    nbla_graph.clear_memory_cache()
+    assert np.array_equal(got, mirror_logits(params, x))

@@ -6,8 +6,10 @@ import numpy as np
 import pytest
 import torch
 
-import oracle_ops
+import cases
+from oracle import ops as oracle_ops
 from golden_util import bits
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -173,6 +175,10 @@ def test_convolution_from_codes_equals_hinted_convolution(F, case):
                                                  delta)
     F.check_device_status()
     assert torch.equal(got, want) and torch.equal(wb1, wb2) and torch.equal(al1, al2)
+    # and against the oracle directly: signs bit-exact, outputs within 1e-5 of the output RMS
+    oy, owb, _ = oracle.binary_weight_convolution(xq, w, bias, pad, stride, (1, 1), g, 1.0)
+    assert np.array_equal(bits(wb2.cpu().numpy()), bits(owb))
+    assert cases.rel_rms(got.cpu().numpy(), oy) < 1e-5
     # binary connect: no alpha
     wb3 = gz(*w.shape)
     want_c = F.binary_connect_convolution(dev(xq), dev(w), wb3, None, 1, pad, stride, (1, 1), g, 1.0,
@@ -199,6 +205,12 @@ def test_prepared_weights_equal_per_call_binarisation(F):
         got = F.binary_convolution_from_codes_prepared(codes, xs, prep, dev(bias), pad, st, (1, 1), delta)
         F.check_device_status()
         assert torch.equal(got, want) and torch.equal(prep.binary_weight, wb) and torch.equal(prep.alpha, al)
+        oy, owb, oal = oracle.binary_weight_convolution(xq, w, bias, pad, st, (1, 1), g, 1.0)
+        assert np.array_equal(bits(prep.binary_weight.cpu().numpy()), bits(owb))
+        np.testing.assert_allclose(prep.alpha.cpu().numpy(), np.abs(w.astype(np.float64)).reshape(ko, -1).mean(1),
+                                   rtol=1e-6)
+        np.testing.assert_allclose(prep.alpha.cpu().numpy(), oal, rtol=1e-5)
+        assert cases.rel_rms(got.cpu().numpy(), oy) < 1e-5
         # BinaryConnect: no alpha
         wbc = torch.zeros(*w.shape, device="cuda")
         want_c = F.binary_weight_convolution_from_codes(codes, xs, dev(w), wbc, None, None, pad, st, (1, 1), g, 1.0, delta)
