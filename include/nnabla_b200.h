@@ -282,6 +282,47 @@ int nb200_binary_convolution_codes_prepared_f32(const int8_t *x_codes, const int
                                                 int pad_w, int stride_h, int stride_w, int dilation_h,
                                                 int dilation_w, int group, float activation_delta, void *stream);
 
+/* ---- batch normalization folded into the convolutions (inference) -------------------
+ * nnabla's BatchNormalizationFolding converter
+ * (python/src/nnabla/experimental/graph_converters/batch_normalization_folding.py:92-200)
+ * rewrites Convolution -> BatchNormalization into one Convolution with
+ * w' = c0 * w, b' = c1 (c0 = gamma / sqrt(var + eps), c1 = beta - gamma * mean /
+ * sqrt(var + eps)). For a binary-weight layer w = Wb * alpha, so the fold lands in
+ * the per-map factor: y = conv(x, Wb) * (alpha * c0) + c1. The two entries below
+ * run such a folded layer with the rest of its inference tail, Add2 of the
+ * residual, ReLU and FixedPointQuantize (relu.cpp, add2.cpp,
+ * fixed_point_quantize.cpp:45-66), inside the convolution's epilogue, and emit the
+ * int8 channel-last codes the next layer reads: nothing but codes travels between
+ * the layers. Results follow the folded graph (Convolution with the folded
+ * weights, then the separate functions) within the contraction tolerance before the
+ * quantizer; they are not bit-identical to the unfolded graph, as the reference's
+ * own folded graphs are not.
+ *
+ * nb200_convolution_codes_folded_nhwc: x_codes [batch][H * W][slots(channels)] int8
+ * (value = code * the step already folded into scale), side = weights prepared by
+ * nb200_binary_weights_prepare_i8 (group 1), scale / bias per output map:
+ *   v = float(acc) * scale[o] + bias[o]          (bias may be NULL)
+ *   v += res_codes * res_delta  |  v += res_f32  (residual in the result's own
+ *                                                 channel-last layout; at most one)
+ *   y_f32 (channel-last [batch][Ho * Wo][slots(outmaps)], may be NULL) = v
+ *   y_codes (may be NULL) = code of FixedPointQuantize(sign, n, delta)(relu ? max(v, 0) : v)
+ * delta must be a power of two, n - sign <= 7, all tensors 16-byte aligned. */
+int nb200_convolution_codes_folded_nhwc(const int8_t *x_codes, const int8_t *side, const float *scale,
+                                        const float *bias, const int8_t *res_codes, float res_delta,
+                                        const float *res_f32, int8_t *y_codes, float *y_f32, int batch, int channels,
+                                        int height, int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                        int pad_w, int stride_h, int stride_w, int dilation_h, int dilation_w,
+                                        int relu, int sign, int n, float delta, void *stream);
+/* The network stem in the same form: full-precision Convolution (few input channels,
+ * convolution.cpp:160-197) with folded weights and bias, then ReLU (optional) and
+ * FixedPointQuantize in the epilogue; y_codes [batch][Ho * Wo][slots(outmaps)] int8. Geometries
+ * outside the tensor-core stem kernel (kernel_w * channels <= 24, kernel_h <= 7, at most 64 maps
+ * and 112 output columns, no dilation, group 1) return NB200_ENOTIMPL. */
+int nb200_convolution_relu_fxp_codes_nhwc(const float *x, const float *w, const float *bias, int8_t *y_codes,
+                                          int batch, int channels, int height, int width, int outmaps, int kernel_h,
+                                          int kernel_w, int pad_h, int pad_w, int stride_h, int stride_w, int relu,
+                                          int sign, int n, float delta, void *stream);
+
 /* Convolution<float>::forward_impl (src/nbla/function/generic/convolution.cpp:160-197)
  * for operands that are outputs of FixedPointQuantize with at most 8 bits (what
  * fixed_point_quantized_convolution builds, python/src/nnabla/parametric_functions.py:2411-):

@@ -6,6 +6,8 @@
 // the reference's operation order, so their results are bit-identical to its
 // CPU code; the convolution accumulates with fused multiply-adds (tolerance
 // parity, like the other contractions).
+#include <cmath>
+
 #include "common.cuh"
 #include "narrow_conv.cuh"
 
@@ -548,6 +550,39 @@ int nb200_global_average_pooling_f32(const float *x, float *y, int64_t maps, int
                                                                                           (int)spatial, y);
   NB_LAUNCH_CHECK();
   return NB200_OK;
+}
+
+int nb200_convolution_relu_fxp_codes_nhwc(const float *x, const float *w, const float *bias, int8_t *y_codes,
+                                          int batch, int channels, int height, int width, int outmaps, int kernel_h,
+                                          int kernel_w, int pad_h, int pad_w, int stride_h, int stride_w, int relu,
+                                          int sign, int n, float delta, void *stream) {
+  NB_CHECK(batch > 0 && channels > 0 && height > 0 && width > 0 && outmaps > 0 && kernel_h > 0 && kernel_w > 0,
+           NB200_EVALUE, "empty convolution operand");
+  NB_CHECK(stride_h > 0 && stride_w > 0 && pad_h >= 0 && pad_w >= 0, NB200_EVALUE,
+           "stride must be positive, pad non-negative");
+  const int eh = height + 2 * pad_h - kernel_h, ew = width + 2 * pad_w - kernel_w;
+  NB_CHECK(eh >= 0 && ew >= 0, NB200_EVALUE, "Invalid configuration of convolution.");
+  const int Ho = eh / stride_h + 1, Wo = ew / stride_w + 1;
+  NB_CHECK(x && w && y_codes, NB200_EVALUE, "null data pointer");
+  NB_CHECK((reinterpret_cast<uintptr_t>(y_codes) & 15) == 0, NB200_EVALUE, "the code tensor must be 16-byte aligned");
+  // the quantizer's setup (fixed_point_quantize.cpp:31-42); codes are stored as int8
+  NB_CHECK(n > 0 && delta > 0.f, NB200_EVALUE, "Both bit width and delta should be positive.");
+  const int nn = sign ? n - 1 : n;
+  NB_CHECK(nn > 0 && nn <= 7, NB200_ENOTIMPL, "codes need 0 < n - sign <= 7 (they are stored as int8)");
+  int ex = 0;
+  NB_CHECK(std::frexp(delta, &ex) == 0.5f && ex > -100 && ex < 100, NB200_ENOTIMPL,
+           "a power-of-two quantizer step is needed (got %g)", delta);
+  NB_CHECK(relu || sign, NB200_ENOTIMPL, "an unsigned quantizer without ReLU is not supported");
+  NB_CHECK(narrow_conv_applies(x, channels, height, width, outmaps, kernel_h, kernel_w, pad_w, stride_w, 1, 1, 1, Wo),
+           NB200_ENOTIMPL,
+           "the fused full-precision convolution is for inputs with few channels (kernel_w * channels <= 24, "
+           "kernel_h <= 7, at most 64 maps and 112 output columns)");
+  const int kmax = (1 << nn) - 1;
+  const int64_t c_pad = (outmaps + 15) / 16 * 16;
+  const int slots = (int)(c_pad < 64 ? 64 : c_pad);
+  return narrow_conv_tc(x, w, bias, nullptr, batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h,
+                        pad_w, stride_h, stride_w, Ho, Wo, as_stream(stream), y_codes, slots, relu, kmax,
+                        sign ? -kmax : 0, delta);
 }
 
 int nb200_convolution_f32(const float *x, const float *w, const float *bias, float *y, int batch, int channels,

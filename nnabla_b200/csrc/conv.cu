@@ -9,8 +9,10 @@
 //                K ordered tap-major, channel-minor, zero padded per tap
 // D = weights x activations^T with rows = output maps, columns = a box of
 // output pixels; y is written NCHW directly from the epilogue.
+#include <cmath>
 #include <cstring>
 
+#include "conv_codes.cuh"
 #include "gemm.cuh"
 #include "prepare.cuh"
 
@@ -465,6 +467,138 @@ void int8_side_layout(int Cg, int taps, int &c_slots, int64_t &wpitch) {
 }
 } // namespace
 
+} // extern "C" (reopened below)
+namespace {
+// ---------------------------------------------------------------------------
+// Convolution of activation codes with the layer's inference tail in the
+// epilogue (conv_codes.cuh): pixels on the MMA rows, channel-last codes out.
+// ---------------------------------------------------------------------------
+template <int BN, int STAGES, int RB>
+int launch_conv_codes(const ConvGeometry &g, const int8_t *x_codes, int64_t ctot, const int8_t *side, int64_t wpitch,
+                      int cblocks, int h_box, int n_box, int slots_out, const ConvCodesEpilogue &ep, cudaStream_t st) {
+  CUtensorMap mx, mw;
+  // activations: (C, W, H, N, 1); the box walks W and H with the convolution stride
+  const uint64_t dims[5] = {(uint64_t)ctot, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N, 1};
+  const uint64_t strides[4] = {(uint64_t)ctot, (uint64_t)ctot * g.W, (uint64_t)ctot * g.W * g.H,
+                               (uint64_t)ctot * g.W * g.H * g.N};
+  const uint32_t box[5] = {(uint32_t)RB, (uint32_t)(g.Wo * g.sw), (uint32_t)(h_box * g.sh), (uint32_t)n_box, 1};
+  const uint32_t estr[5] = {1, (uint32_t)g.sw, (uint32_t)g.sh, 1, 1};
+  NB_TRY(encode_tiled(&mx, 1, 5, x_codes, dims, strides, box, estr, RB));
+  // weights: (K, Ko, 1), BN maps per box
+  NB_TRY(make_operand_map(&mw, side, true, wpitch, wpitch, g.Ko, 1, BN, RB));
+  ConvCodesProblem p;
+  p.Nimg = g.N;
+  p.Ko = g.Ko;
+  p.Ho = g.Ho;
+  p.Wo = g.Wo;
+  p.h_box = h_box;
+  p.n_box = n_box;
+  p.tiles_h = (g.Ho + h_box - 1) / h_box;
+  p.tiles_n = (g.N + n_box - 1) / n_box;
+  p.n_tiles = (g.Ko + BN - 1) / BN;
+  p.bn = BN;
+  p.kw = g.kw;
+  p.taps = g.kh * g.kw;
+  p.cblocks = cblocks;
+  p.sh = g.sh;
+  p.sw = g.sw;
+  p.ph = g.ph;
+  p.pw = g.pw;
+  p.dh = g.dh;
+  p.dw = g.dw;
+  p.pixels = n_box * h_box * g.Wo;
+  p.slots_out = slots_out;
+  auto kernel = conv_codes_tcgen05_kernel<BN, STAGES, RB>;
+  constexpr size_t smem = conv_codes_smem_bytes<BN, STAGES, RB>();
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  static bool configured[64];
+  int dev = 0;
+  NB_CUDA(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    NB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev & 63] = true;
+  }
+  int *status = nullptr;
+  NB_TRY(device_status_word(&status));
+  const int tiles = p.n_tiles * p.tiles_h * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kernel<<<grid, kGemmThreads, smem, st>>>(mx, mw, p, ep, status);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const float *scale, const float *bias,
+                             const int8_t *res_codes, float res_delta, const float *res_f32, int8_t *y_codes,
+                             float *y_f32, ConvGeometry g, int relu, int sign, int n, float delta, cudaStream_t st) {
+  NB_TRY(check_geometry(g));
+  NB_CHECK(g.group == 1, NB200_ENOTIMPL, "grouped convolutions are not supported by the folded code path");
+  NB_CHECK(x_codes && side && scale && (y_codes || y_f32), NB200_EVALUE, "null data pointer");
+  NB_CHECK(!(res_codes && res_f32), NB200_EVALUE, "the residual is either codes or fp32, not both");
+  NB_CHECK(res_codes == nullptr || res_delta > 0.f, NB200_EVALUE, "res_delta should be positive");
+  NB_CHECK(g.Ko <= kCodesMaxMaps, NB200_ENOTIMPL, "more than %d output maps", kCodesMaxMaps);
+  NB_CHECK(g.Wo * g.sw <= 256 && g.Wo <= 128, NB200_ENOTIMPL,
+           "output rows wider than 128 pixels (Wo=%d, stride %d) are not supported", g.Wo, g.sw);
+  ConvCodesEpilogue ep{};
+  ep.scale = scale;
+  ep.bias = bias;
+  ep.res_codes = res_codes;
+  ep.res_delta = res_delta;
+  ep.res_f32 = res_f32;
+  ep.y_codes = y_codes;
+  ep.y_f32 = y_f32;
+  ep.relu = relu;
+  ep.delta = 1.0f;
+  ep.inv_delta = 1.0f;
+  if (y_codes) {
+    // the quantizer's setup (fixed_point_quantize.cpp:31-42); the step must be a power of two
+    NB_CHECK(n > 0 && delta > 0.f, NB200_EVALUE, "Both bit width and delta should be positive.");
+    const int nn = sign ? n - 1 : n;
+    NB_CHECK(nn > 0 && nn <= 7, NB200_ENOTIMPL, "codes need 0 < n - sign <= 7 (they are stored as int8)");
+    int ex = 0;
+    NB_CHECK(std::frexp(delta, &ex) == 0.5f && ex > -100 && ex < 100, NB200_ENOTIMPL,
+             "the folded code path needs a power-of-two quantizer step (got %g)", delta);
+    NB_CHECK(relu || sign, NB200_ENOTIMPL, "an unsigned quantizer without ReLU is not supported");
+    ep.delta = delta;
+    ep.inv_delta = 1.0f / delta;
+    ep.kmax = (1 << nn) - 1;
+    ep.kmin = sign ? -ep.kmax : 0;
+  }
+  const int64_t slots_out = codes_slots(g.Ko, 1);
+  NB_CHECK((((reinterpret_cast<uintptr_t>(x_codes) | reinterpret_cast<uintptr_t>(side) |
+              reinterpret_cast<uintptr_t>(res_codes) | reinterpret_cast<uintptr_t>(res_f32) |
+              reinterpret_cast<uintptr_t>(y_codes) | reinterpret_cast<uintptr_t>(y_f32)) &
+             15) == 0),
+           NB200_EVALUE, "code and result tensors must be 16-byte aligned");
+  const int c_pad = (int)round_up(g.C, 16);
+  const bool narrow_rows = c_pad <= 64;
+  const int E = narrow_rows ? 64 : kRowBytes;
+  const int cblocks = (c_pad + E - 1) / E;
+  const int64_t ctot = codes_slots(g.C, 1);
+  int c_slots;
+  int64_t wpitch;
+  int8_side_layout(g.C, g.kh * g.kw, c_slots, wpitch);
+  int h_box, n_box;
+  plan_box(g, 128, h_box, n_box);
+  NB_CHECK(h_box * n_box * g.Wo <= 128, NB200_ENOTIMPL, "no pixel box of at most 128 pixels");
+#define NB_CC(BN_, ST_, RB_)                                                                                          \
+  return launch_conv_codes<BN_, ST_, RB_>(g, x_codes, ctot, side, wpitch, cblocks, h_box, n_box, (int)slots_out, ep, st)
+  if (narrow_rows) {
+    if (g.Ko <= 64)
+      NB_CC(64, 10, 64);
+    if (g.Ko <= 128)
+      NB_CC(128, 8, 64);
+    NB_CC(256, 6, 64);
+  }
+  if (g.Ko <= 64)
+    NB_CC(64, 8, 128);
+  if (g.Ko <= 128)
+    NB_CC(128, 6, 128);
+  NB_CC(256, 4, 128);
+#undef NB_CC
+}
+} // namespace
+extern "C" {
+
 int64_t nb200_binary_weights_side_bytes(int outmaps, int channels, int kernel_h, int kernel_w, int group) {
   if (outmaps <= 0 || channels <= 0 || kernel_h <= 0 || kernel_w <= 0 || group <= 0 || channels % group != 0)
     return 0;
@@ -549,5 +683,17 @@ int nb200_convolution_fxp8_f32(const float *xq, const float *wq, float delta_x, 
   ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
                  dilation_h, dilation_w, group, 0, 0, 0, 0};
   return binary_convolution(xq, wq, nullptr, nullptr, bias, y, g, 1.0f, delta_x, as_stream(stream), delta_w);
+}
+
+int nb200_convolution_codes_folded_nhwc(const int8_t *x_codes, const int8_t *side, const float *scale,
+                                        const float *bias, const int8_t *res_codes, float res_delta,
+                                        const float *res_f32, int8_t *y_codes, float *y_f32, int batch, int channels,
+                                        int height, int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
+                                        int pad_w, int stride_h, int stride_w, int dilation_h, int dilation_w,
+                                        int relu, int sign, int n, float delta, void *stream) {
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, 1, 0, 0, 0, 0};
+  return convolution_codes_folded(x_codes, side, scale, bias, res_codes, res_delta, res_f32, y_codes, y_f32, g, relu,
+                                  sign, n, delta, as_stream(stream));
 }
 }

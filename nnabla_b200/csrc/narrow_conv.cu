@@ -75,6 +75,15 @@ struct NarrowConv {
   int N, C, H, W, Ko, kh, kw, ph, pw, sh, sw, Ho, Wo;
 };
 
+// Result as int8 channel-last codes [N][Ho * Wo][slots] instead of fp32 NCHW: the epilogue applies
+// ReLU (optional) and FixedPointQuantize (power-of-two step) to conv + bias and stores finished
+// codes, 32 consecutive maps of a pixel per thread and chunk. codes == NULL: fp32 result.
+struct NarrowCodesOut {
+  int8_t *codes;
+  int slots, relu, kmax, kmin;
+  float two_inv; // 2 / delta
+};
+
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void split3(float x, __nv_bfloat16 &h, __nv_bfloat16 &m, __nv_bfloat16 &l) {
@@ -137,7 +146,8 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volati
 
 __global__ void __launch_bounds__(kThreadsNC, 1)
     narrow_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_xs, const __nv_bfloat16 *__restrict__ wprep,
-                               const float *__restrict__ bias, float *__restrict__ y, NarrowConv g, int *status) {
+                               const float *__restrict__ bias, float *__restrict__ y, NarrowConv g, int *status,
+                               NarrowCodesOut co) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t *a_ring = smem;                                 // [stage][piece][112 rows][128 B], swizzled
@@ -380,7 +390,39 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
         ptx::tmem_ld_32x32(t0 + (uint32_t)(64 + half * 32), r1);  // with w_mid
         ptx::tmem_ld_32x32(t0 + (uint32_t)(128 + half * 32), r2); // with w_lo
         ptx::tmem_ld_wait();
-        if (px < g.Wo) {
+        if (co.codes != nullptr) {
+          if (px < g.Wo && half * 32 < co.slots) {
+            const float cap = (float)(2 * co.kmax) + 0.5f;
+            uint32_t wds[8];
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              uint32_t packed = 0;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const int j = 4 * j4 + k, o = half * 32 + j;
+                float v = __fadd_rn(__fadd_rn(__uint_as_float(r2[j]), __uint_as_float(r1[j])), __uint_as_float(r0[j]));
+                if (bias && o < g.Ko)
+                  v = __fadd_rn(v, __ldg(bias + o));
+                int code;
+                if (co.relu) {
+                  v = fmaxf(v, 0.0f);
+                  code = (__float2int_rd(fminf(__fmul_rn(v, co.two_inv), cap)) + 1) >> 1;
+                } else {
+                  const int m = (__float2int_rd(fminf(__fmul_rn(fabsf(v), co.two_inv), cap)) + 1) >> 1;
+                  code = v < 0.0f ? max(-m, co.kmin) : m;
+                }
+                code = o < g.Ko ? code : 0;
+                packed |= ((uint32_t)code & 0xffu) << (8 * k);
+              }
+              wds[j4] = packed;
+            }
+            uint4 *cp = reinterpret_cast<uint4 *>(co.codes + ((int64_t)n * plane + (int64_t)oy * g.Wo + px) * co.slots +
+                                                  half * 32);
+            cp[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+            if (half * 32 + 16 < co.slots)
+              cp[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
+          }
+        } else if (px < g.Wo) {
           float *yp = yrow + (int64_t)(half * 32) * plane;
 #pragma unroll
           for (int j = 0; j < 32; ++j, yp += plane) {
@@ -440,7 +482,9 @@ bool narrow_conv_applies(const float *x, int channels, int height, int width, in
 
 int narrow_conv_tc(const float *x, const float *w, const float *bias, float *y, int batch, int channels, int height,
                    int width, int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w, int stride_h,
-                   int stride_w, int Ho, int Wo, cudaStream_t st) {
+                   int stride_w, int Ho, int Wo, cudaStream_t st, int8_t *y_codes, int slots, int relu, int kmax,
+                   int kmin, float delta) {
+  NarrowCodesOut co{y_codes, slots, relu, kmax, kmin, y_codes ? 2.0f / delta : 0.0f};
   NarrowConv g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, Ho, Wo};
   NB_CHECK(batch <= 65535, NB200_ENOTIMPL, "batch larger than 65535");
   const size_t xs_bytes = (size_t)3 * batch * height * kPatchPitch * 2;
@@ -472,7 +516,7 @@ int narrow_conv_tc(const float *x, const float *w, const float *bias, float *y, 
   NB_TRY(device_status_word(&status));
   const int tiles = batch * Ho;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  narrow_conv_tcgen05_kernel<<<grid, kThreadsNC, kSmemNC, st>>>(map_xs, wprep, bias, y, g, status);
+  narrow_conv_tcgen05_kernel<<<grid, kThreadsNC, kSmemNC, st>>>(map_xs, wprep, bias, y, g, status, co);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }

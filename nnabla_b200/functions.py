@@ -988,6 +988,82 @@ def binary_convolution_from_codes_prepared(x_codes, x_shape, prepared, bias=None
 
 
 # ---------------------------------------------------------------------------
+# Layers with batch normalization folded in (inference)
+# ---------------------------------------------------------------------------
+
+def convolution_codes_folded(x_codes, x_shape, prepared, scale, bias=None, pad=None, stride=None, dilation=None,
+                             residual_codes=None, residual_delta=None, residual=None, relu=True, sign=True, n=8,
+                             delta=2 ** -4, output="codes"):
+    """A binary-weight convolution whose BatchNormalization was folded into a per-map factor and
+    bias (batch_normalization_folding.py:92-200), with Add2 of the residual, ReLU and
+    FixedPointQuantize in the convolution's epilogue.
+
+    x_codes: int8 channel-last codes of a tensor of shape x_shape; prepared: prepare_binary_weights;
+    scale [outmaps] = alpha * c0 * (step of x_codes), bias [outmaps] = c1; residual_codes (with
+    residual_delta) or residual (fp32 channel-last [batch, Ho * Wo, slots]) is added before the ReLU.
+    output="codes": int8 codes [batch, Ho * Wo, slots]; output="float": the fp32 value before ReLU
+    and quantizer, channel-last (what a shortcut branch hands to the main branch's epilogue).
+    Returns (result, (batch, outmaps, Ho, Wo))."""
+    if prepared.group != 1:
+        raise C.NB200Error(4, "grouped convolutions are not supported by the folded code path")
+    scale = _check_input(scale, "scale")
+    bias = _check_input(bias, "bias") if bias is not None else None
+    x_shape = tuple(int(v) for v in x_shape)
+    if len(x_shape) != 4:
+        raise C.NB200Error(4, "only 2-D convolution with one batch axis is implemented for code tensors")
+    like_x = torch.empty(x_shape, dtype=torch.float32, device="meta")
+    like_w = torch.empty(prepared.shape, dtype=torch.float32, device="meta")
+    batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
+        like_x, like_w, bias, 1, pad, stride, dilation, 1)
+    x_codes = _check_codes(x_codes, batch, H * W, Cin, 1, "x_codes")
+    if scale.numel() != Ko:
+        raise RuntimeError("Size of scale must be equal to the number of output maps.")
+    dev = x_codes.device
+    Ho, Wo = out_shape[2], out_shape[3]
+    slots = codes_nhwc_slots(Ko, 1)
+    if residual_codes is not None:
+        residual_codes = _check_codes(residual_codes, batch, Ho * Wo, Ko, 1, "residual_codes")
+    if residual is not None and tuple(residual.shape) != (batch, Ho * Wo, slots):
+        raise RuntimeError("residual must be channel-last fp32 of shape %s" % ((batch, Ho * Wo, slots),))
+    y_codes = y_f32 = None
+    if output == "codes":
+        y_codes = torch.empty((batch, Ho * Wo, slots), dtype=torch.int8, device=dev)
+    elif output == "float":
+        y_f32 = torch.empty((batch, Ho * Wo, slots), dtype=torch.float32, device=dev)
+    else:
+        raise ValueError("output must be 'codes' or 'float'")
+    with torch.cuda.device(dev):
+        C.call("nb200_convolution_codes_folded_nhwc", C.ptr(x_codes), C.ptr(prepared.side), C.ptr(scale), C.ptr(bias),
+               C.ptr(residual_codes), C.c_float(residual_delta or 0.0), C.ptr(residual), C.ptr(y_codes), C.ptr(y_f32),
+               batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1], stride[0], stride[1], dilation[0], dilation[1],
+               int(bool(relu)), int(bool(sign)), int(n), C.c_float(delta), C.stream_ptr(dev))
+    return (y_codes if y_codes is not None else y_f32), tuple(out_shape)
+
+
+def convolution_relu_fixed_point_codes(x, weight, bias=None, pad=None, stride=None, relu=True, sign=True, n=8,
+                                       delta=2 ** -4):
+    """Full-precision convolution of an input with few channels (a network stem, weights and bias
+    with BatchNormalization folded in), ReLU and FixedPointQuantize in one kernel; the result is
+    int8 channel-last codes. Returns (codes [batch, Ho * Wo, slots], (batch, outmaps, Ho, Wo))."""
+    x, weight = _check_input(x), _check_input(weight, "weight")
+    bias = _check_input(bias, "bias") if bias is not None else None
+    batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
+        x, weight, bias, 1, pad, stride, None, 1)
+    slots = codes_nhwc_slots(Ko, 1)
+    y = torch.empty((batch, out_shape[2] * out_shape[3], slots), dtype=torch.int8, device=x.device)
+    with torch.cuda.device(x.device):
+        C.call("nb200_convolution_relu_fxp_codes_nhwc", C.ptr(x), C.ptr(weight), C.ptr(bias), C.ptr(y), batch, Cin, H,
+               W, Ko, kh, kw, pad[0], pad[1], stride[0], stride[1], int(bool(relu)), int(bool(sign)), int(n),
+               C.c_float(delta), C.stream_ptr(x.device))
+    return y, tuple(out_shape)
+
+
+def global_average_pooling_codes(codes, shape, delta=2 ** -4):
+    """GlobalAveragePooling of a tensor held as channel-last codes: [batch, channels, 1, 1] fp32."""
+    return global_average_pooling(codes_nhwc_to_float(codes, shape, delta))
+
+
+# ---------------------------------------------------------------------------
 # Sibling quantization functions
 # ---------------------------------------------------------------------------
 

@@ -191,6 +191,141 @@ class Runner:
         return self._rec("head/affine", "affine", [g], y)
 
 
+# ---------------------------------------------------------------------------
+# The same network with BatchNormalization folded into the convolutions
+# ---------------------------------------------------------------------------
+
+def fold_batch_normalization(params, eps=1e-5):
+    """Folding constants of every BatchNormalization of the network, computed on the host in
+    float32 exactly as nnabla's BatchNormalizationFolding converter computes them
+    (python/src/nnabla/experimental/graph_converters/batch_normalization_folding.py:176-191):
+    c0 = gamma / sqrt(var + eps), c1 = beta - gamma * mean / sqrt(var + eps); a convolution
+    followed by that BN becomes a convolution with weights c0 * w and bias c1.
+    Returns {bn name: (c0, c1)} (numpy float32)."""
+    out = {}
+    for key in params:
+        if not key.endswith("/gamma"):
+            continue
+        name = key[:-len("/gamma")]
+        host = lambda a: np.asarray(a.detach().cpu().numpy() if hasattr(a, "detach") else a, np.float32)
+        beta, gamma = host(params[name + "/beta"]), host(params[name + "/gamma"])
+        mean, var = host(params[name + "/mean"]), host(params[name + "/var"])
+        std = np.sqrt(var + np.float32(eps))
+        out[name] = (gamma / std, beta - (gamma * mean) / std)
+    return out
+
+
+def folded_layers():
+    """(convolution name, BN name, kernel, stride) of the network's binary-weight layers, in order,
+    with the block structure: yields ("block", name, cin, c, stride, has_shortcut)."""
+    cin = 64
+    for s, (c, stride) in enumerate(STAGES):
+        for b in range(2):
+            st = stride if b == 0 else 1
+            yield "stage%d/block%d" % (s + 1, b), cin, c, st, (st != 1 or cin != c)
+            cin = c
+
+
+def folded_reference(ops, params, x, binarize, trace=None):
+    """The folded graph on a plain function namespace (fp32 NCHW arrays; the oracle's): every
+    Convolution -> BatchNormalization pair is one Convolution with folded weights and bias, as the
+    converter leaves it, followed by the graph's own Add2 / ReLU / FixedPointQuantize /
+    MaxPooling functions. `binarize(w)` returns (sign(w), alpha) of a binary-weight layer, whose
+    effective weights sign(w) * alpha are what gets folded. trace (optional list) receives
+    (layer name, output of the layer's quantizer or, for a shortcut branch, of its convolution)."""
+    fold = fold_batch_normalization(params)
+    f32 = np.float32
+
+    def conv(name, bn, h, k, stride, binary=True):
+        w = np.asarray(params[name + "/W"], f32)
+        if binary:
+            wb, alpha = binarize(w)
+            w = wb * alpha.reshape(-1, 1, 1, 1)
+        c0, c1 = fold[bn]
+        return ops.convolution(h, (c0.reshape(-1, 1, 1, 1) * w).astype(f32), c1.astype(f32), 1, (k // 2, k // 2),
+                               (stride, stride), (1, 1), 1)
+
+    def rec(name, y):
+        if trace is not None:
+            trace.append((name, y))
+        return y
+    q = lambda v: ops.fixed_point_quantize(ops.relu(v), True, 8, DELTA)
+    h = rec("stem", q(conv("stem/conv", "stem/bn", x, 7, 2, binary=False)))
+    h = rec("stem/pool", ops.max_pooling(h, (3, 3), (2, 2), True, (1, 1)))
+    for name, cin, c, st, has_sc in folded_layers():
+        r = rec(name + "/conv1", q(conv(name + "/conv1", name + "/bn1", h, 3, st)))
+        r = conv(name + "/conv2", name + "/bn2", r, 3, 1)
+        sc = rec(name + "/shortcut", conv(name + "/shortcut", name + "/bn_s", h, 1, st)) if has_sc else h
+        h = rec(name + "/conv2", q(ops.add2(r, sc)))
+    g = ops.global_average_pooling(h)
+    return ops.affine(g, params["head/W"], params["head/b"], 1)
+
+
+class FoldedRunner:
+    """The folded graph on the GPU: one kernel per convolution, each with its folded scale and
+    bias, the residual addition, ReLU and FixedPointQuantize in its epilogue, int8 channel-last
+    codes between the layers (nnabla_b200.functions.convolution_codes_folded). Weights are
+    binarised and the folding constants computed once, at construction (a graph conversion, as
+    the reference's converter is). The logits follow the folded graph, not the unfolded one bit
+    for bit: folding moves roundings, as it does in the reference."""
+
+    def __init__(self, ops, params, trace=None):
+        import torch
+        self.ops, self.trace = ops, trace
+        dev = params["stem/conv/W"].device
+        up = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(dev)
+        host = lambda a: a.detach().cpu().numpy()
+        fold = fold_batch_normalization(params)
+        c0, c1 = fold["stem/bn"]
+        self.stem_w = up(c0.reshape(-1, 1, 1, 1) * host(params["stem/conv/W"]))
+        self.stem_b = up(c1)
+        self.layers = {}
+
+        def add(conv, bn):
+            prep = ops.prepare_binary_weights(params[conv + "/W"], 1, 1.0)
+            k0, k1 = fold[bn]
+            scale = (host(prep.alpha) * k0).astype(np.float32) * np.float32(DELTA)
+            self.layers[conv] = (prep, up(scale), up(k1))
+        for name, cin, c, st, has_sc in folded_layers():
+            add(name + "/conv1", name + "/bn1")
+            add(name + "/conv2", name + "/bn2")
+            if has_sc:
+                add(name + "/shortcut", name + "/bn_s")
+        self.head = (params["head/W"], params["head/b"])
+
+    def _rec(self, name, x, y, shape, **kw):
+        if self.trace is not None:
+            self.trace.append(dict(layer=name, input=x, output=y, shape=shape, **kw))
+
+    def __call__(self, x):
+        o = self.ops
+        hc, shape = o.convolution_relu_fixed_point_codes(x, self.stem_w, self.stem_b, (3, 3), (2, 2), True, True, 8,
+                                                         DELTA)
+        self._rec("stem", x, hc, shape)
+        pc, pshape = o.max_pooling_codes(hc, shape, (3, 3), (2, 2), True, (1, 1))
+        self._rec("stem/pool", hc, pc, pshape, in_shape=shape)
+        hc, shape = pc, pshape
+        for name, cin, c, st, has_sc in folded_layers():
+            p1, s1, b1 = self.layers[name + "/conv1"]
+            r, rshape = o.convolution_codes_folded(hc, shape, p1, s1, b1, (1, 1), (st, st), (1, 1))
+            self._rec(name + "/conv1", hc, r, rshape, in_shape=shape, stride=st, k=3)
+            p2, s2, b2 = self.layers[name + "/conv2"]
+            if has_sc:
+                ps, ss, bs = self.layers[name + "/shortcut"]
+                sc, _ = o.convolution_codes_folded(hc, shape, ps, ss, bs, (0, 0), (st, st), (1, 1), relu=False,
+                                                   output="float")
+                self._rec(name + "/shortcut", hc, sc, rshape, in_shape=shape, stride=st, k=1)
+                out, _ = o.convolution_codes_folded(r, rshape, p2, s2, b2, (1, 1), (1, 1), (1, 1), residual=sc)
+                self._rec(name + "/conv2", r, out, rshape, in_shape=rshape, stride=1, k=3, residual=sc)
+            else:
+                out, _ = o.convolution_codes_folded(r, rshape, p2, s2, b2, (1, 1), (1, 1), (1, 1), residual_codes=hc,
+                                                    residual_delta=DELTA)
+                self._rec(name + "/conv2", r, out, rshape, in_shape=rshape, stride=1, k=3, residual_codes=hc)
+            hc, shape = out, rshape
+        g = o.global_average_pooling_codes(hc, shape, DELTA)
+        return o.affine(g, self.head[0], self.head[1], 1)
+
+
 def conv_macs_per_image(height=224, width=224, num_classes=1000):
     """Multiply-accumulates of the convolutions and the affine per image,
     counted from the layer shapes."""

@@ -101,3 +101,11 @@ def reference():
     ns.binary_weight_convolution = bwc
     ns.affine = lambda x, w, b=None, base_axis=1, **kw: ref.affine(x, w, b, base_axis)
     return ns
+
+
+def binarize(w):
+    """(sign(w), alpha) of a binary-weight convolution's weights [outmaps, ...]
+    (binary_weight_convolution.cpp:81-104), for graphs that fold them into a plain convolution."""
+    w = np.asarray(w, np.float32)
+    wb, alpha, _ = oracle.binarize_rows(w.reshape(w.shape[0], -1), 1.0)
+    return wb.reshape(w.shape), alpha
