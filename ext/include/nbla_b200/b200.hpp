@@ -106,24 +106,40 @@ public:
   static Context filter_context(const Context &ctx);
 };
 
-/** Fixed-point tags: which device arrays currently hold the output of
-    FixedPointQuantize with at most 8 bits, and with which step size. The
-    contraction functions consult it to take the exact int8 tensor-core path.
-    Keyed by SyncedArray and its modification count
-    (include/nbla/synced_array.hpp:183), so any later write invalidates a tag. */
-void fxp_tag_set(const Variable *v, float delta);
-float fxp_tag_get(const Variable *v); // 0 when untagged or stale
+/** Identity of the current contents of a variable's data. Two equal, valid
+    stamps mean nothing wrote to the array in between.
 
-/** Identity of the current contents of a variable's data: the SyncedArray and
-    its modification count (include/nbla/synced_array.hpp:183). Two equal
-    stamps of a live array mean nothing wrote to it in between. */
+    SyncedArray::modification_count (include/nbla/synced_array.hpp:183) cannot
+    serve alone: every cast() runs clear_all_array(), which sets the count to 0,
+    and then increments it (src/nbla/synced_array.cpp:185-193, :484-489), so it
+    reads 1 after every write; only zero() and fill() move it further. The
+    stamp therefore also carries a write generation that this backend keeps
+    itself through nnabla's SyncedArrayCallback hook (synced_array.hpp:310-345):
+    every CAST or CLEAR of any SyncedArray, on any backend, gives that array a
+    new, never repeated generation. The hook is a single process-wide slot; if
+    another component takes it over (the LMS scheduler does), generations stop
+    moving, so write_tracking_alive() probes the hook and stamps taken while it
+    is dead are invalid (valid == false, never equal to anything). */
 struct DataStamp {
   const SyncedArray *array = nullptr;
   size_t count = 0;
-  bool operator==(const DataStamp &o) const { return array == o.array && count == o.count; }
+  unsigned long long generation = 0;
+  bool valid = false;
+  bool operator==(const DataStamp &o) const {
+    return valid && o.valid && array == o.array && count == o.count && generation == o.generation;
+  }
   bool operator!=(const DataStamp &o) const { return !(*this == o); }
 };
 DataStamp data_stamp(const Variable *v);
+bool write_tracking_alive();
+
+/** Fixed-point tags: which arrays currently hold the output of
+    FixedPointQuantize with at most 8 bits, and with which step size. The
+    contraction functions consult them to take the exact int8 tensor-core path.
+    A tag is the data stamp at the time of tagging: any later write to the array
+    (by any backend) makes it stale. */
+void fxp_tag_set(const Variable *v, float delta);
+float fxp_tag_get(const Variable *v); // 0 when untagged or stale
 
 } // namespace nbla
 #endif

@@ -7,6 +7,7 @@
 #include <nbla/memory/caching_allocator_with_buckets.hpp>
 #include <nbla/memory/naive_allocator.hpp>
 #include <nbla/singleton_manager-internal.hpp>
+#include <nbla/synced_array.hpp>
 
 #include <nnabla_b200.h>
 
@@ -14,6 +15,7 @@
 #include <memory>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 
 namespace nbla {
 
@@ -65,11 +67,63 @@ void b200_reset_counters() {
   g_counters.clear();
 }
 
+// ---- write generations through nnabla's SyncedArrayCallback hook -------------
+namespace {
+std::mutex g_gen_mutex;
+std::unordered_map<const SyncedArray *, unsigned long long> g_generation;
+unsigned long long g_serial = 0;
+
+void on_synced_array_event(SyncedArrayPtr sa, const SyncedArrayCallbackTag tag, const dtypes, const Context &,
+                           const bool, const bool, const bool) {
+  if (tag == SyncedArrayCallbackTag::GET)
+    return; // a read leaves the contents as they are
+  std::lock_guard<std::mutex> lock(g_gen_mutex);
+  if (tag == SyncedArrayCallbackTag::CLEAR) {
+    g_generation.erase(sa.get()); // contents gone; a stamp of them can never match again
+    return;
+  }
+  if (g_generation.size() > (1u << 20))
+    g_generation.clear(); // arrays that died without a clear(); every stamp goes stale once
+  g_generation[sa.get()] = ++g_serial;
+}
+} // namespace
+
+void install_write_tracking() {
+  SingletonManager::get<SyncedArrayCallback>()->set_callback_func(on_synced_array_event);
+}
+
+bool write_tracking_alive() {
+  // A cast of a private one-element host array must move its generation: if it does not, another
+  // component has replaced the hook.
+  static SyncedArrayPtr probe = std::make_shared<SyncedArray>(1);
+  static std::mutex m;
+  std::lock_guard<std::mutex> lock(m);
+  unsigned long long before = 0, after = 0;
+  {
+    std::lock_guard<std::mutex> l2(g_gen_mutex);
+    auto it = g_generation.find(probe.get());
+    before = it == g_generation.end() ? 0 : it->second;
+  }
+  probe->cast(dtypes::FLOAT, Context({"cpu:float"}, "CpuArray", ""), true);
+  {
+    std::lock_guard<std::mutex> l2(g_gen_mutex);
+    auto it = g_generation.find(probe.get());
+    after = it == g_generation.end() ? 0 : it->second;
+  }
+  return after != 0 && after != before;
+}
+
 DataStamp data_stamp(const Variable *v) {
   SyncedArrayPtr a = const_cast<Variable *>(v)->data()->array();
   DataStamp s;
   s.array = a.get();
   s.count = a->modification_count();
+  {
+    std::lock_guard<std::mutex> lock(g_gen_mutex);
+    auto it = g_generation.find(a.get());
+    s.generation = it == g_generation.end() ? 0 : it->second;
+  }
+  s.valid = s.generation != 0 && write_tracking_alive();
   return s;
 }
 
@@ -239,33 +293,34 @@ void synchronizer_b200_to_cpu(Array *src, Array *dst, const int async_flags) {
 // -------------------------------------------------------------- fixed-point tags
 namespace {
 struct FxpTag {
-  std::weak_ptr<SyncedArray> owner; // a freed array whose address is reused must not inherit the tag
-  size_t count;
+  DataStamp stamp;
   float delta;
 };
 std::mutex g_tag_mutex;
-std::map<const SyncedArray *, FxpTag> g_tags;
+std::unordered_map<const SyncedArray *, FxpTag> g_tags;
 } // namespace
 
 void fxp_tag_set(const Variable *v, float delta) {
-  SyncedArrayPtr a = const_cast<Variable *>(v)->data()->array();
+  const DataStamp s = data_stamp(v);
   std::lock_guard<std::mutex> lock(g_tag_mutex);
-  if (g_tags.size() > 1024) {
-    for (auto it = g_tags.begin(); it != g_tags.end();)
-      it = it->second.owner.expired() ? g_tags.erase(it) : std::next(it);
-  }
-  g_tags[a.get()] = FxpTag{a, a->modification_count(), delta};
+  if (g_tags.size() > 4096)
+    g_tags.clear(); // tags of arrays long gone; the live ones are set again by their next forward
+  if (s.valid)
+    g_tags[s.array] = FxpTag{s, delta};
+  else
+    g_tags.erase(s.array);
 }
 
 float fxp_tag_get(const Variable *v) {
-  SyncedArrayPtr a = const_cast<Variable *>(v)->data()->array();
+  const DataStamp s = data_stamp(v);
   std::lock_guard<std::mutex> lock(g_tag_mutex);
-  auto it = g_tags.find(a.get());
+  auto it = g_tags.find(s.array);
   if (it == g_tags.end())
     return 0.0f;
-  SyncedArrayPtr owner = it->second.owner.lock();
-  if (owner.get() != a.get() || it->second.count != a->modification_count())
+  if (it->second.stamp != s) {
+    g_tags.erase(it);
     return 0.0f;
+  }
   return it->second.delta;
 }
 

@@ -45,6 +45,7 @@
 
 namespace nbla {
 
+void install_write_tracking(); // b200_backend.cpp
 void synchronizer_cpu_to_b200(Array *src, Array *dst, const int async_flags);
 void synchronizer_b200_to_cpu(Array *src, Array *dst, const int async_flags);
 
@@ -880,6 +881,7 @@ void init_b200() {
   done = true;
   init_cpu();
   nb200_check(nb200_check_device(), "init_b200");
+  install_write_tracking();
 
   NBLA_REGISTER_BACKEND("b200", []() { return SingletonManager::get<B200>(); });
   NBLA_REGISTER_ARRAY_CREATOR(B200Array);

@@ -301,12 +301,13 @@ int nb200_binary_convolution_codes_prepared_f32(const int8_t *x_codes, const int
  * nb200_convolution_codes_folded_nhwc: x_codes [batch][H * W][slots(channels)] int8
  * (value = code * the step already folded into scale), side = weights prepared by
  * nb200_binary_weights_prepare_i8 (group 1), scale / bias per output map:
- *   v = float(acc) * scale[o] + bias[o]          (bias may be NULL)
- *   v += res_codes * res_delta  |  v += res_f32  (residual in the result's own
- *                                                 channel-last layout; at most one)
- *   y_f32 (channel-last [batch][Ho * Wo][slots(outmaps)], may be NULL) = v
- *   y_codes (may be NULL) = code of FixedPointQuantize(sign, n, delta)(relu ? max(v, 0) : v)
- * delta must be a power of two, n - sign <= 7, all tensors 16-byte aligned. */
+ *   v = fma(acc, scale[o], bias[o])                       (bias may be NULL)
+ *   v = fma(res_codes, res_delta, v)  |  v = v + res_f32  (residual in the result's own
+ *                                                          channel-last layout; at most one)
+ *   either y_f32 (channel-last [batch][Ho * Wo][slots(outmaps)]) = v
+ *   or y_codes = code of FixedPointQuantize(sign, n, delta)(relu ? max(v, 0) : v)
+ * (exactly one of y_f32 / y_codes; one rounding per fused multiply-add). delta must be a
+ * power of two, n - sign <= 7, all tensors 16-byte aligned. */
 int nb200_convolution_codes_folded_nhwc(const int8_t *x_codes, const int8_t *side, const float *scale,
                                         const float *bias, const int8_t *res_codes, float res_delta,
                                         const float *res_f32, int8_t *y_codes, float *y_f32, int batch, int channels,

@@ -473,7 +473,11 @@ namespace {
 // Convolution of activation codes with the layer's inference tail in the
 // epilogue (conv_codes.cuh): pixels on the MMA rows, channel-last codes out.
 // ---------------------------------------------------------------------------
-template <int BN, int STAGES, int RB>
+#ifdef NB200_CC_TRACE
+long long *g_cc_trace = nullptr;
+#endif
+
+template <int BN, int STAGES, int RB, bool kResidentB = false, bool kHalo = false>
 int launch_conv_codes(const ConvGeometry &g, const int8_t *x_codes, int64_t ctot, const int8_t *side, int64_t wpitch,
                       int cblocks, int h_box, int n_box, int slots_out, const ConvCodesEpilogue &ep, cudaStream_t st) {
   CUtensorMap mx, mw;
@@ -481,9 +485,16 @@ int launch_conv_codes(const ConvGeometry &g, const int8_t *x_codes, int64_t ctot
   const uint64_t dims[5] = {(uint64_t)ctot, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N, 1};
   const uint64_t strides[4] = {(uint64_t)ctot, (uint64_t)ctot * g.W, (uint64_t)ctot * g.W * g.H,
                                (uint64_t)ctot * g.W * g.H * g.N};
-  const uint32_t box[5] = {(uint32_t)RB, (uint32_t)(g.Wo * g.sw), (uint32_t)(h_box * g.sh), (uint32_t)n_box, 1};
-  const uint32_t estr[5] = {1, (uint32_t)g.sw, (uint32_t)g.sh, 1, 1};
-  NB_TRY(encode_tiled(&mx, 1, 5, x_codes, dims, strides, box, estr, RB));
+  const int wp = g.Wo + (g.kw - 1) * g.dw, hp = h_box + (g.kh - 1) * g.dh;
+  if (kHalo) {
+    // one box of hp x wp input pixels per tile and channel block
+    const uint32_t hbox[5] = {(uint32_t)RB, (uint32_t)wp, (uint32_t)hp, 1, 1};
+    NB_TRY(encode_tiled(&mx, 1, 5, x_codes, dims, strides, hbox, nullptr, RB));
+  } else {
+    const uint32_t box[5] = {(uint32_t)RB, (uint32_t)(g.Wo * g.sw), (uint32_t)(h_box * g.sh), (uint32_t)n_box, 1};
+    const uint32_t estr[5] = {1, (uint32_t)g.sw, (uint32_t)g.sh, 1, 1};
+    NB_TRY(encode_tiled(&mx, 1, 5, x_codes, dims, strides, box, estr, RB));
+  }
   // weights: (K, Ko, 1), BN maps per box
   NB_TRY(make_operand_map(&mw, side, true, wpitch, wpitch, g.Ko, 1, BN, RB));
   ConvCodesProblem p;
@@ -508,14 +519,24 @@ int launch_conv_codes(const ConvGeometry &g, const int8_t *x_codes, int64_t ctot
   p.dw = g.dw;
   p.pixels = n_box * h_box * g.Wo;
   p.slots_out = slots_out;
-  auto kernel = conv_codes_tcgen05_kernel<BN, STAGES, RB>;
-  constexpr size_t smem = conv_codes_smem_bytes<BN, STAGES, RB>();
-  static_assert(smem <= 227 * 1024, "shared memory budget");
+  p.wp = wp;
+  p.hp = hp;
+  // rows a shifted descriptor may read: the largest tap shift plus the 128 rows of the MMA, in whole
+  // swizzle patterns of 8 rows (rows the box does not write hold stale data that no stored pixel uses)
+  const int rows_alloc = (((g.kh - 1) * g.dh * wp + (g.kw - 1) * g.dw + kTileM) + 7) / 8 * 8;
+  p.a_tile_bytes = (rows_alloc > hp * wp ? rows_alloc : (hp * wp + 7) / 8 * 8) * RB;
+  auto kernel = conv_codes_tcgen05_kernel<BN, STAGES, RB, kResidentB, kHalo>;
+  constexpr size_t smem_fixed = conv_codes_smem_bytes<BN, STAGES, RB, kResidentB, kHalo>();
+  static_assert(smem_fixed <= 227 * 1024, "shared memory budget");
+  const size_t smem = smem_fixed + (kResidentB ? (size_t)p.taps * p.cblocks * BN * RB : 0) +
+                      (kHalo ? (size_t)2 * p.cblocks * p.a_tile_bytes : 0);
+  NB_CHECK(smem <= 227 * 1024, NB200_EVALUE, "resident weights do not fit in shared memory");
   static bool configured[64];
   int dev = 0;
   NB_CUDA(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    NB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    NB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kResidentB ? 227 * 1024 : (int)smem));
     configured[dev & 63] = true;
   }
   int *status = nullptr;
@@ -533,6 +554,7 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
   NB_TRY(check_geometry(g));
   NB_CHECK(g.group == 1, NB200_ENOTIMPL, "grouped convolutions are not supported by the folded code path");
   NB_CHECK(x_codes && side && scale && (y_codes || y_f32), NB200_EVALUE, "null data pointer");
+  NB_CHECK(!(y_codes && y_f32), NB200_EVALUE, "the result is either codes or fp32, not both");
   NB_CHECK(!(res_codes && res_f32), NB200_EVALUE, "the residual is either codes or fp32, not both");
   NB_CHECK(res_codes == nullptr || res_delta > 0.f, NB200_EVALUE, "res_delta should be positive");
   NB_CHECK(g.Ko <= kCodesMaxMaps, NB200_ENOTIMPL, "more than %d output maps", kCodesMaxMaps);
@@ -542,13 +564,12 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
   ep.scale = scale;
   ep.bias = bias;
   ep.res_codes = res_codes;
-  ep.res_delta = res_delta;
   ep.res_f32 = res_f32;
   ep.y_codes = y_codes;
-  ep.y_f32 = y_f32;
+  ep.y_f32 = y_codes ? nullptr : y_f32;
   ep.relu = relu;
-  ep.delta = 1.0f;
-  ep.inv_delta = 1.0f;
+  ep.out_scale = 1.0f;
+  ep.kmax = ep.kmin = 0;
   if (y_codes) {
     // the quantizer's setup (fixed_point_quantize.cpp:31-42); the step must be a power of two
     NB_CHECK(n > 0 && delta > 0.f, NB200_EVALUE, "Both bit width and delta should be positive.");
@@ -558,11 +579,14 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
     NB_CHECK(std::frexp(delta, &ex) == 0.5f && ex > -100 && ex < 100, NB200_ENOTIMPL,
              "the folded code path needs a power-of-two quantizer step (got %g)", delta);
     NB_CHECK(relu || sign, NB200_ENOTIMPL, "an unsigned quantizer without ReLU is not supported");
-    ep.delta = delta;
-    ep.inv_delta = 1.0f / delta;
+    ep.out_scale = 2.0f / delta;
     ep.kmax = (1 << nn) - 1;
     ep.kmin = sign ? -ep.kmax : 0;
   }
+  ep.res_scale = (res_codes ? res_delta : 1.0f) * ep.out_scale;
+#ifdef NB200_CC_TRACE
+  ep.trace = g_cc_trace;
+#endif
   const int64_t slots_out = codes_slots(g.Ko, 1);
   NB_CHECK((((reinterpret_cast<uintptr_t>(x_codes) | reinterpret_cast<uintptr_t>(side) |
               reinterpret_cast<uintptr_t>(res_codes) | reinterpret_cast<uintptr_t>(res_f32) |
@@ -582,6 +606,52 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
   NB_CHECK(h_box * n_box * g.Wo <= 128, NB200_ENOTIMPL, "no pixel box of at most 128 pixels");
 #define NB_CC(BN_, ST_, RB_)                                                                                          \
   return launch_conv_codes<BN_, ST_, RB_>(g, x_codes, ctot, side, wpitch, cblocks, h_box, n_box, (int)slots_out, ep, st)
+#define NB_CC_RES(BN_, ST_, RB_)                                                                                      \
+  return launch_conv_codes<BN_, ST_, RB_, true>(g, x_codes, ctot, side, wpitch, cblocks, h_box, n_box, (int)slots_out, \
+                                                ep, st)
+#define NB_CC_HALO(BN_, RB_)                                                                                          \
+  return launch_conv_codes<BN_, 1, RB_, true, true>(g, x_codes, ctot, side, wpitch, cblocks, hh, 1, (int)slots_out,   \
+                                                    ep, st)
+  // weights resident in shared memory when one column tile covers the maps and they fit beside the ring
+  const size_t w_bytes = (size_t)g.kh * g.kw * cblocks * (narrow_rows ? 64 : 128);
+  if (g.sh == 1 && g.sw == 1 && g.kh * g.kw > 1 && g.Ko <= 128) {
+    // halo form: the tile's rows are h rows of the padded width wp; one input box per tile
+    const int RBh = narrow_rows ? 64 : 128, BNh = g.Ko <= 64 ? 64 : 128;
+    const int wp = g.Wo + (g.kw - 1) * g.dw;
+    int hh = wp <= 128 ? (128 - g.Wo) / wp + 1 : 0; // (hh - 1) * wp + Wo <= 128
+    if (hh > g.Ho)
+      hh = g.Ho;
+    if (hh >= 1) {
+      for (int h = hh; h >= 1; --h) // prefer a divisor of Ho unless it wastes over a third of the rows
+        if (g.Ho % h == 0) {
+          if (3 * h >= 2 * hh)
+            hh = h;
+          break;
+        }
+      const int hp = hh + (g.kh - 1) * g.dh;
+      const int rows_alloc = (((g.kh - 1) * g.dh * wp + (g.kw - 1) * g.dw + kTileM) + 7) / 8 * 8;
+      const size_t a_bytes = (size_t)(rows_alloc > hp * wp ? rows_alloc : (hp * wp + 7) / 8 * 8) * RBh;
+      const size_t need = 2 * cblocks * a_bytes + w_bytes * BNh + 8 * 1024;
+      if (need <= 220 * 1024 && wp <= 256 && hp <= 256) {
+        if (narrow_rows) {
+          if (g.Ko <= 64)
+            NB_CC_HALO(64, 64);
+          NB_CC_HALO(128, 64);
+        }
+        if (g.Ko <= 64)
+          NB_CC_HALO(64, 128);
+        NB_CC_HALO(128, 128);
+      }
+    }
+  }
+  if (narrow_rows && g.Ko <= 64 && w_bytes * 64 <= 96 * 1024)
+    NB_CC_RES(64, 12, 64);
+  if (narrow_rows && g.Ko <= 128 && w_bytes * 128 <= 96 * 1024)
+    NB_CC_RES(128, 12, 64);
+  if (!narrow_rows && g.Ko <= 64 && w_bytes * 64 <= 128 * 1024)
+    NB_CC_RES(64, 5, 128);
+  if (!narrow_rows && g.Ko <= 128 && w_bytes * 128 <= 150 * 1024)
+    NB_CC_RES(128, 4, 128);
   if (narrow_rows) {
     if (g.Ko <= 64)
       NB_CC(64, 10, 64);
@@ -595,6 +665,8 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
     NB_CC(128, 6, 128);
   NB_CC(256, 4, 128);
 #undef NB_CC
+#undef NB_CC_RES
+#undef NB_CC_HALO
 }
 } // namespace
 extern "C" {
@@ -696,4 +768,7 @@ int nb200_convolution_codes_folded_nhwc(const int8_t *x_codes, const int8_t *sid
   return convolution_codes_folded(x_codes, side, scale, bias, res_codes, res_delta, res_f32, y_codes, y_f32, g, relu,
                                   sign, n, delta, as_stream(stream));
 }
+#ifdef NB200_CC_TRACE
+void nb200_debug_conv_trace(long long *buffer) { g_cc_trace = buffer; }
+#endif
 }

@@ -32,6 +32,17 @@ static int get_encode_fn(EncodeTiledFn *out) {
   return NB200_OK;
 }
 
+static CUtensorMapL2promotion l2_promotion() {
+#ifdef NB200_CC_TRACE
+  const char *e = std::getenv("NB_PROMO"); // timing experiments only
+  if (e)
+    return e[0] == '0' ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                       : (e[0] == '1' ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                      : (e[0] == '2' ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_256B));
+#endif
+  return CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+}
+
 // dtype_code: 0 = bf16, 1 = uint8/int8 bytes, 2 = float32
 int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, const uint64_t *dims,
                  const uint64_t *strides_bytes, const uint32_t *box, const uint32_t *elem_strides,
@@ -59,7 +70,7 @@ int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, c
                         swizzle_bytes == 0    ? CU_TENSOR_MAP_SWIZZLE_NONE
                         : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                                               : CU_TENSOR_MAP_SWIZZLE_128B,
-                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        l2_promotion(),
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   NB_CHECK(r == CUDA_SUCCESS, NB200_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return NB200_OK;

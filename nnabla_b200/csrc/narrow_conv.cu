@@ -84,6 +84,14 @@ struct NarrowCodesOut {
   float two_inv; // 2 / delta
 };
 
+// Four codes in [-128, 127] (saturated) -> the four bytes of one word, a in the lowest.
+__device__ __forceinline__ uint32_t pack_codes4(int a, int b, int c, int d) {
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+  return out;
+}
+
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void split3(float x, __nv_bfloat16 &h, __nv_bfloat16 &m, __nv_bfloat16 &l) {
@@ -158,6 +166,12 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
            *patch_full = bars + 8, *patch_empty = bars + 10;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  // bias of every map (0 past Ko or without bias), times 2 / delta when codes are written
+  __shared__ float bias_s[kN];
+  if (threadIdx.x < kN)
+    bias_s[threadIdx.x] = (bias && (int)threadIdx.x < g.Ko)
+                              ? (co.codes ? __fmul_rn(bias[threadIdx.x], co.two_inv) : bias[threadIdx.x])
+                              : 0.0f;
 
   // word offsets, inside a staged piece, of the four words of every 16-byte chunk of the K row:
   // K word wk = (filter row ky, word j2 of its 12-word run) -> ky * 352 + j2
@@ -392,29 +406,27 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
         ptx::tmem_ld_wait();
         if (co.codes != nullptr) {
           if (px < g.Wo && half * 32 < co.slots) {
+            // u = (conv) * (2 / delta) + bias * (2 / delta), one fused multiply-add; then ReLU and the
+            // quantizer of a non-negative value, (floor(u) + 1) >> 1 capped at kmax
             const float cap = (float)(2 * co.kmax) + 0.5f;
             uint32_t wds[8];
 #pragma unroll
             for (int j4 = 0; j4 < 8; ++j4) {
-              uint32_t packed = 0;
+              int c[4];
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                const int j = 4 * j4 + k, o = half * 32 + j;
-                float v = __fadd_rn(__fadd_rn(__uint_as_float(r2[j]), __uint_as_float(r1[j])), __uint_as_float(r0[j]));
-                if (bias && o < g.Ko)
-                  v = __fadd_rn(v, __ldg(bias + o));
-                int code;
+                const int j = 4 * j4 + k;
+                const float conv = __fadd_rn(__fadd_rn(__uint_as_float(r2[j]), __uint_as_float(r1[j])), __uint_as_float(r0[j]));
+                const float u = __fmaf_rn(conv, co.two_inv, bias_s[half * 32 + j]);
                 if (co.relu) {
-                  v = fmaxf(v, 0.0f);
-                  code = (__float2int_rd(fminf(__fmul_rn(v, co.two_inv), cap)) + 1) >> 1;
+                  c[k] = (__float2int_rd(fminf(fmaxf(u, 0.0f), cap)) + 1) >> 1; // a NaN becomes 0
                 } else {
-                  const int m = (__float2int_rd(fminf(__fmul_rn(fabsf(v), co.two_inv), cap)) + 1) >> 1;
-                  code = v < 0.0f ? max(-m, co.kmin) : m;
+                  const int m = (__float2int_rd(fminf(fabsf(u), cap)) + 1) >> 1;
+                  c[k] = u < 0.0f ? max(-m, co.kmin) : m;
                 }
-                code = o < g.Ko ? code : 0;
-                packed |= ((uint32_t)code & 0xffu) << (8 * k);
               }
-              wds[j4] = packed;
+              // maps past Ko have zero weights and zero bias: their code is 0 on its own
+              wds[j4] = pack_codes4(c[0], c[1], c[2], c[3]);
             }
             uint4 *cp = reinterpret_cast<uint4 *>(co.codes + ((int64_t)n * plane + (int64_t)oy * g.Wo + px) * co.slots +
                                                   half * 32);
@@ -430,7 +442,7 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
             if (o < g.Ko) {
               float v = __fadd_rn(__fadd_rn(__uint_as_float(r2[j]), __uint_as_float(r1[j])), __uint_as_float(r0[j]));
               if (bias)
-                v = __fadd_rn(v, __ldg(bias + o));
+                v = __fadd_rn(v, bias_s[o]);
               __stcs(yp, v);
             }
           }

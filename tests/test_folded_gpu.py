@@ -3,8 +3,9 @@ python/src/nnabla/experimental/graph_converters/batch_normalization_folding.py:9
 kernel per convolution with Add2 / ReLU / FixedPointQuantize in the epilogue and int8 codes out.
 
 Two checks per case:
- * EXACT: the kernel's arithmetic (exact integer accumulation, one rounded multiply, one rounded
-   add per step) restated in numpy on the oracle's exact integer convolution: codes bit for bit;
+ * EXACT: the kernel's arithmetic (exact integer accumulation, then one fused multiply-add per step,
+   with the factor 2 / delta folded into its constants) restated in numpy on the oracle's exact
+   integer convolution: codes bit for bit;
  * against the folded graph on the oracle (Convolution with the folded fp32 weights, Add2, ReLU,
    FixedPointQuantize as separate functions): a fp32 convolution rounds where the integer one does
    not, so a value within that rounding of a quantizer tie may land one step away: codes agree up
@@ -115,13 +116,24 @@ def test_folded_convolution(F, case, mode):
     acc = oracle.convolution(np.rint(xq / DELTA).astype(np.float32), wb, None, (pad, pad), (stride, stride),
                              (dil, dil), f64=True)
     assert np.array_equal(acc, np.rint(acc)) and np.abs(acc).max() < 2 ** 24
-    v = acc.astype(np.float32) * scale.reshape(1, -1, 1, 1) + c1.reshape(1, -1, 1, 1)
-    if res is not None:
-        v = v + res
+    # fused multiply-adds in float64 (the products are exact there), rounded once to float32
+    fma = lambda a, b, c: (np.asarray(a, np.float64) * np.asarray(b, np.float64) + np.asarray(c, np.float64)).astype(np.float32)
+    f = np.float32(1.0 if mode == "float_out" else 2.0 / DELTA)  # codes: u is twice the quantizer's argument
+    u = fma(acc, (scale * f).reshape(1, -1, 1, 1), (c1 * f).reshape(1, -1, 1, 1))
+    if mode == "res_codes":
+        u = fma(np.rint(res / (2 * DELTA)), np.float32(2 * DELTA) * f, u)
+    elif mode == "res_float":
+        u = fma(res, f, u)
     if mode == "float_out":
-        assert np.array_equal(bits(from_nhwc(got, shape)), bits(v))
+        assert np.array_equal(bits(from_nhwc(got, shape)), bits(u))
         return
-    assert np.array_equal(from_nhwc(got, shape).astype(np.int64), quant_codes(v, relu, True, 8, DELTA))
+    cap = np.float32(2 * 127 + 0.5)
+    if relu:
+        want_exact = (np.floor(np.minimum(np.maximum(u, 0), cap)).astype(np.int64) + 1) >> 1
+    else:
+        m = (np.floor(np.minimum(np.abs(u), cap)).astype(np.int64) + 1) >> 1
+        want_exact = np.where(u < 0, np.maximum(-m, -127), m)
+    assert np.array_equal(from_nhwc(got, shape).astype(np.int64), want_exact)
     # ---- the folded graph on the oracle: fp32 convolution with folded weights, then the separate functions
     wal = oracle_ops.binarize(w)[1]
     wf = (c0.reshape(-1, 1, 1, 1) * (wb * wal.reshape(-1, 1, 1, 1))).astype(np.float32)
