@@ -35,6 +35,7 @@ def lib():
 
 
 _calls = 0
+_entry = {}  # entry-point name -> ctypes function with its return type set
 
 
 def calls_made():
@@ -46,12 +47,14 @@ def call(name, *args):
     """Calls entry point `name` and raises NB200Error on a non-zero status."""
     global _calls
     _calls += 1
-    L = lib()
-    fn = getattr(L, name)
-    fn.restype = ctypes.c_int
+    fn = _entry.get(name)
+    if fn is None:
+        fn = getattr(lib(), name)
+        fn.restype = ctypes.c_int
+        _entry[name] = fn
     rc = fn(*args)
     if rc != 0:
-        raise NB200Error(rc, L.nb200_last_error().decode("utf-8", "replace"))
+        raise NB200Error(rc, lib().nb200_last_error().decode("utf-8", "replace"))
 
 
 def ptr(t):
@@ -64,8 +67,40 @@ def ptr(t):
 
 
 def stream_ptr(device=None):
+    """torch's current stream of `device` (default: the current device) as a raw cudaStream_t."""
     import torch
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    index = device.index if (device is not None and hasattr(device, "index")) else device
+    if index is None:
+        index = torch.cuda.current_device()
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None:  # no Stream object is built on this path: it is taken dozens of times per forward pass
+        return ctypes.c_void_p(raw(int(index)))
+    return ctypes.c_void_p(torch.cuda.current_stream(index).cuda_stream)
+
+
+class on_device:
+    """`with on_device(dev):` makes `dev` the current CUDA device for the block; when it already
+    is (the common case) nothing is switched, which is much cheaper than torch.cuda.device."""
+    __slots__ = ("index", "prev")
+
+    def __init__(self, device):
+        self.index = device.index if hasattr(device, "index") else device
+        self.prev = None
+
+    def __enter__(self):
+        import torch
+        if self.index is not None:
+            cur = torch.cuda.current_device()
+            if cur != self.index:
+                self.prev = cur
+                torch.cuda.set_device(self.index)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            import torch
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def i64_array(values):

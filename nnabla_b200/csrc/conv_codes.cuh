@@ -83,6 +83,11 @@ struct ConvCodesEpilogue {
   } while (0)
 #endif
 
+// Exact for |a| < 2^22 (the accumulators of this kernel stay below 2^21 in magnitude for K <= 16384).
+__device__ __forceinline__ float int_to_float(int a) {
+  return __fsub_rn(__int_as_float(a + 0x4B400000), 12582912.0f);
+}
+
 // Four int32 codes -> four int8 lanes of one word (a in the lowest byte), each saturated to [-128, 127].
 __device__ __forceinline__ uint32_t pack_s8x4(int a, int b, int c, int d) {
   uint32_t hi, out;
@@ -206,7 +211,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int n0, img0, oy0;
         decode(tile, n0, img0, oy0);
         NB_CC_STAMP(0, (tile - (int)blockIdx.x) / (int)gridDim.x);
-        if (kHalo) {
+        if constexpr (kHalo) {
           const int ab = alocal & 1;
           if (!ptx::mbar_wait(a_empty + ab, ((uint32_t)(alocal >> 1) & 1u) ^ 1u, abort_flag)) {
             if (*abort_flag == 0)
@@ -218,8 +223,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int cb = 0; cb < prob.cblocks; ++cb)
             ptx::tma_load_5d(smem + (size_t)(ab * prob.cblocks + cb) * prob.a_tile_bytes, &map_x, a_full + ab,
                              cb * kElems, -prob.pw, oy0 - prob.ph, img0, 0);
-          continue;
-        }
+        } else {
         for (int kb = 0; kb < k_blocks; ++kb) {
           bool got_slot;
           NB_CC_WAITED(9, (tile - (int)blockIdx.x) / (int)gridDim.x,
@@ -243,6 +247,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             stage = 0;
             phase ^= 1u;
           }
+        }
         }
         NB_CC_STAMP(1, (tile - (int)blockIdx.x) / (int)gridDim.x);
       }
@@ -278,7 +283,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         NB_CC_STAMP(3, local);
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         uint32_t accumulate = 0;
-        if (kHalo) {
+        if constexpr (kHalo) {
           const int ab = local & 1;
           if (!ptx::mbar_wait(a_full + ab, (uint32_t)(local >> 1) & 1u, abort_flag)) {
             if (*abort_flag == 0)
@@ -304,8 +309,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           ptx::mma_commit(a_empty + ab); // the pixel tile is free once these MMAs have read it
           ptx::mma_commit(tmem_full + buf);
-          continue;
-        }
+        } else {
         for (int kb = 0; kb < k_blocks; ++kb) {
           bool got_data;
           NB_CC_WAITED(10, local, got_data = ptx::mbar_wait(full_bar + stage, phase, abort_flag));
@@ -334,6 +338,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         if (ok)
           ptx::mma_commit(tmem_full + buf);
+        }
         NB_CC_STAMP(4, local);
       }
     }
@@ -349,20 +354,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       decode(tile, n0, img0, oy0);
       const int buf = local & 1;
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
-      if (threadIdx.x == 64)
-        NB_CC_STAMP(5, local);
-      const bool got = ptx::mbar_wait(tmem_full + buf, buf_phase, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0) {
-          if (*abort_flag == 0)
-            atomicCAS(status, 0, kStatusEpilogueTimeout);
-          *abort_flag = 1;
-        }
-        break;
-      }
-      ptx::tc_fence_after_sync();
-      if (threadIdx.x == 64)
-        NB_CC_STAMP(6, local);
       // this thread's pixel
       const int row = quarter * 32 + lane;
       bool pix_ok;
@@ -377,18 +368,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         pix_ok = nn < prob.n_box && img < prob.Nimg && q < (prob.Ho - oy0) * prob.Wo;
         pix = (int64_t)img * prob.Ho * prob.Wo + (int64_t)oy0 * prob.Wo + q;
       }
+      // the residual of this warp's first chunk is requested before the accumulator is waited for
+      uint4 ra = make_uint4(0, 0, 0, 0), rb = make_uint4(0, 0, 0, 0);
+      {
+        const int col = n0 + 32 * half;
+        if (ep.res_codes && pix_ok && col < prob.slots_out) {
+          const int64_t off = pix * prob.slots_out + col;
+          ra = __ldg(reinterpret_cast<const uint4 *>(ep.res_codes + off));
+          if (col + 16 < prob.slots_out)
+            rb = __ldg(reinterpret_cast<const uint4 *>(ep.res_codes + off) + 1);
+        }
+      }
+      if (threadIdx.x == 64)
+        NB_CC_STAMP(5, local);
+      const bool got = ptx::mbar_wait(tmem_full + buf, buf_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) {
+          if (*abort_flag == 0)
+            atomicCAS(status, 0, kStatusEpilogueTimeout);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      if (threadIdx.x == 64)
+        NB_CC_STAMP(6, local);
 #pragma unroll 1
       for (int c0 = 32 * half; c0 < BN; c0 += 64) {
         const int col = n0 + c0; // first output map of the chunk
         const bool live = pix_ok && col < prob.slots_out;
         const int64_t off = pix * prob.slots_out + col;
         const bool upper = col + 16 < prob.slots_out; // the pixel's row ends in the middle of this chunk otherwise
-        // the residual is fetched before the accumulator is waited for
-        uint4 ra = make_uint4(0, 0, 0, 0), rb = make_uint4(0, 0, 0, 0);
-        if (ep.res_codes && live) {
+        if (c0 != 32 * half && ep.res_codes && live) { // later chunks: fetched here
           ra = __ldg(reinterpret_cast<const uint4 *>(ep.res_codes + off));
-          if (upper)
-            rb = __ldg(reinterpret_cast<const uint4 *>(ep.res_codes + off) + 1);
+          rb = upper ? __ldg(reinterpret_cast<const uint4 *>(ep.res_codes + off) + 1) : make_uint4(0, 0, 0, 0);
         }
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
@@ -399,19 +412,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           continue;
         // u = acc * scale + bias, one fused multiply-add (scale and bias already carry the factor
         // 2 / delta when codes are written, so u is twice the quantizer's argument)
+        // Integers become floats on the add / multiply pipes instead of the (much narrower) conversion
+        // pipe: for |a| < 2^22, the bit pattern of 1.5 * 2^23 plus a IS the float 1.5 * 2^23 + a.
         float v[32];
 #pragma unroll
         for (int j2 = 0; j2 < 16; ++j2) {
           const float4 k = sb2[(col >> 1) + j2]; // (scale, bias) of two neighbouring maps
-          v[2 * j2] = __fmaf_rn((float)(int)r[2 * j2], k.x, k.y);
-          v[2 * j2 + 1] = __fmaf_rn((float)(int)r[2 * j2 + 1], k.z, k.w);
+          v[2 * j2] = __fmaf_rn(int_to_float((int)r[2 * j2]), k.x, k.y);
+          v[2 * j2 + 1] = __fmaf_rn(int_to_float((int)r[2 * j2 + 1]), k.z, k.w);
         }
         if (ep.res_codes) {
-          const uint32_t w[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+          // code + 128 (one XOR per word) lands in the low mantissa byte of 1.5 * 2^23
+          const uint32_t w[8] = {ra.x ^ 0x80808080u, ra.y ^ 0x80808080u, ra.z ^ 0x80808080u, ra.w ^ 0x80808080u,
+                                 rb.x ^ 0x80808080u, rb.y ^ 0x80808080u, rb.z ^ 0x80808080u, rb.w ^ 0x80808080u};
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int rc = (int)(int8_t)((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
-            v[j] = __fmaf_rn((float)rc, ep.res_scale, v[j]);
+            const float rc = __fsub_rn(__uint_as_float(__byte_perm(w[j >> 2], 0x4B400000u, 0x7650 + (j & 3))),
+                                       12582912.0f + 128.0f);
+            v[j] = __fmaf_rn(rc, ep.res_scale, v[j]);
           }
         } else if (ep.res_f32) {
           const float4 *rp = reinterpret_cast<const float4 *>(ep.res_f32 + off);
@@ -440,9 +458,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int j4 = 0; j4 < 8; ++j4) {
             int c[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              c[k] = (__float2int_rd(fminf(fmaxf(v[4 * j4 + k], 0.0f), cap)) + 1) >> 1; // a NaN becomes 0
-            w[j4] = pack_s8x4(c[0], c[1], c[2], c[3]);
+            for (int k = 0; k < 4; ++k) {
+              // floor of 0 <= u < 2^23 without the conversion pipe: u + 2^23 rounded DOWN has it in its mantissa
+              const float t = __fadd_rd(fminf(fmaxf(v[4 * j4 + k], 0.0f), cap), 8388608.0f); // a NaN becomes 0
+              c[k] = (__float_as_int(t) - 0x4B000000 + 1) >> 1;
+            }
+            w[j4] = (uint32_t)c[0] | ((uint32_t)c[1] << 8) | ((uint32_t)c[2] << 16) | ((uint32_t)c[3] << 24); // each <= 127
           }
         } else {
 #pragma unroll

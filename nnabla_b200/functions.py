@@ -42,7 +42,7 @@ def fixed_point_quantize(x, sign=True, n=8, delta=2 ** -4, quantize=True, ste_fi
         return x
     x = _check_input(x)
     y = _output_like(x, outputs)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_fixed_point_quantize_f32", C.ptr(x), C.ptr(y), C.size_t(x.numel()), int(bool(sign)), int(n),
                C.c_float(delta), C.stream_ptr(x.device))
     return y
@@ -53,7 +53,7 @@ def fixed_point_quantize_with_codes(x, sign=True, n=8, delta=2 ** -4):
     x = _check_input(x)
     y = torch.empty_like(x)
     codes = torch.empty(x.shape, dtype=torch.int8, device=x.device)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_fixed_point_quantize_f32_codes", C.ptr(x), C.ptr(y), C.ptr(codes), C.size_t(x.numel()),
                int(bool(sign)), int(n), C.c_float(delta), C.stream_ptr(x.device))
     return y, codes
@@ -68,7 +68,7 @@ def pow2_quantize(x, sign=True, with_zero=True, n=8, m=1, quantize=True, ste_fin
         return x
     x = _check_input(x)
     y = _output_like(x, outputs)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_pow2_quantize_f32", C.ptr(x), C.ptr(y), C.size_t(x.numel()), int(bool(sign)),
                int(bool(with_zero)), int(n), int(m), C.stream_ptr(x.device))
     return y
@@ -99,7 +99,7 @@ def min_max_quantize(x, qr_min, qr_max, ql_min, ql_max, decay=0.999, x_min_max=F
         if t is not orig:
             raise RuntimeError("qr_min and qr_max are updated in place and must be contiguous")
     y = _output_like(x, outputs)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_min_max_quantize_f32", C.ptr(x), C.i64_array(x.shape), int(x.dim()), C.ptr(qs[0]),
                C.ptr(qs[1]), C.ptr(qs[2]), C.ptr(qs[3]), C.i64_array(qs[0].shape), C.c_float(decay),
                int(bool(x_min_max)), int(bool(ema)), C.c_float(eps), C.ptr(y), ctypes.c_void_p(0),
@@ -129,7 +129,7 @@ def _grad_buffers(x, dy, dx, accum):
 def fixed_point_quantize_backward(x, dy, sign=True, n=8, delta=2 ** -4, ste_fine_grained=True, accum=False, dx=None):
     """FixedPointQuantize::backward_impl (src/nbla/function/generic/fixed_point_quantize.cpp:69-127)."""
     x, dy, dx = _grad_buffers(x, dy, dx, accum)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_fixed_point_quantize_backward_f32", C.ptr(x), C.ptr(dy), C.ptr(dx), C.size_t(x.numel()),
                int(bool(sign)), int(n), C.c_float(delta), int(bool(ste_fine_grained)), int(bool(accum)),
                C.stream_ptr(x.device))
@@ -139,7 +139,7 @@ def fixed_point_quantize_backward(x, dy, sign=True, n=8, delta=2 ** -4, ste_fine
 def pow2_quantize_backward(x, dy, sign=True, with_zero=True, n=8, m=1, ste_fine_grained=True, accum=False, dx=None):
     """Pow2Quantize::backward_impl (src/nbla/function/generic/pow2_quantize.cpp:84-156)."""
     x, dy, dx = _grad_buffers(x, dy, dx, accum)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_pow2_quantize_backward_f32", C.ptr(x), C.ptr(dy), C.ptr(dx), C.size_t(x.numel()),
                int(bool(sign)), int(bool(with_zero)), int(n), int(m), int(bool(ste_fine_grained)), int(bool(accum)),
                C.stream_ptr(x.device))
@@ -166,7 +166,7 @@ def min_max_quantize_backward(x, qr_min, qr_max, ql_min, ql_max, dy, x_min_max=F
                 raise RuntimeError("accum=True needs the gradient buffer to accumulate into")
             g = torch.zeros_like(qs[0])
         gq.append(_check_input(g, "range gradient"))
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_min_max_quantize_backward_f32", C.ptr(x), C.i64_array(x.shape), int(x.dim()), C.ptr(qs[0]),
                C.ptr(qs[1]), C.ptr(qs[2]), C.ptr(qs[3]), C.i64_array(qs[0].shape), C.ptr(dy), int(bool(x_min_max)),
                int(bool(ema)), int(bool(ste_fine_grained)), C.i32_array([bool(v) for v in propagate_down]),
@@ -234,7 +234,7 @@ def binary_weight_affine(x, weight, binary_weight, alpha, bias=None, base_axis=1
     if alpha.numel() != w_col:
         raise RuntimeError("Size of alpha must be equal to output size.")
     y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_binary_weight_affine_f32", C.ptr(x), C.ptr(weight), C.ptr(binary_weight), C.ptr(alpha),
                C.ptr(bias), C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(w_row), ctypes.c_int64(w_col),
                C.c_float(quantize_zero_to), C.stream_ptr(x.device))
@@ -253,7 +253,7 @@ def binary_connect_affine(x, weight, binary_weight, bias=None, base_axis=1, quan
     rows, w_row, w_col, out_shape = _affine_dims(x, weight, base_axis, bias)
     _same_shape(weight, binary_weight, "float vs binary")
     y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_binary_connect_affine_f32", C.ptr(x), C.ptr(weight), C.ptr(binary_weight), C.ptr(bias),
                C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(w_row), ctypes.c_int64(w_col),
                C.c_float(quantize_zero_to), C.stream_ptr(x.device))
@@ -271,7 +271,7 @@ def affine(x, weight, bias=None, base_axis=1, n_outputs=-1, outputs=None, fixed_
     bias = _check_input(bias, "bias") if bias is not None else None
     rows, w_row, w_col, out_shape = _affine_dims(x, weight, base_axis, bias)
     y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         if fixed_point is not None:
             dx, dw = fixed_point
             C.call("nb200_affine_fxp8_f32", C.ptr(x), C.ptr(weight), C.c_float(dx), C.c_float(dw), C.ptr(bias),
@@ -291,7 +291,7 @@ def affine_from_codes(x_codes, w_codes, delta_x, delta_w, bias=None):
     if K != K2:
         raise RuntimeError("Size of input data(inputs[0]) and weights(inputs[1]) mismatch.")
     y = torch.empty((rows, N), dtype=torch.float32, device=x_codes.device)
-    with torch.cuda.device(x_codes.device):
+    with C.on_device(x_codes.device):
         C.call("nb200_affine_codes_i8_f32", C.ptr(x_codes), C.ptr(w_codes), C.c_float(delta_x), C.c_float(delta_w),
                C.ptr(bias), C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(K), ctypes.c_int64(N),
                C.stream_ptr(x_codes.device))
@@ -322,7 +322,7 @@ def _affine_backward(entry, x, w, alpha, dy, base_axis, propagate_down, accum, g
     args = [C.ptr(x), C.ptr(w)] + ([C.ptr(alpha)] if alpha is not None else []) + [C.ptr(dy)] + p + [
         ctypes.c_int64(rows), ctypes.c_int64(w_row), ctypes.c_int64(w_col), int(bool(accum[0])), int(bool(accum[1])),
         int(bool(accum[2])), C.stream_ptr(x.device)]
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call(entry, *args)
     return tuple(out)
 
@@ -359,7 +359,7 @@ def transpose_codes(w_codes):
     K, N = w_codes.shape
     Kp = (K + 15) // 16 * 16
     out = torch.empty((N, Kp), dtype=torch.int8, device=w_codes.device)
-    with torch.cuda.device(w_codes.device):
+    with C.on_device(w_codes.device):
         C.call("nb200_transpose_codes_i8", C.ptr(w_codes.contiguous()), C.ptr(out), ctypes.c_int64(K),
                ctypes.c_int64(N), ctypes.c_int64(Kp), C.stream_ptr(w_codes.device))
     return out
@@ -372,7 +372,7 @@ def affine_from_kmajor_codes(x_codes, w_codes_kmajor, w_row, delta_x, delta_w, b
     if K != w_row or Kp < K:
         raise RuntimeError("Size of input data(inputs[0]) and weights(inputs[1]) mismatch.")
     y = torch.empty((rows, N), dtype=torch.float32, device=x_codes.device)
-    with torch.cuda.device(x_codes.device):
+    with C.on_device(x_codes.device):
         C.call("nb200_affine_codes_i8_kmajor_f32", C.ptr(x_codes), C.ptr(w_codes_kmajor), ctypes.c_int64(Kp),
                C.c_float(delta_x), C.c_float(delta_w), C.ptr(bias), C.ptr(y), ctypes.c_int64(rows), ctypes.c_int64(K),
                ctypes.c_int64(N), C.stream_ptr(x_codes.device))
@@ -398,7 +398,7 @@ def affine_from_codes_gather(x_codes, w_codes, delta_x, delta_w, bias, y_ranks, 
     K2, n = w_codes.shape
     if K != K2:
         raise RuntimeError("Size of input data(inputs[0]) and weights(inputs[1]) mismatch.")
-    with torch.cuda.device(x_codes.device):
+    with C.on_device(x_codes.device):
         C.call("nb200_affine_codes_i8_gather_f32", C.ptr(x_codes), C.ptr(w_codes), C.c_float(delta_x),
                C.c_float(delta_w), C.ptr(bias), _rank_pointers(y_ranks), int(len(y_ranks)), int(rank),
                ctypes.c_int64(rows), ctypes.c_int64(K), ctypes.c_int64(n), ctypes.c_int64(n_total),
@@ -413,7 +413,7 @@ def affine_fixed_point_gather(xq, wq, delta_x, delta_w, bias, y_ranks, rank, n_t
     K2, n = wq.shape
     if K != K2:
         raise RuntimeError("Size of input data(inputs[0]) and weights(inputs[1]) mismatch.")
-    with torch.cuda.device(xq.device):
+    with C.on_device(xq.device):
         C.call("nb200_affine_fxp8_gather_f32", C.ptr(xq), C.ptr(wq), C.c_float(delta_x), C.c_float(delta_w),
                C.ptr(bias), _rank_pointers(y_ranks), int(len(y_ranks)), int(rank), ctypes.c_int64(rows),
                ctypes.c_int64(K), ctypes.c_int64(n), ctypes.c_int64(n_total), ctypes.c_int64(col_begin),
@@ -485,7 +485,7 @@ def _binary_convolution(entry, x, weight, binary_weight, alpha, bias, base_axis,
     args += [C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1], stride[0], stride[1], dilation[0],
              dilation[1], int(group), C.c_float(quantize_zero_to), C.c_float(fixed_point_delta or 0.0),
              C.stream_ptr(x.device)]
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call(entry, *args)
     return y
 
@@ -545,7 +545,7 @@ def _binary_convolution_backward(entry, x, binary_weight, alpha, dy, base_axis, 
         batch, Cin, H, W, Ko, kh, kw, int(pad[0]), int(pad[1]), int(stride[0]), int(stride[1]), int(dilation[0]),
         int(dilation[1]), int(group), int(bool(accum[0])), int(bool(accum[1])), int(bool(accum[2])),
         C.c_float(fixed_point_delta or 0.0), C.stream_ptr(x.device)]
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call(entry, *args)
     return tuple(out)
 
@@ -593,7 +593,7 @@ def convolution_backward(x, weight_shape, dy, base_axis=1, pad=None, stride=None
                 raise RuntimeError("accum=True needs the gradient buffer to accumulate into")
             g = torch.empty(shape, dtype=torch.float32, device=x.device)
         out.append(g)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_convolution_backward_f32", C.ptr(x), C.ptr(dy), C.ptr(out[1]) if propagate_down[1] else
                ctypes.c_void_p(0), C.ptr(out[2]) if propagate_down[2] else ctypes.c_void_p(0), batch, Cin, H, W, Ko,
                kh, kw, int(pad[0]), int(pad[1]), int(stride[0]), int(stride[1]), int(dilation[0]), int(dilation[1]),
@@ -621,12 +621,12 @@ def convolution(x, weight, bias=None, base_axis=1, pad=None, stride=None, dilati
         x, weight, bias, base_axis, pad, stride, dilation, group)
     y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if outputs is None else outputs[0]
     if fixed_point is not None:
-        with torch.cuda.device(x.device):
+        with C.on_device(x.device):
             C.call("nb200_convolution_fxp8_f32", C.ptr(x), C.ptr(weight), C.c_float(fixed_point[0]),
                    C.c_float(fixed_point[1]), C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1],
                    stride[0], stride[1], dilation[0], dilation[1], int(group), C.stream_ptr(x.device))
         return y
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_convolution_f32", C.ptr(x), C.ptr(weight), C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw,
                pad[0], pad[1], stride[0], stride[1], dilation[0], dilation[1], int(group), C.stream_ptr(x.device))
     return y
@@ -660,7 +660,7 @@ def batch_normalization(x, beta, gamma, mean, variance, axes=[1], decay_rate=0.9
     if params[2] is None or params[3] is None:
         raise RuntimeError("mean and variance are required")
     y = torch.empty_like(x)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_batch_normalization_inference_f32", C.ptr(x), C.ptr(params[0]), C.ptr(params[1]),
                C.ptr(params[2]), C.ptr(params[3]), C.ptr(y), ctypes.c_int64(outer), ctypes.c_int64(Cn),
                ctypes.c_int64(inner), C.c_float(eps), C.stream_ptr(x.device))
@@ -671,7 +671,7 @@ def relu(x, inplace=False, n_outputs=-1, outputs=None):
     """ReLU (function_bases.relu; src/nbla/function/generic/relu.cpp)."""
     x = _check_input(x)
     y = x if inplace else _output_like(x, outputs)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_relu_f32", C.ptr(x), C.ptr(y), C.size_t(x.numel()), C.stream_ptr(x.device))
     return y
 
@@ -683,7 +683,7 @@ def add2(x0, x1, inplace=False, n_outputs=-1, outputs=None):
         raise C.NB200Error(4, "broadcasting add2 is not implemented: shapes %s and %s" % (tuple(x0.shape),
                                                                                          tuple(x1.shape)))
     y = x0 if inplace else _output_like(x0, outputs)
-    with torch.cuda.device(x0.device):
+    with C.on_device(x0.device):
         C.call("nb200_add2_f32", C.ptr(x0), C.ptr(x1), C.ptr(y), C.size_t(x0.numel()), C.stream_ptr(x0.device))
     return y
 
@@ -706,7 +706,7 @@ def max_pooling(x, kernel, stride=None, ignore_border=True, pad=None, channel_la
     Ho = (H + pad[0] - (kernel[0] - pad[0] if ignore_border else 1)) // stride[0] + 1
     Wo = (W + pad[1] - (kernel[1] - pad[1] if ignore_border else 1)) // stride[1] + 1
     y = torch.empty(tuple(x.shape[:-2]) + (Ho, Wo), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_max_pooling_f32", C.ptr(x), C.ptr(y), ctypes.c_int64(maps), H, W, kernel[0], kernel[1],
                stride[0], stride[1], pad[0], pad[1], int(bool(ignore_border)), C.stream_ptr(x.device))
     return y
@@ -722,7 +722,7 @@ def global_average_pooling(x, n_outputs=-1, outputs=None):
     N, Cn = int(x.shape[0]), int(x.shape[1])
     S = x.numel() // max(N * Cn, 1)
     y = torch.empty((N, Cn, 1, 1), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_global_average_pooling_f32", C.ptr(x), C.ptr(y), ctypes.c_int64(N * Cn), ctypes.c_int64(S),
                C.stream_ptr(x.device))
     return y
@@ -766,7 +766,7 @@ def bn_add_relu_fixed_point(a, bn_a, b=None, bn_b=None, eps=1e-05, relu=True, qu
     elif bn_b is not None:
         raise RuntimeError("bn_b without b")
     y = _output_like(a, outputs)
-    with torch.cuda.device(a.device):
+    with C.on_device(a.device):
         C.call("nb200_bn_add_relu_fxp_f32", C.ptr(a), C.ptr(pa[0]), C.ptr(pa[1]), C.ptr(pa[2]), C.ptr(pa[3]),
                C.ptr(b), C.ptr(pb[0]), C.ptr(pb[1]), C.ptr(pb[2]), C.ptr(pb[3]), C.ptr(y), ctypes.c_int64(outer),
                ctypes.c_int64(Cn), ctypes.c_int64(inner), C.c_float(eps), int(bool(relu)), int(bool(quantize)),
@@ -802,7 +802,7 @@ def fixed_point_codes_nhwc(xq, delta=2 ** -4, group=1):
     xq = _check_input(xq, "xq")
     batch, ch, inner = _nchw_extents(xq)
     codes = torch.empty((batch, inner, codes_nhwc_slots(ch, group)), dtype=torch.int8, device=xq.device)
-    with torch.cuda.device(xq.device):
+    with C.on_device(xq.device):
         C.call("nb200_fixed_point_codes_nhwc", C.ptr(xq), C.ptr(codes), ctypes.c_int64(batch), ctypes.c_int64(ch),
                ctypes.c_int64(inner), int(group), C.c_float(delta), C.stream_ptr(xq.device))
     return codes
@@ -827,7 +827,7 @@ def codes_nhwc_to_float(codes, shape, delta=2 ** -4, group=1):
         inner *= v
     codes = _check_codes(codes, batch, inner, ch, group)
     y = torch.empty(shape, dtype=torch.float32, device=codes.device)
-    with torch.cuda.device(codes.device):
+    with C.on_device(codes.device):
         C.call("nb200_codes_nhwc_to_f32", C.ptr(codes), C.ptr(y), ctypes.c_int64(batch), ctypes.c_int64(ch),
                ctypes.c_int64(inner), int(group), C.c_float(delta), C.stream_ptr(codes.device))
     return y
@@ -869,7 +869,7 @@ def bn_add_relu_fixed_point_codes(a, bn_a, b=None, bn_b=None, b_codes=None, b_de
     if b_codes is not None:
         b_codes = _check_codes(b_codes, batch, inner, Cn, group, "b_codes")
     y = torch.empty((batch, inner, codes_nhwc_slots(Cn, group)), dtype=torch.int8, device=a.device)
-    with torch.cuda.device(a.device):
+    with C.on_device(a.device):
         C.call("nb200_bn_add_relu_fxp_codes_nhwc", C.ptr(a), C.ptr(pa[0]), C.ptr(pa[1]), C.ptr(pa[2]), C.ptr(pa[3]),
                C.ptr(b), C.ptr(pb[0]), C.ptr(pb[1]), C.ptr(pb[2]), C.ptr(pb[3]), C.ptr(b_codes),
                C.c_float(delta if b_delta is None else b_delta), C.ptr(y), ctypes.c_int64(batch), ctypes.c_int64(Cn),
@@ -896,7 +896,7 @@ def max_pooling_codes(codes, shape, kernel, stride=None, ignore_border=True, pad
     if Ho <= 0 or Wo <= 0:
         raise RuntimeError("pooling output would be empty")
     y = torch.empty((batch, Ho * Wo, codes.shape[2]), dtype=torch.int8, device=codes.device)
-    with torch.cuda.device(codes.device):
+    with C.on_device(codes.device):
         C.call("nb200_max_pooling_codes_nhwc", C.ptr(codes), C.ptr(y), ctypes.c_int64(batch), ctypes.c_int64(Cn), H, W,
                int(group), int(kernel[0]), int(kernel[1]), int(stride[0]), int(stride[1]), int(pad[0]), int(pad[1]),
                int(bool(ignore_border)), C.stream_ptr(codes.device))
@@ -925,7 +925,7 @@ def binary_weight_convolution_from_codes(x_codes, x_shape, weight, binary_weight
         if alpha.numel() != Ko:
             raise RuntimeError("Size of alpha must be equal to the number of output maps.")
     y = torch.empty(out_shape, dtype=torch.float32, device=weight.device) if outputs is None else outputs[0]
-    with torch.cuda.device(weight.device):
+    with C.on_device(weight.device):
         C.call("nb200_binary_convolution_codes_f32", C.ptr(x_codes), C.ptr(weight), C.ptr(binary_weight),
                C.ptr(alpha), C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1], stride[0],
                stride[1], dilation[0], dilation[1], int(group), C.c_float(quantize_zero_to),
@@ -959,7 +959,7 @@ def prepare_binary_weights(weight, group=1, quantize_zero_to=1.0, with_alpha=Tru
     wb = torch.empty_like(weight)
     alpha = torch.empty((Ko,), dtype=torch.float32, device=weight.device) if with_alpha else None
     side = torch.empty((nbytes,), dtype=torch.int8, device=weight.device)
-    with torch.cuda.device(weight.device):
+    with C.on_device(weight.device):
         C.call("nb200_binary_weights_prepare_i8", C.ptr(weight), C.ptr(wb), C.ptr(alpha), C.ptr(side), Ko,
                Cg * int(group), kh, kw, int(group), C.c_float(quantize_zero_to), C.stream_ptr(weight.device))
     return PreparedBinaryWeights(weight.shape, group, wb, alpha, side)
@@ -979,7 +979,7 @@ def binary_convolution_from_codes_prepared(x_codes, x_shape, prepared, bias=None
     x_codes = _check_codes(x_codes, batch, H * W, Cin, prepared.group, "x_codes")
     dev = x_codes.device
     y = torch.empty(out_shape, dtype=torch.float32, device=dev) if outputs is None else outputs[0]
-    with torch.cuda.device(dev):
+    with C.on_device(dev):
         C.call("nb200_binary_convolution_codes_prepared_f32", C.ptr(x_codes), C.ptr(prepared.side),
                C.ptr(prepared.alpha), C.ptr(bias), C.ptr(y), batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1], stride[0],
                stride[1], dilation[0], dilation[1], int(prepared.group), C.c_float(activation_delta),
@@ -1032,7 +1032,7 @@ def convolution_codes_folded(x_codes, x_shape, prepared, scale, bias=None, pad=N
         y_f32 = torch.empty((batch, Ho * Wo, slots), dtype=torch.float32, device=dev)
     else:
         raise ValueError("output must be 'codes' or 'float'")
-    with torch.cuda.device(dev):
+    with C.on_device(dev):
         C.call("nb200_convolution_codes_folded_nhwc", C.ptr(x_codes), C.ptr(prepared.side), C.ptr(scale), C.ptr(bias),
                C.ptr(residual_codes), C.c_float(residual_delta or 0.0), C.ptr(residual), C.ptr(y_codes), C.ptr(y_f32),
                batch, Cin, H, W, Ko, kh, kw, pad[0], pad[1], stride[0], stride[1], dilation[0], dilation[1],
@@ -1051,7 +1051,7 @@ def convolution_relu_fixed_point_codes(x, weight, bias=None, pad=None, stride=No
         x, weight, bias, 1, pad, stride, None, 1)
     slots = codes_nhwc_slots(Ko, 1)
     y = torch.empty((batch, out_shape[2] * out_shape[3], slots), dtype=torch.int8, device=x.device)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_convolution_relu_fxp_codes_nhwc", C.ptr(x), C.ptr(weight), C.ptr(bias), C.ptr(y), batch, Cin, H,
                W, Ko, kh, kw, pad[0], pad[1], stride[0], stride[1], int(bool(relu)), int(bool(sign)), int(n),
                C.c_float(delta), C.stream_ptr(x.device))
@@ -1070,7 +1070,7 @@ def global_average_pooling_codes(codes, shape, delta=2 ** -4):
 def _unary(entry, x, outputs):
     x = _check_input(x)
     y = _output_like(x, outputs)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call(entry, C.ptr(x), C.ptr(y), C.size_t(x.numel()), C.stream_ptr(x.device))
     return y
 
@@ -1088,7 +1088,7 @@ def binary_tanh(x, n_outputs=-1, outputs=None):
 
 def _unary_backward(entry, x, dy, accum, dx):
     x, dy, dx = _grad_buffers(x, dy, dx, accum)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call(entry, C.ptr(x), C.ptr(dy), C.ptr(dx), C.size_t(x.numel()), int(bool(accum)), C.stream_ptr(x.device))
     return dx
 
@@ -1125,7 +1125,7 @@ def quantize_linear(x, scale, zero_point, round_mode="HALF_AWAY_FROM_ZERO", narr
     if dtype not in _QL_DTYPES:
         raise C.NB200Error(4, "dtype must be int8 (BYTE) or uint8 (UBYTE)")
     y = _output_like(x, outputs)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_quantize_linear_f32", C.ptr(x), C.i64_array(x.shape), int(x.dim()), C.ptr(scale),
                C.i64_array(scale.shape), C.ptr(zero_point), C.i64_array(zero_point.shape), C.ptr(y),
                _ROUND_MODES[round_mode], int(bool(narrow_range)), _QL_DTYPES[dtype], C.stream_ptr(x.device))
@@ -1136,7 +1136,7 @@ def dequantize_linear(x, scale, zero_point, n_outputs=-1, outputs=None):
     """(x - zero_point) * scale (src/nbla/function/generic/dequantize_linear.cpp:60-71)."""
     x, scale, zero_point = _linear_params(x, scale, zero_point)
     y = _output_like(x, outputs)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_dequantize_linear_f32", C.ptr(x), C.i64_array(x.shape), int(x.dim()), C.ptr(scale),
                C.i64_array(scale.shape), C.ptr(zero_point), C.i64_array(zero_point.shape), C.ptr(y),
                C.stream_ptr(x.device))
@@ -1146,7 +1146,7 @@ def dequantize_linear(x, scale, zero_point, n_outputs=-1, outputs=None):
 def _linear_backward(entry, dy, scale, accum, dx):
     dy, scale, _ = _linear_params(dy, scale, None)
     _, dy, dx = _grad_buffers(dy, dy, dx, accum)
-    with torch.cuda.device(dy.device):
+    with C.on_device(dy.device):
         C.call(entry, C.ptr(dy), C.i64_array(dy.shape), int(dy.dim()), C.ptr(scale), C.i64_array(scale.shape),
                C.ptr(dx), int(bool(accum)), C.stream_ptr(dy.device))
     return dx
@@ -1167,7 +1167,7 @@ def prune(x, rate=0.9, n_outputs=-1, outputs=None):
     |x| become zero (python/src/nnabla/functions.py prune; src/nbla/function/generic/prune.cpp:38-72)."""
     x = _check_input(x)
     y = _output_like(x, outputs)
-    with torch.cuda.device(x.device):
+    with C.on_device(x.device):
         C.call("nb200_prune_f32", C.ptr(x), C.ptr(y), C.size_t(x.numel()), C.c_float(rate), C.stream_ptr(x.device))
     return y
 
@@ -1175,7 +1175,7 @@ def prune(x, rate=0.9, n_outputs=-1, outputs=None):
 def prune_backward(dy, accum=False, dx=None):
     """Prune::backward_impl (prune.cpp:74-88): the gradient passes unchanged."""
     _, dy, dx = _grad_buffers(dy, dy, dx, accum)
-    with torch.cuda.device(dy.device):
+    with C.on_device(dy.device):
         C.call("nb200_prune_backward_f32", C.ptr(dy), C.ptr(dx), C.size_t(dy.numel()), int(bool(accum)),
                C.stream_ptr(dy.device))
     return dx
