@@ -44,6 +44,11 @@ void nb200_check(int status, const char *what);
     by one stream. */
 void *b200_stream(const string &device_id);
 
+/** Bucket plan of the communicator's packed all-reduce: consecutive arrays (sizes in elements) are
+    grouped into buckets of at most pack_size elements, a larger array alone; returns the index of
+    the first array of every bucket, then the end index (ext/src/b200_communicator.cpp). */
+vector<size_t> b200_plan_buckets(const vector<size_t> &sizes, size_t pack_size);
+
 /** Counters of the paths the functions took since the last reset, by name:
     "int8_convolutions", "bf16_convolutions", "int8_affines",
     "weight_cache_hits", "weight_cache_misses". Unknown names read 0. */

@@ -46,6 +46,7 @@
 namespace nbla {
 
 void install_write_tracking(); // b200_backend.cpp
+void register_b200_communicator(); // b200_communicator.cpp
 void synchronizer_cpu_to_b200(Array *src, Array *dst, const int async_flags);
 void synchronizer_b200_to_cpu(Array *src, Array *dst, const int async_flags);
 
@@ -882,6 +883,7 @@ void init_b200() {
   init_cpu();
   nb200_check(nb200_check_device(), "init_b200");
   install_write_tracking();
+  register_b200_communicator();
 
   NBLA_REGISTER_BACKEND("b200", []() { return SingletonManager::get<B200>(); });
   NBLA_REGISTER_ARRAY_CREATOR(B200Array);

@@ -551,6 +551,9 @@ int nb200_batch_normalization_inference_f32(const float *x, const float *beta, c
 int nb200_relu_f32(const float *x, float *y, size_t size, void *stream);
 /* Add2<float>::forward_impl (src/nbla/function/generic/add2.cpp), equal shapes. */
 int nb200_add2_f32(const float *a, const float *b, float *y, size_t size, void *stream);
+/* x[i] *= factor in place: the division by the number of workers after a summing collective
+ * (Communicator::all_reduce with division, include/nbla/communicator.hpp:157-170). */
+int nb200_scale_f32(float *x, size_t size, float factor, void *stream);
 /* MaxPooling<float>::forward_impl (src/nbla/function/generic/max_pooling.cpp:140-191),
  * 2-D, x [maps, height, width]; output extent by base_pooling.cpp:59. */
 int nb200_max_pooling_f32(const float *x, float *y, int64_t maps, int height, int width, int kernel_h, int kernel_w,

@@ -501,6 +501,25 @@ int nb200_relu_f32(const float *x, float *y, size_t size, void *stream) {
   return NB200_OK;
 }
 
+namespace nb200 {
+namespace {
+__global__ void __launch_bounds__(kThreads) scale_kernel(float *__restrict__ x, size_t total, float factor) {
+  const size_t stride = (size_t)gridDim.x * kThreads;
+  for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride)
+    x[i] = __fmul_rn(x[i], factor);
+}
+} // namespace
+} // namespace nb200
+
+int nb200_scale_f32(float *x, size_t size, float factor, void *stream) {
+  if (size == 0)
+    return NB200_OK;
+  NB_CHECK(x != nullptr, NB200_EVALUE, "null data pointer");
+  scale_kernel<<<grid_for(size, 4), kThreads, 0, as_stream(stream)>>>(x, size, factor);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
 int nb200_add2_f32(const float *a, const float *b, float *y, size_t size, void *stream) {
   if (size == 0)
     return NB200_OK;

@@ -32,6 +32,13 @@ struct ConvGeometry {
   int Cg, Kog, Ho, Wo;
 };
 
+// Pixel-major kernel (conv_codes.cuh), defined further down.
+bool pixel_major_applies(const ConvGeometry &g);
+int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const float *scale, const float *bias,
+                             const int8_t *res_codes, float res_delta, const float *res_f32, int8_t *y_codes,
+                             float *y_f32, ConvGeometry g, int relu, int sign, int n, float delta, cudaStream_t st,
+                             float *y_nchw = nullptr, float nchw_scale = 1.0f);
+
 // The reference's checks (src/nbla/function/generic/convolution.cpp:40-158).
 int check_geometry(ConvGeometry &g) {
   NB_CHECK(g.N > 0 && g.C > 0 && g.H > 0 && g.W > 0 && g.Ko > 0 && g.kh > 0 && g.kw > 0, NB200_EVALUE,
@@ -209,6 +216,12 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   const double fill256 = (double)px256 / (double)round_up(px256, 16) * px256 / 256.0;
   const bool can128 = px128 <= 128;
   const bool use256 = !can128 || (int8 && fill256 > fill128 + 0.05);
+  if (int8 && pixel_major_applies(g)) {
+    // pixels on the MMA rows: same accumulators, same rounded operations in the epilogue, faster loads and stores
+    return convolution_codes_folded(reinterpret_cast<const int8_t *>(act), reinterpret_cast<const int8_t *>(side),
+                                    fxp_weights ? nullptr : alpha, bias, nullptr, 0.0f, nullptr, nullptr, nullptr, g, 0,
+                                    1, 8, 1.0f, st, y, ep.scale);
+  }
   if (int8) {
     // All tiles share the weights when the output maps fit one M tile: keep them in shared
     // memory for the whole launch if their K blocks fit beside the ring (64-byte rows only:
@@ -457,6 +470,8 @@ int nb200_binary_convolution_codes_f32(const int8_t *x_codes, const float *w, fl
                             0.0f, x_codes);
 }
 
+} // extern "C" (reopened below)
+namespace nb200 {
 namespace {
 // slots per filter tap and row pitch of the int8 weight side-band [outmaps][taps * c_slots]
 void int8_side_layout(int Cg, int taps, int &c_slots, int64_t &wpitch) {
@@ -465,10 +480,7 @@ void int8_side_layout(int Cg, int taps, int &c_slots, int64_t &wpitch) {
   c_slots = (c_pad_g + E - 1) / E * E;
   wpitch = (int64_t)taps * c_slots;
 }
-} // namespace
 
-} // extern "C" (reopened below)
-namespace {
 // ---------------------------------------------------------------------------
 // Convolution of activation codes with the layer's inference tail in the
 // epilogue (conv_codes.cuh): pixels on the MMA rows, channel-last codes out.
@@ -548,13 +560,24 @@ int launch_conv_codes(const ConvGeometry &g, const int8_t *x_codes, int64_t ctot
   return NB200_OK;
 }
 
+// Whether a convolution can run on the pixel-major kernel (group 1, at most kCodesMaxMaps maps, output rows
+// of at most 128 pixels).
+bool pixel_major_applies(const ConvGeometry &g) {
+  return g.group == 1 && g.Ko <= kCodesMaxMaps && g.Wo * g.sw <= 256 && g.Wo <= 128;
+}
+
+// y_nchw != NULL: plain fp32 [batch][maps][pixels] result, acc * scale[o] (+ bias[o]) with each operation
+// rounded on its own (what the unfused functions return); no residual, ReLU or quantizer then.
 int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const float *scale, const float *bias,
                              const int8_t *res_codes, float res_delta, const float *res_f32, int8_t *y_codes,
-                             float *y_f32, ConvGeometry g, int relu, int sign, int n, float delta, cudaStream_t st) {
+                             float *y_f32, ConvGeometry g, int relu, int sign, int n, float delta, cudaStream_t st,
+                             float *y_nchw, float nchw_scale) {
   NB_TRY(check_geometry(g));
   NB_CHECK(g.group == 1, NB200_ENOTIMPL, "grouped convolutions are not supported by the folded code path");
-  NB_CHECK(x_codes && side && scale && (y_codes || y_f32), NB200_EVALUE, "null data pointer");
+  NB_CHECK(x_codes && side && (scale || y_nchw) && (y_codes || y_f32 || y_nchw), NB200_EVALUE, "null data pointer");
   NB_CHECK(!(y_codes && y_f32), NB200_EVALUE, "the result is either codes or fp32, not both");
+  NB_CHECK(!y_nchw || !(y_codes || y_f32 || res_codes || res_f32), NB200_EVALUE,
+           "the plain fp32 result takes no residual and no second result");
   NB_CHECK(!(res_codes && res_f32), NB200_EVALUE, "the residual is either codes or fp32, not both");
   NB_CHECK(res_codes == nullptr || res_delta > 0.f, NB200_EVALUE, "res_delta should be positive");
   NB_CHECK(g.Ko <= kCodesMaxMaps, NB200_ENOTIMPL, "more than %d output maps", kCodesMaxMaps);
@@ -567,6 +590,8 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
   ep.res_f32 = res_f32;
   ep.y_codes = y_codes;
   ep.y_f32 = y_codes ? nullptr : y_f32;
+  ep.y_nchw = y_nchw;
+  ep.has_bias = bias != nullptr;
   ep.relu = relu;
   ep.out_scale = 1.0f;
   ep.kmax = ep.kmin = 0;
@@ -583,7 +608,12 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
     ep.kmax = (1 << nn) - 1;
     ep.kmin = sign ? -ep.kmax : 0;
   }
+  ep.bias_scale = ep.out_scale;
   ep.res_scale = (res_codes ? res_delta : 1.0f) * ep.out_scale;
+  if (y_nchw) {
+    ep.out_scale = nchw_scale; // the step of the activation codes (times the weights' step for fixed-point weights)
+    ep.bias_scale = 1.0f;
+  }
 #ifdef NB200_CC_TRACE
   ep.trace = g_cc_trace;
 #endif
@@ -591,7 +621,7 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
   NB_CHECK((((reinterpret_cast<uintptr_t>(x_codes) | reinterpret_cast<uintptr_t>(side) |
               reinterpret_cast<uintptr_t>(res_codes) | reinterpret_cast<uintptr_t>(res_f32) |
               reinterpret_cast<uintptr_t>(y_codes) | reinterpret_cast<uintptr_t>(y_f32)) &
-             15) == 0),
+             15) == 0) && (reinterpret_cast<uintptr_t>(y_nchw) & 3) == 0,
            NB200_EVALUE, "code and result tensors must be 16-byte aligned");
   const int c_pad = (int)round_up(g.C, 16);
   const bool narrow_rows = c_pad <= 64;
@@ -669,6 +699,7 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
 #undef NB_CC_HALO
 }
 } // namespace
+} // namespace nb200
 extern "C" {
 
 int64_t nb200_binary_weights_side_bytes(int outmaps, int channels, int kernel_h, int kernel_w, int group) {

@@ -55,8 +55,13 @@ struct ConvCodesEpilogue {
   float res_scale;             // factor of the residual: (its step, or 1 for fp32) * out_scale
   int8_t *y_codes;             // result as codes (or NULL)
   float *y_f32;                // result as fp32 channel-last, before ReLU / quantizer (or NULL)
+  float *y_nchw;               // result as fp32 [batch][maps][pixels]: acc * scale (+ bias), each operation rounded
+                               // on its own like the reference's product followed by its bias addition (or NULL)
+  int has_bias;
   int relu;
-  float out_scale;             // 2 / delta when codes are written (delta: the quantizer's step, a power of two), else 1
+  float out_scale;             // factor of scale: 2 / delta when codes are written (delta: the quantizer's step, a
+                               // power of two), the activations' step for the plain fp32 result, else 1
+  float bias_scale;            // factor of bias: 2 / delta when codes are written, else 1
   int kmax, kmin;              // code range
 #ifdef NB200_CC_TRACE
   long long *trace; // timing experiments: block 0 writes %globaltimer at its phase boundaries
@@ -173,8 +178,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     ptx::prefetch_tensormap(&map_w);
   }
   for (int c = threadIdx.x; c < prob.n_tiles * BN; c += kGemmThreads)
-    sb[c] = c < prob.Ko ? make_float2(__fmul_rn(ep.scale[c], ep.out_scale),
-                                      ep.bias ? __fmul_rn(ep.bias[c], ep.out_scale) : 0.0f)
+    sb[c] = c < prob.Ko ? make_float2(ep.scale ? __fmul_rn(ep.scale[c], ep.out_scale) : ep.out_scale,
+                                      ep.bias ? __fmul_rn(ep.bias[c], ep.bias_scale) : 0.0f)
                         : make_float2(0.0f, 0.0f);
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
@@ -357,17 +362,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // this thread's pixel
       const int row = quarter * 32 + lane;
       bool pix_ok;
-      int64_t pix;
+      int img, in_plane; // image and pixel inside the image's plane
       if (kHalo) {
         const int y = row / prob.wp, x = row - y * prob.wp;
+        img = img0;
         pix_ok = x < prob.Wo && y < prob.h_box && oy0 + y < prob.Ho && img0 < prob.Nimg;
-        pix = (int64_t)img0 * prob.Ho * prob.Wo + (int64_t)(oy0 + y) * prob.Wo + x;
+        in_plane = (oy0 + y) * prob.Wo + x;
       } else {
         const int nn = row / per_img, q = row - nn * per_img;
-        const int img = img0 + nn;
+        img = img0 + nn;
         pix_ok = nn < prob.n_box && img < prob.Nimg && q < (prob.Ho - oy0) * prob.Wo;
-        pix = (int64_t)img * prob.Ho * prob.Wo + (int64_t)oy0 * prob.Wo + q;
+        in_plane = oy0 * prob.Wo + q;
       }
+      const int64_t pix = (int64_t)img * prob.Ho * prob.Wo + in_plane;
       // the residual of this warp's first chunk is requested before the accumulator is waited for
       uint4 ra = make_uint4(0, 0, 0, 0), rb = make_uint4(0, 0, 0, 0);
       {
@@ -396,7 +403,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll 1
       for (int c0 = 32 * half; c0 < BN; c0 += 64) {
         const int col = n0 + c0; // first output map of the chunk
-        const bool live = pix_ok && col < prob.slots_out;
+        const bool live = pix_ok && col < (ep.y_nchw ? prob.Ko : prob.slots_out);
         const int64_t off = pix * prob.slots_out + col;
         const bool upper = col + 16 < prob.slots_out; // the pixel's row ends in the middle of this chunk otherwise
         if (c0 != 32 * half && ep.res_codes && live) { // later chunks: fetched here

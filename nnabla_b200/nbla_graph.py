@@ -203,3 +203,74 @@ class Graph:
 
     def global_average_pooling(self, x):
         return self.function("GlobalAveragePooling", [], [], [self.leaf(x)])
+
+
+class Communicator:
+    """nnabla's MultiProcessDataParallelCommunicator as registered for `backend` (one process per
+    GPU; ranks from RANK / WORLD_SIZE / LOCAL_RANK). Collectives take and return numpy arrays, which
+    travel through nnabla's NdArray machinery to the device and back."""
+    ALL_REDUCE, REDUCE, BCAST, ALL_GATHER, REDUCE_SCATTER, CALLBACK = range(6)
+
+    def __init__(self, backend="b200:float", device_id="0"):
+        L = lib()
+        L.nbc_create.restype = ctypes.c_void_p
+        L.nbc_last_error.restype = ctypes.c_char_p
+        self._h = ctypes.c_void_p(L.nbc_create(backend.encode(), str(device_id).encode()))
+        if not self._h:
+            raise RuntimeError(L.nbc_last_error().decode())
+
+    def _check(self, rc):
+        if rc != 0:
+            raise RuntimeError(lib().nbc_last_error().decode())
+
+    def init(self):
+        self._check(lib().nbc_init(self._h))
+
+    @property
+    def rank(self):
+        return lib().nbc_rank(self._h)
+
+    @property
+    def size(self):
+        return lib().nbc_size(self._h)
+
+    def barrier(self):
+        self._check(lib().nbc_barrier(self._h))
+
+    def new_group(self, name, ranks):
+        arr = (ctypes.c_int32 * len(ranks))(*ranks)
+        self._check(lib().nbc_new_group(self._h, name.encode(), arr, len(ranks)))
+
+    def _run(self, op, arrays, root=0, division=False, inplace=False, group="world"):
+        bufs = [np.ascontiguousarray(a, np.float32).copy() for a in arrays]
+        ptrs = (ctypes.POINTER(ctypes.c_float) * len(bufs))(*[b.ctypes.data_as(ctypes.POINTER(ctypes.c_float)) for b in bufs])
+        sizes = (ctypes.c_int64 * len(bufs))(*[b.size for b in bufs])
+        self._check(lib().nbc_collective(self._h, op, ptrs, sizes, len(bufs), int(root), int(division), int(inplace),
+                                         group.encode()))
+        return bufs
+
+    def all_reduce(self, arrays, division=False, inplace=False, group="world"):
+        return self._run(self.ALL_REDUCE, arrays, 0, division, inplace, group)
+
+    def reduce(self, arrays, dst, division=False, inplace=False, group="world"):
+        return self._run(self.REDUCE, arrays, dst, division, inplace, group)
+
+    def bcast(self, arrays, src, inplace=False, group="world"):
+        return self._run(self.BCAST, arrays, src, False, inplace, group)
+
+    def all_gather(self, array, group="world", n=None):
+        n = self.size if n is None else n
+        out = self._run(self.ALL_GATHER, [array] + [np.zeros_like(array)] * n, group=group)
+        return out[1:]
+
+    def reduce_scatter(self, arrays, division=False, group="world"):
+        return self._run(self.REDUCE_SCATTER, [np.zeros_like(arrays[0])] + list(arrays), 0, division, group=group)[0]
+
+    def all_reduce_packed(self, arrays, pack_size, division=False, group="world"):
+        """The all_reduce_callback (gradient buckets of pack_size values), run as at the end of a backward pass."""
+        return self._run(self.CALLBACK, arrays, pack_size, division, group=group)
+
+    def close(self):
+        if self._h:
+            lib().nbc_destroy(self._h)
+            self._h = None
