@@ -417,6 +417,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           NB_CC_STAMP(7, local);
         if (!live)
           continue;
+        if (ep.y_nchw) {
+          // fp32 [batch][maps][pixels]: the 32 lanes of a store are 32 neighbouring pixels of one map
+          const int64_t plane = (int64_t)prob.Ho * prob.Wo;
+          float *yp = ep.y_nchw + ((int64_t)img * prob.Ko + col) * plane + in_plane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col + j < prob.Ko) {
+              const float2 k = sb[col + j];
+              float val = __fmul_rn((float)(int)r[j], k.x);
+              if (ep.has_bias)
+                val = __fadd_rn(val, k.y);
+              yp[(int64_t)j * plane] = val;
+            }
+          }
+          continue;
+        }
         // u = acc * scale + bias, one fused multiply-add (scale and bias already carry the factor
         // 2 / delta when codes are written, so u is twice the quantizer's argument)
         // Integers become floats on the add / multiply pipes instead of the (much narrower) conversion
@@ -491,6 +507,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             w[j4] = packed;
           }
         }
+        if (ep.y_codes == nullptr)
+          continue; // no result configured (the host refuses this; never store through a null pointer)
         uint4 *yp = reinterpret_cast<uint4 *>(ep.y_codes + off);
         yp[0] = make_uint4(w[0], w[1], w[2], w[3]);
         if (upper)
