@@ -53,7 +53,133 @@ def parse_args():
     ap.add_argument("--small-extras", action="store_true",
                     help="reduced sizes for the other configurations (ncu captures must stay small)")
     ap.add_argument("--sweep-max-log2", type=int, default=30, help="largest size of the quantizer sweep")
+    ap.add_argument("--case", default=None, choices=sorted(KERNEL_CASES),
+                    help="run one small single-kernel case a few times and exit (what the ncu captures under "
+                         "profiles/ run; prints its CUDA-event time)")
     return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- single-kernel cases
+def _case_folded_conv(C, HW, batch=256, residual=True):
+    def make():
+        import torch
+        from nnabla_b200 import functions as F
+        torch.manual_seed(0)
+        w = torch.randn(C, C, 3, 3, device="cuda") * 0.1
+        prep = F.prepare_binary_weights(w, 1, 1.0)
+        scale, bias = (prep.alpha * 0.0625).contiguous(), torch.randn(C, device="cuda") * 0.1
+        slots = F.codes_nhwc_slots(C)
+        x = torch.randint(0, 128, (batch, HW * HW, slots), device="cuda", dtype=torch.int8)
+        r = torch.randint(0, 128, (batch, HW * HW, slots), device="cuda", dtype=torch.int8)
+        kw = dict(residual_codes=r, residual_delta=0.0625) if residual else {}
+        return lambda: F.convolution_codes_folded(x, (batch, C, HW, HW), prep, scale, bias, (1, 1), (1, 1), (1, 1), **kw)
+    return make
+
+
+def _case_stem(codes, batch=256):
+    def make():
+        import torch
+        from nnabla_b200 import functions as F
+        torch.manual_seed(0)
+        x = torch.randn(batch, 3, 224, 224, device="cuda")
+        w, b = torch.randn(64, 3, 7, 7, device="cuda") * 0.1, torch.randn(64, device="cuda") * 0.1
+        if codes:
+            return lambda: F.convolution_relu_fixed_point_codes(x, w, b, (3, 3), (2, 2))
+        return lambda: F.convolution(x, w, None, 1, (3, 3), (2, 2), (1, 1), 1)
+    return make
+
+
+def _case_quantizers(log2n):
+    def make():
+        import torch
+        from nnabla_b200 import functions as F
+        x = torch.rand(1 << log2n, device="cuda") * 8 - 4
+        y = torch.empty_like(x)
+        one = lambda v: torch.tensor([v], device="cuda")
+        q = (one(-4.0), one(4.0), one(0.0), one(255.0))
+
+        def run():
+            F.fixed_point_quantize(x, True, 8, 2.0 ** -4, outputs=[y])
+            F.pow2_quantize(x, True, True, 8, 1, outputs=[y])
+            F.min_max_quantize(x, *q, outputs=[y])
+        return run
+    return make
+
+
+def _case_quantizer_backward(log2n):
+    def make():
+        import torch
+        from nnabla_b200 import functions as F
+        n = 1 << log2n
+        x, dy = torch.rand(n, device="cuda") * 9 - 4.5, torch.randn(n, device="cuda")
+        dx = torch.empty_like(x)
+        one = lambda v: torch.tensor([v], device="cuda")
+        q = (one(-4.0), one(4.0), one(0.0), one(255.0))
+        F.min_max_quantize(x, *q)
+
+        def run():
+            F.fixed_point_quantize_backward(x, dy, True, 8, 2.0 ** -4, True, False, dx)
+            F.pow2_quantize_backward(x, dy, True, True, 8, 1, True, False, dx)
+            F.min_max_quantize_backward(x, *q, dy, grads=(dx, None, None))
+        return run
+    return make
+
+
+def _case_int8_gemm(n):
+    def make():
+        import torch
+        from nnabla_b200 import functions as F
+        x, w, b = torch.randn(n, n, device="cuda"), 0.02 * torch.randn(n, n, device="cuda"), torch.zeros(n, device="cuda")
+        _, xc = F.fixed_point_quantize_with_codes(x, True, 8, 2.0 ** -5)
+        _, wc = F.fixed_point_quantize_with_codes(w, True, 8, 2.0 ** -10)
+        wk = F.transpose_codes(wc)
+        return lambda: F.affine_from_kmajor_codes(xc, wk, n, 2.0 ** -5, 2.0 ** -10, b)
+    return make
+
+
+def _case_bwconv_bf16(batch):
+    def make():
+        import torch
+        from nnabla_b200 import functions as F
+        x = torch.relu(torch.randn(batch, 256, 28, 28, device="cuda"))
+        w = torch.randn(256, 256, 3, 3, device="cuda") * (2.0 / 2304) ** 0.5
+        wb, al = torch.zeros_like(w), torch.zeros(256, device="cuda")
+        return lambda: F.binary_weight_convolution(x, w, wb, al, None, 1, (1, 1), (1, 1))
+    return make
+
+
+def _case_fused_codes_pass(batch):
+    def make():
+        import torch
+        from nnabla_b200 import functions as F
+        a = torch.randn(batch, 64, 56, 56, device="cuda")
+        bn = [torch.randn(64, device="cuda") * 0.1, 1 + 0.1 * torch.randn(64, device="cuda"),
+              torch.randn(64, device="cuda") * 0.1, 0.5 + torch.rand(64, device="cuda")]
+        return lambda: F.bn_add_relu_fixed_point_codes(a, bn)
+    return make
+
+
+KERNEL_CASES = {
+    "folded_conv_64_56x56": _case_folded_conv(64, 56),
+    "folded_conv_128_28x28": _case_folded_conv(128, 28),
+    "folded_conv_256_14x14": _case_folded_conv(256, 14),
+    "stem_codes": _case_stem(True),
+    "stem_float": _case_stem(False),
+    "quantizers_2p26": _case_quantizers(26),
+    "quantizer_backward_2p26": _case_quantizer_backward(26),
+    "int8_gemm_4096": _case_int8_gemm(4096),
+    "bwconv_bf16_batch16": _case_bwconv_bf16(16),
+    "fused_codes_pass_batch128": _case_fused_codes_pass(128),
+}
+
+
+def run_case(name):
+    import torch
+    from nnabla_b200 import _capi as C
+    torch.cuda.set_device(0)
+    C.call("nb200_check_device")
+    fn = KERNEL_CASES[name]()
+    print(json.dumps({"case": name, "ms": float("%.5g" % time_gpu(fn, 5, warm=3))}))
 
 
 def round_floats(o, digits=5):
@@ -686,6 +812,9 @@ def run_b200_arm(args):
 
 def main():
     args = parse_args()
+    if args.case:
+        run_case(args.case)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
     else:
