@@ -594,8 +594,8 @@ int nb200_convolution_relu_fxp_codes_nhwc(const float *x, const float *w, const 
   NB_CHECK(relu || sign, NB200_ENOTIMPL, "an unsigned quantizer without ReLU is not supported");
   NB_CHECK(narrow_conv_applies(x, channels, height, width, outmaps, kernel_h, kernel_w, pad_w, stride_w, 1, 1, 1, Wo),
            NB200_ENOTIMPL,
-           "the fused full-precision convolution is for inputs with few channels (kernel_w * channels <= 24, "
-           "kernel_h <= 7, at most 64 maps and 112 output columns)");
+           "the fused full-precision convolution is for inputs with few channels (at most 8 / stride_w, stride_w 1 "
+           "or 2, kernel_h * ceil(kernel_w / (2 * stride_w)) <= 16, at most 64 maps and 128 output columns)");
   const int kmax = (1 << nn) - 1;
   const int64_t c_pad = (outmaps + 15) / 16 * 16;
   const int slots = (int)(c_pad < 64 ? 64 : c_pad);

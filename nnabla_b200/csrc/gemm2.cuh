@@ -97,22 +97,6 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr) {
                : "memory");
 }
 
-// Tiled store of a shared-memory box to global memory (bulk async group); rows
-// or columns outside the tensor are clipped by the copy engine.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *smem_src, int c0, int c1,
-                                             uint64_t l2_policy) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
-               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "l"(l2_policy)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// Waits until at most `N` of this thread's bulk groups still read shared memory.
-template <int N> __device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// Makes this thread's shared-memory writes visible to the copy engine.
-__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 } // namespace ptx
 

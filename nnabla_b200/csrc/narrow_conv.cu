@@ -3,35 +3,40 @@
 //
 // Convolution<float>::forward_impl (src/nbla/function/generic/convolution.cpp:160-197)
 // unfolds every sample to patches and multiplies. Here the product is an
-// implicit GEMM whose rows are the pixels of ONE output row (M = 128 >= Wo),
-// whose columns are the output maps (64 >= Ko) and whose K axis is the filter
-// window laid out as (ky, kx, c) with every filter row padded to 24 values:
-// K = 8 x 24 = 192. With c innermost the 24 values of one filter row are
-// CONTIGUOUS in a channel-last copy of the input row, so the A operand can be
-// built by the SM itself (a TMA box cannot: a 3-channel pixel is 6 bytes):
+// implicit GEMM whose rows are the pixels of ONE output row (M = 128 >= Wo) and
+// whose columns are the output maps (64 >= Ko). No patch matrix is ever built,
+// neither in global nor in shared memory:
 //
-//   1. a pre-pass writes x as three bf16 pieces (x = hi + mid + lo, exact),
-//      channel-last, every row padded left and right: xs [piece][n][row][704];
-//   2. per output row, one TMA box brings the kh staged rows of the three
-//      pieces into shared memory (two tiles ahead);
-//   3. ten builder warps copy 48-byte runs from there into the 128-byte-swizzled
-//      K-major layout that the tensor core reads, one K chunk (64 values) at a time;
-//   4. the weights, three bf16 pieces as well, stay resident in shared memory,
-//      the pieces stacked along N: hi x [w_hi; w_mid; w_lo] (N = 192),
-//      mid x [w_hi; w_mid] (N = 128), lo x [w_hi] (N = 64) accumulate into three
-//      groups of 64 TMEM columns, which the epilogue adds up (smallest first).
-//      The six products kept are those above 2^-24 of the leading one.
+//   1. A pre-pass writes x channel-last in fp16, every pixel in a slot of
+//      16 / stride_w bytes (4 channels at stride 2, 8 at stride 1), rows and
+//      columns zero-padded. A slot group of 16 bytes then holds the stride_w
+//      pixels that separate two neighbouring outputs, so "output pixel m, filter
+//      taps kx = c * stride_w .. (c + 1) * stride_w - 1" is the 16-byte unit m + c
+//      of the staged input row.
+//   2. The tensor core reads that row in place. An un-swizzled K-major operand is
+//      addressed as start + (row / 8) * 128 + (row % 8) * 16 + chunk * LBO; with
+//      LBO = 16 the second K chunk of row m is the first one of row m + 1: the
+//      overlapping windows of a convolution, straight from the staged row. One
+//      instruction (K = 16) covers 2 * stride_w filter taps of one filter row;
+//      a 7x7 / stride 2 filter takes 7 x 2 of them.
+//   3. The staged rows of a persistent block form a ring in shared memory: the
+//      next output row needs stride_h new input rows, fetched with one bulk copy
+//      each (both pieces of a row are contiguous); the other rows are reused.
+//   4. fp32 accuracy from fp16 operands: x * 2^-e = x0 + 2^-11 x1 and
+//      w * 2^S = w0 + 2^-11 w1 with fp16 x0, x1, w0, w1 (e per sample from
+//      max |x|, S from max |w|, so that every piece is in fp16's normal range and
+//      a residual keeps 11 more bits: 22 bits in all). The weights are stacked along
+//      N: x0 x [w0; w1] (N = 128) gives the main product in TMEM columns 0..63
+//      and one cross product in 64..127; x1 x [w0] (N = 64) accumulates the other
+//      cross product there as well. The epilogue forms
+//      (main + 2^-11 cross) * 2^(e - S). The product left out, x1 w1, is 2^-22 of
+//      the main one, the size of the representation error.
 //
-// Shared-memory bandwidth bounds the kernel (operand reads of the tensor core
-// plus the builders' copies), which is why the weight pieces are stacked: the
-// pixel operand is read once per piece instead of once per product.
-//
-// Warps: 0-3 epilogue (TMEM lanes = pixels, columns = maps; stores run along
-// the pixels of y's rows), 4 MMA issue + TMEM allocation, 5 TMA, 6-15 builders.
-// Every mbarrier wait is time-bounded; a wait that gives up stores a code in
-// *status and raises the block's abort flag, every role then falls through to
-// the common teardown.
-#include <cuda_bf16.h>
+// Warps: 0-7 epilogue (TMEM lanes = pixels, columns = maps; warp w takes lanes 32 (w % 4) and
+// maps 32 (w / 4)), 8 MMA issue + TMEM allocation, 9 loader. Every mbarrier wait is time-bounded; a wait that gives
+// up stores a code in *status and raises the block's abort flag, every role then
+// falls through to the common teardown.
+#include <cuda_fp16.h>
 
 #include <cstdlib>
 
@@ -47,32 +52,27 @@ int encode_tiled(CUtensorMap *map, int dtype_code, int rank, const void *base, c
 
 namespace {
 
-constexpr int kThreadsNC = 512;
-constexpr int kFirstBuilder = 6;  // warps 0-3 epilogue, 4 MMA, 5 TMA, 6-15 builders
-constexpr int kBuilderWarps = 10;
-constexpr int kSeg = 24;          // K values per filter row (kw * C <= 24)
-constexpr int kRowsK = 8;         // filter rows in K (the filter itself has kh <= 7)
-constexpr int kK = kSeg * kRowsK; // 192
-constexpr int kChunks = 3;        // K chunks of 64 bf16 = one 128-byte swizzled row each
+constexpr int kThreadsNC = 320;
+constexpr int kEpilogueWarps = 8, kMmaWarp = 8, kLoadWarp = 9;
 constexpr int kM = 128, kN = 64;
-constexpr int kMaxWo = 112;                         // output columns: the A ring holds 112 rows per piece
-constexpr int kPieceBytes = kMaxWo * 128;           // one piece of one A chunk (rows past Wo alias what follows)
-constexpr int kStageBytesNC = 3 * kPieceBytes;      // A chunk: three pieces
-constexpr int kStages = 2;
-constexpr int kBPieceBytes = kN * 128;               // one piece of one B chunk
-constexpr int kBBytesNC = kChunks * 3 * kBPieceBytes; // resident weights [chunk][piece][64 rows]
-constexpr int kMaxKh = 7, kPatchPitch = 704;         // staged rows of 704 bf16 = 11 x 128 bytes
-constexpr int kPatchStageBytes = 3 * kMaxKh * kPatchPitch * 2;
-constexpr int kPatchStages = 2;
-constexpr int kAccCols = 256; // TMEM columns between the two accumulators (192 used)
+constexpr int kMaxSteps = 16;             // K steps of 16 values: kernel_h * ceil(kernel_w / (2 * stride_w))
+constexpr int kStepBytes = 2 * kN * 32;   // resident weights of one K step: [w0; w1] x 16 values
+constexpr int kRing = 16;                 // staged input rows kept in shared memory
+constexpr int kMaxKh = 8;
+constexpr int kMaxRowBytes = 2560;        // one piece of one staged row
+constexpr int kInFlight = 8;              // tiles between the loader and the completed MMAs (barrier ring)
+constexpr size_t kMaxSmemNC = 224 * 1024;
+constexpr int kAccCols = 128;             // TMEM columns of one accumulator: main | cross
 
-constexpr int kStatusBuilderTimeout = 0x201;
 constexpr int kStatusNcMmaTimeout = 0x202;
 constexpr int kStatusNcEpilogueTimeout = 0x203;
 constexpr int kStatusNcLoadTimeout = 0x204;
 
 struct NarrowConv {
   int N, C, H, W, Ko, kh, kw, ph, pw, sh, sw, Ho, Wo;
+  int Hp;        // staged rows per sample: H + 2 * ph
+  int row_bytes; // one piece of one staged row (a multiple of 16)
+  int jsteps;    // K steps per filter row
 };
 
 // Result as int8 channel-last codes [N][Ho * Wo][slots] instead of fp32 NCHW: the epilogue applies
@@ -94,77 +94,171 @@ __device__ __forceinline__ uint32_t pack_codes4(int a, int b, int c, int d) {
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ void split3(float x, __nv_bfloat16 &h, __nv_bfloat16 &m, __nv_bfloat16 &l) {
-  h = __float2bfloat16_rn(x);
-  const float r1 = __fsub_rn(x, __bfloat162float(h));
-  m = __float2bfloat16_rn(r1);
-  const float r2 = __fsub_rn(r1, __bfloat162float(m));
-  l = __float2bfloat16_rn(r2);
+// e with max * 2^-e in [2^top, 2^(top + 1)) for the largest magnitude `maxbits` (fp32 bits of a
+// non-negative value); 0 for zero, denormal and non-finite maxima.
+__device__ __forceinline__ int scale_exponent(uint32_t maxbits, int top) {
+  const int E = (int)(maxbits >> 23);
+  if (E == 0 || E >= 255)
+    return 0;
+  const int e = E - 127 - top;
+  return e < -120 ? -120 : e;
+}
+__device__ __forceinline__ float pow2i(int e) { return __int_as_float((127 + e) << 23); } // -126 <= e <= 127
+
+// v = p0 + 2^-11 p1 up to 2^-22 |v| (v within fp16's range)
+__device__ __forceinline__ void split2(float v, __half &p0, __half &p1) {
+  p0 = __float2half_rn(v);
+  p1 = __float2half_rn(__fmul_rn(__fsub_rn(v, __half2float(p0)), 2048.0f));
 }
 
-// w [Ko][C][kh][kw] fp32 -> wprep [chunk][piece][kN rows][64] bf16, K index = ky * 24 + kx * C + c, zero elsewhere.
-__global__ void narrow_conv_weights_kernel(const float *__restrict__ w, NarrowConv g, __nv_bfloat16 *__restrict__ out) {
-  const int total = kN * kK;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-    const int o = i / kK, k = i - o * kK;
-    const int ky = k / kSeg, j = k - ky * kSeg;
-    const int kx = j / g.C, c = j - kx * g.C;
-    float v = 0.0f;
-    if (o < g.Ko && ky < g.kh && kx < g.kw)
-      v = w[((o * g.C + c) * g.kh + ky) * g.kw + kx];
-    __nv_bfloat16 p[3];
-    split3(v, p[0], p[1], p[2]);
-    const int chunk = k / 64, kk = k - chunk * 64;
-#pragma unroll
-    for (int q = 0; q < 3; ++q)
-      out[((chunk * 3 + q) * kN + o) * 64 + kk] = p[q];
+// max |x| of every sample as fp32 bits (non-negative floats order like their bits; a NaN ends above infinity)
+__global__ void __launch_bounds__(256) narrow_conv_absmax_kernel(const float *__restrict__ x, int64_t per_sample,
+                                                                 uint32_t *__restrict__ maxbits) {
+  const int n = blockIdx.y;
+  const float *xs = x + (int64_t)n * per_sample;
+  uint32_t m = 0;
+  const int64_t vecs = ((reinterpret_cast<uintptr_t>(xs) & 15) == 0) ? per_sample / 4 : 0;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < vecs; i += (int64_t)gridDim.x * 256) {
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(xs) + i);
+    m = max(max(m, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)), __float_as_uint(fabsf(v.z))));
+    m = max(m, __float_as_uint(fabsf(v.w)));
+  }
+  for (int64_t i = vecs * 4 + (int64_t)blockIdx.x * 256 + threadIdx.x; i < per_sample; i += (int64_t)gridDim.x * 256)
+    m = max(m, __float_as_uint(fabsf(__ldg(xs + i))));
+  m = __reduce_max_sync(0xffffffffu, m);
+  __shared__ uint32_t part[8];
+  if ((threadIdx.x & 31) == 0)
+    part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i)
+      m = max(m, part[i]);
+    atomicMax(maxbits + n, m);
   }
 }
 
-// x [N][C][H][W] fp32 -> xs [piece][N][H][704] bf16, channel-last with pw zero pixels in front:
-// xs[.., (ix + pw) * C + c]; the rest of the row is zero. One block per (row, sample).
+// x [N][C][H][W] fp32 -> xs [N][Hp][piece][row_bytes] fp16: unit u of a row holds the stride_w pixels
+// u * stride_w .. (padded column), 8 / stride_w channel slots each; zero outside the image and past C.
+// One block per (kSplitRows staged rows, sample); xscale[n] = 2^e of the sample.
+constexpr int kSplitRows = 8;
+template <int SW>
 __global__ void __launch_bounds__(256) narrow_conv_split_kernel(const float *__restrict__ x, NarrowConv g,
-                                                                __nv_bfloat16 *__restrict__ xs) {
-  const int iy = blockIdx.x, n = blockIdx.y;
-  const int64_t piece_stride = (int64_t)g.N * g.H * kPatchPitch;
-  __nv_bfloat16 *row = xs + ((int64_t)n * g.H + iy) * kPatchPitch;
-  const int first = g.pw * g.C, count = g.W * g.C;
-  for (int e = threadIdx.x; e < kPatchPitch; e += 256) {
-    const int i = e - first;
-    float v = 0.0f;
-    if (i >= 0 && i < count) {
-      const int ix = i / g.C, c = i - ix * g.C;
-      v = __ldg(x + (((int64_t)n * g.C + c) * g.H + iy) * g.W + ix);
+                                                                const uint32_t *__restrict__ maxbits,
+                                                                uint8_t *__restrict__ xs, float *__restrict__ xscale) {
+  constexpr int cpp = 8 / SW; // channel slots per pixel
+  const int n = blockIdx.y;
+  const int e = scale_exponent(maxbits[n], 14);
+  const float down = pow2i(-e);
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    xscale[n] = pow2i(e);
+  const int units = g.row_bytes >> 4;
+  const int py0 = blockIdx.x * kSplitRows;
+  const int rows = min(kSplitRows, g.Hp - py0);
+  for (int i = threadIdx.x; i < rows * units; i += 256) {
+    const int r = i / units, u = i - r * units;
+    const int py = py0 + r, iy = py - g.ph;
+    const bool row_in = iy >= 0 && iy < g.H;
+    uint8_t *row = xs + ((int64_t)n * g.Hp + py) * 2 * g.row_bytes;
+    __align__(16) __half p0[8], p1[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int t = k / cpp, c = k % cpp;
+      const int ix = u * SW + t - g.pw;
+      float v = 0.0f;
+      if (row_in && c < g.C && ix >= 0 && ix < g.W)
+        v = __fmul_rn(__ldg(x + (((int64_t)n * g.C + c) * g.H + iy) * g.W + ix), down);
+      split2(v, p0[k], p1[k]);
     }
-    __nv_bfloat16 q0, q1, q2;
-    split3(v, q0, q1, q2);
-    row[e] = q0;
-    row[piece_stride + e] = q1;
-    row[2 * piece_stride + e] = q2;
+    *reinterpret_cast<uint4 *>(row + (size_t)u * 16) = *reinterpret_cast<const uint4 *>(p0);
+    *reinterpret_cast<uint4 *>(row + g.row_bytes + (size_t)u * 16) = *reinterpret_cast<const uint4 *>(p1);
   }
 }
 
-// Lane 0 polls for its warp; the verdict is shared.
-__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort, int lane) {
-  int got = 1;
-  if (lane == 0)
-    got = ptx::mbar_wait(bar, parity, abort) ? 1 : 0;
-  return __shfl_sync(0xffffffffu, got, 0) != 0;
+// w [Ko][C][kh][kw] fp32 -> wprep [step][group of 8 rows][chunk][row % 8][8] fp16, rows = [w0 (64); w1 (64)]
+// of w * 2^S, the layout the tensor core reads without swizzle (8 x 16-byte core matrices contiguous;
+// chunk stride 128, group stride 256 bytes). Step = (ky, j); value k of chunk c2 is tap
+// kx = (2 j + c2) * stride_w + k / cpp, channel k % cpp. One block per step (every block finds max |w|
+// for itself: the filter is a few thousand values); wscale[0] = 2^-S.
+__global__ void __launch_bounds__(256) narrow_conv_weights_kernel(const float *__restrict__ w, NarrowConv g,
+                                                                  __half *__restrict__ out, float *__restrict__ wscale) {
+  __shared__ uint32_t part[8];
+  const int count = g.Ko * g.C * g.kh * g.kw;
+  uint32_t m = 0;
+  for (int i = threadIdx.x; i < count; i += 256)
+    m = max(m, __float_as_uint(fabsf(w[i])));
+  m = __reduce_max_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0)
+    part[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = part[0];
+  for (int i = 1; i < 8; ++i)
+    m = max(m, part[i]);
+  const int e = scale_exponent(m, 13);
+  const float down = pow2i(-e);
+  if (threadIdx.x == 0 && blockIdx.x == 0)
+    wscale[0] = pow2i(e);
+  const int cpp = 8 / g.sw;
+  const int s = blockIdx.x;
+  for (int rem = threadIdx.x; rem < kN * 16; rem += 256) { // (map, K value); both pieces
+    const int o = rem >> 4, kk = rem & 15;
+    const int c2 = kk >> 3, k = kk & 7;
+    const int ky = s / g.jsteps, j = s - ky * g.jsteps;
+    const int t = k / cpp, c = k - t * cpp;
+    const int kx = (2 * j + c2) * g.sw + t;
+    float v = 0.0f;
+    if (o < g.Ko && c < g.C && kx < g.kw)
+      v = __fmul_rn(w[((o * g.C + c) * g.kh + ky) * g.kw + kx], down);
+    __half p0, p1;
+    split2(v, p0, p1);
+    __half *base = out + (size_t)s * (kStepBytes / 2);
+    base[(((o >> 3) * 2 + c2) * 8 + (o & 7)) * 8 + k] = p0;
+    base[((((o + kN) >> 3) * 2 + c2) * 8 + (o & 7)) * 8 + k] = p1;
+  }
 }
+
+// The staged rows a tile needs and where they sit in the ring. Loader and MMA issuer walk the same
+// sequence of tiles and keep one of these each: rows are loaded in increasing order within a sample,
+// every loaded row takes the next ring slot (count % kRing).
+struct RowWalk {
+  int count = 0;       // rows loaded so far by this block
+  int sample = -1;     // sample of the previous tile
+  int loaded_upto = 0; // first staged row of `sample` that is not in the ring
+  // Advances to the tile (n, first row r0, kh rows); returns the number of rows to load, the first of
+  // them in `first`, and the load count of row r0 in `s0`.
+  __device__ __forceinline__ int next(int n, int r0, int kh, int &first, int &s0) {
+    if (n != sample || r0 > loaded_upto) {
+      sample = n;
+      loaded_upto = r0;
+    }
+    first = loaded_upto;
+    s0 = count - (loaded_upto - r0);
+    const int nload = r0 + kh - first;
+    count += nload;
+    loaded_upto = r0 + kh;
+    return nload;
+  }
+};
 
 __global__ void __launch_bounds__(kThreadsNC, 1)
-    narrow_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_xs, const __nv_bfloat16 *__restrict__ wprep,
+    narrow_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_y, int box_store,
+                               const uint8_t *__restrict__ xs, const uint8_t *__restrict__ wprep,
+                               const float *__restrict__ xscale, const float *__restrict__ wscale,
                                const float *__restrict__ bias, float *__restrict__ y, NarrowConv g, int *status,
                                NarrowCodesOut co) {
   extern __shared__ uint8_t smem_raw[];
-  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t *a_ring = smem;                                 // [stage][piece][112 rows][128 B], swizzled
-  uint8_t *b_res = smem + kStages * kStageBytesNC;        // [chunk][piece][64 rows][128 B], swizzled
-  uint8_t *patch = b_res + kBBytesNC;                     // [stage][piece][kh rows][704] bf16, as the TMA box arrives
-  uint64_t *bars = reinterpret_cast<uint64_t *>(patch + kPatchStages * kPatchStageBytes);
-  uint64_t *full_bar = bars, *empty_bar = bars + 2, *tmem_full = bars + 4, *tmem_empty = bars + 6,
-           *patch_full = bars + 8, *patch_empty = bars + 10;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  const int steps = g.kh * g.jsteps;
+  const uint32_t slot_bytes = 2u * (uint32_t)g.row_bytes;
+  // rows past Wo of the last ring slot read up to (kM + 2 * jsteps) units of its second piece
+  const uint32_t tail = (uint32_t)(kM + 2 * g.jsteps) * 16u;
+  uint8_t *b_res = smem;                           // [step][16 groups][2 chunks][8 rows][16 B]
+  uint8_t *ring = b_res + (size_t)steps * kStepBytes; // [slot][piece][row_bytes]
+  // fp32 result: every epilogue warp stages [32 maps][32 pixels] boxes (two, used in turn) for bulk stores
+  float *stage = reinterpret_cast<float *>(ring + ((kRing * slot_bytes + tail + 127u) & ~127u));
+  uint64_t *bars = reinterpret_cast<uint64_t *>(stage + kEpilogueWarps * 2 * 1024);
+  uint64_t *full_bar = bars, *done_bar = bars + kInFlight, *tmem_full = bars + 2 * kInFlight,
+           *tmem_empty = bars + 2 * kInFlight + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kInFlight + 4);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   // bias of every map (0 past Ko or without bias), times 2 / delta when codes are written
   __shared__ float bias_s[kN];
@@ -172,170 +266,95 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
     bias_s[threadIdx.x] = (bias && (int)threadIdx.x < g.Ko)
                               ? (co.codes ? __fmul_rn(bias[threadIdx.x], co.two_inv) : bias[threadIdx.x])
                               : 0.0f;
-
-  // word offsets, inside a staged piece, of the four words of every 16-byte chunk of the K row:
-  // K word wk = (filter row ky, word j2 of its 12-word run) -> ky * 352 + j2
-  __shared__ uint4 run_offsets[kChunks * 8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // consecutive output rows per block, so that a tile finds most of its input rows in the ring
   const int num_tiles = g.N * g.Ho;
-  constexpr uint32_t kTmemCols = 512; // two accumulators of 192 columns, 256 apart
-  if (threadIdx.x < kChunks * 8) {
-    uint32_t o[4];
-#pragma unroll
-    for (int w4 = 0; w4 < 4; ++w4) {
-      const int wk = threadIdx.x * 4 + w4;
-      int ky = wk / (kSeg / 2);
-      const int j2 = wk - ky * (kSeg / 2);
-      ky = ky < g.kh ? ky : g.kh - 1; // rows of K past the filter meet zero weights: any finite data
-      o[w4] = (uint32_t)(ky * (kPatchPitch / 2) + j2);
-    }
-    run_offsets[threadIdx.x] = make_uint4(o[0], o[1], o[2], o[3]);
-  }
+  const int tile_first = (int)((int64_t)num_tiles * blockIdx.x / gridDim.x);
+  const int tile_last = (int)((int64_t)num_tiles * (blockIdx.x + 1) / gridDim.x);
+  constexpr uint32_t kTmemCols = 2 * kAccCols;
 
   if (threadIdx.x == 0) {
+    for (int s = 0; s < kInFlight; ++s) {
+      ptx::mbar_init(full_bar + s, 1);
+      ptx::mbar_init(done_bar + s, 1);
+    }
     for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(full_bar + s, kBuilderWarps);
-      ptx::mbar_init(empty_bar + s, 1);
       ptx::mbar_init(tmem_full + s, 1);
-      ptx::mbar_init(tmem_empty + s, 4);
-      ptx::mbar_init(patch_full + s, 1);
-      ptx::mbar_init(patch_empty + s, kBuilderWarps);
+      ptx::mbar_init(tmem_empty + s, kEpilogueWarps);
     }
     *abort_flag = 0;
     ptx::mbar_fence_init();
-    ptx::prefetch_tensormap(&map_xs);
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     ptx::tmem_alloc(tmem_slot, kTmemCols);
     ptx::tmem_relinquish();
   }
-  // resident weights: plain copy into the swizzled layout (16-byte chunk c of row r sits at chunk c ^ (r & 7))
   {
+    // resident weights (already in the tensor core's layout) and zeros behind the ring
     const uint4 *src = reinterpret_cast<const uint4 *>(wprep);
-    constexpr int kVecs = kBBytesNC / 16;
-    for (int i = threadIdx.x; i < kVecs; i += kThreadsNC) {
-      const int row_all = i >> 3, c16 = i & 7; // row over [chunk][piece][64]
-      *reinterpret_cast<uint4 *>(b_res + (size_t)row_all * 128 + ((c16 ^ (row_all & 7)) << 4)) = __ldg(src + i);
-    }
+    const int vecs = steps * (kStepBytes / 16);
+    for (int i = threadIdx.x; i < vecs; i += kThreadsNC)
+      reinterpret_cast<uint4 *>(b_res)[i] = __ldg(src + i);
+    for (uint32_t i = threadIdx.x; i < tail / 16u; i += kThreadsNC)
+      reinterpret_cast<uint4 *>(ring + kRing * slot_bytes)[i] = make_uint4(0, 0, 0, 0);
     fence_async_smem();
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t piece_bytes = (uint32_t)((g.Wo + 7) >> 3) * 1024u; // whole groups of 8 rows
-  const uint32_t patch_piece_words = (uint32_t)(g.kh * kPatchPitch) / 2u;
-  const uint32_t patch_bytes = 3u * (uint32_t)g.kh * kPatchPitch * 2u;
 
-  if (warp >= kFirstBuilder) {
-    // ------------------------------------------------------------ operand builders
-    const int bw = warp - kFirstBuilder;
-    int stage = 0, pstage = 0;
-    uint32_t phase = 0, pphase = 0;
-    const int rows_pad = ((g.Wo + 7) >> 3) << 3;
-    const int groups32 = (rows_pad + 31) >> 5;
-    const int step = (g.sw * g.C) / 2; // 32-bit words between the runs of neighbouring pixels
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      if (!warp_wait(patch_full + pstage, pphase, abort_flag, lane)) {
-        if (lane == 0) {
-          if (*abort_flag == 0)
-            atomicCAS(status, 0, kStatusBuilderTimeout);
-          *abort_flag = 1;
-        }
-        break;
-      }
-      const uint32_t *pwords = reinterpret_cast<const uint32_t *>(patch + pstage * kPatchStageBytes);
-      for (int chunk = 0; chunk < kChunks; ++chunk) {
-        if (!warp_wait(empty_bar + stage, phase ^ 1u, abort_flag, lane)) {
-          if (lane == 0) {
-            if (*abort_flag == 0)
-              atomicCAS(status, 0, kStatusBuilderTimeout);
-            *abort_flag = 1;
-          }
-          ok = false;
-          break;
-        }
-        uint8_t *dst = a_ring + stage * kStageBytesNC;
-        // item = (piece, group of 32 rows, pair of 16-byte chunks of the K chunk); lane = row. The
-        // loads of a warp are 3 words apart (all banks), a quarter warp stores eight rows of one
-        // chunk column, whose swizzled positions cover all banks too.
-        const int items = 3 * groups32 * 4;
-#pragma unroll 2
-        for (int it = bw; it < items; it += kBuilderWarps) {
-          const int pair = it & 3, prg = it >> 2;
-          const int piece = (prg >= groups32 ? 1 : 0) + (prg >= 2 * groups32 ? 1 : 0);
-          const int r = (prg - piece * groups32) * 32 + lane;
-          if (r < rows_pad) {
-            const uint32_t *srow = pwords + piece * patch_piece_words + r * step;
-            uint8_t *drow = dst + piece * piece_bytes + r * 128;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int c16 = 2 * pair + h;
-              const uint4 off = run_offsets[chunk * 8 + c16];
-              uint4 v;
-              v.x = srow[off.x];
-              v.y = srow[off.y];
-              v.z = srow[off.z];
-              v.w = srow[off.w];
-              *reinterpret_cast<uint4 *>(drow + ((c16 ^ (r & 7)) << 4)) = v;
-            }
-          }
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0)
-          ptx::mbar_arrive(full_bar + stage); // one arrival per warp
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
-      }
-      __syncwarp();
-      if (lane == 0)
-        ptx::mbar_arrive(patch_empty + pstage); // this warp has read the staged rows
-      if (++pstage == kPatchStages) {
-        pstage = 0;
-        pphase ^= 1u;
-      }
-    }
-  } else if (warp == 5) {
-    // ------------------------------------------------------------ TMA: staged rows, two tiles ahead
+  if (warp == kLoadWarp) {
+    // ------------------------------------------------------------ loader: the new rows of every tile
     if (ptx::elect_one()) {
-      int pstage = 0;
-      uint32_t pphase = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        if (!ptx::mbar_wait(patch_empty + pstage, pphase ^ 1u, abort_flag)) {
-          if (*abort_flag == 0)
-            atomicCAS(status, 0, kStatusNcLoadTimeout);
-          *abort_flag = 1;
-          break;
-        }
+      RowWalk walk;
+      int s0_of[2 * kInFlight];
+      int seq = 0, oldest = 0;
+      bool ok = true;
+      for (int tile = tile_first; tile < tile_last && ok; ++tile, ++seq) {
         const int n = tile / g.Ho, oy = tile - n * g.Ho;
-        ptx::mbar_expect_tx(patch_full + pstage, patch_bytes);
-        // box = (64, 11, kh, 1, 3) at (0, 0, first input row, n, 0); rows outside the image arrive as zeros
-        ptx::tma_load_5d(patch + pstage * kPatchStageBytes, &map_xs, patch_full + pstage, 0, 0, oy * g.sh - g.ph, n,
-                         0);
-        if (++pstage == kPatchStages) {
-          pstage = 0;
-          pphase ^= 1u;
+        int first, s0;
+        const int count_before = walk.count;
+        const int nload = walk.next(n, oy * g.sh, g.kh, first, s0);
+        // ring slots about to be overwritten, and the barrier of this tile, must have been released
+        // by the tiles that used them
+        while (oldest < seq && (s0_of[oldest & (2 * kInFlight - 1)] + kRing < walk.count || seq - oldest >= kInFlight)) {
+          if (!ptx::mbar_wait(done_bar + (oldest & (kInFlight - 1)), (uint32_t)(oldest / kInFlight) & 1u, abort_flag)) {
+            if (*abort_flag == 0)
+              atomicCAS(status, 0, kStatusNcLoadTimeout);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ++oldest;
         }
+        if (!ok)
+          break;
+        s0_of[seq & (2 * kInFlight - 1)] = s0;
+        uint64_t *bar = full_bar + (seq & (kInFlight - 1));
+        ptx::mbar_expect_tx(bar, (uint32_t)nload * slot_bytes);
+        const uint8_t *src = xs + ((int64_t)n * g.Hp + first) * slot_bytes;
+        for (int i = 0; i < nload; ++i)
+          ptx::bulk_load(ring + (uint32_t)((count_before + i) % kRing) * slot_bytes, src + (int64_t)i * slot_bytes,
+                         slot_bytes, bar);
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == kMmaWarp) {
     // -------------------------------------------------------------- MMA issuer
     if (ptx::elect_one()) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int local = 0;
+      RowWalk walk;
+      int seq = 0;
       bool ok = true;
-      const uint32_t idesc192 = ptx::make_idesc(1u, 1u, kM, 192), idesc128 = ptx::make_idesc(1u, 1u, kM, 128),
-                     idesc64 = ptx::make_idesc(1u, 1u, kM, 64);
-      const uint32_t b_base = ptx::smem_u32(b_res);
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        const int buf = local & 1;
-        const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
-        if (!ptx::mbar_wait(tmem_empty + buf, buf_phase ^ 1u, abort_flag)) {
+      const uint32_t idesc128 = ptx::make_idesc(1u, 0u, kM, 128), idesc64 = ptx::make_idesc(1u, 0u, kM, 64);
+      const uint32_t b_base = ptx::smem_u32(b_res), ring_base = ptx::smem_u32(ring);
+      for (int tile = tile_first; tile < tile_last && ok; ++tile, ++seq) {
+        const int buf = seq & 1;
+        const uint32_t buf_phase = (uint32_t)(seq >> 1) & 1u;
+        const int n = tile / g.Ho, oy = tile - n * g.Ho;
+        int first, s0;
+        walk.next(n, oy * g.sh, g.kh, first, s0);
+        if (!ptx::mbar_wait(tmem_empty + buf, buf_phase ^ 1u, abort_flag) ||
+            !ptx::mbar_wait(full_bar + (seq & (kInFlight - 1)), (uint32_t)(seq / kInFlight) & 1u, abort_flag)) {
           if (*abort_flag == 0)
             atomicCAS(status, 0, kStatusNcMmaTimeout);
           *abort_flag = 1;
@@ -344,46 +363,36 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kAccCols);
         uint32_t accumulate = 0;
-        for (int chunk = 0; chunk < kChunks; ++chunk) {
-          if (!ptx::mbar_wait(full_bar + stage, phase, abort_flag)) {
-            if (*abort_flag == 0)
-              atomicCAS(status, 0, kStatusNcMmaTimeout);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          ptx::tc_fence_after_sync();
-          const uint32_t a_base = ptx::smem_u32(a_ring + stage * kStageBytesNC);
-          const uint64_t a0 = ptx::smem_desc_k(a_base, 128u), a1 = ptx::smem_desc_k(a_base + piece_bytes, 128u),
-                         a2 = ptx::smem_desc_k(a_base + 2 * piece_bytes, 128u);
-          // weight pieces of this chunk, stacked along N: rows [w_hi; w_mid; w_lo]
-          const uint64_t bdesc = ptx::smem_desc_k(b_base + chunk * 3 * kBPieceBytes, 128u);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            ptx::mma_bf16(d_tmem, a0 + 2 * k, bdesc + 2 * k, idesc192, accumulate); // hi x (hi, mid, lo) -> columns 0..191
-            ptx::mma_bf16(d_tmem, a1 + 2 * k, bdesc + 2 * k, idesc128, 1u);        // mid x (hi, mid)    -> columns 0..127
-            ptx::mma_bf16(d_tmem, a2 + 2 * k, bdesc + 2 * k, idesc64, 1u);         // lo x hi            -> columns 0..63
+        int step = 0;
+        for (int ky = 0; ky < g.kh; ++ky) {
+          const uint32_t row = ring_base + (uint32_t)((s0 + ky) % kRing) * slot_bytes;
+          for (int j = 0; j < g.jsteps; ++j, ++step) {
+            // rows 16 bytes apart, the second K chunk 16 bytes behind the first: sliding windows
+            const uint64_t a0 = ptx::smem_desc_k_plain(row + (uint32_t)j * 32u, 16u, 128u);
+            const uint64_t a1 = ptx::smem_desc_k_plain(row + (uint32_t)g.row_bytes + (uint32_t)j * 32u, 16u, 128u);
+            const uint64_t b = ptx::smem_desc_k_plain(b_base + (uint32_t)step * kStepBytes, 128u, 256u);
+            ptx::mma_bf16(d_tmem, a0, b, idesc128, accumulate);  // x0 x [w0; w1] -> columns 0..127
+            ptx::mma_bf16(d_tmem + kN, a1, b, idesc64, 1u);      // x1 x [w0]     -> columns 64..127
             accumulate = 1;
           }
-          ptx::mma_commit(empty_bar + stage);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
         }
-        if (ok)
-          ptx::mma_commit(tmem_full + buf);
+        ptx::mma_commit(done_bar + (seq & (kInFlight - 1)));
+        ptx::mma_commit(tmem_full + buf);
       }
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int quarter = warp; // TMEM lanes [32 * warp, 32 * warp + 32)
+    const int quarter = warp & 3; // TMEM lanes [32 * quarter, 32 * quarter + 32)
+    const int half = warp >> 2;   // maps [32 * half, 32 * half + 32)
     int local = 0;
     const int px = quarter * 32 + lane;
     const int64_t plane = (int64_t)g.Ho * g.Wo;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+    const float ws = __ldg(wscale);
+    for (int tile = tile_first; tile < tile_last; ++tile, ++local) {
       const int buf = local & 1;
       const uint32_t buf_phase = (uint32_t)(local >> 1) & 1u;
+      const int n = tile / g.Ho, oy = tile - n * g.Ho;
+      const float scale = __fmul_rn(__ldg(xscale + n), ws); // 2^(e - S)
       const bool got = ptx::mbar_wait_backoff(tmem_full + buf, buf_phase, abort_flag, 100u);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) {
@@ -394,21 +403,19 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
         break;
       }
       ptx::tc_fence_after_sync();
-      const int n = tile / g.Ho, oy = tile - n * g.Ho;
       float *yrow = y + (int64_t)n * g.Ko * plane + (int64_t)oy * g.Wo + px;
       const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kAccCols);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t r0[32], r1[32], r2[32];
-        ptx::tmem_ld_32x32(t0 + (uint32_t)(half * 32), r0);       // products with w_hi
-        ptx::tmem_ld_32x32(t0 + (uint32_t)(64 + half * 32), r1);  // with w_mid
-        ptx::tmem_ld_32x32(t0 + (uint32_t)(128 + half * 32), r2); // with w_lo
+      {
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld_32x32(t0 + (uint32_t)(half * 32), r0);      // x0 w0
+        ptx::tmem_ld_32x32(t0 + (uint32_t)(kN + half * 32), r1); // x0 w1 + x1 w0, times 2^11
         ptx::tmem_ld_wait();
         if (co.codes != nullptr) {
           if (px < g.Wo && half * 32 < co.slots) {
-            // u = (conv) * (2 / delta) + bias * (2 / delta), one fused multiply-add; then ReLU and the
+            // u = conv * (2 / delta) + bias * (2 / delta), one fused multiply-add; then ReLU and the
             // quantizer of a non-negative value, (floor(u) + 1) >> 1 capped at kmax
             const float cap = (float)(2 * co.kmax) + 0.5f;
+            const float k2 = __fmul_rn(scale, co.two_inv);
             uint32_t wds[8];
 #pragma unroll
             for (int j4 = 0; j4 < 8; ++j4) {
@@ -416,8 +423,8 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
                 const int j = 4 * j4 + k;
-                const float conv = __fadd_rn(__fadd_rn(__uint_as_float(r2[j]), __uint_as_float(r1[j])), __uint_as_float(r0[j]));
-                const float u = __fmaf_rn(conv, co.two_inv, bias_s[half * 32 + j]);
+                const float raw = __fmaf_rn(__uint_as_float(r1[j]), 0.00048828125f, __uint_as_float(r0[j]));
+                const float u = __fmaf_rn(raw, k2, bias_s[half * 32 + j]);
                 if (co.relu) {
                   c[k] = (__float2int_rd(fminf(fmaxf(u, 0.0f), cap)) + 1) >> 1; // a NaN becomes 0
                 } else {
@@ -434,13 +441,32 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
             if (half * 32 + 16 < co.slots)
               cp[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
           }
+        } else if (box_store) {
+          // the copy engine writes the box: whole lines, clipped at Wo and Ko, while the warp goes on
+          float *box = stage + (warp * 2 + (local & 1)) * 1024;
+          if (lane == 0)
+            ptx::tma_store_wait_read<1>(); // the store before the previous one read this box
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = __fmul_rn(__fmaf_rn(__uint_as_float(r1[j]), 0.00048828125f, __uint_as_float(r0[j])), scale);
+            if (bias)
+              v = __fadd_rn(v, bias_s[half * 32 + j]);
+            box[j * 32 + lane] = v;
+          }
+          ptx::fence_async_shared();
+          __syncwarp();
+          if (lane == 0 && quarter * 32 < g.Wo && half * 32 < g.Ko) {
+            ptx::tma_store_4d(&map_y, box, quarter * 32, oy, half * 32, n);
+            ptx::tma_store_commit();
+          }
         } else if (px < g.Wo) {
           float *yp = yrow + (int64_t)(half * 32) * plane;
 #pragma unroll
           for (int j = 0; j < 32; ++j, yp += plane) {
             const int o = half * 32 + j;
             if (o < g.Ko) {
-              float v = __fadd_rn(__fadd_rn(__uint_as_float(r2[j]), __uint_as_float(r1[j])), __uint_as_float(r0[j]));
+              float v = __fmul_rn(__fmaf_rn(__uint_as_float(r1[j]), 0.00048828125f, __uint_as_float(r0[j])), scale);
               if (bias)
                 v = __fadd_rn(v, bias_s[o]);
               __stcs(yp, v);
@@ -456,6 +482,8 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
   }
 
   // ------------------------------------------------------------------ teardown
+  if (warp < kEpilogueWarps && lane == 0)
+    ptx::tma_store_wait_all(); // this thread's bulk stores have been written
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0) {
@@ -465,14 +493,29 @@ __global__ void __launch_bounds__(kThreadsNC, 1)
       __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
-constexpr size_t kSmemNC = (size_t)kStages * kStageBytesNC + kBBytesNC + kPatchStages * kPatchStageBytes + 12 * 8 +
-                           16 + 1024;
+// K steps per filter row, bytes of one staged piece row, shared memory of the kernel
+struct NarrowPlan {
+  int jsteps, steps, row_bytes;
+  size_t smem;
+};
+
+NarrowPlan narrow_plan(int width, int kernel_h, int kernel_w, int pad_w, int stride_w, int Wo) {
+  NarrowPlan p;
+  p.jsteps = (kernel_w + 2 * stride_w - 1) / (2 * stride_w);
+  p.steps = kernel_h * p.jsteps;
+  const int units_image = (width + 2 * pad_w + stride_w - 1) / stride_w;
+  const int units_read = Wo - 1 + 2 * p.jsteps; // by rows that hold an output pixel
+  p.row_bytes = 16 * (units_image > units_read ? units_image : units_read);
+  const size_t ring = ((size_t)kRing * 2 * p.row_bytes + (size_t)(kM + 2 * p.jsteps) * 16 + 127) & ~size_t(127);
+  p.smem = (size_t)p.steps * kStepBytes + ring + kEpilogueWarps * 2 * 4096 + (2 * kInFlight + 4) * 8 + 16 + 128;
+  return p;
+}
 
 } // namespace
 
@@ -486,10 +529,11 @@ bool narrow_conv_applies(const float *x, int channels, int height, int width, in
     return false;
   (void)x;
   (void)height;
-  return group == 1 && dilation_h == 1 && dilation_w == 1 && kernel_w * channels <= kSeg && kernel_h <= kMaxKh &&
-         outmaps <= kN && Wo <= kMaxWo && ((stride_w * channels) & 1) == 0 &&
-         ((Wo + 7) / 8 * 8 - 1) * stride_w * channels + kSeg <= kPatchPitch &&
-         (width + 2 * pad_w) * channels <= kPatchPitch;
+  if (!(group == 1 && dilation_h == 1 && dilation_w == 1 && (stride_w == 1 || stride_w == 2) &&
+        channels <= 8 / stride_w && outmaps <= kN && Wo <= kM && kernel_h <= kMaxKh))
+    return false;
+  const NarrowPlan p = narrow_plan(width, kernel_h, kernel_w, pad_w, stride_w, Wo);
+  return p.steps <= kMaxSteps && p.row_bytes <= kMaxRowBytes && p.smem <= kMaxSmemNC;
 }
 
 int narrow_conv_tc(const float *x, const float *w, const float *bias, float *y, int batch, int channels, int height,
@@ -497,38 +541,61 @@ int narrow_conv_tc(const float *x, const float *w, const float *bias, float *y, 
                    int stride_w, int Ho, int Wo, cudaStream_t st, int8_t *y_codes, int slots, int relu, int kmax,
                    int kmin, float delta) {
   NarrowCodesOut co{y_codes, slots, relu, kmax, kmin, y_codes ? 2.0f / delta : 0.0f};
-  NarrowConv g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, Ho, Wo};
-  NB_CHECK(batch <= 65535, NB200_ENOTIMPL, "batch larger than 65535");
-  const size_t xs_bytes = (size_t)3 * batch * height * kPatchPitch * 2;
+  const NarrowPlan p = narrow_plan(width, kernel_h, kernel_w, pad_w, stride_w, Wo);
+  NarrowConv g{batch,    channels, height, width, outmaps, kernel_h,          kernel_w,    pad_h,
+               pad_w,    stride_h, stride_w, Ho,  Wo,      height + 2 * pad_h, p.row_bytes, p.jsteps};
+  NB_CHECK(batch <= 65535 && g.Hp <= 65535, NB200_ENOTIMPL, "batch or padded height larger than 65535");
+  // scratch: weights | staged input | per-sample maxima (bits) | per-sample 2^e | 2^-S
+  const size_t w_bytes = (size_t)p.steps * kStepBytes;
+  const size_t xs_bytes = (size_t)batch * g.Hp * 2 * p.row_bytes;
+  const size_t tail_bytes = ((size_t)batch * 8 + 16 + 255) & ~size_t(255);
   AsyncScratch scratch(st);
-  NB_TRY(scratch.alloc(kBBytesNC + xs_bytes));
-  __nv_bfloat16 *wprep = static_cast<__nv_bfloat16 *>(scratch.p);
-  __nv_bfloat16 *xs = wprep + kBBytesNC / 2;
-  narrow_conv_weights_kernel<<<(kN * kK + 255) / 256, 256, 0, st>>>(w, g, wprep);
+  NB_TRY(scratch.alloc(w_bytes + xs_bytes + tail_bytes));
+  uint8_t *wprep = static_cast<uint8_t *>(scratch.p);
+  uint8_t *xs = wprep + w_bytes;
+  uint32_t *maxbits = reinterpret_cast<uint32_t *>(xs + xs_bytes);
+  float *xscale = reinterpret_cast<float *>(maxbits + batch);
+  float *wscale = xscale + batch;
+  NB_CUDA(cudaMemsetAsync(maxbits, 0, (size_t)batch * 4, st));
+  const int64_t per_sample = (int64_t)channels * height * width;
+  int blocks = (int)((per_sample / 4 + 255) / 256);
+  const int cap = (8 * sm_count() + batch - 1) / batch;
+  blocks = blocks < 1 ? 1 : (blocks > cap ? (cap < 1 ? 1 : cap) : blocks);
+  narrow_conv_absmax_kernel<<<dim3((unsigned)blocks, (unsigned)batch), 256, 0, st>>>(x, per_sample, maxbits);
   NB_LAUNCH_CHECK();
-  narrow_conv_split_kernel<<<dim3((unsigned)height, (unsigned)batch), 256, 0, st>>>(x, g, xs);
+  narrow_conv_weights_kernel<<<p.steps, 256, 0, st>>>(w, g, reinterpret_cast<__half *>(wprep), wscale);
   NB_LAUNCH_CHECK();
-  // xs as (64, 11, H, N, piece) bf16: a staged row is 11 runs of 128 bytes (a box extent is at most 256);
-  // one box = the kh staged rows of an output row, all three pieces
-  CUtensorMap map_xs;
-  const uint64_t row_b = (uint64_t)kPatchPitch * 2;
-  const uint64_t dims[5] = {64, (uint64_t)kPatchPitch / 64, (uint64_t)height, (uint64_t)batch, 3};
-  const uint64_t strides[4] = {128, row_b, row_b * height, row_b * height * batch};
-  const uint32_t box[5] = {64, (uint32_t)kPatchPitch / 64, (uint32_t)kernel_h, 1, 3};
-  NB_TRY(encode_tiled(&map_xs, 0, 5, xs, dims, strides, box, nullptr, 0));
+  const dim3 split_grid((unsigned)((g.Hp + kSplitRows - 1) / kSplitRows), (unsigned)batch);
+  if (stride_w == 2)
+    narrow_conv_split_kernel<2><<<split_grid, 256, 0, st>>>(x, g, maxbits, xs, xscale);
+  else
+    narrow_conv_split_kernel<1><<<split_grid, 256, 0, st>>>(x, g, maxbits, xs, xscale);
+  NB_LAUNCH_CHECK();
   static bool configured[64];
   int dev = 0;
   NB_CUDA(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    NB_CUDA(cudaFuncSetAttribute(narrow_conv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kSmemNC));
+    NB_CUDA(cudaFuncSetAttribute(narrow_conv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmemNC));
     configured[dev & 63] = true;
+  }
+  // y as (Wo, Ho, Ko, N) fp32 for the bulk stores of the fp32 result (needs 16-byte row pitch and base)
+  CUtensorMap map_y;
+  const bool box_store = y_codes == nullptr && (Wo % 4) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+  {
+    const bool real = box_store;
+    const uint64_t dims[4] = {(uint64_t)(real ? Wo : 32), (uint64_t)(real ? Ho : 1), (uint64_t)(real ? outmaps : 32),
+                              (uint64_t)(real ? batch : 1)};
+    const uint64_t strides[3] = {dims[0] * 4, dims[0] * dims[1] * 4, dims[0] * dims[1] * dims[2] * 4};
+    const uint32_t box[4] = {32, 1, 32, 1};
+    // without a usable y the map covers the (16-byte aligned) scratch and is never used
+    NB_TRY(encode_tiled(&map_y, 2, 4, real ? static_cast<const void *>(y) : static_cast<const void *>(wprep), dims,
+                        strides, box, nullptr, 0));
   }
   int *status = nullptr;
   NB_TRY(device_status_word(&status));
   const int tiles = batch * Ho;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  narrow_conv_tcgen05_kernel<<<grid, kThreadsNC, kSmemNC, st>>>(map_xs, wprep, bias, y, g, status, co);
+  narrow_conv_tcgen05_kernel<<<grid, kThreadsNC, p.smem, st>>>(map_y, box_store ? 1 : 0, xs, wprep, xscale, wscale, bias, y, g, status, co);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }

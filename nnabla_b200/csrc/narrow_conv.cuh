@@ -4,9 +4,9 @@
 
 namespace nb200 {
 
-// Whether the geometry fits the kernel: group 1, no dilation, kernel_w * channels <= 24,
-// kernel_h <= 7, at most 64 output maps and 112 output columns, an even stride_w * channels,
-// padded rows of at most 704 values (channels * (width + 2 * pad_w)).
+// Whether the geometry fits the kernel: group 1, no dilation, stride_w 1 or 2 with at most
+// 8 / stride_w channels, kernel_h <= 8, kernel_h * ceil(kernel_w / (2 * stride_w)) <= 16, at most 64
+// output maps and 128 output columns, padded rows of at most 2560 bytes in fp16 channel slots.
 // NNABLA_B200_DIRECT_CONV=1 switches the path off (the CUDA-core kernel then runs).
 bool narrow_conv_applies(const float *x, int channels, int height, int width, int outmaps, int kernel_h,
                          int kernel_w, int pad_w, int stride_w, int dilation_h, int dilation_w, int group, int Wo);

@@ -116,6 +116,37 @@ __device__ __forceinline__ void tma_load_5d(void *smem_dst, const CUtensorMap *m
                : "memory");
 }
 
+// Untiled bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) from global
+// memory into this CTA's shared memory; completion on an mbarrier.
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// Tiled store of a shared-memory box to global memory (bulk async group); rows
+// or columns outside the tensor are clipped by the copy engine.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *smem_src, int c0, int c1,
+                                             uint64_t l2_policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "l"(l2_policy)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *m, const void *smem_src, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most `N` of this thread's bulk groups still read shared memory.
+template <int N> __device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Makes this thread's shared-memory writes visible to the copy engine.
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // ---- tcgen05 ----------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
@@ -185,6 +216,18 @@ __device__ __forceinline__ uint64_t smem_desc_k(uint32_t smem_addr, uint32_t row
   return d;
 }
 __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) { return smem_desc_k(smem_addr, 128u); }
+
+// The same for an operand stored without swizzle: row r, 16-byte chunk c of the K extent of one
+// instruction sits at start + (r / 8) * group_bytes + (r % 8) * 16 + c * chunk_bytes (the 8 x 16-byte
+// core matrices are contiguous; chunk_bytes is the leading and group_bytes the stride byte offset).
+__device__ __forceinline__ uint64_t smem_desc_k_plain(uint32_t smem_addr, uint32_t chunk_bytes, uint32_t group_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)((chunk_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((group_bytes >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
 
 // Instruction descriptor: dense, D format (1 = f32, 2 = s32), A/B formats,
 // both operands K-major, N at bits [17,23) as N/8, M at bits [24,29) as M/16.
