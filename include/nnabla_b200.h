@@ -561,6 +561,44 @@ int nb200_max_pooling_f32(const float *x, float *y, int64_t maps, int height, in
 /* GlobalAveragePooling<float>::forward_impl
  * (src/nbla/function/generic/global_average_pooling.cpp): x [maps, spatial] -> y [maps]. */
 int nb200_global_average_pooling_f32(const float *x, float *y, int64_t maps, int64_t spatial, void *stream);
+/* ---- training side of the companions ---- */
+/* BatchNormalization<float>::forward_impl_batch
+ * (src/nbla/function/generic/batch_normalization.cpp:157-226), batch_stat = true, one normalised
+ * axis: batch_mean / batch_var [channels] receive the statistics of x (variance = E[x^2] - mean^2),
+ * y = (x - mean) * gamma / sqrt(var + eps) + beta in that operation order, and (update_running != 0)
+ * running = decay * running + (1 - decay) * batch (the variance unbiased by n / (n - 1)) as :201-205.
+ * The per-channel sums are block partials added in a fixed order (deterministic; they agree with the
+ * reference's sequential fp32 sums to rounding). beta / gamma may be NULL. */
+int nb200_batch_normalization_batch_f32(const float *x, const float *beta, const float *gamma, float *running_mean,
+                                        float *running_var, float *y, float *batch_mean, float *batch_var,
+                                        int64_t outer, int64_t channels, int64_t inner, float eps, float decay_rate,
+                                        int update_running, void *stream);
+/* BatchNormalization<float>::backward_impl (batch_normalization.cpp:262-486). batch_stat != 0
+ * (backward_impl_batch): mean / var are the batch statistics of the forward pass, dmean / dvar the
+ * gradients arriving at the statistics outputs (NULL: none). batch_stat == 0 (backward_impl_global):
+ * mean / var are the running statistics, dx = dy * gamma * (var + eps)^-0.5. dx, dbeta, dgamma may
+ * each be NULL (not propagated); the accum flags add to what the buffers hold. */
+int nb200_batch_normalization_backward_f32(const float *x, const float *dy, const float *gamma, const float *mean,
+                                           const float *var, const float *dmean, const float *dvar, float *dx,
+                                           float *dbeta, float *dgamma, int64_t outer, int64_t channels,
+                                           int64_t inner, float eps, int batch_stat, int accum_dx, int accum_dbeta,
+                                           int accum_dgamma, void *stream);
+/* ReLU<float>::backward_impl (src/nbla/function/generic/relu.cpp:41-66): dx (+)= y > 0 ? dy : 0 with
+ * y the forward OUTPUT. */
+int nb200_relu_backward_f32(const float *y, const float *dy, float *dx, size_t size, int accum, void *stream);
+/* Add2<float>::backward_impl (src/nbla/function/generic/add2.cpp), equal shapes: one call per input,
+ * dx (+)= dy. */
+int nb200_add2_backward_f32(const float *dy, float *dx, size_t size, int accum, void *stream);
+/* GlobalAveragePooling<float>::backward_impl (global_average_pooling.cpp:75-117):
+ * dx[m][.] (+)= dy[m] / spatial. */
+int nb200_global_average_pooling_backward_f32(const float *dy, float *dx, int64_t maps, int64_t spatial, int accum,
+                                              void *stream);
+/* MaxPooling<float>::backward_impl (src/nbla/function/generic/max_pooling.cpp:194-228): dy of every
+ * output goes to the FIRST maximum of its clipped window (:63-73), summed in output order, which is
+ * how the reference's index map and its `dx[index] += dy` loop behave; x is the forward input. */
+int nb200_max_pooling_backward_f32(const float *x, const float *dy, float *dx, int64_t maps, int height, int width,
+                                   int kernel_h, int kernel_w, int stride_h, int stride_w, int pad_h, int pad_w,
+                                   int ignore_border, int accum, void *stream);
 /* Convolution<float>::forward_impl (src/nbla/function/generic/convolution.cpp:160-197)
  * in full precision for layers with few input channels (the network stem):
  * direct convolution, products accumulated with fused multiply-adds in the

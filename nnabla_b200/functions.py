@@ -634,10 +634,11 @@ def convolution(x, weight, bias=None, base_axis=1, pad=None, stride=None, dilati
 
 def batch_normalization(x, beta, gamma, mean, variance, axes=[1], decay_rate=0.9, eps=1e-05, batch_stat=True,
                         output_stat=False, n_outputs=None):
-    """Batch normalization (python/src/nnabla/functions.py batch_normalization), inference only:
-    BatchNormalization::forward_impl_global (src/nbla/function/generic/batch_normalization.cpp:228-260)."""
-    if batch_stat:
-        raise C.NB200Error(4, "batch_stat=True (training statistics) is outside the forward inference path")
+    """Batch normalization (python/src/nnabla/functions.py batch_normalization).
+    batch_stat=False: BatchNormalization::forward_impl_global
+    (src/nbla/function/generic/batch_normalization.cpp:228-260). batch_stat=True: forward_impl_batch
+    (:157-226): normalises with the statistics of x and updates `mean` / `variance` (the running
+    statistics) in place; output_stat=True also returns the batch mean and variance."""
     x = _check_input(x)
     axes = list(axes)
     if len(axes) != 1:
@@ -660,6 +661,17 @@ def batch_normalization(x, beta, gamma, mean, variance, axes=[1], decay_rate=0.9
     if params[2] is None or params[3] is None:
         raise RuntimeError("mean and variance are required")
     y = torch.empty_like(x)
+    if batch_stat:
+        bm = torch.empty(Cn, dtype=torch.float32, device=x.device)
+        bv = torch.empty(Cn, dtype=torch.float32, device=x.device)
+        with C.on_device(x.device):
+            C.call("nb200_batch_normalization_batch_f32", C.ptr(x), C.ptr(params[0]), C.ptr(params[1]),
+                   C.ptr(params[2]), C.ptr(params[3]), C.ptr(y), C.ptr(bm), C.ptr(bv), ctypes.c_int64(outer),
+                   ctypes.c_int64(Cn), ctypes.c_int64(inner), C.c_float(eps), C.c_float(decay_rate), 1,
+                   C.stream_ptr(x.device))
+        if output_stat:
+            return y, bm.reshape(params[2].shape), bv.reshape(params[3].shape)
+        return y
     with C.on_device(x.device):
         C.call("nb200_batch_normalization_inference_f32", C.ptr(x), C.ptr(params[0]), C.ptr(params[1]),
                C.ptr(params[2]), C.ptr(params[3]), C.ptr(y), ctypes.c_int64(outer), ctypes.c_int64(Cn),
@@ -726,6 +738,91 @@ def global_average_pooling(x, n_outputs=-1, outputs=None):
         C.call("nb200_global_average_pooling_f32", C.ptr(x), C.ptr(y), ctypes.c_int64(N * Cn), ctypes.c_int64(S),
                C.stream_ptr(x.device))
     return y
+
+
+def _grad_out(like, accum, dx):
+    if dx is None:
+        if accum:
+            raise RuntimeError("accum needs the gradient buffer to add to")
+        return torch.empty_like(like)
+    return _check_input(dx, "dx")
+
+
+def batch_normalization_backward(x, dy, gamma, mean, variance, axes=[1], eps=1e-05, batch_stat=True, dmean=None,
+                                 dvar=None, propagate_down=(True, True, True), accum=(False, False, False),
+                                 grads=(None, None, None)):
+    """BatchNormalization::backward_impl (batch_normalization.cpp:262-486). mean / variance: the batch
+    statistics the forward pass returned (batch_stat) or the running ones. Returns (dx, dbeta, dgamma),
+    None where propagate_down is False."""
+    x, dy = _check_input(x), _check_input(dy, "dy")
+    axes = list(axes)
+    if len(axes) != 1:
+        raise C.NB200Error(4, "one normalised axis is supported (got axes=%s)" % (axes,))
+    ax = axes[0] + x.dim() if axes[0] < 0 else axes[0]
+    Cn = int(x.shape[ax])
+    outer = 1
+    for s_ in x.shape[:ax]:
+        outer *= int(s_)
+    inner = x.numel() // max(outer * Cn, 1)
+    dx = _grad_out(x, accum[0], grads[0]) if propagate_down[0] else None
+    like = torch.empty(Cn, dtype=torch.float32, device=x.device)
+    db = _grad_out(like, accum[1], grads[1]) if propagate_down[1] else None
+    dg = _grad_out(like, accum[2], grads[2]) if propagate_down[2] else None
+    with C.on_device(x.device):
+        C.call("nb200_batch_normalization_backward_f32", C.ptr(x), C.ptr(dy), C.ptr(gamma), C.ptr(mean),
+               C.ptr(variance), C.ptr(dmean), C.ptr(dvar), C.ptr(dx), C.ptr(db), C.ptr(dg), ctypes.c_int64(outer),
+               ctypes.c_int64(Cn), ctypes.c_int64(inner), C.c_float(eps), int(bool(batch_stat)), int(bool(accum[0])),
+               int(bool(accum[1])), int(bool(accum[2])), C.stream_ptr(x.device))
+    return dx, db, dg
+
+
+def relu_backward(y, dy, accum=False, dx=None):
+    """ReLU::backward_impl (relu.cpp:41-66); y is the forward output."""
+    y, dy = _check_input(y), _check_input(dy, "dy")
+    dx = _grad_out(y, accum, dx)
+    with C.on_device(y.device):
+        C.call("nb200_relu_backward_f32", C.ptr(y), C.ptr(dy), C.ptr(dx), C.size_t(y.numel()), int(bool(accum)),
+               C.stream_ptr(y.device))
+    return dx
+
+
+def add2_backward(dy, accum=False, dx=None):
+    """Add2::backward_impl for one input of equal shape: dx (+)= dy."""
+    dy = _check_input(dy, "dy")
+    dx = _grad_out(dy, accum, dx)
+    with C.on_device(dy.device):
+        C.call("nb200_add2_backward_f32", C.ptr(dy), C.ptr(dx), C.size_t(dy.numel()), int(bool(accum)),
+               C.stream_ptr(dy.device))
+    return dx
+
+
+def global_average_pooling_backward(x_shape, dy, accum=False, dx=None):
+    """GlobalAveragePooling::backward_impl (global_average_pooling.cpp:75-117)."""
+    dy = _check_input(dy, "dy")
+    N, Cn = int(x_shape[0]), int(x_shape[1])
+    S = 1
+    for s_ in x_shape[2:]:
+        S *= int(s_)
+    dx = _grad_out(torch.empty(tuple(x_shape), dtype=torch.float32, device=dy.device), accum, dx)
+    with C.on_device(dy.device):
+        C.call("nb200_global_average_pooling_backward_f32", C.ptr(dy), C.ptr(dx), ctypes.c_int64(N * Cn),
+               ctypes.c_int64(S), int(bool(accum)), C.stream_ptr(dy.device))
+    return dx
+
+
+def max_pooling_backward(x, dy, kernel, stride=None, ignore_border=True, pad=None, accum=False, dx=None):
+    """MaxPooling::backward_impl (max_pooling.cpp:194-228); x is the forward input."""
+    x, dy = _check_input(x), _check_input(dy, "dy")
+    stride = tuple(kernel) if stride is None else tuple(stride)
+    pad = (0, 0) if pad is None else tuple(pad)
+    H, W = int(x.shape[-2]), int(x.shape[-1])
+    maps = x.numel() // max(H * W, 1)
+    dx = _grad_out(x, accum, dx)
+    with C.on_device(x.device):
+        C.call("nb200_max_pooling_backward_f32", C.ptr(x), C.ptr(dy), C.ptr(dx), ctypes.c_int64(maps), H, W,
+               int(kernel[0]), int(kernel[1]), int(stride[0]), int(stride[1]), int(pad[0]), int(pad[1]),
+               int(bool(ignore_border)), int(bool(accum)), C.stream_ptr(x.device))
+    return dx
 
 
 def bn_add_relu_fixed_point(a, bn_a, b=None, bn_b=None, eps=1e-05, relu=True, quantize=True, sign=True, n=8,

@@ -251,6 +251,82 @@ def global_average_pooling(x):
     return y
 
 
+def batch_norm_batch(x, beta, gamma, rmean, rvar, eps=1e-5, decay_rate=0.9, update=True):
+    """Batch-statistics BatchNormalization. Returns (y, batch mean, batch var, running mean after, running var after)."""
+    x = _f(x)
+    N, C = x.shape[:2]
+    S = x.size // (N * C)
+    y = np.empty_like(x)
+    m, v = np.empty(C, np.float32), np.empty(C, np.float32)
+    rm, rv = _f(rmean).reshape(-1).copy(), _f(rvar).reshape(-1).copy()
+    lib().oracle_batch_norm_batch(_p(x), _p(_f(beta).reshape(-1)) if beta is not None else None,
+                                  _p(_f(gamma).reshape(-1)) if gamma is not None else None, _p(rm), _p(rv),
+                                  ctypes.c_int64(N), ctypes.c_int64(C), ctypes.c_int64(S), ctypes.c_float(eps),
+                                  ctypes.c_float(decay_rate), int(update), _p(y), _p(m), _p(v))
+    return y, m, v, rm, rv
+
+
+def _grad_buffer(like, accum, init):
+    g = np.zeros(like, np.float32) if init is None else _f(init).reshape(like).copy()
+    return g
+
+
+def batch_norm_backward(x, dy, gamma, mean, var, eps=1e-5, batch_stat=True, dmean=None, dvar=None,
+                        propagate_down=(True, True, True), accum=(False, False, False), grads=(None, None, None)):
+    """Returns (dx, dbeta, dgamma); mean / var are the batch statistics (batch_stat) or the running ones."""
+    x, dy = _f(x), _f(dy)
+    N, C = x.shape[:2]
+    S = x.size // (N * C)
+    dx = _grad_buffer(x.shape, accum[0], grads[0])
+    db = _grad_buffer((C,), accum[1], grads[1])
+    dg = _grad_buffer((C,), accum[2], grads[2])
+    g = _p(_f(gamma).reshape(-1)) if gamma is not None else None
+    common = (ctypes.c_int64(N), ctypes.c_int64(C), ctypes.c_int64(S), ctypes.c_float(eps),
+              _p(dx) if propagate_down[0] else None, int(accum[0]), _p(db) if propagate_down[1] else None,
+              int(accum[1]), _p(dg) if propagate_down[2] else None, int(accum[2]))
+    m, v = _f(mean).reshape(-1), _f(var).reshape(-1)
+    if batch_stat:
+        lib().oracle_batch_norm_batch_backward(_p(x), _p(dy), g, _p(m), _p(v),
+                                               _p(_f(dmean).reshape(-1)) if dmean is not None else None,
+                                               _p(_f(dvar).reshape(-1)) if dvar is not None else None, *common)
+    else:
+        lib().oracle_batch_norm_global_backward(_p(x), _p(dy), g, _p(m), _p(v), *common)
+    return dx, db, dg
+
+
+def relu_backward(y, dy, accum=False, dx=None):
+    y, dy = _f(y), _f(dy)
+    g = _grad_buffer(y.shape, accum, dx)
+    lib().oracle_relu_backward(_p(y), _p(dy), _p(g), ctypes.c_int64(y.size), int(accum))
+    return g
+
+
+def add2_backward(dy, accum=False, dx=None):
+    dy = _f(dy)
+    g = _grad_buffer(dy.shape, accum, dx)
+    lib().oracle_add2_backward(_p(dy), _p(g), ctypes.c_int64(dy.size), int(accum))
+    return g
+
+
+def global_average_pooling_backward(xshape, dy, accum=False, dx=None):
+    dy = _f(dy)
+    N, C = xshape[:2]
+    S = int(np.prod(xshape[2:]))
+    g = _grad_buffer(tuple(xshape), accum, dx)
+    lib().oracle_global_average_pooling_backward(_p(dy), _p(g), ctypes.c_int64(N * C), ctypes.c_int64(S), int(accum))
+    return g
+
+
+def max_pooling_backward(x, dy, kernel, stride, ignore_border=True, pad=(0, 0), accum=False, dx=None):
+    x, dy = _f(x), _f(dy)
+    H, W = x.shape[-2:]
+    maps = x.size // (H * W)
+    g = _grad_buffer(x.shape, accum, dx)
+    lib().oracle_max_pooling_backward(_p(x), _p(dy), _p(g), ctypes.c_int64(maps), H, W, kernel[0], kernel[1],
+                                      stride[0], stride[1], pad[0], pad[1], int(ignore_border), int(accum))
+    return g
+
+
 # Backward passes -------------------------------------------------------------
 
 def fixed_point_quantize_backward(x, dy, sign=True, n=8, delta=2.0 ** -4, ste_fine_grained=True, accum=False,

@@ -312,6 +312,43 @@ def binary_connect_convolution_backward(x, w, b, dy, base_axis=1, pad=(0, 0), st
 
 # Sibling quantization functions -------------------------------------------------
 
+def batch_normalization_batch(x, beta, gamma, mean, var, axes=(1,), decay_rate=0.9, eps=1e-5):
+    """Batch-statistics forward. Returns (y, batch mean, batch var, running mean after, running var after)."""
+    o, ins, _ = forward("BatchNormalization", [decay_rate, eps, True, False, False], [axes],
+                        [x, beta, gamma, mean, var], n_out=3)
+    return o[0], o[1], o[2], ins[3], ins[4]
+
+
+def batch_normalization_backward(x, beta, gamma, mean, var, dy, axes=(1,), decay_rate=0.9, eps=1e-5,
+                                 batch_stat=True, dmean=None, dvar=None, propagate_down=(True, True, True),
+                                 accum=(False, False, False), grads=(None, None, None)):
+    """Returns (dx, dbeta, dgamma) after forward + BatchNormalization::backward."""
+    ogs = [dy]
+    if batch_stat:
+        ogs += [np.zeros_like(mean) if dmean is None else dmean, np.zeros_like(var) if dvar is None else dvar]
+    g, _, _ = backward("BatchNormalization", [decay_rate, eps, batch_stat, False, False], [axes],
+                       [x, beta, gamma, mean, var], ogs, list(propagate_down) + [False, False],
+                       list(accum) + [False, False], list(grads) + [None, None])
+    return g[0], g[1], g[2]
+
+
+def relu_backward(x, dy, accum=False, dx=None):
+    return backward("ReLU", [False], [], [x], [dy], [True], [accum], [dx])[0][0]
+
+
+def add2_backward(a, b, dy, accum=(False, False), grads=(None, None)):
+    g, _, _ = backward("Add2", [False], [], [a, b], [dy], [True, True], list(accum), list(grads))
+    return g[0], g[1]
+
+
+def global_average_pooling_backward(x, dy, accum=False, dx=None):
+    return backward("GlobalAveragePooling", [], [], [x], [dy], [True], [accum], [dx])[0][0]
+
+
+def max_pooling_backward(x, dy, kernel, stride, ignore_border=True, pad=(0, 0), accum=False, dx=None):
+    return backward("MaxPooling", [ignore_border, False], [kernel, stride, pad], [x], [dy], [True], [accum], [dx])[0][0]
+
+
 def binary_sigmoid(x):
     return forward("BinarySigmoid", [], [], [x])[0][0]
 
