@@ -57,11 +57,6 @@ vector<string> device_array_classes() { return SingletonManager::get<B200>()->ar
 // Makes the context's device current; returns the stream the function enqueues its work on.
 void *enter(const Context &ctx) { return b200_stream(ctx.device_id); }
 
-#define B200_NO_BACKWARD(NAME)                                                                                  \
-  virtual void backward_impl(const Variables &, const Variables &, const vector<bool> &, const vector<bool> &) { \
-    NBLA_ERROR(error_code::not_implemented, NAME " backward is not implemented in the b200 backend");            \
-  }
-
 const float *rd(Variable *v, const Context &ctx) { return v->get_data_pointer<float>(ctx); }
 // Gradient buffer of an input for backward: NULL when nothing propagates to it.
 float *grad_wr(Variable *v, const Context &ctx, bool propagate, bool accum) {
@@ -737,7 +732,26 @@ protected:
                                       this->dilation_[1], this->group_, st),
                 "Convolution");
   }
-  B200_NO_BACKWARD("Convolution")
+  // convolution.cpp:199-300: weight and bias gradients; the input gradient of a full-precision
+  // convolution (a network's first layer) is not provided by the b200 library.
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    const bool has_b = in.size() == 3;
+    if (!(pd[0] || pd[1] || (has_b && pd[2])))
+      return;
+    NBLA_CHECK(!pd[0], error_code::not_implemented,
+               "the b200 backend does not compute the input gradient of a full-precision Convolution");
+    void *st = enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
+    float *db = has_b ? grad_wr(in[2], this->ctx_, pd[2], accum[2]) : nullptr;
+    nb200_check(nb200_convolution_backward_f32(x, dy, dw, db, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw,
+                                               this->pad_[0], this->pad_[1], this->stride_[0], this->stride_[1],
+                                               this->dilation_[0], this->dilation_[1], this->group_,
+                                               pd[1] && accum[1], has_b && pd[2] && accum[2], st),
+                "Convolution backward");
+  }
 };
 
 template <typename T> class BatchNormalizationB200 : public BatchNormalization<T> {
@@ -747,11 +761,10 @@ public:
 
 protected:
   virtual void setup_impl(const Variables &in, const Variables &out) {
-    // Index and size rules of batch_normalization.cpp:31-115 for the inference case.
-    NBLA_CHECK(!this->batch_stat_, error_code::not_implemented,
-               "batch_stat=true (training statistics) is outside the b200 forward path");
+    // Index and size rules of batch_normalization.cpp:31-115.
     NBLA_CHECK(this->axes_.size() == 1, error_code::not_implemented, "Specifying axis more than one is not supported");
-    NBLA_CHECK(out.size() == 1, error_code::value,
+    NBLA_CHECK(out.size() == 1 || out.size() == 3, error_code::value, "1 or 3 outputs are expected.");
+    NBLA_CHECK(this->batch_stat_ || out.size() == 1, error_code::value,
                "If batch_stat_ is false, it cannot output batch mean and variance.");
     const int n = (int)in.size();
     this->b_idx_ = this->no_bias_ ? -1 : 1;
@@ -774,20 +787,72 @@ protected:
                  "Shape of inputs[%d] does not match the normalised axis (%d elements expected).", i,
                  (int)this->size1_);
     out[0]->reshape(sx, true);
+    const Shape_t sm = in[this->m_idx_]->shape();
+    if (out.size() == 3) {
+      out[1]->reshape(sm, true);
+      out[2]->reshape(sm, true);
+    } else {
+      this->mean_.reshape(sm, true);
+      this->var_.reshape(sm, true);
+    }
   }
-  virtual void forward_impl(const Variables &in, const Variables &out) {
+  Variable *batch_mean(const Variables &out) { return out.size() == 3 ? out[1] : &this->mean_; }
+  Variable *batch_var(const Variables &out) { return out.size() == 3 ? out[2] : &this->var_; }
+  void run_forward(const Variables &in, const Variables &out, bool update_running) {
     void *st = enter(this->ctx_);
     const float *x = rd(in[0], this->ctx_);
     const float *beta = this->no_bias_ ? nullptr : rd(in[this->b_idx_], this->ctx_);
     const float *gamma = this->no_scale_ ? nullptr : rd(in[this->g_idx_], this->ctx_);
-    const float *mean = rd(in[this->m_idx_], this->ctx_), *var = rd(in[this->v_idx_], this->ctx_);
     float *y = wr(out[0], this->ctx_);
-    nb200_check(nb200_batch_normalization_inference_f32(x, beta, gamma, mean, var, y, this->size0_, this->size1_,
-                                                        this->size2_, this->eps_, st),
+    if (!this->batch_stat_) {
+      const float *mean = rd(in[this->m_idx_], this->ctx_), *var = rd(in[this->v_idx_], this->ctx_);
+      nb200_check(nb200_batch_normalization_inference_f32(x, beta, gamma, mean, var, y, this->size0_, this->size1_,
+                                                          this->size2_, this->eps_, st),
+                  "BatchNormalization");
+      return;
+    }
+    // forward_impl_batch (batch_normalization.cpp:157-226): the running statistics are inputs written in place
+    float *m = wr(batch_mean(out), this->ctx_), *v = wr(batch_var(out), this->ctx_);
+    float *rm = update_running ? wr(in[this->m_idx_], this->ctx_, false) : nullptr;
+    float *rv = update_running ? wr(in[this->v_idx_], this->ctx_, false) : nullptr;
+    nb200_check(nb200_batch_normalization_batch_f32(x, beta, gamma, rm, rv, y, m, v, this->size0_, this->size1_,
+                                                    this->size2_, this->eps_, this->decay_rate_, update_running, st),
                 "BatchNormalization");
   }
-  virtual void recompute_impl(const Variables &in, const Variables &out) { forward_impl(in, out); }
-  B200_NO_BACKWARD("BatchNormalization")
+  virtual void forward_impl(const Variables &in, const Variables &out) { run_forward(in, out, true); }
+  virtual void recompute_impl(const Variables &in, const Variables &out) { run_forward(in, out, false); }
+  // batch_normalization.cpp:262-486 (both modes)
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    const bool pd_beta = !this->no_bias_ && pd[this->b_idx_];
+    const bool pd_gamma = !this->no_scale_ && pd[this->g_idx_];
+    if (!(pd[0] || pd_beta || pd_gamma))
+      return;
+    void *st = enter(this->ctx_);
+    const float *x = rd(in[0], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    const float *gamma = this->no_scale_ ? nullptr : rd(in[this->g_idx_], this->ctx_);
+    const float *mean, *var, *dm = nullptr, *dv = nullptr;
+    if (this->batch_stat_) {
+      mean = rd(batch_mean(out), this->ctx_);
+      var = rd(batch_var(out), this->ctx_);
+      if (out.size() == 3) {
+        dm = out[1]->get_grad_pointer<float>(this->ctx_);
+        dv = out[2]->get_grad_pointer<float>(this->ctx_);
+      }
+    } else {
+      mean = rd(in[this->m_idx_], this->ctx_);
+      var = rd(in[this->v_idx_], this->ctx_);
+    }
+    float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]);
+    float *db = pd_beta ? grad_wr(in[this->b_idx_], this->ctx_, true, accum[this->b_idx_]) : nullptr;
+    float *dg = pd_gamma ? grad_wr(in[this->g_idx_], this->ctx_, true, accum[this->g_idx_]) : nullptr;
+    nb200_check(nb200_batch_normalization_backward_f32(
+                    x, dy, gamma, mean, var, dm, dv, dx, db, dg, this->size0_, this->size1_, this->size2_, this->eps_,
+                    this->batch_stat_, pd[0] && accum[0], pd_beta && accum[this->b_idx_],
+                    pd_gamma && accum[this->g_idx_], st),
+                "BatchNormalization backward");
+  }
 };
 
 template <typename T> class ReLUB200 : public ReLU<T> {
@@ -805,7 +870,17 @@ protected:
     if (tag > 0.f)
       fxp_tag_set(out[0], tag); // max(0, k * delta) is still a multiple of delta
   }
-  B200_NO_BACKWARD("ReLU")
+  // relu.cpp:52-66
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    if (!pd[0])
+      return;
+    void *st = enter(this->ctx_);
+    const float *y = rd(out[0], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dx = grad_wr(in[0], this->ctx_, true, accum[0]);
+    nb200_check(nb200_relu_backward_f32(y, dy, dx, in[0]->size(), accum[0], st), "ReLU backward");
+  }
 };
 
 template <typename T> class Add2B200 : public Add2<T> {
@@ -825,7 +900,18 @@ protected:
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_add2_f32(a, b, y, in[0]->size(), st), "Add2");
   }
-  B200_NO_BACKWARD("Add2")
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    if (!(pd[0] || pd[1]))
+      return;
+    void *st = enter(this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    for (int i = 0; i < 2; ++i)
+      if (pd[i]) {
+        float *dx = grad_wr(in[i], this->ctx_, true, accum[i]);
+        nb200_check(nb200_add2_backward_f32(dy, dx, in[i]->size(), accum[i], st), "Add2 backward");
+      }
+  }
 };
 
 template <typename T> class MaxPoolingB200 : public MaxPooling<T> {
@@ -850,7 +936,24 @@ protected:
     if (tag > 0.f)
       fxp_tag_set(out[0], tag); // a maximum of multiples of delta is one of them
   }
-  B200_NO_BACKWARD("MaxPooling")
+  // max_pooling.cpp:194-228. No index map is kept: the backward pass finds the windows' first maxima
+  // again from the input, which therefore has to stay alive until then.
+  virtual bool grad_depends_input_data_impl(int i, int j) const { return true; }
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    if (!pd[0])
+      return;
+    void *st = enter(this->ctx_);
+    const Shape_t sx = in[0]->shape();
+    const int H = sx[sx.size() - 2], W = sx[sx.size() - 1];
+    const float *x = rd(in[0], this->ctx_);
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dx = grad_wr(in[0], this->ctx_, true, accum[0]);
+    nb200_check(nb200_max_pooling_backward_f32(x, dy, dx, in[0]->size() / (H * W), H, W, this->kernel_[0],
+                                               this->kernel_[1], this->stride_[0], this->stride_[1], this->pad_[0],
+                                               this->pad_[1], this->ignore_border_, accum[0], st),
+                "MaxPooling backward");
+  }
 };
 
 template <typename T> class GlobalAveragePoolingB200 : public GlobalAveragePooling<T> {
@@ -867,7 +970,19 @@ protected:
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_global_average_pooling_f32(x, y, maps, in[0]->size() / maps, st), "GlobalAveragePooling");
   }
-  B200_NO_BACKWARD("GlobalAveragePooling")
+  // global_average_pooling.cpp:75-117
+  virtual void backward_impl(const Variables &in, const Variables &out, const vector<bool> &pd,
+                             const vector<bool> &accum) {
+    if (!pd[0])
+      return;
+    void *st = enter(this->ctx_);
+    const Shape_t sx = in[0]->shape();
+    const Size_t maps = sx[0] * sx[1];
+    const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    float *dx = grad_wr(in[0], this->ctx_, true, accum[0]);
+    nb200_check(nb200_global_average_pooling_backward_f32(dy, dx, maps, in[0]->size() / maps, accum[0], st),
+                "GlobalAveragePooling backward");
+  }
 };
 
 } // namespace

@@ -119,6 +119,56 @@ def test_companions_and_full_precision_layers():
     assert cases.rel_rms(g[0][0], c[0][0]) < 1e-5
 
 
+def test_companions_training_side():
+    """Batch-statistics BatchNormalization and the backward passes of the companions through
+    Function::forward / Function::backward of both backends."""
+    rng = np.random.RandomState(cases.SEED + 1)
+    x = (rng.randn(4, 6, 9, 12) * 2 + 0.5).astype(np.float32)
+    x[rng.rand(*x.shape) < 0.1] = 0.0
+    beta, gamma, mean = (rng.randn(1, 6, 1, 1).astype(np.float32) for _ in range(3))
+    var = (rng.rand(1, 6, 1, 1) + 0.5).astype(np.float32)
+    bn_in = [x, beta, gamma, mean, var]
+    # forward with batch statistics: y, batch mean, batch variance; the running statistics are written in place
+    c, g = both("BatchNormalization", [0.9, 1e-5, True, False, False], [(1,)], bn_in, n_out=3)
+    for k in range(3):
+        assert np.allclose(g[0][k], c[0][k], rtol=1e-4, atol=1e-5), k
+    for k in (3, 4):
+        assert np.allclose(g[1][k], c[1][k], rtol=1e-4, atol=1e-5), k
+    dy, dx0 = cases.grad_inputs(x)
+    small = lambda: rng.randn(1, 6, 1, 1).astype(np.float32)
+    for batch_stat in (True, False):
+        for accum in (False, True):
+            ogs = [dy] + ([small(), small()] if batch_stat else [])
+            g0 = [dx0, small(), small(), small(), small()]
+            args = ("BatchNormalization", [0.9, 1e-5, batch_stat, False, False], [(1,)], bn_in, ogs,
+                    [True, True, True, False, False], [accum] * 3 + [False, False], g0)
+            cb, gb = H.backward(CPU, *args), H.backward(B200, *args)
+            for k in range(3):
+                tol = 2e-5 * (np.abs(cb[0][k]).max() + 1.0) * (1 if k == 0 else 30)
+                assert np.abs(gb[0][k] - cb[0][k]).max() <= tol, (batch_stat, accum, k)
+    for op, sc, iv, ins, exact in [("ReLU", [False], [], [x], True), ("Add2", [False], [], [x, x[::-1].copy()], True),
+                                   ("MaxPooling", [True, False], [(3, 3), (2, 2), (1, 1)], [x], True),
+                                   ("GlobalAveragePooling", [], [], [x], True)]:
+        yshape = H.forward(CPU, op, sc, iv, ins)[0][0].shape
+        gy = rng.randn(*yshape).astype(np.float32)
+        for accum in (False, True):
+            g0 = [rng.randn(*a.shape).astype(np.float32) for a in ins]
+            args = (op, sc, iv, ins, [gy], [True] * len(ins), [accum] * len(ins), g0)
+            cb, gb = H.backward(CPU, *args), H.backward(B200, *args)
+            for k in range(len(ins)):
+                assert np.array_equal(bits(gb[0][k]), bits(cb[0][k])), (op, accum, k)
+    # full-precision convolution: weight and bias gradients (the input gradient is not provided)
+    xs = rng.randn(2, 3, 20, 20).astype(np.float32)
+    ws = rng.randn(8, 3, 7, 7).astype(np.float32)
+    bs = rng.randn(8).astype(np.float32)
+    gy = rng.randn(2, 8, 10, 10).astype(np.float32)
+    g0 = [np.zeros_like(xs), rng.randn(*ws.shape).astype(np.float32), rng.randn(8).astype(np.float32)]
+    args = ("Convolution", [1, 1, False], [(3, 3), (2, 2), (1, 1)], [xs, ws, bs], [gy], [False, True, True],
+            [False, True, True], g0)
+    cb, gb = H.backward(CPU, *args), H.backward(B200, *args)
+    assert cases.rel_rms(gb[0][1], cb[0][1]) < 1e-5 and cases.rel_rms(gb[0][2], cb[0][2]) < 1e-5
+
+
 def test_errors_surface_as_exceptions():
     x = np.zeros((4, 8), np.float32)
     with pytest.raises(RuntimeError, match="positive"):
@@ -126,8 +176,8 @@ def test_errors_surface_as_exceptions():
     w = np.zeros((9, 3), np.float32)
     with pytest.raises(RuntimeError, match="mismatch"):
         H.forward(B200, "BinaryWeightAffine", [1, 1.0], [], [x, w, w.copy(), np.zeros(3, np.float32)])
-    with pytest.raises(RuntimeError, match="not implemented|not_implemented|outside"):
-        H.forward(B200, "BatchNormalization", [0.9, 1e-5, True, False, False], [(1,)],
+    with pytest.raises(RuntimeError, match="not implemented|not_implemented|not supported"):
+        H.forward(B200, "BatchNormalization", [0.9, 1e-5, True, False, False], [(1, 2)],
                   [x.reshape(4, 8, 1, 1)] + [np.zeros((1, 8, 1, 1), np.float32)] * 4)
 
 
