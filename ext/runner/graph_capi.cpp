@@ -171,6 +171,42 @@ int nbg_forward(void *h, int id, int clear_buffer, int repeat, double *seconds) 
   });
 }
 
+// CgVariable::backward from variable `id` with the initial gradient `grad` (host data of the variable's
+// shape; NULL: the gradient array the variable already holds) and waits for the device. Gradients of
+// leaf variables created with need_grad accumulate, as nnabla's do: zero them first (nbg_zero_grad).
+int nbg_backward(void *h, int id, const float *grad, int clear_buffer, double *seconds) {
+  Graph *g = static_cast<Graph *>(h);
+  return guarded([&] {
+    CgVariablePtr v = var_of(g, id);
+    NdArrayPtr g0;
+    if (grad) {
+      g0 = NdArray::create(v->variable()->shape());
+      float *p = g0->cast(dtypes::FLOAT, g->cpu, true)->pointer<float>();
+      std::memcpy(p, grad, sizeof(float) * v->variable()->size());
+    }
+    g->device_sync();
+    const auto t0 = std::chrono::steady_clock::now();
+    v->backward(g0, clear_buffer != 0);
+    g->device_sync();
+    if (seconds)
+      *seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+  });
+}
+
+int nbg_zero_grad(void *h, int id) {
+  Graph *g = static_cast<Graph *>(h);
+  return guarded([&] { var_of(g, id)->variable()->grad()->zero(); });
+}
+
+int nbg_get_grad(void *h, int id, float *data) {
+  Graph *g = static_cast<Graph *>(h);
+  return guarded([&] {
+    VariablePtr v = var_of(g, id)->variable();
+    const float *p = v->get_grad_pointer<float>(g->cpu);
+    std::memcpy(data, p, sizeof(float) * v->size());
+  });
+}
+
 // Per-function times of one forward pass, the way nnabla's GraphProfiler takes
 // them (python/src/nnabla/utils/profiler.py): the device is synchronised
 // before and after every function. Up to `capacity` entries of `names`

@@ -72,8 +72,11 @@ class Var:
 
 
 class Graph:
-    def __init__(self, backend="b200:float", device_id="0"):
+    def __init__(self, backend="b200:float", device_id="0", need_grad=False):
+        """need_grad: parameter leaves (arrays passed to the function methods) are created with
+        need_grad, so that backward() reaches them."""
         self.backend = backend
+        self.need_grad = need_grad
         self._h = ctypes.c_void_p(lib().nbg_create(backend.encode(), str(device_id).encode()))
         if not self._h:
             raise RuntimeError(lib().nbg_last_error().decode())
@@ -90,13 +93,13 @@ class Graph:
             raise RuntimeError(lib().nbg_last_error().decode())
 
     # ---- variables -------------------------------------------------------------------
-    def variable(self, data=None, shape=None):
+    def variable(self, data=None, shape=None, need_grad=False):
         """A leaf variable; `data` (numpy / torch) is copied into it."""
         if data is not None:
             data = _host(data)
             shape = data.shape
         sh = (ctypes.c_int64 * len(shape))(*[int(s) for s in shape])
-        vid = lib().nbg_variable(self._h, len(shape), sh, 0)
+        vid = lib().nbg_variable(self._h, len(shape), sh, int(need_grad))
         if vid < 0:
             raise RuntimeError(lib().nbg_last_error().decode())
         v = Var(self, vid)
@@ -112,8 +115,13 @@ class Graph:
         if key not in self._leaves:
             self._keep.append(a)
             h = _host(a)
-            self._leaves[key] = self.variable(h.reshape(shape) if shape else h)
+            self._leaves[key] = self.variable(h.reshape(shape) if shape else h, need_grad=self.need_grad)
         return self._leaves[key]
+
+    def parameter_leaves(self):
+        """[(the array passed in, its leaf variable)] in creation order."""
+        by_id = {id(a): a for a in self._keep}
+        return [(by_id[k[0]], v) for k, v in self._leaves.items()]
 
     def set_data(self, v, data):
         data = _host(data)
@@ -139,6 +147,23 @@ class Graph:
         sec = ctypes.c_double(0.0)
         self._check(lib().nbg_forward(self._h, v.id, int(clear_buffer), int(repeat), ctypes.byref(sec)))
         return sec.value
+
+    def backward(self, v, grad=None, clear_buffer=True):
+        """CgVariable::backward from `v` with initial gradient `grad` (host array of v's shape); returns
+        seconds. Leaf gradients accumulate: zero_grad() them first."""
+        sec = ctypes.c_double(0.0)
+        g = None if grad is None else _host(grad)
+        self._check(lib().nbg_backward(self._h, v.id, None if g is None else g.ctypes.data_as(ctypes.c_void_p),
+                                       int(clear_buffer), ctypes.byref(sec)))
+        return sec.value
+
+    def zero_grad(self, v):
+        self._check(lib().nbg_zero_grad(self._h, v.id))
+
+    def grad(self, v):
+        out = np.empty(self.shape(v), np.float32)
+        self._check(lib().nbg_get_grad(self._h, v.id, out.ctypes.data_as(ctypes.c_void_p)))
+        return out
 
     def profile(self, v, clear_buffer=True, capacity=512):
         """[(function name, ms)] of one forward pass, the device synchronised around every function."""

@@ -59,7 +59,7 @@ class Runner:
     """Applies the network with a given function namespace and array factory."""
 
     def __init__(self, ops, params, zeros_like, trace=None, fixed_point_hint=True, fused=False,
-                 prepared_weights=False):
+                 prepared_weights=False, batch_stat=False):
         """fused=True applies BN (+ residual) + ReLU + FixedPointQuantize as one
         function (ops.bn_add_relu_fixed_point), which is bit-identical to the
         separate functions and reads / writes each activation once.
@@ -69,6 +69,8 @@ class Runner:
         same logits, bit for bit."""
         # prepared_weights (with fused="codes"): binarise every weight once, at its first use,
         # instead of in every forward pass; for inference with weights that do not change
+        # batch_stat=True: BatchNormalization uses (and updates) batch statistics, the training graph
+        self.batch_stat = batch_stat
         self.prepared_weights = prepared_weights
         self.prepared = {}
         self.fused = fused
@@ -87,7 +89,7 @@ class Runner:
     def bn(self, name, x):
         p = self.p
         y = self.ops.batch_normalization(x, p[name + "/beta"], p[name + "/gamma"], p[name + "/mean"],
-                                         p[name + "/var"], [1], 0.9, 1e-5, False)
+                                         p[name + "/var"], [1], 0.9, 1e-5, self.batch_stat)
         return self._rec(name, "batch_normalization", [x], y)
 
     def relu_q(self, name, x):
