@@ -145,3 +145,44 @@ def test_max_pooling_backward(F, shape, kernel, stride, pad, ib, accum):
     x = rng.randn(*shape).astype(np.float32)
     got = F.max_pooling_backward(dev(x), dev(dy), kernel, stride, ib, pad, accum, dev(g0) if accum else None)
     assert np.array_equal(bits(host(got)), bits(oracle.max_pooling_backward(x, dy, kernel, stride, ib, pad, accum, g0)))
+
+
+def test_against_the_golden_fixtures(F):
+    """The committed outputs of the reference build (tests/golden/golden_companions.npz): exact passes
+    bit for bit, the passes with per-channel sums within fp32 summation error."""
+    import os
+    import companion_cases as cc
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_companions.npz"))
+    for i in range(len(cc.POOL_CASES)):
+        c = cc.pool_case(i)
+        for accum in (False, True):
+            got = F.max_pooling_backward(dev(c["x"]), dev(g["pool%d/dy" % i]), c["kernel"], c["stride"], c["ib"],
+                                         c["pad"], accum, dev(c["g0"]) if accum else None)
+            assert np.array_equal(bits(host(got)), bits(g["pool%d/dx_%d" % (i, int(accum))]))
+    e = cc.elementwise_case()
+    for accum in (False, True):
+        init = lambda: dev(e["g0"]) if accum else None
+        y = F.relu(dev(e["x"]))
+        assert np.array_equal(bits(host(F.relu_backward(y, dev(e["dy"]), accum, init()))), bits(g["relu/dx_%d" % accum]))
+        assert np.array_equal(bits(host(F.add2_backward(dev(e["dy"]), accum, init()))), bits(g["add2/dx_%d" % accum]))
+        assert np.array_equal(bits(host(F.global_average_pooling_backward(e["x"].shape, dev(e["dyp"]), accum, init()))),
+                              bits(g["gap/dx_%d" % accum]))
+    for i in range(len(cc.BN_SHAPES)):
+        c = cc.bn_case(i)
+        rm, rv = dev(c["mean"]), dev(c["var"])
+        y, m, v = F.batch_normalization(dev(c["x"]), dev(c["beta"]), dev(c["gamma"]), rm, rv, [1], 0.9, 1e-5, True, True)
+        for t, k, tol in ((y, "y", 1e-4), (m, "m", 1e-5), (v, "v", 1e-4), (rm, "rm", 1e-5), (rv, "rv", 1e-4)):
+            assert np.allclose(host(t).reshape(-1), g["bn%d/fwd_%s" % (i, k)].reshape(-1), rtol=tol, atol=tol), (i, k)
+        n = c["x"].size // c["x"].shape[1]
+        for batch_stat in (True, False):
+            mm, vv = (g["bn%d/fwd_m" % i], g["bn%d/fwd_v" % i]) if batch_stat else (c["mean"], c["var"])
+            for accum in (False, True):
+                got = F.batch_normalization_backward(
+                    dev(c["x"]), dev(c["dy"]), dev(c["gamma"]), dev(mm), dev(vv), [1], 1e-5, batch_stat,
+                    dev(c["dmean"]) if batch_stat else None, dev(c["dvar"]) if batch_stat else None,
+                    accum=(accum,) * 3, grads=[dev(a) for a in c["g0"]])
+                k = "bn%d/bwd_%d%d" % (i, int(batch_stat), int(accum))
+                want = g[k + "_dx"]
+                assert np.abs(host(got[0]) - want).max() <= 2e-5 * (np.abs(want).max() + 1e-6)
+                assert np.allclose(host(got[1]).reshape(-1), g[k + "_dbeta"].reshape(-1), rtol=2e-5, atol=2e-5 * np.sqrt(n))
+                assert np.allclose(host(got[2]).reshape(-1), g[k + "_dgamma"].reshape(-1), rtol=2e-5, atol=2e-5 * np.sqrt(n))

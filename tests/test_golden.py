@@ -117,3 +117,46 @@ def test_sibling_quantize_linear(i):
 @pytest.mark.parametrize("accum", [False, True])
 def test_sibling_linear_rest(i, accum):
     sibling_cases.check_linear_rest(oracle, i, accum)
+
+
+# ---- training side of the companions against golden_companions.npz ----------
+
+def _gc():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_companions.npz"))
+
+
+@pytest.mark.parametrize("i", range(3))
+def test_companions_batch_normalization_training(i):
+    import companion_cases as cc
+    g, c = _gc(), cc.bn_case(i)
+    got = oracle.batch_norm_batch(c["x"], c["beta"], c["gamma"], c["mean"], c["var"])
+    for k, a in zip(("y", "m", "v", "rm", "rv"), got):
+        assert np.array_equal(bits(a).reshape(-1), bits(g["bn%d/fwd_%s" % (i, k)]).reshape(-1)), k
+    for batch_stat in (True, False):
+        m, v = (got[1], got[2]) if batch_stat else (c["mean"], c["var"])
+        for accum in (False, True):
+            r = oracle.batch_norm_backward(c["x"], c["dy"], c["gamma"], m, v, 1e-5, batch_stat,
+                                           c["dmean"] if batch_stat else None, c["dvar"] if batch_stat else None,
+                                           accum=(accum,) * 3, grads=c["g0"])
+            k = "bn%d/bwd_%d%d" % (i, int(batch_stat), int(accum))
+            for a, nm in zip(r, ("dx", "dbeta", "dgamma")):
+                assert np.array_equal(bits(a).reshape(-1), bits(g[k + "_" + nm]).reshape(-1)), (k, nm)
+
+
+def test_companions_backward_elementwise_and_pooling():
+    import companion_cases as cc
+    g = _gc()
+    for i in range(len(cc.POOL_CASES)):
+        c = cc.pool_case(i)
+        for accum in (False, True):
+            got = oracle.max_pooling_backward(c["x"], g["pool%d/dy" % i], c["kernel"], c["stride"], c["ib"], c["pad"],
+                                              accum, c["g0"])
+            assert np.array_equal(bits(got), bits(g["pool%d/dx_%d" % (i, int(accum))]))
+    e = cc.elementwise_case()
+    for accum in (False, True):
+        assert np.array_equal(bits(oracle.relu_backward(oracle.relu(e["x"]), e["dy"], accum, e["g0"])),
+                              bits(g["relu/dx_%d" % accum]))
+        assert np.array_equal(bits(oracle.add2_backward(e["dy"], accum, e["g0"])), bits(g["add2/dx_%d" % accum]))
+        assert np.array_equal(bits(oracle.global_average_pooling_backward(e["x"].shape, e["dyp"], accum, e["g0"])),
+                              bits(g["gap/dx_%d" % accum]))
