@@ -66,6 +66,32 @@ __global__ void __launch_bounds__(kThreads) bn_inference_kernel(const float *__r
   }
 }
 
+// The same for planes of at least a few hundred float4: one block per (plane, chunk of the plane), so the
+// channel's four parameters and the square root are taken once per thread and the loop is loads, four
+// rounded operations per value and stores. blockIdx.x = plane (n * C + c), blockIdx.y = chunk.
+__global__ void __launch_bounds__(kThreads) bn_inference_plane_kernel(const float *__restrict__ x, const float *beta,
+                                                                      const float *gamma, const float *mean,
+                                                                      const float *var, int C, int S4, float eps,
+                                                                      float *__restrict__ y) {
+  const unsigned plane = blockIdx.x;
+  const int c = (int)(plane % (unsigned)C);
+  const float m = __ldg(mean + c);
+  const float sd = __fsqrt_rn(__fadd_rn(__ldg(var + c), eps));
+  const float g = gamma ? __ldg(gamma + c) : 1.0f;
+  const float b = beta ? __ldg(beta + c) : 0.0f;
+  const float4 *xp = reinterpret_cast<const float4 *>(x) + (size_t)plane * S4;
+  float4 *yp = reinterpret_cast<float4 *>(y) + (size_t)plane * S4;
+  for (int i = blockIdx.y * kThreads + threadIdx.x; i < S4; i += gridDim.y * kThreads) {
+    const float4 v = __ldcs(xp + i);
+    float4 r;
+    r.x = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(v.x, m), g), sd), b);
+    r.y = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(v.y, m), g), sd), b);
+    r.z = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(v.z, m), g), sd), b);
+    r.w = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(v.w, m), g), sd), b);
+    __stcs(yp + i, r);
+  }
+}
+
 // ReLU (src/nbla/function/generic/relu.cpp): y = max(0, x); Add2 (add2.cpp): y = a + b.
 template <int kOp, bool kVec>
 __global__ void __launch_bounds__(kThreads) unary_binary_kernel(const float *__restrict__ a,
@@ -478,7 +504,13 @@ int nb200_batch_normalization_inference_f32(const float *x, const float *beta, c
     return NB200_OK;
   NB_CHECK(x && y && mean && var, NB200_EVALUE, "null data pointer");
   const bool vec = (inner % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
-  if (vec)
+  if (vec && inner >= 4 * kThreads && outer * channels < (1ll << 31)) {
+    const int S4 = (int)(inner / 4);
+    int chunks = (S4 + 2 * kThreads - 1) / (2 * kThreads); // about two float4 per thread
+    chunks = chunks > 64 ? 64 : chunks;
+    bn_inference_plane_kernel<<<dim3((unsigned)(outer * channels), (unsigned)chunks), kThreads, 0,
+                                as_stream(stream)>>>(x, beta, gamma, mean, var, (int)channels, S4, eps, y);
+  } else if (vec)
     bn_inference_kernel<true><<<grid_for(total / 4, 2), kThreads, 0, as_stream(stream)>>>(
         x, beta, gamma, mean, var, total, (int)channels, (int)inner, eps, y);
   else

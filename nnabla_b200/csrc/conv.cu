@@ -86,7 +86,7 @@ void plan_box(const ConvGeometry &g, int bn_max, int &h_box, int &n_box) {
   h_box = best;
 }
 
-template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes, bool kSkip = false,
+template <bool kInt8, int PA, int PB, int BN, int STAGES, int RB = kRowBytes, int kSkip = 0,
           bool kResidentA = false>
 int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ctot, const void *wside, int64_t wpitch,
                 int c_pad_g, int cblocks, int h_box, int n_box, const GemmEpilogue &ep, cudaStream_t st,
@@ -105,7 +105,7 @@ int launch_conv(const ConvGeometry &g, const void *act, int planes_b, int64_t ct
   NB_TRY(encode_tiled(&mb, kInt8 ? 1 : 0, 5, act, dims, strides, box, estr, RB));
   ConvProblem p;
   p.row_bytes = RB;
-  p.chunk_blocks = kInt8 ? 0 : k_chunk_blocks((kSkip ? 6 : PA * PB) * (RB / 32));
+  p.chunk_blocks = kInt8 ? 0 : k_chunk_blocks((kSkip == 1 ? 6 : PA * PB) * (RB / 32));
   p.Nimg = g.N;
   p.Ko = g.Ko;
   p.Kog = g.Kog;
@@ -180,11 +180,16 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   NB_CHECK(!int8 || ctot == codes_slots(g.C, g.group), NB200_EVALUE, "activation code layout mismatch");
   const int taps = g.kh * g.kw;
   const int64_t wpitch = (int64_t)taps * c_slots;
-  const int planes = int8 ? 1 : 3;
+  // fp32 activations against +-1 weights: two fp16 pieces of the activations scaled by a power of two
+  // (x * 2^-e = p0 + p1), two thirds of the operand rows and MMAs of the exact three-piece bf16 split;
+  // the bf16 form stays for a quantize_zero_to other than -1, 0, 1
+  const bool half_pair = !int8 && (zero_to == 1.0f || zero_to == -1.0f || zero_to == 0.0f);
+  const int planes = int8 ? 1 : (half_pair ? 2 : 3);
   const size_t act_bytes = x_codes ? 0 : (size_t)planes * g.N * g.H * g.W * ctot * es;
   const size_t side_bytes = prepared_side ? 0 : (size_t)g.Ko * wpitch * es;
+  const size_t extra_bytes = half_pair ? round_up((size_t)g.Ko * 4 + 16, 1024) : 0;
   AsyncScratch scratch(st);
-  NB_TRY(scratch.alloc(round_up(act_bytes, 1024) + round_up(side_bytes, 1024)));
+  NB_TRY(scratch.alloc(round_up(act_bytes, 1024) + round_up(side_bytes, 1024) + extra_bytes));
   const uint8_t *act = x_codes ? reinterpret_cast<const uint8_t *>(x_codes) : static_cast<uint8_t *>(scratch.p);
   uint8_t *side = prepared_side ? const_cast<uint8_t *>(reinterpret_cast<const uint8_t *>(prepared_side))
                                 : static_cast<uint8_t *>(scratch.p) + round_up(act_bytes, 1024);
@@ -196,15 +201,21 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
     if (fxp_weights)
       NB_TRY(codes_conv_weights(w, g.Ko, g.Cg, g.kh, g.kw, weight_delta, side, wpitch, c_slots, st));
     else
-      NB_TRY(binarize_rows(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, int8, st));
+      NB_TRY(binarize_rows(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, int8, st, half_pair));
   }
-  if (!x_codes)
+  float *row_scale_half = nullptr;
+  if (half_pair) {
+    uint8_t *extra = static_cast<uint8_t *>(scratch.p) + round_up(act_bytes, 1024) + round_up(side_bytes, 1024);
+    row_scale_half = reinterpret_cast<float *>(extra + 16);
+    NB_TRY(nchw_to_nhwc_half_pair(x, g.N, g.C, g.H * g.W, g.group, g.Cg, c_pad_g, (int)ctot, scratch.p,
+                                  reinterpret_cast<uint32_t *>(extra), alpha, g.Ko, row_scale_half, st));
+  } else if (!x_codes)
     NB_TRY(nchw_to_nhwc_planes(x, g.N, g.C, g.H * g.W, g.group, g.Cg, c_pad_g, (int)ctot, int8 ? 0 : 3, act_delta,
                                static_cast<uint8_t *>(scratch.p), st));
   GemmEpilogue ep{};
   ep.y = y;
   ep.scale = fxp_weights ? act_delta * weight_delta : (int8 ? act_delta : 1.0f);
-  ep.row_scale = fxp_weights ? nullptr : alpha;
+  ep.row_scale = fxp_weights ? nullptr : (half_pair ? row_scale_half : alpha);
   ep.row_bias = bias;
   // Box selection: prefer the 128-column kernel (deeper pipeline) unless the
   // 256-column box is better filled.
@@ -247,6 +258,13 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
   }
   NB_CHECK(can128, NB200_ENOTIMPL,
            "fp32-activation convolution with output rows wider than 128 pixels (Wo=%d) is not supported", g.Wo);
+  if (half_pair) {
+    if (narrow_rows)
+      return launch_conv<false, 1, 2, 128, 8, 64, 2>(g, act, 2, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep,
+                                                     st);
+    return launch_conv<false, 1, 2, 128, 4, kRowBytes, 2>(g, act, 2, ctot, side, wpitch, c_pad_g, cblocks, h128, n128,
+                                                          ep, st);
+  }
   if (narrow_rows)
     return launch_conv<false, 1, 3, 128, 6, 64>(g, act, 3, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);
   return launch_conv<false, 1, 3, 128, 3>(g, act, 3, ctot, side, wpitch, c_pad_g, cblocks, h128, n128, ep, st);

@@ -196,7 +196,10 @@ struct ConvProblem {
 // beside the ring: A is loaded once per CTA and only the B tiles stream. With
 // few channels the copy engine's request rate bounds the kernel (one request
 // per 64-byte row), and A was half of the requests.
-template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkipSmallPairs, typename Problem, int RB = kRowBytes,
+// kPairs selects the plane products: 0 = all (pa, pb); 1 = those with pa + pb <= 2 (both operands split in
+// three bf16 pieces); 2 = all, with operands in fp16 instead of bf16 (two fp16 pieces of scaled activations
+// against +-1 weights).
+template <bool kInt8, int PA, int PB, int BN, int STAGES, int kPairs, typename Problem, int RB = kRowBytes,
           bool kResidentA = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -313,7 +316,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      const uint32_t idesc = ptx::make_idesc(kInt8 ? 2u : 1u, 1u, kTileM, prob.umma_n()); // S8 and BF16 both encode as 1
+      const uint32_t idesc = ptx::make_idesc(kInt8 ? 2u : 1u, kPairs == 2 ? 0u : 1u, kTileM,
+                                             prob.umma_n()); // operand format: S8 and BF16 encode as 1, F16 as 0
       if (kResidentA && (int)blockIdx.x < num_tiles) {
         if (!ptx::mbar_wait(a_full, 0u, abort_flag)) {
           if (*abort_flag == 0)
@@ -355,9 +359,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             for (int pa = 0; pa < PA; ++pa) {
 #pragma unroll
               for (int pb = 0; pb < PB; ++pb) {
-                // With both operands split, pieces whose product is below fp32
+                // With both operands split in three, pieces whose product is below fp32
                 // resolution of the leading term (pa + pb > 2) are skipped.
-                if (kSkipSmallPairs && pa + pb > 2)
+                if (kPairs == 1 && pa + pb > 2)
                   continue;
                 const uint64_t adesc =
                     kResidentA ? ptx::smem_desc_k(ptx::smem_u32(a_resident) + (uint32_t)(kb * PA + pa) * kABytes, RB)
@@ -627,7 +631,7 @@ int run_gemm(bool int8, int planes_a, int planes_b, const void *A, int64_t pitch
 
 // Launches the contraction kernel for one problem: one persistent CTA per SM
 // (or per tile when there are fewer tiles than SMs).
-template <bool kInt8, int PA, int PB, int BN, int STAGES, bool kSkip, typename Problem, int RB = kRowBytes,
+template <bool kInt8, int PA, int PB, int BN, int STAGES, int kSkip, typename Problem, int RB = kRowBytes,
           bool kResidentA = false>
 inline int launch_contraction(const CUtensorMap &ma, const CUtensorMap &mb, const Problem &prob, int tiles,
                        const GemmEpilogue &ep, cudaStream_t st, int resident_k_blocks = 0) {

@@ -5,6 +5,7 @@
 //    for normal-range values), optionally with NCHW -> NHWC re-layout,
 //  * int8 code transposition.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "prepare.cuh"
 
@@ -149,7 +150,8 @@ __global__ void finalize_alpha_kernel(const float *__restrict__ partial, int blo
 // block is one filter tap over consecutive channels, matching the NHWC
 // activation planes.
 // ---------------------------------------------------------------------------
-template <bool kInt8>
+// kMode: 0 = bf16 signs, 1 = int8 signs, 2 = fp16 signs.
+template <int kMode>
 __global__ void __launch_bounds__(256) binarize_rows_kernel(const float *__restrict__ w, int Cg, int kh, int kw,
                                                             float zero_to, float inv, float *__restrict__ wb,
                                                             float *__restrict__ alpha, void *__restrict__ side,
@@ -165,10 +167,13 @@ __global__ void __launch_bounds__(256) binarize_rows_kernel(const float *__restr
     acc += fabsf(v);
     const int c = k / taps, t = k - c * taps;
     const int64_t dst = (int64_t)o * side_pitch + (int64_t)t * c_pad + c;
-    if (kInt8)
+    if (kMode == 1) {
       reinterpret_cast<int8_t *>(side)[dst] = (int8_t)(int)s;
-    else
+    } else if (kMode == 2) {
+      reinterpret_cast<__half *>(side)[dst] = __float2half_rn(s);
+    } else {
       reinterpret_cast<__nv_bfloat16 *>(side)[dst] = __float2bfloat16_rn(s);
+    }
   }
   if (alpha == nullptr)
     return;
@@ -462,12 +467,14 @@ int binarize_columns(const float *w, int R, int C, float zero_to, float *wb, flo
 }
 
 int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to, float *wb, float *alpha, void *side,
-                  int64_t side_pitch, int c_pad, bool int8, cudaStream_t st) {
+                  int64_t side_pitch, int c_pad, bool int8, cudaStream_t st, bool half) {
   const float inv = (float)1 / (Cg * kh * kw); // binary_weight_convolution.cpp:66
   if (int8)
-    binarize_rows_kernel<true><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
+    binarize_rows_kernel<1><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
+  else if (half)
+    binarize_rows_kernel<2><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
   else
-    binarize_rows_kernel<false><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
+    binarize_rows_kernel<0><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }
@@ -489,6 +496,96 @@ int split_rows_bf16(const float *x, int64_t rows, int K, int64_t Kp, int planes,
   gy = gy > 65535 ? 65535 : gy;
   split_rows_kernel<<<dim3((unsigned)(Kp / 64), (unsigned)gy), dim3(64, 4), 0, st>>>(
       x, rows, K, Kp, planes, col_scale, reinterpret_cast<__nv_bfloat16 *>(out));
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Two fp16 pieces of an fp32 tensor: with s = 2^-e chosen from the tensor's largest magnitude so that
+// max |x| * s lies in [2^14, 2^15), x * s = p0 + p1 with p0 = fp16(x * s), p1 = fp16(x * s - p0): 22
+// significant bits for every element within 2^-18 of the maximum, an absolute error of at most 2^-40
+// of the maximum below that (p1 is then subnormal), which no fp32 sum over a filter window resolves.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int half_pair_exponent(uint32_t maxbits) {
+  const int E = (int)(maxbits >> 23);
+  if (E == 0 || E >= 255)
+    return 0; // zero, denormal or non-finite maximum: no scaling
+  const int e = E - 127 - 14;
+  return e < -100 ? -100 : e;
+}
+
+__global__ void __launch_bounds__(256) absmax_bits_kernel(const float *__restrict__ x, size_t n,
+                                                          uint32_t *__restrict__ maxbits) {
+  uint32_t m = 0;
+  const size_t stride = (size_t)gridDim.x * 256;
+  const size_t n4 = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) ? n / 4 : 0;
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += stride) {
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
+    m = max(max(m, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)), __float_as_uint(fabsf(v.z))));
+    m = max(m, __float_as_uint(fabsf(v.w)));
+  }
+  for (size_t i = n4 * 4 + (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride)
+    m = max(m, __float_as_uint(fabsf(__ldg(x + i))));
+  m = __reduce_max_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0 && m != 0)
+    atomicMax(maxbits, m);
+}
+
+// out[i] = (in ? in[i] : 1) * 2^e: the per-row factor that undoes the activation scaling
+__global__ void half_pair_row_scale_kernel(const float *__restrict__ in, int n, const uint32_t *__restrict__ maxbits,
+                                           float *__restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const float up = __int_as_float((127 + half_pair_exponent(*maxbits)) << 23);
+    out[i] = in ? __fmul_rn(in[i], up) : up;
+  }
+}
+
+// nchw_to_nhwc_kernel for the two fp16 pieces; plane 1 lies plane_stride elements behind plane 0.
+__global__ void __launch_bounds__(256) nchw_to_nhwc_half_pair_kernel(const float *__restrict__ x, int C, int HW,
+                                                                     int groups, int Cg, int c_pad_g, int ctot,
+                                                                     const uint32_t *__restrict__ maxbits,
+                                                                     __half *__restrict__ out, int64_t plane_stride) {
+  __shared__ float tile[32][33];
+  const float down = __int_as_float((127 - half_pair_exponent(*maxbits)) << 23);
+  const int n = blockIdx.z;
+  const int p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int dd = ty; dd < 32; dd += 8) {
+    const int d = d0 + dd, p = p0 + tx;
+    const int g = d / c_pad_g, cc = d - g * c_pad_g;
+    const bool live = d < ctot && g < groups && cc < Cg && p < HW;
+    tile[dd][tx] = live ? x[((int64_t)n * C + (g * Cg + cc)) * HW + p] : 0.0f;
+  }
+  __syncthreads();
+  for (int pp = ty; pp < 32; pp += 8) {
+    const int p = p0 + pp, d = d0 + tx;
+    if (p < HW && d < ctot) {
+      const float v = __fmul_rn(tile[tx][pp], down);
+      const __half h0 = __float2half_rn(v);
+      const int64_t dst = ((int64_t)n * HW + p) * ctot + d;
+      out[dst] = h0;
+      out[plane_stride + dst] = __float2half_rn(__fsub_rn(v, __half2float(h0)));
+    }
+  }
+}
+
+int nchw_to_nhwc_half_pair(const float *x, int N, int C, int HW, int groups, int Cg, int c_pad_g, int ctot, void *out,
+                           uint32_t *maxbits, const float *row_scale_in, int rows, float *row_scale_out,
+                           cudaStream_t st) {
+  NB_CHECK(N <= 65535, NB200_ENOTIMPL, "batch larger than 65535");
+  NB_CUDA(cudaMemsetAsync(maxbits, 0, 4, st));
+  const size_t n = (size_t)N * C * HW;
+  size_t blocks = (n / 4 + 255) / 256;
+  const size_t cap = (size_t)sm_count() * 16;
+  blocks = blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
+  absmax_bits_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, n, maxbits);
+  NB_LAUNCH_CHECK();
+  half_pair_row_scale_kernel<<<(rows + 255) / 256, 256, 0, st>>>(row_scale_in, rows, maxbits, row_scale_out);
+  NB_LAUNCH_CHECK();
+  const dim3 grid((HW + 31) / 32, (ctot + 31) / 32, N);
+  nchw_to_nhwc_half_pair_kernel<<<grid, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot, maxbits,
+                                                      reinterpret_cast<__half *>(out), (int64_t)N * HW * ctot);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }

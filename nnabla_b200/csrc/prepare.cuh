@@ -11,8 +11,9 @@ int binarize_columns(const float *w, int R, int C, float zero_to, float *wb, flo
                      int64_t side_pitch, bool int8, float *partial_scratch, cudaStream_t st);
 // W [Ko, Cg, kh, kw] -> wb, alpha[Ko] (NULL to skip), side-band [Ko][side_pitch]
 // with K ordered (ky, kx, c) and c padded to c_pad.
+// half: the signs of the side-band are fp16 instead of bf16.
 int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to, float *wb, float *alpha, void *side,
-                  int64_t side_pitch, int c_pad, bool int8, cudaStream_t st);
+                  int64_t side_pitch, int c_pad, bool int8, cudaStream_t st, bool half = false);
 // wq [Ko, Cg, kh, kw] multiples of delta -> int8 codes in the side-band layout of binarize_rows.
 int codes_conv_weights(const float *wq, int Ko, int Cg, int kh, int kw, float delta, void *side, int64_t side_pitch,
                        int c_pad, cudaStream_t st);
@@ -36,6 +37,12 @@ int column_sums(const float *a, int64_t rows, int C, float *out, int accumulate,
 // at slot g * c_pad_g + (c - g * Cg); all other slots are zero.
 int nchw_to_nhwc_planes(const float *x, int N, int C, int HW, int groups, int Cg, int c_pad_g, int ctot, int planes,
                         float delta, void *out, cudaStream_t st);
+// fp32 NCHW -> two fp16 NHWC planes [2][N][HW][ctot] of x * 2^-e (e from the tensor's largest magnitude,
+// left in *maxbits as the bits of that magnitude): p0 + p1 = x * 2^-e. row_scale_out[r] =
+// (row_scale_in ? row_scale_in[r] : 1) * 2^e for r < rows: the factor that undoes the scaling.
+int nchw_to_nhwc_half_pair(const float *x, int N, int C, int HW, int groups, int Cg, int c_pad_g, int ctot, void *out,
+                           uint32_t *maxbits, const float *row_scale_in, int rows, float *row_scale_out,
+                           cudaStream_t st);
 // int8 [R, C] -> [C][pitch].
 int transpose_i8(const int8_t *src, int R, int C, int8_t *dst, int64_t pitch, cudaStream_t st);
 // fp32 [R, C] -> [C][R].
