@@ -77,6 +77,37 @@ def test_full_precision_convolution(F, xs, ws, pad, stride):
     assert cases.rel_rms(y, want) < 2e-6
 
 
+@pytest.mark.parametrize("xs,ws,pad,stride", [((1, 3, 20, 256), (64, 3, 7, 7), (3, 3), (2, 2)),   # 128 output columns: every MMA row
+                                              ((2, 8, 12, 128), (40, 8, 3, 3), (1, 1), (1, 1)),   # 8 channels at stride 1, 128 columns
+                                              ((2, 1, 33, 41), (7, 1, 8, 4), (4, 1), (1, 2)),     # 8 filter rows, one channel
+                                              ((5, 3, 32, 32), (64, 3, 7, 7), (3, 3), (2, 2))])
+def test_stem_convolution_edges(F, xs, ws, pad, stride):
+    """Geometries at the limits of the tensor-core stem kernel, and inputs that exercise its per-sample
+    scaling: samples of very different magnitude in one batch, a sample of zeros, tiny and large weights."""
+    rng = np.random.RandomState(sum(xs))
+    x = rng.randn(*xs).astype(np.float32)
+    w = rng.randn(*ws).astype(np.float32)
+    b = rng.randn(ws[0]).astype(np.float32)
+    scales = [1.0, 3e4, 1e-5, 0.0, 7.0][:xs[0]]
+    for n, sc in enumerate(scales):
+        x[n] *= np.float32(sc)
+    for wscale in (1.0, 1e-4, 2e3):
+        ww = (w * np.float32(wscale)).astype(np.float32)
+        y = host(F.convolution(dev(x), dev(ww), dev(b), 1, pad, stride))
+        F.check_device_status()
+        want = oracle.convolution(x, ww, None, pad, stride)
+        got = y - b.reshape(1, -1, 1, 1)
+        for n in range(xs[0]):  # every sample against its own magnitude
+            if scales[n] == 0.0:
+                assert np.array_equal(y[n], np.broadcast_to(b.reshape(-1, 1, 1), y[n].shape))
+                continue
+            rms = np.sqrt(np.mean(want[n].astype(np.float64) ** 2))
+            err = np.sqrt(np.mean((y[n].astype(np.float64) - (want[n].astype(np.float64) + b.reshape(-1, 1, 1))) ** 2))
+            # the bias addition rounds at the size of max(|conv|, |bias|)
+            assert err <= 2e-6 * rms + 1.2e-7 * (np.abs(b).max() + np.abs(want[n]).max()), (n, wscale, err, rms)
+    del got
+
+
 @pytest.mark.parametrize("shape", [(2, 3, 16, 16), (1, 4, 13, 24), (3, 2, 8, 8), (1, 1, 56, 112)])
 @pytest.mark.parametrize("ib", [True, False])
 def test_pooling_3x3_stride2_vector_path(F, shape, ib):

@@ -256,3 +256,21 @@ def test_folded_resnet18_benchmark_size(F):
           "graph (2 images) %.3g; vs the unfolded GPU graph %.3g, top-1 agreement with it %.3f"
           % (worst, err, cases.rel_rms(logits, unfolded), agree))
     assert err < 2e-2 and agree > 0.9
+
+
+def test_converter_gives_the_hand_written_folded_network(F):
+    """The recorded-graph converter (nnabla_b200/graph_converters.py) applied to the network's own code
+    emits the same calls with the same constants as the hand-written FoldedRunner: identical logits."""
+    from nnabla_b200 import graph_converters as gc
+    rng = np.random.RandomState(8)
+    params = resnet18.init_parameters(rng, num_classes=32)
+    x = rng.randn(3, 3, 64, 64).astype(np.float32)
+    gp = {k: dev(v) for k, v in params.items()}
+    rec = gc.Recorder()
+    out = resnet18.Runner(rec, gp, lambda w, shape=None: None, None, fixed_point_hint=False)(rec.input)
+    prog = gc.BatchNormalizationFolding().convert(rec, out, F)
+    assert prog.calls.count("convolution_codes_folded") == 19
+    got = prog(dev(x))
+    F.check_device_status()
+    want = resnet18.FoldedRunner(F, gp)(dev(x))
+    assert torch.equal(got, want)
