@@ -64,12 +64,40 @@ __global__ void __launch_bounds__(kThreads) gap_backward_kernel(const float *__r
 }
 
 // max_pooling.cpp:44-77, :134-139, :194-228. The reference stores the index of the first maximum of
-// every clipped window and then runs dx[index] += dy over the outputs in order. Here every INPUT pixel
-// walks the windows that contain it in the same (ascending output) order, finds each window's first
-// maximum again and adds dy when it is the pixel itself: the same additions in the same order, no atomics.
+// every clipped window and then runs dx[index] += dy over the outputs in order. Two passes here: the
+// first writes that index map (one thread per output, the reference's scan with its strict compare);
+// in the second every INPUT pixel walks the windows that contain it in ascending output order and adds
+// dy of those whose index is its own: the same additions in the same order, without atomics.
+__global__ void __launch_bounds__(kThreads)
+    max_pooling_index_kernel(const float *__restrict__ x, int *__restrict__ index, size_t outputs, int H, int W,
+                             int Ho, int Wo, int kh, int kw, int sh, int sw, int ph, int pw) {
+  const size_t stride = (size_t)gridDim.x * kThreads;
+  for (size_t o = (size_t)blockIdx.x * kThreads + threadIdx.x; o < outputs; o += stride) {
+    const int ox = (int)(o % Wo);
+    const size_t t = o / Wo;
+    const int oy = (int)(t % Ho);
+    const float *xm = x + (t / Ho) * H * W;
+    int y0 = oy * sh - ph, x0 = ox * sw - pw;
+    const int y1 = min(y0 + kh, H), x1 = min(x0 + kw, W);
+    y0 = max(y0, 0);
+    x0 = max(x0, 0);
+    int best_i = y0 * W + x0;
+    float best = __ldg(xm + best_i);
+    for (int yy = y0; yy < y1; ++yy)
+      for (int xx = x0; xx < x1; ++xx) {
+        const float v = __ldg(xm + yy * W + xx);
+        if (best < v) {
+          best = v;
+          best_i = yy * W + xx;
+        }
+      }
+    index[o] = best_i;
+  }
+}
+
 template <bool kAccum>
 __global__ void __launch_bounds__(kThreads)
-    max_pooling_backward_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
+    max_pooling_backward_kernel(const int *__restrict__ index, const float *__restrict__ dy, float *__restrict__ dx,
                                 size_t total, int H, int W, int Ho, int Wo, int kh, int kw, int sh, int sw, int ph,
                                 int pw) {
   const size_t stride = (size_t)gridDim.x * kThreads;
@@ -78,7 +106,7 @@ __global__ void __launch_bounds__(kThreads)
     const size_t t = i / W;
     const int iy = (int)(t % H);
     const size_t m = t / H;
-    const float *xm = x + m * H * W;
+    const int *im = index + m * Ho * Wo;
     const float *dym = dy + m * Ho * Wo;
     float acc = kAccum ? dx[i] : 0.0f;
     // windows oy with oy * sh - ph <= iy < oy * sh - ph + kh
@@ -90,30 +118,11 @@ __global__ void __launch_bounds__(kThreads)
     ox0 = ox0 <= 0 ? 0 : (ox0 + sw - 1) / sw;
     int ox1 = (ix + pw) / sw;
     ox1 = ox1 < Wo - 1 ? ox1 : Wo - 1;
-    const float mine = xm[iy * W + ix];
+    const int mine = iy * W + ix;
     for (int oy = oy0; oy <= oy1; ++oy)
-      for (int ox = ox0; ox <= ox1; ++ox) {
-        int y0 = oy * sh - ph, x0 = ox * sw - pw;
-        const int y1 = min(y0 + kh, H), x1 = min(x0 + kw, W);
-        y0 = max(y0, 0);
-        x0 = max(x0, 0);
-        // The first maximum under the reference's strict compare is this pixel iff every earlier tap
-        // (scan order) is strictly smaller and no later tap is larger.
-        bool win = true;
-        for (int yy = y0; yy < y1 && win; ++yy)
-          for (int xx = x0; xx < x1; ++xx) {
-            if (yy == iy && xx == ix)
-              continue;
-            const float v = xm[yy * W + xx];
-            const bool before = yy < iy || (yy == iy && xx < ix);
-            if (before ? !(v < mine) : (mine < v)) {
-              win = false;
-              break;
-            }
-          }
-        if (win)
-          acc = __fadd_rn(acc, dym[oy * Wo + ox]);
-      }
+      for (int ox = ox0; ox <= ox1; ++ox)
+        if (__ldg(im + oy * Wo + ox) == mine)
+          acc = __fadd_rn(acc, __ldg(dym + oy * Wo + ox));
     dx[i] = acc;
   }
 }
@@ -314,6 +323,43 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+// The same for planes of whole float4: one block per (plane, chunk), the channel's constants taken once.
+template <bool kBatch, bool kAccum>
+__global__ void __launch_bounds__(kThreads)
+    bn_backward_dx_plane_kernel(const float *__restrict__ x, const float *__restrict__ dy,
+                                const float *__restrict__ gamma, const float *__restrict__ mean,
+                                const float *__restrict__ var, float eps, const float *__restrict__ coef, float count,
+                                int C, int S4, float *__restrict__ dx) {
+  const unsigned plane = blockIdx.x;
+  const int c = (int)(plane % (unsigned)C);
+  const float scale = gamma ? __ldg(gamma + c) : 1.0f;
+  const float sd = __fsqrt_rn(__fadd_rn(__ldg(var + c), eps));
+  const float m = __ldg(mean + c), k0 = __ldg(coef + c * 4), k1 = __ldg(coef + c * 4 + 1), k2 = __ldg(coef + c * 4 + 2);
+  const float4 *xp = reinterpret_cast<const float4 *>(x) + (size_t)plane * S4;
+  const float4 *gp = reinterpret_cast<const float4 *>(dy) + (size_t)plane * S4;
+  float4 *op = reinterpret_cast<float4 *>(dx) + (size_t)plane * S4;
+  auto one = [&](float xv, float g, float old) {
+    float r;
+    if (kBatch) {
+      const float a = __fdiv_rn(__fmul_rn(g, scale), sd);
+      const float b = __fdiv_rn(__fmul_rn(k0, __fsub_rn(xv, m)), count);
+      r = __fadd_rn(__fadd_rn(a, b), k1);
+    } else {
+      r = __fmul_rn(g, k2);
+    }
+    return kAccum ? __fadd_rn(old, r) : r;
+  };
+  for (int i = blockIdx.y * kThreads + threadIdx.x; i < S4; i += gridDim.y * kThreads) {
+    const float4 g = __ldcs(gp + i);
+    float4 xv = make_float4(0, 0, 0, 0), o = make_float4(0, 0, 0, 0);
+    if (kBatch)
+      xv = __ldcs(xp + i);
+    if (kAccum)
+      o = op[i];
+    op[i] = make_float4(one(xv.x, g.x, o.x), one(xv.y, g.y, o.y), one(xv.z, g.z, o.z), one(xv.w, g.w, o.w));
+  }
+}
+
 int channel_blocks(int64_t outer, int64_t channels, int64_t inner, bool vec) {
   const int64_t items = outer * (vec ? inner / 4 : inner);
   int64_t p = (8ll * sm_count() + channels - 1) / channels;
@@ -402,6 +448,28 @@ int nb200_batch_normalization_backward_f32(const float *x, const float *dy, cons
   if (dx) {
     const size_t total = (size_t)outer * channels * inner;
     const unsigned grid = grid_for(total, 4);
+    const bool planes = vec && inner >= 4 * kThreads && outer * channels < (1ll << 31) &&
+                        (reinterpret_cast<uintptr_t>(dx) & 15) == 0;
+    if (planes) {
+      const int S4 = (int)(inner / 4);
+      int chunks = (S4 + 2 * kThreads - 1) / (2 * kThreads);
+      chunks = chunks > 64 ? 64 : chunks;
+      const dim3 pgrid((unsigned)(outer * channels), (unsigned)chunks);
+#define NB_BN_DXP(B, A)                                                                                                \
+  bn_backward_dx_plane_kernel<B, A><<<pgrid, kThreads, 0, st>>>(x, dy, gamma, mean, var, eps, coef,                    \
+                                                                (float)(outer * inner), (int)channels, S4, dx)
+      if (batch_stat && accum_dx)
+        NB_BN_DXP(true, true);
+      else if (batch_stat)
+        NB_BN_DXP(true, false);
+      else if (accum_dx)
+        NB_BN_DXP(false, true);
+      else
+        NB_BN_DXP(false, false);
+#undef NB_BN_DXP
+      NB_LAUNCH_CHECK();
+      return NB200_OK;
+    }
 #define NB_BN_DX(B, A)                                                                                                 \
   bn_backward_dx_kernel<B, A><<<grid, kThreads, 0, st>>>(x, dy, gamma, mean, var, eps, coef, (float)(outer * inner),   \
                                                           total, (unsigned)channels, (unsigned)inner, dx)
@@ -477,12 +545,22 @@ int nb200_max_pooling_backward_f32(const float *x, const float *dy, float *dx, i
   if (total == 0)
     return NB200_OK;
   NB_CHECK(x && dy && dx, NB200_EVALUE, "null data pointer");
+  NB_CHECK((int64_t)height * width < (1ll << 31), NB200_EVALUE, "map larger than 2^31 pixels");
+  cudaStream_t st = as_stream(stream);
+  const size_t outputs = (size_t)maps * Ho * Wo;
+  AsyncScratch scratch(st);
+  NB_TRY(scratch.alloc(outputs * sizeof(int)));
+  int *index = static_cast<int *>(scratch.p);
+  max_pooling_index_kernel<<<grid_for(outputs, 1), kThreads, 0, st>>>(x, index, outputs, height, width, Ho, Wo,
+                                                                       kernel_h, kernel_w, stride_h, stride_w, pad_h,
+                                                                       pad_w);
+  NB_LAUNCH_CHECK();
   if (accum)
-    max_pooling_backward_kernel<true><<<grid_for(total, 2), kThreads, 0, as_stream(stream)>>>(
-        x, dy, dx, total, height, width, Ho, Wo, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w);
+    max_pooling_backward_kernel<true><<<grid_for(total, 1), kThreads, 0, st>>>(
+        index, dy, dx, total, height, width, Ho, Wo, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w);
   else
-    max_pooling_backward_kernel<false><<<grid_for(total, 2), kThreads, 0, as_stream(stream)>>>(
-        x, dy, dx, total, height, width, Ho, Wo, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w);
+    max_pooling_backward_kernel<false><<<grid_for(total, 1), kThreads, 0, st>>>(
+        index, dy, dx, total, height, width, Ho, Wo, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }
