@@ -542,30 +542,36 @@ __global__ void half_pair_row_scale_kernel(const float *__restrict__ in, int n, 
 }
 
 // nchw_to_nhwc_kernel for the two fp16 pieces; plane 1 lies plane_stride elements behind plane 0.
+// Tiles of 32 pixels x 64 channel slots: loads run along the pixels, every thread stores two
+// neighbouring slots of a pixel as one 32-bit word per plane (ctot is even: slots come in sixteens).
 __global__ void __launch_bounds__(256) nchw_to_nhwc_half_pair_kernel(const float *__restrict__ x, int C, int HW,
                                                                      int groups, int Cg, int c_pad_g, int ctot,
                                                                      const uint32_t *__restrict__ maxbits,
                                                                      __half *__restrict__ out, int64_t plane_stride) {
-  __shared__ float tile[32][33];
+  __shared__ float tile[64][33];
   const float down = __int_as_float((127 - half_pair_exponent(*maxbits)) << 23);
   const int n = blockIdx.z;
-  const int p0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const int p0 = blockIdx.x * 32, d0 = blockIdx.y * 64;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  for (int dd = ty; dd < 32; dd += 8) {
+#pragma unroll
+  for (int dd = ty; dd < 64; dd += 8) {
     const int d = d0 + dd, p = p0 + tx;
     const int g = d / c_pad_g, cc = d - g * c_pad_g;
     const bool live = d < ctot && g < groups && cc < Cg && p < HW;
-    tile[dd][tx] = live ? x[((int64_t)n * C + (g * Cg + cc)) * HW + p] : 0.0f;
+    tile[dd][tx] = live ? __ldcs(x + ((int64_t)n * C + (g * Cg + cc)) * HW + p) : 0.0f;
   }
   __syncthreads();
+#pragma unroll
   for (int pp = ty; pp < 32; pp += 8) {
-    const int p = p0 + pp, d = d0 + tx;
+    const int p = p0 + pp, d = d0 + 2 * tx;
     if (p < HW && d < ctot) {
-      const float v = __fmul_rn(tile[tx][pp], down);
-      const __half h0 = __float2half_rn(v);
+      const float v0 = __fmul_rn(tile[2 * tx][pp], down), v1 = __fmul_rn(tile[2 * tx + 1][pp], down);
+      const __half a0 = __float2half_rn(v0), a1 = __float2half_rn(v1);
+      const __half b0 = __float2half_rn(__fsub_rn(v0, __half2float(a0)));
+      const __half b1 = __float2half_rn(__fsub_rn(v1, __half2float(a1)));
       const int64_t dst = ((int64_t)n * HW + p) * ctot + d;
-      out[dst] = h0;
-      out[plane_stride + dst] = __float2half_rn(__fsub_rn(v, __half2float(h0)));
+      *reinterpret_cast<__half2 *>(out + dst) = __halves2half2(a0, a1);
+      *reinterpret_cast<__half2 *>(out + plane_stride + dst) = __halves2half2(b0, b1);
     }
   }
 }
@@ -583,7 +589,8 @@ int nchw_to_nhwc_half_pair(const float *x, int N, int C, int HW, int groups, int
   NB_LAUNCH_CHECK();
   half_pair_row_scale_kernel<<<(rows + 255) / 256, 256, 0, st>>>(row_scale_in, rows, maxbits, row_scale_out);
   NB_LAUNCH_CHECK();
-  const dim3 grid((HW + 31) / 32, (ctot + 31) / 32, N);
+  NB_CHECK(ctot % 2 == 0, NB200_EVALUE, "channel slots must come in pairs");
+  const dim3 grid((HW + 31) / 32, (ctot + 63) / 64, N);
   nchw_to_nhwc_half_pair_kernel<<<grid, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot, maxbits,
                                                       reinterpret_cast<__half *>(out), (int64_t)N * HW * ctot);
   NB_LAUNCH_CHECK();
