@@ -773,6 +773,12 @@ def run_b200_arm(args):
             folded = resnet18.FoldedRunner(F, params)
             form("bn_folded_int8_epilogue", folded)
             fl = folded(x)
+            try:
+                cap_folded = graphs.Captured(folded, x)
+                form("bn_folded_cuda_graph_replay", cap_folded)
+                del cap_folded
+            except RuntimeError:
+                forms["bn_folded_cuda_graph_replay_ms"] = None
             forms["bn_folded_logits_rel_rms_vs_as_written"] = float(
                 ((fl - logits).double().pow(2).mean() / logits.double().pow(2).mean()).sqrt())
             forms["bn_folded_top1_agreement"] = float((fl.argmax(1) == logits.argmax(1)).float().mean())

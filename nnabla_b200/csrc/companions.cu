@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "narrow_conv.cuh"
+#include "pdl.cuh"
 
 namespace nb200 {
 namespace {
@@ -33,6 +34,8 @@ __global__ void __launch_bounds__(kThreads) bn_inference_kernel(const float *__r
                                                                 const float *gamma, const float *mean,
                                                                 const float *var, size_t total, int C, int S,
                                                                 float eps, float *__restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   const size_t stride = (size_t)gridDim.x * kThreads;
   if (kVec) {
     const size_t total4 = total / 4;
@@ -73,6 +76,8 @@ __global__ void __launch_bounds__(kThreads) bn_inference_plane_kernel(const floa
                                                                       const float *gamma, const float *mean,
                                                                       const float *var, int C, int S4, float eps,
                                                                       float *__restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   const unsigned plane = blockIdx.x;
   const int c = (int)(plane % (unsigned)C);
   const float m = __ldg(mean + c);
@@ -97,6 +102,8 @@ template <int kOp, bool kVec>
 __global__ void __launch_bounds__(kThreads) unary_binary_kernel(const float *__restrict__ a,
                                                                 const float *__restrict__ b, size_t total,
                                                                 float *__restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   const size_t stride = (size_t)gridDim.x * kThreads;
   if (kVec) {
     const size_t total4 = total / 4;
@@ -130,6 +137,8 @@ __global__ void __launch_bounds__(kThreads) unary_binary_kernel(const float *__r
 __global__ void __launch_bounds__(kThreads) max_pooling_kernel(const float *__restrict__ x, size_t maps, int H, int W,
                                                                int Ho, int Wo, int kh, int kw, int sh, int sw, int ph,
                                                                int pw, float *__restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   const size_t total = maps * Ho * Wo;
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += stride) {
@@ -161,6 +170,8 @@ __global__ void __launch_bounds__(kThreads) max_pooling_kernel(const float *__re
 // inner, first maximum wins) so that ties between +0 and -0 resolve alike.
 __global__ void __launch_bounds__(kThreads) max_pooling_3x3s2_kernel(const float *__restrict__ x, size_t maps, int H,
                                                                      int W, int Ho, int Wo, float *__restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   const int Wo4 = Wo / 4;
   const size_t total = maps * Ho * Wo4;
   const size_t stride = (size_t)gridDim.x * kThreads;
@@ -205,6 +216,8 @@ __global__ void __launch_bounds__(kThreads) max_pooling_3x3s2_kernel(const float
 // keeps that order.
 __global__ void __launch_bounds__(kThreads) global_average_pooling_kernel(const float *__restrict__ x, size_t maps,
                                                                           int S, float *__restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
   const size_t stride = (size_t)gridDim.x * kThreads;
   for (size_t m = (size_t)blockIdx.x * kThreads + threadIdx.x; m < maps; m += stride) {
     const float *xm = x + m * (size_t)S;
@@ -508,15 +521,15 @@ int nb200_batch_normalization_inference_f32(const float *x, const float *beta, c
     const int S4 = (int)(inner / 4);
     int chunks = (S4 + 2 * kThreads - 1) / (2 * kThreads); // about two float4 per thread
     chunks = chunks > 64 ? 64 : chunks;
-    bn_inference_plane_kernel<<<dim3((unsigned)(outer * channels), (unsigned)chunks), kThreads, 0,
-                                as_stream(stream)>>>(x, beta, gamma, mean, var, (int)channels, S4, eps, y);
+    NB_CUDA(launch_dependent(bn_inference_plane_kernel, dim3((unsigned)(outer * channels), (unsigned)chunks),
+                             dim3(kThreads), 0, as_stream(stream), x, beta, gamma, mean, var, (int)channels, S4, eps,
+                             y));
   } else if (vec)
-    bn_inference_kernel<true><<<grid_for(total / 4, 2), kThreads, 0, as_stream(stream)>>>(
-        x, beta, gamma, mean, var, total, (int)channels, (int)inner, eps, y);
+    NB_CUDA(launch_dependent(bn_inference_kernel<true>, dim3(grid_for(total / 4, 2)), dim3(kThreads), 0,
+                             as_stream(stream), x, beta, gamma, mean, var, total, (int)channels, (int)inner, eps, y));
   else
-    bn_inference_kernel<false><<<grid_for(total, 4), kThreads, 0, as_stream(stream)>>>(
-        x, beta, gamma, mean, var, total, (int)channels, (int)inner, eps, y);
-  NB_LAUNCH_CHECK();
+    NB_CUDA(launch_dependent(bn_inference_kernel<false>, dim3(grid_for(total, 4)), dim3(kThreads), 0,
+                             as_stream(stream), x, beta, gamma, mean, var, total, (int)channels, (int)inner, eps, y));
   return NB200_OK;
 }
 
@@ -525,11 +538,13 @@ int nb200_relu_f32(const float *x, float *y, size_t size, void *stream) {
     return NB200_OK;
   NB_CHECK(x && y, NB200_EVALUE, "null data pointer");
   const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  const float *none = nullptr;
   if (vec)
-    unary_binary_kernel<0, true><<<grid_for(size / 4 + 1, 2), kThreads, 0, as_stream(stream)>>>(x, nullptr, size, y);
+    NB_CUDA(launch_dependent(unary_binary_kernel<0, true>, dim3(grid_for(size / 4 + 1, 2)), dim3(kThreads), 0,
+                             as_stream(stream), x, none, size, y));
   else
-    unary_binary_kernel<0, false><<<grid_for(size, 4), kThreads, 0, as_stream(stream)>>>(x, nullptr, size, y);
-  NB_LAUNCH_CHECK();
+    NB_CUDA(launch_dependent(unary_binary_kernel<0, false>, dim3(grid_for(size, 4)), dim3(kThreads), 0,
+                             as_stream(stream), x, none, size, y));
   return NB200_OK;
 }
 
@@ -559,10 +574,11 @@ int nb200_add2_f32(const float *a, const float *b, float *y, size_t size, void *
   const bool vec =
       ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
   if (vec)
-    unary_binary_kernel<1, true><<<grid_for(size / 4 + 1, 2), kThreads, 0, as_stream(stream)>>>(a, b, size, y);
+    NB_CUDA(launch_dependent(unary_binary_kernel<1, true>, dim3(grid_for(size / 4 + 1, 2)), dim3(kThreads), 0,
+                             as_stream(stream), a, b, size, y));
   else
-    unary_binary_kernel<1, false><<<grid_for(size, 4), kThreads, 0, as_stream(stream)>>>(a, b, size, y);
-  NB_LAUNCH_CHECK();
+    NB_CUDA(launch_dependent(unary_binary_kernel<1, false>, dim3(grid_for(size, 4)), dim3(kThreads), 0,
+                             as_stream(stream), a, b, size, y));
   return NB200_OK;
 }
 
@@ -583,12 +599,12 @@ int nb200_max_pooling_f32(const float *x, float *y, int64_t maps, int height, in
                     width % 4 == 0 && Wo % 4 == 0 && 2 * Wo == width &&
                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
   if (fast)
-    max_pooling_3x3s2_kernel<<<grid_for(total / 4, 1), kThreads, 0, as_stream(stream)>>>(x, (size_t)maps, height,
-                                                                                         width, Ho, Wo, y);
+    NB_CUDA(launch_dependent(max_pooling_3x3s2_kernel, dim3(grid_for(total / 4, 1)), dim3(kThreads), 0,
+                             as_stream(stream), x, (size_t)maps, height, width, Ho, Wo, y));
   else
-    max_pooling_kernel<<<grid_for(total, 2), kThreads, 0, as_stream(stream)>>>(
-        x, (size_t)maps, height, width, Ho, Wo, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, y);
-  NB_LAUNCH_CHECK();
+    NB_CUDA(launch_dependent(max_pooling_kernel, dim3(grid_for(total, 2)), dim3(kThreads), 0, as_stream(stream), x,
+                             (size_t)maps, height, width, Ho, Wo, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w,
+                             y));
   return NB200_OK;
 }
 
@@ -597,9 +613,8 @@ int nb200_global_average_pooling_f32(const float *x, float *y, int64_t maps, int
   if (maps == 0)
     return NB200_OK;
   NB_CHECK(x && y, NB200_EVALUE, "null data pointer");
-  global_average_pooling_kernel<<<grid_for((size_t)maps), kThreads, 0, as_stream(stream)>>>(x, (size_t)maps,
-                                                                                          (int)spatial, y);
-  NB_LAUNCH_CHECK();
+  NB_CUDA(launch_dependent(global_average_pooling_kernel, dim3(grid_for((size_t)maps)), dim3(kThreads), 0,
+                           as_stream(stream), x, (size_t)maps, (int)spatial, y));
   return NB200_OK;
 }
 

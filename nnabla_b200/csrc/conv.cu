@@ -711,6 +711,23 @@ int convolution_codes_folded(const int8_t *x_codes, const int8_t *side, const fl
     NB_CC(64, 8, 128);
   if (g.Ko <= 128)
     NB_CC(128, 6, 128);
+  {
+    // Few pixels (late stages, small batches): 256-map tiles would leave most SMs idle. Narrower tiles give
+    // more blocks; an MMA of N columns costs about 55 + 0.6 N cycles, so a narrower tile pays only while it
+    // does not add a second round of tiles per SM.
+    const int64_t ptiles = ((int64_t)g.N * g.Ho * g.Wo + kTileM - 1) / kTileM;
+    const int sms = sm_count();
+    if (ptiles * ((g.Ko + 255) / 256) < sms) {
+      auto cost = [&](int bn) {
+        const int64_t blocks = ptiles * ((g.Ko + bn - 1) / bn);
+        return (double)((blocks + sms - 1) / sms) * (55.0 + 0.6 * bn);
+      };
+      if (cost(64) < cost(128) && cost(64) < cost(256))
+        NB_CC(64, 8, 128);
+      if (cost(128) < cost(256))
+        NB_CC(128, 6, 128);
+    }
+  }
   NB_CC(256, 4, 128);
 #undef NB_CC
 #undef NB_CC_RES

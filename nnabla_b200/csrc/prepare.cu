@@ -8,6 +8,7 @@
 #include <cuda_fp16.h>
 
 #include "prepare.cuh"
+#include "pdl.cuh"
 
 namespace nb200 {
 namespace {
@@ -156,6 +157,8 @@ __global__ void __launch_bounds__(256) binarize_rows_kernel(const float *__restr
                                                             float zero_to, float inv, float *__restrict__ wb,
                                                             float *__restrict__ alpha, void *__restrict__ side,
                                                             int64_t side_pitch, int c_pad) {
+  pdl_wait();
+  pdl_trigger();
   const int o = blockIdx.x;
   const int taps = kh * kw, Kd = Cg * taps;
   const float *wr = w + (int64_t)o * Kd;
@@ -352,6 +355,9 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_i8_vec_kernel(const float *_
                                                                   int groups, int Cg, int c_pad_g, int ctot,
                                                                   int8_t *__restrict__ out, float inv_delta) {
   __shared__ uint32_t tile[64][17];
+  pdl_wait();
+  pdl_trigger();
+
   int8_t *tile8 = reinterpret_cast<int8_t *>(&tile[0][0]);
   const int n = blockIdx.z;
   const int p0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
@@ -470,7 +476,8 @@ int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to,
                   int64_t side_pitch, int c_pad, bool int8, cudaStream_t st, bool half) {
   const float inv = (float)1 / (Cg * kh * kw); // binary_weight_convolution.cpp:66
   if (int8)
-    binarize_rows_kernel<1><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
+    NB_CUDA(launch_dependent(binarize_rows_kernel<1>, dim3(Ko), dim3(256), 0, st, w, Cg, kh, kw, zero_to, inv, wb, alpha,
+                             side, side_pitch, c_pad));
   else if (half)
     binarize_rows_kernel<2><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
   else
@@ -606,8 +613,8 @@ int nchw_to_nhwc_planes(const float *x, int N, int C, int HW, int groups, int Cg
     // ctot is a multiple of 16 (channel slots are padded to 16 per group), so word stores are aligned.
     const dim3 grid8((HW + 63) / 64, (ctot + 63) / 64, N);
     if (HW % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
-      nchw_to_nhwc_i8_vec_kernel<<<grid8, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
-                                                        reinterpret_cast<int8_t *>(out), 1.0f / delta);
+      NB_CUDA(launch_dependent(nchw_to_nhwc_i8_vec_kernel, grid8, dim3(256), 0, st, x, C, HW, groups, Cg, c_pad_g, ctot,
+                               reinterpret_cast<int8_t *>(out), 1.0f / delta));
     else
       nchw_to_nhwc_i8_kernel<<<grid8, 256, 0, st>>>(x, C, HW, groups, Cg, c_pad_g, ctot,
                                                     reinterpret_cast<int8_t *>(out), 1.0f / delta);

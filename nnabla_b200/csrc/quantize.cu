@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "pdl.cuh"
 
 namespace nb200 {
 namespace {
@@ -45,6 +46,8 @@ __device__ __forceinline__ void apply4(const Op &op, const typename Op::State &s
 template <typename Op>
 __global__ void __launch_bounds__(kThreads) ew_vec_kernel(const float *__restrict__ x, float *__restrict__ y,
                                                           size_t size, size_t head, size_t n4, Op op) {
+  pdl_wait();
+  pdl_trigger();
   const float4 *x4 = reinterpret_cast<const float4 *>(x + head);
   float4 *y4 = reinterpret_cast<float4 *>(y + head);
   const size_t stride = (size_t)gridDim.x * kThreads;
@@ -78,6 +81,8 @@ __global__ void __launch_bounds__(kThreads) ew_vec_kernel(const float *__restric
 template <typename Op>
 __global__ void __launch_bounds__(kThreads) ew_scalar_kernel(const float *__restrict__ x, float *__restrict__ y,
                                                              size_t size, Op op) {
+  pdl_wait();
+  pdl_trigger();
   const size_t stride = (size_t)gridDim.x * kThreads;
   const typename Op::State st = op.init();
   for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < size; i += stride) {
@@ -116,13 +121,12 @@ template <typename Op> int launch_elementwise(const float *x, float *y, size_t s
   if (head > size)
     head = size;
   if (phase_x != phase_y || !op.codes_aligned(head)) {
-    ew_scalar_kernel<Op><<<grid_for(size), kThreads, 0, st>>>(x, y, size, op);
-    NB_LAUNCH_CHECK();
+    NB_CUDA(launch_dependent(ew_scalar_kernel<Op>, dim3(grid_for(size)), dim3(kThreads), 0, st, x, y, size, op));
     return NB200_OK;
   }
   const size_t n4 = (size - head) / 4;
-  ew_vec_kernel<Op><<<grid_for((n4 + kUnroll - 1) / kUnroll), kThreads, 0, st>>>(x, y, size, head, n4, op);
-  NB_LAUNCH_CHECK();
+  NB_CUDA(launch_dependent(ew_vec_kernel<Op>, dim3(grid_for((n4 + kUnroll - 1) / kUnroll)), dim3(kThreads), 0, st, x, y,
+                           size, head, n4, op));
   return NB200_OK;
 }
 
