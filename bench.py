@@ -137,7 +137,7 @@ def _case_int8_gemm(n):
     return make
 
 
-def _case_bwconv_bf16(batch):
+def _case_bwconv_f32act(batch):
     def make():
         import torch
         from nnabla_b200 import functions as F
@@ -168,7 +168,7 @@ KERNEL_CASES = {
     "quantizers_2p26": _case_quantizers(26),
     "quantizer_backward_2p26": _case_quantizer_backward(26),
     "int8_gemm_4096": _case_int8_gemm(4096),
-    "bwconv_bf16_batch16": _case_bwconv_bf16(16),
+    "bwconv_f32_activations_batch16": _case_bwconv_f32act(16),
     "fused_codes_pass_batch128": _case_fused_codes_pass(128),
 }
 
