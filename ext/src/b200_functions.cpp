@@ -40,6 +40,7 @@
 #include <nbla/utils/axis_utils.hpp>
 
 #include <nnabla_b200.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <mutex>
 
@@ -56,6 +57,19 @@ vector<string> device_array_classes() { return SingletonManager::get<B200>()->ar
 
 // Makes the context's device current; returns the stream the function enqueues its work on.
 void *enter(const Context &ctx) { return b200_stream(ctx.device_id); }
+
+// NVTX range "<Function>::forward_impl" / "::backward_impl" around every function of the backend, so that a
+// timeline shows nnabla's functions over the kernels they launch (header-only NVTX: a few nanoseconds
+// when no tool is attached).
+struct NvtxRange {
+  NvtxRange(const string &function, const char *method) { nvtxRangePushA((function + "::" + method).c_str()); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange &) = delete;
+  NvtxRange &operator=(const NvtxRange &) = delete;
+};
+#define B200_ENTER(ST)                                                                                            \
+  NvtxRange nvtx_range_(this->name(), __func__);                                                                  \
+  void *ST = enter(this->ctx_)
 
 const float *rd(Variable *v, const Context &ctx) { return v->get_data_pointer<float>(ctx); }
 // Gradient buffer of an input for backward: NULL when nothing propagates to it.
@@ -163,7 +177,7 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_);
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_fixed_point_quantize_f32(x, y, in[0]->size(), this->sign_, this->n_, this->delta_, st),
@@ -176,7 +190,7 @@ protected:
                              const vector<bool> &accum) {
     if (!propagate_down[0])
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_);
     float *dx = in[0]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[0]);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
@@ -193,7 +207,7 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_);
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_pow2_quantize_f32(x, y, in[0]->size(), this->sign_, this->with_zero_, this->n_, this->m_,
@@ -205,7 +219,7 @@ protected:
                              const vector<bool> &accum) {
     if (!propagate_down[0])
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_);
     float *dx = in[0]->cast_grad_and_get_pointer<float>(this->ctx_, !accum[0]);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
@@ -237,7 +251,7 @@ protected:
     this->scale_sptr_ = make_shared<Variable>(q->shape());
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const Shape_t sx = in[0]->shape(), sq = in[1]->shape();
     const float *x = rd(in[0], this->ctx_);
     float *qr_min = wr(in[1], this->ctx_, false), *qr_max = wr(in[2], this->ctx_, false);
@@ -254,7 +268,7 @@ protected:
     NBLA_CHECK(!(propagate_down[3] || propagate_down[4]), error_code::value,
                "Backward to x(inputs[0]), qr_min(inputs[1]), and/or qr_max(inputs[2])"
                "are only allowed.");
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const bool ranges = !(this->x_min_max_ || this->ema_);
     const int32_t pd[3] = {propagate_down[0], ranges && propagate_down[1], ranges && propagate_down[2]};
     const int32_t ac[3] = {accum[0], accum[1], accum[2]};
@@ -283,7 +297,7 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     nb200_check(nb200_binary_sigmoid_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), st),
                 "BinarySigmoid");
   }
@@ -291,7 +305,7 @@ protected:
                              const vector<bool> &accum) {
     if (!pd[0])
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_), *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     nb200_check(nb200_binary_sigmoid_backward_f32(x, dy, grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(),
                                                   accum[0], st),
@@ -306,7 +320,7 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     nb200_check(nb200_binary_tanh_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), st),
                 "BinaryTanh");
   }
@@ -314,7 +328,7 @@ protected:
                              const vector<bool> &accum) {
     if (!pd[0])
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_), *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     nb200_check(nb200_binary_tanh_backward_f32(x, dy, grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(),
                                                accum[0], st),
@@ -329,7 +343,7 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     nb200_check(nb200_prune_f32(rd(in[0], this->ctx_), wr(out[0], this->ctx_), in[0]->size(), this->rate_, st),
                 "Prune");
   }
@@ -337,7 +351,7 @@ protected:
                              const vector<bool> &accum) {
     if (!pd[0])
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     nb200_check(nb200_prune_backward_f32(out[0]->get_grad_pointer<float>(this->ctx_),
                                          grad_wr(in[0], this->ctx_, true, accum[0]), in[0]->size(), accum[0], st),
                 "Prune backward");
@@ -365,7 +379,7 @@ public:
 protected:
   virtual void setup_impl(const Variables &in, const Variables &out) { setup_linear_shapes(in, out); }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     NBLA_CHECK(this->round_mode_ == "HALF_AWAY_FROM_ZERO" || this->round_mode_ == "HALF_TO_EVEN", error_code::value,
                "unknown round_mode %s", this->round_mode_.c_str());
     const Shape_t sx = in[0]->shape(), ss = in[1]->shape(), sz = in[2]->shape();
@@ -382,7 +396,7 @@ protected:
       return;
     NBLA_CHECK(!pd[1], error_code::not_implemented, "Backward w.r.t. the scale is not supported now.");
     NBLA_CHECK(!pd[2], error_code::not_implemented, "Backward w.r.t. the zero point is not supported now.");
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const Shape_t sx = in[0]->shape(), ss = in[1]->shape();
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_), *scale = rd(in[1], this->ctx_);
     nb200_check(nb200_quantize_linear_backward_f32(dy, sx.data(), (int)sx.size(), scale, ss.data(),
@@ -399,7 +413,7 @@ public:
 protected:
   virtual void setup_impl(const Variables &in, const Variables &out) { setup_linear_shapes(in, out); }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const Shape_t sx = in[0]->shape(), ss = in[1]->shape(), sz = in[2]->shape();
     nb200_check(nb200_dequantize_linear_f32(rd(in[0], this->ctx_), sx.data(), (int)sx.size(), rd(in[1], this->ctx_),
                                             ss.data(), rd(in[2], this->ctx_), sz.data(), wr(out[0], this->ctx_),
@@ -412,7 +426,7 @@ protected:
       return;
     NBLA_CHECK(!pd[1], error_code::not_implemented, "Backward w.r.t. the scale is not supported now.");
     NBLA_CHECK(!pd[2], error_code::not_implemented, "Backward w.r.t. the zero point is not supported now.");
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const Shape_t sx = in[0]->shape(), ss = in[1]->shape();
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_), *scale = rd(in[1], this->ctx_);
     nb200_check(nb200_dequantize_linear_backward_f32(dy, sx.data(), (int)sx.size(), scale, ss.data(),
@@ -439,7 +453,7 @@ protected:
     NBLA_CHECK(in[3]->size() == this->w_col_, error_code::value, "Size of alpha must be equal to output size.");
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     float *wb = wr(in[2], this->ctx_), *alpha = wr(in[3], this->ctx_);
     const float *b = in.size() == 5 ? rd(in[4], this->ctx_) : nullptr;
@@ -454,7 +468,7 @@ protected:
     const bool has_b = in.size() == 5;
     if (!(pd[0] || pd[1] || (has_b && pd[4])))
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_), *alpha = rd(in[3], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]), *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
@@ -478,7 +492,7 @@ protected:
     check_same_shape(in[1], in[2]);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     float *wb = wr(in[2], this->ctx_);
     const float *b = in.size() == 4 ? rd(in[3], this->ctx_) : nullptr;
@@ -493,7 +507,7 @@ protected:
     const bool has_b = in.size() == 4;
     if (!(pd[0] || pd[1] || (has_b && pd[3])))
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]);
@@ -535,7 +549,7 @@ protected:
     NBLA_CHECK(in[3]->size() == d_.Ko, error_code::value, "Size of alpha must be equal to the number of output maps.");
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float delta = fxp_tag_get(in[0]);
     const bool sign_ok = this->quantize_zero_to_ == 1.f || this->quantize_zero_to_ == -1.f ||
                          this->quantize_zero_to_ == 0.f;
@@ -594,7 +608,7 @@ protected:
     const bool has_b = in.size() == 5;
     if (!(pd[0] || pd[1] || (has_b && pd[4])))
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float delta = fxp_tag_get(in[0]);
     const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_), *alpha = rd(in[3], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
@@ -622,7 +636,7 @@ protected:
     check_same_shape(in[1], in[2]);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float delta = fxp_tag_get(in[0]);
     const bool sign_ok = this->quantize_zero_to_ == 1.f || this->quantize_zero_to_ == -1.f ||
                          this->quantize_zero_to_ == 0.f;
@@ -643,7 +657,7 @@ protected:
     const bool has_b = in.size() == 4;
     if (!(pd[0] || pd[1] || (has_b && pd[3])))
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float delta = fxp_tag_get(in[0]);
     const float *x = rd(in[0], this->ctx_), *wb = rd(in[2], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
@@ -679,7 +693,7 @@ protected:
     d_ = setup_affine_shapes(this->base_axis_, in[0], in[1], in.size() == 3 ? in[2] : nullptr, out[0]);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float dx = fxp_tag_get(in[0]), dw = fxp_tag_get(in[1]);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     const float *b = in.size() == 3 ? rd(in[2], this->ctx_) : nullptr;
@@ -698,7 +712,7 @@ protected:
     const bool has_b = in.size() == 3;
     if (!(pd[0] || pd[1] || (has_b && pd[2])))
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     float *dx = grad_wr(in[0], this->ctx_, pd[0], accum[0]), *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
@@ -723,7 +737,7 @@ protected:
                            in.size() == 3 ? in[2] : nullptr, out[0]);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_), *w = rd(in[1], this->ctx_);
     const float *b = in.size() == 3 ? rd(in[2], this->ctx_) : nullptr;
     float *y = wr(out[0], this->ctx_);
@@ -741,7 +755,7 @@ protected:
       return;
     NBLA_CHECK(!pd[0], error_code::not_implemented,
                "the b200 backend does not compute the input gradient of a full-precision Convolution");
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     float *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
@@ -799,7 +813,7 @@ protected:
   Variable *batch_mean(const Variables &out) { return out.size() == 3 ? out[1] : &this->mean_; }
   Variable *batch_var(const Variables &out) { return out.size() == 3 ? out[2] : &this->var_; }
   void run_forward(const Variables &in, const Variables &out, bool update_running) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_);
     const float *beta = this->no_bias_ ? nullptr : rd(in[this->b_idx_], this->ctx_);
     const float *gamma = this->no_scale_ ? nullptr : rd(in[this->g_idx_], this->ctx_);
@@ -828,7 +842,7 @@ protected:
     const bool pd_gamma = !this->no_scale_ && pd[this->g_idx_];
     if (!(pd[0] || pd_beta || pd_gamma))
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     const float *gamma = this->no_scale_ ? nullptr : rd(in[this->g_idx_], this->ctx_);
@@ -862,7 +876,7 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float tag = fxp_tag_get(in[0]);
     const float *x = rd(in[0], this->ctx_);
     float *y = wr(out[0], this->ctx_);
@@ -875,7 +889,7 @@ protected:
                              const vector<bool> &accum) {
     if (!pd[0])
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *y = rd(out[0], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     float *dx = grad_wr(in[0], this->ctx_, true, accum[0]);
@@ -895,7 +909,7 @@ protected:
     out[0]->reshape(in[0]->shape(), true);
   }
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *a = rd(in[0], this->ctx_), *b = rd(in[1], this->ctx_);
     float *y = wr(out[0], this->ctx_);
     nb200_check(nb200_add2_f32(a, b, y, in[0]->size(), st), "Add2");
@@ -904,7 +918,7 @@ protected:
                              const vector<bool> &accum) {
     if (!(pd[0] || pd[1]))
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
     for (int i = 0; i < 2; ++i)
       if (pd[i]) {
@@ -923,7 +937,7 @@ protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
     NBLA_CHECK(!this->channel_last_, error_code::not_implemented, "channel_last is not supported");
     NBLA_CHECK(this->kernel_.size() == 2, error_code::not_implemented, "the b200 backend implements 2-D pooling only");
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const float tag = fxp_tag_get(in[0]);
     const Shape_t sx = in[0]->shape();
     const int H = sx[sx.size() - 2], W = sx[sx.size() - 1];
@@ -943,7 +957,7 @@ protected:
                              const vector<bool> &accum) {
     if (!pd[0])
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const Shape_t sx = in[0]->shape();
     const int H = sx[sx.size() - 2], W = sx[sx.size() - 1];
     const float *x = rd(in[0], this->ctx_);
@@ -963,7 +977,7 @@ public:
 
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const Shape_t sx = in[0]->shape();
     const Size_t maps = sx[0] * sx[1];
     const float *x = rd(in[0], this->ctx_);
@@ -975,7 +989,7 @@ protected:
                              const vector<bool> &accum) {
     if (!pd[0])
       return;
-    void *st = enter(this->ctx_);
+    B200_ENTER(st);
     const Shape_t sx = in[0]->shape();
     const Size_t maps = sx[0] * sx[1];
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
