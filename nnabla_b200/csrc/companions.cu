@@ -80,21 +80,36 @@ __global__ void __launch_bounds__(kThreads) bn_inference_plane_kernel(const floa
   pdl_trigger();
   const unsigned plane = blockIdx.x;
   const int c = (int)(plane % (unsigned)C);
+  const float4 *xp = reinterpret_cast<const float4 *>(x) + (size_t)plane * S4;
+  float4 *yp = reinterpret_cast<float4 *>(y) + (size_t)plane * S4;
+  // the data loads go out first: they do not depend on the channel's constants, whose own loads, square
+  // root and reciprocal would otherwise stand in front of them in every (short) block
+  constexpr int kPer = 4;
+  const int step = gridDim.y * kThreads;
+  int i = blockIdx.y * kThreads + threadIdx.x;
+  float4 v[kPer];
+#pragma unroll
+  for (int u = 0; u < kPer; ++u)
+    if (i + u * step < S4)
+      v[u] = __ldcs(xp + i + u * step);
   const float m = __ldg(mean + c);
   const float sd = __fsqrt_rn(__fadd_rn(__ldg(var + c), eps));
   const float g = gamma ? __ldg(gamma + c) : 1.0f;
   const float b = beta ? __ldg(beta + c) : 0.0f;
-  const float4 *xp = reinterpret_cast<const float4 *>(x) + (size_t)plane * S4;
-  float4 *yp = reinterpret_cast<float4 *>(y) + (size_t)plane * S4;
-  for (int i = blockIdx.y * kThreads + threadIdx.x; i < S4; i += gridDim.y * kThreads) {
-    const float4 v = __ldcs(xp + i);
+  auto one = [&](float4 a) {
     float4 r;
-    r.x = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(v.x, m), g), sd), b);
-    r.y = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(v.y, m), g), sd), b);
-    r.z = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(v.z, m), g), sd), b);
-    r.w = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(v.w, m), g), sd), b);
-    __stcs(yp + i, r);
-  }
+    r.x = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(a.x, m), g), sd), b);
+    r.y = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(a.y, m), g), sd), b);
+    r.z = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(a.z, m), g), sd), b);
+    r.w = __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(a.w, m), g), sd), b);
+    return r;
+  };
+#pragma unroll
+  for (int u = 0; u < kPer; ++u)
+    if (i + u * step < S4)
+      __stcs(yp + i + u * step, one(v[u]));
+  for (i += kPer * step; i < S4; i += step)
+    __stcs(yp + i, one(__ldcs(xp + i)));
 }
 
 // ReLU (src/nbla/function/generic/relu.cpp): y = max(0, x); Add2 (add2.cpp): y = a + b.
@@ -519,7 +534,7 @@ int nb200_batch_normalization_inference_f32(const float *x, const float *beta, c
   const bool vec = (inner % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
   if (vec && inner >= 4 * kThreads && outer * channels < (1ll << 31)) {
     const int S4 = (int)(inner / 4);
-    int chunks = (S4 + 2 * kThreads - 1) / (2 * kThreads); // about two float4 per thread
+    int chunks = (S4 + 4 * kThreads - 1) / (4 * kThreads); // about four float4 per thread
     chunks = chunks > 64 ? 64 : chunks;
     NB_CUDA(launch_dependent(bn_inference_plane_kernel, dim3((unsigned)(outer * channels), (unsigned)chunks),
                              dim3(kThreads), 0, as_stream(stream), x, beta, gamma, mean, var, (int)channels, S4, eps,

@@ -118,3 +118,28 @@ def test_pooling_3x3_stride2_vector_path(F, shape, ib):
     x = np.minimum(x, 0.0) if shape[0] == 3 else x          # all windows hold only zeros and negatives
     got = F.max_pooling(dev(x), (3, 3), (2, 2), ib, (1, 1))
     assert np.array_equal(bits(host(got)), bits(oracle.max_pooling(x, (3, 3), (2, 2), ib, (1, 1))))
+
+
+def test_batch_normalization_division_is_ieee_exact_over_wide_ranges(F):
+    """The normalisation's quotient must be the IEEE fp32 quotient for every magnitude, down to subnormal
+    results, whatever way the kernel takes to divide by its per-channel constant."""
+    rng = np.random.RandomState(21)
+    C, S = 96, 4096
+    mag = np.exp(rng.uniform(np.log(1e-38), np.log(1e38), size=(8, C, S))).astype(np.float32)
+    x = (mag * rng.choice([-1.0, 1.0], size=mag.shape)).astype(np.float32)
+    x[0, :, :64] = 0.0
+    x[1, :, :64] = -0.0
+    x[2, :, :256] = rng.randint(-2 ** 23, 2 ** 23, size=(C, 256)).astype(np.float32) * np.float32(2.0 ** -149)  # subnormals
+    x[3, :, :256] = rng.randint(1, 2 ** 24, size=(C, 256)).astype(np.float32)                              # integers
+    var = np.exp(rng.uniform(np.log(1e-12), np.log(1e12), size=C)).astype(np.float32)
+    var[:8] = np.float32([4.0, 0.25, 1.0, 9.0, 2.0 ** 40, 2.0 ** -40, 3.0, 1e-30]) - np.float32(1e-5)  # exact roots, tiny
+    var = np.maximum(var, np.float32(0.0))
+    gamma = np.ones(C, np.float32)
+    gamma[::3] = np.exp(rng.uniform(-20, 20, size=len(gamma[::3]))).astype(np.float32)
+    beta = np.zeros(C, np.float32)
+    mean = np.zeros(C, np.float32)
+    mean[1::2] = rng.randn(len(mean[1::2])).astype(np.float32)
+    with np.errstate(all="ignore"):
+        want = oracle.batch_norm_inference(x, beta, gamma, mean, var, 1e-5)
+    got = host(F.batch_normalization(dev(x), dev(beta), dev(gamma), dev(mean), dev(var), [1], 0.9, 1e-5, False))
+    assert np.array_equal(bits(got).reshape(-1), bits(want).reshape(-1))
