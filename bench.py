@@ -395,7 +395,11 @@ class FunctionTimer:
             w = a[1]
             k = w.shape[1] * w.shape[2] * w.shape[3]
             kind = "int8_ops" if (name == "binary_weight_convolution" and kw.get("fixed_point_delta")) else "flops"
-            return (kind, 2.0 * n_out * k)
+            # the function as the graph calls it also moves its fp32 input and result (and reads the weights,
+            # and writes their signs): with quantized activations that traffic, not the contraction, is the
+            # larger floor for most layers
+            extra = 2 if name == "binary_weight_convolution" else 1
+            return (kind, 2.0 * n_out * k, 4.0 * (n_in + n_out + extra * w.numel()))
         if name == "affine":
             return ("flops", 2.0 * n_out * a[1].shape[0])
         return ("bytes", 0.0)
@@ -404,11 +408,13 @@ class FunctionTimer:
         import torch
         torch.cuda.synchronize()
         fam = {}
-        for name, e0, e1, (kind, work) in self.records:
-            f = fam.setdefault(name, {"calls": 0, "ms": 0.0, "kind": kind, "work": 0.0})
+        for name, e0, e1, rec in self.records:
+            kind, work = rec[0], rec[1]
+            f = fam.setdefault(name, {"calls": 0, "ms": 0.0, "kind": kind, "work": 0.0, "bytes": 0.0})
             f["calls"] += 1
             f["ms"] += e0.elapsed_time(e1)
             f["work"] += work
+            f["bytes"] += rec[2] if len(rec) > 2 else (work if kind == "bytes" else 0.0)
         return fam
 
 
@@ -438,19 +444,34 @@ def function_table(F, params, gz, x, peaks, int8_peak, passes=3):
         else:
             row["tflops"] = f["work"] / f["ms"] / 1e9
             row["frac_bf16"] = row["tflops"] / peaks["bf16_tflops"]
+        if f["kind"] != "bytes" and f["bytes"] > 0:
+            row["GBps_fp32_tensors"] = f["bytes"] / f["ms"] / 1e6
+            row["frac_hbm"] = row["GBps_fp32_tensors"] / peaks["hbm_gbs"]
         rows[name] = row
     top = max(fam.items(), key=lambda kv: kv[1]["ms"])
     name, f = top
     per_call_ms = f["ms"] / f["calls"]
-    if f["kind"] == "bytes":
-        ach, peak, unit, bound = f["work"] / f["ms"] / 1e6, peaks["hbm_gbs"], "GB/s", "hbm"
-    elif f["kind"] == "int8_ops":
-        ach, peak, unit, bound = f["work"] / f["ms"] / 1e9, int8_peak, "TOP/s", "tensor"
+    tensor_peak = int8_peak if f["kind"] == "int8_ops" else peaks["bf16_tflops"]
+    # the bound of a function is the larger of its two floors: moving its tensors, or its operations
+    t_hbm = f["bytes"] / peaks["hbm_gbs"] / 1e6
+    t_tensor = 0.0 if f["kind"] == "bytes" else f["work"] / tensor_peak / 1e9
+    if t_hbm >= t_tensor:
+        ach, peak, unit, bound, work = f["bytes"] / f["ms"] / 1e6, peaks["hbm_gbs"], "GB/s", "hbm", f["bytes"]
     else:
-        ach, peak, unit, bound = f["work"] / f["ms"] / 1e9, peaks["bf16_tflops"], "TFLOP/s", "tensor"
+        unit = "TOP/s" if f["kind"] == "int8_ops" else "TFLOP/s"
+        ach, peak, bound, work = f["work"] / f["ms"] / 1e9, tensor_peak, "tensor", f["work"]
     roof = {"bound": bound, "kernel": name, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
             "traffic": None, "share_of_step": f["ms"] / total, "ms_per_call": per_call_ms,
-            "algorithmic_work_per_call": f["work"] / f["calls"]}
+            "algorithmic_work_per_call": work / f["calls"],
+            "floors_ms_per_pass": {"hbm": t_hbm / passes, "tensor": t_tensor / passes}}
+    # the whole step against the sum of every function's larger floor
+    step_floor = 0.0
+    for g in fam.values():
+        tp = int8_peak if g["kind"] == "int8_ops" else peaks["bf16_tflops"]
+        step_floor += max(g["bytes"] / peaks["hbm_gbs"] / 1e6, 0.0 if g["kind"] == "bytes" else g["work"] / tp / 1e9)
+    roof["step_floor_ms"] = step_floor / passes
+    roof["step_ms_sum_of_functions"] = total / passes
+    roof["step_frac_of_floor"] = step_floor / total
     return rows, roof
 
 
@@ -834,6 +855,8 @@ def run_b200_arm(args):
     # ---- per-function table and the roofline entry -----------------------------------------
     table, roofline = function_table(F, params, gz, x, peaks, int8_peak)
     roofline["peak_source"] = peak_kind if roofline["unit"] != "TOP/s" else "measured in this run (torch._int_mm 8192^3)"
+    if roofline["bound"] == "hbm" and roofline["kernel"].endswith("convolution"):
+        roofline["bytes_counted"] = "fp32 input and result of every call, its weights read, their signs written"
 
     del x, logits
     torch.cuda.empty_cache()
