@@ -28,7 +28,7 @@ void init_b200();
 
 /** Context of this backend: Context({"b200:float"}, "B200CachedArray", device_id).
     There is no "cpu:float" entry: no function falls back to the CPU. */
-Context b200_context(const string &device_id = "0");
+Context b200_context(const string &device_id = "0", const string &type_config = "float");
 
 /** Raises nbla::Exception for a non-zero status of the C ABI (the message is
     nb200_last_error()). */

@@ -34,7 +34,11 @@ def array_classes():
 
 def context(device_id="0", type_config="float", **kw):
     """Context of the b200 backend. There is deliberately no 'cpu:float' entry:
-    a function without a b200 implementation raises instead of falling back."""
+    a function without a b200 implementation raises instead of falling back.
+    type_config='half' gives ['b200:half', 'b200:float'] as nnabla's extensions do; nothing is registered under
+    'b200:half', so the function registry resolves every function to its float implementation."""
+    if type_config == "half":
+        return nn.Context(["b200:half", "b200:float"], array_classes()[0], str(device_id))
     if type_config != "float":
         raise ValueError("Unknown data type config is given %s" % type_config)
     return nn.Context(["b200:float"], array_classes()[0], str(device_id))

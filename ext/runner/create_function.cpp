@@ -41,9 +41,10 @@ namespace nbla_b200_runner {
 Context context_for(const std::string &backend, const std::string &device_id) {
   if (backend == "cpu:float")
     return Context({"cpu:float"}, "CpuCachedArray", device_id);
-  NBLA_CHECK(backend == "b200:float", error_code::value, "unknown backend %s", backend.c_str());
+  NBLA_CHECK(backend == "b200:float" || backend == "b200:half", error_code::value, "unknown backend %s",
+             backend.c_str());
   init_b200();
-  return b200_context(device_id);
+  return b200_context(device_id, backend == "b200:half" ? "half" : "float");
 }
 
 FunctionPtr create_function(const std::string &name, const Context &ctx, const double *s, int n_s,

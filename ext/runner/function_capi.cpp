@@ -78,7 +78,8 @@ int nbext_forward(const char *backend, const char *op, const double *s, int n_s,
                   nbext_tensor *out, int n_out, int mode, char *fname, int fname_len) {
   try {
     const std::string be(backend);
-    Context ctx = be == "cpu:float" ? Context({"cpu:float"}, "CpuCachedArray", "0") : b200_context("0");
+    Context ctx = be == "cpu:float" ? Context({"cpu:float"}, "CpuCachedArray", "0")
+                                    : b200_context("0", be == "b200:half" ? "half" : "float");
     if (be != "cpu:float")
       init_b200();
     Context cpu({"cpu:float"}, "CpuCachedArray", "0");
@@ -158,7 +159,8 @@ int nbext_backward(const char *backend, const char *op, const double *s, int n_s
                    const int32_t *accum) {
   try {
     const std::string be(backend);
-    Context ctx = be == "cpu:float" ? Context({"cpu:float"}, "CpuCachedArray", "0") : b200_context("0");
+    Context ctx = be == "cpu:float" ? Context({"cpu:float"}, "CpuCachedArray", "0")
+                                    : b200_context("0", be == "b200:half" ? "half" : "float");
     if (be != "cpu:float")
       init_b200();
     Context cpu({"cpu:float"}, "CpuCachedArray", "0");

@@ -127,7 +127,15 @@ DataStamp data_stamp(const Variable *v) {
   return s;
 }
 
-Context b200_context(const string &device_id) { return Context({"b200:float"}, "B200CachedArray", device_id); }
+Context b200_context(const string &device_id, const string &type_config) {
+  // "half": the backend list an nnabla extension gives for that type config. No function is registered under
+  // "b200:half", so the registry's query (function_registry.hpp:57-72) goes on to "b200:float": the half
+  // configuration runs the float implementations (fp32 arrays) rather than failing.
+  if (type_config == "half")
+    return Context({"b200:half", "b200:float"}, "B200CachedArray", device_id);
+  NBLA_CHECK(type_config == "float", error_code::value, "Unknown data type config is given %s", type_config.c_str());
+  return Context({"b200:float"}, "B200CachedArray", device_id);
+}
 
 // ---------------------------------------------------------------- B200Memory
 B200Memory::B200Memory(size_t bytes, const string &device_id) : Memory(bytes, device_id) {}

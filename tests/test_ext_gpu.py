@@ -169,6 +169,20 @@ def test_companions_training_side():
     assert cases.rel_rms(gb[0][1], cb[0][1]) < 1e-5 and cases.rel_rms(gb[0][2], cb[0][2]) < 1e-5
 
 
+def test_half_type_config_resolves_to_the_float_implementations():
+    """Context(['b200:half', 'b200:float']) (what an nnabla extension hands out for type_config='half'): nothing is
+    registered under 'b200:half', so nnabla's registry goes on to 'b200:float' (function_registry.hpp:57-72)."""
+    x = cases.fxp_input()
+    g = H.forward(B200, "FixedPointQuantize", [True, 8, 2.0 ** -4, True], [], [x])
+    h = H.forward("b200:half", "FixedPointQuantize", [True, 8, 2.0 ** -4, True], [], [x])
+    assert h[2] == "FixedPointQuantize" and np.array_equal(bits(h[0][0]), bits(g[0][0]))
+    xa, wa, ba = cases.affine_inputs((3, 5, 7), (35, 40))
+    wb, al = np.zeros_like(wa), np.zeros(wa.shape[1], np.float32)
+    g = H.forward(B200, "BinaryWeightAffine", [1, 1.0], [], [xa, wa, wb, al, ba])
+    h = H.forward("b200:half", "BinaryWeightAffine", [1, 1.0], [], [xa, wa, wb, al, ba])
+    assert np.array_equal(bits(h[0][0]), bits(g[0][0]))
+
+
 def test_errors_surface_as_exceptions():
     x = np.zeros((4, 8), np.float32)
     with pytest.raises(RuntimeError, match="positive"):
