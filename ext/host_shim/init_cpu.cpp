@@ -52,6 +52,7 @@
 #include <nbla/function/round.hpp>
 #include <nbla/function/sign.hpp>
 #include <nbla/function/sub2.hpp>
+#include <nbla/function/inq_affine.hpp>
 #include <nbla/function/sum.hpp>
 #include <nbla/function/transpose.hpp>
 
@@ -130,6 +131,10 @@ void init_cpu() {
   REG(QuantizeLinear, const string &, bool, int);
   REG(DequantizeLinear);
   REG(Prune, float);
+  {
+    using INQAffine_float_int = INQAffine<float, int>;
+    NBLA_REGISTER_FUNCTION_IMPL(INQAffine, INQAffine_float_int, "cpu:float", int, int, ivec, const string &, int);
+  }
 }
 
 void clear_cpu_memory_cache() {

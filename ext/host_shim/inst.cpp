@@ -7,5 +7,9 @@
 // TEST INFRASTRUCTURE ONLY (part of the oracle build).
 #include NBHOST_SRC
 namespace nbla {
+#ifdef NBHOST_TWO_TYPES // functions with a second type parameter for integer side data (INQAffine<float, int>)
+template class NBHOST_CLASS<float, int>;
+#else
 template class NBHOST_CLASS<float>;
+#endif
 }

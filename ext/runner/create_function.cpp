@@ -17,6 +17,7 @@
 #include <nbla/function/convolution.hpp>
 #include <nbla/function/fixed_point_quantize.hpp>
 #include <nbla/function/global_average_pooling.hpp>
+#include <nbla/function/inq_affine.hpp>
 #include <nbla/function/max_pooling.hpp>
 #include <nbla/function/binary_sigmoid.hpp>
 #include <nbla/function/binary_tanh.hpp>
@@ -89,6 +90,8 @@ FunctionPtr create_function(const std::string &name, const Context &ctx, const d
     return create_BinarySigmoid(ctx);
   if (name == "BinaryTanh")
     return create_BinaryTanh(ctx);
+  if (name == "INQAffine") // scalars: base_axis, num_bits, selection (0 = largest_abs, 1 = random), seed; ivecs: inq_iterations
+    return create_INQAffine(ctx, (int)S(0), (int)S(1), ivs.at(0), S(2) != 0 ? "random" : "largest_abs", (int)S(3));
   if (name == "QuantizeLinear") // scalars: round mode (0 = HALF_AWAY_FROM_ZERO, 1 = HALF_TO_EVEN), narrow_range, dtype
     return create_QuantizeLinear(ctx, S(0) != 0 ? "HALF_TO_EVEN" : "HALF_AWAY_FROM_ZERO", S(1) != 0, (int)S(2));
   if (name == "DequantizeLinear")

@@ -26,6 +26,8 @@
 #include <nbla/function/convolution.hpp>
 #include <nbla/function/fixed_point_quantize.hpp>
 #include <nbla/function/global_average_pooling.hpp>
+#include <nbla/function/inq_affine.hpp>
+#include <nbla/random_manager.hpp>
 #include <nbla/function/max_pooling.hpp>
 #include <nbla/function/binary_sigmoid.hpp>
 #include <nbla/function/binary_tanh.hpp>
@@ -42,7 +44,10 @@
 #include <nnabla_b200.h>
 #include <nvtx3/nvToolsExt.h>
 
+#include <algorithm>
 #include <mutex>
+#include <numeric>
+#include <random>
 
 namespace nbla {
 
@@ -999,6 +1004,78 @@ protected:
   }
 };
 
+
+// INQAffine (src/nbla/function/generic/inq_affine.cpp). The reference's setup_impl is reused as it is: it
+// creates the inner Affine through the registry under this context, i.e. AffineB200, and sizes the state.
+// forward_impl runs the weight update on the device; only the selection step (a few iterations of a training
+// run) is done on the host with the reference's own loop (std::sort's order among equal magnitudes and the
+// mt19937 / bernoulli stream are then the same library's, hence identical), reading and writing the arrays
+// through the CPU context, which nnabla synchronises in both directions.
+template <typename T, typename T1> class INQAffineB200 : public INQAffine<T, T1> {
+public:
+  using INQAffine<T, T1>::INQAffine;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    B200_ENTER(st);
+    const Size_t n = in[1]->size();
+    {
+      float *w = in[1]->template cast_data_and_get_pointer<float>(this->ctx_);
+      const float *ow = this->old_weights_.template get_data_pointer<float>(this->ctx_);
+      const int *oi = this->old_indicators_.template get_data_pointer<int>(this->ctx_);
+      nb200_check(nb200_inq_restore_f32(w, ow, oi, n, st), "INQAffine");
+    }
+    int fix_all = 0;
+    const vector<int> &its = this->inq_iterations_;
+    if (std::find(its.begin(), its.end(), this->minibatch_counter_) != its.end()) {
+      if (its.back() == this->minibatch_counter_) {
+        fix_all = 1;
+      } else {
+        const Context cpu({"cpu:float"}, "CpuCachedArray", "0");
+        const float *weights = in[1]->template get_data_pointer<float>(cpu);
+        int *indicators = in[2]->template cast_data_and_get_pointer<int>(cpu);
+        if (this->selection_algorithm_ == "largest_abs") { // inq_affine.cpp:118-139
+          vector<size_t> indices(n);
+          std::iota(begin(indices), end(indices), 0);
+          std::sort(begin(indices), end(indices),
+                    [&](size_t a, size_t b) { return std::abs(weights[a]) > std::abs(weights[b]); });
+          int num_learnable = 0;
+          for (Size_t i = 0; i < n; ++i)
+            num_learnable += indicators[i] == 0;
+          int num_fixed = 0;
+          for (Size_t i = 0; i < n; ++i) {
+            if (indicators[indices[i]] == 0) {
+              indicators[indices[i]] = 1;
+              num_fixed++;
+            }
+            if (num_fixed >= num_learnable / 2)
+              break;
+          }
+        } else { // :140-147
+          std::mt19937 &rgen =
+              this->seed_ == -1 ? SingletonManager::get<RandomManager>()->get_rand_generator() : this->rgen_;
+          for (Size_t i = 0; i < n; ++i)
+            if (indicators[i] == 0)
+              indicators[i] = this->rdist_(rgen);
+        }
+      }
+    }
+    {
+      float *w = in[1]->template cast_data_and_get_pointer<float>(this->ctx_);
+      int *ind = in[2]->template cast_data_and_get_pointer<int>(this->ctx_);
+      float *ow = this->old_weights_.template cast_data_and_get_pointer<float>(this->ctx_);
+      int *oi = this->old_indicators_.template cast_data_and_get_pointer<int>(this->ctx_);
+      nb200_check(nb200_inq_quantize_f32(w, ind, ow, oi, n, this->num_bits_, fix_all, st), "INQAffine");
+    }
+    if (in.size() == 4)
+      this->affine_->forward(Variables{in[0], in[1], in[3]}, out);
+    else
+      this->affine_->forward(Variables{in[0], in[1]}, out);
+    this->minibatch_counter_++;
+  }
+};
+
 } // namespace
 
 // ------------------------------------------------------------------- init
@@ -1060,6 +1137,10 @@ void init_b200() {
   REG(MaxPooling, ivec, ivec, bool, ivec, bool);
   REG(GlobalAveragePooling);
 #undef REG
+  {
+    using INQAffine_b200 = INQAffineB200<float, int>;
+    NBLA_REGISTER_FUNCTION_IMPL(INQAffine, INQAffine_b200, "b200:float", int, int, ivec, const string &, int);
+  }
 }
 
 } // namespace nbla

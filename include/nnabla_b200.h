@@ -561,6 +561,23 @@ int nb200_max_pooling_f32(const float *x, float *y, int64_t maps, int height, in
 /* GlobalAveragePooling<float>::forward_impl
  * (src/nbla/function/generic/global_average_pooling.cpp): x [maps, spatial] -> y [maps]. */
 int nb200_global_average_pooling_f32(const float *x, float *y, int64_t maps, int64_t spatial, void *stream);
+/* ---- incremental network quantization (INQAffine / INQConvolution) ---- */
+/* The weight update of INQAffine<float, int>::forward_impl (src/nbla/function/generic/inq_affine.cpp:82-203)
+ * in two calls, around the selection step that the caller performs a few times per training run (:108-148:
+ * a sort by magnitude or a Bernoulli draw per learnable weight, then indicator = 1 for the chosen ones):
+ *   nb200_inq_restore_f32   :101-105  weights[i] = old_weights[i] where old_indicators[i] == 1
+ *   nb200_inq_quantize_f32  :150-203  n1 from max |w|, n2 = n1 + 1 - 2^(num_bits - 2); every weight whose
+ *       indicator is 1 (all of them when fix_all != 0, the last INQ iteration, which also sets the
+ *       indicators) becomes 0 below 2^(n2 - 1), else sign * 2^e with e = floor(log2 |w|) +
+ *       (log2 |w| - floor >= log2 1.5) clipped to [n2, n1]; then weights and indicators are copied to
+ *       old_weights / old_indicators. The exponent rule reproduces the host libm's log2f binade by binade
+ *       (the step near a mantissa of 1.5 is located with it at first use); NB200_ENOTIMPL if that libm does
+ *       not behave as one step per binade. Indicators are int32 (the reference's T1 = int). */
+int nb200_inq_restore_f32(float *weights, const float *old_weights, const int32_t *old_indicators, size_t size,
+                          void *stream);
+int nb200_inq_quantize_f32(float *weights, int32_t *indicators, float *old_weights, int32_t *old_indicators,
+                           size_t size, int num_bits, int fix_all, void *stream);
+
 /* ---- training side of the companions ---- */
 /* BatchNormalization<float>::forward_impl_batch
  * (src/nbla/function/generic/batch_normalization.cpp:157-226), batch_stat = true, one normalised

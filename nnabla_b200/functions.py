@@ -740,6 +740,70 @@ def global_average_pooling(x, n_outputs=-1, outputs=None):
     return y
 
 
+class INQState:
+    """What one INQAffine function instance keeps across forward passes (inq_affine.cpp:74-80): the
+    weights and indicators of the previous pass, the pass counter, the random stream."""
+
+    def __init__(self, weight, seed=-1):
+        self.old_weights = torch.zeros_like(weight)
+        self.old_indicators = torch.zeros(weight.shape, dtype=torch.int32, device=weight.device)
+        self.counter = 0
+        self.generator = None
+        if seed != -1:
+            self.generator = torch.Generator(device=weight.device)
+            self.generator.manual_seed(int(seed))
+
+
+def inq_update_weights(weight, indicators, state, num_bits=4, inq_iterations=(), selection_algorithm="largest_abs"):
+    """The weight update of INQAffine / INQConvolution (inq_affine.cpp:82-203), in place on `weight` (fp32)
+    and `indicators` (int32). The selection step runs on the device through torch's sort / Bernoulli
+    sampler; the random stream is torch's, not the reference's mt19937."""
+    if selection_algorithm not in ("largest_abs", "random"):
+        raise ValueError('Provided value for selection algorithm not valid: %s. Valid values are "largest_abs" '
+                         'and "random".' % selection_algorithm)
+    weight = _check_input(weight, "weight")
+    if indicators.dtype != torch.int32 or indicators.shape != weight.shape or not indicators.is_contiguous():
+        raise RuntimeError("Indicators and weights must have same size (indicators as contiguous int32).")
+    n = weight.numel()
+    its = [int(v) for v in inq_iterations]
+    with C.on_device(weight.device):
+        C.call("nb200_inq_restore_f32", C.ptr(weight), C.ptr(state.old_weights), C.ptr(state.old_indicators),
+               C.size_t(n), C.stream_ptr(weight.device))
+    fix_all = 0
+    if state.counter in its:
+        if its[-1] == state.counter:
+            fix_all = 1
+        elif selection_algorithm == "largest_abs":
+            flat = indicators.view(-1)
+            order = torch.argsort(weight.abs().view(-1), descending=True, stable=True)
+            learnable = flat[order] == 0
+            k = int(learnable.sum().item()) // 2
+            if k == 0:  # the reference's loop looks at the largest weight once before it stops (:131-139)
+                chosen = order[:1][learnable[:1]]
+            else:
+                chosen = order[learnable & (torch.cumsum(learnable, 0) <= k)]
+            flat[chosen] = 1
+        else:
+            flat = indicators.view(-1)
+            draws = torch.bernoulli(torch.full((n,), 0.5, device=weight.device), generator=state.generator).to(torch.int32)
+            flat.copy_(torch.where(flat == 0, draws, flat))
+    with C.on_device(weight.device):
+        C.call("nb200_inq_quantize_f32", C.ptr(weight), C.ptr(indicators), C.ptr(state.old_weights),
+               C.ptr(state.old_indicators), C.size_t(n), int(num_bits), fix_all, C.stream_ptr(weight.device))
+    state.counter += 1
+
+
+def inq_affine(x, weight, indicator_fixedweights, bias=None, base_axis=1, num_bits=4, inq_iterations=(),
+               selection_algorithm="largest_abs", seed=-1, state=None):
+    """INQ Affine (python/src/nnabla/functions.py inq_affine; src/nbla/function/generic/inq_affine.cpp:82-203):
+    updates `weight` and `indicator_fixedweights` in place, then the affine. `state` (INQState) stands for the
+    function instance, which in nnabla carries the previous weights, indicators and the pass counter."""
+    if state is None:
+        raise RuntimeError("inq_affine needs the INQState of its layer (the reference keeps it in the function)")
+    inq_update_weights(weight, indicator_fixedweights, state, num_bits, inq_iterations, selection_algorithm)
+    return affine(x, weight, bias, base_axis)
+
+
 def _grad_out(like, accum, dx):
     if dx is None:
         if accum:

@@ -507,3 +507,37 @@ def prune(x, rate=0.9):
     y = np.empty_like(x)
     lib().oracle_prune(_p(x), _p(y), ctypes.c_int64(x.size), ctypes.c_float(rate))
     return y
+
+
+# Incremental network quantization ---------------------------------------------
+
+class INQState:
+    """The weights' state a function instance of INQAffine keeps across forward passes."""
+
+    def __init__(self, shape):
+        self.old_w = np.zeros(shape, np.float32)
+        self.old_ind = np.zeros(shape, np.int32)
+        self.counter = 0
+
+
+def inq_update(w, ind, state, num_bits, inq_iterations, selection_algorithm="largest_abs", draws=None):
+    """One forward pass's weight update (inq_affine.cpp:82-203). Returns (weights after, indicators after);
+    `state` advances. selection_algorithm="random" needs the Bernoulli draws of this pass in `draws`."""
+    w = _f(w).copy()
+    ind = np.ascontiguousarray(ind, np.int32).copy()
+    trigger = 0
+    if state.counter in list(inq_iterations):
+        trigger = 2 if list(inq_iterations)[-1] == state.counter else (1 if selection_algorithm == "largest_abs" else 3)
+    d = np.ascontiguousarray(draws if draws is not None else [0], np.int32)
+    lib().oracle_inq_update(_p(w), ind.ctypes.data_as(ctypes.c_void_p), _p(state.old_w),
+                            state.old_ind.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(w.size), int(num_bits),
+                            trigger, d.ctypes.data_as(ctypes.c_void_p))
+    state.counter += 1
+    return w, ind
+
+
+def inq_affine(x, w, ind, b, state, base_axis=1, num_bits=4, inq_iterations=(), selection_algorithm="largest_abs",
+               draws=None):
+    """INQAffine forward: returns (y, weights after, indicators after)."""
+    w2, ind2 = inq_update(w, ind, state, num_bits, inq_iterations, selection_algorithm, draws)
+    return affine(x, w2, b, base_axis), w2, ind2

@@ -26,6 +26,7 @@
 #include <nbla/function/convolution.hpp>
 #include <nbla/function/fixed_point_quantize.hpp>
 #include <nbla/function/global_average_pooling.hpp>
+#include <nbla/function/inq_affine.hpp>
 #include <nbla/function/max_pooling.hpp>
 #include <nbla/function/binary_sigmoid.hpp>
 #include <nbla/function/binary_tanh.hpp>
@@ -119,6 +120,8 @@ static FunctionPtr make_function(const Context &ctx, const char *op,
     f = create_BinarySigmoid(ctx);
   else if (name == "BinaryTanh")
     f = create_BinaryTanh(ctx);
+  else if (name == "INQAffine") // scalars: base_axis, num_bits, selection (0 = largest_abs, 1 = random), seed; ivecs: inq_iterations
+    f = create_INQAffine(ctx, (int)S(0), (int)S(1), ivs.at(0), S(2) != 0 ? "random" : "largest_abs", (int)S(3));
   else if (name == "QuantizeLinear") // scalars: round mode (0 = HALF_AWAY_FROM_ZERO, 1 = HALF_TO_EVEN), narrow_range, dtype
     f = create_QuantizeLinear(ctx, S(0) != 0 ? "HALF_TO_EVEN" : "HALF_AWAY_FROM_ZERO", S(1) != 0, (int)S(2));
   else if (name == "DequantizeLinear")

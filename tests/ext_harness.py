@@ -33,8 +33,8 @@ def init():
         raise RuntimeError(lib().nbext_last_error().decode())
 
 
-def forward(backend, op, scalars, ivecs, inputs, n_out=1, prequant=None):
-    """Returns (outputs, inputs_after, function_name)."""
+def forward(backend, op, scalars, ivecs, inputs, n_out=1, prequant=None, repeat=1):
+    """Returns (outputs, inputs_after, function_name); `repeat` forward passes of the one function instance."""
     L = lib()
     ins = [np.ascontiguousarray(a, dtype=np.float32).copy() for a in inputs if a is not None]
     s = (ctypes.c_double * max(1, len(scalars)))(*[float(v) for v in scalars])
@@ -64,7 +64,7 @@ def forward(backend, op, scalars, ivecs, inputs, n_out=1, prequant=None):
         a = np.empty(tuple(t.shape[d] for d in range(t.ndim)), dtype=np.float32)
         t.data = a.ctypes.data
         outs.append(a)
-    call(1)
+    call(int(repeat))
     return outs, ins, name.value.decode()
 
 
