@@ -53,6 +53,7 @@
 #include <nbla/function/sign.hpp>
 #include <nbla/function/sub2.hpp>
 #include <nbla/function/inq_affine.hpp>
+#include <nbla/function/inq_convolution.hpp>
 #include <nbla/function/sum.hpp>
 #include <nbla/function/transpose.hpp>
 
@@ -134,6 +135,9 @@ void init_cpu() {
   {
     using INQAffine_float_int = INQAffine<float, int>;
     NBLA_REGISTER_FUNCTION_IMPL(INQAffine, INQAffine_float_int, "cpu:float", int, int, ivec, const string &, int);
+    using INQConvolution_float_int = INQConvolution<float, int>;
+    NBLA_REGISTER_FUNCTION_IMPL(INQConvolution, INQConvolution_float_int, "cpu:float", int, ivec, ivec, ivec, int, int,
+                                ivec, const string &, int);
   }
 }
 

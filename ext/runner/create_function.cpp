@@ -18,6 +18,7 @@
 #include <nbla/function/fixed_point_quantize.hpp>
 #include <nbla/function/global_average_pooling.hpp>
 #include <nbla/function/inq_affine.hpp>
+#include <nbla/function/inq_convolution.hpp>
 #include <nbla/function/max_pooling.hpp>
 #include <nbla/function/binary_sigmoid.hpp>
 #include <nbla/function/binary_tanh.hpp>
@@ -92,6 +93,9 @@ FunctionPtr create_function(const std::string &name, const Context &ctx, const d
     return create_BinaryTanh(ctx);
   if (name == "INQAffine") // scalars: base_axis, num_bits, selection (0 = largest_abs, 1 = random), seed; ivecs: inq_iterations
     return create_INQAffine(ctx, (int)S(0), (int)S(1), ivs.at(0), S(2) != 0 ? "random" : "largest_abs", (int)S(3));
+  if (name == "INQConvolution") // scalars: base_axis, group, num_bits, selection, seed; ivecs: pad, stride, dilation, inq_iterations
+    return create_INQConvolution(ctx, (int)S(0), V(0), V(1), V(2), (int)S(1), (int)S(2), ivs.at(3),
+                                 S(3) != 0 ? "random" : "largest_abs", (int)S(4));
   if (name == "QuantizeLinear") // scalars: round mode (0 = HALF_AWAY_FROM_ZERO, 1 = HALF_TO_EVEN), narrow_range, dtype
     return create_QuantizeLinear(ctx, S(0) != 0 ? "HALF_TO_EVEN" : "HALF_AWAY_FROM_ZERO", S(1) != 0, (int)S(2));
   if (name == "DequantizeLinear")

@@ -27,6 +27,7 @@
 #include <nbla/function/fixed_point_quantize.hpp>
 #include <nbla/function/global_average_pooling.hpp>
 #include <nbla/function/inq_affine.hpp>
+#include <nbla/function/inq_convolution.hpp>
 #include <nbla/random_manager.hpp>
 #include <nbla/function/max_pooling.hpp>
 #include <nbla/function/binary_sigmoid.hpp>
@@ -1005,12 +1006,72 @@ protected:
 };
 
 
-// INQAffine (src/nbla/function/generic/inq_affine.cpp). The reference's setup_impl is reused as it is: it
-// creates the inner Affine through the registry under this context, i.e. AffineB200, and sizes the state.
-// forward_impl runs the weight update on the device; only the selection step (a few iterations of a training
-// run) is done on the host with the reference's own loop (std::sort's order among equal magnitudes and the
-// mt19937 / bernoulli stream are then the same library's, hence identical), reading and writing the arrays
-// through the CPU context, which nnabla synchronises in both directions.
+// INQAffine / INQConvolution (src/nbla/function/generic/inq_affine.cpp, inq_convolution.cpp). The reference's
+// setup_impl is reused as it is: it creates the inner Affine / Convolution through the registry under this
+// context, i.e. AffineB200 / ConvolutionB200, and sizes the state. forward_impl runs the weight update on the
+// device; only the selection step (a few iterations of a training run) is done on the host with the
+// reference's own loop (std::sort's order among equal magnitudes and the mt19937 / bernoulli stream are then
+// the same library's, hence identical), reading and writing the arrays through the CPU context, which nnabla
+// synchronises in both directions.
+struct InqState { // the members of the two reference classes the update works on
+  const vector<int> &iterations;
+  const string &selection_algorithm;
+  int seed, num_bits, minibatch_counter;
+  std::mt19937 &rgen;
+  std::bernoulli_distribution &rdist;
+  Variable &old_weights, &old_indicators;
+};
+
+void inq_weight_update(const Context &ctx, void *st, Variable *weights_var, Variable *indicators_var, InqState s,
+                       const char *what) {
+  const Size_t n = weights_var->size();
+  {
+    float *w = weights_var->cast_data_and_get_pointer<float>(ctx);
+    const float *ow = s.old_weights.get_data_pointer<float>(ctx);
+    const int *oi = s.old_indicators.get_data_pointer<int>(ctx);
+    nb200_check(nb200_inq_restore_f32(w, ow, oi, n, st), what);
+  }
+  int fix_all = 0;
+  const vector<int> &its = s.iterations;
+  if (std::find(its.begin(), its.end(), s.minibatch_counter) != its.end()) {
+    if (its.back() == s.minibatch_counter) {
+      fix_all = 1;
+    } else {
+      const Context cpu({"cpu:float"}, "CpuCachedArray", "0");
+      const float *weights = weights_var->get_data_pointer<float>(cpu);
+      int *indicators = indicators_var->cast_data_and_get_pointer<int>(cpu);
+      if (s.selection_algorithm == "largest_abs") { // inq_affine.cpp:118-139
+        vector<size_t> indices(n);
+        std::iota(begin(indices), end(indices), 0);
+        std::sort(begin(indices), end(indices),
+                  [&](size_t a, size_t b) { return std::abs(weights[a]) > std::abs(weights[b]); });
+        int num_learnable = 0;
+        for (Size_t i = 0; i < n; ++i)
+          num_learnable += indicators[i] == 0;
+        int num_fixed = 0;
+        for (Size_t i = 0; i < n; ++i) {
+          if (indicators[indices[i]] == 0) {
+            indicators[indices[i]] = 1;
+            num_fixed++;
+          }
+          if (num_fixed >= num_learnable / 2)
+            break;
+        }
+      } else { // :140-147
+        std::mt19937 &rgen = s.seed == -1 ? SingletonManager::get<RandomManager>()->get_rand_generator() : s.rgen;
+        for (Size_t i = 0; i < n; ++i)
+          if (indicators[i] == 0)
+            indicators[i] = s.rdist(rgen);
+      }
+    }
+  }
+  float *w = weights_var->cast_data_and_get_pointer<float>(ctx);
+  int *ind = indicators_var->cast_data_and_get_pointer<int>(ctx);
+  float *ow = s.old_weights.cast_data_and_get_pointer<float>(ctx);
+  int *oi = s.old_indicators.cast_data_and_get_pointer<int>(ctx);
+  nb200_check(nb200_inq_quantize_f32(w, ind, ow, oi, n, s.num_bits, fix_all, st), what);
+}
+
 template <typename T, typename T1> class INQAffineB200 : public INQAffine<T, T1> {
 public:
   using INQAffine<T, T1>::INQAffine;
@@ -1019,59 +1080,36 @@ public:
 protected:
   virtual void forward_impl(const Variables &in, const Variables &out) {
     B200_ENTER(st);
-    const Size_t n = in[1]->size();
-    {
-      float *w = in[1]->template cast_data_and_get_pointer<float>(this->ctx_);
-      const float *ow = this->old_weights_.template get_data_pointer<float>(this->ctx_);
-      const int *oi = this->old_indicators_.template get_data_pointer<int>(this->ctx_);
-      nb200_check(nb200_inq_restore_f32(w, ow, oi, n, st), "INQAffine");
-    }
-    int fix_all = 0;
-    const vector<int> &its = this->inq_iterations_;
-    if (std::find(its.begin(), its.end(), this->minibatch_counter_) != its.end()) {
-      if (its.back() == this->minibatch_counter_) {
-        fix_all = 1;
-      } else {
-        const Context cpu({"cpu:float"}, "CpuCachedArray", "0");
-        const float *weights = in[1]->template get_data_pointer<float>(cpu);
-        int *indicators = in[2]->template cast_data_and_get_pointer<int>(cpu);
-        if (this->selection_algorithm_ == "largest_abs") { // inq_affine.cpp:118-139
-          vector<size_t> indices(n);
-          std::iota(begin(indices), end(indices), 0);
-          std::sort(begin(indices), end(indices),
-                    [&](size_t a, size_t b) { return std::abs(weights[a]) > std::abs(weights[b]); });
-          int num_learnable = 0;
-          for (Size_t i = 0; i < n; ++i)
-            num_learnable += indicators[i] == 0;
-          int num_fixed = 0;
-          for (Size_t i = 0; i < n; ++i) {
-            if (indicators[indices[i]] == 0) {
-              indicators[indices[i]] = 1;
-              num_fixed++;
-            }
-            if (num_fixed >= num_learnable / 2)
-              break;
-          }
-        } else { // :140-147
-          std::mt19937 &rgen =
-              this->seed_ == -1 ? SingletonManager::get<RandomManager>()->get_rand_generator() : this->rgen_;
-          for (Size_t i = 0; i < n; ++i)
-            if (indicators[i] == 0)
-              indicators[i] = this->rdist_(rgen);
-        }
-      }
-    }
-    {
-      float *w = in[1]->template cast_data_and_get_pointer<float>(this->ctx_);
-      int *ind = in[2]->template cast_data_and_get_pointer<int>(this->ctx_);
-      float *ow = this->old_weights_.template cast_data_and_get_pointer<float>(this->ctx_);
-      int *oi = this->old_indicators_.template cast_data_and_get_pointer<int>(this->ctx_);
-      nb200_check(nb200_inq_quantize_f32(w, ind, ow, oi, n, this->num_bits_, fix_all, st), "INQAffine");
-    }
+    inq_weight_update(this->ctx_, st, in[1], in[2],
+                      InqState{this->inq_iterations_, this->selection_algorithm_, this->seed_, this->num_bits_,
+                               this->minibatch_counter_, this->rgen_, this->rdist_, this->old_weights_,
+                               this->old_indicators_},
+                      "INQAffine");
     if (in.size() == 4)
       this->affine_->forward(Variables{in[0], in[1], in[3]}, out);
     else
       this->affine_->forward(Variables{in[0], in[1]}, out);
+    this->minibatch_counter_++;
+  }
+};
+
+template <typename T, typename T1> class INQConvolutionB200 : public INQConvolution<T, T1> {
+public:
+  using INQConvolution<T, T1>::INQConvolution;
+  virtual vector<string> allowed_array_classes() { return device_array_classes(); }
+
+protected:
+  virtual void forward_impl(const Variables &in, const Variables &out) {
+    B200_ENTER(st);
+    inq_weight_update(this->ctx_, st, in[1], in[2],
+                      InqState{this->inq_iterations_, this->selection_algorithm_, this->seed_, this->num_bits_,
+                               this->minibatch_counter_, this->rgen_, this->rdist_, this->old_weights_,
+                               this->old_indicators_},
+                      "INQConvolution");
+    if (in.size() == 4)
+      this->convolution_->forward(Variables{in[0], in[1], in[3]}, out);
+    else
+      this->convolution_->forward(Variables{in[0], in[1]}, out);
     this->minibatch_counter_++;
   }
 };
@@ -1140,6 +1178,9 @@ void init_b200() {
   {
     using INQAffine_b200 = INQAffineB200<float, int>;
     NBLA_REGISTER_FUNCTION_IMPL(INQAffine, INQAffine_b200, "b200:float", int, int, ivec, const string &, int);
+    using INQConvolution_b200 = INQConvolutionB200<float, int>;
+    NBLA_REGISTER_FUNCTION_IMPL(INQConvolution, INQConvolution_b200, "b200:float", int, ivec, ivec, ivec, int, int,
+                                ivec, const string &, int);
   }
 }
 

@@ -804,6 +804,16 @@ def inq_affine(x, weight, indicator_fixedweights, bias=None, base_axis=1, num_bi
     return affine(x, weight, bias, base_axis)
 
 
+def inq_convolution(x, weight, indicator_fixedweights, bias=None, base_axis=1, pad=None, stride=None, dilation=None,
+                    group=1, num_bits=4, inq_iterations=(), selection_algorithm="largest_abs", seed=-1, state=None):
+    """INQ Convolution (src/nbla/function/generic/inq_convolution.cpp:86-204): INQAffine's weight update, in
+    place, then the convolution."""
+    if state is None:
+        raise RuntimeError("inq_convolution needs the INQState of its layer (the reference keeps it in the function)")
+    inq_update_weights(weight, indicator_fixedweights, state, num_bits, inq_iterations, selection_algorithm)
+    return convolution(x, weight, bias, base_axis, pad, stride, dilation, group)
+
+
 def _grad_out(like, accum, dx):
     if dx is None:
         if accum:

@@ -541,3 +541,10 @@ def inq_affine(x, w, ind, b, state, base_axis=1, num_bits=4, inq_iterations=(), 
     """INQAffine forward: returns (y, weights after, indicators after)."""
     w2, ind2 = inq_update(w, ind, state, num_bits, inq_iterations, selection_algorithm, draws)
     return affine(x, w2, b, base_axis), w2, ind2
+
+
+def inq_convolution(x, w, ind, b, state, pad=(0, 0), stride=(1, 1), dilation=(1, 1), group=1, num_bits=4,
+                    inq_iterations=(), selection_algorithm="largest_abs", draws=None):
+    """INQConvolution forward (inq_convolution.cpp:86-204, the same update around Convolution)."""
+    w2, ind2 = inq_update(w, ind, state, num_bits, inq_iterations, selection_algorithm, draws)
+    return convolution(x, w2, b, pad, stride, dilation, group), w2, ind2

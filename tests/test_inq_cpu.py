@@ -31,6 +31,20 @@ def test_inq_affine_largest_abs(i):
         assert np.array_equal(np.exp2(np.round(np.log2(nz))), nz)
 
 
+@pytest.mark.parametrize("i", range(len(inq_cases.CONV_CASES)))
+def test_inq_convolution_largest_abs(i):
+    x, w, ind, b, pad, stride, dilation, group, nbits, its, passes = inq_cases.conv_inputs(i)
+    outs, ins, _ = ref.forward("INQConvolution", [1, group, nbits, 0, 7], [list(pad), list(stride), list(dilation), its],
+                               [x, w, ind, b], repeat=passes)
+    st = oracle.INQState(w.shape)
+    ww, ii = w, ind.astype(np.int32)
+    for _ in range(passes):
+        y, ww, ii = oracle.inq_convolution(x, ww, ii, b, st, pad, stride, dilation, group, nbits, its)
+    assert np.array_equal(bits(ins[1]), bits(ww))
+    assert np.array_equal(ins[2].astype(np.int32), ii)
+    assert np.allclose(outs[0], y, rtol=1e-4, atol=1e-4 * float(np.abs(y).max()))
+
+
 def test_exponent_rule_is_one_step_per_binade():
     """floor(log2 a) + (log2 a - floor >= log2 1.5) with a float logarithm: inside every binade the result is e
     below some mantissa and e + 1 from it on (where exactly depends on how log2f rounds at that magnitude,

@@ -1,4 +1,4 @@
-"""INQAffine on the GPU: the C-ABI weight update (nb200_inq_restore_f32 / nb200_inq_quantize_f32 through
+"""INQAffine / INQConvolution on the GPU: the C-ABI weight update (nb200_inq_restore_f32 / nb200_inq_quantize_f32 through
 nnabla_b200.functions.inq_affine) against the oracle over several forward passes, and the extension class
 against nnabla's own CPU function through Function::forward (largest-magnitude and random selection)."""
 import numpy as np
@@ -78,4 +78,35 @@ def test_inq_affine_extension_against_cpu_context(i, algorithm):
     assert c[2] == g[2] == "INQAffine"
     assert np.array_equal(bits(g[1][1]), bits(c[1][1]))        # weights after
     assert np.array_equal(g[1][2], c[1][2])                    # indicators after
+    assert close_to_rms(g[0][0], c[0][0])
+
+
+@pytest.mark.parametrize("i", range(len(inq_cases.CONV_CASES)))
+def test_inq_convolution_mirror_against_oracle(F, i):
+    x, w, ind, b, pad, stride, dilation, group, nbits, its, passes = inq_cases.conv_inputs(i)
+    st = oracle.INQState(w.shape)
+    ww, ii = w, ind.astype(np.int32)
+    gw, gi = dev(w), dev(ind, np.int32)
+    gst = F.INQState(gw)
+    for _ in range(passes):
+        y, ww, ii = oracle.inq_convolution(x, ww, ii, b, st, pad, stride, dilation, group, nbits, its)
+        gy = F.inq_convolution(dev(x), gw, gi, dev(b), 1, pad, stride, dilation, group, nbits, its, "largest_abs", -1,
+                               gst)
+        F.check_device_status()
+        assert np.array_equal(bits(gw.cpu().numpy()), bits(ww))
+        assert np.array_equal(gi.cpu().numpy(), ii)
+        assert close_to_rms(gy.cpu().numpy(), y)
+
+
+@pytest.mark.parametrize("i", range(len(inq_cases.CONV_CASES)))
+@pytest.mark.parametrize("algorithm", [0, 1])
+def test_inq_convolution_extension_against_cpu_context(i, algorithm):
+    x, w, ind, b, pad, stride, dilation, group, nbits, its, passes = inq_cases.conv_inputs(i)
+    args = ("INQConvolution", [1, group, nbits, algorithm, 5 + i], [list(pad), list(stride), list(dilation), its],
+            [x, w, ind, b])
+    c = H.forward("cpu:float", *args, repeat=passes)
+    g = H.forward("b200:float", *args, repeat=passes)
+    assert c[2] == g[2] == "INQConvolution"
+    assert np.array_equal(bits(g[1][1]), bits(c[1][1]))
+    assert np.array_equal(g[1][2], c[1][2])
     assert close_to_rms(g[0][0], c[0][0])
