@@ -759,11 +759,20 @@ protected:
     const bool has_b = in.size() == 3;
     if (!(pd[0] || pd[1] || (has_b && pd[2])))
       return;
-    NBLA_CHECK(!pd[0], error_code::not_implemented,
-               "the b200 backend does not compute the input gradient of a full-precision Convolution");
     B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_);
     const float *dy = out[0]->get_grad_pointer<float>(this->ctx_);
+    if (pd[0]) {
+      const float *w = rd(in[1], this->ctx_);
+      float *dx = grad_wr(in[0], this->ctx_, true, accum[0]);
+      nb200_check(nb200_convolution_input_backward_f32(w, dy, dx, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw,
+                                                       this->pad_[0], this->pad_[1], this->stride_[0], this->stride_[1],
+                                                       this->dilation_[0], this->dilation_[1], this->group_, accum[0],
+                                                       st),
+                  "Convolution backward (input)");
+    }
+    if (!(pd[1] || (has_b && pd[2])))
+      return;
     float *dw = grad_wr(in[1], this->ctx_, pd[1], accum[1]);
     float *db = has_b ? grad_wr(in[2], this->ctx_, pd[2], accum[2]) : nullptr;
     nb200_check(nb200_convolution_backward_f32(x, dy, dw, db, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw,

@@ -370,6 +370,13 @@ int nb200_convolution_backward_f32(const float *x, const float *dy, float *dw, f
                                    int height, int width, int outmaps, int kernel_h, int kernel_w, int pad_h,
                                    int pad_w, int stride_h, int stride_w, int dilation_h, int dilation_w, int group,
                                    int accum_dw, int accum_db, void *stream);
+/* Its gradient w.r.t. x (convolution.cpp:236-262): dx (+)= transposed convolution of dy with w, both operands in
+ * three bf16 pieces on the tensor cores (the products that matter at fp32 resolution). Images up to 128 pixels
+ * wide. */
+int nb200_convolution_input_backward_f32(const float *w, const float *dy, float *dx, int batch, int channels, int height,
+                                         int width, int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w,
+                                         int stride_h, int stride_w, int dilation_h, int dilation_w, int group,
+                                         int accum_dx, void *stream);
 
 /* ---- quantizer backward passes (straight-through estimators) -------------------
  * dx (+)= gradient for n elements; accum != 0 adds to dx (elements that pass no

@@ -286,8 +286,10 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
 //       output is the kh x kw filter window. One launch per group.
 //  db = sums of dy over batch and pixels.
 // ---------------------------------------------------------------------------
+// full_precision: the weights are arbitrary fp32 values (three bf16 pieces, the products that matter at fp32
+// resolution) instead of values exact in one bf16 piece
 int conv_input_grad(const float *wb, const float *alpha, const float *dy, float *dx, const ConvGeometry &g,
-                    int accum, cudaStream_t st) {
+                    int accum, cudaStream_t st, bool full_precision = false) {
   // geometry of the equivalent forward convolution
   ConvGeometry b = g;
   b.C = g.Ko;
@@ -304,7 +306,7 @@ int conv_input_grad(const float *wb, const float *alpha, const float *dy, float 
   NB_CHECK(b.Wo <= 128, NB200_ENOTIMPL, "input gradient for images wider than 128 pixels (W=%d) is not supported",
            b.Wo);
   const int k_pad_g = (int)round_up(b.Cg, 16);
-  const bool narrow_rows = k_pad_g * 2 <= 64;
+  const bool narrow_rows = !full_precision && k_pad_g * 2 <= 64; // the three-piece kernel has 128-byte rows only
   const int E = (narrow_rows ? 64 : kRowBytes) / 2;
   const int cblocks = (k_pad_g + E - 1) / E;
   const int k_slots = cblocks * E;
@@ -314,7 +316,7 @@ int conv_input_grad(const float *wb, const float *alpha, const float *dy, float 
   const int taps = g.kh * g.kw;
   const int64_t wpitch = (int64_t)taps * k_slots;
   const size_t act_bytes = (size_t)3 * g.N * b.H * b.W * ctot * 2;
-  const size_t side_bytes = (size_t)g.C * wpitch * 2;
+  const size_t side_bytes = (size_t)(full_precision ? 3 : 1) * g.C * wpitch * 2;
   AsyncScratch scratch(st);
   NB_TRY(scratch.alloc(round_up(act_bytes, 1024) + round_up(side_bytes, 1024)));
   uint8_t *act = static_cast<uint8_t *>(scratch.p);
@@ -322,12 +324,17 @@ int conv_input_grad(const float *wb, const float *alpha, const float *dy, float 
   NB_CUDA(cudaMemsetAsync(act, 0, round_up(act_bytes, 1024) + side_bytes, st));
   NB_TRY(dy_to_nhwc_stuffed(dy, g.N, g.Ko, g.Ho, g.Wo, g.group, g.Kog, k_pad_g, (int)ctot, b.H, b.W, g.sh, g.sw, alpha,
                             act, st));
-  NB_TRY(flip_transpose_weights(wb, g.Ko, g.Cg, g.kh, g.kw, g.group, k_slots, side, st));
+  NB_TRY(flip_transpose_weights(wb, g.Ko, g.Cg, g.kh, g.kw, g.group, k_slots, side, st, full_precision ? 3 : 1));
   GemmEpilogue ep{};
   ep.y = dx;
   ep.scale = 1.0f;
   ep.accumulate = accum;
   int h_box, n_box;
+  if (full_precision) {
+    plan_box(b, 64, h_box, n_box);
+    return launch_conv<false, 3, 3, 64, 2, kRowBytes, 1>(b, act, 3, ctot, side, wpitch, k_pad_g, cblocks, h_box, n_box,
+                                                         ep, st);
+  }
   plan_box(b, 128, h_box, n_box);
   if (narrow_rows)
     return launch_conv<false, 1, 3, 128, 6, 64>(b, act, 3, ctot, side, wpitch, k_pad_g, cblocks, h_box, n_box, ep, st);
@@ -408,12 +415,12 @@ int conv_weight_grad(const float *x, const float *dy, float *dw, const ConvGeome
 
 int convolution_backward(const float *x, const float *w_exact, const float *alpha, const float *dy, float *dx,
                          float *dw, float *db, ConvGeometry g, int accum_dx, int accum_dw, int accum_db,
-                         float act_delta, cudaStream_t st) {
+                         float act_delta, cudaStream_t st, bool full_precision_weights = false) {
   NB_TRY(check_geometry(g));
   NB_CHECK(dy != nullptr, NB200_EVALUE, "dy is NULL");
   if (dx) {
-    NB_CHECK(w_exact != nullptr, NB200_EVALUE, "the gradient w.r.t. x needs the binary weights");
-    NB_TRY(conv_input_grad(w_exact, alpha, dy, dx, g, accum_dx, st));
+    NB_CHECK(w_exact != nullptr, NB200_EVALUE, "the gradient w.r.t. x needs the weights");
+    NB_TRY(conv_input_grad(w_exact, alpha, dy, dx, g, accum_dx, st, full_precision_weights));
   }
   if (dw) {
     NB_CHECK(x != nullptr, NB200_EVALUE, "the gradient w.r.t. the weights needs x");
@@ -811,6 +818,17 @@ int nb200_convolution_backward_f32(const float *x, const float *dy, float *dw, f
                  dilation_h, dilation_w, group, 0, 0, 0, 0};
   return convolution_backward(x, nullptr, nullptr, dy, nullptr, dw, db, g, 0, accum_dw, accum_db, 0.0f,
                               as_stream(stream));
+}
+
+int nb200_convolution_input_backward_f32(const float *w, const float *dy, float *dx, int batch, int channels, int height,
+                                         int width, int outmaps, int kernel_h, int kernel_w, int pad_h, int pad_w,
+                                         int stride_h, int stride_w, int dilation_h, int dilation_w, int group,
+                                         int accum_dx, void *stream) {
+  NB_CHECK(w && dx, NB200_EVALUE, "null data pointer");
+  ConvGeometry g{batch, channels, height, width, outmaps, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w,
+                 dilation_h, dilation_w, group, 0, 0, 0, 0};
+  return convolution_backward(nullptr, w, nullptr, dy, dx, nullptr, nullptr, g, accum_dx, 0, 0, 0.0f,
+                              as_stream(stream), true);
 }
 
 int nb200_convolution_fxp8_f32(const float *xq, const float *wq, float delta_x, float delta_w, const float *bias,

@@ -56,9 +56,10 @@ int codes_rows_i8(const float *x, int64_t rows, int K, int64_t pitch, float delt
 // multiplied by chan_scale[o] first when given.
 int dy_to_nhwc_stuffed(const float *dy, int N, int Ko, int Ho, int Wo, int groups, int Kog, int k_pad_g, int ctot,
                        int Hs, int Ws, int sh, int sw, const float *chan_scale, void *out, cudaStream_t st);
-// wb [Ko][Cg][kh][kw] -> side [C][kh * kw][k_slots] bf16 (pre-zeroed), taps flipped, maps innermost.
+// wb [Ko][Cg][kh][kw] -> side [planes][C][kh * kw][k_slots] bf16 (pre-zeroed), taps flipped, maps innermost;
+// planes = 1 for weights exact in bf16, 3 for full-precision weights (hi, mid, lo pieces).
 int flip_transpose_weights(const float *wb, int Ko, int Cg, int kh, int kw, int groups, int k_slots, void *side,
-                           cudaStream_t st);
+                           cudaStream_t st, int planes = 1);
 // N rows of R fp32 values (rows src_row_stride apart) -> bf16 [planes][R][Np] (pre-zeroed), batch innermost.
 int batch_to_inner(const float *src, int N, int64_t R, int64_t src_row_stride, int Np, int planes, void *out,
                    cudaStream_t st);

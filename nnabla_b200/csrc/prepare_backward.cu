@@ -66,10 +66,12 @@ __global__ void __launch_bounds__(256) dy_to_nhwc_stuffed_kernel(const float *__
   }
 }
 
-// wb [Ko][Cg][kh][kw] fp32 (values exact in bf16) -> side [C][kh * kw][k_slots] bf16:
-// side[g * Cg + c][ky * kw + kx][o] = wb[g * Kog + o][c][kh - 1 - ky][kw - 1 - kx].
+// wb [Ko][Cg][kh][kw] fp32 -> side [planes][C][kh * kw][k_slots] bf16:
+// side[g * Cg + c][ky * kw + kx][o] = wb[g * Kog + o][c][kh - 1 - ky][kw - 1 - kx]; one plane for values
+// exact in bf16 (binary weights), three (hi, mid, lo) for full-precision weights.
+template <int PLANES>
 __global__ void flip_transpose_weights_kernel(const float *__restrict__ wb, int Ko, int Cg, int kh, int kw, int Kog,
-                                              int k_slots, __nv_bfloat16 *__restrict__ side) {
+                                              int k_slots, __nv_bfloat16 *__restrict__ side, int64_t plane_stride) {
   const int taps = kh * kw;
   const int64_t total = (int64_t)Ko * Cg * taps;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -79,7 +81,16 @@ __global__ void flip_transpose_weights_kernel(const float *__restrict__ wb, int 
     const int g = o / Kog, oo = o - g * Kog;
     const int ky = t / kw, kx = t - ky * kw;
     const int tf = (kh - 1 - ky) * kw + (kw - 1 - kx);
-    side[((int64_t)(g * Cg + c) * taps + tf) * k_slots + oo] = __float2bfloat16_rn(wb[i]);
+    const int64_t dst = ((int64_t)(g * Cg + c) * taps + tf) * k_slots + oo;
+    if (PLANES == 1) {
+      side[dst] = __float2bfloat16_rn(wb[i]);
+    } else {
+      __nv_bfloat16 h, m, l;
+      split3(wb[i], h, m, l);
+      side[dst] = h;
+      side[dst + plane_stride] = m;
+      side[dst + 2 * plane_stride] = l;
+    }
   }
 }
 
@@ -189,9 +200,14 @@ int dy_to_nhwc_stuffed(const float *dy, int N, int Ko, int Ho, int Wo, int group
 }
 
 int flip_transpose_weights(const float *wb, int Ko, int Cg, int kh, int kw, int groups, int k_slots, void *side,
-                           cudaStream_t st) {
-  flip_transpose_weights_kernel<<<capped((int64_t)Ko * Cg * kh * kw, 256), 256, 0, st>>>(
-      wb, Ko, Cg, kh, kw, Ko / groups, k_slots, reinterpret_cast<__nv_bfloat16 *>(side));
+                           cudaStream_t st, int planes) {
+  const int64_t plane_stride = (int64_t)groups * Cg * kh * kw * k_slots;
+  if (planes == 3)
+    flip_transpose_weights_kernel<3><<<capped((int64_t)Ko * Cg * kh * kw, 256), 256, 0, st>>>(
+        wb, Ko, Cg, kh, kw, Ko / groups, k_slots, reinterpret_cast<__nv_bfloat16 *>(side), plane_stride);
+  else
+    flip_transpose_weights_kernel<1><<<capped((int64_t)Ko * Cg * kh * kw, 256), 256, 0, st>>>(
+        wb, Ko, Cg, kh, kw, Ko / groups, k_slots, reinterpret_cast<__nv_bfloat16 *>(side), plane_stride);
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }

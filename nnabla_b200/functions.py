@@ -574,30 +574,38 @@ def binary_connect_convolution_backward(x, binary_weight, dy, base_axis=1, pad=N
 
 
 def convolution_backward(x, weight_shape, dy, base_axis=1, pad=None, stride=None, dilation=None, group=1,
-                         propagate_down=(False, True, True), accum=(False, False, False), grads=(None, None, None)):
-    """Weight and bias gradients of the full-precision convolution
+                         propagate_down=(False, True, True), accum=(False, False, False), grads=(None, None, None),
+                         weight=None):
+    """Gradients of the full-precision convolution
     (Convolution::backward_impl, src/nbla/function/generic/convolution.cpp:199-300).
-    Returns (None, dw, db): the gradient w.r.t. x is not provided."""
-    if propagate_down[0]:
-        raise C.NB200Error(4, "the gradient w.r.t. the input of a full-precision convolution is not implemented")
+    Returns (dx, dw, db), None where propagate_down is False; dx needs `weight`."""
     x, dy = _check_input(x), _check_input(dy, "dy")
+    if weight is not None:
+        weight_shape = tuple(_check_input(weight, "weight").shape)
+    elif propagate_down[0]:
+        raise RuntimeError("the gradient w.r.t. x needs the weights (weight=)")
     w_like = torch.empty(tuple(weight_shape), device="meta")
     batch, Cin, H, W, Ko, kh, kw, pad, stride, dilation, out_shape = _conv_geometry(
         x, w_like, None, base_axis, pad, stride, dilation, group)
     if tuple(dy.shape) != tuple(out_shape):
         raise RuntimeError("dy must have the output's shape")
-    out = [None]
-    for g, shape, pd, ac in zip(grads[1:], (tuple(weight_shape), (Ko,)), propagate_down[1:], accum[1:]):
+    out = []
+    for g, shape, pd, ac in zip(grads, (tuple(x.shape), tuple(weight_shape), (Ko,)), propagate_down, accum):
         if pd and g is None:
             if ac:
                 raise RuntimeError("accum=True needs the gradient buffer to accumulate into")
             g = torch.empty(shape, dtype=torch.float32, device=x.device)
-        out.append(g)
+        out.append(g if pd else None)
     with C.on_device(x.device):
-        C.call("nb200_convolution_backward_f32", C.ptr(x), C.ptr(dy), C.ptr(out[1]) if propagate_down[1] else
-               ctypes.c_void_p(0), C.ptr(out[2]) if propagate_down[2] else ctypes.c_void_p(0), batch, Cin, H, W, Ko,
-               kh, kw, int(pad[0]), int(pad[1]), int(stride[0]), int(stride[1]), int(dilation[0]), int(dilation[1]),
-               int(group), int(bool(accum[1])), int(bool(accum[2])), C.stream_ptr(x.device))
+        if propagate_down[0]:
+            C.call("nb200_convolution_input_backward_f32", C.ptr(weight), C.ptr(dy), C.ptr(out[0]), batch, Cin, H, W, Ko,
+                   kh, kw, int(pad[0]), int(pad[1]), int(stride[0]), int(stride[1]), int(dilation[0]),
+                   int(dilation[1]), int(group), int(bool(accum[0])), C.stream_ptr(x.device))
+        if propagate_down[1] or propagate_down[2]:
+            C.call("nb200_convolution_backward_f32", C.ptr(x), C.ptr(dy), C.ptr(out[1]) if propagate_down[1] else
+                   ctypes.c_void_p(0), C.ptr(out[2]) if propagate_down[2] else ctypes.c_void_p(0), batch, Cin, H, W, Ko,
+                   kh, kw, int(pad[0]), int(pad[1]), int(stride[0]), int(stride[1]), int(dilation[0]),
+                   int(dilation[1]), int(group), int(bool(accum[1])), int(bool(accum[2])), C.stream_ptr(x.device))
     return tuple(out)
 
 

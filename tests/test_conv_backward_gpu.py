@@ -121,3 +121,19 @@ def test_full_precision_convolution_weight_gradient(F, xs, ws, pad, stride, accu
         assert cases.rel_rms(got[k].cpu().numpy(), exact[k]) < TOL
     with pytest.raises(RuntimeError):
         F.convolution_backward(dev(x), ws, dev(dy), 1, pad, stride, propagate_down=(True, True, True))
+
+
+@pytest.mark.parametrize("xs,ws,pad,stride,dil,grp", BACKWARD_CASES)
+@pytest.mark.parametrize("accum", [False, True])
+def test_full_precision_convolution_input_gradient(F, xs, ws, pad, stride, dil, grp, accum):
+    """dx of the full-precision Convolution (arbitrary fp32 weights, three bf16 pieces each side)."""
+    x, w, b, dy, g0 = grad_case(xs, ws, pad, stride, dil)
+    pd, ac = (True, False, False), (accum, False, False)
+    got = F.convolution_backward(dev(x), ws, dev(dy), 1, pad, stride, dil, grp, propagate_down=pd, accum=ac,
+                                 grads=[dev(g0[0]), None, None], weight=dev(w))
+    F.check_device_status()
+    assert got[1] is None and got[2] is None
+    want = oracle.convolution_backward(x, w, dy, pad, stride, dil, grp, propagate_down=pd, accum=ac, grads=g0)
+    exact = oracle.convolution_backward(x, w, dy, pad, stride, dil, grp, propagate_down=pd, accum=ac, grads=g0, f64=True)
+    assert cases.rel_rms(got[0].cpu().numpy(), want[0]) < TOL
+    assert cases.rel_rms(got[0].cpu().numpy(), exact[0]) < TOL

@@ -157,16 +157,19 @@ def test_companions_training_side():
             cb, gb = H.backward(CPU, *args), H.backward(B200, *args)
             for k in range(len(ins)):
                 assert np.array_equal(bits(gb[0][k]), bits(cb[0][k])), (op, accum, k)
-    # full-precision convolution: weight and bias gradients (the input gradient is not provided)
+    # full-precision convolution: input, weight and bias gradients
     xs = rng.randn(2, 3, 20, 20).astype(np.float32)
     ws = rng.randn(8, 3, 7, 7).astype(np.float32)
     bs = rng.randn(8).astype(np.float32)
     gy = rng.randn(2, 8, 10, 10).astype(np.float32)
-    g0 = [np.zeros_like(xs), rng.randn(*ws.shape).astype(np.float32), rng.randn(8).astype(np.float32)]
-    args = ("Convolution", [1, 1, False], [(3, 3), (2, 2), (1, 1)], [xs, ws, bs], [gy], [False, True, True],
-            [False, True, True], g0)
-    cb, gb = H.backward(CPU, *args), H.backward(B200, *args)
-    assert cases.rel_rms(gb[0][1], cb[0][1]) < 1e-5 and cases.rel_rms(gb[0][2], cb[0][2]) < 1e-5
+    g0 = [rng.randn(*xs.shape).astype(np.float32), rng.randn(*ws.shape).astype(np.float32),
+          rng.randn(8).astype(np.float32)]
+    for accum in (True, False):
+        args = ("Convolution", [1, 1, False], [(3, 3), (2, 2), (1, 1)], [xs, ws, bs], [gy], [True, True, True],
+                [accum] * 3, g0)
+        cb, gb = H.backward(CPU, *args), H.backward(B200, *args)
+        for k in range(3):
+            assert cases.rel_rms(gb[0][k], cb[0][k]) < 1e-5, (accum, k)
 
 
 def test_half_type_config_resolves_to_the_float_implementations():

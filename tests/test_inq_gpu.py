@@ -110,3 +110,28 @@ def test_inq_convolution_extension_against_cpu_context(i, algorithm):
     assert np.array_equal(bits(g[1][1]), bits(c[1][1]))
     assert np.array_equal(g[1][2], c[1][2])
     assert close_to_rms(g[0][0], c[0][0])
+
+
+def test_inq_backward_goes_through_the_inner_function():
+    """INQAffine / INQConvolution::backward_impl hand the gradients to the inner Affine / Convolution
+    (inq_affine.cpp:218-232, inq_convolution.cpp:222-237), which under this context are the device ones."""
+    import cases
+    x, w, ind, b, nbits, its, _ = inq_cases.inputs(3)
+    rng = np.random.RandomState(3)
+    gy = rng.randn(x.shape[0], w.shape[1]).astype(np.float32)
+    g0 = [rng.randn(*a.shape).astype(np.float32) for a in (x, w, ind, b)]
+    for accum in (False, True):
+        args = ("INQAffine", [1, nbits, 0, 3], [its], [x, w, ind, b], [gy], [True, True, False, True], [accum] * 4, g0)
+        c, g = H.backward("cpu:float", *args), H.backward("b200:float", *args)
+        for k in (0, 1, 3):
+            assert cases.rel_rms(g[0][k], c[0][k]) < 1e-5, (accum, k)
+    x, w, ind, b, pad, stride, dilation, group, nbits, its, _ = inq_cases.conv_inputs(0)
+    y_shape = oracle.conv_out_shape(x.shape, w.shape, pad, stride, dilation)
+    gy = rng.randn(*y_shape).astype(np.float32)
+    g0 = [rng.randn(*a.shape).astype(np.float32) for a in (x, w, ind, b)]
+    for accum in (False, True):
+        args = ("INQConvolution", [1, group, nbits, 0, 3], [list(pad), list(stride), list(dilation), its],
+                [x, w, ind, b], [gy], [True, True, False, True], [accum] * 4, g0)
+        c, g = H.backward("cpu:float", *args), H.backward("b200:float", *args)
+        for k in (0, 1, 3):
+            assert cases.rel_rms(g[0][k], c[0][k]) < 1e-5, (accum, k)
