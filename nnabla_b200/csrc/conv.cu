@@ -195,12 +195,18 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
                                 : static_cast<uint8_t *>(scratch.p) + round_up(act_bytes, 1024);
   NB_CHECK(((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(side)) & 15) == 0, NB200_EVALUE,
            "activation codes and prepared weights must be 16-byte aligned");
+  bool operands_done = false;
   if (!prepared_side) {
     if (c_slots != g.Cg)
       NB_CUDA(cudaMemsetAsync(side, 0, side_bytes, st));
     if (fxp_weights)
       NB_TRY(codes_conv_weights(w, g.Ko, g.Cg, g.kh, g.kw, weight_delta, side, wpitch, c_slots, st));
-    else
+    else if (int8 && !x_codes && binary_conv_operands_i8_applies(x, g.N, g.H * g.W, (int)ctot, g.Ko)) {
+      // weights and activations in one launch
+      NB_TRY(binary_conv_operands_i8(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, x, g.N, g.C,
+                                     g.H * g.W, g.group, c_pad_g, (int)ctot, act_delta, scratch.p, st));
+      operands_done = true;
+    } else
       NB_TRY(binarize_rows(w, g.Ko, g.Cg, g.kh, g.kw, zero_to, wb, alpha, side, wpitch, c_slots, int8, st, half_pair));
   }
   float *row_scale_half = nullptr;
@@ -209,7 +215,7 @@ int binary_convolution(const float *x, const float *w, float *wb, float *alpha, 
     row_scale_half = reinterpret_cast<float *>(extra + 16);
     NB_TRY(nchw_to_nhwc_half_pair(x, g.N, g.C, g.H * g.W, g.group, g.Cg, c_pad_g, (int)ctot, scratch.p,
                                   reinterpret_cast<uint32_t *>(extra), alpha, g.Ko, row_scale_half, st));
-  } else if (!x_codes)
+  } else if (!x_codes && !operands_done)
     NB_TRY(nchw_to_nhwc_planes(x, g.N, g.C, g.H * g.W, g.group, g.Cg, c_pad_g, (int)ctot, int8 ? 0 : 3, act_delta,
                                static_cast<uint8_t *>(scratch.p), st));
   GemmEpilogue ep{};

@@ -153,13 +153,10 @@ __global__ void finalize_alpha_kernel(const float *__restrict__ partial, int blo
 // ---------------------------------------------------------------------------
 // kMode: 0 = bf16 signs, 1 = int8 signs, 2 = fp16 signs.
 template <int kMode>
-__global__ void __launch_bounds__(256) binarize_rows_kernel(const float *__restrict__ w, int Cg, int kh, int kw,
-                                                            float zero_to, float inv, float *__restrict__ wb,
-                                                            float *__restrict__ alpha, void *__restrict__ side,
-                                                            int64_t side_pitch, int c_pad) {
-  pdl_wait();
-  pdl_trigger();
-  const int o = blockIdx.x;
+__device__ __forceinline__ void binarize_row(int o, const float *__restrict__ w, int Cg, int kh, int kw,
+                                             float zero_to, float inv, float *__restrict__ wb,
+                                             float *__restrict__ alpha, void *__restrict__ side, int64_t side_pitch,
+                                             int c_pad) {
   const int taps = kh * kw, Kd = Cg * taps;
   const float *wr = w + (int64_t)o * Kd;
   float acc = 0.0f;
@@ -193,6 +190,16 @@ __global__ void __launch_bounds__(256) binarize_rows_kernel(const float *__restr
       s += s_part[i];
     alpha[o] = __fmul_rn(s, inv);
   }
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(256) binarize_rows_kernel(const float *__restrict__ w, int Cg, int kh, int kw,
+                                                            float zero_to, float inv, float *__restrict__ wb,
+                                                            float *__restrict__ alpha, void *__restrict__ side,
+                                                            int64_t side_pitch, int c_pad) {
+  pdl_wait();
+  pdl_trigger();
+  binarize_row<kMode>(blockIdx.x, w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
 }
 
 // Fixed-point convolution weights: wq [Ko, Cg, kh, kw] holds multiples of delta
@@ -351,16 +358,12 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_i8_kernel(const float *__res
 
 // Same conversion with 128-bit loads (HW a multiple of 4): every thread has
 // four independent float4 loads in flight (4 pixels x 4 channel rows).
-__global__ void __launch_bounds__(256) nchw_to_nhwc_i8_vec_kernel(const float *__restrict__ x, int C, int HW,
-                                                                  int groups, int Cg, int c_pad_g, int ctot,
-                                                                  int8_t *__restrict__ out, float inv_delta) {
+__device__ __forceinline__ void nchw_to_nhwc_i8_vec_tile(int bx, int by, int n, const float *__restrict__ x, int C,
+                                                         int HW, int groups, int Cg, int c_pad_g, int ctot,
+                                                         int8_t *__restrict__ out, float inv_delta) {
   __shared__ uint32_t tile[64][17];
-  pdl_wait();
-  pdl_trigger();
-
   int8_t *tile8 = reinterpret_cast<int8_t *>(&tile[0][0]);
-  const int n = blockIdx.z;
-  const int p0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  const int p0 = bx * 64, d0 = by * 64;
   const int px4 = threadIdx.x & 15, ch = threadIdx.x >> 4; // 16 pixel quads x 16 channel rows
   const int p = p0 + 4 * px4;
   float4 v[4];
@@ -388,6 +391,35 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_i8_vec_kernel(const float *_
     if (pix < HW && d < ctot)
       *reinterpret_cast<uint32_t *>(out + ((int64_t)n * HW + pix) * ctot + d) = tile[pp][word];
   }
+}
+
+__global__ void __launch_bounds__(256) nchw_to_nhwc_i8_vec_kernel(const float *__restrict__ x, int C, int HW,
+                                                                  int groups, int Cg, int c_pad_g, int ctot,
+                                                                  int8_t *__restrict__ out, float inv_delta) {
+  pdl_wait();
+  pdl_trigger();
+  nchw_to_nhwc_i8_vec_tile(blockIdx.x, blockIdx.y, blockIdx.z, x, C, HW, groups, Cg, c_pad_g, ctot, out, inv_delta);
+}
+
+// Both operands of a binary-weight convolution over fixed-point activations in one launch: blocks
+// [0, Ko) binarise one filter each (sign, scale, int8 side-band), the others convert one 64 x 64 tile of
+// the activations to channel-last codes. The two jobs are independent, and at a few dozen images the
+// weights' pass costs as much as the activations': side by side it disappears behind them.
+__global__ void __launch_bounds__(256)
+    binary_conv_operands_i8_kernel(const float *__restrict__ w, int Ko, int Cg_w, int kh, int kw, float zero_to, float inv,
+                                   float *__restrict__ wb, float *__restrict__ alpha, void *__restrict__ side,
+                                   int64_t side_pitch, int c_pad, const float *__restrict__ x, int C, int HW,
+                                   int groups, int Cg, int c_pad_g, int ctot, int8_t *__restrict__ out,
+                                   float inv_delta, int gx, int gy) {
+  pdl_wait();
+  pdl_trigger();
+  if ((int)blockIdx.x < Ko) {
+    binarize_row<1>(blockIdx.x, w, Cg_w, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
+    return;
+  }
+  const int lin = (int)blockIdx.x - Ko;
+  const int bx = lin % gx, r = lin / gx;
+  nchw_to_nhwc_i8_vec_tile(bx, r % gy, r / gy, x, C, HW, groups, Cg, c_pad_g, ctot, out, inv_delta);
 }
 
 // int8 [R, C] -> [C][pitch] (transpose), tile 64 x 64 through shared memory.
@@ -482,6 +514,25 @@ int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to,
     binarize_rows_kernel<2><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
   else
     binarize_rows_kernel<0><<<Ko, 256, 0, st>>>(w, Cg, kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad);
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
+bool binary_conv_operands_i8_applies(const float *x, int N, int HW, int ctot, int Ko) {
+  const int64_t blocks = (int64_t)Ko + (int64_t)((HW + 63) / 64) * ((ctot + 63) / 64) * N;
+  return HW % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && blocks < (1ll << 31);
+}
+
+int binary_conv_operands_i8(const float *w, int Ko, int Cg, int kh, int kw, float zero_to, float *wb, float *alpha,
+                            void *side, int64_t side_pitch, int c_pad, const float *x, int N, int C, int HW, int groups,
+                            int c_pad_g, int ctot, float delta, void *out, cudaStream_t st) {
+  const float inv = (float)1 / (Cg * kh * kw); // binary_weight_convolution.cpp:66
+  const int gx = (HW + 63) / 64, gy = (ctot + 63) / 64;
+  const int64_t blocks = (int64_t)Ko + (int64_t)gx * gy * N;
+  NB_CHECK(binary_conv_operands_i8_applies(x, N, HW, ctot, Ko), NB200_EVALUE, "operand preparation does not apply");
+  NB_CUDA(launch_dependent(binary_conv_operands_i8_kernel, dim3((unsigned)blocks), dim3(256), 0, st, w, Ko, Cg, kh, kw,
+                           zero_to, inv, wb, alpha, side, side_pitch, c_pad, x, C, HW, groups, Cg, c_pad_g, ctot,
+                           reinterpret_cast<int8_t *>(out), 1.0f / delta, gx, gy));
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }
