@@ -330,13 +330,12 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const float *__restri
 // the codes are transposed through shared memory (row pitch 17 words, so both
 // the byte writes and the word reads are bank-conflict free) and written as
 // 64-byte runs per pixel.
-__global__ void __launch_bounds__(256) nchw_to_nhwc_i8_kernel(const float *__restrict__ x, int C, int HW, int groups,
-                                                              int Cg, int c_pad_g, int ctot,
-                                                              int8_t *__restrict__ out, float inv_delta) {
+__device__ __forceinline__ void nchw_to_nhwc_i8_tile(int bx, int by, int n, const float *__restrict__ x, int C, int HW,
+                                                     int groups, int Cg, int c_pad_g, int ctot,
+                                                     int8_t *__restrict__ out, float inv_delta) {
   __shared__ uint32_t tile[64][17]; // [pixel][16 words of 4 codes + 1 pad]
   int8_t *tile8 = reinterpret_cast<int8_t *>(&tile[0][0]);
-  const int n = blockIdx.z;
-  const int p0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  const int p0 = bx * 64, d0 = by * 64;
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
   const int p = p0 + tx;
   for (int dd = ty; dd < 64; dd += 4) {
@@ -354,6 +353,12 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_i8_kernel(const float *__res
     if (pix < HW && d < ctot)
       *reinterpret_cast<uint32_t *>(out + ((int64_t)n * HW + pix) * ctot + d) = tile[pp][word];
   }
+}
+
+__global__ void __launch_bounds__(256) nchw_to_nhwc_i8_kernel(const float *__restrict__ x, int C, int HW, int groups,
+                                                              int Cg, int c_pad_g, int ctot,
+                                                              int8_t *__restrict__ out, float inv_delta) {
+  nchw_to_nhwc_i8_tile(blockIdx.x, blockIdx.y, blockIdx.z, x, C, HW, groups, Cg, c_pad_g, ctot, out, inv_delta);
 }
 
 // Same conversion with 128-bit loads (HW a multiple of 4): every thread has
@@ -405,6 +410,7 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_i8_vec_kernel(const float *_
 // [0, Ko) binarise one filter each (sign, scale, int8 side-band), the others convert one 64 x 64 tile of
 // the activations to channel-last codes. The two jobs are independent, and at a few dozen images the
 // weights' pass costs as much as the activations': side by side it disappears behind them.
+template <bool kVec>
 __global__ void __launch_bounds__(256)
     binary_conv_operands_i8_kernel(const float *__restrict__ w, int Ko, int Cg_w, int kh, int kw, float zero_to, float inv,
                                    float *__restrict__ wb, float *__restrict__ alpha, void *__restrict__ side,
@@ -419,7 +425,10 @@ __global__ void __launch_bounds__(256)
   }
   const int lin = (int)blockIdx.x - Ko;
   const int bx = lin % gx, r = lin / gx;
-  nchw_to_nhwc_i8_vec_tile(bx, r % gy, r / gy, x, C, HW, groups, Cg, c_pad_g, ctot, out, inv_delta);
+  if (kVec)
+    nchw_to_nhwc_i8_vec_tile(bx, r % gy, r / gy, x, C, HW, groups, Cg, c_pad_g, ctot, out, inv_delta);
+  else
+    nchw_to_nhwc_i8_tile(bx, r % gy, r / gy, x, C, HW, groups, Cg, c_pad_g, ctot, out, inv_delta);
 }
 
 // int8 [R, C] -> [C][pitch] (transpose), tile 64 x 64 through shared memory.
@@ -520,7 +529,7 @@ int binarize_rows(const float *w, int Ko, int Cg, int kh, int kw, float zero_to,
 
 bool binary_conv_operands_i8_applies(const float *x, int N, int HW, int ctot, int Ko) {
   const int64_t blocks = (int64_t)Ko + (int64_t)((HW + 63) / 64) * ((ctot + 63) / 64) * N;
-  return HW % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && blocks < (1ll << 31);
+  return x != nullptr && blocks < (1ll << 31);
 }
 
 int binary_conv_operands_i8(const float *w, int Ko, int Cg, int kh, int kw, float zero_to, float *wb, float *alpha,
@@ -530,9 +539,15 @@ int binary_conv_operands_i8(const float *w, int Ko, int Cg, int kh, int kw, floa
   const int gx = (HW + 63) / 64, gy = (ctot + 63) / 64;
   const int64_t blocks = (int64_t)Ko + (int64_t)gx * gy * N;
   NB_CHECK(binary_conv_operands_i8_applies(x, N, HW, ctot, Ko), NB200_EVALUE, "operand preparation does not apply");
-  NB_CUDA(launch_dependent(binary_conv_operands_i8_kernel, dim3((unsigned)blocks), dim3(256), 0, st, w, Ko, Cg, kh, kw,
-                           zero_to, inv, wb, alpha, side, side_pitch, c_pad, x, C, HW, groups, Cg, c_pad_g, ctot,
-                           reinterpret_cast<int8_t *>(out), 1.0f / delta, gx, gy));
+  // 128-bit loads when the planes allow it (nchw_to_nhwc_planes has the same rule)
+  if (HW % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
+    NB_CUDA(launch_dependent(binary_conv_operands_i8_kernel<true>, dim3((unsigned)blocks), dim3(256), 0, st, w, Ko, Cg,
+                             kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad, x, C, HW, groups, Cg, c_pad_g,
+                             ctot, reinterpret_cast<int8_t *>(out), 1.0f / delta, gx, gy));
+  else
+    NB_CUDA(launch_dependent(binary_conv_operands_i8_kernel<false>, dim3((unsigned)blocks), dim3(256), 0, st, w, Ko, Cg,
+                             kh, kw, zero_to, inv, wb, alpha, side, side_pitch, c_pad, x, C, HW, groups, Cg, c_pad_g,
+                             ctot, reinterpret_cast<int8_t *>(out), 1.0f / delta, gx, gy));
   NB_LAUNCH_CHECK();
   return NB200_OK;
 }

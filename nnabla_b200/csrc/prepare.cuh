@@ -57,7 +57,7 @@ int codes_rows_i8(const float *x, int64_t rows, int K, int64_t pitch, float delt
 int dy_to_nhwc_stuffed(const float *dy, int N, int Ko, int Ho, int Wo, int groups, int Kog, int k_pad_g, int ctot,
                        int Hs, int Ws, int sh, int sw, const float *chan_scale, void *out, cudaStream_t st);
 // binarize_rows (int8 side-band) and the activations' conversion to channel-last int8 codes (nchw_to_nhwc_planes
-// with planes = 0) as ONE launch; applies when the planes' size is a multiple of 4 values and x is 16-byte aligned.
+// with planes = 0) as ONE launch.
 bool binary_conv_operands_i8_applies(const float *x, int N, int HW, int ctot, int Ko);
 int binary_conv_operands_i8(const float *w, int Ko, int Cg, int kh, int kw, float zero_to, float *wb, float *alpha,
                             void *side, int64_t side_pitch, int c_pad, const float *x, int N, int C, int HW, int groups,
