@@ -418,6 +418,13 @@ class FunctionTimer:
         return fam
 
 
+# DRAM bytes of the 19 binary-weight convolutions of one pass at 256 images, from one ncu capture of this file's
+# own command line (dram__bytes_read.sum + dram__bytes_write.sum over their 38 kernels: 2610 MB read, 850 MB
+# written; lines of a result that were still in L2 when its kernel ended are not in the write figure). The
+# tensors of the pass grow in proportion to the images, so other batch sizes scale it.
+NCU_DRAM_BYTES_BINARY_WEIGHT_CONVOLUTIONS_AT_256 = 3460.3e6
+
+
 def function_table(F, params, gz, x, peaks, int8_peak, passes=3):
     """Per-function time table of the as-written graph (each function's calls bracketed by CUDA
     events, averaged over `passes` forward passes) and the roofline entry of the family with the
@@ -460,8 +467,12 @@ def function_table(F, params, gz, x, peaks, int8_peak, passes=3):
     else:
         unit = "TOP/s" if f["kind"] == "int8_ops" else "TFLOP/s"
         ach, peak, bound, work = f["work"] / f["ms"] / 1e9, tensor_peak, "tensor", f["work"]
+    traffic = None
+    if name == "binary_weight_convolution":
+        traffic = NCU_DRAM_BYTES_BINARY_WEIGHT_CONVOLUTIONS_AT_256 * int(x.shape[0]) / 256.0 / (f["calls"] / passes)
     roof = {"bound": bound, "kernel": name, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
-            "traffic": None, "share_of_step": f["ms"] / total, "ms_per_call": per_call_ms,
+            "traffic": traffic, "traffic_note": "bytes per call, ncu capture of one pass at 256 images scaled by images",
+            "share_of_step": f["ms"] / total, "ms_per_call": per_call_ms,
             "algorithmic_work_per_call": work / f["calls"],
             "floors_ms_per_pass": {"hbm": t_hbm / passes, "tensor": t_tensor / passes}}
     # the whole step against the sum of every function's larger floor
