@@ -2,7 +2,7 @@
 
 Same function names, argument order, defaults and parameter names ("W", "Wb",
 "alpha", "b", "beta", "gamma", "mean", "var" under the scopes "bwn_conv",
-"bwn_affine", "bicon_conv", "bicon_affine", "conv", "affine", "bn") as
+"bwn_affine", "bicon_conv", "bicon_affine", "inq_conv", "inq_affine", "conv", "affine", "bn") as
 python/src/nnabla/parametric_functions.py:129, :319-485, :563, :946-1117,
 :1815, so a network definition written against `PF.*` reads the same here.
 Parameters live in a scoped registry like nnabla's (parameter.py:260-355) and
@@ -45,6 +45,7 @@ def get_parameters():
 
 def clear_parameters():
     _parameters.clear()
+    _inq_states.clear()
 
 
 def get_parameter_or_create(name, shape, initializer):
@@ -266,6 +267,50 @@ def pruned_affine(inp, n_outmaps, base_axis=1, w_init=None, b_init=None, fix_par
                 b_q = get_parameter_or_create("b_q", n_outmaps, _zeros)
                 real_b = F.prune(b, rate_b, outputs=[b_q])
     return F.affine(inp, real_w, real_b, base_axis)
+
+
+_inq_states = {}
+
+
+def _inq_layer(scope, shape, init, i_init, b_shape, b_init, with_bias, seed):
+    """Parameters "W", "I" (indicators: 0 learnable, 1 fixed; int32 here, where nnabla stores them as its
+    default float arrays and the function reads them as int) and "b" of an INQ layer, plus the state the
+    reference keeps inside the function instance, kept per scope."""
+    with parameter_scope(scope):
+        w = get_parameter_or_create("W", shape, init)
+        key = "/".join(_scope + ["I"])
+        ind = _parameters.get(key)
+        if ind is None:
+            a = np.zeros(shape) if i_init is None else (i_init(shape) if callable(i_init) else np.asarray(i_init))
+            ind = torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32).reshape(shape)).to(_dev())
+            _parameters[key] = ind
+        b = get_parameter_or_create("b", b_shape, b_init if b_init is not None else _zeros) if with_bias else None
+        state = _inq_states.get(key)
+        if state is None or state.old_weights.shape != w.shape:
+            state = _inq_states[key] = F.INQState(w, seed)
+    return w, ind, b, state
+
+
+def inq_affine(inp, n_outmaps, base_axis=1, num_bits=4, inq_iterations=(), selection_algorithm='random', seed=-1,
+               w_init=None, i_init=None, b_init=None, fix_parameters=False, rng=None, with_bias=True):
+    """python/src/nnabla/parametric_functions.py:493-557 (scope "inq_affine", parameters W, I, b)."""
+    n_outmaps = (n_outmaps,) if isinstance(n_outmaps, int) else tuple(n_outmaps)
+    inmaps = int(np.prod(inp.shape[base_axis:]))
+    init = w_init if w_init is not None else _glorot_uniform(inmaps, int(np.prod(n_outmaps)), (1, 1), _rng(rng))
+    w, ind, b, state = _inq_layer("inq_affine", (inmaps,) + n_outmaps, init, i_init, n_outmaps, b_init, with_bias, seed)
+    return F.inq_affine(inp, w, ind, b, base_axis, num_bits, inq_iterations, selection_algorithm, seed, state)
+
+
+def inq_convolution(inp, outmaps, kernel, pad=None, stride=None, dilation=None, group=1, num_bits=4,
+                    inq_iterations=(), selection_algorithm='random', seed=-1, w_init=None, i_init=None, b_init=None,
+                    base_axis=1, fix_parameters=False, rng=None, with_bias=True):
+    """python/src/nnabla/parametric_functions.py:1126-1196 (scope "inq_conv", parameters W, I, b)."""
+    inmaps = int(inp.shape[base_axis])
+    init = w_init if w_init is not None else _glorot_uniform(inmaps, outmaps, tuple(kernel), _rng(rng))
+    shape = (outmaps, inmaps // group) + tuple(kernel)
+    w, ind, b, state = _inq_layer("inq_conv", shape, init, i_init, (outmaps,), b_init, with_bias, seed)
+    return F.inq_convolution(inp, w, ind, b, base_axis, pad, stride, dilation, group, num_bits, inq_iterations,
+                             selection_algorithm, seed, state)
 
 
 def _constant(value):

@@ -135,3 +135,34 @@ def test_inq_backward_goes_through_the_inner_function():
         c, g = H.backward("cpu:float", *args), H.backward("b200:float", *args)
         for k in (0, 1, 3):
             assert cases.rel_rms(g[0][k], c[0][k]) < 1e-5, (accum, k)
+
+
+def test_parametric_inq_layers(F):
+    """PF.inq_affine / PF.inq_convolution (parametric_functions.py:493, :1126): parameters W, I, b under the
+    scopes "inq_affine" / "inq_conv", the function's state kept with the layer across calls."""
+    from nnabla_b200 import parametric_functions as PF
+    PF.clear_parameters()
+    x, w, ind, b, nbits, its, passes = inq_cases.inputs(3)
+    st = oracle.INQState(w.shape)
+    ww, ii = w, ind.astype(np.int32)
+    for _ in range(passes):
+        y, ww, ii = oracle.inq_affine(x, ww, ii, b, st, 1, nbits, its)
+        with PF.parameter_scope("fc"):
+            gy = PF.inq_affine(dev(x), w.shape[1], 1, nbits, its, "largest_abs", w_init=w, b_init=b)
+        params = PF.get_parameters()
+        assert np.array_equal(bits(params["fc/inq_affine/W"].cpu().numpy()), bits(ww))
+        assert np.array_equal(params["fc/inq_affine/I"].cpu().numpy(), ii)
+        assert close_to_rms(gy.cpu().numpy(), y)
+    x, w, ind, b, pad, stride, dilation, group, nbits, its, passes = inq_cases.conv_inputs(0)
+    st = oracle.INQState(w.shape)
+    ww, ii = w, ind.astype(np.int32)
+    for _ in range(passes):
+        y, ww, ii = oracle.inq_convolution(x, ww, ii, b, st, pad, stride, dilation, group, nbits, its)
+        with PF.parameter_scope("c1"):
+            gy = PF.inq_convolution(dev(x), w.shape[0], w.shape[2:], pad, stride, dilation, group, nbits, its,
+                                    "largest_abs", w_init=w, b_init=b)
+        params = PF.get_parameters()
+        assert np.array_equal(bits(params["c1/inq_conv/W"].cpu().numpy()), bits(ww))
+        assert np.array_equal(params["c1/inq_conv/I"].cpu().numpy(), ii)
+        assert close_to_rms(gy.cpu().numpy(), y)
+    PF.clear_parameters()
