@@ -148,6 +148,22 @@ def _case_bwconv_f32act(batch):
     return make
 
 
+def _case_bwconv_fixed_point_act(batch, C=64, HW=56):
+    """BinaryWeightConvolution as the graph calls it after a FixedPointQuantize: fp32 multiples of 2^-4 in,
+    fp32 out; two kernels (operands in one launch, then the int8 contraction)."""
+    def make():
+        import torch
+        from nnabla_b200 import functions as F
+        torch.manual_seed(0)
+        x = torch.randint(0, 128, (batch, C, HW, HW), device="cuda").float() * 0.0625
+        w = torch.randn(C, C, 3, 3, device="cuda") * (2.0 / (9 * C)) ** 0.5
+        wb, al = torch.zeros_like(w), torch.zeros(C, device="cuda")
+        y = torch.empty(batch, C, HW, HW, device="cuda")
+        return lambda: F.binary_weight_convolution(x, w, wb, al, None, 1, (1, 1), (1, 1), outputs=[y],
+                                                   fixed_point_delta=0.0625)
+    return make
+
+
 def _case_fused_codes_pass(batch):
     def make():
         import torch
@@ -169,6 +185,7 @@ KERNEL_CASES = {
     "quantizer_backward_2p26": _case_quantizer_backward(26),
     "int8_gemm_4096": _case_int8_gemm(4096),
     "bwconv_f32_activations_batch16": _case_bwconv_f32act(16),
+    "bwconv_fixed_point_activations_64_56x56_batch192": _case_bwconv_fixed_point_act(192),
     "fused_codes_pass_batch128": _case_fused_codes_pass(128),
 }
 

@@ -367,27 +367,32 @@ __device__ __forceinline__ void nchw_to_nhwc_i8_vec_tile(int bx, int by, int n, 
                                                          int HW, int groups, int Cg, int c_pad_g, int ctot,
                                                          int8_t *__restrict__ out, float inv_delta) {
   __shared__ uint32_t tile[64][17];
-  int8_t *tile8 = reinterpret_cast<int8_t *>(&tile[0][0]);
   const int p0 = bx * 64, d0 = by * 64;
-  const int px4 = threadIdx.x & 15, ch = threadIdx.x >> 4; // 16 pixel quads x 16 channel rows
+  // 16 pixel quads x 16 channel quads: a thread converts four neighbouring channel slots of four pixels, so
+  // that the four codes of a pixel leave as one word
+  const int px4 = threadIdx.x & 15, chq = threadIdx.x >> 4;
   const int p = p0 + 4 * px4;
-  float4 v[4];
+  const int dq = d0 + 4 * chq;
+  const int g = dq / c_pad_g, cc0 = dq - g * c_pad_g; // c_pad_g is a multiple of 16: one group for the four slots
+  const bool ok = dq < ctot && g < groups && p < HW;
+  const float *base = x + ((int64_t)n * C + (g * Cg + cc0)) * HW + p;
+  // round(v / delta) on the add pipe: for |t| < 2^22 the low mantissa bits of 1.5 * 2^23 + t, rounded to
+  // nearest even by the addition itself, are the two's complement integer (its low byte is the code)
+  uint32_t f[4][4];
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int d = d0 + ch + 16 * r;
-    const int g = d / c_pad_g, cc = d - g * c_pad_g;
-    v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (d < ctot && g < groups && cc < Cg && p < HW)
-      v[r] = __ldcs(reinterpret_cast<const float4 *>(x + ((int64_t)n * C + (g * Cg + cc)) * HW + p));
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ok && cc0 + r < Cg)
+      v = __ldcs(reinterpret_cast<const float4 *>(base + (int64_t)r * HW));
+    f[r][0] = __float_as_uint(__fadd_rn(__fmul_rn(v.x, inv_delta), 12582912.0f));
+    f[r][1] = __float_as_uint(__fadd_rn(__fmul_rn(v.y, inv_delta), 12582912.0f));
+    f[r][2] = __float_as_uint(__fadd_rn(__fmul_rn(v.z, inv_delta), 12582912.0f));
+    f[r][3] = __float_as_uint(__fadd_rn(__fmul_rn(v.w, inv_delta), 12582912.0f));
   }
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const int dd = ch + 16 * r;
-    tile8[(4 * px4 + 0) * 68 + dd] = (int8_t)__float2int_rn(__fmul_rn(v[r].x, inv_delta));
-    tile8[(4 * px4 + 1) * 68 + dd] = (int8_t)__float2int_rn(__fmul_rn(v[r].y, inv_delta));
-    tile8[(4 * px4 + 2) * 68 + dd] = (int8_t)__float2int_rn(__fmul_rn(v[r].z, inv_delta));
-    tile8[(4 * px4 + 3) * 68 + dd] = (int8_t)__float2int_rn(__fmul_rn(v[r].w, inv_delta));
-  }
+  for (int k = 0; k < 4; ++k)
+    tile[4 * px4 + k][chq] = __byte_perm(__byte_perm(f[0][k], f[1][k], 0x0040), __byte_perm(f[2][k], f[3][k], 0x0040),
+                                         0x5410);
   __syncthreads();
   const int word = threadIdx.x & 15, prow = threadIdx.x >> 4;
 #pragma unroll
