@@ -421,15 +421,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           // fp32 [batch][maps][pixels]: the 32 lanes of a store are 32 neighbouring pixels of one map
           const int64_t plane = (int64_t)prob.Ho * prob.Wo;
           float *yp = ep.y_nchw + ((int64_t)img * prob.Ko + col) * plane + in_plane;
+          // all 32 values first, without branches (maps past Ko have scale = bias = 0), then the stores:
+          // with a test per map in between, the maps went through the pipes one after the other
+          float val[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (col + j < prob.Ko) {
-              const float2 k = sb[col + j];
-              float val = __fmul_rn((float)(int)r[j], k.x);
-              if (ep.has_bias)
-                val = __fadd_rn(val, k.y);
-              yp[(int64_t)j * plane] = val;
+          for (int j2 = 0; j2 < 16; ++j2) {
+            const float4 k = sb2[(col >> 1) + j2]; // (scale, bias) of two neighbouring maps
+            val[2 * j2] = __fmul_rn((float)(int)r[2 * j2], k.x);
+            val[2 * j2 + 1] = __fmul_rn((float)(int)r[2 * j2 + 1], k.z);
+            if (ep.has_bias) {
+              val[2 * j2] = __fadd_rn(val[2 * j2], k.y);
+              val[2 * j2 + 1] = __fadd_rn(val[2 * j2 + 1], k.w);
             }
+          }
+          if (col + 32 <= prob.Ko) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              yp[(int64_t)j * plane] = val[j];
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < prob.Ko)
+                yp[(int64_t)j * plane] = val[j];
           }
           continue;
         }
