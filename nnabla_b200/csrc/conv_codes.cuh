@@ -102,6 +102,7 @@ __device__ __forceinline__ uint32_t pack_s8x4(int a, int b, int c, int d) {
 }
 
 constexpr int kCodesMaxMaps = 512;
+constexpr int kCodesKTable = 64; // K blocks whose coordinates are tabulated once per block
 
 // kResidentB: all tiles use the same weights (one column tile) and all their K blocks fit in
 // shared memory beside the ring: the weights are loaded once per CTA and only the activation
@@ -152,6 +153,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   // (scale, bias) of every output map, times out_scale; read as float4 pairs, so 16-byte aligned
   float2 *sb = reinterpret_cast<float2 *>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));
   const float4 *sb2 = reinterpret_cast<const float4 *>(sb);
+  // per K block (filter tap x channel block): x = halo form's operand offset in 16-byte units, y = channel
+  // coordinate, z / w = the tap's column / row shift. One thread issues all copies and all MMAs of a tile;
+  // the two integer divisions per K block that these take cost it more than the instruction they feed.
+  int4 *kb_table = reinterpret_cast<int4 *>(sb + kCodesMaxMaps);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -177,6 +182,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     ptx::prefetch_tensormap(&map_x);
     ptx::prefetch_tensormap(&map_w);
   }
+  auto kb_entry = [&](int kb) {
+    const int tap = kb / prob.cblocks, cb = kb - tap * prob.cblocks;
+    const int ky = tap / prob.kw, kx = tap - ky * prob.kw;
+    return make_int4((cb * prob.a_tile_bytes + (ky * prob.dh * prob.wp + kx * prob.dw) * RB) >> 4, cb * kElems,
+                     kx * prob.dw, ky * prob.dh);
+  };
+  const bool tabulated = k_blocks <= kCodesKTable;
+  for (int kb = threadIdx.x; kb < k_blocks && kb < kCodesKTable; kb += kGemmThreads)
+    kb_table[kb] = kb_entry(kb);
   for (int c = threadIdx.x; c < prob.n_tiles * BN; c += kGemmThreads)
     sb[c] = c < prob.Ko ? make_float2(ep.scale ? __fmul_rn(ep.scale[c], ep.out_scale) : ep.out_scale,
                                       ep.bias ? __fmul_rn(ep.bias[c], ep.bias_scale) : 0.0f)
@@ -242,10 +256,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           uint8_t *st = smem + stage * kStageBytes;
           ptx::mbar_expect_tx(full_bar + stage, tx_bytes);
-          const int tap = kb / prob.cblocks, cb = kb - tap * prob.cblocks;
-          const int ky = tap / prob.kw, kx = tap - ky * prob.kw;
-          ptx::tma_load_5d(st, &map_x, full_bar + stage, cb * kElems, kx * prob.dw - prob.pw,
-                           oy0 * prob.sh - prob.ph + ky * prob.dh, img0, 0);
+          const int4 e = tabulated ? kb_table[kb] : kb_entry(kb);
+          ptx::tma_load_5d(st, &map_x, full_bar + stage, e.y, e.z - prob.pw, oy0 * prob.sh - prob.ph + e.w, img0, 0);
           if (!kResidentB)
             ptx::tma_load_3d(st + kABytes, &map_w, full_bar + stage, kb * kElems, n0, 0);
           if (++stage == STAGES) {
@@ -298,14 +310,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           ptx::tc_fence_after_sync();
           const uint32_t a_base = ptx::smem_u32(smem) + (uint32_t)(ab * prob.cblocks * prob.a_tile_bytes);
-          const uint32_t b_base = ptx::smem_u32(b_resident);
+          // (start addresses are 16-byte units in the low 14 bits of a descriptor; shared memory ends below 2^18)
+          const uint64_t adesc0 = ptx::smem_desc_k(a_base, RB);
+          const uint64_t bdesc0 = ptx::smem_desc_k(ptx::smem_u32(b_resident), RB);
           for (int kb = 0; kb < k_blocks; ++kb) {
-            const int tap = kb / prob.cblocks, cb = kb - tap * prob.cblocks;
-            const int ky = tap / prob.kw, kx = tap - ky * prob.kw;
-            const uint32_t a_addr = a_base + (uint32_t)(cb * prob.a_tile_bytes) +
-                                    (uint32_t)((ky * prob.dh * prob.wp + kx * prob.dw) * RB);
-            const uint64_t adesc = ptx::smem_desc_k(a_addr, RB);
-            const uint64_t bdesc = ptx::smem_desc_k(b_base + (uint32_t)kb * kBBytes, RB);
+            const uint64_t adesc = adesc0 + (uint64_t)(uint32_t)(tabulated ? kb_table[kb].x : kb_entry(kb).x);
+            const uint64_t bdesc = bdesc0 + (uint64_t)((uint32_t)kb * (kBBytes >> 4));
 #pragma unroll
             for (int k = 0; k < kMmasPerBlock; ++k) {
               ptx::mma_i8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, accumulate);
@@ -556,7 +566,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 template <int BN, int STAGES, int RB, bool kResidentB = false, bool kHalo = false>
 constexpr size_t conv_codes_smem_bytes() {
   return (kHalo ? 0 : (size_t)STAGES * (kTileM * RB + (kResidentB ? 0 : BN * RB))) + (2 * STAGES + 9) * 8 + 32 +
-         kCodesMaxMaps * sizeof(float2) + 1024;
+         kCodesMaxMaps * sizeof(float2) + kCodesKTable * sizeof(int4) + 1024;
 }
 
 } // namespace nb200
