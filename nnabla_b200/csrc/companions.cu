@@ -177,6 +177,67 @@ __global__ void __launch_bounds__(kThreads) bn_inference_warp_kernel(const float
   }
 }
 
+// Planes whose size is not a multiple of 4 (7 x 7 = 49 values): four consecutive planes are S float4, 16-byte
+// aligned when the plane count is a multiple of 4, and a warp takes such a group. Lanes 0..3 hold the constants of
+// the group's four channels; a float4 lies in one channel or across two neighbours (S >= 32), whose constants come
+// by shuffle. A quarter of the load / store instructions of the scalar form, the same rounded operations.
+__global__ void __launch_bounds__(kThreads) bn_inference_warp4_kernel(const float *__restrict__ x, const float *beta,
+                                                                      const float *gamma, const float *mean,
+                                                                      const float *var, unsigned groups, int C, int S,
+                                                                      float eps, float *__restrict__ y) {
+  pdl_wait();
+  pdl_trigger();
+  const unsigned group = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  if (group >= groups)
+    return;
+  const int lane = threadIdx.x & 31;
+  const float4 *xp = reinterpret_cast<const float4 *>(x) + (size_t)group * S;
+  float4 *yp = reinterpret_cast<float4 *>(y) + (size_t)group * S;
+  constexpr int kPer = 2;
+  float4 v[kPer];
+#pragma unroll
+  for (int u = 0; u < kPer; ++u)
+    if (lane + 32 * u < S)
+      v[u] = __ldcs(xp + lane + 32 * u);
+  const int c = (int)((group * 4u + (unsigned)(lane & 3)) % (unsigned)C);
+  const float m = __ldg(mean + c);
+  const float sd = __fsqrt_rn(__fadd_rn(__ldg(var + c), eps));
+  const float g = gamma ? __ldg(gamma + c) : 1.0f;
+  const float b = beta ? __ldg(beta + c) : 0.0f;
+  auto one = [&](int j, float4 a) { // all lanes of the warp call this together (shuffles)
+    const int e = 4 * j;
+    const int k0 = (e >= S) + (e >= 2 * S) + (e >= 3 * S);
+    const int k1 = k0 < 3 ? k0 + 1 : 3;
+    const float m0 = __shfl_sync(0xffffffffu, m, k0), m1 = __shfl_sync(0xffffffffu, m, k1);
+    const float g0 = __shfl_sync(0xffffffffu, g, k0), g1 = __shfl_sync(0xffffffffu, g, k1);
+    const float s0 = __shfl_sync(0xffffffffu, sd, k0), s1 = __shfl_sync(0xffffffffu, sd, k1);
+    const float b0 = __shfl_sync(0xffffffffu, b, k0), b1 = __shfl_sync(0xffffffffu, b, k1);
+    const int edge = (k0 + 1) * S; // first element of the next plane
+    auto el = [&](float t, int idx) {
+      const bool nx = idx >= edge;
+      return __fadd_rn(__fdiv_rn(__fmul_rn(__fsub_rn(t, nx ? m1 : m0), nx ? g1 : g0), nx ? s1 : s0), nx ? b1 : b0);
+    };
+    return make_float4(el(a.x, e), el(a.y, e + 1), el(a.z, e + 2), el(a.w, e + 3));
+  };
+  const int rounds = (S + 31) / 32;
+#pragma unroll
+  for (int u = 0; u < kPer; ++u) {
+    if (u < rounds) { // warp-uniform
+      const int j = lane + 32 * u;
+      const float4 r = one(j < S ? j : 0, j < S ? v[u] : make_float4(0.f, 0.f, 0.f, 0.f));
+      if (j < S)
+        __stcs(yp + j, r);
+    }
+  }
+  for (int u = kPer; u < rounds; ++u) {
+    const int j = lane + 32 * u;
+    const float4 a = j < S ? __ldcs(xp + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 r = one(j < S ? j : 0, a);
+    if (j < S)
+      __stcs(yp + j, r);
+  }
+}
+
 // ReLU (src/nbla/function/generic/relu.cpp): y = max(0, x); Add2 (add2.cpp): y = a + b.
 template <int kOp, bool kVec>
 __global__ void __launch_bounds__(kThreads) unary_binary_kernel(const float *__restrict__ a,
@@ -607,9 +668,14 @@ int nb200_batch_normalization_inference_f32(const float *x, const float *beta, c
   } else if (inner >= 32 && inner < 4 * kThreads && outer * channels < (1ll << 31)) {
     const unsigned planes = (unsigned)(outer * channels);
     const dim3 grid((planes + kThreads / 32 - 1) / (kThreads / 32));
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
     if (vec)
       NB_CUDA(launch_dependent(bn_inference_warp_kernel<true>, grid, dim3(kThreads), 0, as_stream(stream), x, beta, gamma,
                                mean, var, planes, (int)channels, (int)inner, eps, y));
+    else if (aligned && planes % 4 == 0)
+      NB_CUDA(launch_dependent(bn_inference_warp4_kernel, dim3((planes / 4 + kThreads / 32 - 1) / (kThreads / 32)),
+                               dim3(kThreads), 0, as_stream(stream), x, beta, gamma, mean, var, planes / 4,
+                               (int)channels, (int)inner, eps, y));
     else
       NB_CUDA(launch_dependent(bn_inference_warp_kernel<false>, grid, dim3(kThreads), 0, as_stream(stream), x, beta,
                                gamma, mean, var, planes, (int)channels, (int)inner, eps, y));

@@ -32,7 +32,7 @@ def F():
 # (a block per plane)
 @pytest.mark.parametrize("shape", [(2, 6, 9, 11), (3, 16, 8, 8), (1, 5, 1, 1), (4, 7), (2, 5, 7, 7), (2, 3, 28, 28),
                                    (3, 4, 20, 10), (2, 3, 13, 31), (2, 2, 4, 8), (1, 3, 31, 33), (1, 2, 32, 32),
-                                   (9, 3, 5, 6), (2, 3, 48, 48)])
+                                   (9, 3, 5, 6), (2, 3, 48, 48), (4, 8, 7, 7), (2, 6, 13, 31), (2, 2, 5, 7), (1, 4, 11, 93)])
 def test_batch_normalization_relu_add2(F, shape):
     rng = np.random.RandomState(sum(shape))
     x = rng.randn(*shape).astype(np.float32)
