@@ -899,7 +899,7 @@ def run_b200_arm(args):
 
     cpu_baseline = None
     if not args.no_cpu_baseline:
-        n_img = 4
+        n_img = 24  # about 12 s of one host thread
         kind, ips, dt = cpu_images_per_second(n_img, 1)
         cpu_baseline = {"value": ips, "unit": "images/s", "cores": 1, "kind": kind,
                         "sample": "%d images of the batch, whole network per image, 1 thread (%.1f s)" % (n_img, dt)}
