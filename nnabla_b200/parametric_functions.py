@@ -284,6 +284,8 @@ def _inq_layer(scope, shape, init, i_init, b_shape, b_init, with_bias, seed):
             a = np.zeros(shape) if i_init is None else (i_init(shape) if callable(i_init) else np.asarray(i_init))
             ind = torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32).reshape(shape)).to(_dev())
             _parameters[key] = ind
+        elif ind.dtype != torch.int32:  # loaded from a parameter file, which holds floats
+            ind = _parameters[key] = ind.to(torch.int32).contiguous()
         b = get_parameter_or_create("b", b_shape, b_init if b_init is not None else _zeros) if with_bias else None
         state = _inq_states.get(key)
         if state is None or state.old_weights.shape != w.shape:
@@ -365,3 +367,130 @@ def min_max_quantized_affine(inp, n_outmaps, base_axis=1, w_init=None, b_init=No
                                           qr_min_b_init or _constant(-6.0), qr_max_b_init or _constant(6.0),
                                           fix_parameters, outputs=[b_q], name="min_max_quantize_b")
     return F.affine(inp, real_w, real_b, base_axis)
+
+
+# ---------------------------------------------------------------------------
+# Parameter files in nnabla's `.protobuf` format, so that the parameters of a network trained or converted
+# here ("W", the binarised "Wb" and "alpha", BatchNormalization statistics, INQ indicators) load in nnabla
+# with nn.load_parameters and the other way round. Written by hand on the wire format (no generated module):
+#   NNablaProtoBuf { repeated Parameter parameter = 200; }
+#   Parameter { string variable_name = 1; Shape shape = 20; repeated float data = 100; bool need_grad = 101; }
+#   Shape { repeated int64 dim = 1 [packed]; }
+# (src/nbla/proto/nnabla.proto.tmpl:24-26, :38-49, :105-110; the writer of
+# python/src/nnabla/utils/get_file_handle.py:476-486, the reader of python/src/nnabla/parameter.py:392-399.)
+# ---------------------------------------------------------------------------
+_NO_GRAD_NAMES = ("Wb", "alpha", "mean", "var", "I")  # registered with need_grad=False by nnabla's layers
+
+
+def _varint(n):
+    n &= (1 << 64) - 1
+    out = bytearray()
+    while True:
+        b = n & 0x7F
+        n >>= 7
+        if n:
+            out.append(b | 0x80)
+        else:
+            out.append(b)
+            return bytes(out)
+
+
+def _field(number, wire_type, payload):
+    head = _varint((number << 3) | wire_type)
+    return head + (_varint(len(payload)) + payload if wire_type == 2 else payload)
+
+
+def _read_varint(buf, pos):
+    shift = value = 0
+    while True:
+        if pos >= len(buf):
+            raise ValueError("truncated varint")
+        b = buf[pos]
+        pos += 1
+        value |= (b & 0x7F) << shift
+        if not b & 0x80:
+            return value, pos
+        shift += 7
+        if shift > 63:
+            raise ValueError("varint too long")
+
+
+def _fields(buf):
+    """(field number, wire type, value) of one message; value is an int (varint, fixed) or a memoryview."""
+    pos = 0
+    view = memoryview(buf)
+    while pos < len(buf):
+        key, pos = _read_varint(buf, pos)
+        number, wt = key >> 3, key & 7
+        if wt == 0:
+            value, pos = _read_varint(buf, pos)
+        elif wt == 1:
+            value, pos = int.from_bytes(buf[pos:pos + 8], "little"), pos + 8
+        elif wt == 5:
+            value, pos = int.from_bytes(buf[pos:pos + 4], "little"), pos + 4
+        elif wt == 2:
+            n, pos = _read_varint(buf, pos)
+            if pos + n > len(buf):
+                raise ValueError("truncated field")
+            value, pos = view[pos:pos + n], pos + n
+        else:
+            raise ValueError("unsupported wire type %d" % wt)
+        yield number, wt, value
+
+
+def save_parameters(path, params=None):
+    """nn.save_parameters for the `.protobuf` format (python/src/nnabla/parameter.py:424-447)."""
+    if not str(path).endswith(".protobuf"):
+        raise ValueError("Only supported .protobuf.")
+    params = get_parameters() if params is None else params
+    out = bytearray()
+    for name, p in params.items():
+        a = np.asarray(p.detach().cpu().numpy() if isinstance(p, torch.Tensor) else p)
+        shape = b"".join(_varint(int(d)) for d in a.shape)
+        msg = _field(1, 2, name.encode("utf-8"))
+        msg += _field(20, 2, _field(1, 2, shape) if a.ndim else b"")
+        msg += _field(100, 2, a.astype("<f4").tobytes())
+        if name.rsplit("/", 1)[-1] not in _NO_GRAD_NAMES:
+            msg += _field(101, 0, _varint(1))
+        out += _field(200, 2, msg)
+    with open(path, "wb") as f:
+        f.write(bytes(out))
+
+
+def load_parameters(path):
+    """nn.load_parameters for the `.protobuf` format: every Parameter of the file replaces or creates the
+    entry of that name in the registry (set_parameter_from_proto, parameter.py:392-399). Returns
+    {name: need_grad}."""
+    if not str(path).endswith(".protobuf"):
+        raise ValueError("Only supported .protobuf.")
+    with open(path, "rb") as f:
+        buf = f.read()
+    flags = OrderedDict()
+    for number, wt, value in _fields(buf):
+        if number != 200 or wt != 2:
+            continue  # networks, optimizers, ... of a full model file are not parameters
+        name, dims, chunks, need_grad = "", [], [], False
+        for n2, w2, v2 in _fields(bytes(value)):
+            if n2 == 1 and w2 == 2:
+                name = bytes(v2).decode("utf-8")
+            elif n2 == 20 and w2 == 2:
+                for n3, w3, v3 in _fields(bytes(v2)):
+                    if n3 == 1 and w3 == 2:  # packed
+                        b3, pos = bytes(v3), 0
+                        while pos < len(b3):
+                            d, pos = _read_varint(b3, pos)
+                            dims.append(d)
+                    elif n3 == 1 and w3 == 0:
+                        dims.append(v3)
+            elif n2 == 100 and w2 == 2:  # packed floats
+                chunks.append(np.frombuffer(bytes(v2), dtype="<f4"))
+            elif n2 == 100 and w2 == 5:  # one float per field
+                chunks.append(np.array([v2], dtype="<u4").view("<f4"))
+            elif n2 == 101 and w2 == 0:
+                need_grad = bool(v2)
+        data = np.concatenate(chunks) if chunks else np.zeros(0, np.float32)
+        if data.size != int(np.prod(dims, dtype=np.int64)):
+            raise ValueError("parameter %s: %d values for shape %s" % (name, data.size, tuple(dims)))
+        _parameters[name] = torch.from_numpy(data.astype(np.float32).reshape(dims)).to(_dev())
+        flags[name] = need_grad
+    return flags

@@ -196,3 +196,32 @@ def test_quantized_parametric_layers(F):
     assert np.array_equal(bits(p[pre + "min_max_quantize_w/qr_max"].cpu().numpy()), bits(qmax_after))
     assert cases.rel_rms(ym.cpu().numpy(), oracle.affine(x, wq, p[pre + "b_q"].cpu().numpy())) < 1e-5
     PF.clear_parameters()
+
+
+def test_parameter_file_round_trip_of_a_binary_weight_layer(F, tmp_path):
+    """Wb and alpha written by the forward pass survive nn.save_parameters / nn.load_parameters (`.protobuf`), and
+    the reloaded layer gives the same output bit for bit; INQ indicators come back as int32."""
+    from nnabla_b200 import parametric_functions as PF
+    PF.clear_parameters()
+    rng = np.random.RandomState(5)
+    x = dev(rng.randn(2, 8, 12, 12).astype(np.float32))
+    with PF.parameter_scope("c1"):
+        y0 = PF.binary_weight_convolution(x, 16, (3, 3), pad=(1, 1), rng=rng)
+    with PF.parameter_scope("fc"):
+        z0 = PF.inq_affine(y0, 10, inq_iterations=(0, 5), selection_algorithm="largest_abs", rng=rng)
+    before = {k: v.clone() for k, v in PF.get_parameters().items()}
+    assert float(before["c1/bwn_conv/alpha"].abs().sum()) > 0 and int(before["fc/inq_affine/I"].sum()) > 0
+    path = str(tmp_path / "net.protobuf")
+    PF.save_parameters(path)
+    PF.clear_parameters()
+    flags = PF.load_parameters(path)
+    assert list(flags) == list(before) and flags["c1/bwn_conv/W"] and not flags["c1/bwn_conv/Wb"]
+    for k, v in before.items():
+        assert torch.equal(PF.get_parameters()[k].float(), v.float()), k
+    with PF.parameter_scope("c1"):
+        y1 = PF.binary_weight_convolution(x, 16, (3, 3), pad=(1, 1))
+    assert torch.equal(y1, y0)
+    with PF.parameter_scope("fc"):
+        PF.inq_affine(y1, 10, inq_iterations=(), selection_algorithm="largest_abs")
+    assert PF.get_parameters()["fc/inq_affine/I"].dtype == torch.int32
+    PF.clear_parameters()
