@@ -18,6 +18,10 @@ falls back to another execution.
 
 The folding constants are computed on the host in float32 exactly as the reference's converter does
 (batch_normalization_folding.py:176-191): c0 = gamma / sqrt(var + eps), c1 = beta - gamma * mean / sqrt(var + eps).
+
+`FusedBatchNormalization` (end of this file) is the milder conversion: only the activation tail
+BatchNormalization [-> Add2] [-> ReLU] [-> FixedPointQuantize] becomes one function, everything keeps its
+rounding and the result is the as-written graph's, bit for bit.
 """
 import numpy as np
 
@@ -297,3 +301,143 @@ class BatchNormalizationFolding:
             env[id(out)] = ops.convolution_codes_folded(codes, shape, prep, scale, bias, a["pad"], a["stride"],
                                                         a["dilation"], **kw2)
         emit("convolution_codes_folded", step)
+
+
+class FusedBatchNormalization:
+    """The activation tail of every layer as ONE function, the other functions as they are:
+
+        BatchNormalization [-> Add2(., BatchNormalization(s) | s)] [-> ReLU] [-> FixedPointQuantize]
+            -> bn_add_relu_fixed_point(a, bn_a, b, bn_b, eps, relu, quantize, sign, n, delta)
+
+    in the manner of nnabla's FusedBatchNormalization converter
+    (python/src/nnabla/experimental/graph_converters/fused_batch_normalization.py, which rewrites
+    BatchNormalization -> Add2 -> ReLU into the FusedBatchNormalization function); the quantizer that follows
+    in a quantized network joins the same pass. Every operation keeps its own rounding, so the converted
+    graph gives the as-written graph's result bit for bit, and each activation is read and written once
+    instead of up to four times. A binary-weight convolution whose input comes out of a fused quantizer is
+    told the quantizer's step (`fixed_point_delta`), which selects the exact int8 contraction.
+
+    convert(recorder, output_sym, ops, zeros_like) -> FoldedProgram on `ops` (nnabla_b200.functions or a
+    namespace of the same shape); zeros_like(w, shape=None) makes the Wb / alpha buffers of the binary layers."""
+
+    class _Tail:
+        def __init__(self, bn):
+            self.bn, self.add, self.relu, self.fxp = bn, None, None, None
+            self.other, self.other_bn = None, None  # second operand of the addition: Sym, and its BN node if any
+
+        @property
+        def last(self):
+            for n in (self.fxp, self.relu, self.add):
+                if n is not None:
+                    return n
+            return self.bn
+
+    @staticmethod
+    def _foldable(bn):
+        return not bn.attrs["batch_stat"] and bn.attrs["axes"] == (1,)
+
+    def _tails(self, rec):
+        tails, owner = {}, {}  # by index of the tail's LAST node; node index -> tail
+        for n in rec.nodes:
+            if n.fn != "batch_normalization" or n.index in owner or not self._foldable(n):
+                continue
+            add = _single(n.out, "add2")
+            if add is not None and add.inputs[1] is n.out and add.inputs[0] is not n.out:
+                first = add.inputs[0].node
+                if (first is not None and first.fn == "batch_normalization" and self._foldable(first)
+                        and _single(first.out, "add2") is add):
+                    continue  # the second operand's BN: taken in by the first operand's tail
+            t = self._Tail(n)
+            cur = n.out
+            if add is not None and add.inputs[0] is not add.inputs[1]:
+                t.add = add
+                t.other = add.inputs[1] if add.inputs[0] is n.out else add.inputs[0]
+                m = t.other.node
+                if (m is not None and m.fn == "batch_normalization" and self._foldable(m)
+                        and _single(m.out, "add2") is add and m.index not in owner
+                        and float(m.attrs["eps"]) == float(n.attrs["eps"])):
+                    t.other_bn = m
+                cur = add.out
+            relu = _single(cur, "relu")
+            if relu is not None:
+                t.relu, cur = relu, relu.out
+            fxp = _single(cur, "fixed_point_quantize")
+            if fxp is not None:
+                t.fxp = fxp
+            if t.last is t.bn:
+                continue  # nothing to fuse with: stays a plain BatchNormalization
+            for m in (t.bn, t.add, t.relu, t.fxp, t.other_bn):
+                if m is not None:
+                    owner[m.index] = t
+            tails[t.last.index] = t
+        return tails, owner
+
+    def convert(self, rec, output_sym, ops, zeros_like):
+        tails, owner = self._tails(rec)
+        steps, calls = [], []
+        step_of = {}  # Sym id -> quantizer step, for tensors that leave a fused quantizer
+        side = {}
+
+        def bn_tuple(node):
+            a = node.attrs
+            return (a["beta"], a["gamma"], a["mean"], a["var"])
+
+        for n in rec.nodes:
+            t = owner.get(n.index)
+            if t is not None:
+                if n is not t.last:
+                    continue
+                a_sym = t.bn.inputs[0]
+                b_sym = None if t.add is None else (t.other_bn.inputs[0] if t.other_bn is not None else t.other)
+                bn_a, bn_b = bn_tuple(t.bn), (bn_tuple(t.other_bn) if t.other_bn is not None else None)
+                q = t.fxp.attrs if t.fxp is not None else dict(sign=True, n=8, delta=2 ** -4)
+                args = (float(t.bn.attrs["eps"]), t.relu is not None, t.fxp is not None, q["sign"], q["n"], q["delta"])
+                out = t.last.out
+                if t.fxp is not None:
+                    step_of[id(out)] = q["delta"]
+
+                def step(env, a_sym=a_sym, b_sym=b_sym, bn_a=bn_a, bn_b=bn_b, args=args, out=out):
+                    b = env[id(b_sym)] if b_sym is not None else None
+                    env[id(out)] = ops.bn_add_relu_fixed_point(env[id(a_sym)], bn_a, b, bn_b, *args)
+                steps.append(step)
+                calls.append("bn_add_relu_fixed_point")
+                continue
+            a, src, out = n.attrs, n.inputs, n.out
+            if n.fn == "fixed_point_quantize":
+                step_of[id(out)] = a["delta"]
+            if n.fn == "convolution":
+                fn = lambda x, a=a: ops.convolution(x, a["w"], a["b"], a["base_axis"], a["pad"], a["stride"],
+                                                    a["dilation"], a["group"])
+            elif n.fn == "binary_weight_convolution":
+                w = a["w"]
+                side[n.index] = (zeros_like(w), zeros_like(w, (w.shape[0],)))
+                hint = step_of.get(id(src[0]))
+                kw = {"fixed_point_delta": hint} if hint is not None else {}
+                fn = lambda x, a=a, s=side[n.index], kw=kw: ops.binary_weight_convolution(
+                    x, a["w"], s[0], s[1], a["b"], a["base_axis"], a["pad"], a["stride"], a["dilation"], a["group"],
+                    a["quantize_zero_to"], **kw)
+            elif n.fn == "batch_normalization":
+                fn = lambda x, a=a: ops.batch_normalization(x, a["beta"], a["gamma"], a["mean"], a["var"], list(a["axes"]),
+                                                            0.9, a["eps"], a["batch_stat"])
+            elif n.fn == "relu":
+                fn = lambda x: ops.relu(x)
+            elif n.fn == "add2":
+                fn = lambda x, y: ops.add2(x, y)
+            elif n.fn == "fixed_point_quantize":
+                fn = lambda x, a=a: ops.fixed_point_quantize(x, a["sign"], a["n"], a["delta"])
+            elif n.fn == "max_pooling":
+                fn = lambda x, a=a: ops.max_pooling(x, a["kernel"], a["stride"], a["ignore_border"], a["pad"])
+                if id(src[0]) in step_of:
+                    step_of[id(out)] = step_of[id(src[0])]  # the maximum of multiples of a step is one of them
+            elif n.fn == "global_average_pooling":
+                fn = lambda x: ops.global_average_pooling(x)
+            elif n.fn == "affine":
+                fn = lambda x, a=a: ops.affine(x, a["w"], a["b"], a["base_axis"])
+            else:
+                raise NotImplementedError("no rule for the function %s" % n.fn)
+
+            def step(env, fn=fn, src=src, out=out):
+                env[id(out)] = fn(*[env[id(s)] for s in src])
+            steps.append(step)
+            calls.append(n.fn)
+        return FoldedProgram(steps, rec.input, output_sym, calls)

@@ -274,3 +274,24 @@ def test_converter_gives_the_hand_written_folded_network(F):
     F.check_device_status()
     want = resnet18.FoldedRunner(F, gp)(dev(x))
     assert torch.equal(got, want)
+
+
+def test_fusion_converter_gives_the_as_written_logits(F):
+    """FusedBatchNormalization converter on the recorded network: 17 fused activation calls, every binary-weight
+    convolution told the quantizer's step; logits identical to the graph as written and to the hand-written
+    Runner(fused=True), bit for bit."""
+    from nnabla_b200 import graph_converters as gc
+    rng = np.random.RandomState(9)
+    params = resnet18.init_parameters(rng, num_classes=32)
+    x = rng.randn(3, 3, 64, 64).astype(np.float32)
+    gp = {k: dev(v) for k, v in params.items()}
+    gz = lambda w, shape=None: torch.zeros(shape if shape is not None else tuple(w.shape), device="cuda")
+    rec = gc.Recorder()
+    out = resnet18.Runner(rec, gp, lambda w, shape=None: None, None, fixed_point_hint=False)(rec.input)
+    prog = gc.FusedBatchNormalization().convert(rec, out, F, gz)
+    assert prog.calls.count("bn_add_relu_fixed_point") == 17 and len(prog.calls) == 40
+    got = prog(dev(x))
+    F.check_device_status()
+    as_written = resnet18.Runner(F, gp, gz)(dev(x))
+    by_hand = resnet18.Runner(F, gp, gz, fused=True)(dev(x))
+    assert torch.equal(got, as_written) and torch.equal(got, by_hand)

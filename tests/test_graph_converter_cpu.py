@@ -120,3 +120,47 @@ def test_bias_of_the_convolution_is_folded_too():
     std = np.sqrt(var + np.float32(1e-5))
     c0, c1 = gamma / std, beta - gamma * mean / std
     assert np.array_equal(ops.log[0][2].numpy(), c0 * b.numpy() + c1)  # b' = c0 * b + c1
+
+
+def test_fused_batch_normalization_converter_on_the_oracle():
+    """FusedBatchNormalization: 20 BatchNormalization, 8 Add2, 17 ReLU and 17 FixedPointQuantize calls become 17
+    fused calls (the three shortcut normalisations join the pass of the block they are added to), everything
+    else stays; on the oracle's function namespace the converted program gives the as-written network's
+    logits bit for bit (every operation keeps its own rounding)."""
+    from oracle import ops as oracle_ops
+    rng = np.random.RandomState(3)
+    params = resnet18.init_parameters(rng, num_classes=10)
+    zeros = lambda w, shape=None: np.zeros(shape if shape is not None else w.shape, np.float32)
+    rec = gc.Recorder()
+    out = resnet18.Runner(rec, params, zeros, None, fixed_point_hint=False)(rec.input)
+    prog = gc.FusedBatchNormalization().convert(rec, out, oracle_ops, zeros)
+    assert prog.calls.count("bn_add_relu_fixed_point") == 17 and prog.calls.count("binary_weight_convolution") == 19
+    assert not {"batch_normalization", "relu", "add2", "fixed_point_quantize"} & set(prog.calls)
+    assert len(prog.calls) == 19 + 17 + 4
+    x = rng.randn(1, 3, 32, 32).astype(np.float32)
+    want = resnet18.Runner(oracle_ops, params, zeros, None, fixed_point_hint=False)(x)
+    got = prog(x)
+    assert np.array_equal(np.asarray(got, np.float32).view(np.uint32), np.asarray(want, np.float32).view(np.uint32))
+
+
+def test_fused_batch_normalization_converter_leaves_other_patterns_alone():
+    """A BatchNormalization with nothing to fuse with, one in training mode and one that feeds two functions
+    stay plain calls; an Add2 of a tensor with itself is not taken apart."""
+    rec = gc.Recorder()
+    c = np.ones(4, np.float32).reshape(1, 4, 1, 1)
+    a = rec.batch_normalization(rec.input, c, c, c, c, [1], 0.9, 1e-5, False)          # -> max_pooling: plain
+    p = rec.max_pooling(a, (2, 2), (2, 2))
+    b = rec.batch_normalization(p, c, c, c, c, [1], 0.9, 1e-5, True)                   # batch statistics: plain
+    r = rec.relu(b)
+    d = rec.batch_normalization(r, c, c, c, c, [1], 0.9, 1e-5, False)                  # two consumers: plain
+    e = rec.add2(rec.relu(d), rec.fixed_point_quantize(d))
+    f = rec.batch_normalization(e, c, c, c, c, [1], 0.9, 1e-5, False)                  # -> ReLU: fused
+    g = rec.relu(f)
+    h = rec.add2(g, g)
+
+    class Ops:
+        def __getattr__(self, name):
+            return lambda *a, **k: name
+    prog = gc.FusedBatchNormalization().convert(rec, h, Ops(), None)
+    assert prog.calls == ["batch_normalization", "max_pooling", "batch_normalization", "relu", "batch_normalization",
+                          "relu", "fixed_point_quantize", "add2", "bn_add_relu_fixed_point", "add2"]
