@@ -400,9 +400,14 @@ class FunctionTimer:
 
     @staticmethod
     def _work(name, a, kw, y):
+        from nnabla_b200 import functions as lib
         n_in = a[0].numel()
         n_out = y.numel() if hasattr(y, "numel") else 0
-        if name in ("batch_normalization", "relu", "fixed_point_quantize"):
+        if name == "fixed_point_quantize":
+            # a quantizer that also left int8 codes with its result wrote one byte more per value
+            with_codes = lib._sideband_get(y, a[3] if len(a) > 3 else kw.get("delta", 2 ** -4)) is not None
+            return ("bytes", (9.0 if with_codes else 8.0) * n_in)
+        if name in ("batch_normalization", "relu"):
             return ("bytes", 8.0 * n_in)
         if name == "add2":
             return ("bytes", 12.0 * n_in)
@@ -416,7 +421,10 @@ class FunctionTimer:
             # and writes their signs): with quantized activations that traffic, not the contraction, is the
             # larger floor for most layers
             extra = 2 if name == "binary_weight_convolution" else 1
-            return (kind, 2.0 * n_out * k, 4.0 * (n_in + n_out + extra * w.numel()))
+            # an input that carries its quantizer's codes is read as one byte per value
+            from_codes = (name == "binary_weight_convolution" and kw.get("fixed_point_delta") is not None
+                          and lib._sideband_get(a[0], kw["fixed_point_delta"]) is not None)
+            return (kind, 2.0 * n_out * k, (1.0 if from_codes else 4.0) * n_in + 4.0 * (n_out + extra * w.numel()))
         if name == "affine":
             return ("flops", 2.0 * n_out * a[1].shape[0])
         return ("bytes", 0.0)
@@ -436,10 +444,12 @@ class FunctionTimer:
 
 
 # DRAM bytes of the 19 binary-weight convolutions of one pass at 256 images, from one ncu capture of this file's
-# own command line (dram__bytes_read.sum + dram__bytes_write.sum over their 38 kernels: 2610 MB read, 850 MB
-# written; lines of a result that were still in L2 when its kernel ended are not in the write figure). The
-# tensors of the pass grow in proportion to the images, so other batch sizes scale it.
-NCU_DRAM_BYTES_BINARY_WEIGHT_CONVOLUTIONS_AT_256 = 3460.3e6
+# own command line (dram__bytes_read.sum + dram__bytes_write.sum over their 38 kernels: 812 MB read, 794 MB
+# written; lines of a result that were still in L2 when its kernel ended are not in the write figure; 15 of the
+# 19 read their quantizer's int8 codes, not the fp32 tensor). The tensors of the pass grow in proportion to the
+# images, so other batch sizes scale it (below 2^23 values per tensor the quantizers leave no codes and the
+# convolutions read fp32: the figure is then low).
+NCU_DRAM_BYTES_BINARY_WEIGHT_CONVOLUTIONS_AT_256 = 1605.9e6
 
 
 def function_table(F, params, gz, x, peaks, int8_peak, passes=3):
@@ -448,7 +458,7 @@ def function_table(F, params, gz, x, peaks, int8_peak, passes=3):
     largest share."""
     from nnabla_b200 import resnet18
     timer = FunctionTimer(F)
-    net = resnet18.Runner(timer, params, gz)
+    net = resnet18.Runner(timer, params, gz, codes_sideband=True)
     net(x)
     timer.records.clear()
     for _ in range(passes):
@@ -703,7 +713,9 @@ def run_b200_arm(args):
     hx = torch.from_numpy(np.random.RandomState(1000 + rank).randn(Bg, *IMAGE).astype(np.float32)).pin_memory()
     x = hx.cuda()
     gz = lambda t, shape=None: torch.zeros(shape or tuple(t.shape), device="cuda")
-    net = resnet18.Runner(F, params, gz)
+    # every FixedPointQuantize of a large tensor also leaves its int8 channel-last codes with its result, and the
+    # binary-weight convolutions called on that result read them (same functions, same results bit for bit)
+    net = resnet18.Runner(F, params, gz, codes_sideband=True)
 
     # ---- the timed region: K forward passes of the graph as written ------------------------
     # The calls of one forward pass (one C-ABI call per reference function) are recorded once into a CUDA
@@ -808,6 +820,7 @@ def run_b200_arm(args):
             return runner
         same_as = lambda r: bool(torch.equal(r(x), logits))
         same &= same_as(form("as_written_call_by_call", net))
+        same &= same_as(form("as_written_without_quantizer_codes_call_by_call", resnet18.Runner(F, params, gz)))
         same &= same_as(form("fused_activation_pass", resnet18.Runner(F, params, gz, fused=True)))
         same &= same_as(form("int8_codes_between_layers", resnet18.Runner(F, params, gz, fused="codes")))
         prep = form("int8_codes_prepared_weights", resnet18.Runner(F, params, gz, fused="codes", prepared_weights=True))
@@ -884,7 +897,8 @@ def run_b200_arm(args):
     table, roofline = function_table(F, params, gz, x, peaks, int8_peak)
     roofline["peak_source"] = peak_kind if roofline["unit"] != "TOP/s" else "measured in this run (torch._int_mm 8192^3)"
     if roofline["bound"] == "hbm" and roofline["kernel"].endswith("convolution"):
-        roofline["bytes_counted"] = "fp32 input and result of every call, its weights read, their signs written"
+        roofline["bytes_counted"] = ("input of every call (int8 codes where its quantizer left them, else fp32), fp32 "
+                                     "result, weights read, their signs written")
 
     del x, logits
     torch.cuda.empty_cache()
@@ -914,6 +928,8 @@ def run_b200_arm(args):
         "config": dict(workload_config(args.batch, world),
                        execution=("the pass's C-ABI calls recorded once into a CUDA graph and replayed" if captured
                                   is not None else "call by call"),
+                       quantizer_codes="FixedPointQuantize of tensors of 2^23 values and more leaves int8 channel-last codes "
+                                       "with its result; the binary-weight convolution called on it reads them",
                        l2="per-step activations (over 800 MB at 256 images) exceed L2; no flush needed"),
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
         "gpu_launches": calls, "gpu_launches_note": "C-ABI calls whose kernels ran in the timed region (replayed from the CUDA graph when "

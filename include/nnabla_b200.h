@@ -111,6 +111,13 @@ int nb200_fixed_point_quantize_f32(const float *x, float *y, size_t size, int si
  * tensor-core contraction. Requires n - sign <= 7. */
 int nb200_fixed_point_quantize_f32_codes(const float *x, float *y, int8_t *codes, size_t size, int sign, int n,
                                          float delta, void *stream);
+/* FixedPointQuantize of x [batch, channels, inner] that also leaves the result as int8 channel-last codes
+ * [batch][inner][nb200_codes_nhwc_slots(channels, 1)] (zero in the padding slots): the activation operand of
+ * nb200_binary_convolution_codes_f32 and the other *_codes_* entry points, written by the quantizer itself so
+ * that the convolution behind it does not read the fp32 tensor again. inner % 4 == 0, 16-byte aligned tensors,
+ * n - sign <= 7, batch <= 65535. y is bit-identical to nb200_fixed_point_quantize_f32's. */
+int nb200_fixed_point_quantize_nhwc_codes_f32(const float *x, float *y, int8_t *codes, int64_t batch, int64_t channels,
+                                              int64_t inner, int sign, int n, float delta, void *stream);
 int nb200_fixed_point_quantize_f32_host(const float *x, float *y, size_t size, int sign, int n, float delta);
 
 /* Pow2Quantize<float>::forward_impl

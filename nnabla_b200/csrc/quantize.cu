@@ -215,6 +215,87 @@ int fxp_launch(const float *x, float *y, int8_t *codes, size_t size, int sign, i
   return launch_elementwise(x, y, size, op, st);
 }
 
+// FixedPointQuantize of an [N, C, S] tensor that also leaves the result as int8 channel-last codes
+// [N][S][slots] (the layout the int8 convolutions read): the quantizer of a layer and the re-layout pass of
+// the convolution behind it in one pass over the activations (4 B read, 4 + 1 B written per value instead of
+// 4 + 4 and then 4 + 1). Blocks of 64 pixels x 64 channel slots; a thread quantizes four neighbouring
+// channels of four pixels, stores the fp32 results where they came from and hands the four codes of each
+// pixel to shared memory as one word; the codes leave as 64-byte runs per pixel. S % 4 == 0, 16-byte aligned.
+template <bool kPow2Delta>
+__global__ void __launch_bounds__(256)
+    fxp_nhwc_codes_kernel(const float *__restrict__ x, float *__restrict__ y, int8_t *__restrict__ codes, int C, int HW,
+                          int slots, FxpOp<kPow2Delta, false> op) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ uint32_t tile[64][17];
+  const int n = blockIdx.z;
+  const int p0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  const int px4 = threadIdx.x & 15, chq = threadIdx.x >> 4;
+  const int p = p0 + 4 * px4;
+  const int c0 = d0 + 4 * chq;
+  const typename FxpOp<kPow2Delta, false>::State st = op.init();
+  uint32_t f[4][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;
+    if (c0 + r < C && p < HW) {
+      const size_t off = ((size_t)n * C + (c0 + r)) * HW + p;
+      const float4 v = ld_stream(reinterpret_cast<const float4 *>(x + off));
+      float4 q;
+      q.x = op(v.x, 0, k0, st);
+      q.y = op(v.y, 0, k1, st);
+      q.z = op(v.z, 0, k2, st);
+      q.w = op(v.w, 0, k3, st);
+      st_stream(reinterpret_cast<float4 *>(y + off), q);
+    }
+    // the codes are small integers: 1.5 * 2^23 + k has k's two's complement in its low mantissa bits
+    f[r][0] = __float_as_uint(__fadd_rn(k0, 12582912.0f));
+    f[r][1] = __float_as_uint(__fadd_rn(k1, 12582912.0f));
+    f[r][2] = __float_as_uint(__fadd_rn(k2, 12582912.0f));
+    f[r][3] = __float_as_uint(__fadd_rn(k3, 12582912.0f));
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    tile[4 * px4 + k][chq] = __byte_perm(__byte_perm(f[0][k], f[1][k], 0x0040), __byte_perm(f[2][k], f[3][k], 0x0040),
+                                         0x5410);
+  __syncthreads();
+  const int word = threadIdx.x & 15, prow = threadIdx.x >> 4;
+#pragma unroll
+  for (int pp = prow; pp < 64; pp += 16) {
+    const int pix = p0 + pp, d = d0 + 4 * word;
+    if (pix < HW && d < slots)
+      *reinterpret_cast<uint32_t *>(codes + ((size_t)n * HW + pix) * slots + d) = tile[pp][word];
+  }
+}
+
+int fxp_nhwc_codes(const float *x, float *y, int8_t *codes, int64_t batch, int64_t channels, int64_t inner, int slots,
+                   int sign, int n, float delta, cudaStream_t st) {
+  FxpLimits L;
+  NB_TRY(fxp_limits(sign, n, delta, &L));
+  NB_CHECK((sign ? n - 1 : n) <= 7, NB200_EVALUE, "int8 codes need n - sign <= 7 (got n=%d, sign=%d)", n, sign);
+  NB_CHECK(batch >= 0 && channels > 0 && inner > 0 && batch <= 65535 && channels < (1 << 30) && inner < (1 << 30),
+           NB200_EVALUE, "bad extents");
+  if (batch == 0)
+    return NB200_OK;
+  NB_CHECK(x && y && codes, NB200_EVALUE, "null data pointer");
+  NB_CHECK(inner % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 &&
+               (reinterpret_cast<uintptr_t>(codes) & 3) == 0,
+           NB200_ENOTIMPL, "the quantizer with channel-last codes needs planes of a multiple of 4 values and aligned tensors");
+  NB_CHECK(slots >= channels && slots % 16 == 0, NB200_EVALUE, "bad slot count");
+  const dim3 grid((unsigned)((inner + 63) / 64), (unsigned)((slots + 63) / 64), (unsigned)batch);
+  if (L.pow2) {
+    FxpOp<true, false> op{L.maxv, L.minv, delta, L.inv, L.code_max, L.code_min, nullptr};
+    NB_CUDA(launch_dependent(fxp_nhwc_codes_kernel<true>, grid, dim3(256), 0, st, x, y, codes, (int)channels, (int)inner,
+                             slots, op));
+  } else {
+    FxpOp<false, false> op{L.maxv, L.minv, delta, L.inv, L.code_max, L.code_min, nullptr};
+    NB_CUDA(launch_dependent(fxp_nhwc_codes_kernel<false>, grid, dim3(256), 0, st, x, y, codes, (int)channels, (int)inner,
+                             slots, op));
+  }
+  NB_LAUNCH_CHECK();
+  return NB200_OK;
+}
+
 // ---------------------------------------------------------------------------
 // Pow2Quantize — replaces the loop of
 // src/nbla/function/generic/pow2_quantize.cpp:57-81.
@@ -875,6 +956,15 @@ int nb200_fixed_point_quantize_f32(const float *x, float *y, size_t size, int si
 int nb200_fixed_point_quantize_f32_codes(const float *x, float *y, int8_t *codes, size_t size, int sign, int n,
                                          float delta, void *stream) {
   return fxp_launch<true>(x, y, codes, size, sign, n, delta, as_stream(stream));
+}
+
+int nb200_fixed_point_quantize_nhwc_codes_f32(const float *x, float *y, int8_t *codes, int64_t batch, int64_t channels,
+                                              int64_t inner, int sign, int n, float delta, void *stream) {
+  // slots of a one-group code tensor (nb200_codes_nhwc_slots): channels padded to 16, at least 64
+  const int64_t padded = (channels + 15) / 16 * 16;
+  const int64_t block = padded <= 64 ? 64 : 128;
+  const int slots = (int)(padded < block ? block : padded);
+  return fxp_nhwc_codes(x, y, codes, batch, channels, inner, slots, sign, n, delta, as_stream(stream));
 }
 
 int nb200_fixed_point_quantize_f32_host(const float *x, float *y, size_t size, int sign, int n, float delta) {

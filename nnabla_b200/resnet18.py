@@ -59,7 +59,7 @@ class Runner:
     """Applies the network with a given function namespace and array factory."""
 
     def __init__(self, ops, params, zeros_like, trace=None, fixed_point_hint=True, fused=False,
-                 prepared_weights=False, batch_stat=False):
+                 prepared_weights=False, batch_stat=False, codes_sideband=False):
         """fused=True applies BN (+ residual) + ReLU + FixedPointQuantize as one
         function (ops.bn_add_relu_fixed_point), which is bit-identical to the
         separate functions and reads / writes each activation once.
@@ -70,6 +70,9 @@ class Runner:
         # prepared_weights (with fused="codes"): binarise every weight once, at its first use,
         # instead of in every forward pass; for inference with weights that do not change
         # batch_stat=True: BatchNormalization uses (and updates) batch statistics, the training graph
+        # codes_sideband (graph as written): every FixedPointQuantize also leaves int8 channel-last codes with its
+        # result, which the binary-weight convolutions behind it read instead of converting the fp32 tensor again
+        self.codes_sideband = codes_sideband
         self.batch_stat = batch_stat
         self.prepared_weights = prepared_weights
         self.prepared = {}
@@ -92,9 +95,10 @@ class Runner:
                                          p[name + "/var"], [1], 0.9, 1e-5, self.batch_stat)
         return self._rec(name, "batch_normalization", [x], y)
 
-    def relu_q(self, name, x):
+    def relu_q(self, name, x, to_convolution=True):
         y = self._rec(name + "/relu", "relu", [x], self.ops.relu(x))
-        q = self.ops.fixed_point_quantize(y, True, 8, DELTA)
+        kw = {"codes_sideband": True} if self.codes_sideband and to_convolution else {}
+        q = self.ops.fixed_point_quantize(y, True, 8, DELTA, **kw)
         return self._rec(name + "/fxp", "fixed_point_quantize", [y], q)
 
     def bn_params(self, name):
@@ -161,7 +165,7 @@ class Runner:
         o = self.ops
         h = o.convolution(x, self.p["stem/conv/W"], None, 1, (3, 3), (2, 2), (1, 1), 1)
         self._rec("stem/conv", "convolution", [x], h)
-        h = self.fused_act("stem/act", h, "stem/bn") if self.fused else self.relu_q("stem", self.bn("stem/bn", h))
+        h = self.fused_act("stem/act", h, "stem/bn") if self.fused else self.relu_q("stem", self.bn("stem/bn", h), to_convolution=False)
         h = self._rec("stem/pool", "max_pooling", [h], o.max_pooling(h, (3, 3), (2, 2), True, (1, 1)))
         cin = 64
         for s, (c, stride) in enumerate(STAGES):
