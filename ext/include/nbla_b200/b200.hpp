@@ -145,6 +145,11 @@ bool write_tracking_alive();
     (by any backend) makes it stale. */
 void fxp_tag_set(const Variable *v, float delta);
 float fxp_tag_get(const Variable *v); // 0 when untagged or stale
+/** The same tag with the int8 channel-last codes of the tensor (nb200_fixed_point_quantize_nhwc_codes_f32),
+    which the quantizer wrote in the pass that made it; a convolution that finds them does not convert the
+    fp32 values again. The codes live as long as the tag (until the array is written or tagged again). */
+void fxp_tag_set(const Variable *v, float delta, const NdArrayPtr &codes);
+NdArrayPtr fxp_tag_codes(const Variable *v); // nullptr when untagged, stale or tagged without codes
 
 } // namespace nbla
 #endif

@@ -303,20 +303,32 @@ namespace {
 struct FxpTag {
   DataStamp stamp;
   float delta;
+  NdArrayPtr codes;
 };
 std::mutex g_tag_mutex;
 std::unordered_map<const SyncedArray *, FxpTag> g_tags;
 } // namespace
 
-void fxp_tag_set(const Variable *v, float delta) {
+void fxp_tag_set(const Variable *v, float delta, const NdArrayPtr &codes) {
   const DataStamp s = data_stamp(v);
   std::lock_guard<std::mutex> lock(g_tag_mutex);
   if (g_tags.size() > 4096)
     g_tags.clear(); // tags of arrays long gone; the live ones are set again by their next forward
   if (s.valid)
-    g_tags[s.array] = FxpTag{s, delta};
+    g_tags[s.array] = FxpTag{s, delta, codes};
   else
     g_tags.erase(s.array);
+}
+
+void fxp_tag_set(const Variable *v, float delta) { fxp_tag_set(v, delta, nullptr); }
+
+NdArrayPtr fxp_tag_codes(const Variable *v) {
+  const DataStamp s = data_stamp(v);
+  std::lock_guard<std::mutex> lock(g_tag_mutex);
+  auto it = g_tags.find(s.array);
+  if (it == g_tags.end() || it->second.stamp != s)
+    return nullptr;
+  return it->second.codes;
 }
 
 float fxp_tag_get(const Variable *v) {

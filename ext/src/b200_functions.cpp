@@ -186,9 +186,24 @@ protected:
     B200_ENTER(st);
     const float *x = rd(in[0], this->ctx_);
     float *y = wr(out[0], this->ctx_);
+    const bool small_codes = (this->sign_ ? this->n_ - 1 : this->n_) <= 7;
+    const Shape_t shape = in[0]->shape();
+    // [N, C, H, W] with planes of a multiple of 4 values: the same pass leaves the int8 channel-last codes that the
+    // convolution behind this quantizer reads (its weights are kept prepared, so the codes always save it a pass)
+    if (small_codes && shape.size() == 4 && (shape[2] * shape[3]) % 4 == 0 && shape[0] > 0 && shape[0] <= 65535 &&
+        in[0]->size() >= (1 << 16) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+      const int64_t slots = nb200_codes_nhwc_slots(shape[1], 1);
+      NdArrayPtr codes = make_shared<NdArray>(Shape_t{shape[0] * shape[2] * shape[3] * slots});
+      int8_t *c = codes->cast(dtypes::BYTE, this->ctx_, true)->template pointer<int8_t>();
+      nb200_check(nb200_fixed_point_quantize_nhwc_codes_f32(x, y, c, shape[0], shape[1], shape[2] * shape[3], this->sign_,
+                                                            this->n_, this->delta_, st),
+                  "FixedPointQuantize (with codes)");
+      fxp_tag_set(out[0], this->delta_, codes);
+      return;
+    }
     nb200_check(nb200_fixed_point_quantize_f32(x, y, in[0]->size(), this->sign_, this->n_, this->delta_, st),
                 "FixedPointQuantize");
-    if ((this->sign_ ? this->n_ - 1 : this->n_) <= 7)
+    if (small_codes)
       fxp_tag_set(out[0], this->delta_);
   }
   // fixed_point_quantize.cpp:103-127
@@ -586,11 +601,23 @@ protected:
       const int8_t *side = side_->get(dtypes::BYTE, this->ctx_)->template const_pointer<int8_t>();
       const float *alpha = rd(in[3], this->ctx_);
       const int64_t slots = nb200_codes_nhwc_slots(d_.C, this->group_);
-      NdArray codes(Shape_t{(int64_t)d_.batch * d_.H * d_.W * slots});
-      int8_t *xc = codes.cast(dtypes::BYTE, this->ctx_, true)->template pointer<int8_t>();
+      const int64_t n_codes = (int64_t)d_.batch * d_.H * d_.W * slots;
+      // the quantizer that made the input may have left its codes (one group, this very layout)
+      NdArrayPtr left = this->group_ == 1 ? fxp_tag_codes(in[0]) : nullptr;
+      if (left && left->size() != n_codes)
+        left = nullptr;
+      NdArray codes(Shape_t{left ? 1 : n_codes});
+      const int8_t *xc;
+      if (left) {
+        b200_count("activation_codes_from_quantizer");
+        xc = left->get(dtypes::BYTE, this->ctx_)->template const_pointer<int8_t>();
+      } else {
+        int8_t *fresh = codes.cast(dtypes::BYTE, this->ctx_, true)->template pointer<int8_t>();
+        nb200_check(nb200_fixed_point_codes_nhwc(x, fresh, d_.batch, d_.C, (int64_t)d_.H * d_.W, this->group_, delta, st),
+                    "BinaryWeightConvolution (activation codes)");
+        xc = fresh;
+      }
       float *y = wr(out[0], this->ctx_);
-      nb200_check(nb200_fixed_point_codes_nhwc(x, xc, d_.batch, d_.C, (int64_t)d_.H * d_.W, this->group_, delta, st),
-                  "BinaryWeightConvolution (activation codes)");
       nb200_check(nb200_binary_convolution_codes_prepared_f32(
                       xc, side, alpha, b, y, d_.batch, d_.C, d_.H, d_.W, d_.Ko, d_.kh, d_.kw, this->pad_[0],
                       this->pad_[1], this->stride_[0], this->stride_[1], this->dilation_[0], this->dilation_[1],
