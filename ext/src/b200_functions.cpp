@@ -191,7 +191,7 @@ protected:
     // [N, C, H, W] with planes of a multiple of 4 values: the same pass leaves the int8 channel-last codes that the
     // convolution behind this quantizer reads (its weights are kept prepared, so the codes always save it a pass)
     if (small_codes && shape.size() == 4 && (shape[2] * shape[3]) % 4 == 0 && shape[0] > 0 && shape[0] <= 65535 &&
-        in[0]->size() >= (1 << 16) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
+        in[0]->size() >= (1 << 12) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0) {
       const int64_t slots = nb200_codes_nhwc_slots(shape[1], 1);
       NdArrayPtr codes = make_shared<NdArray>(Shape_t{shape[0] * shape[2] * shape[3] * slots});
       int8_t *c = codes->cast(dtypes::BYTE, this->ctx_, true)->template pointer<int8_t>();

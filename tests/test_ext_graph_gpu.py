@@ -42,6 +42,8 @@ def test_resnet18_graph_on_b200_context_small():
             # every binary-weight convolution saw the fixed-point tag of its input and took the int8 path
             assert nbla_graph.counter("int8_convolutions") == 19 and nbla_graph.counter("bf16_convolutions") == 0
             assert nbla_graph.counter("weight_cache_misses") == 19
+            # all but the first (whose input comes out of the max-pooling) read the codes their quantizer left
+            assert nbla_graph.counter("activation_codes_from_quantizer") == 18
             g.forward(y, clear_buffer=True)
             assert nbla_graph.counter("weight_cache_hits") == 19 and nbla_graph.counter("weight_cache_misses") == 19
             assert np.array_equal(g.data(y), logits[backend])
